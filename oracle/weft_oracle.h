@@ -1,0 +1,91 @@
+/* CPU oracle for the quantized matrix path -- TEST INFRASTRUCTURE ONLY.
+ *
+ * A plain-C restatement of the GGML-semantics algorithms that the reference
+ * (zzyu5/Weft) uses as its own correctness oracle.  Only tests/, the smoke
+ * check and the cpu_baseline leg of bench.py may load this library; the
+ * product (libweft_b200.so) never links or calls it.
+ *
+ * Parity status: PINNED.  Every function here is checked bit-for-bit against
+ * the reference's own GGML C compiled from its sources (oracle/_ref) on the
+ * reference harnesses' closed-form inputs and on seeded random inputs; the
+ * resulting golden vectors are committed under tests/golden/.
+ *
+ * Paths cited as "ggml/..." are under source/c/ggml/llama.cpp/ggml/ of the
+ * reference; "examples/..." are under the reference root.
+ */
+#ifndef WEFT_ORACLE_H
+#define WEFT_ORACLE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Format ids: the numbering of the reference harnesses
+ * (examples/repro/weft/vec_dot_runtime.cpp:185-344); 100 is local (Q8_K). */
+enum wo_format {
+    WO_Q4_0 = 1,
+    WO_Q8_0 = 5,
+    WO_Q4_K = 8,
+    WO_IQ2_XXS = 15,
+    WO_TQ1_0 = 20,
+    WO_Q8_K = 100
+};
+
+/* record geometry (ggml/src/ggml-common.h:184-189,241-246,266-271,317-328,361-366,371-375) */
+size_t wo_record_bytes(int fmt);
+size_t wo_record_elements(int fmt);
+size_t wo_row_bytes(int fmt, int64_t k);
+
+float wo_f16_to_f32(uint16_t h);
+uint16_t wo_f32_to_f16(float f);
+
+/* weight quantizers (inputs for the tests; IQ2_XXS has none here, see weft_oracle.c) */
+void wo_quantize_row_q4_0(const float *x, uint8_t *y, int64_t k);
+void wo_quantize_row_q4_K(const float *x, uint8_t *y, int64_t k);
+void wo_quantize_row_tq1_0(const float *x, uint8_t *y, int64_t k);
+/* activation quantizers, GGML rule */
+void wo_quantize_row_q8_0(const float *x, uint8_t *y, int64_t k);
+void wo_quantize_row_q8_K(const float *x, uint8_t *y, int64_t k);
+/* activation quantizers, Weft DSL rule (differs from GGML only on exact ties) */
+void wo_quantize_row_q8_0_weft(const float *x, uint8_t *y, int64_t k);
+void wo_quantize_row_q8_K_weft(const float *x, uint8_t *y, int64_t k);
+/* rows [0,nrows) of a row-major matrix, one thread per contiguous row range; rule: 0 = GGML, 1 = Weft (activations only) */
+int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrows, int64_t k);
+
+/* dequantizers; grid = int8[256*8], signs = int8[128*8] (+1/-1), the tables in kernel-argument form */
+void wo_dequantize_row_q4_0(const uint8_t *w, float *y, int64_t k);
+void wo_dequantize_row_q8_0(const uint8_t *w, float *y, int64_t k);
+void wo_dequantize_row_q4_K(const uint8_t *w, float *y, int64_t k);
+void wo_dequantize_row_iq2_xxs(const uint8_t *w, const int8_t *grid, const int8_t *signs, float *y, int64_t k);
+void wo_dequantize_row_tq1_0(const uint8_t *w, float *y, int64_t k);
+int wo_dequantize_rows(int fmt, const uint8_t *w, const int8_t *grid, const int8_t *signs,
+                       float *y, int64_t nrows, int64_t k);
+
+/* block dot products, one output */
+float wo_vec_dot_q4_0_q8_0(const uint8_t *w, const uint8_t *x, int64_t k);
+float wo_vec_dot_q8_0_q8_0(const uint8_t *w, const uint8_t *x, int64_t k);
+float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
+float wo_vec_dot_iq2_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k);
+float wo_vec_dot_tq1_0_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
+int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs,
+               int64_t k, float *out);
+
+/* Y[m, n] for n in [n0, n1): optional activation quantize into xq (rule as above),
+ * then the double loop over vec_dot, threads over weight rows. */
+int wo_mul_mat(int fmt, int rule, const uint8_t *w, const float *x, uint8_t *xq,
+               const int8_t *grid, const int8_t *signs, float *y,
+               int64_t n, int64_t k, int64_t m, int64_t n0, int64_t n1, int quantize_x);
+
+/* sign table in kernel-argument form, derived (7 index bits + even-parity bit) */
+void wo_iq2_sign_table(int8_t *signs /* [128*8] */);
+
+int wo_max_threads(void);
+void wo_set_threads(int n);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
