@@ -1,0 +1,448 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized matrix hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+Default workload (the configuration the headline metric is quoted on): Q4_K x Q8_K mul_mat decode on
+a Llama-3-8B-shaped layer, N = 14336, K = 4096, batch 1.  One step = one production_mul_mat_q4_k_decode
+call: quantize the fp32 activation row to Q8_K, then the GEMV over every weight row.  Metric:
+algorithmic bytes streamed per second (weights once + activation records + fp32 output).
+
+Inputs are synthetic and seeded: weights ~N(0, 0.02) quantized to Q4_K with the CPU oracle's
+quantize_row_q4_K restatement, activations ~N(0, 1).  Successive steps walk through several distinct
+copies of the weight matrix whose total size exceeds twice the L2, so every step streams from HBM.
+
+Prints ONE JSON line (rank 0).  With --impl reference the same workload runs on the host cores through
+the reference's own GGML C (oracle/_ref, compiled from the reference sources) or, where that is
+absent, this repository's C restatement of it.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (format, mode, N, K, M)
+    "q4_k_decode_14336x4096": ("Q4_K", "decode", 14336, 4096, 1),
+    "q4_k_decode_4096x4096": ("Q4_K", "decode", 4096, 4096, 1),
+    "q4_k_decode_4096x14336": ("Q4_K", "decode", 4096, 14336, 1),
+    "q4_0_decode_4096x4096": ("Q4_0", "decode", 4096, 4096, 1),
+    "iq2_xxs_decode_28672x8192": ("IQ2_XXS", "decode", 28672, 8192, 1),
+    "q4_k_prefill_14336x4096": ("Q4_K", "prefill", 14336, 4096, 512),
+    "q4_k_prefill_4096x4096": ("Q4_K", "prefill", 4096, 4096, 512),
+    "q4_k_prefill_4096x14336": ("Q4_K", "prefill", 4096, 14336, 512),
+    "tq1_0_prefill_28672x8192": ("TQ1_0", "prefill", 28672, 8192, 512),
+}
+DEFAULT_WORKLOAD = "q4_k_decode_14336x4096"
+L2_BYTES = 126 * 1024 * 1024
+SEED = 20240611
+
+
+def load_peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return json.loads(path.read_text()), "measured"
+        except ValueError:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+def algorithmic_bytes(fmt: str, n: int, k: int, m: int) -> int:
+    from weft_b200.formats import row_bytes
+
+    act = "Q8_0" if fmt in ("Q4_0", "Q8_0") else "Q8_K"
+    return n * row_bytes(fmt, k) + m * row_bytes(act, k) + 4 * m * n
+
+
+def make_inputs(fmt: str, n: int, k: int, m: int, seed: int):
+    """Seeded host inputs: packed weights (n, row_bytes) uint8, fp32 activations (m, k), codebook tables."""
+    import oracle
+
+    rng = np.random.default_rng(seed)
+    fid = oracle.FORMAT_IDS[fmt]
+    golden = np.load(ROOT / "tests" / "golden" / "golden.npz")
+    grid, signs = golden["iq2xxs_grid"], golden["iq2xxs_signs"]
+    base_rows = min(n, 1024)            # quantize 1024 distinct rows, rotate them to fill the matrix (timing is data-independent)
+    if fmt == "TQ1_0":
+        src = (rng.integers(-1, 2, size=(base_rows, k)) * np.float32(0.02)).astype(np.float32)
+        base = oracle.quantize(fid, src)
+    elif fmt == "IQ2_XXS":
+        if oracle.ref_available():
+            base_rows = min(n, 128)
+            base = oracle.ref_quantize_weights(fid, (rng.standard_normal((base_rows, k)) * 0.02).astype(np.float32))
+        else:
+            base = rng.integers(0, 256, size=(base_rows, k // 256, 66), dtype=np.uint8)
+            base[:, :, 0:2] = (np.abs(rng.standard_normal((base_rows, k // 256))) * 0.01 + 1e-3).astype(np.float16).view(np.uint8).reshape(base_rows, -1, 2)
+            base = base.reshape(base_rows, -1)
+    else:
+        base = oracle.quantize(fid, (rng.standard_normal((base_rows, k)) * 0.02).astype(np.float32))
+    reps = -(-n // base_rows)
+    w = np.concatenate([np.roll(base, s, axis=0) for s in range(reps)], axis=0)[:n]
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    return np.ascontiguousarray(w), x, grid, signs
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int) -> None:
+        self.device_index, self.proc, self.lines = device_index, None, []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                clocks.append(float(parts[1])); maxes.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max(maxes) if maxes else None,
+                "samples": len(clocks), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ CPU side (reference arm and cpu_baseline)
+
+def cpu_mul_mat_runner(fmt: str, n: int, k: int, m: int, w: np.ndarray, x: np.ndarray, grid, signs, threads: int):
+    """Returns (callable running one full mul_mat on the host cores, kind)."""
+    import oracle
+
+    fid = oracle.FORMAT_IDS[fmt]
+    act = oracle.ACTIVATION[fid]
+    xq = np.zeros((m, oracle.row_bytes(act, k)), dtype=np.uint8)
+    y = np.zeros((m, n), dtype=np.float32)
+    if oracle.ref_available():
+        lib = oracle.ref()
+        quant = lib.weft_ref_quantize_q8_0 if act == oracle.Q8_0 else lib.weft_ref_quantize_q8_K
+        pool = ThreadPoolExecutor(max_workers=threads)
+        bounds = [(n * t // threads, n * (t + 1) // threads) for t in range(threads)]
+        xp = x.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+        yp = y.ctypes.data_as(ctypes.POINTER(ctypes.c_float))
+
+        def run_reference() -> None:
+            for r in range(m):
+                quant(x[r].ctypes.data_as(ctypes.POINTER(ctypes.c_float)), xq[r].ctypes.data, k)
+            # ctypes drops the GIL during the call: the row ranges run on separate cores
+            list(pool.map(lambda b: lib.weft_ref_mul_mat(fid, w.ctypes.data, xp, xq.ctypes.data, yp, n, k, m, b[0], b[1], 0), bounds))
+
+        return run_reference, "reference"
+    oracle.port().wo_set_threads(threads)
+
+    def run_port() -> None:
+        oracle.mul_mat(fid, w, x, n, k, m, rule=0, grid=grid, signs=signs)
+
+    return run_port, "port"
+
+
+def reference_arm(args, fmt, mode, n, k, m) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import oracle
+
+    oracle.build(ref=True)
+    w, x, grid, signs = make_inputs(fmt, n, k, m, SEED)
+    threads = os.cpu_count() or 1
+    sample_m = m if mode == "decode" else min(m, 4)       # prefill on CPU: a bounded slice of the token rows
+    run, kind = cpu_mul_mat_runner(fmt, n, k, sample_m, w, x[:sample_m], grid, signs, threads)
+    for _ in range(max(1, min(args.warmup, 3))):
+        run()
+    times = []
+    budget = time.perf_counter() + 120.0
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+        if time.perf_counter() > budget:
+            break
+    per_step = sum(times) / len(times)
+    if mode == "decode":
+        metric, unit = "mul_mat_decode_algorithmic_gbps", "GB/s"
+        value = algorithmic_bytes(fmt, n, k, m) / per_step / 1e9
+    else:
+        metric, unit = "mul_mat_prefill_int8_tops", "TOP/s"
+        value = 2.0 * sample_m * n * k / per_step / 1e12
+    sample = f"{len(times)} x full {fmt} mul_mat N={n} K={k} M={sample_m}" + ("" if sample_m == m else f" (of M={m})")
+    line = {
+        "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": len(times),
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3 * (m / sample_m), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "format": fmt, "mode": mode, "N": n, "K": k, "M": m,
+                   "cpu": oracle.cpu_model(), "code": "reference GGML C (oracle/_ref)" if kind == "reference" else "C restatement (oracle port)"},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------ GPU side
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=10)
+    parser.add_argument("--impl", default="weft_b200", choices=["weft_b200", "reference"])
+    parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3)
+    fmt, mode, n, k, m = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        reference_arm(args, fmt, mode, n, k, m)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from weft_b200.formats import FORMAT_IDS, TQ1_POWERS, row_bytes
+    from weft_b200.runtime.driver import Toolchain, last_error, load_library
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    lib = load_library(Toolchain().resolve().compiler)
+    if lib.weft_b200_init(local_rank):
+        raise SystemExit("weft_b200_init failed: " + last_error(lib))
+    stream = torch.cuda.current_stream()
+    lib.weft_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
+    lib.weft_b200_set_async(1)
+
+    def check(status: int) -> None:
+        if status:
+            raise SystemExit("weft_b200 call failed: " + last_error(lib))
+
+    # ---- inputs, sharded by weight rows
+    act = "Q8_0" if fmt in ("Q4_0", "Q8_0") else "Q8_K"
+    w_host, x_host, grid, signs = make_inputs(fmt, n, k, m, SEED)
+    n0, n1 = n * rank // world, n * (rank + 1) // world
+    n_local = n1 - n0
+    shard = w_host[n0:n1]
+    copies = max(2, -(-2 * L2_BYTES // max(1, shard.nbytes)) + 1)
+    copies = min(copies, 64)
+    w_dev = [torch.from_numpy(shard).cuda() if c == 0 else None for c in range(copies)]
+    for c in range(1, copies):
+        w_dev[c] = w_dev[0].clone()
+    x_dev = torch.from_numpy(x_host).cuda()
+    xq_dev = torch.zeros((m, row_bytes(act, k)), dtype=torch.uint8, device="cuda")
+    y_dev = torch.zeros((m, n), device="cuda")
+    grid_dev = torch.from_numpy(grid).cuda()
+    signs_dev = torch.from_numpy(signs).cuda()
+    powers_dev = torch.tensor(TQ1_POWERS, dtype=torch.int32, device="cuda")
+    fid = FORMAT_IDS[fmt]
+    mode_id = 0 if mode == "decode" else 1
+    shard_fn = lib.weft_b200_mul_mat_shard
+    shard_fn.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_size_t] * 4 + [ctypes.c_uint]
+    gathered = torch.zeros((world, m, n_local), device="cuda") if world > 1 else None
+    y_local = torch.zeros((m, n_local), device="cuda") if world > 1 else None
+
+    def step(i: int, flags: int = 0) -> None:
+        wbuf = w_dev[i % copies]
+        if world == 1:
+            check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
+                           powers_dev.data_ptr(), y_dev.data_ptr(), n_local, k, m, n, flags))
+        else:
+            check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
+                           powers_dev.data_ptr(), y_local.data_ptr(), n_local, k, m, n_local, flags))
+            dist.all_gather_into_tensor(gathered, y_local)
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- parity spot check before timing (one step against the oracle, rank-local columns)
+    step(0)
+    torch.cuda.synchronize()
+    check(lib.weft_b200_synchronize())
+    got = (y_dev[:, n0:n1] if world == 1 else y_local).cpu().numpy()
+    probe = min(n_local, 256)
+    want, _ = oracle.mul_mat(oracle.FORMAT_IDS[fmt], shard[:probe], x_host[: min(m, 4)], probe, k, min(m, 4), rule=1, grid=grid, signs=signs)
+    err = float(np.linalg.norm(got[: min(m, 4), :probe].astype(np.float64) - want) / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
+    if not err <= 1e-5:
+        raise SystemExit(f"parity check failed before timing: relative L2 {err}")
+
+    # ---- timed region: K steps on the device
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = lib.weft_b200_launch_count()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    begin.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    end.record()
+    barrier()
+    launches = int(lib.weft_b200_launch_count() - launches_before)
+    check(lib.weft_b200_synchronize())
+    elapsed_ms = begin.elapsed_time(end)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+        lt = torch.tensor([launches], device="cuda")
+        dist.all_reduce(lt)
+        launches = int(lt.item())
+    ms_per_step = elapsed_ms / args.steps
+
+    # ---- the dominant kernel alone (activations already quantized, no collective): average launch duration
+    def kernel_step(i: int) -> None:
+        out = y_dev if world == 1 else y_local
+        check(shard_fn(fid, mode_id, w_dev[i % copies].data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(),
+                       signs_dev.data_ptr(), powers_dev.data_ptr(), out.data_ptr(), n_local, k, m, n if world == 1 else n_local, 1))
+
+    for i in range(args.warmup):
+        kernel_step(i)
+    barrier()
+    begin.record()
+    for i in range(args.steps):
+        kernel_step(args.warmup + i)
+    end.record()
+    barrier()
+    kernel_ms = begin.elapsed_time(end) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the C ABI with host buffers (weights resident on the device)
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    xq_pin = torch.zeros((m, row_bytes(act, k)), dtype=torch.uint8).pin_memory()
+    y_pin = torch.zeros((m, n_local), dtype=torch.float32).pin_memory()
+    grid_pin, signs_pin = torch.from_numpy(grid).pin_memory(), torch.from_numpy(signs).pin_memory()
+    powers_pin = torch.tensor(TQ1_POWERS, dtype=torch.int32).pin_memory()
+
+    def e2e_step(i: int) -> None:
+        check(shard_fn(fid, mode_id, w_dev[i % copies].data_ptr(), x_pin.data_ptr(), xq_pin.data_ptr(), grid_pin.data_ptr(),
+                       signs_pin.data_ptr(), powers_pin.data_ptr(), y_pin.data_ptr(), n_local, k, m, n_local, 0))
+
+    e2e_steps = max(3, min(args.steps, 200))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        e2e_step(3 + i)
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_err = float(np.abs(y_pin.numpy()[: min(m, 4), :probe] - got[: min(m, 4), :probe]).max())
+    if e2e_err != 0.0:
+        raise SystemExit(f"host-buffer path disagrees with the device-buffer path by {e2e_err}")
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peaks_kind = load_peaks()
+    total_bytes = algorithmic_bytes(fmt, n, k, m)
+    if mode == "decode":
+        metric, unit = "mul_mat_decode_algorithmic_gbps", "GB/s"
+        value = total_bytes / (ms_per_step * 1e-3) / 1e9
+        e2e_value = total_bytes / e2e_s / 1e9
+        shard_bytes = algorithmic_bytes(fmt, n_local, k, m)
+        achieved = shard_bytes / (kernel_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                "traffic": None, "peak_source": peaks_kind, "kernel": "gemv_kernel (per GPU)", "kernel_ms": kernel_ms,
+                "algorithmic_bytes_per_launch": shard_bytes}
+        dtype = "int8 dot (dp4a), f32 accumulate"
+    else:
+        metric, unit = "mul_mat_prefill_int8_tops", "TOP/s"
+        ops = 2.0 * m * n * k
+        value = ops / (ms_per_step * 1e-3) / 1e12
+        e2e_value = ops / e2e_s / 1e12
+        achieved = 2.0 * m * n_local * k / (kernel_ms * 1e-3) / 1e12
+        peak = 2.0 * peaks["bf16_tflops"]
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": None,
+                "peak_source": peaks_kind + " bf16 dense x2 (no int8 entry in MEASURED_PEAKS.json)", "kernel": "prefill kernel (per GPU)",
+                "kernel_ms": kernel_ms}
+        dtype = "int8 tensor-core MMA, i32/f32 accumulate"
+
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype,
+        "data": "synthetic",
+        "config": {"workload": args.workload, "format": fmt, "mode": mode, "N": n, "K": k, "M": m,
+                   "sharding": f"weight rows split {world} ways, fp32 outputs all-gathered (NCCL)" if world > 1 else "none",
+                   "l2": f"steps rotate over {copies} weight copies ({copies * shard.nbytes / 2**20:.0f} MiB per GPU > 2 x L2)",
+                   "timed_scope": "activation quantize + mul_mat" + (" + all-gather" if world > 1 else ""), "seed": SEED,
+                   "parity_rel_l2_before_timing": err},
+        "roofline": roof, "clocks": clocks, "gpu_launches": launches,
+        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(x_pin.numel() * 4),
+                "d2h_bytes_per_step": int(y_pin.numel() * 4 + xq_pin.numel()), "ms_per_step": e2e_s * 1e3,
+                "what": "weft_b200_mul_mat_shard with host X/Xq/Y (pinned), weights resident in HBM"},
+    }
+    if not args.no_cpu_baseline and world == 1:
+        threads = os.cpu_count() or 1
+        sample_m = m if mode == "decode" else min(m, 2)
+        run, kind = cpu_mul_mat_runner(fmt, n, k, sample_m, w_host, x_host[:sample_m], grid, signs, threads)
+        run()
+        times, t_end = [], time.perf_counter() + 12.0
+        while time.perf_counter() < t_end and len(times) < 200:
+            t0 = time.perf_counter(); run(); times.append(time.perf_counter() - t0)
+        per = sum(times) / len(times)
+        cpu_value = (algorithmic_bytes(fmt, n, k, m) / per / 1e9) if mode == "decode" else (2.0 * sample_m * n * k / per / 1e12)
+        line["cpu_baseline"] = {"value": cpu_value, "unit": unit, "cores": threads, "kind": kind,
+                                "sample": f"{len(times)} x full mul_mat N={n} K={k} M={sample_m}" + ("" if sample_m == m else f" of M={m}"),
+                                "cpu": oracle.cpu_model(), "ms_per_step": per * 1e3 * (m / sample_m)}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,135 @@
+/* weft_b200 -- C ABI of the B200 (sm_100a) quantized matrix path.
+ *
+ * Every kernel symbol below carries the name, pointer order and trailing size_t dimension order of
+ * the C function the reference compiler emits for the same @weft.kernel definition (one function per
+ * kernel: pointers in signature order, then every unbound shape symbol as size_t in first-appearance
+ * order -- lib/Target/Emission/Emitter.h:205-229,491-512), so the reference's FFI
+ * (python/weft/runtime/compiler.py:91-97,154: argtypes = void* x nargs + size_t x ndims) binds them
+ * unchanged.  Two differences, both additive:
+ *   - the reference functions return void; these return int (0 = ok, non-zero = error, message from
+ *     weft_b200_last_error()).  A caller that ignores the return value sees the reference behaviour.
+ *   - every pointer may be a device pointer or a host pointer.  Device pointers are used in place.
+ *     Host pointers are staged through stream-ordered device memory inside the call (inputs copied
+ *     in, written arguments copied back) -- the literal drop-in for the reference's host-memory
+ *     callers.  Host weights registered with weft_b200_weights_resident() are uploaded once and
+ *     found again by address, so only activations and outputs move per call.
+ *
+ * Records are the GGML block formats, never repacked: Q4_0 18 B/32, Q8_0 34 B/32, Q4_K 144 B/256,
+ * Q8_K 292 B/256, IQ2_XXS 66 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
+ * device-pointer arguments: Xq is the caller's written workspace, as in the reference.
+ * IQ2_XXS tables arrive as arguments: grid int8[256][8], signs int8[128][8] with entries +1 / -1.
+ * TQ1_0 takes powers uint32[5] = {1, 3, 9, 27, 81}.
+ *
+ * Calls are synchronous by default (they return after the work has finished, like the reference's
+ * blocking C call).  weft_b200_set_stream / weft_b200_set_async let a caller that owns a CUDA stream
+ * enqueue without waiting.
+ */
+#ifndef WEFT_B200_H
+#define WEFT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ library control (no reference counterpart) */
+
+const char *weft_b200_last_error(void);              /* message of the calling thread's last failure */
+int weft_b200_init(int device);                      /* select the device (default: current); idempotent */
+int weft_b200_device_info(int *cc_major, int *cc_minor, int *sm_count, size_t *total_bytes, char *name, size_t name_len);
+int weft_b200_set_stream(void *cuda_stream);         /* NULL = the library's own stream */
+int weft_b200_set_async(int enabled);                /* 1: device-pointer calls return after enqueue */
+int weft_b200_synchronize(void);                     /* wait for the stream and report device-side status */
+unsigned long long weft_b200_launch_count(void);     /* kernels launched by this library so far */
+/* Keep a device copy of a host weight buffer; later calls that receive an address inside
+ * [host, host+bytes) use the copy.  The host bytes must not change while registered. */
+int weft_b200_weights_resident(const void *host, size_t bytes);
+int weft_b200_weights_release(const void *host);
+
+/* ------------------------------------------------------------------ quantized_vec_dot: one row x one activation row -> Y[1]
+ * examples/kernels/vec_dot/q4_0_q8_0.py:18-23      harness binding examples/repro/weft/vec_dot_runtime.cpp:191 */
+int quantized_vec_dot_q4_0_q8_0(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
+/* examples/kernels/vec_dot/q8_0_q8_0.py:17-22      vec_dot_runtime.cpp:223 */
+int quantized_vec_dot_q8_0_q8_0(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
+/* examples/kernels/vec_dot/q4_k_q8_k.py:31-36      vec_dot_runtime.cpp:247 */
+int quantized_vec_dot_q4_k_q8_k(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
+/* examples/kernels/vec_dot/iq2_xxs_q8_k.py:45-54   vec_dot_runtime.cpp:303 */
+int quantized_vec_dot_iq2_xxs_q8_k(const uint8_t *W, const uint8_t *X, const int8_t *grid, const int8_t *signs, float *Y, size_t K);
+/* examples/kernels/vec_dot/tq1_0_q8_k.py:47-55     vec_dot_runtime.cpp:343 */
+int quantized_vec_dot_tq1_0_q8_k(const uint8_t *W, const uint8_t *X, const uint32_t *powers, float *Y, size_t K);
+
+/* ------------------------------------------------------------------ row_dequantize: one row of K elements -> fp32
+ * examples/kernels/dequantize/q4_0.py:9-13, q8_0.py:9-13, q4_k.py:9-20   examples/repro/weft/row_dequantize_runtime.cpp:177,197,212 */
+int row_dequantize_q4_0(const uint8_t *W, float *Y, size_t K);
+int row_dequantize_q8_0(const uint8_t *W, float *Y, size_t K);
+int row_dequantize_q4_k(const uint8_t *W, float *Y, size_t K);
+/* examples/kernels/dequantize/iq2_xxs.py:9-53; grid int8[2048], signs int8[1024]   row_dequantize_runtime.cpp:247 */
+int row_dequantize_iq2_xxs(const uint8_t *W, const int8_t *grid, const int8_t *signs, float *Y, size_t K);
+/* examples/kernels/dequantize/tq1_0.py:9-46        row_dequantize_runtime.cpp:272 */
+int row_dequantize_tq1_0(const uint8_t *W, const uint32_t *powers, float *Y, size_t K);
+
+/* ------------------------------------------------------------------ activation quantizers, one row
+ * examples/kernels/quantize/q8_0.py:20-23, q8_k.py:32-35   examples/repro/weft/q8_quantize_runtime.cpp:25-26 */
+int q8_0_quantize(const float *X, uint8_t *Y, size_t K);
+int q8_K_quantize(const float *X, uint8_t *Y, size_t K);
+
+/* ------------------------------------------------------------------ production_mul_mat, decode form (GEMV per activation row)
+ * W (N,K) records, X (M,K) fp32, Xq (M,K) activation records (written), Y (M,N) fp32 (written).
+ * examples/kernels/mul_mat/q4_0_decode.py:10-20, q8_0_decode.py, q4_k_decode.py:10-20
+ * examples/repro/weft/mul_mat_runtime.cpp:217-221,277-281,332-336 */
+int production_mul_mat_q4_0_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_q8_0_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_q4_k_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/iq2_xxs_decode.py:10-23   mul_mat_runtime.cpp:458-473 */
+int production_mul_mat_iq2_xxs_decode(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, const int8_t *signs,
+                                      float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/tq1_0_decode.py:10-21     mul_mat_runtime.cpp:534-538 */
+int production_mul_mat_tq1_0_decode(const uint8_t *W, const float *X, uint8_t *Xq, const uint32_t *powers,
+                                    float *Y, size_t N, size_t K, size_t M);
+
+/* ------------------------------------------------------------------ production_mul_mat, prefill form (tiled contraction)
+ * Same arguments.  The reference binds its tile sizes (NC/MC/MR/NR/KC) at compile time
+ * (Emitter.h:505-510), so they are not C parameters here either.
+ * examples/kernels/mul_mat/q4_0.py:9-30, q8_0.py:9-29, q4_k_staged.py:9-37   mul_mat_runtime.cpp:217-221,277-281,350-357 */
+int production_mul_mat_q4_0(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_q8_0(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_q4_k_staged(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/tq1_0.py:10-64            mul_mat_runtime.cpp:534-538 */
+int production_mul_mat_tq1_0(const uint8_t *W, const float *X, uint8_t *Xq, const uint32_t *powers,
+                             float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/iq2_xxs_staged.py:9-97    mul_mat_runtime.cpp:458-473 */
+int production_mul_mat_iq2_xxs_staged(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, const int8_t *signs,
+                                      float *Y, size_t N, size_t K, size_t M);
+
+/* ------------------------------------------------------------------ whole-matrix forms (no reference counterpart)
+ * The reference's standalone symbols above take one row and its harness loops rows on the host
+ * (vec_dot_runtime.cpp:468-475, row_dequantize_runtime.cpp:433-438).  One launch per row is
+ * meaningless on a GPU, so the same kernels are also exported over (N,K) views. */
+int row_dequantize_q4_0_rows(const uint8_t *W, float *Y, size_t N, size_t K);
+int row_dequantize_q8_0_rows(const uint8_t *W, float *Y, size_t N, size_t K);
+int row_dequantize_q4_k_rows(const uint8_t *W, float *Y, size_t N, size_t K);
+int row_dequantize_iq2_xxs_rows(const uint8_t *W, const int8_t *grid, const int8_t *signs, float *Y, size_t N, size_t K);
+int row_dequantize_tq1_0_rows(const uint8_t *W, const uint32_t *powers, float *Y, size_t N, size_t K);
+/* Y[n] = vec_dot(W[n], X) for n < N; X one row of activation records */
+int quantized_vec_dot_q4_0_q8_0_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
+int quantized_vec_dot_q8_0_q8_0_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
+int quantized_vec_dot_q4_k_q8_k_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
+int quantized_vec_dot_iq2_xxs_q8_k_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, const int8_t *signs, float *Y, size_t N, size_t K);
+int quantized_vec_dot_tq1_0_q8_k_rows(const uint8_t *W, const uint8_t *X, const uint32_t *powers, float *Y, size_t N, size_t K);
+int q8_0_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
+int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
+
+/* Row-sharded mul_mat: this process holds weight rows [n0, n0+N_local) of an (N,K) matrix and writes
+ * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 8 Q4_K, 15 IQ2_XXS,
+ * 20 TQ1_0 (the reference harness numbering).  mode: 0 decode (GEMV), 1 prefill (tensor cores).
+ * flags bit 0: Xq already holds the quantized activations (X may be NULL). */
+int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
+                            const int8_t *grid, const int8_t *signs, const uint32_t *powers,
+                            float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WEFT_B200_H */

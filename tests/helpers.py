@@ -1,0 +1,52 @@
+"""Shared input builders for the parity tests (test infrastructure)."""
+from __future__ import annotations
+
+import numpy as np
+
+import oracle as o
+
+TQ1_POWERS = np.array([1, 3, 9, 27, 81], dtype=np.uint32)
+
+
+def rel_l2(got: np.ndarray, want: np.ndarray) -> float:
+    got64, want64 = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    denom = np.linalg.norm(want64)
+    return float(np.linalg.norm(got64 - want64) / denom) if denom else float(np.linalg.norm(got64))
+
+
+def reference_tolerance_ok(got: np.ndarray, want: np.ndarray) -> bool:
+    """|a - e| <= 1e-4 + 2e-3 |e| and finite: the reference harnesses' bound (vec_dot_runtime.cpp:23-38)."""
+    got, want = np.asarray(got, dtype=np.float64), np.asarray(want, dtype=np.float64)
+    return bool(np.isfinite(got).all() and (np.abs(got - want) <= 1e-4 + 2e-3 * np.abs(want)).all())
+
+
+def random_iq2_xxs(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
+    """Random but valid IQ2_XXS records: any grid index, sign index and 4-bit scale is legal; d is a small f16."""
+    nb = k // 256
+    rec = rng.integers(0, 256, size=(n, nb, 66), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal((n, nb))) * 0.01 + 1e-3).astype(np.float16)
+    rec[:, :, 0:2] = d.view(np.uint8).reshape(n, nb, 2)
+    return rec.reshape(n, nb * 66)
+
+
+def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
+    """Seeded weights of the benchmark distributions, quantized: N(0, 0.02) (scale * {-1,0,+1} for TQ1_0).
+
+    IQ2_XXS goes through the compiled reference quantizer when it is present and falls back to
+    random valid records otherwise (the port has no IQ2_XXS quantizer)."""
+    if fmt == o.TQ1_0:
+        src = (rng.integers(-1, 2, size=(n, k)) * np.float32(0.02)).astype(np.float32)
+        return o.quantize(fmt, src)
+    if fmt == o.IQ2_XXS:
+        if o.ref_available() and n * k <= 1 << 22:
+            return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        return random_iq2_xxs(rng, n, k)
+    return o.quantize(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+
+
+def activations(rng: np.random.Generator, m: int, k: int) -> np.ndarray:
+    return rng.standard_normal((m, k)).astype(np.float32)
+
+
+def tables(golden: dict):
+    return golden["iq2xxs_grid"], golden["iq2xxs_signs"]

@@ -1,0 +1,363 @@
+// extern "C" surface of libweft_b200.so (declared in include/weft_b200.h).
+//
+// Host logic only: argument checks, host/device pointer handling, stream and status plumbing.
+// All arithmetic happens in the kernels behind launch_*; there is no CPU fallback -- a missing or
+// unusable GPU is an error.
+#include "../../include/weft_b200.h"
+
+#include "common.cuh"
+#include "kernels.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <vector>
+
+using namespace weft;
+
+namespace {
+
+thread_local char t_error[512] = "";
+
+int fail(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_error, sizeof(t_error), fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+struct Resident { void *device; size_t bytes; };
+
+struct State {
+    std::recursive_mutex lock;
+    bool ready = false;
+    int device = -1;
+    cudaDeviceProp prop{};
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    bool async = false;
+    int *status_host = nullptr;   // mapped, pinned: the kernels write here only on failure
+    int *status_dev = nullptr;
+    unsigned long long launches = 0;
+    std::map<uintptr_t, Resident> resident;   // keyed by host base address
+};
+State g;
+
+#define CU(call)                                                                                   \
+    do {                                                                                           \
+        cudaError_t e_ = (call);                                                                   \
+        if (e_ != cudaSuccess) return fail("%s failed: %s", #call, cudaGetErrorString(e_));        \
+    } while (0)
+
+int ensure_init(int device) {
+    if (g.ready) {
+        if (device >= 0 && device != g.device) return fail("weft_b200 is already bound to device %d", g.device);
+        cudaSetDevice(g.device);
+        return 0;
+    }
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return fail("no CUDA device is available (%s); weft_b200 has no CPU fallback", cudaGetErrorString(e));
+    if (device < 0) { if (cudaGetDevice(&device) != cudaSuccess) device = 0; }
+    CU(cudaSetDevice(device));
+    CU(cudaGetDeviceProperties(&g.prop, device));
+    if (g.prop.major != 10)
+        return fail("device %d (%s) is compute capability %d.%d; this library carries sm_100a code only",
+                    device, g.prop.name, g.prop.major, g.prop.minor);
+    CU(cudaStreamCreateWithFlags(&g.own_stream, cudaStreamNonBlocking));
+    g.stream = g.own_stream;
+    CU(cudaHostAlloc(reinterpret_cast<void **>(&g.status_host), sizeof(int), cudaHostAllocMapped));
+    *g.status_host = 0;
+    CU(cudaHostGetDevicePointer(reinterpret_cast<void **>(&g.status_dev), g.status_host, 0));
+    g.device = device;
+    g.ready = true;
+    return 0;
+}
+
+int device_status() {
+    const int s = *g.status_host;
+    if (s == ST_OK) return 0;
+    *g.status_host = 0;
+    return fail("device-side failure: %s", s == ST_WAIT_TIMEOUT ? "a bounded wait on an asynchronous copy or MMA ran out"
+                                           : s == ST_TMEM_ALLOC ? "tensor memory allocation failed" : "unknown status");
+}
+
+// One argument of a call: where the caller's bytes live and where the kernel will find them.
+struct Arg {
+    const void *user = nullptr;
+    void *dev = nullptr;
+    size_t bytes = 0;
+    bool host = false, staged = false, written = false;
+};
+
+class Call {
+  public:
+    ~Call() {
+        for (Arg &a : args_)
+            if (a.staged && a.dev) cudaFreeAsync(a.dev, g.stream);
+    }
+    // Returns the device address for `ptr` (bytes long). read: copy in when host; written: copy back.
+    int map(const void *ptr, size_t bytes, bool read, bool written, void **out) {
+        *out = nullptr;
+        if (bytes == 0) { *out = const_cast<void *>(ptr); return 0; }
+        if (!ptr) return fail("a required buffer is NULL");
+        cudaPointerAttributes attr{};
+        cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
+        if (e != cudaSuccess) { cudaGetLastError(); attr.type = cudaMemoryTypeUnregistered; }
+        if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) {
+            if (attr.type == cudaMemoryTypeDevice && attr.device != g.device)
+                return fail("buffer lives on device %d, the library is bound to device %d", attr.device, g.device);
+            *out = const_cast<void *>(ptr);
+            return 0;
+        }
+        any_host_ = true;
+        if (!written) {   // registered resident weights: no copy
+            const uintptr_t a = reinterpret_cast<uintptr_t>(ptr);
+            auto it = g.resident.upper_bound(a);
+            if (it != g.resident.begin()) {
+                --it;
+                if (a >= it->first && a + bytes <= it->first + it->second.bytes) {
+                    *out = static_cast<uint8_t *>(it->second.device) + (a - it->first);
+                    return 0;
+                }
+            }
+        }
+        Arg arg;
+        arg.user = ptr; arg.bytes = bytes; arg.host = true; arg.staged = true; arg.written = written;
+        CU(cudaMallocAsync(&arg.dev, bytes, g.stream));
+        args_.push_back(arg);
+        if (read) CU(cudaMemcpyAsync(arg.dev, ptr, bytes, cudaMemcpyHostToDevice, g.stream));
+        *out = arg.dev;
+        return 0;
+    }
+    // Copy written host arguments back and decide whether to wait.
+    int finish() {
+        for (Arg &a : args_)
+            if (a.written) CU(cudaMemcpyAsync(const_cast<void *>(a.user), a.dev, a.bytes, cudaMemcpyDeviceToHost, g.stream));
+        if (any_host_ || !g.async) {
+            CU(cudaStreamSynchronize(g.stream));
+            return device_status();
+        }
+        return 0;
+    }
+
+  private:
+    std::vector<Arg> args_;
+    bool any_host_ = false;
+};
+
+size_t row_bytes(int fmt, size_t k) { return k / record_elements(fmt) * record_bytes(fmt); }
+
+int check_k(int fmt, size_t k) {
+    if (k % record_elements(fmt)) return fail("K = %zu does not contain complete %d-element records", k, record_elements(fmt));
+    return 0;
+}
+
+int launched(cudaError_t e, const char *what, unsigned count = 1) {
+    if (e != cudaSuccess) return fail("%s launch failed: %s", what, cudaGetErrorString(e));
+    g.launches += count;
+    return 0;
+}
+
+int do_dequantize(int fmt, const void *W, const int8_t *grid, const int8_t *signs, const uint32_t *powers, float *Y, size_t N, size_t K) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (check_k(fmt, K)) return 1;
+    Call call;
+    void *w, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
+    if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
+    if (fmt == F_IQ2_XXS && (call.map(grid, 2048, true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
+    if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
+    if (call.map(Y, N * K * sizeof(float), false, true, &y)) return 1;
+    if (launched(launch_dequantize(fmt, w, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw, (float *)y,
+                                   (long long)(N * K), g.prop.multiProcessorCount, g.stream), "row_dequantize"))
+        return 1;
+    return call.finish();
+}
+
+int do_quantize(int act, const float *X, uint8_t *Y, size_t M, size_t K) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (check_k(act, K)) return 1;
+    Call call;
+    void *x, *y;
+    if (call.map(X, M * K * sizeof(float), true, false, &x)) return 1;
+    if (call.map(Y, M * row_bytes(act, K), false, true, &y)) return 1;
+    if ((reinterpret_cast<uintptr_t>(y) & (act == F_Q8_K ? 3u : 1u)) || (reinterpret_cast<uintptr_t>(x) & 3u))
+        return fail("activation buffers do not meet their Encoding alignment");
+    if (launched(launch_quantize(act, (const float *)x, y, (long long)M, (long long)K, g.prop.multiProcessorCount, g.stream), "quantize"))
+        return 1;
+    return call.finish();
+}
+
+// mode 0: GEMV per activation row; mode 1: tensor-core contraction when the shape allows, else GEMV.
+int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const int8_t *grid, const int8_t *signs,
+               const uint32_t *powers, float *Y, size_t N, size_t K, size_t M, size_t ldy, unsigned flags, bool vec_dot_only) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    const int act = activation_of(fmt);
+    if (check_k(fmt, K) || check_k(act, K)) return 1;
+    if (K == 0 || N == 0 || M == 0) return 0;
+    if (ldy < N) return fail("Y row pitch %zu is smaller than N = %zu", ldy, N);
+    const bool have_xq = vec_dot_only || (flags & 1u);
+    Call call;
+    void *w, *x = nullptr, *xq, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
+    if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
+    if (!have_xq && call.map(X, M * K * sizeof(float), true, false, &x)) return 1;
+    if (call.map(Xq, M * row_bytes(act, K), have_xq, !have_xq, &xq)) return 1;
+    if (fmt == F_IQ2_XXS && (call.map(grid, 2048, true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
+    if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
+    // a host Y with a pitch is staged whole (pitch * M floats); device Y is written in place
+    const size_t y_floats = (M - 1) * ldy + N;
+    if (call.map(Y, y_floats * sizeof(float), ldy != N, true, &y)) return 1;
+    if ((reinterpret_cast<uintptr_t>(w) & 1u) || (reinterpret_cast<uintptr_t>(xq) & (act == F_Q8_K ? 3u : 1u)) ||
+        (reinterpret_cast<uintptr_t>(y) & 3u) || (x && (reinterpret_cast<uintptr_t>(x) & 3u)))
+        return fail("a buffer does not meet its Encoding alignment");
+    const int sms = g.prop.multiProcessorCount;
+    if (!have_xq && launched(launch_quantize(act, (const float *)x, xq, (long long)M, (long long)K, sms, g.stream), "activation quantize"))
+        return 1;
+    bool done = false;
+    if (mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq)) {
+        PrefillArgs pa{fmt, w, xq, (const uint32_t *)pw, (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
+        if (launched(launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
+        done = true;
+    }
+    if (!done) {
+        GemvArgs ga{fmt, w, xq, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw, (float *)y,
+                    (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
+        if (launched(launch_gemv(ga, sms, g.stream), "decode mul_mat")) return 1;
+    }
+    return call.finish();
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *weft_b200_last_error(void) { return t_error; }
+
+int weft_b200_init(int device) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    return ensure_init(device);
+}
+
+int weft_b200_device_info(int *cc_major, int *cc_minor, int *sm_count, size_t *total_bytes, char *name, size_t name_len) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (cc_major) *cc_major = g.prop.major;
+    if (cc_minor) *cc_minor = g.prop.minor;
+    if (sm_count) *sm_count = g.prop.multiProcessorCount;
+    if (total_bytes) *total_bytes = g.prop.totalGlobalMem;
+    if (name && name_len) { strncpy(name, g.prop.name, name_len - 1); name[name_len - 1] = 0; }
+    return 0;
+}
+
+int weft_b200_set_stream(void *cuda_stream) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    g.stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : g.own_stream;
+    return 0;
+}
+
+int weft_b200_set_async(int enabled) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    g.async = enabled != 0;
+    return 0;
+}
+
+int weft_b200_synchronize(void) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    CU(cudaStreamSynchronize(g.stream));
+    return device_status();
+}
+
+unsigned long long weft_b200_launch_count(void) { return g.launches; }
+
+int weft_b200_weights_resident(const void *host, size_t bytes) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (!host || !bytes) return fail("weights_resident needs a buffer");
+    const uintptr_t a = reinterpret_cast<uintptr_t>(host);
+    if (g.resident.count(a)) return fail("this host buffer is already resident");
+    Resident r{nullptr, bytes};
+    CU(cudaMalloc(&r.device, bytes));
+    cudaError_t e = cudaMemcpy(r.device, host, bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) { cudaFree(r.device); return fail("upload failed: %s", cudaGetErrorString(e)); }
+    g.resident[a] = r;
+    return 0;
+}
+
+int weft_b200_weights_release(const void *host) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    auto it = g.resident.find(reinterpret_cast<uintptr_t>(host));
+    if (it == g.resident.end()) return fail("this host buffer is not resident");
+    cudaStreamSynchronize(g.stream);
+    cudaFree(it->second.device);
+    g.resident.erase(it);
+    return 0;
+}
+
+// ---- vec_dot
+#define VEC_DOT(name, fmt, TABLE_PARAMS, GRID, SIGNS, POWERS)                                                          \
+    int name(const uint8_t *W, const uint8_t *X TABLE_PARAMS, float *Y, size_t K) {                                   \
+        return do_mul_mat(fmt, 0, W, nullptr, const_cast<uint8_t *>(X), GRID, SIGNS, POWERS, Y, 1, K, 1, 1, 0, true); \
+    }                                                                                                                  \
+    int name##_rows(const uint8_t *W, const uint8_t *X TABLE_PARAMS, float *Y, size_t N, size_t K) {                  \
+        return do_mul_mat(fmt, 0, W, nullptr, const_cast<uint8_t *>(X), GRID, SIGNS, POWERS, Y, N, K, 1, N, 0, true); \
+    }
+#define NO_TABLES
+#define IQ_TABLES , const int8_t *grid, const int8_t *signs
+#define TQ_TABLES , const uint32_t *powers
+VEC_DOT(quantized_vec_dot_q4_0_q8_0, F_Q4_0, NO_TABLES, nullptr, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_q8_0_q8_0, F_Q8_0, NO_TABLES, nullptr, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_q4_k_q8_k, F_Q4_K, NO_TABLES, nullptr, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_iq2_xxs_q8_k, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
+VEC_DOT(quantized_vec_dot_tq1_0_q8_k, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
+
+// ---- dequantize
+#define DEQUANT(name, fmt, TABLE_PARAMS, GRID, SIGNS, POWERS)                                                          \
+    int name(const uint8_t *W TABLE_PARAMS, float *Y, size_t K) { return do_dequantize(fmt, W, GRID, SIGNS, POWERS, Y, 1, K); } \
+    int name##_rows(const uint8_t *W TABLE_PARAMS, float *Y, size_t N, size_t K) { return do_dequantize(fmt, W, GRID, SIGNS, POWERS, Y, N, K); }
+DEQUANT(row_dequantize_q4_0, F_Q4_0, NO_TABLES, nullptr, nullptr, nullptr)
+DEQUANT(row_dequantize_q8_0, F_Q8_0, NO_TABLES, nullptr, nullptr, nullptr)
+DEQUANT(row_dequantize_q4_k, F_Q4_K, NO_TABLES, nullptr, nullptr, nullptr)
+DEQUANT(row_dequantize_iq2_xxs, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
+DEQUANT(row_dequantize_tq1_0, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
+
+// ---- quantize
+int q8_0_quantize(const float *X, uint8_t *Y, size_t K) { return do_quantize(F_Q8_0, X, Y, 1, K); }
+int q8_K_quantize(const float *X, uint8_t *Y, size_t K) { return do_quantize(F_Q8_K, X, Y, 1, K); }
+int q8_0_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K) { return do_quantize(F_Q8_0, X, Y, M, K); }
+int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K) { return do_quantize(F_Q8_K, X, Y, M, K); }
+
+// ---- mul_mat
+#define MUL_MAT(name, fmt, mode, TABLE_PARAMS, GRID, SIGNS, POWERS)                                                    \
+    int name(const uint8_t *W, const float *X, uint8_t *Xq TABLE_PARAMS, float *Y, size_t N, size_t K, size_t M) {    \
+        return do_mul_mat(fmt, mode, W, X, Xq, GRID, SIGNS, POWERS, Y, N, K, M, N, 0, false);                         \
+    }
+MUL_MAT(production_mul_mat_q4_0_decode, F_Q4_0, 0, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q8_0_decode, F_Q8_0, 0, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q4_k_decode, F_Q4_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_iq2_xxs_decode, F_IQ2_XXS, 0, IQ_TABLES, grid, signs, nullptr)
+MUL_MAT(production_mul_mat_tq1_0_decode, F_TQ1_0, 0, TQ_TABLES, nullptr, nullptr, powers)
+MUL_MAT(production_mul_mat_q4_0, F_Q4_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q8_0, F_Q8_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q4_k_staged, F_Q4_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_tq1_0, F_TQ1_0, 1, TQ_TABLES, nullptr, nullptr, powers)
+MUL_MAT(production_mul_mat_iq2_xxs_staged, F_IQ2_XXS, 1, IQ_TABLES, grid, signs, nullptr)
+
+int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
+                            const int8_t *grid, const int8_t *signs, const uint32_t *powers,
+                            float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags) {
+    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q4_K && format != F_IQ2_XXS && format != F_TQ1_0)
+        return fail("unknown weight format id %d", format);
+    if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
+    return do_mul_mat(format, mode, W_local, X, Xq, grid, signs, powers, Y_columns, N_local, K, M, ldy, flags, false);
+}
+
+}  // extern "C"

@@ -1,0 +1,266 @@
+// row_dequantize_<fmt>: packed records -> fp32, bit-exact with the reference's GGML semantics.
+//
+// HBM-bound and write-dominated (4 bytes out per 0.5..1.06 bytes in).  A weight matrix (N, K) is a
+// contiguous stream of records and its fp32 image a contiguous stream of floats, so every kernel
+// here is flat: one warp owns one 256-element unit per step and every lane stores whole float4s
+// that are contiguous across the warp (128-byte segments, no partial sectors).
+//
+// Float op trees follow the reference exactly and are spelled with __fmul_rn/__fsub_rn so the
+// compiler cannot contract them:
+//   Q4_0/Q8_0  f32(q - zero) * f32(d)            examples/functions/quantization.py:6-7,  ggml-quants.c:401-419,495-509
+//   Q4_K       (d*sc)*q - (dmin*m)               quantization.py:14-17,                   ggml-quants.c:1471-1493
+//   IQ2_XXS    (d*(0.5+s)*0.25) * (grid*sign)    examples/kernels/dequantize/iq2_xxs.py:9-53, ggml-quants.c:2416-2440
+//   TQ1_0      f32(trit-1) * d                   examples/kernels/dequantize/tq1_0.py:9-46,   ggml-quants.c:2356-2393
+#include "common.cuh"
+#include "kernels.h"
+
+namespace weft {
+
+template <bool A4>
+__device__ __forceinline__ uint32_t ldw(const uint8_t *p) {
+    if (A4) return __ldg(reinterpret_cast<const uint32_t *>(p));
+    return ld_u32_a2(p);
+}
+
+__device__ __forceinline__ void st4(float *y, float a, float b, float c, float d) {
+    __stcs(reinterpret_cast<float4 *>(y), make_float4(a, b, c, d));   // streaming store: output is never re-read
+}
+
+constexpr int DQ_WARPS = 8;
+
+// ---- Q4_K: lane = (64-element group j, 4-byte slice t): low nibbles -> 64j+4t.., high -> 64j+32+4t..
+template <bool A4>
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q4_k_kernel(const uint8_t *__restrict__ w, float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    const int j = lane >> 3, t = lane & 7;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 144;
+        const uint32_t dd = ldw<A4>(rec);
+        const Q4KScales s = q4k_unpack_scales(ldw<A4>(rec + 4), ldw<A4>(rec + 8), ldw<A4>(rec + 12));
+        const uint32_t q = ldw<A4>(rec + 16 + 32 * j + 4 * t);
+        const float d = half_bits_to_float(dd), dmin = half_bits_to_float(dd >> 16);
+        // scale index 2j and 2j+1
+        const uint32_t scv = j < 2 ? s.sc_lo : s.sc_hi, mnv = j < 2 ? s.mn_lo : s.mn_hi;
+        const int b0 = (2 * j) & 3;
+        const float d1 = __fmul_rn(d, (float)byte_of(scv, b0)), m1 = __fmul_rn(dmin, (float)byte_of(mnv, b0));
+        const float d2 = __fmul_rn(d, (float)byte_of(scv, b0 + 1)), m2 = __fmul_rn(dmin, (float)byte_of(mnv, b0 + 1));
+        float lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t b = byte_of(q, i);
+            lo[i] = __fsub_rn(__fmul_rn(d1, (float)(b & 15u)), m1);
+            hi[i] = __fsub_rn(__fmul_rn(d2, (float)(b >> 4)), m2);
+        }
+        float *out = y + u * 256 + 64 * j + 4 * t;
+        st4(out, lo[0], lo[1], lo[2], lo[3]);
+        st4(out + 32, hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
+// ---- Q4_0: a warp covers 8 records; lane = (record b, 4-byte slice s)
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q4_0_kernel(const uint8_t *__restrict__ w, float *__restrict__ y, long long records) {
+    const int lane = threadIdx.x & 31;
+    const int b = lane >> 2, s = lane & 3;
+    const long long groups = (records + 7) / 8;
+    for (long long g = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); g < groups; g += (long long)gridDim.x * DQ_WARPS) {
+        const long long r = g * 8 + b;
+        if (r >= records) continue;
+        const uint8_t *rec = w + r * 18;
+        const float d = half_bits_to_float(ld_u16(rec));
+        const uint32_t q = ld_u32_a2(rec + 2 + 4 * s);
+        float lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int v = (int)byte_of(q, i);
+            lo[i] = __fmul_rn((float)((v & 15) - 8), d);
+            hi[i] = __fmul_rn((float)((v >> 4) - 8), d);
+        }
+        float *out = y + r * 32 + 4 * s;
+        st4(out, lo[0], lo[1], lo[2], lo[3]);
+        st4(out + 16, hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
+// ---- Q8_0: a warp covers 8 records; lane = (record b, 8-byte slice s)
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q8_0_kernel(const uint8_t *__restrict__ w, float *__restrict__ y, long long records) {
+    const int lane = threadIdx.x & 31;
+    const int b = lane >> 2, s = lane & 3;
+    const long long groups = (records + 7) / 8;
+    for (long long g = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); g < groups; g += (long long)gridDim.x * DQ_WARPS) {
+        const long long r = g * 8 + b;
+        if (r >= records) continue;
+        const uint8_t *rec = w + r * 34;
+        const float d = half_bits_to_float(ld_u16(rec));
+        const uint32_t q0 = ld_u32_a2(rec + 2 + 8 * s), q1 = ld_u32_a2(rec + 6 + 8 * s);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[i] = __fmul_rn((float)(int)(int8_t)byte_of(q0, i), d);
+            v[4 + i] = __fmul_rn((float)(int)(int8_t)byte_of(q1, i), d);
+        }
+        float *out = y + r * 32 + 8 * s;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
+// ---- IQ2_XXS: lane = (32-element group g, 8-element entry e); tables staged in shared memory
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq2_xxs_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                                                         const int8_t *__restrict__ signs, float *__restrict__ y, long long units) {
+    __shared__ __align__(8) int8_t s_grid[2048];
+    __shared__ __align__(8) int8_t s_signs[1024];
+    for (int i = threadIdx.x; i < 2048; i += blockDim.x) s_grid[i] = grid[i];
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) s_signs[i] = signs[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, e = lane & 3;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 66;
+        const float d = half_bits_to_float(ld_u16(rec));
+        const uint8_t *grp = rec + 2 + 8 * g;
+        const uint32_t index = rec[2 + 8 * g + e];
+        const uint32_t meta = ld_u32_a2(grp + 4);
+        const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(meta >> 28))), 0.25f);
+        const int8_t *gv = s_grid + 8 * index;
+        const int8_t *sv = s_signs + 8 * ((meta >> (7 * e)) & 127u);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(db, (float)gv[i]), (float)sv[i]);
+        float *out = y + u * 256 + 32 * g + 8 * e;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
+// ---- TQ1_0: every lane produces 8 consecutive outputs; lanes 0-19 region 0 (5 digits x 32 bytes),
+//      20-29 region 1 (5 digits x 16 bytes), 30-31 region 2 (4 digits x 4 bytes)
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_tq1_0_kernel(const uint8_t *__restrict__ w, const uint32_t *__restrict__ powers,
+                                                                       float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    uint32_t pw[5];
+#pragma unroll
+    for (int i = 0; i < 5; ++i) pw[i] = __ldg(powers + i);
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 54;
+        const float d = half_bits_to_float(ld_u16(rec + 52));
+        float v[8];
+        if (lane < 30) {
+            int digit, byte0;
+            if (lane < 20) { digit = lane >> 2; byte0 = (lane & 3) * 8; }
+            else { const int i = lane - 20; digit = i >> 1; byte0 = 32 + (i & 1) * 8; }
+            const uint32_t p = digit == 0 ? pw[0] : digit == 1 ? pw[1] : digit == 2 ? pw[2] : digit == 3 ? pw[3] : pw[4];
+            const uint32_t q0 = ld_u32_a2(rec + byte0), q1 = ld_u32_a2(rec + byte0 + 4);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[i] = __fmul_rn((float)tq1_digit(byte_of(q0, i), p), d);
+                v[4 + i] = __fmul_rn((float)tq1_digit(byte_of(q1, i), p), d);
+            }
+        } else {
+            const uint32_t qh = ld_u32_a2(rec + 48);
+            const int n0 = (lane - 30) * 2;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[i] = __fmul_rn((float)tq1_digit(byte_of(qh, i), n0 == 0 ? pw[0] : pw[2]), d);
+                v[4 + i] = __fmul_rn((float)tq1_digit(byte_of(qh, i), n0 == 0 ? pw[1] : pw[3]), d);
+            }
+        }
+        float *out = y + u * 256 + 8 * lane;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
+// ---- any alignment of W and Y: one thread per output element (slow path, same op trees)
+__global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                           const int8_t *__restrict__ signs, const uint32_t *__restrict__ powers,
+                                           float *__restrict__ y, long long elements) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < elements; i += (long long)gridDim.x * blockDim.x) {
+        float v = 0.f;
+        if (fmt == F_Q4_0) {
+            const uint8_t *rec = w + (i / 32) * 18;
+            const int e = (int)(i % 32);
+            const int q = e < 16 ? (rec[2 + e] & 15) : (rec[2 + e - 16] >> 4);
+            v = __fmul_rn((float)(q - 8), half_bits_to_float(ld_u16(rec)));
+        } else if (fmt == F_Q8_0) {
+            const uint8_t *rec = w + (i / 32) * 34;
+            v = __fmul_rn((float)(int)(int8_t)rec[2 + i % 32], half_bits_to_float(ld_u16(rec)));
+        } else if (fmt == F_Q4_K) {
+            const uint8_t *rec = w + (i / 256) * 144;
+            const int e = (int)(i % 256), j = e / 64, p = e % 64;
+            const Q4KScales s = q4k_unpack_scales(ld_u32_a2(rec + 4), ld_u32_a2(rec + 8), ld_u32_a2(rec + 12));
+            const int is = 2 * j + (p >= 32);
+            const uint32_t sc = byte_of(is < 4 ? s.sc_lo : s.sc_hi, is & 3), mn = byte_of(is < 4 ? s.mn_lo : s.mn_hi, is & 3);
+            const uint32_t b = rec[16 + 32 * j + (p & 31)];
+            const uint32_t q = p < 32 ? (b & 15u) : (b >> 4);
+            const float d1 = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)sc);
+            const float m1 = __fmul_rn(half_bits_to_float(ld_u16(rec + 2)), (float)mn);
+            v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+        } else if (fmt == F_IQ2_XXS) {
+            const uint8_t *rec = w + (i / 256) * 66;
+            const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8;
+            const uint32_t meta = ld_u32_a2(rec + 2 + 8 * g + 4);
+            const float db = __fmul_rn(__fmul_rn(half_bits_to_float(ld_u16(rec)), __fadd_rn(0.5f, (float)(meta >> 28))), 0.25f);
+            const int gv = grid[8 * rec[2 + 8 * g + en] + l], sv = signs[8 * ((meta >> (7 * en)) & 127u) + l];
+            v = __fmul_rn(__fmul_rn(db, (float)gv), (float)sv);
+        } else if (fmt == F_TQ1_0) {
+            const uint8_t *rec = w + (i / 256) * 54;
+            const int e = (int)(i % 256);
+            int byte, digit;
+            if (e < 160) { digit = e / 32; byte = e % 32; }
+            else if (e < 240) { digit = (e - 160) / 16; byte = 32 + (e - 160) % 16; }
+            else { digit = (e - 240) / 4; byte = 48 + (e - 240) % 4; }
+            v = __fmul_rn((float)tq1_digit(rec[byte], powers[digit]), half_bits_to_float(ld_u16(rec + 52)));
+        }
+        y[i] = v;
+    }
+}
+
+static int dq_grid(long long warps_needed, int sm_count) {
+    const long long blocks = (warps_needed + DQ_WARPS - 1) / DQ_WARPS;
+    const long long cap = (long long)sm_count * 64;   // 8 resident blocks per SM, 8 waves deep
+    return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const int8_t *signs, const uint32_t *powers,
+                              float *y, long long elements, int sm_count, cudaStream_t stream) {
+    if (elements == 0) return cudaSuccess;
+    const uint8_t *wb = static_cast<const uint8_t *>(w);
+    if ((reinterpret_cast<uintptr_t>(y) & 15u) || (reinterpret_cast<uintptr_t>(w) & 1u)) {
+        const long long blocks = (elements + 255) / 256, cap = (long long)sm_count * 32;
+        dequant_elementwise_kernel<<<(int)(blocks > cap ? cap : blocks), 256, 0, stream>>>(fmt, wb, grid, signs, powers, y, elements);
+        return cudaGetLastError();
+    }
+    const bool a4 = (reinterpret_cast<uintptr_t>(w) & 3u) == 0;
+    switch (fmt) {
+    case F_Q4_K: {
+        const long long units = elements / 256;
+        if (a4) dequant_q4_k_kernel<true><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
+        else dequant_q4_k_kernel<false><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
+        break;
+    }
+    case F_Q4_0: {
+        const long long records = elements / 32;
+        dequant_q4_0_kernel<<<dq_grid((records + 7) / 8, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, records);
+        break;
+    }
+    case F_Q8_0: {
+        const long long records = elements / 32;
+        dequant_q8_0_kernel<<<dq_grid((records + 7) / 8, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, records);
+        break;
+    }
+    case F_IQ2_XXS: {
+        const long long units = elements / 256;
+        dequant_iq2_xxs_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, signs, y, units);
+        break;
+    }
+    case F_TQ1_0: {
+        const long long units = elements / 256;
+        dequant_tq1_0_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, powers, y, units);
+        break;
+    }
+    default: return cudaErrorInvalidValue;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace weft

@@ -1,0 +1,43 @@
+// Host-side launchers of the sm_100a kernels (internal; the public surface is include/weft_b200.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace weft {
+
+// W: `elements` logical values as contiguous records of `fmt`; Y: `elements` floats.
+cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const int8_t *signs, const uint32_t *powers,
+                              float *y, long long elements, int sm_count, cudaStream_t stream);
+
+// X (rows, k) fp32 -> Q8_0 / Q8_K records, Weft rounding and tie rules.
+cudaError_t launch_quantize(int act_fmt, const float *x, void *y, long long rows, long long k, int sm_count, cudaStream_t stream);
+
+struct GemvArgs {
+    int fmt;                 // weight format
+    const void *w;           // (n, k) records
+    const void *xq;          // (m, k) activation records (Q8_0 or Q8_K)
+    const int8_t *grid;      // IQ2_XXS only
+    const int8_t *signs;     // IQ2_XXS only
+    const uint32_t *powers;  // TQ1_0 only
+    float *y;                // (m, ldy) fp32; column n of row r at y[r * ldy + n]
+    long long n, k, m, ldy;
+    int *status;             // mapped status word
+};
+cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream);
+
+struct PrefillArgs {
+    int fmt;
+    const void *w;           // (n, k) records
+    const void *xq;          // (m, k) Q8_K records (already quantized)
+    const uint32_t *powers;  // TQ1_0 only
+    float *y;                // (m, ldy)
+    long long n, k, m, ldy;
+    int *status;
+};
+// tcgen05 int8 tensor-core path; returns cudaErrorNotSupported for shapes it does not take.
+cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stream);
+bool prefill_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
+
+}  // namespace weft

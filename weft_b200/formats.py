@@ -1,0 +1,98 @@
+"""The GGML record layouts on the quantized matrix path, declared with ``@weft.encoding``.
+
+These are the six hot-path encodings of the reference's examples/formats/ggml.py (Q4_0 :16-22,
+Q8_0 :56-62, Q4_K :88-97, IQ2_XXS :164-170, I8X8 :173-178, TQ1_0 :231-238, Q8_K :276-283), byte for
+byte the block structs of ggml-common.h:184-189,241-246,266-271,317-328,361-366,371-375.  A kernel
+file may use these or the reference's own declarations: ``weft.compile`` identifies an Encoding by
+its name and checks the record geometry, not the declaring module.
+"""
+from __future__ import annotations
+
+from . import language as wl
+from .api import encoding
+
+_LE = (wl.bitorder.lsb_first, wl.byteorder.little)
+
+
+@encoding
+class Q4_0:                      # 18 bytes / 32 elements
+    layout = _LE
+    alignment = 2
+    elements = 32
+    d: wl.f16                    # @0
+    q: wl.u4[32] @ wl.grouped(elements=32) @ wl.bit_layers(elements=16, order=wl.lo_first)   # @2: byte j = elem j | elem j+16 << 4
+
+
+@encoding
+class Q8_0:                      # 34 bytes / 32 elements
+    layout = _LE
+    alignment = 2
+    elements = 32
+    d: wl.f16
+    q: wl.i8[32]
+
+
+@encoding
+class Q4_K:                      # 144 bytes / 256 elements
+    layout = _LE
+    alignment = 2
+    elements = 256
+    d: wl.f16                    # @0
+    dmin: wl.f16                 # @2
+    sc: wl.u6[8] @ wl.pack_fields(group=4, fields=2, low_bits=4, order=wl.lo_first)   # @4, 12 bytes shared with m
+    m: wl.u6[8] @ wl.pack_fields(group=4, fields=2, low_bits=4, order=wl.lo_first)
+    q: wl.u4[256] @ wl.grouped(elements=64) @ wl.bit_layers(elements=32, order=wl.lo_first)   # @16
+
+
+@encoding
+class IQ2_XXS:                   # 66 bytes / 256 elements
+    layout = _LE
+    alignment = 2
+    elements = 256
+    d: wl.f16
+    q: wl.u16[32]                # per 32 elements: 4 grid indices, then u32 {4 x 7-bit sign index, 4-bit scale}
+
+
+@encoding
+class I8X8:                      # one codebook row
+    layout = _LE
+    alignment = 8
+    elements = 8
+    values: wl.i8[8]
+
+
+@encoding
+class TQ1_0:                     # 54 bytes / 256 elements
+    layout = _LE
+    alignment = 2
+    elements = 256
+    q: wl.u8[48]                 # 5 trits per byte: 32 bytes over 160 elements, 16 bytes over 80
+    qh: wl.u8[4]                 # 4 trits per byte over the last 16 elements
+    d: wl.f16                    # @52
+
+
+@encoding
+class Q8_K:                      # 292 bytes / 256 elements
+    layout = _LE
+    alignment = 4
+    elements = 256
+    ds: wl.f32                   # @0
+    q: wl.i8[256]                # @4
+    bsum: wl.i16[16]             # @260
+
+
+#: name -> (storage bytes per record, logical elements per record, alignment)
+RECORDS = {"Q4_0": (18, 32, 2), "Q8_0": (34, 32, 2), "Q4_K": (144, 256, 2), "IQ2_XXS": (66, 256, 2),
+           "TQ1_0": (54, 256, 2), "Q8_K": (292, 256, 4), "I8X8": (8, 8, 8)}
+
+#: numbering of the reference harnesses (examples/repro/weft/vec_dot_runtime.cpp:185-344), used by the C ABI
+FORMAT_IDS = {"Q4_0": 1, "Q8_0": 5, "Q4_K": 8, "IQ2_XXS": 15, "TQ1_0": 20}
+
+TQ1_POWERS = (1, 3, 9, 27, 81)
+
+
+def row_bytes(name: str, k: int) -> int:
+    storage, elements, _ = RECORDS[name]
+    if k % elements:
+        raise ValueError(f"K = {k} does not contain complete {name} records")
+    return k // elements * storage

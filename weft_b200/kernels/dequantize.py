@@ -1,0 +1,36 @@
+"""Row dequantizers: K packed elements -> K fp32 values, bit-exact with the reference's GGML semantics.
+
+Signatures follow examples/kernels/dequantize/q4_0.py:9-13, q8_0.py:9-13, q4_k.py:9-20,
+iq2_xxs.py:9-53 and tq1_0.py:9-46 of the reference (Y is its own alias group where the reference says so).
+"""
+from __future__ import annotations
+
+from .. import formats as ggml
+from .. import language as wl
+from ..api import kernel
+
+
+@kernel
+def row_dequantize_q4_0(W: wl.View[ggml.Q4_0, (K,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = f32(q - 8) * f32(d)."""
+
+
+@kernel
+def row_dequantize_q8_0(W: wl.View[ggml.Q8_0, (K,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = f32(q) * f32(d)."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_q4_k(W: wl.View[ggml.Q4_K, (K,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * sc) * q - (dmin * m), three rounded multiplies and one subtract."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq2_xxs(W: wl.View[ggml.IQ2_XXS, (K,)], grid: wl.View[wl.i8, (2048,)],
+                           signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (0.5 + s) * 0.25) * (grid[idx] * signs[sidx])."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_tq1_0(W: wl.View[ggml.TQ1_0, (K,)], powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = f32(trit - 1) * d, digit-major within each of the record's three regions."""

@@ -1,0 +1,77 @@
+"""production_mul_mat_*: quantize X into the Xq workspace, then Y[m, n] = vec_dot(W[n], Xq[m]).
+
+Signatures and alias groups follow the reference: examples/kernels/mul_mat/q4_0_decode.py:10-20,
+q8_0_decode.py, q4_k_decode.py:10-20, iq2_xxs_decode.py:10-23, tq1_0_decode.py:10-21 (decode: a GEMV
+per activation row) and q4_0.py:9-30, q8_0.py:9-29, q4_k_staged.py:9-37, tq1_0.py:10-64,
+iq2_xxs_staged.py:9-97 (prefill: tiled contraction).  The reference's tile symbols NC/MC/MR/NR/KC are
+bound through CompileOptions.meta and are not call parameters.
+"""
+from __future__ import annotations
+
+from .. import formats as ggml
+from .. import language as wl
+from ..api import kernel
+
+
+@kernel
+def production_mul_mat_q4_0_decode(W: wl.View[ggml.Q4_0, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                   Xq: wl.View[ggml.Q8_0, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, Q4_0 weights x Q8_0 activations."""
+
+
+@kernel
+def production_mul_mat_q8_0_decode(W: wl.View[ggml.Q8_0, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                   Xq: wl.View[ggml.Q8_0, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, Q8_0 weights x Q8_0 activations."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_q4_k_decode(W: wl.View[ggml.Q4_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                   Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, Q4_K weights x Q8_K activations."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq2_xxs_decode(W: wl.View[ggml.IQ2_XXS, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                      Xq: wl.View[ggml.Q8_K, (M, K)], grid: wl.View[ggml.I8X8, (256, 8)],
+                                      signs: wl.View[ggml.I8X8, (128, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, IQ2_XXS codebook weights x Q8_K activations."""
+
+
+@kernel
+def production_mul_mat_tq1_0_decode(W: wl.View[ggml.TQ1_0, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                    Xq: wl.View[ggml.Q8_K, (M, K)], powers: wl.View[wl.u32, (5,)],
+                                    Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, TQ1_0 ternary weights x Q8_K activations."""
+
+
+@kernel
+def production_mul_mat_q4_0(W: wl.View[ggml.Q4_0, (N, K)], X: wl.View[wl.f32, (M, K)],
+                            Xq: wl.View[ggml.Q8_0, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Prefill contraction, Q4_0 x Q8_0."""
+
+
+@kernel
+def production_mul_mat_q8_0(W: wl.View[ggml.Q8_0, (N, K)], X: wl.View[wl.f32, (M, K)],
+                            Xq: wl.View[ggml.Q8_0, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Prefill contraction, Q8_0 x Q8_0."""
+
+
+@kernel
+def production_mul_mat_q4_k_staged(W: wl.View[ggml.Q4_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                   Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Prefill contraction, Q4_K x Q8_K, int8 tensor cores."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_tq1_0(W: wl.View[ggml.TQ1_0, (N, K)], X: wl.View[wl.f32, (M, K)],
+                             Xq: wl.View[ggml.Q8_K, (M, K)], powers: wl.View[wl.u32, (5,)],
+                             Y: wl.View[wl.f32, (M, N)]):
+    """Prefill contraction, TQ1_0 x Q8_K, int8 tensor cores."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq2_xxs_staged(W: wl.View[ggml.IQ2_XXS, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                      Xq: wl.View[ggml.Q8_K, (M, K)], grid: wl.View[ggml.I8X8, (256, 8)],
+                                      signs: wl.View[ggml.I8X8, (128, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """Prefill form, IQ2_XXS x Q8_K."""

@@ -1,0 +1,38 @@
+"""Block dot products: one weight row against one activation row, one fp32 result.
+
+Signatures follow examples/kernels/vec_dot/q4_0_q8_0.py:18-23, q8_0_q8_0.py:17-22, q4_k_q8_k.py:31-36,
+iq2_xxs_q8_k.py:45-54 and tq1_0_q8_k.py:47-55 of the reference.
+"""
+from __future__ import annotations
+
+from .. import formats as ggml
+from .. import language as wl
+from ..api import kernel
+
+
+@kernel
+def quantized_vec_dot_q4_0_q8_0(W: wl.View[ggml.Q4_0, (K,)], X: wl.View[ggml.Q8_0, (K,)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 32-blocks of f32(d_w) * f32(d_x) * f32(sum((q - 8) * x))."""
+
+
+@kernel
+def quantized_vec_dot_q8_0_q8_0(W: wl.View[ggml.Q8_0, (K,)], X: wl.View[ggml.Q8_0, (K,)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 32-blocks of f32(sum(w * x)) * (f32(d_w) * f32(d_x))."""
+
+
+@kernel
+def quantized_vec_dot_q4_k_q8_k(W: wl.View[ggml.Q4_K, (K,)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 256-blocks of x.ds * (d * sum_g sc_g * dot32_g - dmin * sum_g m_g * (bsum_2g + bsum_2g+1))."""
+
+
+@kernel
+def quantized_vec_dot_iq2_xxs_q8_k(W: wl.View[ggml.IQ2_XXS, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                   grid: wl.View[ggml.I8X8, (256, 8)], signs: wl.View[ggml.I8X8, (128, 8)],
+                                   Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = 0.125 * sum over 256-blocks of d * x.ds * sum_g (2 s_g + 1) * dot(grid[idx] * signs[sidx], x)."""
+
+
+@kernel
+def quantized_vec_dot_tq1_0_q8_k(W: wl.View[ggml.TQ1_0, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                 powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 256-blocks of f32(sum((trit - 1) * x)) * (d * x.ds); trits decoded with powers[]."""
