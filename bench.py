@@ -228,6 +228,7 @@ def main() -> None:
     parser.add_argument("--impl", default="weft_b200", choices=["weft_b200", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-graph", action="store_true", help="time direct launches instead of a CUDA graph replay")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     fmt, mode, n, k, m = WORKLOADS[args.workload]
@@ -253,7 +254,11 @@ def main() -> None:
     lib = load_library(Toolchain().resolve().compiler)
     if lib.weft_b200_init(local_rank):
         raise SystemExit("weft_b200_init failed: " + last_error(lib))
-    stream = torch.cuda.current_stream()
+    # A real (non-default) stream: the library treats a NULL handle as "use your own stream", and the
+    # events that time the run must sit on the stream the kernels are launched on.
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    assert stream.cuda_stream != 0
     lib.weft_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
     lib.weft_b200_set_async(1)
 
@@ -311,6 +316,42 @@ def main() -> None:
     if not err <= 1e-5:
         raise SystemExit(f"parity check failed before timing: relative L2 {err}")
 
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def run_timed(fn, steps: int, first: int) -> tuple[float, str]:
+        """Device time of `steps` consecutive calls of fn.  The calls are captured once into a CUDA graph and
+        the graph is replayed between the two events, so host launch cost (Python + ctypes, several
+        microseconds per call, comparable to the kernel itself) stays out of the measurement.  Falls back to
+        direct launches when capture is refused."""
+        if not args.no_graph:
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            try:
+                side.wait_stream(torch.cuda.current_stream())
+                lib.weft_b200_set_stream(ctypes.c_void_p(side.cuda_stream))
+                with torch.cuda.graph(graph, stream=side):
+                    for i in range(steps):
+                        fn(first + i)
+                lib.weft_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
+                graph.replay()          # untimed: first replay uploads the graph
+                barrier()
+                begin.record()
+                graph.replay()
+                end.record()
+                barrier()
+                return begin.elapsed_time(end), "cuda graph replay of all steps"
+            except Exception as error:  # capture refused: measure direct launches instead
+                lib.weft_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
+                torch.cuda.synchronize()
+                sys.stderr.write(f"graph capture unavailable ({error}); timing direct launches\n")
+        barrier()
+        begin.record()
+        for i in range(steps):
+            fn(first + i)
+        end.record()
+        barrier()
+        return begin.elapsed_time(end), "direct launches"
+
     # ---- timed region: K steps on the device
     for i in range(args.warmup):
         step(i)
@@ -319,16 +360,9 @@ def main() -> None:
     if rank == 0:
         sampler.start()
     launches_before = lib.weft_b200_launch_count()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    begin.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    end.record()
-    barrier()
+    elapsed_ms, launch_mode = run_timed(step, args.steps, args.warmup)
     launches = int(lib.weft_b200_launch_count() - launches_before)
     check(lib.weft_b200_synchronize())
-    elapsed_ms = begin.elapsed_time(end)
     if world > 1:
         t = torch.tensor([elapsed_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -347,12 +381,8 @@ def main() -> None:
     for i in range(args.warmup):
         kernel_step(i)
     barrier()
-    begin.record()
-    for i in range(args.steps):
-        kernel_step(args.warmup + i)
-    end.record()
-    barrier()
-    kernel_ms = begin.elapsed_time(end) / args.steps
+    kernel_total_ms, _ = run_timed(kernel_step, args.steps, args.warmup)
+    kernel_ms = kernel_total_ms / args.steps
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end through the C ABI with host buffers (weights resident on the device)
@@ -419,7 +449,7 @@ def main() -> None:
         "config": {"workload": args.workload, "format": fmt, "mode": mode, "N": n, "K": k, "M": m,
                    "sharding": f"weight rows split {world} ways, fp32 outputs all-gathered (NCCL)" if world > 1 else "none",
                    "l2": f"steps rotate over {copies} weight copies ({copies * shard.nbytes / 2**20:.0f} MiB per GPU > 2 x L2)",
-                   "timed_scope": "activation quantize + mul_mat" + (" + all-gather" if world > 1 else ""), "seed": SEED,
+                   "launch": launch_mode, "timed_scope": "activation quantize + mul_mat" + (" + all-gather" if world > 1 else ""), "seed": SEED,
                    "parity_rel_l2_before_timing": err},
         "roofline": roof, "clocks": clocks, "gpu_launches": launches,
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(x_pin.numel() * 4),

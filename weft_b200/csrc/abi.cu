@@ -43,6 +43,8 @@ struct State {
     int *status_dev = nullptr;
     unsigned long long launches = 0;
     std::map<uintptr_t, Resident> resident;   // keyed by host base address
+    uint8_t *arena = nullptr;                 // staging for host-pointer arguments; grows, never shrinks
+    size_t arena_bytes = 0;
 };
 State g;
 
@@ -91,14 +93,18 @@ struct Arg {
     const void *user = nullptr;
     void *dev = nullptr;
     size_t bytes = 0;
-    bool host = false, staged = false, written = false;
+    bool written = false, overflow = false;
 };
 
+// Host-pointer arguments are staged in one device arena owned by the library (256-byte aligned slices).
+// An argument that does not fit gets a one-off allocation, and the arena is regrown after the call so
+// that the same call fits next time.  Calls that stage anything always end with a stream synchronize,
+// so the arena is free again when the next call starts.
 class Call {
   public:
     ~Call() {
         for (Arg &a : args_)
-            if (a.staged && a.dev) cudaFreeAsync(a.dev, g.stream);
+            if (a.overflow && a.dev) { cudaStreamSynchronize(g.stream); cudaFree(a.dev); }
     }
     // Returns the device address for `ptr` (bytes long). read: copy in when host; written: copy back.
     int map(const void *ptr, size_t bytes, bool read, bool written, void **out) {
@@ -127,8 +133,16 @@ class Call {
             }
         }
         Arg arg;
-        arg.user = ptr; arg.bytes = bytes; arg.host = true; arg.staged = true; arg.written = written;
-        CU(cudaMallocAsync(&arg.dev, bytes, g.stream));
+        arg.user = ptr; arg.bytes = bytes; arg.written = written;
+        const size_t offset = (used_ + 255) & ~size_t(255);
+        wanted_ = ((wanted_ + 255) & ~size_t(255)) + bytes;
+        if (offset + bytes <= g.arena_bytes) {
+            arg.dev = g.arena + offset;
+            used_ = offset + bytes;
+        } else {
+            CU(cudaMalloc(&arg.dev, bytes));
+            arg.overflow = true;
+        }
         args_.push_back(arg);
         if (read) CU(cudaMemcpyAsync(arg.dev, ptr, bytes, cudaMemcpyHostToDevice, g.stream));
         *out = arg.dev;
@@ -140,6 +154,14 @@ class Call {
             if (a.written) CU(cudaMemcpyAsync(const_cast<void *>(a.user), a.dev, a.bytes, cudaMemcpyDeviceToHost, g.stream));
         if (any_host_ || !g.async) {
             CU(cudaStreamSynchronize(g.stream));
+            if (wanted_ > g.arena_bytes) {   // make the next identical call fit
+                if (g.arena) cudaFree(g.arena);
+                g.arena = nullptr;
+                g.arena_bytes = 0;
+                const size_t want = (wanted_ + wanted_ / 4 + (size_t(1) << 16)) & ~size_t(255);
+                if (cudaMalloc(reinterpret_cast<void **>(&g.arena), want) == cudaSuccess) g.arena_bytes = want;
+                else cudaGetLastError();
+            }
             return device_status();
         }
         return 0;
@@ -147,6 +169,7 @@ class Call {
 
   private:
     std::vector<Arg> args_;
+    size_t used_ = 0, wanted_ = 0;
     bool any_host_ = false;
 };
 
@@ -218,17 +241,18 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
         (reinterpret_cast<uintptr_t>(y) & 3u) || (x && (reinterpret_cast<uintptr_t>(x) & 3u)))
         return fail("a buffer does not meet its Encoding alignment");
     const int sms = g.prop.multiProcessorCount;
-    if (!have_xq && launched(launch_quantize(act, (const float *)x, xq, (long long)M, (long long)K, sms, g.stream), "activation quantize"))
+    const bool to_prefill = mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
+    // decode: the GEMV's own prologue quantizes X (one launch) when the fp32 rows allow 16-byte loads
+    const bool fuse_quantize = !have_xq && !to_prefill && K % 256 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    if (!have_xq && !fuse_quantize &&
+        launched(launch_quantize(act, (const float *)x, xq, (long long)M, (long long)K, sms, g.stream), "activation quantize"))
         return 1;
-    bool done = false;
-    if (mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq)) {
+    if (to_prefill) {
         PrefillArgs pa{fmt, w, xq, (const uint32_t *)pw, (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
         if (launched(launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
-        done = true;
-    }
-    if (!done) {
-        GemvArgs ga{fmt, w, xq, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw, (float *)y,
-                    (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
+    } else {
+        GemvArgs ga{fmt, w, xq, fuse_quantize ? (const float *)x : nullptr, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw,
+                    (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
         if (launched(launch_gemv(ga, sms, g.stream), "decode mul_mat")) return 1;
     }
     return call.finish();

@@ -16,9 +16,10 @@
 //   Q4_0  acc += (d_w*d_x) * f32(sum)              Q8_0  acc += f32(sum) * (d_w*d_x)
 //   Q4_K  acc += x.d * (d*f32(isum) - dmin*f32(msum))
 //   IQ2_XXS acc += (d_w*x.d) * f32(bsum), result *= 0.125     TQ1_0 acc += f32(sum) * (d_w*x.d)
-#include "common.cuh"
+#include "quantize.cuh"
 #include "kernels.h"
 
+#include <climits>
 #include <cstdlib>
 
 namespace weft {
@@ -28,7 +29,8 @@ constexpr int XAUX_BYTES = 64;  // per unit: Q8_K {f32 d, i32 total, -, -, i32 p
 
 struct GemvParams {
     const uint8_t *w;
-    const uint8_t *xq;
+    const uint8_t *xq;       // activation records: read, or written by CTA column 0 when the prologue quantizes
+    const float *x;          // fp32 activations (fused-quantize kernels only)
     const int8_t *grid;
     const int8_t *signs;
     const uint32_t *powers;
@@ -38,6 +40,7 @@ struct GemvParams {
     long long ldy;
     int lanes_per_row; // power of two, <= 32
     int stage_bytes;   // per-buffer bytes (16-byte multiple, includes slack)
+    int nbuf;          // ring depth per warp (2..4)
     int *status;
 };
 
@@ -298,9 +301,51 @@ __device__ void stage_q8_0(const uint8_t *xq, int nb, uint8_t *s_q, uint8_t *s_a
     }
 }
 
+// fp32 row -> staged Q8_K units (same arithmetic as q8_K_quantize); `out` non-null: also write the records
+__device__ void quantize_stage_q8_k(const float *x, int nb, uint8_t *s_q, uint8_t *s_aux, uint8_t *out) {
+    const int lane = threadIdx.x & 31;
+    for (int u = threadIdx.x >> 5; u < nb; u += blockDim.x >> 5) {
+        float v[8];
+        load8<true>(x + u * 256 + 8 * lane, v);
+        uint32_t q0, q1;
+        int sum16;
+        float d;
+        q8_k_warp(v, q0, q1, sum16, d);
+        *reinterpret_cast<uint2 *>(s_q + u * XQ_PITCH + 8 * lane) = make_uint2(q0, q1);
+        // pair sum g covers 32 codes = lanes 4g..4g+3; total = all 32 lanes
+        int s32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+        int total = s32;
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        int *aux = reinterpret_cast<int *>(s_aux + u * XAUX_BYTES);
+        if ((lane & 3) == 0) aux[4 + (lane >> 2)] = s32;
+        if (lane == 0) { aux[0] = __float_as_int(d); aux[1] = total; }
+        if (out) store_q8_k(out + (size_t)u * 292, lane, q0, q1, sum16, d);
+    }
+}
+
+// fp32 row -> staged Q8_0 units (same arithmetic as q8_0_quantize); the staged d is the stored f16 value
+__device__ void quantize_stage_q8_0(const float *x, int nb, uint8_t *s_q, uint8_t *s_aux, uint8_t *out) {
+    const int lane = threadIdx.x & 31, b = lane >> 2, sub = lane & 3;
+    for (int u = threadIdx.x >> 5; u < nb; u += blockDim.x >> 5) {
+        float v[8];
+        load8<true>(x + u * 256 + 8 * lane, v);
+        uint32_t q0, q1;
+        int sum32;
+        float d;
+        q8_0_warp(v, q0, q1, sum32, d);
+        *reinterpret_cast<uint2 *>(s_q + u * XQ_PITCH + 8 * lane) = make_uint2(q0, q1);
+        if (sub == 0) {
+            reinterpret_cast<float *>(s_aux + u * XAUX_BYTES)[b] = __half2float(__float2half_rn(d));
+            reinterpret_cast<int *>(s_aux + u * XAUX_BYTES + 32)[b] = sum32;
+        }
+        if (out) store_q8_0(out + ((size_t)u * 8 + b) * 34, sub, q0, q1, d);
+    }
+}
+
 // ------------------------------------------------------------------ the kernel
 
-template <int FMT, int RL, bool BULK>
+template <int FMT, int RL, bool BULK, bool QX>
 __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int UB = Unit<FMT>::BYTES;
@@ -311,30 +356,34 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
     const int row_bytes = nb * UB;
 
     // carve shared memory
+    const int NBUF = p.nbuf;
     int *s_next = reinterpret_cast<int *>(smem);
-    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + 16);
-    uint8_t *cursor = smem + 16 + 16 * warps;   // two barriers per warp
+    uint64_t *s_bar = reinterpret_cast<uint64_t *>(smem + 16);          // four barriers per warp
+    int *s_rows = reinterpret_cast<int *>(smem + 16 + 32 * warps);      // four claimed row offsets per warp
+    uint8_t *cursor = smem + 16 + 48 * warps;
     uint8_t *s_tab0 = cursor, *s_tab1 = cursor;
     if (FMT == F_IQ2_XXS) { s_tab1 = cursor + 2048; cursor += 3072; }
     uint8_t *s_xq = cursor;
     cursor += nb * XQ_PITCH;
     uint8_t *s_xaux = cursor;
     cursor += nb * XAUX_BYTES;
-    uint8_t *s_ring = cursor + (size_t)warp * 2 * p.stage_bytes;
+    uint8_t *s_ring = cursor + (size_t)warp * NBUF * p.stage_bytes;
 
     // this CTA's rows
     const long long r_begin = p.n * blockIdx.x / gridDim.x, r_end = p.n * (blockIdx.x + 1) / gridDim.x;
-    const uint8_t *xq = p.xq + (size_t)blockIdx.y * nb * (ACT_Q8_0 ? 272 : 292);
+    const size_t xq_row = (size_t)blockIdx.y * nb * (ACT_Q8_0 ? 272 : 292);
+    const uint8_t *xq = p.xq + xq_row;
     float *y = p.y + (size_t)blockIdx.y * p.ldy;
 
     if (threadIdx.x == 0) {
         *s_next = 0;
-        for (int i = 0; i < 2 * warps; ++i) mbar_init(s_bar + i, 1);
+        for (int i = 0; i < 4 * warps; ++i) mbar_init(s_bar + i, 1);
         mbar_fence_init();
     }
     __syncthreads();
 
-    uint64_t *bar = s_bar + 2 * warp;
+    uint64_t *bar = s_bar + 4 * warp;
+    int *my_rows = s_rows + 4 * warp;
     const long long rows_here = r_end - r_begin;
 
     auto claim = [&]() -> long long {
@@ -361,8 +410,11 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
     };
 
     // first copies go out before anything else is touched
-    long long cur = claim();
-    issue(0, cur);
+    for (int b = 0; b < NBUF - 1; ++b) {
+        const long long r = claim();
+        if (lane == 0) my_rows[b] = (int)min(r, (long long)INT_MAX);
+        issue(b, r);
+    }
 
     // stage tables and activations
     if (FMT == F_IQ2_XXS) {
@@ -374,16 +426,28 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
 #pragma unroll
         for (int i = 0; i < 5; ++i) pw[i] = __ldg(p.powers + i) & 0xffu;
     }
-    if (ACT_Q8_0) stage_q8_0(xq, nb, s_xq, s_xaux); else stage_q8_k(xq, nb, s_xq, s_xaux);
+    if (QX) {
+        uint8_t *out = blockIdx.x == 0 ? const_cast<uint8_t *>(xq) : nullptr;
+        const float *x = p.x + (size_t)blockIdx.y * nb * 256;
+        if (ACT_Q8_0) quantize_stage_q8_0(x, nb, s_xq, s_xaux, out); else quantize_stage_q8_k(x, nb, s_xq, s_xaux, out);
+    } else {
+        if (ACT_Q8_0) stage_q8_0(xq, nb, s_xq, s_xaux); else stage_q8_k(xq, nb, s_xq, s_xaux);
+    }
     __syncthreads();
 
     const int slot = lane / L, ul = lane % L;
     uint32_t phases = 0;   // bit b = parity the next wait on buffer b expects
     int buf = 0;
-    while (cur < rows_here) {
-        const long long nxt = claim();
+    while (true) {
         __syncwarp();
-        issue(buf ^ 1, nxt);
+        const long long cur = my_rows[buf];
+        if (cur >= rows_here) break;
+        {   // refill the buffer that the previous iteration finished reading
+            const int spare = buf == 0 ? NBUF - 1 : buf - 1;
+            const long long nxt = claim();
+            if (lane == 0) my_rows[spare] = (int)min(nxt, (long long)INT_MAX);
+            issue(spare, nxt);
+        }
         if (BULK) {
             if (!mbar_wait(bar + buf, (phases >> buf) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
             phases ^= 1u << buf;
@@ -417,8 +481,7 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
             if (FMT == F_IQ2_XXS) v *= 0.125f;
             if (ul == 0 && live[r]) y[r_begin + cur + slot * RL + r] = v;
         }
-        cur = nxt;
-        buf ^= 1;
+        buf = buf + 1 == NBUF ? 0 : buf + 1;
     }
 }
 
@@ -458,6 +521,10 @@ static int env_int(const char *name, int fallback) {
     const char *v = getenv(name);
     return v && *v ? atoi(v) : fallback;
 }
+// tuning overrides, read once
+static const int kEnvWarps = env_int("WEFT_B200_GEMV_WARPS", 12);
+static const int kEnvRowsPerLane = env_int("WEFT_B200_GEMV_RL", 1);
+static const int kEnvRingDepth = env_int("WEFT_B200_GEMV_NBUF", 3);
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stream) {
@@ -468,13 +535,16 @@ static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stre
     while (L < 32 && L < nb) L <<= 1;
     const bool bulk = (row_bytes % 16 == 0) && ((reinterpret_cast<uintptr_t>(a.w) & 15u) == 0);
     const int smem_cap = 200 * 1024;
-    int warps = env_int("WEFT_B200_GEMV_WARPS", 12);
+    int warps = kEnvWarps;
     warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
-    int rl = env_int("WEFT_B200_GEMV_RL", 2);
-    const long long x_bytes = (long long)nb * (XQ_PITCH + XAUX_BYTES) + (FMT == F_IQ2_XXS ? 3072 : 0) + 16 + 16 * 16;
-    auto ring = [&](int w_, int rl_) { return (long long)w_ * 2 * (((32 / L) * rl_ * row_bytes + 31) / 16 * 16); };
+    int rl = kEnvRowsPerLane;
+    const long long x_bytes = (long long)nb * (XQ_PITCH + XAUX_BYTES) + (FMT == F_IQ2_XXS ? 3072 : 0) + 16 + 48 * 16;
+    int nbuf = kEnvRingDepth;
+    nbuf = nbuf < 2 ? 2 : (nbuf > 4 ? 4 : nbuf);
+    auto ring = [&](int w_, int rl_) { return (long long)w_ * nbuf * (((32 / L) * rl_ * row_bytes + 31) / 16 * 16); };
     if (FMT == F_Q8_0) rl = 1;   // 68 weight words per row already fill the register budget
     while (rl > 1 && x_bytes + ring(warps, rl) > smem_cap) rl = 1;
+    while (nbuf > 2 && x_bytes + ring(warps, rl) > smem_cap) --nbuf;
     while (warps > 1 && x_bytes + ring(warps, rl) > smem_cap) --warps;
     if (x_bytes + ring(warps, rl) > smem_cap) return cudaErrorInvalidConfiguration;   // K too large for shared-memory staging
     const int stage_rows = (32 / L) * rl;
@@ -484,7 +554,10 @@ static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stre
     GemvParams p;
     p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq);
     p.grid = a.grid; p.signs = a.signs; p.powers = a.powers; p.y = a.y;
-    p.n = a.n; p.nb = nb; p.ldy = a.ldy; p.lanes_per_row = L; p.stage_bytes = stage_bytes; p.status = a.status;
+    p.n = a.n; p.nb = nb; p.ldy = a.ldy; p.lanes_per_row = L; p.stage_bytes = stage_bytes; p.nbuf = nbuf; p.status = a.status;
+    p.x = a.x;
+    // the prologue can quantize X itself when the fp32 rows allow 16-byte loads
+    const bool qx = a.x != nullptr;
 
     const long long stages = (a.n + stage_rows - 1) / stage_rows;
     long long ctas = (stages + warps - 1) / warps;   // never more CTAs than there is work for whole warps
@@ -492,14 +565,20 @@ static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stre
     if (ctas < 1) ctas = 1;
     dim3 grid((unsigned)ctas, (unsigned)a.m);
 
-#define WEFT_LAUNCH(RLV, BULKV)                                                                                      \
+#define WEFT_LAUNCH(RLV, BULKV, QXV)                                                                                 \
     do {                                                                                                              \
-        cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, RLV, BULKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        if (e != cudaSuccess) return e;                                                                               \
-        gemv_kernel<FMT, RLV, BULKV><<<grid, warps * 32, smem, stream>>>(p);                                          \
+        static int smem_set = 0;   /* the attribute sticks to the function: raise it only when a launch needs more */ \
+        if ((int)smem > smem_set) {                                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, RLV, BULKV, QXV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return e;                                                                           \
+            smem_set = (int)smem;                                                                                     \
+        }                                                                                                             \
+        gemv_kernel<FMT, RLV, BULKV, QXV><<<grid, warps * 32, smem, stream>>>(p);                                     \
     } while (0)
-    if (rl == 2) { if (bulk) WEFT_LAUNCH(2, true); else WEFT_LAUNCH(2, false); }
-    else { if (bulk) WEFT_LAUNCH(1, true); else WEFT_LAUNCH(1, false); }
+#define WEFT_LAUNCH_Q(RLV, BULKV) do { if (qx) WEFT_LAUNCH(RLV, BULKV, true); else WEFT_LAUNCH(RLV, BULKV, false); } while (0)
+    if (rl == 2) { if (bulk) WEFT_LAUNCH_Q(2, true); else WEFT_LAUNCH_Q(2, false); }
+    else { if (bulk) WEFT_LAUNCH_Q(1, true); else WEFT_LAUNCH_Q(1, false); }
+#undef WEFT_LAUNCH_Q
 #undef WEFT_LAUNCH
     return cudaGetLastError();
 }

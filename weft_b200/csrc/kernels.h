@@ -17,7 +17,8 @@ cudaError_t launch_quantize(int act_fmt, const float *x, void *y, long long rows
 struct GemvArgs {
     int fmt;                 // weight format
     const void *w;           // (n, k) records
-    const void *xq;          // (m, k) activation records (Q8_0 or Q8_K)
+    const void *xq;          // (m, k) activation records (Q8_0 or Q8_K); written when x is given
+    const float *x;          // (m, k) fp32 activations, 16-byte aligned rows: the kernel quantizes them itself; else NULL
     const int8_t *grid;      // IQ2_XXS only
     const int8_t *signs;     // IQ2_XXS only
     const uint32_t *powers;  // TQ1_0 only
