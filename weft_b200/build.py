@@ -15,8 +15,8 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libweft_b200.so"
-SOURCES = ["abi.cu", "dequantize.cu", "quantize.cu", "gemv.cu", "prefill.cu"]
-HEADERS = ["common.cuh", "kernels.h", "../../include/weft_b200.h"]
+SOURCES = ["abi.cu", "dequantize.cu", "quantize.cu", "gemv.cu", "gemv_q4k.cu", "prefill.cu"]
+HEADERS = ["common.cuh", "quantize.cuh", "kernels.h", "../../include/weft_b200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -597,6 +597,8 @@ cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
         return cudaGetLastError();
     }
     if (a.k % 256 != 0 || a.k == 0) return cudaErrorInvalidValue;
+    static const bool generic_only = getenv("WEFT_B200_GENERIC_GEMV") != nullptr;
+    if (!generic_only && gemv_q4k_supported(a)) return launch_gemv_q4k(a, sm_count, stream);
     switch (a.fmt) {
     case F_Q4_0: return launch_fmt<F_Q4_0>(a, sm_count, stream);
     case F_Q8_0: return launch_fmt<F_Q8_0>(a, sm_count, stream);

@@ -27,6 +27,9 @@ struct GemvArgs {
     int *status;             // mapped status word
 };
 cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream);
+// Q4_K x Q8_K specialisation (producer/consumer ring, activations in registers)
+bool gemv_q4k_supported(const GemvArgs &a);
+cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream);
 
 struct PrefillArgs {
     int fmt;
