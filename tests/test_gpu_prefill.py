@@ -1,0 +1,82 @@
+"""GPU parity of the tensor-core prefill path (production_mul_mat_q4_k_staged) against the CPU oracle.
+
+Bound: 1e-5 relative L2.  The integer part (int8 MMAs, int32 / exact-f16 accumulation) is exact; only
+the per-block fp32 combine is rounded, in the reference's own order.
+"""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+from helpers import activations, reference_tolerance_ok, rel_l2, weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def torch():
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.fail("these tests need a CUDA device; there is no CPU fallback to test")
+    return torch
+
+
+def _run(torch, oracle, m, n, k, seed, column_ranges=None):
+    import weft_b200 as weft
+    from weft_b200.kernels import mul_mat
+    from weft_b200.runtime import Buffer
+
+    rng = np.random.default_rng(seed)
+    w = weights(oracle.Q4_K, rng, n, k)
+    x = activations(rng, m, k)
+    xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
+    y = torch.full((m, n), float("nan"), device="cuda")
+    weft.compile(mul_mat.production_mul_mat_q4_k_staged)(
+        Buffer(torch.from_numpy(w).cuda(), shape=(n, k), encoding="Q4_K"), torch.from_numpy(x).cuda(),
+        Buffer(xq, shape=(m, k), encoding="Q8_K"), y)
+    got = y.cpu().numpy()
+    want_xq = oracle.quantize(oracle.Q8_K, x, rule=1)
+    assert np.array_equal(xq.cpu().numpy(), want_xq)
+    assert np.isfinite(got).all()
+    for lo, hi in (column_ranges or [(0, n)]):
+        want, _ = oracle.mul_mat(oracle.Q4_K, w, None, n, k, m, xq=want_xq, rows=(lo, hi))
+        err = rel_l2(got[:, lo:hi], want[:, lo:hi])
+        assert err <= 1e-5, (m, n, k, lo, hi, err)
+        assert reference_tolerance_ok(got[:, lo:hi], want[:, lo:hi])
+
+
+def test_prefill_q4_k_one_tile(torch, oracle):
+    _run(torch, oracle, 128, 128, 256, seed=1)
+
+
+@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 512), (512, 384, 1024), (32, 128, 4096), (200, 1000, 2048)])
+def test_prefill_q4_k_shapes(torch, oracle, mnk):
+    m, n, k = mnk
+    _run(torch, oracle, m, n, k, seed=sum(mnk))
+
+
+@pytest.mark.parametrize("nk", [(4096, 4096), (14336, 4096), (4096, 14336)])
+def test_prefill_q4_k_benchmark_shapes(torch, oracle, nk):
+    """Config 4: M = 512 tokens on the three Llama-3-8B-shaped layers; three column bands against the oracle."""
+    n, k = nk
+    _run(torch, oracle, 512, n, k, seed=n + k, column_ranges=[(0, 128), (n // 2 - 60, n // 2 + 70), (n - 128, n)])
+
+
+def test_prefill_matches_decode_path(torch, oracle):
+    """The tensor-core contraction and the GEMV kernels are two implementations of the same function."""
+    import weft_b200 as weft
+    from weft_b200.kernels import mul_mat
+    from weft_b200.runtime import Buffer
+
+    m, n, k = 64, 512, 2048
+    rng = np.random.default_rng(3)
+    w = torch.from_numpy(weights(oracle.Q4_K, rng, n, k)).cuda()
+    x = torch.from_numpy(activations(rng, m, k)).cuda()
+    outs = []
+    for definition in (mul_mat.production_mul_mat_q4_k_staged, mul_mat.production_mul_mat_q4_k_decode):
+        xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
+        y = torch.zeros((m, n), device="cuda")
+        weft.compile(definition)(Buffer(w, shape=(n, k), encoding="Q4_K"), x, Buffer(xq, shape=(m, k), encoding="Q8_K"), y)
+        outs.append(y.cpu().numpy())
+    assert rel_l2(outs[0], outs[1]) <= 1e-5
