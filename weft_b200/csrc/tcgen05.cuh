@@ -19,6 +19,14 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
            ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
 
+// K-major operand with the 128-byte swizzle: rows of 128 bytes, 8-row groups of 1024 bytes (1024-byte
+// aligned), the 16-byte chunk c of row r stored at chunk position c ^ (r & 7).  The leading-dimension
+// field is fixed to one 16-byte unit, the stride field is the 8-row group pitch, swizzle mode 2.
+// Advancing along K inside the 128-byte row is done by adding the byte offset to the start address.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
 // ---- instruction descriptors ---------------------------------------------------------------------------
 //   bits [4,6) accumulator format (1 = f32, 2 = s32)   bits [7,10) A format   bits [10,13) B format
 //   bit 15 / 16: A / B major (0 = K-major)   bits [17,23) N >> 3   bits [24,29) M >> 4
