@@ -287,7 +287,7 @@ def main() -> None:
     mode_id = 0 if mode == "decode" else 1
     shard_fn = lib.weft_b200_mul_mat_shard
     shard_fn.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_size_t] * 4 + [ctypes.c_uint]
-    gathered = torch.zeros((world, m, n_local), device="cuda") if world > 1 else None
+    gathered = torch.zeros((world * m, n_local), device="cuda") if world > 1 else None
     y_local = torch.zeros((m, n_local), device="cuda") if world > 1 else None
 
     def step(i: int, flags: int = 0) -> None:
