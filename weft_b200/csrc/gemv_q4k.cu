@@ -95,33 +95,10 @@ __device__ __forceinline__ void bulk_g2s_a(uint32_t dst, const void *src, uint32
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
-// One half-record: 64 nibble bytes at `q` (two 64-weight groups), activations xr[32] (128 codes),
-// scales/mins of sub-blocks 4h..4h+3 as packed bytes, pair sums ps[4].  Returns d*isum - dmin*msum.
-__device__ __forceinline__ float half_record(uint32_t q, float d, float dmin, uint32_t sc4, uint32_t mn4,
-                                             const uint32_t (&xr)[32], const int (&ps)[4]) {
-    int isum = 0;
-#pragma unroll
-    for (int jj = 0; jj < 2; ++jj) {
-        const uint4 qa = lds128(q + 32 * jj), qb = lds128(q + 32 * jj + 16);
-        const uint32_t L = 0x0f0f0f0fu, H = 0xf0f0f0f0u;
-        const uint32_t *xa = xr + 16 * jj;
-        int lo = dp4a_us(qa.x & L, xa[0], 0);
-        lo = dp4a_us(qa.y & L, xa[1], lo); lo = dp4a_us(qa.z & L, xa[2], lo); lo = dp4a_us(qa.w & L, xa[3], lo);
-        lo = dp4a_us(qb.x & L, xa[4], lo); lo = dp4a_us(qb.y & L, xa[5], lo);
-        lo = dp4a_us(qb.z & L, xa[6], lo); lo = dp4a_us(qb.w & L, xa[7], lo);
-        // high nibbles left in place: the dot product comes out multiplied by 16, exactly
-        int hi = dp4a_us(qa.x & H, xa[8], 0);
-        hi = dp4a_us(qa.y & H, xa[9], hi); hi = dp4a_us(qa.z & H, xa[10], hi); hi = dp4a_us(qa.w & H, xa[11], hi);
-        hi = dp4a_us(qb.x & H, xa[12], hi); hi = dp4a_us(qb.y & H, xa[13], hi);
-        hi = dp4a_us(qb.z & H, xa[14], hi); hi = dp4a_us(qb.w & H, xa[15], hi);
-        isum += lo * (int)byte_of(sc4, 2 * jj) + (hi >> 4) * (int)byte_of(sc4, 2 * jj + 1);
-    }
-    const int msum = ps[0] * (int)byte_of(mn4, 0) + ps[1] * (int)byte_of(mn4, 1) + ps[2] * (int)byte_of(mn4, 2) + ps[3] * (int)byte_of(mn4, 3);
-    return d * (float)isum - dmin * (float)msum;
-}
-
-// The same for the same half-record position of two different rows at once: two independent
-// instruction streams per lane hide the shared-memory and dp4a latencies of one another.
+// One half-record (64 nibble bytes at q0 / q1: two 64-weight groups) of two different rows at once against
+// the same activations xr[32] (128 codes), scales/mins of sub-blocks 4h..4h+3 from the record headers h0 / h1,
+// bsum pair sums ps[4]; returns d*isum - dmin*msum per row.  Two independent instruction streams per lane
+// hide the shared-memory and dp4a latencies of one another.
 __device__ __forceinline__ void half_record2(uint32_t q0, uint32_t q1, const uint4 &h0, const uint4 &h1, int h,
                                              const uint32_t (&xr)[32], const int (&ps)[4], float &r0, float &r1) {
     const Q4KScales s0 = q4k_unpack_scales(h0.y, h0.z, h0.w), s1 = q4k_unpack_scales(h1.y, h1.z, h1.w);

@@ -133,13 +133,6 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, Co
     return ok != 0;
 }
 
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // Coordinates of one 256-block of this CTA's work list (tiles taken round-robin, blocks in K order),
 // advanced incrementally: no division on the critical path of the producer loop.
 struct BlockAt {
