@@ -46,6 +46,7 @@ WORKLOADS = {
     "q4_k_prefill_4096x4096": ("Q4_K", "prefill", 4096, 4096, 512),
     "q4_k_prefill_4096x14336": ("Q4_K", "prefill", 4096, 14336, 512),
     "tq1_0_prefill_28672x8192": ("TQ1_0", "prefill", 28672, 8192, 512),
+    "q4_k_dequantize_14336x4096": ("Q4_K", "dequantize", 14336, 4096, 0),
 }
 DEFAULT_WORKLOAD = "q4_k_decode_14336x4096"
 L2_BYTES = 126 * 1024 * 1024
@@ -177,6 +178,49 @@ def cpu_mul_mat_runner(fmt: str, n: int, k: int, m: int, w: np.ndarray, x: np.nd
     return run_port, "port"
 
 
+def cpu_dequantize(fmt: str, n: int, k: int, w: np.ndarray, threads: int):
+    """(callable dequantizing the whole matrix on the host cores, kind)."""
+    import oracle
+
+    fid = oracle.FORMAT_IDS[fmt]
+    out = np.empty((n, k), dtype=np.float32)
+    if oracle.ref_available() and fmt != "IQ2_XXS":
+        lib = oracle.ref()
+        pool = ThreadPoolExecutor(max_workers=threads)
+        rb = oracle.row_bytes(fid, k)
+        bounds = [(n * t // threads, n * (t + 1) // threads) for t in range(threads)]
+
+        def run_rows(b):
+            # one call per contiguous range: the reference dequantizer takes an element count, rows are contiguous
+            lib.weft_ref_dequantize(fid, w.ctypes.data + b[0] * rb, out[b[0]:].ctypes.data_as(ctypes.POINTER(ctypes.c_float)), (b[1] - b[0]) * k)
+
+        return (lambda: list(pool.map(run_rows, bounds))), "reference"
+    oracle.port().wo_set_threads(threads)
+    return (lambda: oracle.dequantize(fid, w, k)), "port"
+
+
+def cpu_dequantize_line(args, fmt, n, k, w, grid, signs, threads) -> dict:
+    import oracle
+    from weft_b200.formats import row_bytes
+
+    run, kind = cpu_dequantize(fmt, n, k, w, threads)
+    run()
+    times = []
+    budget = time.perf_counter() + 60.0
+    for _ in range(max(1, args.steps)):
+        t0 = time.perf_counter(); run(); times.append(time.perf_counter() - t0)
+        if time.perf_counter() > budget:
+            break
+    per = sum(times) / len(times)
+    value = (n * row_bytes(fmt, k) + 4 * n * k) / per / 1e9
+    return {"impl": "reference", "metric": "row_dequantize_algorithmic_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": len(times), "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "format": fmt, "mode": "dequantize", "N": n, "K": k, "cpu": oracle.cpu_model()},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": f"{len(times)} x full {n} x {k} dequantize"},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
 def reference_arm(args, fmt, mode, n, k, m) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -184,8 +228,11 @@ def reference_arm(args, fmt, mode, n, k, m) -> None:
     import oracle
 
     oracle.build(ref=True)
-    w, x, grid, signs = make_inputs(fmt, n, k, m, SEED)
+    w, x, grid, signs = make_inputs(fmt, n, k, max(m, 1), SEED)
     threads = os.cpu_count() or 1
+    if mode == "dequantize":
+        print(json.dumps(cpu_dequantize_line(args, fmt, n, k, w, grid, signs, threads)))
+        return
     sample_m = m if mode == "decode" else min(m, 4)       # prefill on CPU: a bounded slice of the token rows
     run, kind = cpu_mul_mat_runner(fmt, n, k, sample_m, w, x[:sample_m], grid, signs, threads)
     for _ in range(max(1, min(args.warmup, 3))):
@@ -219,6 +266,114 @@ def reference_arm(args, fmt, mode, n, k, m) -> None:
 
 
 # ------------------------------------------------------------------ GPU side
+
+def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank) -> None:
+    """row_dequantize over an (n, k) matrix, rows split across ranks (no collective: rows are independent)."""
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from weft_b200.formats import FORMAT_IDS, TQ1_POWERS, row_bytes
+
+    w_host, _, grid, signs = make_inputs(fmt, n, k, 1, SEED)
+    n0, n1 = n * rank // world, n * (rank + 1) // world
+    rows = n1 - n0
+    shard = w_host[n0:n1]
+    copies = min(64, max(2, -(-2 * L2_BYTES // max(1, shard.nbytes)) + 1))
+    w_dev = [torch.from_numpy(shard).cuda() for _ in range(copies)]
+    y_dev = torch.empty((rows, k), device="cuda")
+    grid_dev, signs_dev = torch.from_numpy(grid).cuda(), torch.from_numpy(signs).cuda()
+    powers_dev = torch.tensor(TQ1_POWERS, dtype=torch.int32, device="cuda")
+    name = {"Q4_0": "q4_0", "Q8_0": "q8_0", "Q4_K": "q4_k", "IQ2_XXS": "iq2_xxs", "TQ1_0": "tq1_0"}[fmt]
+    fn = getattr(lib, f"row_dequantize_{name}_rows")
+    extra = [grid_dev.data_ptr(), signs_dev.data_ptr()] if fmt == "IQ2_XXS" else [powers_dev.data_ptr()] if fmt == "TQ1_0" else []
+    fn.argtypes = [ctypes.c_void_p] * (2 + len(extra)) + [ctypes.c_size_t] * 2
+
+    def call(w_ptr, y_ptr):
+        check(fn(w_ptr, *extra, y_ptr, rows, k))
+
+    def step(i):
+        call(w_dev[i % copies].data_ptr(), y_dev.data_ptr())
+
+    step(0)
+    torch.cuda.synchronize()
+    want = oracle.dequantize(oracle.FORMAT_IDS[fmt], shard[:64], k, grid, signs)
+    if not np.array_equal(y_dev[:64].cpu().numpy().view(np.uint32), want.view(np.uint32)):
+        raise SystemExit("parity check failed before timing: dequantize is not bit-exact")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    before = lib.weft_b200_launch_count()
+    begin.record()
+    for i in range(args.steps):
+        step(args.warmup + i)
+    end.record()
+    barrier()
+    launches = int(lib.weft_b200_launch_count() - before)
+    ms = begin.elapsed_time(end) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+        lt = torch.tensor([launches], device="cuda"); dist.all_reduce(lt); launches = int(lt.item())
+    # end to end: host record bytes in, host fp32 out (pinned), copies inside the timed region
+    w_pin = torch.from_numpy(shard).pin_memory()
+    y_pin = torch.empty((rows, k), dtype=torch.float32).pin_memory()
+    e2e_steps = max(3, min(args.steps, 10))
+    call(w_pin.data_ptr(), y_pin.data_ptr())
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        call(w_pin.data_ptr(), y_pin.data_ptr())
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_s = float(t.item())
+    if not np.array_equal(y_pin[:64].numpy().view(np.uint32), want.view(np.uint32)):
+        raise SystemExit("host-buffer dequantize is not bit-exact")
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    peaks, peaks_kind = load_peaks()
+    total_bytes = n * row_bytes(fmt, k) + 4 * n * k
+    shard_bytes = rows * row_bytes(fmt, k) + 4 * rows * k
+    achieved = shard_bytes / (ms * 1e-3) / 1e9
+    line = {"metric": "row_dequantize_algorithmic_gbps", "value": total_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 (bit-exact)", "data": "synthetic",
+            "config": {"workload": args.workload, "format": fmt, "mode": "dequantize", "N": n, "K": k,
+                       "sharding": f"rows split {world} ways, no collective" if world > 1 else "none",
+                       "l2": f"{copies} input copies rotate; the {4 * rows * k / 2**20:.0f} MiB output exceeds L2", "launch": "direct launches", "seed": SEED},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "traffic": None, "peak_source": peaks_kind, "kernel": "dequant kernel (per GPU)", "kernel_ms": ms,
+                         "algorithmic_bytes_per_launch": shard_bytes},
+            "clocks": clocks, "gpu_launches": launches,
+            "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(shard.nbytes), "d2h_bytes_per_step": int(4 * rows * k),
+                    "ms_per_step": e2e_s * 1e3, "what": "row_dequantize_*_rows with host W and Y (pinned)"}}
+    if not args.no_cpu_baseline and world == 1:
+        threads = os.cpu_count() or 1
+        run, kind = cpu_dequantize(fmt, n, k, w_host, threads)
+        run()
+        times, t_end = [], time.perf_counter() + 10.0
+        while time.perf_counter() < t_end and len(times) < 100:
+            t0 = time.perf_counter(); run(); times.append(time.perf_counter() - t0)
+        per = sum(times) / len(times)
+        line["cpu_baseline"] = {"value": total_bytes / per / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+                                "sample": f"{len(times)} x full {n} x {k} dequantize", "cpu": oracle.cpu_model(), "ms_per_step": per * 1e3}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
 
 def main() -> None:
     parser = argparse.ArgumentParser()
@@ -265,6 +420,10 @@ def main() -> None:
     def check(status: int) -> None:
         if status:
             raise SystemExit("weft_b200 call failed: " + last_error(lib))
+
+    if mode == "dequantize":
+        gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
+        return
 
     # ---- inputs, sharded by weight rows
     act = "Q8_0" if fmt in ("Q4_0", "Q8_0") else "Q8_K"
