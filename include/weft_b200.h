@@ -129,6 +129,19 @@ int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const 
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags);
 
+/* ------------------------------------------------------------------ no-allocation variant (no counterpart in the reference)
+ * production_mul_mat_q4_k_decode for hosts that cannot allocate device memory once running (all device
+ * memory owned by the host's own pool, a frozen memory budget, or a loop that cannot afford the device-wide
+ * synchronisation of cudaMalloc).  Host-side X / Xq / Y are staged through a fixed WEFT_B200_NOALLOC_BYTES
+ * array inside the library image instead of an arena grown on demand; nothing is allocated.  W must be
+ * device memory.  Calls needing more staging than the array holds are refused.  Calls are serialised (the
+ * array is shared and keeps the last call's contents); the first call on a device resolves the array's
+ * address and should happen outside stream capture.  Runs on the legacy default stream, returns when done.
+ * Message of the last refusal: weft_b200_noalloc_last_error(). */
+#define WEFT_B200_NOALLOC_BYTES (1 << 20)
+int production_mul_mat_q4_k_decode_noalloc(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+const char *weft_b200_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif
