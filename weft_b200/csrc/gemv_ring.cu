@@ -1,0 +1,263 @@
+// Decode GEMV for Q4_0, Q8_0, IQ2_XXS and TQ1_0 weights whose rows are whole 16-byte multiples:
+// Y[m, n] = quantized_vec_dot(W[n], Xq[m])  (examples/kernels/mul_mat/{q4_0,q8_0,iq2_xxs,tq1_0}_decode.py).
+//
+// Same streaming scheme as the Q4_K kernel: one persistent CTA per SM, a producer warp that fills a
+// CTA-wide shared-memory ring with bulk asynchronous copies of about 18 KB (copies of a few KB each
+// reach well under half of the HBM rate), stages dealt round-robin over the grid so that the whole grid
+// reads one contiguous window of the matrix, consumer warps that wait on a stage's "full" barrier and
+// arrive on its "empty" barrier, bounded waits throughout, programmatic dependent launch.
+//
+// A consumer iteration takes 2 * (32 / L) consecutive rows of one stage, L = lanes per row (the power of
+// two >= units per row, at most 32): lane group g computes rows 2g and 2g + 1 of the iteration, each lane
+// one 256-element unit of both rows per step (two independent instruction streams), and the group
+// reduces with shuffles.  A row is never split across warps, so results do not depend on the grid.
+#include "gemv_units.cuh"
+#include "ring.cuh"
+
+#include <cstdlib>
+
+namespace weft {
+
+namespace {
+
+constexpr int RG_MAX_STAGES = 24;
+constexpr int RG_MAX_THREADS = 512;
+
+struct RingParams {
+    const uint8_t *w;
+    const uint8_t *xq;
+    const float *x;
+    const int8_t *grid;
+    const int8_t *signs;
+    const uint32_t *powers;
+    float *y;
+    long long n;
+    long long ldy;
+    int nb;              // 256-element units per row
+    int log_lanes;       // lanes per row = 1 << log_lanes
+    int log_stage_rows;  // rows per ring stage
+    int log_stages;      // ring depth
+    int full_rounds;
+    int tail_rows;
+    int *status;
+};
+
+template <int FMT, bool QX>
+__global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int UB = Unit<FMT>::BYTES;
+    constexpr bool ACT_Q8_0 = (FMT == F_Q4_0 || FMT == F_Q8_0);
+    constexpr int TABLE_BYTES = FMT == F_IQ2_XXS ? 3072 : 0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nb = p.nb, LSR = p.log_stage_rows, SR = 1 << LSR, LS = p.log_stages, S = 1 << LS;
+    const int LL = p.log_lanes, L = 1 << LL, RPI = 2 * (32 >> LL);   // rows per consumer iteration
+    const uint32_t row_bytes = (uint32_t)nb * UB, stage_bytes = row_bytes << LSR;
+    const int G = gridDim.x, b = blockIdx.x;
+
+    volatile int *s_issued = reinterpret_cast<volatile int *>(smem);
+    uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + 16);
+    uint64_t *s_empty = s_full + RG_MAX_STAGES;
+    uint8_t *s_grid = smem + 512, *s_neg = s_grid + 2048;
+    uint8_t *s_xq = smem + 512 + TABLE_BYTES;
+    uint8_t *s_aux = s_xq + (size_t)nb * XQ_PITCH;
+    uint8_t *s_ring = smem + ((512 + TABLE_BYTES + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127));
+    const uint32_t ring_addr = smem_addr(s_ring), full_addr = smem_addr(s_full), empty_addr = smem_addr(s_empty);
+
+    const long long main_rows = (long long)p.full_rounds * G * SR;
+    const long long tail_begin = min(p.n, main_rows + (long long)b * p.tail_rows);
+    const int tail_here = (int)(min(p.n, tail_begin + p.tail_rows) - tail_begin);
+    const int rows_here = p.full_rounds * SR + tail_here;
+    const int total_stages = p.full_rounds + (tail_here > 0 ? 1 : 0);
+    const size_t xq_row = (size_t)blockIdx.y * nb * (ACT_Q8_0 ? 272 : 292);
+    float *y = p.y + (size_t)blockIdx.y * p.ldy;
+
+    asm volatile("griddepcontrol.launch_dependents;");
+    if (threadIdx.x < S) {
+        mbar_init(s_full + threadIdx.x, 1);
+        mbar_init(s_empty + threadIdx.x, (uint32_t)(SR / RPI));   // one arrival per consumer iteration
+        mbar_fence_init();
+    }
+    if (threadIdx.x == 0) *s_issued = 0;
+    __syncthreads();
+
+    auto issue = [&](int s) {
+        const int slot = s & (S - 1);
+        const bool tail = s >= p.full_rounds;
+        const long long row0 = tail ? tail_begin : ((long long)s * G + b) << LSR;
+        const uint32_t bytes = tail ? (uint32_t)tail_here * row_bytes : stage_bytes;
+        mbar_expect_tx_a(full_addr + 8 * slot, bytes);
+        bulk_g2s_a(ring_addr + (uint32_t)slot * stage_bytes, p.w + (size_t)row0 * row_bytes, bytes, full_addr + 8 * slot);
+    };
+    if (warp == 0 && lane == 0) {
+        const int first = min(S, total_stages);
+        for (int s = 0; s < first; ++s) issue(s);
+        *s_issued = first;
+    }
+
+    // Activations, tables and outputs may belong to the kernel that precedes this one in the stream.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    if (FMT == F_IQ2_XXS) {
+        for (int i = threadIdx.x; i < 2048; i += blockDim.x) s_grid[i] = (uint8_t)p.grid[i];
+        for (int i = threadIdx.x; i < 1024; i += blockDim.x) s_neg[i] = p.signs[i] < 0 ? 0xffu : 0u;
+    }
+    uint32_t pw[5] = {1, 3, 9, 27, 81};
+    if (FMT == F_TQ1_0) {
+#pragma unroll
+        for (int i = 0; i < 5; ++i) pw[i] = __ldg(p.powers + i) & 0xffu;
+    }
+    if (QX) {
+        uint8_t *out = b == 0 ? const_cast<uint8_t *>(p.xq) + xq_row : nullptr;
+        const float *x = p.x + (size_t)blockIdx.y * nb * 256;
+        if (ACT_Q8_0) quantize_stage_q8_0(x, nb, s_xq, s_aux, out); else quantize_stage_q8_k(x, nb, s_xq, s_aux, out);
+    } else {
+        if (ACT_Q8_0) stage_q8_0(p.xq + xq_row, nb, s_xq, s_aux); else stage_q8_k(p.xq + xq_row, nb, s_xq, s_aux);
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int s = S; s < total_stages; ++s) {
+                if (!mbar_wait_a(empty_addr + 8 * (s & (S - 1)), (uint32_t)((s >> LS) - 1) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
+                fence_proxy_async();
+                issue(s);
+                *s_issued = s + 1;
+            }
+        }
+        return;
+    }
+
+    const int consumers = (blockDim.x >> 5) - 1;
+    const int group = lane >> LL, ul = lane & (L - 1);
+    for (int t = RPI * (warp - 1); t < rows_here; t += RPI * consumers) {
+        const int s = t >> LSR;   // SR is a multiple of RPI: the iteration's rows lie in one stage
+        if (*s_issued <= s) {     // a parity wait cannot tell fill n of a slot from fill n-2
+            bool issued = false;
+            for (uint32_t spin = 0; spin < (1u << 24) && !issued; ++spin) issued = *s_issued > s;
+            if (!issued) { report(p.status, ST_WAIT_TIMEOUT); return; }
+        }
+        if (!mbar_wait_a(full_addr + 8 * (s & (S - 1)), (uint32_t)(s >> LS) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
+        const uint8_t *stage = s_ring + (size_t)(s & (S - 1)) * stage_bytes;
+        const int in_stage = (t & (SR - 1)) + 2 * group;
+        const int ta = t + 2 * group;
+        const bool live0 = ta < rows_here, live1 = ta + 1 < rows_here;
+        // rows past the end read row 0 of the stage (always valid) and are dropped
+        const uint8_t *base0 = stage + (size_t)(live0 ? in_stage : 0) * row_bytes;
+        const uint8_t *base1 = stage + (size_t)(live1 ? in_stage + 1 : 0) * row_bytes;
+        float acc[2] = {0.f, 0.f};
+        for (int u = ul; u < nb; u += L) {
+            const uint8_t *const wp[2] = {base0 + (size_t)u * UB, base1 + (size_t)u * UB};
+            const uint8_t *xu = s_xq + u * XQ_PITCH, *xa = s_aux + u * XAUX_BYTES;
+            if (FMT == F_Q4_0) dot_q4_0<2>(wp, xu, xa, acc);
+            else if (FMT == F_Q8_0) dot_q8_0<2>(wp, xu, xa, acc);
+            else if (FMT == F_IQ2_XXS) dot_iq2_xxs<2>(wp, xu, xa, s_grid, s_neg, acc);
+            else dot_tq1_0<2>(wp, xu, xa, pw, acc);
+        }
+        float v0 = acc[0], v1 = acc[1];
+        for (int o = L >> 1; o > 0; o >>= 1) {
+            v0 += __shfl_xor_sync(0xffffffffu, v0, o);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+        }
+        if (FMT == F_IQ2_XXS) { v0 *= 0.125f; v1 *= 0.125f; }
+        __syncwarp();   // every lane's shared loads of this stage have completed
+        if (ul == 0) {
+            const long long grow = s < p.full_rounds ? ((((long long)s * G + b) << LSR) + in_stage) : tail_begin + (ta - (p.full_rounds << LSR));
+            if (live0) y[grow] = v0;
+            if (live1) y[grow + 1] = v1;
+        }
+        if (lane == 0) mbar_arrive_a(empty_addr + 8 * (s & (S - 1)));
+    }
+}
+
+int env_or(const char *name, int fallback) {
+    const char *v = getenv(name);
+    return v && *v ? atoi(v) : fallback;
+}
+const int kRingConsumers = env_or("WEFT_B200_RING_WARPS", 15);
+const int kRingStageBytes = env_or("WEFT_B200_RING_STAGE", 18432);
+const int kRingMaxStages = env_or("WEFT_B200_RING_STAGES", 8);
+const int kRingOverlap = env_or("WEFT_B200_RING_OVERLAP", 1);
+
+struct RingPlan { int log_lanes, log_stage_rows, log_stages; size_t smem; bool ok; };
+
+RingPlan plan_ring(int fmt, long long nb) {
+    RingPlan plan{0, 0, 0, 0, false};
+    const long long row_bytes = nb * unit_bytes(fmt);
+    if (row_bytes % 16 != 0 || nb <= 0) return plan;
+    const long long fixed = (512 + (fmt == F_IQ2_XXS ? 3072 : 0) + nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~127LL;
+    int ll = 0;
+    while ((1 << ll) < 32 && (1 << ll) < nb) ++ll;
+    const int log_rpi = 1 + (5 - ll);
+    int lsr = log_rpi;   // at least one consumer iteration per stage
+    while (lsr < 8 && (row_bytes << (lsr + 1)) <= kRingStageBytes) ++lsr;
+    int ls = 0;
+    while ((1 << (ls + 1)) <= kRingMaxStages && (1 << (ls + 1)) <= RG_MAX_STAGES && fixed + ((row_bytes << lsr) << (ls + 1)) <= 200LL * 1024) ++ls;
+    if (ls < 1) return plan;
+    plan.log_lanes = ll; plan.log_stage_rows = lsr; plan.log_stages = ls;
+    plan.smem = (size_t)(fixed + ((row_bytes << lsr) << ls)) + 16;   // the 2-byte-aligned record loaders read up to 4 bytes past a record
+    plan.ok = true;
+    return plan;
+}
+
+template <int FMT, bool QX>
+cudaError_t launch_variant(const RingParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
+    static int smem_set = 0;
+    if ((int)smem > smem_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_ring_kernel<FMT, QX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        smem_set = (int)smem;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = dim3((unsigned)threads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = kRingOverlap ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, gemv_ring_kernel<FMT, QX>, p);
+}
+
+template <int FMT>
+cudaError_t launch_fmt(const RingParams &p, bool qx, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
+    return qx ? launch_variant<FMT, true>(p, grid, threads, smem, stream) : launch_variant<FMT, false>(p, grid, threads, smem, stream);
+}
+
+}  // namespace
+
+bool gemv_ring_supported(const GemvArgs &a) {
+    if (a.fmt != F_Q4_0 && a.fmt != F_Q8_0 && a.fmt != F_IQ2_XXS && a.fmt != F_TQ1_0) return false;
+    return a.k % 256 == 0 && a.k > 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0 && a.n < (1LL << 30) &&
+           plan_ring(a.fmt, a.k / 256).ok;
+}
+
+cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t stream) {
+    RingParams p;
+    p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.x = a.x;
+    p.grid = a.grid; p.signs = a.signs; p.powers = a.powers; p.y = a.y;
+    p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
+    const RingPlan plan = plan_ring(a.fmt, p.nb);
+    if (!plan.ok) return cudaErrorInvalidConfiguration;
+    p.log_lanes = plan.log_lanes; p.log_stage_rows = plan.log_stage_rows; p.log_stages = plan.log_stages;
+    const long long stage_rows = 1LL << plan.log_stage_rows;
+    long long ctas = (a.n + stage_rows - 1) / stage_rows;
+    if (ctas > sm_count) ctas = sm_count;
+    if (ctas < 1) ctas = 1;
+    p.full_rounds = (int)(a.n / (ctas * stage_rows));
+    const long long rest = a.n - (long long)p.full_rounds * ctas * stage_rows;
+    p.tail_rows = (int)((rest + ctas - 1) / ctas);
+    int consumers = kRingConsumers < 1 ? 1 : (kRingConsumers > RG_MAX_THREADS / 32 - 1 ? RG_MAX_THREADS / 32 - 1 : kRingConsumers);
+    const int threads = (consumers + 1) * 32;
+    dim3 grid((unsigned)ctas, (unsigned)a.m);
+    const bool qx = a.x != nullptr;
+    switch (a.fmt) {
+    case F_Q4_0: return launch_fmt<F_Q4_0>(p, qx, grid, threads, plan.smem, stream);
+    case F_Q8_0: return launch_fmt<F_Q8_0>(p, qx, grid, threads, plan.smem, stream);
+    case F_IQ2_XXS: return launch_fmt<F_IQ2_XXS>(p, qx, grid, threads, plan.smem, stream);
+    default: return launch_fmt<F_TQ1_0>(p, qx, grid, threads, plan.smem, stream);
+    }
+}
+
+}  // namespace weft

@@ -1,0 +1,315 @@
+// Shared pieces of the decode GEMV kernels: the per-format dot product of one 256-element weight unit
+// against one staged activation unit, and the staging of activation records (or of fp32 activations,
+// quantized on the way) into shared memory.
+// (examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q4_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py;
+//  GGML ggml-cpu/quants.c:174-208, 400-428, 645-718, 855-895, 430-480.)
+#pragma once
+
+#include "quantize.cuh"
+#include "kernels.h"
+
+namespace weft {
+
+constexpr int XQ_PITCH = 272;   // 256 code bytes + 16: consecutive units start on different bank groups
+constexpr int XAUX_BYTES = 64;  // per unit: Q8_K {f32 d, i32 total, -, -, i32 pair_sums[8]}; Q8_0 {f32 d[8], i32 sums[8]}
+
+template <int FMT> struct Unit { static constexpr int BYTES = unit_bytes(FMT); };
+
+// ------------------------------------------------------------------ unit dot products
+// Each takes RL weight units (same unit index of RL different rows) against one staged activation unit.
+
+template <int RL>
+__device__ __forceinline__ void dot_q4_k(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux, float (&acc)[RL]) {
+    Q4KScales sc[RL];
+    float d[RL], dmin[RL];
+    int isum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        const uint4 h = *reinterpret_cast<const uint4 *>(wp[r]);
+        d[r] = half_bits_to_float(h.x);
+        dmin[r] = half_bits_to_float(h.x >> 16);
+        sc[r] = q4k_unpack_scales(h.y, h.z, h.w);
+        isum[r] = 0;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 64 * j);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 64 * j + 16);
+        const uint4 xc = *reinterpret_cast<const uint4 *>(xq + 64 * j + 32);
+        const uint4 xd = *reinterpret_cast<const uint4 *>(xq + 64 * j + 48);
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint4 qa = *reinterpret_cast<const uint4 *>(wp[r] + 16 + 32 * j);
+            const uint4 qb = *reinterpret_cast<const uint4 *>(wp[r] + 32 + 32 * j);
+            const uint32_t M = 0x0f0f0f0fu;
+            int lo = dp4a_us(qa.x & M, xa.x, 0);
+            lo = dp4a_us(qa.y & M, xa.y, lo); lo = dp4a_us(qa.z & M, xa.z, lo); lo = dp4a_us(qa.w & M, xa.w, lo);
+            lo = dp4a_us(qb.x & M, xb.x, lo); lo = dp4a_us(qb.y & M, xb.y, lo);
+            lo = dp4a_us(qb.z & M, xb.z, lo); lo = dp4a_us(qb.w & M, xb.w, lo);
+            int hi = dp4a_us((qa.x >> 4) & M, xc.x, 0);
+            hi = dp4a_us((qa.y >> 4) & M, xc.y, hi); hi = dp4a_us((qa.z >> 4) & M, xc.z, hi); hi = dp4a_us((qa.w >> 4) & M, xc.w, hi);
+            hi = dp4a_us((qb.x >> 4) & M, xd.x, hi); hi = dp4a_us((qb.y >> 4) & M, xd.y, hi);
+            hi = dp4a_us((qb.z >> 4) & M, xd.z, hi); hi = dp4a_us((qb.w >> 4) & M, xd.w, hi);
+            const uint32_t scv = j < 2 ? sc[r].sc_lo : sc[r].sc_hi;
+            isum[r] += lo * (int)byte_of(scv, (2 * j) & 3) + hi * (int)byte_of(scv, ((2 * j) & 3) + 1);
+        }
+    }
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    const int4 p0 = *reinterpret_cast<const int4 *>(xaux + 16), p1 = *reinterpret_cast<const int4 *>(xaux + 32);
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        int msum = p0.x * (int)byte_of(sc[r].mn_lo, 0) + p0.y * (int)byte_of(sc[r].mn_lo, 1)
+                 + p0.z * (int)byte_of(sc[r].mn_lo, 2) + p0.w * (int)byte_of(sc[r].mn_lo, 3)
+                 + p1.x * (int)byte_of(sc[r].mn_hi, 0) + p1.y * (int)byte_of(sc[r].mn_hi, 1)
+                 + p1.z * (int)byte_of(sc[r].mn_hi, 2) + p1.w * (int)byte_of(sc[r].mn_hi, 3);
+        acc[r] += xd_ * (d[r] * (float)isum[r] - dmin[r] * (float)msum);
+    }
+}
+
+// 8 consecutive Q4_0 records = 144 bytes. Record r starts at byte 18r: f16 d, then 16 nibble bytes.
+template <int RL>
+__device__ __forceinline__ void dot_q4_0(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux, float (&acc)[RL]) {
+    uint32_t wv[RL][36];
+#pragma unroll
+    for (int r = 0; r < RL; ++r)
+#pragma unroll
+        for (int i = 0; i < 9; ++i) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(wp[r] + 16 * i);
+            wv[r][4 * i] = v.x; wv[r][4 * i + 1] = v.y; wv[r][4 * i + 2] = v.z; wv[r][4 * i + 3] = v.w;
+        }
+#pragma unroll
+    for (int b = 0; b < 8; ++b) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * b);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * b + 16);
+        const float xd_ = *reinterpret_cast<const float *>(xaux + 4 * b);
+        const int xs = *reinterpret_cast<const int *>(xaux + 32 + 4 * b);
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const int w0 = (18 * b) / 4;
+            uint32_t q[4];
+            float d;
+            if (b & 1) {   // record starts 2 bytes into word w0: d in its high half, nibbles word-aligned after it
+                d = half_bits_to_float(wv[r][w0] >> 16);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) q[i] = wv[r][w0 + 1 + i];
+            } else {       // record word-aligned: d in the low half, nibbles straddle words
+                d = half_bits_to_float(wv[r][w0]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) q[i] = __funnelshift_r(wv[r][w0 + i], wv[r][w0 + i + 1], 16);
+            }
+            const uint32_t M = 0x0f0f0f0fu;
+            int s = dp4a_us(q[0] & M, xa.x, 0);
+            s = dp4a_us(q[1] & M, xa.y, s); s = dp4a_us(q[2] & M, xa.z, s); s = dp4a_us(q[3] & M, xa.w, s);
+            s = dp4a_us((q[0] >> 4) & M, xb.x, s); s = dp4a_us((q[1] >> 4) & M, xb.y, s);
+            s = dp4a_us((q[2] >> 4) & M, xb.z, s); s = dp4a_us((q[3] >> 4) & M, xb.w, s);
+            s -= 8 * xs;   // sum((q-8)*x) = sum(q*x) - 8*sum(x)
+            acc[r] += (d * xd_) * (float)s;
+        }
+    }
+}
+
+// 8 consecutive Q8_0 records = 272 bytes. Record r starts at byte 34r: f16 d, then 32 code bytes.
+template <int RL>
+__device__ __forceinline__ void dot_q8_0(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux, float (&acc)[RL]) {
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        uint32_t wv[68];
+#pragma unroll
+        for (int i = 0; i < 17; ++i) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(wp[r] + 16 * i);
+            wv[4 * i] = v.x; wv[4 * i + 1] = v.y; wv[4 * i + 2] = v.z; wv[4 * i + 3] = v.w;
+        }
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * b);
+            const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * b + 16);
+            const float xd_ = *reinterpret_cast<const float *>(xaux + 4 * b);
+            const int w0 = (34 * b) / 4;
+            uint32_t q[8];
+            float d;
+            if (b & 1) {
+                d = half_bits_to_float(wv[w0] >> 16);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) q[i] = wv[w0 + 1 + i];
+            } else {
+                d = half_bits_to_float(wv[w0]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) q[i] = __funnelshift_r(wv[w0 + i], wv[w0 + i + 1], 16);
+            }
+            int s = dp4a_ss(q[0], xa.x, 0);
+            s = dp4a_ss(q[1], xa.y, s); s = dp4a_ss(q[2], xa.z, s); s = dp4a_ss(q[3], xa.w, s);
+            s = dp4a_ss(q[4], xb.x, s); s = dp4a_ss(q[5], xb.y, s); s = dp4a_ss(q[6], xb.z, s); s = dp4a_ss(q[7], xb.w, s);
+            acc[r] += (float)s * (d * xd_);
+        }
+    }
+}
+
+// One IQ2_XXS record (66 bytes, 2-byte aligned): f16 d, then 8 x {4 grid indices, u32 sign/scale word}.
+// s_grid: int8[256][8]; s_neg: per sign index a byte mask, 0xff where the sign is negative (entries are +1/-1).
+template <int RL>
+__device__ __forceinline__ void dot_iq2_xxs(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                             const uint8_t *s_grid, const uint8_t *s_neg, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    uint32_t qw[RL][16];
+    int bsum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<16>(wp[r] + 2, qw[r]); bsum[r] = 0; }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t index = qw[r][2 * g], meta = qw[r][2 * g + 1];
+            int pos = 0, neg = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + 8 * byte_of(index, e));
+                const uint2 nm = *reinterpret_cast<const uint2 *>(s_neg + 8 * ((meta >> (7 * e)) & 127u));
+                pos = dp4a_ss(gv.x, xw[2 * e], pos);
+                pos = dp4a_ss(gv.y, xw[2 * e + 1], pos);
+                neg = dp4a_ss(gv.x & nm.x, xw[2 * e], neg);
+                neg = dp4a_ss(gv.y & nm.y, xw[2 * e + 1], neg);
+            }
+            bsum[r] += (pos - 2 * neg) * (int)(2u * (meta >> 28) + 1u);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
+}
+
+// digits of four packed bytes at once: ((byte*power) & 255) * 3 >> 8, in 16-bit lanes
+__device__ __forceinline__ uint32_t tq1_digits4(uint32_t q4, uint32_t power) {
+    const uint32_t M = 0x00ff00ffu;
+    uint32_t e = ((q4 & M) * power) & M, o = (((q4 >> 8) & M) * power) & M;
+    e = ((e * 3u) >> 8) & M;
+    o = ((o * 3u) >> 8) & M;
+    return e | (o << 8);
+}
+
+// One TQ1_0 record (54 bytes, 2-byte aligned): 32 + 16 bytes of 5 trits, 4 bytes of 4 trits, f16 d.
+// sum((digit-1)*x) = sum(digit*x) - sum(x); every element of the unit is covered exactly once.
+template <int RL>
+__device__ __forceinline__ void dot_tq1_0(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                           const uint32_t (&pw)[5], float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    const int total = *reinterpret_cast<const int *>(xaux + 4);
+    uint32_t wv[RL][14];
+    int sum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<14>(wp[r], wv[r]); sum[r] = -total; }
+#pragma unroll
+    for (int n = 0; n < 5; ++n) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {   // region 0: x[32n + 16h ..], weight words 4h..4h+3
+            const uint4 xv = *reinterpret_cast<const uint4 *>(xq + 32 * n + 16 * h);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int r = 0; r < RL; ++r)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sum[r] = dp4a_us(tq1_digits4(wv[r][4 * h + i], pw[n]), xw[i], sum[r]);
+        }
+        {                                // region 1: x[160 + 16n ..], weight words 8..11
+            const uint4 xv = *reinterpret_cast<const uint4 *>(xq + 160 + 16 * n);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int r = 0; r < RL; ++r)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sum[r] = dp4a_us(tq1_digits4(wv[r][8 + i], pw[n]), xw[i], sum[r]);
+        }
+    }
+    {                                    // region 2: x[240 + 4n ..], weight word 12
+        const uint4 xv = *reinterpret_cast<const uint4 *>(xq + 240);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r)
+#pragma unroll
+            for (int n = 0; n < 4; ++n) sum[r] = dp4a_us(tq1_digits4(wv[r][12], pw[n]), xw[n], sum[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (float)sum[r] * (half_bits_to_float(wv[r][13]) * xd_);
+}
+
+// ------------------------------------------------------------------ activation staging
+
+// Q8_K records (292 B, 4-byte aligned) -> codes at unit*XQ_PITCH, aux {d, total, pair sums}
+__device__ inline void stage_q8_k(const uint8_t *xq, int nb, uint8_t *s_q, uint8_t *s_aux) {
+    for (int i = threadIdx.x; i < nb * 64; i += blockDim.x) {
+        const int u = i >> 6, wd = i & 63;
+        *reinterpret_cast<uint32_t *>(s_q + u * XQ_PITCH + 4 * wd) = *reinterpret_cast<const uint32_t *>(xq + (size_t)u * 292 + 4 + 4 * wd);
+    }
+    for (int u = threadIdx.x; u < nb; u += blockDim.x) {
+        const uint8_t *rec = xq + (size_t)u * 292;
+        int *aux = reinterpret_cast<int *>(s_aux + u * XAUX_BYTES);
+        aux[0] = *reinterpret_cast<const int *>(rec);
+        int total = 0;
+        for (int g = 0; g < 8; ++g) {
+            const uint32_t pr = *reinterpret_cast<const uint32_t *>(rec + 260 + 4 * g);
+            const int s = (int)(int16_t)(pr & 0xffffu) + (int)(int16_t)(pr >> 16);
+            aux[4 + g] = s;
+            total += s;
+        }
+        aux[1] = total;
+    }
+}
+
+// Q8_0 records (34 B, 2-byte aligned), eight per unit -> codes at unit*XQ_PITCH + 32*b, aux {d[8], sums[8]}
+__device__ inline void stage_q8_0(const uint8_t *xq, int nb, uint8_t *s_q, uint8_t *s_aux) {
+    for (int i = threadIdx.x; i < nb * 8; i += blockDim.x) {
+        const int u = i >> 3, b = i & 7;
+        const uint8_t *rec = xq + (size_t)i * 34;
+        reinterpret_cast<float *>(s_aux + u * XAUX_BYTES)[b] = half_bits_to_float(ld_u16(rec));
+        int sum = 0;
+        for (int wd = 0; wd < 8; ++wd) {
+            const uint32_t v = ld_u32_a2(rec + 2 + 4 * wd);
+            *reinterpret_cast<uint32_t *>(s_q + u * XQ_PITCH + 32 * b + 4 * wd) = v;
+            sum = dp4a_ss(v, 0x01010101u, sum);
+        }
+        reinterpret_cast<int *>(s_aux + u * XAUX_BYTES + 32)[b] = sum;
+    }
+}
+
+// fp32 row -> staged Q8_K units (same arithmetic as q8_K_quantize); `out` non-null: also write the records
+__device__ inline void quantize_stage_q8_k(const float *x, int nb, uint8_t *s_q, uint8_t *s_aux, uint8_t *out) {
+    const int lane = threadIdx.x & 31;
+    for (int u = threadIdx.x >> 5; u < nb; u += blockDim.x >> 5) {
+        float v[8];
+        load8<true>(x + u * 256 + 8 * lane, v);
+        uint32_t q0, q1;
+        int sum16;
+        float d;
+        q8_k_warp(v, q0, q1, sum16, d);
+        *reinterpret_cast<uint2 *>(s_q + u * XQ_PITCH + 8 * lane) = make_uint2(q0, q1);
+        // pair sum g covers 32 codes = lanes 4g..4g+3; total = all 32 lanes
+        int s32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+        int total = s32;
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+        int *aux = reinterpret_cast<int *>(s_aux + u * XAUX_BYTES);
+        if ((lane & 3) == 0) aux[4 + (lane >> 2)] = s32;
+        if (lane == 0) { aux[0] = __float_as_int(d); aux[1] = total; }
+        if (out) store_q8_k(out + (size_t)u * 292, lane, q0, q1, sum16, d);
+    }
+}
+
+// fp32 row -> staged Q8_0 units (same arithmetic as q8_0_quantize); the staged d is the stored f16 value
+__device__ inline void quantize_stage_q8_0(const float *x, int nb, uint8_t *s_q, uint8_t *s_aux, uint8_t *out) {
+    const int lane = threadIdx.x & 31, b = lane >> 2, sub = lane & 3;
+    for (int u = threadIdx.x >> 5; u < nb; u += blockDim.x >> 5) {
+        float v[8];
+        load8<true>(x + u * 256 + 8 * lane, v);
+        uint32_t q0, q1;
+        int sum32;
+        float d;
+        q8_0_warp(v, q0, q1, sum32, d);
+        *reinterpret_cast<uint2 *>(s_q + u * XQ_PITCH + 8 * lane) = make_uint2(q0, q1);
+        if (sub == 0) {
+            reinterpret_cast<float *>(s_aux + u * XAUX_BYTES)[b] = __half2float(__float2half_rn(d));
+            reinterpret_cast<int *>(s_aux + u * XAUX_BYTES + 32)[b] = sum32;
+        }
+        if (out) store_q8_0(out + ((size_t)u * 8 + b) * 34, sub, q0, q1, d);
+    }
+}
+
+}  // namespace weft

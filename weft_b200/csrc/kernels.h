@@ -30,6 +30,9 @@ cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream);
 // Q4_K x Q8_K specialisation (producer/consumer ring, activations in registers)
 bool gemv_q4k_supported(const GemvArgs &a);
 cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream);
+// Q4_0 / Q8_0 / IQ2_XXS / TQ1_0 with 16-byte-multiple rows: the same CTA-wide producer/consumer ring
+bool gemv_ring_supported(const GemvArgs &a);
+cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t stream);
 
 struct PrefillArgs {
     int fmt;
