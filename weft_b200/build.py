@@ -16,7 +16,7 @@ PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libweft_b200.so"
 SOURCES = ["abi.cu", "abi_noalloc.cu", "dequantize.cu", "quantize.cu", "gemv.cu", "gemv_q4k.cu", "gemv_ring.cu", "prefill.cu"]
-HEADERS = ["common.cuh", "quantize.cuh", "kernels.h", "../../include/weft_b200.h"]
+HEADERS = ["common.cuh", "quantize.cuh", "kernels.h", "gemv_units.cuh", "ring.cuh", "tcgen05.cuh", "tensormap.cuh", "../../include/weft_b200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

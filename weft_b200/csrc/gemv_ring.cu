@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int UB = Unit<FMT>::BYTES;
     constexpr bool ACT_Q8_0 = (FMT == F_Q4_0 || FMT == F_Q8_0);
-    constexpr int TABLE_BYTES = FMT == F_IQ2_XXS ? 3072 : 0;
+    constexpr int TABLE_BYTES = FMT == F_IQ2_XXS ? 4096 : 0;   // grid, sign masks, compressed grid
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = p.nb, LSR = p.log_stage_rows, SR = 1 << LSR, LS = p.log_stages, S = 1 << LS;
     const int LL = p.log_lanes, L = 1 << LL, RPI = 2 * (32 >> LL);   // rows per consumer iteration
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
     volatile int *s_issued = reinterpret_cast<volatile int *>(smem);
     uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + 16);
     uint64_t *s_empty = s_full + RG_MAX_STAGES;
-    uint8_t *s_grid = smem + 512, *s_neg = s_grid + 2048;
+    uint8_t *s_grid = smem + 512, *s_neg = s_grid + 2048, *s_sel = s_neg + 1024;
     uint8_t *s_xq = smem + 512 + TABLE_BYTES;
     uint8_t *s_aux = s_xq + (size_t)nb * XQ_PITCH;
     uint8_t *s_ring = smem + ((512 + TABLE_BYTES + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127));
@@ -97,10 +97,8 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
     // Activations, tables and outputs may belong to the kernel that precedes this one in the stream.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    if (FMT == F_IQ2_XXS) {
-        for (int i = threadIdx.x; i < 2048; i += blockDim.x) s_grid[i] = (uint8_t)p.grid[i];
-        for (int i = threadIdx.x; i < 1024; i += blockDim.x) s_neg[i] = p.signs[i] < 0 ? 0xffu : 0u;
-    }
+    bool own_tables = false;
+    if (FMT == F_IQ2_XXS) own_tables = stage_iq2_tables(p.grid, p.signs, s_grid, s_neg, s_sel);
     uint32_t pw[5] = {1, 3, 9, 27, 81};
     if (FMT == F_TQ1_0) {
 #pragma unroll
@@ -150,7 +148,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
             const uint8_t *xu = s_xq + u * XQ_PITCH, *xa = s_aux + u * XAUX_BYTES;
             if (FMT == F_Q4_0) dot_q4_0<2>(wp, xu, xa, acc);
             else if (FMT == F_Q8_0) dot_q8_0<2>(wp, xu, xa, acc);
-            else if (FMT == F_IQ2_XXS) dot_iq2_xxs<2>(wp, xu, xa, s_grid, s_neg, acc);
+            else if (FMT == F_IQ2_XXS) { if (own_tables) dot_iq2_xxs_fast<2>(wp, xu, xa, s_sel, acc); else dot_iq2_xxs<2>(wp, xu, xa, s_grid, s_neg, acc); }
             else dot_tq1_0<2>(wp, xu, xa, pw, acc);
         }
         float v0 = acc[0], v1 = acc[1];
@@ -184,7 +182,7 @@ RingPlan plan_ring(int fmt, long long nb) {
     RingPlan plan{0, 0, 0, 0, false};
     const long long row_bytes = nb * unit_bytes(fmt);
     if (row_bytes % 16 != 0 || nb <= 0) return plan;
-    const long long fixed = (512 + (fmt == F_IQ2_XXS ? 3072 : 0) + nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~127LL;
+    const long long fixed = (512 + (fmt == F_IQ2_XXS ? 4096 : 0) + nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~127LL;
     int ll = 0;
     while ((1 << ll) < 32 && (1 << ll) < nb) ++ll;
     const int log_rpi = 1 + (5 - ll);

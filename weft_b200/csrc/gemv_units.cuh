@@ -179,6 +179,77 @@ __device__ __forceinline__ void dot_iq2_xxs(const uint8_t *const (&wp)[RL], cons
     for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
 }
 
+// The same record against codebooks in compressed form, usable when the tables passed by the caller are the
+// format's own (every grid byte one of 0x08 / 0x19 / 0x2b; sign row i negative exactly at the set bits of
+// i | parity(i) << 7).  s_sel: per grid entry eight 4-bit selectors into the byte pool {0x08, 0x19, 0x2b},
+// one 32-bit word per entry: a lookup is one 4-byte shared load (random 8-byte loads of the full table
+// serialize on bank conflicts, which is what bounds the uncompressed version) plus two byte permutes.
+// Signs are applied to the grid bytes arithmetically: g' = (g ^ m) + t, t = 0x01 and m = 0xff in negative bytes.
+__device__ __forceinline__ uint32_t iq2_signed4(uint32_t g, uint32_t bits4) {
+    const uint32_t t = (bits4 * 0x00204081u) & 0x01010101u;
+    return (g ^ (t * 0xffu)) + t;
+}
+template <int RL>
+__device__ __forceinline__ void dot_iq2_xxs_fast(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                                  const uint8_t *s_sel, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    uint32_t qw[RL][16];
+    int bsum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<16>(wp[r] + 2, qw[r]); bsum[r] = 0; }
+    const uint32_t POOL = 0x002b1908u;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t index = qw[r][2 * g], meta = qw[r][2 * g + 1];
+            int sum = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t sel = *reinterpret_cast<const uint32_t *>(s_sel + 4 * byte_of(index, e));
+                const uint32_t s7 = (meta >> (7 * e)) & 127u;
+                const uint32_t s8 = s7 | ((__popc(s7) & 1u) << 7);
+                const uint32_t glo = iq2_signed4(__byte_perm(POOL, 0, sel), s8 & 15u);
+                const uint32_t ghi = iq2_signed4(__byte_perm(POOL, 0, sel >> 16), s8 >> 4);
+                sum = dp4a_ss(glo, xw[2 * e], sum);
+                sum = dp4a_ss(ghi, xw[2 * e + 1], sum);
+            }
+            bsum[r] += sum * (int)(2u * (meta >> 28) + 1u);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
+}
+
+// Stage the IQ2_XXS codebooks: the full tables (grid bytes, sign masks) and the compressed selectors.
+// Returns (to every thread of the CTA) whether the tables are the format's own.
+__device__ inline bool stage_iq2_tables(const int8_t *grid, const int8_t *signs, uint8_t *s_grid, uint8_t *s_neg, uint8_t *s_sel) {
+    int bad = 0;
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        uint32_t sel = 0;
+        for (int j = 0; j < 8; ++j) {
+            const uint8_t v = (uint8_t)grid[8 * i + j];
+            s_grid[8 * i + j] = v;
+            const uint32_t code = v == 0x08 ? 0u : v == 0x19 ? 1u : v == 0x2b ? 2u : 3u;
+            bad |= code == 3u;
+            sel |= code << (4 * j);
+        }
+        reinterpret_cast<uint32_t *>(s_sel)[i] = sel;
+    }
+    for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+        const uint32_t s8 = (uint32_t)i | ((__popc((uint32_t)i) & 1u) << 7);
+        for (int j = 0; j < 8; ++j) {
+            const int8_t v = signs[8 * i + j];
+            s_neg[8 * i + j] = v < 0 ? 0xffu : 0u;
+            bad |= v != (((s8 >> j) & 1u) ? -1 : 1);
+        }
+    }
+    return __syncthreads_or(bad) == 0;
+}
+
 // digits of four packed bytes at once: ((byte*power) & 255) * 3 >> 8, in 16-bit lanes
 __device__ __forceinline__ uint32_t tq1_digits4(uint32_t q4, uint32_t power) {
     const uint32_t M = 0x00ff00ffu;

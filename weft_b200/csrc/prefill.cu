@@ -20,15 +20,19 @@
 // CTA = 128 tokens (TMEM lanes) x 128 weights, persistent over tiles.  The 128 weights are two halves of
 // 64; each half owns 192 TMEM columns ([q*a | q*c | min term]), so the tensor core works on one half
 // while the epilogue drains the other.  Warp roles:
-//   warps 0-3  epilogue: tcgen05.ld the accumulators, combine, keep 128 x 128 fp32 in registers
-//   warps 4-7  producers: read Q4_K records and Q8_K records from global memory (in place, no repack in
-//              HBM; next block prefetched in registers), expand them into the 128-byte-swizzled K-major
-//              layout the MMA reads from shared memory
-//   warp 8     allocates TMEM; one lane issues the MMAs and commits them to mbarriers
-// Two shared-memory stages let the producers run one 256-block ahead of the tensor core.  Every wait is
+//   warps 0-7   epilogue, warp = (half, 32-token quarter): tcgen05.ld the accumulators, combine, keep
+//               32 x 64 fp32 in registers across the blocks of a tile
+//   warps 8-11  weight producers, one weight row per thread: Q4_K records arrive in a raw ring by
+//               144-byte bulk copies (in place, no repack in HBM) and are expanded into the
+//               128-byte-swizzled K-major layout the MMA reads from shared memory
+//   warps 12-14 activation producers: Q8_K codes, scales and bsums read from global memory one block
+//               ahead (in registers) and stored into the swizzled A slot when it is free
+//   warp 15     allocates TMEM; one lane issues the MMAs and commits them to mbarriers
+// Two activation slots and three weight slots let the producers run ahead of the tensor core.  Every wait is
 // bounded; a wait that runs out sets an abort flag, all roles leave their loops, TMEM is freed, and the
 // host sees a status code instead of a hang.
 #include "tcgen05.cuh"
+#include "tensormap.cuh"
 #include "kernels.h"
 
 #include <cstdlib>
@@ -40,7 +44,8 @@ namespace {
 constexpr int PF_BM = 128;               // tokens per tile = TMEM lanes
 constexpr int PF_BN = 128;               // weights per tile, two halves of 64
 constexpr int PF_HALF = 64;
-constexpr int PF_THREADS = 288;          // 4 epilogue + 4 producer + 1 MMA warp
+constexpr int PF_THREADS = 512;          // 8 epilogue + 4 weight producer + 3 activation producer + 1 MMA warp
+constexpr int PF_W_WARP0 = 8, PF_A_WARP0 = 12, PF_MMA_WARP = 15;
 
 // Shared memory.  int8 operands live in 128-byte-swizzled slabs of 128 K-bytes (K = 256 -> two slabs);
 // the f16 min-term operands are unswizzled core matrices.
@@ -54,8 +59,9 @@ constexpr int PF_B_Q = 2 * PF_B_SLAB;
 constexpr int PF_B_M = PF_HALF * 32;                   // {mn, 64 mn} f16 per weight
 constexpr int PF_B_SLOT = PF_B_Q + PF_B_M;             // 34 KB, one 256-block of one 64-weight half
 constexpr int PF_B_SLOTS = 3;
-constexpr int PF_RAW_SLOT = PF_BN * 144;               // 18 KB of Q4_K records as they are in HBM
-constexpr int PF_RAW_SLOTS = 2;
+constexpr int PF_RAWA_WORDS = 76;                      // 304 bytes: a Q8_K record (292) from the 16-byte boundary at or before it
+constexpr int PF_RAWA_PITCH = 4 * PF_RAWA_WORDS;
+constexpr int PF_RAWA_SLOT = PF_BM * PF_RAWA_PITCH;    // 38 KB: one 256-block of Q8_K records as they are in HBM
 constexpr int PF_WD_SLOT = PF_HALF * 8;                // {d, dmin} per weight of one half
 constexpr int PF_WD_SLOTS = 8;
 constexpr int PF_XD_SLOT = PF_BM * 4;                  // x.ds per token
@@ -63,13 +69,14 @@ constexpr int PF_XD_SLOTS = 4;
 constexpr int PF_CONTROL = 1024;
 constexpr int PF_OFF_A = PF_CONTROL;
 constexpr int PF_OFF_B = PF_OFF_A + PF_A_SLOTS * PF_A_SLOT;
-constexpr int PF_OFF_RAW = PF_OFF_B + PF_B_SLOTS * PF_B_SLOT;
-constexpr int PF_OFF_WD = PF_OFF_RAW + PF_RAW_SLOTS * PF_RAW_SLOT;
+constexpr int PF_OFF_RAWA = PF_OFF_B + PF_B_SLOTS * PF_B_SLOT;
+constexpr int PF_OFF_WD = PF_OFF_RAWA + PF_RAWA_SLOT;
 constexpr int PF_OFF_XD = PF_OFF_WD + PF_WD_SLOTS * PF_WD_SLOT;
 constexpr int PF_SMEM = PF_OFF_XD + PF_XD_SLOTS * PF_XD_SLOT;
 constexpr int PF_TMEM_COLS = 512;                      // 2 x 192 used
 constexpr int PF_HALF_COLS = 192;
 static_assert(PF_A_SLOT % 1024 == 0 && PF_B_SLOT % 1024 == 0 && PF_OFF_B % 1024 == 0, "swizzled slabs must stay 1024-byte aligned");
+static_assert(PF_OFF_RAWA % 128 == 0, "TMA destinations are 128-byte aligned");
 static_assert(PF_SMEM <= 227 * 1024, "shared memory budget");
 
 struct PfParams {
@@ -79,7 +86,6 @@ struct PfParams {
     long long n, m, ldy;
     int nb;               // 256-blocks per row
     int m_tiles, n_tiles;
-    int debug;            // timing experiments (bit mask of work to skip); 0 in normal use
     int *status;
 };
 
@@ -92,6 +98,16 @@ __device__ __forceinline__ uint32_t core_offset(int row, int chunk, int chunks) 
     return (uint32_t)((row >> 3) * (chunks * 128) + chunk * 128 + (row & 7) * 16);
 }
 
+// f32(8 * hi + lo), rounded to nearest like an int-to-float conversion of the sum, on the full-rate fp32 pipe
+// (the conversion unit runs at a quarter of it): |hi|, |lo| <= 256 * 105 * 128 < 2^22, so adding the integer
+// to the bit pattern of 1.5 * 2^23 and subtracting that constant gives its exact float; 8 * f(hi) + f(lo) is
+// exact before the single rounding of the fused multiply-add.
+__device__ __forceinline__ float limbs_to_float(uint32_t hi, uint32_t lo) {
+    const float fh = __uint_as_float(hi + 0x4b400000u) - 12582912.f;
+    const float fl = __uint_as_float(lo + 0x4b400000u) - 12582912.f;
+    return fmaf(8.f, fh, fl);
+}
+
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
 }
@@ -99,14 +115,15 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 struct Control {
     uint64_t a_full[PF_A_SLOTS], a_empty[PF_A_SLOTS];
     uint64_t b_full[PF_B_SLOTS], b_empty[PF_B_SLOTS];
-    uint64_t raw_full[PF_RAW_SLOTS], raw_empty[PF_RAW_SLOTS];
+    uint64_t rawa_full, rawa_empty;
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     volatile int abort;
 };
 
 // Bounded wait by ONE thread that also gives up as soon as another role has aborted.  test_wait does not
-// suspend the thread: the hand-offs between the roles are on the critical path of every 256-block.
+// suspend the thread: the hand-offs between the roles are on the critical path of every 256-block
+// (measured: try_wait with a suspend hint makes every hand-off, and the whole kernel, 1.6x slower).
 __device__ __forceinline__ bool wait_one(uint64_t *bar, uint32_t parity, Control *ctl, int *status) {
     const uint32_t addr = smem_addr(bar);
     for (uint32_t i = 0; i < (1u << 26); ++i) {
@@ -133,6 +150,17 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, Co
     return ok != 0;
 }
 
+#ifdef WEFT_PF_PROFILE
+__device__ unsigned long long g_pf_prof[16][8];
+#define PF_TIMED(slot, call) ([&] { const long long t_ = clock64(); const bool r_ = (call); prof[slot] += clock64() - t_; return r_; }())
+#define PF_MARK(slot) do { const long long n_ = clock64(); prof[slot] += n_ - mark; mark = n_; } while (0)
+#define PF_MARK0() (mark = clock64())
+#else
+#define PF_TIMED(slot, call) (call)
+#define PF_MARK(slot) do { } while (0)
+#define PF_MARK0() do { } while (0)
+#endif
+
 // Coordinates of one 256-block of this CTA's work list (tiles taken round-robin, blocks in K order),
 // advanced incrementally: no division on the critical path of the producer loop.
 struct BlockAt {
@@ -157,76 +185,83 @@ __device__ __forceinline__ BlockAt first_block(const PfParams &p, int steps) {
 
 // ---- producer pieces -----------------------------------------------------------------------------------
 
-// Activation codes of one block, coalesced: for each of the warp's 32 token rows, lane l takes code words
-// l and 32+l (4-byte loads: Q8_K codes start 4 bytes into a 292-byte record, so nothing wider is
-// aligned).  Loaded into registers early, stored into the swizzled A slot after the weight expansion.
-__device__ __forceinline__ void load_codes(const PfParams &p, const BlockAt &at, int wg, int lane, uint32_t (&xa)[64]) {
-    const size_t x_row_bytes = (size_t)p.nb * 292;
-    const uint8_t *src = p.xq + (size_t)(at.m0 + wg * 32) * x_row_bytes + (size_t)at.b * 292 + 4 + 4 * lane;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        if (at.m0 + wg * 32 + i < p.m) {
-            xa[2 * i] = __ldg(reinterpret_cast<const uint32_t *>(src));
-            xa[2 * i + 1] = __ldg(reinterpret_cast<const uint32_t *>(src + 128));
-        } else {
-            xa[2 * i] = 0; xa[2 * i + 1] = 0;
-        }
-        src += x_row_bytes;
-    }
-}
-__device__ __forceinline__ void store_codes(const uint32_t (&xa)[64], uint8_t *a_slot, int wg, int lane) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        const uint32_t at = sw128_offset(wg * 32 + i, lane >> 2) + (lane & 3) * 4;
-        *reinterpret_cast<uint32_t *>(a_slot + at) = xa[2 * i];                  // K bytes 0..127
-        *reinterpret_cast<uint32_t *>(a_slot + PF_A_SLAB + at) = xa[2 * i + 1];  // K bytes 128..255
-    }
-}
+constexpr int PF_A_WARPS = 3;                                        // activation producer warps
+constexpr int PF_A_ROWS = (PF_BM + PF_A_WARPS - 1) / PF_A_WARPS;     // token rows per warp: wa, wa + 3, ...
+constexpr int PF_SP_ITEMS = (PF_BM * 9 + 32 * PF_A_WARPS - 1) / (32 * PF_A_WARPS);
 
-// The nine other words of each record (x.ds and eight bsum pairs): 32 rows x 9 words per warp, dealt to
-// the lanes as item j = lane + 32 t (row j / 9, word j % 9), so neighbouring lanes read neighbouring words.
-__device__ __forceinline__ void load_specials(const PfParams &p, const BlockAt &at, int wg, int lane, uint32_t (&sp)[9]) {
-    const size_t x_row_bytes = (size_t)p.nb * 292;
-#pragma unroll
-    for (int t = 0; t < 9; ++t) {
-        const int j = lane + 32 * t, i = j / 9, wd = j - 9 * i;
-        const long long m = at.m0 + wg * 32 + i;
-        sp[t] = 0;
-        if (m < p.m) {
-            const uint32_t *words = reinterpret_cast<const uint32_t *>(p.xq + (size_t)m * x_row_bytes + (size_t)at.b * 292);
-            sp[t] = __ldg(words + (wd == 0 ? 0 : 64 + wd));
-        }
-    }
-}
-
-// x.ds to the scale ring; each bsum pair s = 64 h + l (l in 0..63) to the f16 min-term operand {l | h}.
-__device__ __forceinline__ void store_specials(const uint32_t (&sp)[9], uint8_t *a_slot, uint8_t *xd_slot, int wg, int lane) {
-    uint8_t *a_m = a_slot + PF_A_Q;
-#pragma unroll
-    for (int t = 0; t < 9; ++t) {
-        const int j = lane + 32 * t, i = j / 9, wd = j - 9 * i;
-        const int r = wg * 32 + i;
-        if (wd == 0) {
-            reinterpret_cast<uint32_t *>(xd_slot)[r] = sp[t];
-        } else {
-            const int g = wd - 1;
-            const int s = (int)(int16_t)(sp[t] & 0xffffu) + (int)(int16_t)(sp[t] >> 16);
-            const int l = s & 63;
-            *reinterpret_cast<__half *>(a_m + core_offset(r, 0, 2) + 2 * g) = __float2half_rn((float)l);
-            *reinterpret_cast<__half *>(a_m + core_offset(r, 1, 2) + 2 * g) = __float2half_rn((float)((s - l) >> 6));
-        }
-    }
-}
-
-// One thread asks for its weight row's record of the block: a 144-byte bulk copy into the raw slot.
-__device__ __forceinline__ void issue_raw(const PfParams &p, const BlockAt &at, uint8_t *raw_slot, int row, uint64_t *bar) {
+// A weight producer thread reads its row's Q4_K record of a block straight from global memory (nine
+// 16-byte loads, one block ahead of its use, in place: no repack in HBM).  Rows past N read as zero.
+__device__ __forceinline__ void load_record(const PfParams &p, const BlockAt &at, int row, uint4 (&w)[9]) {
     const long long n = at.n0 + row;
     if (n < p.n) {
-        mbar_expect_tx(bar, 144);
-        bulk_g2s(raw_slot + row * 144, p.w + ((size_t)n * p.nb + at.b) * 144, 144, bar);
+        const uint4 *rec = reinterpret_cast<const uint4 *>(p.w + ((size_t)n * p.nb + at.b) * 144);
+#pragma unroll
+        for (int i = 0; i < 9; ++i) w[i] = __ldg(rec + i);
     } else {
-        mbar_arrive(bar);   // past the last weight row: whatever is in the slot is expanded, its columns are never stored
+#pragma unroll
+        for (int i = 0; i < 9; ++i) w[i] = make_uint4(0, 0, 0, 0);
     }
+}
+// One elected thread asks for the tile's Q8_K records of a block with one TMA box copy.  A record starts 4 * (b & 3) bytes past a 16-byte boundary (rows are
+// 16-byte multiples because K is a multiple of 1024), so the box starts at that boundary and is 304 bytes wide.
+__device__ __forceinline__ void issue_raw_a(const CUtensorMap *map, const BlockAt &at, uint8_t *raw, uint64_t *bar) {
+    mbar_expect_tx(bar, PF_RAWA_SLOT);
+    tma_load_2d(raw, map, 73 * at.b - (at.b & 3), (int)at.m0, bar);
+}
+
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory"); }
+
+// Raw Q8_K records -> the MMA's activation operands.
+// Codes: warp wa takes the 8-row groups wa, wa + 3, ...; within a group lane l moves code words l and 32 + l
+// of each row into the swizzled A slabs: sixteen independent loads, then sixteen stores, all at offsets
+// that are compile-time constants from per-lane bases.
+// The nine other words of each record: bsum pair g of row r is item j = 8 r + g, dealt to the 96 threads as
+// j = thread + 96 t (so a thread keeps its g and walks 12 rows at a time); the pair s = 64 h + l
+// (l in 0..63) goes to the f16 min-term operand {l | h}.  x.ds of rows thread, thread + 96 goes to the scale ring.
+__device__ __forceinline__ void relayout_activations(const uint8_t *raw, int shift, uint8_t *a_slot, uint8_t *xd_slot, int wa, int ta, int lane) {
+    const uint32_t src = smem_addr(raw) + (uint32_t)shift + 4u + 4u * (uint32_t)lane;
+    const uint32_t dst = smem_addr(a_slot) + (uint32_t)(lane & 3) * 4u;
+    const uint32_t ch = (uint32_t)lane >> 2;
+    for (int grp = wa; grp < PF_BM / 8; grp += PF_A_WARPS) {
+        uint32_t c[16];
+        const uint32_t s0 = src + (uint32_t)grp * (8 * PF_RAWA_PITCH), d0 = dst + (uint32_t)grp * 1024u;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            c[2 * i] = lds_u32(s0 + i * PF_RAWA_PITCH);
+            c[2 * i + 1] = lds_u32(s0 + i * PF_RAWA_PITCH + 128);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t at = d0 + i * 128 + ((ch ^ (uint32_t)i) << 4);
+            sts_u32(at, c[2 * i]);                  // K bytes 0..127
+            sts_u32(at + PF_A_SLAB, c[2 * i + 1]);  // K bytes 128..255
+        }
+    }
+    const uint32_t raw_s = smem_addr(raw) + (uint32_t)shift;
+    {
+        const int g = ta & 7, r0 = ta >> 3;
+        const uint32_t a_m = smem_addr(a_slot) + PF_A_Q + 2u * (uint32_t)g;
+        uint32_t v[11];
+#pragma unroll
+        for (int t = 0; t < 11; ++t) v[t] = (t < 10 || ta < 64) ? lds_u32(raw_s + (uint32_t)(r0 + 12 * t) * PF_RAWA_PITCH + 260u + 4u * (uint32_t)g) : 0u;
+#pragma unroll
+        for (int t = 0; t < 11; ++t) {
+            const int r = r0 + 12 * t;
+            if (t == 10 && ta >= 64) break;
+            const int s_ = (int)(int16_t)(v[t] & 0xffffu) + (int)(int16_t)(v[t] >> 16);
+            const int l = s_ & 63, h = (s_ - l) >> 6;
+            const uint32_t at = a_m + (uint32_t)r * 16u + (uint32_t)(r >> 3) * 128u;   // core_offset(r, 0, 2)
+            sts_u16(at, (uint32_t)__half_as_ushort(__int2half_rn(l)));
+            sts_u16(at + 128u, (uint32_t)__half_as_ushort(__int2half_rn(h)));
+        }
+    }
+    for (int r = ta; r < PF_BM; r += 32 * PF_A_WARPS) reinterpret_cast<uint32_t *>(xd_slot)[r] = lds_u32(raw_s + (uint32_t)r * PF_RAWA_PITCH);
 }
 
 // Expand one Q4_K record (in registers) into this half's B slot: rows rh (q*a) and 64+rh (q*c) of both
@@ -264,7 +299,7 @@ __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_s
     }
 }
 
-__global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams p) {
+__global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams p, const __grid_constant__ CUtensorMap x_map) {
     extern __shared__ __align__(1024) uint8_t smem[];
     Control *ctl = reinterpret_cast<Control *>(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -274,70 +309,80 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
     const int total = my_tiles * nb;   // 256-blocks this CTA works through
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PF_A_SLOTS; ++s) { mbar_init(&ctl->a_full[s], 4); mbar_init(&ctl->a_empty[s], 1); }
+        for (int s = 0; s < PF_A_SLOTS; ++s) { mbar_init(&ctl->a_full[s], PF_A_WARPS); mbar_init(&ctl->a_empty[s], 1); }
         for (int s = 0; s < PF_B_SLOTS; ++s) { mbar_init(&ctl->b_full[s], 2); mbar_init(&ctl->b_empty[s], 1); }
-        for (int s = 0; s < PF_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 128); mbar_init(&ctl->raw_empty[s], 4); }
+        mbar_init(&ctl->rawa_full, 1); mbar_init(&ctl->rawa_empty, PF_A_WARPS);
         for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 4); }
         ctl->abort = 0;
         ctl->tmem_base = 0xffffffffu;
         mbar_fence_init();
     }
     __syncthreads();
-    if (warp == 8) tc::tmem_alloc(&ctl->tmem_base, PF_TMEM_COLS);
+    if (warp == PF_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PF_TMEM_COLS);
     tc::fence_before_sync();
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = ctl->tmem_base;
+#ifdef WEFT_PF_PROFILE
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_begin = clock64();
+    long long mark = prof_begin;
+#endif
 
-    if (warp >= 4 && warp < 8) {
-        // ------------------------------------------------------------------ producers
-        const int row = threadIdx.x - 128, wg = warp - 4, half = row >> 6, rh = row & 63;
-        uint8_t *a_ring = smem + PF_OFF_A, *b_ring = smem + PF_OFF_B, *raw_ring = smem + PF_OFF_RAW;
-        if (total > 0 && !(p.debug & 4)) {
-            issue_raw(p, first_block(p, 0), raw_ring, row, &ctl->raw_full[0]);
-            if (total > 1) issue_raw(p, first_block(p, 1), raw_ring + PF_RAW_SLOT, row, &ctl->raw_full[1]);
-        }
-        BlockAt cur = first_block(p, 0), next2 = first_block(p, 2);   // blocks it and it+2
-        for (int it = 0; it < total && !ctl->abort; ++it, cur.advance(p), next2.advance(p)) {
-            const int sa = it & 1;
-            // activations of this block: the slot was last read by the MMAs of block it-2
-            if (!wait_or_abort(&ctl->a_empty[sa], (uint32_t)((it >> 1) & 1) ^ 1u, ctl, p.status)) break;
-            uint32_t sp[9];
-            uint32_t xa[64];
-            if (!(p.debug & 1)) load_codes(p, cur, wg, lane, xa);   // in flight while the weights are expanded
-            if (!(p.debug & 2)) load_specials(p, cur, wg, lane, sp);
-
-            // weights: this thread's record is in the raw slot
-            if (!(p.debug & 4) && !wait_or_abort(&ctl->raw_full[sa], (uint32_t)((it >> 1) & 1), ctl, p.status)) break;
+    if (warp >= PF_W_WARP0 && warp < PF_W_WARP0 + 4) {
+        // ------------------------------------------------------------------ weight producers
+        const int row = threadIdx.x - 32 * PF_W_WARP0, half = row >> 6, rh = row & 63;
+        uint8_t *b_ring = smem + PF_OFF_B;
+        BlockAt next = first_block(p, 0);
+        uint4 wn[9];
+        if (total > 0) load_record(p, next, row, wn);
+        for (int it = 0; it < total && !ctl->abort; ++it) {
             uint4 w[9];
-            {
-                const uint4 *rec = reinterpret_cast<const uint4 *>(raw_ring + sa * PF_RAW_SLOT + row * 144);
 #pragma unroll
-                for (int i = 0; i < 9; ++i) w[i] = rec[i];
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->raw_empty[sa]);
-            if (it + 2 < total && !(p.debug & 4)) {   // refill the raw slot two blocks ahead once all four warps have read it
-                if (!wait_or_abort(&ctl->raw_empty[sa], (uint32_t)((it >> 1) & 1), ctl, p.status)) break;
-                fence_proxy_async();
-                issue_raw(p, next2, raw_ring + sa * PF_RAW_SLOT, row, &ctl->raw_full[sa]);
-            }
+            for (int i = 0; i < 9; ++i) w[i] = wn[i];
+            next.advance(p);
+            if (it + 1 < total) load_record(p, next, row, wn);   // in flight while this block is expanded
             const int u = 2 * it + half;
             const int sb = u % PF_B_SLOTS;
-            if (!wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status)) break;
-            if (!(p.debug & 8)) expand_weights(w, b_ring + sb * PF_B_SLOT, smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT, rh);
+            if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
+            PF_MARK0();
+            expand_weights(w, b_ring + sb * PF_B_SLOT, smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT, rh);
+            PF_MARK(4);
             fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->b_full[sb]);
-
-            // finish the activations
-            if (!(p.debug & 1)) store_codes(xa, a_ring + sa * PF_A_SLOT, wg, lane);
-            if (!(p.debug & 2)) store_specials(sp, a_ring + sa * PF_A_SLOT, smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, wg, lane);
+            PF_MARK(5);
+        }
+    } else if (warp >= PF_A_WARP0 && warp < PF_A_WARP0 + PF_A_WARPS) {
+        // ------------------------------------------------------------------ activation producers
+        const int wa = warp - PF_A_WARP0, ta = threadIdx.x - 32 * PF_A_WARP0;
+        uint8_t *a_ring = smem + PF_OFF_A, *raw = smem + PF_OFF_RAWA;
+        BlockAt next = first_block(p, 0);
+        int issued = 0, landed = 0;
+        if (ta == 0 && total > 0) { issue_raw_a(&x_map, next, raw, &ctl->rawa_full); issued = 1; }
+        for (int it = 0; it < total && !ctl->abort; ++it) {
+            const int sa = it & 1, shift = 4 * (next.b & 3);
+            next.advance(p);
+            if (!PF_TIMED(1, wait_or_abort(&ctl->rawa_full, (uint32_t)(it & 1), ctl, p.status))) break;
+            landed = it + 1;
+            // the A slot was last read by the MMAs of block it - 2
+            if (!PF_TIMED(0, wait_or_abort(&ctl->a_empty[sa], (uint32_t)((it >> 1) & 1) ^ 1u, ctl, p.status))) break;
+            PF_MARK0();
+            relayout_activations(raw, shift, a_ring + sa * PF_A_SLOT, smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, wa, ta, lane);
+            PF_MARK(4);
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->a_full[sa]);
+            if (lane == 0) { mbar_arrive(&ctl->a_full[sa]); mbar_arrive(&ctl->rawa_empty); }
+            PF_MARK(5);
+            if (ta == 0 && it + 1 < total) {   // refill the raw slot once all three warps have read it
+                if (!PF_TIMED(2, wait_one(&ctl->rawa_empty, (uint32_t)(it & 1), ctl, p.status))) break;
+                fence_proxy_async();
+                issue_raw_a(&x_map, next, raw, &ctl->rawa_full);
+                issued = it + 2;
+            }
         }
-    } else if (warp == 8) {
+        if (ta == 0 && issued > landed) mbar_wait(&ctl->rawa_full, (uint32_t)(landed & 1));
+    } else if (warp == PF_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
             const uint32_t idesc_q = tc::idesc_i8(PF_BM, 2 * PF_HALF, true, true);
@@ -345,102 +390,104 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
             bool ok = true;
             for (int it = 0; it < total && ok && !ctl->abort; ++it) {
                 const int sa = it & 1;
-                if (!wait_one(&ctl->a_full[sa], (uint32_t)((it >> 1) & 1), ctl, p.status)) break;
+                if (!PF_TIMED(0, wait_one(&ctl->a_full[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
                 const uint32_t a_q = smem_addr(smem + PF_OFF_A + sa * PF_A_SLOT), a_m = a_q + PF_A_Q;
                 for (int h = 0; h < 2; ++h) {
                     const int u = 2 * it + h;
                     const int sb = u % PF_B_SLOTS;
-                    if (!wait_one(&ctl->b_full[sb], (uint32_t)((u / PF_B_SLOTS) & 1), ctl, p.status)) { ok = false; break; }
-                    if (!wait_one(&ctl->tmem_empty[h], (uint32_t)(it & 1) ^ 1u, ctl, p.status)) { ok = false; break; }
-                    if (!(p.debug & 256)) tc::fence_after_sync();
+                    if (!PF_TIMED(1, wait_one(&ctl->b_full[sb], (uint32_t)((u / PF_B_SLOTS) & 1), ctl, p.status))) { ok = false; break; }
+                    if (!PF_TIMED(2, wait_one(&ctl->tmem_empty[h], (uint32_t)(it & 1) ^ 1u, ctl, p.status))) { ok = false; break; }
+                    tc::fence_after_sync();
+                    PF_MARK0();
                     const uint32_t b_q = smem_addr(smem + PF_OFF_B + sb * PF_B_SLOT), b_m = b_q + PF_B_Q;
                     const uint32_t d = tmem + h * PF_HALF_COLS;
-                    if (!(p.debug & 32))
 #pragma unroll
                     for (int j = 0; j < 8; ++j)   // K = 32 per instruction: 32 bytes further inside the swizzled row, next slab after 4
                         tc::mma_i8(d, tc::smem_desc_sw128(a_q + (j >> 2) * PF_A_SLAB + (j & 3) * 32),
                                    tc::smem_desc_sw128(b_q + (j >> 2) * PF_B_SLAB + (j & 3) * 32), idesc_q, j > 0);
-                    if (!(p.debug & 32)) tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_m, 128, 256), tc::smem_desc(b_m, 128, 256), idesc_m, 0);
-                    if (p.debug & 64) mbar_arrive(&ctl->tmem_full[h]); else tc::commit(&ctl->tmem_full[h]);   // this half's accumulators are complete
-                    if (p.debug & 64) mbar_arrive(&ctl->b_empty[sb]); else tc::commit(&ctl->b_empty[sb]);    // and its weight slot may be refilled
+                    tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_m, 128, 256), tc::smem_desc(b_m, 128, 256), idesc_m, 0);
+                    tc::commit(&ctl->tmem_full[h]);   // this half's accumulators are complete
+                    tc::commit(&ctl->b_empty[sb]);    // and its weight slot may be refilled
+                    PF_MARK(4);
                 }
-                if (ok) { if (p.debug & 64) mbar_arrive(&ctl->a_empty[sa]); else tc::commit(&ctl->a_empty[sa]); }
+                if (ok) tc::commit(&ctl->a_empty[sa]);
             }
         }
-    } else {
-        // ------------------------------------------------------------------ epilogue (warps 0-3)
-        const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-        float acc[PF_BN];
+    } else if (warp < 8) {
+        // ------------------------------------------------------------------ epilogue: warp = (64-weight half, 32-token quarter)
+        const int quarter = warp & 3, h = warp >> 2;
+        const int row = quarter * 32 + lane;   // token row of the tile = TMEM lane
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16) + h * PF_HALF_COLS;
+        float acc[PF_HALF];
         int it = 0;
         bool ok = true;
         for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
             const int tile = (int)blockIdx.x + t * (int)gridDim.x;
-            const long long n0 = (long long)(tile / p.m_tiles) * PF_BN, m0 = (long long)(tile % p.m_tiles) * PF_BM;
+            const long long n0 = (long long)(tile / p.m_tiles) * PF_BN + h * PF_HALF, m0 = (long long)(tile % p.m_tiles) * PF_BM;
 #pragma unroll
-            for (int i = 0; i < PF_BN; ++i) acc[i] = 0.f;
-            for (int b = 0; b < nb && ok; ++b, ++it) {
-                const float *xds = reinterpret_cast<const float *>(smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT);
+            for (int i = 0; i < PF_HALF; ++i) acc[i] = 0.f;
+            for (int b = 0; b < nb; ++b, ++it) {
+                if (!PF_TIMED(0, wait_or_abort(&ctl->tmem_full[h], (uint32_t)(it & 1), ctl, p.status))) { ok = false; break; }
+                tc::fence_after_sync();
+                const float4 *wd = reinterpret_cast<const float4 *>(smem + PF_OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT);
+                const float xd = reinterpret_cast<const float *>(smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT)[row];
+                PF_MARK0();
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    if (!wait_or_abort(&ctl->tmem_full[h], (uint32_t)(it & 1), ctl, p.status)) { ok = false; break; }
-                    tc::fence_after_sync();
-                    const float4 *wd = reinterpret_cast<const float4 *>(smem + PF_OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT);
-                    const float xd = xds[threadIdx.x];
-                    if (p.debug & 16) {
+                for (int c = 0; c < PF_HALF / 8; ++c) {
+                    uint32_t hi[8], lo[8], mt[8];
+                    tc::tmem_ld8(lane_base + 8 * c, hi);
+                    tc::tmem_ld8(lane_base + PF_HALF + 8 * c, lo);
+                    tc::tmem_ld8(lane_base + 2 * PF_HALF + 8 * c, mt);
+                    tc::tmem_ld_wait();
+                    if (c == PF_HALF / 8 - 1) {   // last read of this half: hand its columns back to the MMA warp
                         tc::fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&ctl->tmem_empty[h]);
-                        continue;
                     }
 #pragma unroll
-                    for (int c = 0; c < PF_HALF / 16; ++c) {
-                        uint32_t hi[16], lo[16], mt[16];
-                        tc::tmem_ld16(lane_base + h * PF_HALF_COLS + 16 * c, hi);
-                        tc::tmem_ld16(lane_base + h * PF_HALF_COLS + PF_HALF + 16 * c, lo);
-                        tc::tmem_ld16(lane_base + h * PF_HALF_COLS + 2 * PF_HALF + 16 * c, mt);
-                        tc::tmem_ld_wait();
-                        if (c == PF_HALF / 16 - 1) {   // last read of this half: hand its columns back to the MMA warp
-                            tc::fence_before_sync();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&ctl->tmem_empty[h]);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 16; i += 2) {
-                            const float4 s2 = wd[(16 * c + i) >> 1];
-                            const int v0 = 8 * (int)hi[i] + (int)lo[i], v1 = 8 * (int)hi[i + 1] + (int)lo[i + 1];
-                            acc[h * PF_HALF + 16 * c + i] += xd * (s2.x * (float)v0 - s2.y * __uint_as_float(mt[i]));
-                            acc[h * PF_HALF + 16 * c + i + 1] += xd * (s2.z * (float)v1 - s2.w * __uint_as_float(mt[i + 1]));
-                        }
+                    for (int i = 0; i < 8; i += 2) {
+                        const float4 s2 = wd[(8 * c + i) >> 1];
+                        const float v0 = limbs_to_float(hi[i], lo[i]), v1 = limbs_to_float(hi[i + 1], lo[i + 1]);
+                        acc[8 * c + i] += xd * (s2.x * v0 - s2.y * __uint_as_float(mt[i]));
+                        acc[8 * c + i + 1] += xd * (s2.z * v1 - s2.w * __uint_as_float(mt[i + 1]));
                     }
                 }
+                PF_MARK(4);
             }
             if (!ok) break;
-            const long long m = m0 + threadIdx.x;
+            const long long m = m0 + row;
             if (m < p.m) {
                 float *out = p.y + (size_t)m * p.ldy + n0;
-                if (n0 + PF_BN <= p.n && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) {
+                if (n0 + PF_HALF <= p.n && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) {
 #pragma unroll
-                    for (int i = 0; i < PF_BN; i += 4) *reinterpret_cast<float4 *>(out + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+                    for (int i = 0; i < PF_HALF; i += 4) *reinterpret_cast<float4 *>(out + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
                 } else {
 #pragma unroll
-                    for (int i = 0; i < PF_BN; ++i)
+                    for (int i = 0; i < PF_HALF; ++i)
                         if (n0 + i < p.n) out[i] = acc[i];
                 }
             }
         }
     }
 
+#ifdef WEFT_PF_PROFILE
+    if (blockIdx.x == 0 && lane == 0) {
+        prof[7] = clock64() - prof_begin;
+        for (int i = 0; i < 8; ++i) g_pf_prof[warp][i] = (unsigned long long)prof[i];
+    }
+#endif
     tc::fence_before_sync();
     __syncthreads();
-    if (warp == 8 && tmem != 0xffffffffu) tc::tmem_free(tmem, PF_TMEM_COLS);
+    if (warp == PF_MMA_WARP && tmem != 0xffffffffu) tc::tmem_free(tmem, PF_TMEM_COLS);
 }
 
 }  // namespace
 
 bool prefill_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq) {
     static const bool disabled = getenv("WEFT_B200_NO_TENSOR_PREFILL") != nullptr;
-    return !disabled && fmt == F_Q4_K && k > 0 && k % 256 == 0 && n > 0 && m >= 32 &&
-           (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 3u) == 0 &&
+    // K a multiple of 1024: Q8_K rows (292 bytes per 256) are then whole 16-byte multiples, which the TMA box loads need
+    return !disabled && fmt == F_Q4_K && k > 0 && k % 1024 == 0 && n > 0 && m >= 32 &&
+           (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0 &&
            n < (1LL << 31) && m < (1LL << 31);
 }
 
@@ -449,8 +496,6 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
     PfParams p;
     p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.y = a.y;
     p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
-    static const int debug = getenv("WEFT_B200_PF_DEBUG") ? atoi(getenv("WEFT_B200_PF_DEBUG")) : 0;
-    p.debug = debug;
     p.m_tiles = (int)((a.m + PF_BM - 1) / PF_BM);
     p.n_tiles = (int)((a.n + PF_BN - 1) / PF_BN);
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
@@ -460,9 +505,19 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
         if (e != cudaSuccess) return e;
         configured = true;
     }
+    CUtensorMap x_map;
+    cudaError_t e = encode_tile_map(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
+                        (unsigned long long)p.nb * 292, PF_RAWA_WORDS, PF_BM);
+    if (e != cudaSuccess) return e;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    prefill_q4k_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(p);
+    prefill_q4k_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_map);
     return cudaGetLastError();
 }
+
+#ifdef WEFT_PF_PROFILE
+extern "C" int weft_b200_debug_prefill_profile(unsigned long long *out) {
+    return (int)cudaMemcpyFromSymbol(out, g_pf_prof, sizeof(unsigned long long) * 128);
+}
+#endif
 
 }  // namespace weft
