@@ -17,20 +17,28 @@
 // sum are exact (< 2^24).  The per-block float combine runs on the CUDA cores in the epilogue with the
 // reference's own op order, accumulating in fp32 registers across blocks.
 //
+// Activation codes are never touched by a CUDA core.  A Q8_K record is 292 bytes: f32 d, 256 codes, 16
+// bsums; with K a multiple of 1024 every token row is a whole number of 16-byte units and record b of a
+// row starts 4 * (b & 3) bytes past a 16-byte boundary.  TMA box copies starting at that boundary bring
+// the records of 128 tokens straight into the 128-byte-swizzled K-major layout the MMA reads (two boxes
+// 128 bytes wide) plus three 16-byte wide boxes for the tail; in that operand the code of weight k sits at
+// K position k + S, S = 4 * (b & 3) + 4, and the bytes before and after the codes (d, bsums) are garbage.
+// The weight operand is therefore written with the same shift: limb byte k at K position k + S, zeros
+// everywhere else, so garbage only ever meets zeros.  The MMA runs over K = 288 (nine K = 32 steps).
+//
 // CTA = 128 tokens (TMEM lanes) x 128 weights, persistent over tiles.  The 128 weights are two halves of
 // 64; each half owns 192 TMEM columns ([q*a | q*c | min term]), so the tensor core works on one half
 // while the epilogue drains the other.  Warp roles:
 //   warps 0-7   epilogue, warp = (half, 32-token quarter): tcgen05.ld the accumulators, combine, keep
 //               32 x 64 fp32 in registers across the blocks of a tile
-//   warps 8-11  weight producers, one weight row per thread: Q4_K records arrive in a raw ring by
-//               144-byte bulk copies (in place, no repack in HBM) and are expanded into the
-//               128-byte-swizzled K-major layout the MMA reads from shared memory
-//   warps 12-14 activation producers: Q8_K codes, scales and bsums read from global memory one block
-//               ahead (in registers) and stored into the swizzled A slot when it is free
+//   warps 8-11  weight producers, one weight row per thread: the row's Q4_K record is read from global
+//               memory in place (no repack in HBM), one block ahead, and expanded into the shifted
+//               two-limb operand
+//   warps 12-13 read x.ds and the bsums out of the landed activation boxes and build the min-term operand
+//   warp 14     one lane issues the activation TMA copies, up to two blocks ahead
 //   warp 15     allocates TMEM; one lane issues the MMAs and commits them to mbarriers
-// Two activation slots and three weight slots let the producers run ahead of the tensor core.  Every wait is
-// bounded; a wait that runs out sets an abort flag, all roles leave their loops, TMEM is freed, and the
-// host sees a status code instead of a hang.
+// Every wait is bounded; a wait that runs out sets an abort flag, all roles leave their loops, copies in
+// flight are waited for, TMEM is freed, and the host sees a status code instead of a hang.
 #include "tcgen05.cuh"
 #include "tensormap.cuh"
 #include "kernels.h"
@@ -44,24 +52,24 @@ namespace {
 constexpr int PF_BM = 128;               // tokens per tile = TMEM lanes
 constexpr int PF_BN = 128;               // weights per tile, two halves of 64
 constexpr int PF_HALF = 64;
-constexpr int PF_THREADS = 512;          // 8 epilogue + 4 weight producer + 3 activation producer + 1 MMA warp
-constexpr int PF_W_WARP0 = 8, PF_A_WARP0 = 12, PF_MMA_WARP = 15;
+constexpr int PF_THREADS = 512;
+constexpr int PF_W_WARP0 = 8, PF_S_WARP0 = 12, PF_TMA_WARP = 14, PF_MMA_WARP = 15;
+constexpr int PF_S_WARPS = 2;
 
-// Shared memory.  int8 operands live in 128-byte-swizzled slabs of 128 K-bytes (K = 256 -> two slabs);
-// the f16 min-term operands are unswizzled core matrices.
-constexpr int PF_A_SLAB = PF_BM * 128;                 // 16 KB: 128 tokens x 128 K-bytes
-constexpr int PF_A_Q = 2 * PF_A_SLAB;
-constexpr int PF_A_M = PF_BM * 32;                     // {l, h} f16 per token
-constexpr int PF_A_SLOT = PF_A_Q + PF_A_M;             // 36 KB, one 256-block of activations
+// Shared memory.  int8 operands: K bytes 0..255 in two 128-byte-swizzled slabs of 128 rows x 128 bytes,
+// K bytes 256.. in unswizzled 16-byte columns (128 rows x 16 bytes each = stacked 8 x 16 core matrices).
+// The f16 min-term operands are unswizzled core matrices.
+constexpr int PF_SLAB = 128 * 128;                     // 16 KB
+constexpr int PF_COL = 128 * 16;                       // 2 KB: one 16-byte column of 128 rows
+constexpr int PF_A_THIN = 2 * PF_SLAB;                 // three columns: K bytes 256..303
+constexpr int PF_A_M = PF_A_THIN + 3 * PF_COL;         // {l, h} f16 per token (128 x 32 bytes)
+constexpr int PF_A_SLOT = PF_A_M + PF_BM * 32;         // 42 KB, one 256-block of activations
+constexpr int PF_A_TMA_BYTES = 2 * PF_SLAB + 3 * PF_COL;
 constexpr int PF_A_SLOTS = 2;
-constexpr int PF_B_SLAB = 2 * PF_HALF * 128;           // 16 KB: [q*a rows 0-63 | q*c rows 64-127] x 128 K-bytes
-constexpr int PF_B_Q = 2 * PF_B_SLAB;
-constexpr int PF_B_M = PF_HALF * 32;                   // {mn, 64 mn} f16 per weight
-constexpr int PF_B_SLOT = PF_B_Q + PF_B_M;             // 34 KB, one 256-block of one 64-weight half
+constexpr int PF_B_THIN = 2 * PF_SLAB;                 // two columns: K bytes 256..287 of [q*a rows 0-63 | q*c rows 64-127]
+constexpr int PF_B_M = PF_B_THIN + 2 * PF_COL;         // {mn, 64 mn} f16 per weight (64 x 32 bytes)
+constexpr int PF_B_SLOT = PF_B_M + PF_HALF * 32;       // 38 KB, one 256-block of one 64-weight half
 constexpr int PF_B_SLOTS = 3;
-constexpr int PF_RAWA_WORDS = 76;                      // 304 bytes: a Q8_K record (292) from the 16-byte boundary at or before it
-constexpr int PF_RAWA_PITCH = 4 * PF_RAWA_WORDS;
-constexpr int PF_RAWA_SLOT = PF_BM * PF_RAWA_PITCH;    // 38 KB: one 256-block of Q8_K records as they are in HBM
 constexpr int PF_WD_SLOT = PF_HALF * 8;                // {d, dmin} per weight of one half
 constexpr int PF_WD_SLOTS = 8;
 constexpr int PF_XD_SLOT = PF_BM * 4;                  // x.ds per token
@@ -69,19 +77,16 @@ constexpr int PF_XD_SLOTS = 4;
 constexpr int PF_CONTROL = 1024;
 constexpr int PF_OFF_A = PF_CONTROL;
 constexpr int PF_OFF_B = PF_OFF_A + PF_A_SLOTS * PF_A_SLOT;
-constexpr int PF_OFF_RAWA = PF_OFF_B + PF_B_SLOTS * PF_B_SLOT;
-constexpr int PF_OFF_WD = PF_OFF_RAWA + PF_RAWA_SLOT;
+constexpr int PF_OFF_WD = PF_OFF_B + PF_B_SLOTS * PF_B_SLOT;
 constexpr int PF_OFF_XD = PF_OFF_WD + PF_WD_SLOTS * PF_WD_SLOT;
 constexpr int PF_SMEM = PF_OFF_XD + PF_XD_SLOTS * PF_XD_SLOT;
 constexpr int PF_TMEM_COLS = 512;                      // 2 x 192 used
 constexpr int PF_HALF_COLS = 192;
 static_assert(PF_A_SLOT % 1024 == 0 && PF_B_SLOT % 1024 == 0 && PF_OFF_B % 1024 == 0, "swizzled slabs must stay 1024-byte aligned");
-static_assert(PF_OFF_RAWA % 128 == 0, "TMA destinations are 128-byte aligned");
 static_assert(PF_SMEM <= 227 * 1024, "shared memory budget");
 
 struct PfParams {
     const uint8_t *w;     // (n, k) Q4_K records, 16-byte aligned rows
-    const uint8_t *xq;    // (m, k) Q8_K records
     float *y;             // (m, ldy)
     long long n, m, ldy;
     int nb;               // 256-blocks per row
@@ -111,11 +116,20 @@ __device__ __forceinline__ float limbs_to_float(uint32_t hi, uint32_t lo) {
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
     return (uint32_t)__half_as_ushort(__float2half_rn(lo)) | ((uint32_t)__half_as_ushort(__float2half_rn(hi)) << 16);
 }
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
+__device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory"); }
+__device__ __forceinline__ void sts_u128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
 struct Control {
-    uint64_t a_full[PF_A_SLOTS], a_empty[PF_A_SLOTS];
+    uint64_t a_landed[PF_A_SLOTS], a_full[PF_A_SLOTS], a_empty[PF_A_SLOTS];
     uint64_t b_full[PF_B_SLOTS], b_empty[PF_B_SLOTS];
-    uint64_t rawa_full, rawa_empty;
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     volatile int abort;
@@ -161,8 +175,8 @@ __device__ unsigned long long g_pf_prof[16][8];
 #define PF_MARK0() do { } while (0)
 #endif
 
-// Coordinates of one 256-block of this CTA's work list (tiles taken round-robin, blocks in K order),
-// advanced incrementally: no division on the critical path of the producer loop.
+// Coordinates of one 256-block of this CTA's work list (tiles taken round-robin),
+// advanced incrementally: no division on the critical path of the producer loops.
 struct BlockAt {
     long long n0, m0;
     int b, tile;
@@ -171,26 +185,28 @@ struct BlockAt {
         n0 = (long long)(t / p.m_tiles) * PF_BN;
         m0 = (long long)(t % p.m_tiles) * PF_BM;
     }
+    // Blocks of a tile are taken as 0, 4, 8, ..., 1, 5, 9, ..., 2, ..., 3, ...: blocks with the same operand
+    // shift follow each other, so the weight producers stay in one of their four code variants for a
+    // quarter of the tile instead of switching (and refetching instructions) every block.
     __device__ __forceinline__ void advance(const PfParams &p) {
-        if (++b == p.nb) { b = 0; set_tile(p, tile + (int)gridDim.x); }
+        b += 4;
+        if (b >= p.nb) {
+            b = (b & 3) + 1;
+            if (b == 4) { b = 0; set_tile(p, tile + (int)gridDim.x); }
+        }
     }
 };
-__device__ __forceinline__ BlockAt first_block(const PfParams &p, int steps) {
+__device__ __forceinline__ BlockAt first_block(const PfParams &p) {
     BlockAt at;
     at.b = 0;
     at.set_tile(p, (int)blockIdx.x);
-    for (int i = 0; i < steps; ++i) at.advance(p);
     return at;
 }
 
 // ---- producer pieces -----------------------------------------------------------------------------------
 
-constexpr int PF_A_WARPS = 3;                                        // activation producer warps
-constexpr int PF_A_ROWS = (PF_BM + PF_A_WARPS - 1) / PF_A_WARPS;     // token rows per warp: wa, wa + 3, ...
-constexpr int PF_SP_ITEMS = (PF_BM * 9 + 32 * PF_A_WARPS - 1) / (32 * PF_A_WARPS);
-
 // A weight producer thread reads its row's Q4_K record of a block straight from global memory (nine
-// 16-byte loads, one block ahead of its use, in place: no repack in HBM).  Rows past N read as zero.
+// 16-byte loads, one block ahead of its use).  Rows past N read as zero.
 __device__ __forceinline__ void load_record(const PfParams &p, const BlockAt &at, int row, uint4 (&w)[9]) {
     const long long n = at.n0 + row;
     if (n < p.n) {
@@ -202,70 +218,14 @@ __device__ __forceinline__ void load_record(const PfParams &p, const BlockAt &at
         for (int i = 0; i < 9; ++i) w[i] = make_uint4(0, 0, 0, 0);
     }
 }
-// One elected thread asks for the tile's Q8_K records of a block with one TMA box copy.  A record starts 4 * (b & 3) bytes past a 16-byte boundary (rows are
-// 16-byte multiples because K is a multiple of 1024), so the box starts at that boundary and is 304 bytes wide.
-__device__ __forceinline__ void issue_raw_a(const CUtensorMap *map, const BlockAt &at, uint8_t *raw, uint64_t *bar) {
-    mbar_expect_tx(bar, PF_RAWA_SLOT);
-    tma_load_2d(raw, map, 73 * at.b - (at.b & 3), (int)at.m0, bar);
-}
 
-__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void sts_u32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
-__device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory"); }
-
-// Raw Q8_K records -> the MMA's activation operands.
-// Codes: warp wa takes the 8-row groups wa, wa + 3, ...; within a group lane l moves code words l and 32 + l
-// of each row into the swizzled A slabs: sixteen independent loads, then sixteen stores, all at offsets
-// that are compile-time constants from per-lane bases.
-// The nine other words of each record: bsum pair g of row r is item j = 8 r + g, dealt to the 96 threads as
-// j = thread + 96 t (so a thread keeps its g and walks 12 rows at a time); the pair s = 64 h + l
-// (l in 0..63) goes to the f16 min-term operand {l | h}.  x.ds of rows thread, thread + 96 goes to the scale ring.
-__device__ __forceinline__ void relayout_activations(const uint8_t *raw, int shift, uint8_t *a_slot, uint8_t *xd_slot, int wa, int ta, int lane) {
-    const uint32_t src = smem_addr(raw) + (uint32_t)shift + 4u + 4u * (uint32_t)lane;
-    const uint32_t dst = smem_addr(a_slot) + (uint32_t)(lane & 3) * 4u;
-    const uint32_t ch = (uint32_t)lane >> 2;
-    for (int grp = wa; grp < PF_BM / 8; grp += PF_A_WARPS) {
-        uint32_t c[16];
-        const uint32_t s0 = src + (uint32_t)grp * (8 * PF_RAWA_PITCH), d0 = dst + (uint32_t)grp * 1024u;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            c[2 * i] = lds_u32(s0 + i * PF_RAWA_PITCH);
-            c[2 * i + 1] = lds_u32(s0 + i * PF_RAWA_PITCH + 128);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t at = d0 + i * 128 + ((ch ^ (uint32_t)i) << 4);
-            sts_u32(at, c[2 * i]);                  // K bytes 0..127
-            sts_u32(at + PF_A_SLAB, c[2 * i + 1]);  // K bytes 128..255
-        }
-    }
-    const uint32_t raw_s = smem_addr(raw) + (uint32_t)shift;
-    {
-        const int g = ta & 7, r0 = ta >> 3;
-        const uint32_t a_m = smem_addr(a_slot) + PF_A_Q + 2u * (uint32_t)g;
-        uint32_t v[11];
-#pragma unroll
-        for (int t = 0; t < 11; ++t) v[t] = (t < 10 || ta < 64) ? lds_u32(raw_s + (uint32_t)(r0 + 12 * t) * PF_RAWA_PITCH + 260u + 4u * (uint32_t)g) : 0u;
-#pragma unroll
-        for (int t = 0; t < 11; ++t) {
-            const int r = r0 + 12 * t;
-            if (t == 10 && ta >= 64) break;
-            const int s_ = (int)(int16_t)(v[t] & 0xffffu) + (int)(int16_t)(v[t] >> 16);
-            const int l = s_ & 63, h = (s_ - l) >> 6;
-            const uint32_t at = a_m + (uint32_t)r * 16u + (uint32_t)(r >> 3) * 128u;   // core_offset(r, 0, 2)
-            sts_u16(at, (uint32_t)__half_as_ushort(__int2half_rn(l)));
-            sts_u16(at + 128u, (uint32_t)__half_as_ushort(__int2half_rn(h)));
-        }
-    }
-    for (int r = ta; r < PF_BM; r += 32 * PF_A_WARPS) reinterpret_cast<uint32_t *>(xd_slot)[r] = lds_u32(raw_s + (uint32_t)r * PF_RAWA_PITCH);
-}
-
-// Expand one Q4_K record (in registers) into this half's B slot: rows rh (q*a) and 64+rh (q*c) of both
-// K slabs, the f16 {mn | 64 mn} row, and {d, dmin} for the epilogue.
+// Expand one Q4_K record (in registers) into this half's B slot: rows rh (q*a) and 64+rh (q*c), limb byte
+// k at K position k + 4*W (W = 1..4 words, the shift of this block's activation operand), zeros before
+// and after; the f16 {mn | 64 mn} row; {d, dmin} for the epilogue.
+// The limb bytes form a stream of 64 words per limb.  Sub-block pair j contributes stream words 16j..16j+15;
+// with the W words carried over from pair j-1 in front of them they are exactly the output chunks
+// 4j..4j+3, so the shift costs no instructions: it only changes which register goes into which store.
+template <int W>
 __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_slot, uint8_t *wd_slot, int rh) {
     const uint4 hd = w[0];
     reinterpret_cast<float2 *>(wd_slot)[rh] = make_float2(half_bits_to_float(hd.x), half_bits_to_float(hd.x >> 16));
@@ -273,33 +233,101 @@ __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_s
     float mn[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) mn[g] = (float)byte_of(g < 4 ? s.mn_lo : s.mn_hi, g & 3);
-    uint8_t *bm = b_slot + PF_B_Q;
+    uint8_t *bm = b_slot + PF_B_M;
     *reinterpret_cast<uint4 *>(bm + core_offset(rh, 0, 2)) =
         make_uint4(pack_half2(mn[0], mn[1]), pack_half2(mn[2], mn[3]), pack_half2(mn[4], mn[5]), pack_half2(mn[6], mn[7]));
     *reinterpret_cast<uint4 *>(bm + core_offset(rh, 1, 2)) =
         make_uint4(pack_half2(64.f * mn[0], 64.f * mn[1]), pack_half2(64.f * mn[2], 64.f * mn[3]),
                    pack_half2(64.f * mn[4], 64.f * mn[5]), pack_half2(64.f * mn[6], 64.f * mn[7]));
+
+    // row rh of a swizzled slab; row 64 + rh (the q*c limb) is 8192 bytes further with the same swizzle
+    const uint32_t base = smem_addr(b_slot) + (uint32_t)(rh >> 3) * 1024u + (uint32_t)(rh & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(rh & 7) << 4;
+    uint32_t ca[4] = {0, 0, 0, 0}, cc[4] = {0, 0, 0, 0};   // the last W stream words of the previous pair
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {   // 16 nibble bytes: low nibbles -> 16 weights, high nibbles -> the 16 weights 32 further
-        const uint4 qv = w[1 + c];
-        const int j = c >> 1, hf = c & 1;
+    for (int j = 0; j < 4; ++j) {
+        uint32_t cur_a[16], cur_c[16];
         const uint32_t scv = j < 2 ? s.sc_lo : s.sc_hi;
         const uint32_t sl = byte_of(scv, (2 * j) & 3), sh = byte_of(scv, ((2 * j) & 3) + 1);
         const uint32_t al = sl >> 3, cl = sl & 7u, ah = sh >> 3, ch = sh & 7u;
-        const uint32_t M4 = 0x0f0f0f0fu;
-        const uint32_t lo[4] = {qv.x & M4, qv.y & M4, qv.z & M4, qv.w & M4};
-        const uint32_t hi[4] = {(qv.x >> 4) & M4, (qv.y >> 4) & M4, (qv.z >> 4) & M4, (qv.w >> 4) & M4};
-        // every byte product is <= 15 * 7 = 105, so one 32-bit multiply scales four weights at once
-        const int kl = 4 * j + hf, kh = 4 * j + 2 + hf;          // 16-byte K chunk index 0..15
-        uint8_t *slab_l = b_slot + (kl >> 3) * PF_B_SLAB, *slab_h = b_slot + (kh >> 3) * PF_B_SLAB;
-        *reinterpret_cast<uint4 *>(slab_l + sw128_offset(rh, kl & 7)) = make_uint4(lo[0] * al, lo[1] * al, lo[2] * al, lo[3] * al);
-        *reinterpret_cast<uint4 *>(slab_l + sw128_offset(PF_HALF + rh, kl & 7)) = make_uint4(lo[0] * cl, lo[1] * cl, lo[2] * cl, lo[3] * cl);
-        *reinterpret_cast<uint4 *>(slab_h + sw128_offset(rh, kh & 7)) = make_uint4(hi[0] * ah, hi[1] * ah, hi[2] * ah, hi[3] * ah);
-        *reinterpret_cast<uint4 *>(slab_h + sw128_offset(PF_HALF + rh, kh & 7)) = make_uint4(hi[0] * ch, hi[1] * ch, hi[2] * ch, hi[3] * ch);
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {   // 16 nibble bytes: low nibbles -> 16 weights, high nibbles -> the 16 weights 32 further
+            const uint4 qv = w[1 + 2 * j + hf];
+            const uint32_t q[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t lo = q[i] & 0x0f0f0f0fu, hi = (q[i] >> 4) & 0x0f0f0f0fu;
+                // every byte product is <= 15 * 7 = 105, so one 32-bit multiply scales four weights at once
+                cur_a[4 * hf + i] = lo * al;      cur_c[4 * hf + i] = lo * cl;
+                cur_a[8 + 4 * hf + i] = hi * ah;  cur_c[8 + 4 * hf + i] = hi * ch;
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t oa[4], oc[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = 4 * q + k;
+                oa[k] = idx < W ? ca[idx < W ? idx : 0] : cur_a[idx < W ? 0 : idx - W];
+                oc[k] = idx < W ? cc[idx < W ? idx : 0] : cur_c[idx < W ? 0 : idx - W];
+            }
+            const int chunk = 4 * j + q;   // 16-byte K chunk 0..15
+            const uint32_t at = base + (uint32_t)(chunk >> 3) * PF_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7);
+            sts_u128(at, oa[0], oa[1], oa[2], oa[3]);
+            sts_u128(at + 8192u, oc[0], oc[1], oc[2], oc[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < W; ++i) { ca[i] = cur_a[16 - W + i]; cc[i] = cur_c[16 - W + i]; }
+    }
+    // K chunk 16: the carried words, then zeros; chunk 17: zeros
+    const uint32_t thin = smem_addr(b_slot) + PF_B_THIN + (uint32_t)rh * 16u;
+    sts_u128(thin, ca[0], W > 1 ? ca[1] : 0u, W > 2 ? ca[2] : 0u, W > 3 ? ca[3] : 0u);
+    sts_u128(thin + 1024u, cc[0], W > 1 ? cc[1] : 0u, W > 2 ? cc[2] : 0u, W > 3 ? cc[3] : 0u);
+    sts_u128(thin + PF_COL, 0u, 0u, 0u, 0u);
+    sts_u128(thin + PF_COL + 1024u, 0u, 0u, 0u, 0u);
+}
+
+// One thread asks for the tile's Q8_K records of a block: word x0 = 73 b - (b & 3) of each token row is the
+// 16-byte boundary at or before the record; two swizzled boxes of 128 bytes, three plain columns of 16.
+__device__ __forceinline__ void issue_activations(const CUtensorMap *wide, const CUtensorMap *narrow, const BlockAt &at, uint8_t *slot, uint64_t *bar) {
+    const int x0 = 73 * at.b - (at.b & 3), m0 = (int)at.m0;
+    mbar_expect_tx(bar, PF_A_TMA_BYTES);
+    tma_load_2d(slot, wide, x0, m0, bar);
+    tma_load_2d(slot + PF_SLAB, wide, x0 + 32, m0, bar);
+    tma_load_2d(slot + PF_A_THIN, narrow, x0 + 64, m0, bar);
+    tma_load_2d(slot + PF_A_THIN + PF_COL, narrow, x0 + 68, m0, bar);
+    tma_load_2d(slot + PF_A_THIN + 2 * PF_COL, narrow, x0 + 72, m0, bar);
+}
+
+// Out of the landed boxes: x.ds of every token to the scale ring, and the eight bsum pairs of every token,
+// each split as s = 64 h + l (l in 0..63), to the f16 min-term operand {l | h}.  64 threads; thread ts keeps
+// pair g = ts & 7 and walks the rows (ts >> 3) + 8 t.  `shift` = 4 * (b & 3): record byte r sits at operand
+// byte r + shift.
+__device__ __forceinline__ void build_specials(uint8_t *a_slot, int shift, uint8_t *xd_slot, int ts) {
+    const int g = ts & 7, r0 = ts >> 3;
+    const uint32_t slot = smem_addr(a_slot);
+    const uint32_t tb = 4u + (uint32_t)shift + 4u * (uint32_t)g;   // byte inside the tail columns (operand byte 256 + tb)
+    const uint32_t src = slot + PF_A_THIN + (tb >> 4) * PF_COL + (tb & 15u) + (uint32_t)r0 * 16u;
+    const uint32_t dst = slot + PF_A_M + (uint32_t)r0 * 16u + 2u * (uint32_t)g;   // core_offset(r0 + 8 t, 0, 2) = 256 t + 16 r0
+    uint32_t v[16];
+#pragma unroll
+    for (int t = 0; t < 16; ++t) v[t] = lds_u32(src + t * 128);
+#pragma unroll
+    for (int t = 0; t < 16; ++t) {
+        const int s_ = (int)(int16_t)(v[t] & 0xffffu) + (int)(int16_t)(v[t] >> 16);
+        const int l = s_ & 63, h = (s_ - l) >> 6;
+        sts_u16(dst + t * 256, (uint32_t)__half_as_ushort(__int2half_rn(l)));
+        sts_u16(dst + t * 256 + 128, (uint32_t)__half_as_ushort(__int2half_rn(h)));
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const int r = ts + 64 * k;
+        sts_u32(smem_addr(xd_slot) + 4u * (uint32_t)r, lds_u32(slot + sw128_offset(r, 0) + (uint32_t)shift));
     }
 }
 
-__global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams p, const __grid_constant__ CUtensorMap x_map) {
+__global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams p, const __grid_constant__ CUtensorMap x_wide,
+                                                                   const __grid_constant__ CUtensorMap x_narrow) {
     extern __shared__ __align__(1024) uint8_t smem[];
     Control *ctl = reinterpret_cast<Control *>(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -309,9 +337,8 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
     const int total = my_tiles * nb;   // 256-blocks this CTA works through
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PF_A_SLOTS; ++s) { mbar_init(&ctl->a_full[s], PF_A_WARPS); mbar_init(&ctl->a_empty[s], 1); }
+        for (int s = 0; s < PF_A_SLOTS; ++s) { mbar_init(&ctl->a_landed[s], 1); mbar_init(&ctl->a_full[s], PF_S_WARPS); mbar_init(&ctl->a_empty[s], 1); }
         for (int s = 0; s < PF_B_SLOTS; ++s) { mbar_init(&ctl->b_full[s], 2); mbar_init(&ctl->b_empty[s], 1); }
-        mbar_init(&ctl->rawa_full, 1); mbar_init(&ctl->rawa_empty, PF_A_WARPS);
         for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 4); }
         ctl->abort = 0;
         ctl->tmem_base = 0xffffffffu;
@@ -333,55 +360,65 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
         // ------------------------------------------------------------------ weight producers
         const int row = threadIdx.x - 32 * PF_W_WARP0, half = row >> 6, rh = row & 63;
         uint8_t *b_ring = smem + PF_OFF_B;
-        BlockAt next = first_block(p, 0);
+        BlockAt next = first_block(p);
         uint4 wn[9];
         if (total > 0) load_record(p, next, row, wn);
         for (int it = 0; it < total && !ctl->abort; ++it) {
             uint4 w[9];
 #pragma unroll
             for (int i = 0; i < 9; ++i) w[i] = wn[i];
+            const int words = (next.b & 3) + 1;   // this block's operand shift
             next.advance(p);
             if (it + 1 < total) load_record(p, next, row, wn);   // in flight while this block is expanded
             const int u = 2 * it + half;
             const int sb = u % PF_B_SLOTS;
             if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
             PF_MARK0();
-            expand_weights(w, b_ring + sb * PF_B_SLOT, smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT, rh);
+            uint8_t *slot = b_ring + sb * PF_B_SLOT, *wd = smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
+            switch (words) {
+            case 1: expand_weights<1>(w, slot, wd, rh); break;
+            case 2: expand_weights<2>(w, slot, wd, rh); break;
+            case 3: expand_weights<3>(w, slot, wd, rh); break;
+            default: expand_weights<4>(w, slot, wd, rh); break;
+            }
             PF_MARK(4);
             fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->b_full[sb]);
             PF_MARK(5);
         }
-    } else if (warp >= PF_A_WARP0 && warp < PF_A_WARP0 + PF_A_WARPS) {
-        // ------------------------------------------------------------------ activation producers
-        const int wa = warp - PF_A_WARP0, ta = threadIdx.x - 32 * PF_A_WARP0;
-        uint8_t *a_ring = smem + PF_OFF_A, *raw = smem + PF_OFF_RAWA;
-        BlockAt next = first_block(p, 0);
-        int issued = 0, landed = 0;
-        if (ta == 0 && total > 0) { issue_raw_a(&x_map, next, raw, &ctl->rawa_full); issued = 1; }
+    } else if (warp >= PF_S_WARP0 && warp < PF_S_WARP0 + PF_S_WARPS) {
+        // ------------------------------------------------------------------ scales and bsums of the landed activations
+        const int ts = threadIdx.x - 32 * PF_S_WARP0;
+        BlockAt at = first_block(p);
         for (int it = 0; it < total && !ctl->abort; ++it) {
-            const int sa = it & 1, shift = 4 * (next.b & 3);
-            next.advance(p);
-            if (!PF_TIMED(1, wait_or_abort(&ctl->rawa_full, (uint32_t)(it & 1), ctl, p.status))) break;
-            landed = it + 1;
-            // the A slot was last read by the MMAs of block it - 2
-            if (!PF_TIMED(0, wait_or_abort(&ctl->a_empty[sa], (uint32_t)((it >> 1) & 1) ^ 1u, ctl, p.status))) break;
+            const int sa = it & 1, shift = 4 * (at.b & 3);
+            at.advance(p);
+            if (!PF_TIMED(0, wait_or_abort(&ctl->a_landed[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
             PF_MARK0();
-            relayout_activations(raw, shift, a_ring + sa * PF_A_SLOT, smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, wa, ta, lane);
+            build_specials(smem + PF_OFF_A + sa * PF_A_SLOT, shift, smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, ts);
             PF_MARK(4);
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) { mbar_arrive(&ctl->a_full[sa]); mbar_arrive(&ctl->rawa_empty); }
+            if (lane == 0) mbar_arrive(&ctl->a_full[sa]);
             PF_MARK(5);
-            if (ta == 0 && it + 1 < total) {   // refill the raw slot once all three warps have read it
-                if (!PF_TIMED(2, wait_one(&ctl->rawa_empty, (uint32_t)(it & 1), ctl, p.status))) break;
-                fence_proxy_async();
-                issue_raw_a(&x_map, next, raw, &ctl->rawa_full);
-                issued = it + 2;
-            }
         }
-        if (ta == 0 && issued > landed) mbar_wait(&ctl->rawa_full, (uint32_t)(landed & 1));
+    } else if (warp == PF_TMA_WARP) {
+        // ------------------------------------------------------------------ activation copies
+        if (lane == 0) {
+            BlockAt at = first_block(p);
+            int issued = 0;
+            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
+                const int sa = it & 1;
+                // the slot was last read by the MMAs of block it - 2 (and, before them, by the warps above)
+                if (!PF_TIMED(0, wait_one(&ctl->a_empty[sa], (uint32_t)((it >> 1) & 1) ^ 1u, ctl, p.status))) break;
+                fence_proxy_async();
+                issue_activations(&x_wide, &x_narrow, at, smem + PF_OFF_A + sa * PF_A_SLOT, &ctl->a_landed[sa]);
+                issued = it + 1;
+            }
+            // left early: let the copies in flight land (a phase that has completed already returns at once)
+            for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) mbar_wait(&ctl->a_landed[j & 1], (uint32_t)((j >> 1) & 1));
+        }
     } else if (warp == PF_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
@@ -390,8 +427,9 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
             bool ok = true;
             for (int it = 0; it < total && ok && !ctl->abort; ++it) {
                 const int sa = it & 1;
-                if (!PF_TIMED(0, wait_one(&ctl->a_full[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
-                const uint32_t a_q = smem_addr(smem + PF_OFF_A + sa * PF_A_SLOT), a_m = a_q + PF_A_Q;
+                if (!PF_TIMED(0, wait_one(&ctl->a_landed[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
+                if (!PF_TIMED(3, wait_one(&ctl->a_full[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
+                const uint32_t a_q = smem_addr(smem + PF_OFF_A + sa * PF_A_SLOT);
                 for (int h = 0; h < 2; ++h) {
                     const int u = 2 * it + h;
                     const int sb = u % PF_B_SLOTS;
@@ -399,13 +437,15 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
                     if (!PF_TIMED(2, wait_one(&ctl->tmem_empty[h], (uint32_t)(it & 1) ^ 1u, ctl, p.status))) { ok = false; break; }
                     tc::fence_after_sync();
                     PF_MARK0();
-                    const uint32_t b_q = smem_addr(smem + PF_OFF_B + sb * PF_B_SLOT), b_m = b_q + PF_B_Q;
+                    const uint32_t b_q = smem_addr(smem + PF_OFF_B + sb * PF_B_SLOT);
                     const uint32_t d = tmem + h * PF_HALF_COLS;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)   // K = 32 per instruction: 32 bytes further inside the swizzled row, next slab after 4
-                        tc::mma_i8(d, tc::smem_desc_sw128(a_q + (j >> 2) * PF_A_SLAB + (j & 3) * 32),
-                                   tc::smem_desc_sw128(b_q + (j >> 2) * PF_B_SLAB + (j & 3) * 32), idesc_q, j > 0);
-                    tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_m, 128, 256), tc::smem_desc(b_m, 128, 256), idesc_m, 0);
+                        tc::mma_i8(d, tc::smem_desc_sw128(a_q + (j >> 2) * PF_SLAB + (j & 3) * 32),
+                                   tc::smem_desc_sw128(b_q + (j >> 2) * PF_SLAB + (j & 3) * 32), idesc_q, j > 0);
+                    // K bytes 256..287: two 16-byte columns, K-adjacent core matrices one column apart
+                    tc::mma_i8(d, tc::smem_desc(a_q + PF_A_THIN, PF_COL, 128), tc::smem_desc(b_q + PF_B_THIN, PF_COL, 128), idesc_q, 1);
+                    tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_q + PF_A_M, 128, 256), tc::smem_desc(b_q + PF_B_M, 128, 256), idesc_m, 0);
                     tc::commit(&ctl->tmem_full[h]);   // this half's accumulators are complete
                     tc::commit(&ctl->b_empty[sb]);    // and its weight slot may be refilled
                     PF_MARK(4);
@@ -494,7 +534,7 @@ bool prefill_supported(int fmt, long long n, long long k, long long m, const voi
 cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!prefill_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
     PfParams p;
-    p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.y = a.y;
+    p.w = static_cast<const uint8_t *>(a.w); p.y = a.y;
     p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
     p.m_tiles = (int)((a.m + PF_BM - 1) / PF_BM);
     p.n_tiles = (int)((a.n + PF_BN - 1) / PF_BN);
@@ -505,12 +545,16 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    CUtensorMap x_map;
-    cudaError_t e = encode_tile_map(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
-                        (unsigned long long)p.nb * 292, PF_RAWA_WORDS, PF_BM);
+    // the Q8_K matrix as (m) rows of 73 * nb 32-bit words
+    CUtensorMap x_wide, x_narrow;
+    cudaError_t e = encode_tile_map(&x_wide, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
+                                    (unsigned long long)p.nb * 292, 32, PF_BM, true);
+    if (e != cudaSuccess) return e;
+    e = encode_tile_map(&x_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
+                        (unsigned long long)p.nb * 292, 4, PF_BM, false);
     if (e != cudaSuccess) return e;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    prefill_q4k_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_map);
+    prefill_q4k_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_wide, x_narrow);
     return cudaGetLastError();
 }
 

@@ -11,10 +11,13 @@
 namespace weft {
 
 // A 2-D row-major array of `rows` x `inner` elements with `row_pitch` bytes between rows (a multiple of 16,
-// base 16-byte aligned); the copied box is box_inner x box_rows elements, unswizzled, rows packed in
-// shared memory.  Elements outside the array read as zero and still count toward the barrier's bytes.
+// base 16-byte aligned); the copied box is box_inner x box_rows elements, rows packed in shared memory,
+// optionally with the 128-byte swizzle (16-byte chunk c of row r stored at chunk c ^ (r & 7); box rows of
+// exactly 128 bytes, destination 1024-byte aligned).  Elements outside the array read as zero and still
+// count toward the barrier's bytes.
 inline cudaError_t encode_tile_map(CUtensorMap *map, CUtensorMapDataType type, const void *base, unsigned long long inner,
-                                   unsigned long long rows, unsigned long long row_pitch, unsigned box_inner, unsigned box_rows) {
+                                   unsigned long long rows, unsigned long long row_pitch, unsigned box_inner, unsigned box_rows,
+                                   bool swizzle128 = false) {
     static PFN_cuTensorMapEncodeTiled_v12000 encode = [] {
         void *fn = nullptr;
         cudaDriverEntryPointQueryResult query;
@@ -27,7 +30,7 @@ inline cudaError_t encode_tile_map(CUtensorMap *map, CUtensorMapDataType type, c
     const cuuint32_t box[2] = {box_inner, box_rows};
     const cuuint32_t element_strides[2] = {1, 1};
     const CUresult r = encode(map, type, 2, const_cast<void *>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
