@@ -1,4 +1,5 @@
-"""GPU parity of the tensor-core prefill path (production_mul_mat_q4_k_staged) against the CPU oracle.
+"""GPU parity of the tensor-core prefill path (production_mul_mat_q4_k_staged, production_mul_mat_tq1_0)
+against the CPU oracle.
 
 Bound: 1e-5 relative L2.  The integer part (int8 MMAs, int32 / exact-f16 accumulation) is exact; only
 the per-block fp32 combine is rounded, in the reference's own order.
@@ -80,3 +81,41 @@ def test_prefill_matches_decode_path(torch, oracle):
         weft.compile(definition)(Buffer(w, shape=(n, k), encoding="Q4_K"), x, Buffer(xq, shape=(m, k), encoding="Q8_K"), y)
         outs.append(y.cpu().numpy())
     assert rel_l2(outs[0], outs[1]) <= 1e-5
+
+
+def _run_tq1_0(torch, oracle, m, n, k, seed, column_ranges=None):
+    import weft_b200 as weft
+    from weft_b200.kernels import mul_mat
+    from weft_b200.runtime import Buffer
+
+    rng = np.random.default_rng(seed)
+    w = weights(oracle.TQ1_0, rng, n, k)
+    x = activations(rng, m, k)
+    xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
+    y = torch.full((m, n), float("nan"), device="cuda")
+    powers = torch.tensor([1, 3, 9, 27, 81], dtype=torch.int32, device="cuda")
+    weft.compile(mul_mat.production_mul_mat_tq1_0)(
+        Buffer(torch.from_numpy(w).cuda(), shape=(n, k), encoding="TQ1_0"), torch.from_numpy(x).cuda(),
+        Buffer(xq, shape=(m, k), encoding="Q8_K"), Buffer(powers, shape=(5,), encoding="dense.u32"), y)
+    got = y.cpu().numpy()
+    want_xq = oracle.quantize(oracle.Q8_K, x, rule=1)
+    assert np.array_equal(xq.cpu().numpy(), want_xq)
+    assert np.isfinite(got).all()
+    for lo, hi in (column_ranges or [(0, n)]):
+        want, _ = oracle.mul_mat(oracle.TQ1_0, w, None, n, k, m, xq=want_xq, rows=(lo, hi))
+        err = rel_l2(got[:, lo:hi], want[:, lo:hi])
+        assert err <= 1e-5, (m, n, k, lo, hi, err)
+        assert reference_tolerance_ok(got[:, lo:hi], want[:, lo:hi])
+
+
+@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 2048), (512, 384, 1024), (32, 130, 4096), (200, 1001, 3072)])
+def test_prefill_tq1_0_shapes(torch, oracle, mnk):
+    """K a multiple of 1024 takes the tensor-core kernel; odd N exercises 2-byte-aligned weight rows."""
+    m, n, k = mnk
+    _run_tq1_0(torch, oracle, m, n, k, seed=sum(mnk))
+
+
+def test_prefill_tq1_0_benchmark_shape(torch, oracle):
+    """Config 5b: M = 512 tokens, (N, K) = (28672, 8192); three column bands against the oracle."""
+    n, k = 28672, 8192
+    _run_tq1_0(torch, oracle, 512, n, k, seed=5, column_ranges=[(0, 128), (n // 2 - 60, n // 2 + 70), (n - 128, n)])

@@ -132,4 +132,13 @@ __device__ __forceinline__ int tq1_digit(uint32_t packed, uint32_t power) {
     return (int)((wrapped * 3u) >> 8) - 1;
 }
 
+// digits of four packed bytes at once: ((byte*power) & 255) * 3 >> 8, in 16-bit lanes
+__device__ __forceinline__ uint32_t tq1_digits4(uint32_t q4, uint32_t power) {
+    const uint32_t M = 0x00ff00ffu;
+    uint32_t e = ((q4 & M) * power) & M, o = (((q4 >> 8) & M) * power) & M;
+    e = ((e * 3u) >> 8) & M;
+    o = ((o * 3u) >> 8) & M;
+    return e | (o << 8);
+}
+
 }  // namespace weft

@@ -250,15 +250,6 @@ __device__ inline bool stage_iq2_tables(const int8_t *grid, const int8_t *signs,
     return __syncthreads_or(bad) == 0;
 }
 
-// digits of four packed bytes at once: ((byte*power) & 255) * 3 >> 8, in 16-bit lanes
-__device__ __forceinline__ uint32_t tq1_digits4(uint32_t q4, uint32_t power) {
-    const uint32_t M = 0x00ff00ffu;
-    uint32_t e = ((q4 & M) * power) & M, o = (((q4 >> 8) & M) * power) & M;
-    e = ((e * 3u) >> 8) & M;
-    o = ((o * 3u) >> 8) & M;
-    return e | (o << 8);
-}
-
 // One TQ1_0 record (54 bytes, 2-byte aligned): 32 + 16 bytes of 5 trits, 4 bytes of 4 trits, f16 d.
 // sum((digit-1)*x) = sum(digit*x) - sum(x); every element of the unit is covered exactly once.
 template <int RL>

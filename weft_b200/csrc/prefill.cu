@@ -86,7 +86,8 @@ static_assert(PF_A_SLOT % 1024 == 0 && PF_B_SLOT % 1024 == 0 && PF_OFF_B % 1024 
 static_assert(PF_SMEM <= 227 * 1024, "shared memory budget");
 
 struct PfParams {
-    const uint8_t *w;     // (n, k) Q4_K records, 16-byte aligned rows
+    const uint8_t *w;     // (n, k) weight records (Q4_K: 16-byte aligned rows)
+    const uint32_t *powers;   // TQ1_0: {1, 3, 9, 27, 81}
     float *y;             // (m, ldy)
     long long n, m, ldy;
     int nb;               // 256-blocks per row
@@ -287,6 +288,75 @@ __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_s
     sts_u128(thin + PF_COL + 1024u, 0u, 0u, 0u, 0u);
 }
 
+// ---- TQ1_0 weights (examples/kernels/vec_dot/tq1_0_q8_k.py; GGML ggml-cpu/quants.c:430-480) ---------------------
+// A record is 54 bytes, 2-byte aligned: 32 + 16 bytes of five base-3 digits, 4 bytes of four, f16 d.  The
+// digits minus one are the int8 weight operand as they are (one limb, N = 64 per half, no min term), and
+// isum = sum (digit - 1) * x comes out of the MMA exactly.
+
+// The record as 14 words {12 x digits, qh, d}: aligned 4-byte loads and a 16-bit funnel shift when the
+// record starts in the middle of a word.  Rows past N read as zero (digit - 1 = -1 times d = 0).
+__device__ __forceinline__ void load_record_tq1(const PfParams &p, const BlockAt &at, int row, uint32_t (&w)[14]) {
+    const long long n = at.n0 + row;
+    if (n < p.n) {
+        const uintptr_t a = reinterpret_cast<uintptr_t>(p.w + ((size_t)n * p.nb + at.b) * 54);
+        const uint32_t *base = reinterpret_cast<const uint32_t *>(a & ~uintptr_t(3));
+        uint32_t raw[14];
+#pragma unroll
+        for (int i = 0; i < 13; ++i) raw[i] = __ldg(base + i);
+        if (a & 2u) {
+            raw[13] = __ldg(base + 13);
+#pragma unroll
+            for (int i = 0; i < 13; ++i) w[i] = __funnelshift_r(raw[i], raw[i + 1], 16);
+            w[13] = raw[13] >> 16;
+        } else {
+            raw[13] = (uint32_t)__ldg(reinterpret_cast<const unsigned short *>(base + 13));
+#pragma unroll
+            for (int i = 0; i < 14; ++i) w[i] = raw[i];
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 14; ++i) w[i] = 0;
+    }
+}
+
+// Element e of the block: digit n of byte j with e = 32 n + j (bytes 0..31), 160 + 16 n + j (bytes 32..47),
+// 240 + 4 n + j (qh).  Stream word g (elements 4g..4g+3) is therefore the digits n of one record word.
+template <int W>
+__device__ __forceinline__ void expand_tq1(const uint32_t (&w)[14], const uint32_t (&pw)[5], uint8_t *b_slot, uint8_t *wd_slot, int rh) {
+    reinterpret_cast<float2 *>(wd_slot)[rh] = make_float2(half_bits_to_float(w[13]), 0.f);
+    const uint32_t base = smem_addr(b_slot) + (uint32_t)(rh >> 3) * 1024u + (uint32_t)(rh & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(rh & 7) << 4;
+    uint32_t carry[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t cur[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int g = 16 * j + i;
+            const int n = g < 40 ? g >> 3 : g < 60 ? (g - 40) >> 2 : g - 60;
+            const int src = g < 40 ? (g & 7) : g < 60 ? 8 + ((g - 40) & 3) : 12;
+            // digits 0..2 -> -1, 0, +1 in every byte
+            cur[i] = (tq1_digits4(w[src], pw[n]) + 0x7f7f7f7fu) ^ 0x80808080u;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int idx = 4 * q + k;
+                o[k] = idx < W ? carry[idx < W ? idx : 0] : cur[idx < W ? 0 : idx - W];
+            }
+            const int chunk = 4 * j + q;
+            sts_u128(base + (uint32_t)(chunk >> 3) * PF_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7), o[0], o[1], o[2], o[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < W; ++i) carry[i] = cur[16 - W + i];
+    }
+    const uint32_t thin = smem_addr(b_slot) + PF_B_THIN + (uint32_t)rh * 16u;
+    sts_u128(thin, carry[0], W > 1 ? carry[1] : 0u, W > 2 ? carry[2] : 0u, W > 3 ? carry[3] : 0u);
+    sts_u128(thin + PF_COL, 0u, 0u, 0u, 0u);
+}
+
 // One thread asks for the tile's Q8_K records of a block: word x0 = 73 b - (b & 3) of each token row is the
 // 16-byte boundary at or before the record; two swizzled boxes of 128 bytes, three plain columns of 16.
 __device__ __forceinline__ void issue_activations(const CUtensorMap *wide, const CUtensorMap *narrow, const BlockAt &at, uint8_t *slot, uint64_t *bar) {
@@ -303,9 +373,11 @@ __device__ __forceinline__ void issue_activations(const CUtensorMap *wide, const
 // each split as s = 64 h + l (l in 0..63), to the f16 min-term operand {l | h}.  64 threads; thread ts keeps
 // pair g = ts & 7 and walks the rows (ts >> 3) + 8 t.  `shift` = 4 * (b & 3): record byte r sits at operand
 // byte r + shift.
+template <bool MIN_TERM>
 __device__ __forceinline__ void build_specials(uint8_t *a_slot, int shift, uint8_t *xd_slot, int ts) {
     const int g = ts & 7, r0 = ts >> 3;
     const uint32_t slot = smem_addr(a_slot);
+    if (MIN_TERM) {
     const uint32_t tb = 4u + (uint32_t)shift + 4u * (uint32_t)g;   // byte inside the tail columns (operand byte 256 + tb)
     const uint32_t src = slot + PF_A_THIN + (tb >> 4) * PF_COL + (tb & 15u) + (uint32_t)r0 * 16u;
     const uint32_t dst = slot + PF_A_M + (uint32_t)r0 * 16u + 2u * (uint32_t)g;   // core_offset(r0 + 8 t, 0, 2) = 256 t + 16 r0
@@ -319,6 +391,7 @@ __device__ __forceinline__ void build_specials(uint8_t *a_slot, int shift, uint8
         sts_u16(dst + t * 256, (uint32_t)__half_as_ushort(__int2half_rn(l)));
         sts_u16(dst + t * 256 + 128, (uint32_t)__half_as_ushort(__int2half_rn(h)));
     }
+    }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
         const int r = ts + 64 * k;
@@ -326,8 +399,10 @@ __device__ __forceinline__ void build_specials(uint8_t *a_slot, int shift, uint8
     }
 }
 
-__global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams p, const __grid_constant__ CUtensorMap x_wide,
-                                                                   const __grid_constant__ CUtensorMap x_narrow) {
+template <int FMT>
+__global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, const __grid_constant__ CUtensorMap x_wide,
+                                                               const __grid_constant__ CUtensorMap x_narrow) {
+    constexpr bool Q4K = FMT == F_Q4_K;
     extern __shared__ __align__(1024) uint8_t smem[];
     Control *ctl = reinterpret_cast<Control *>(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,32 +435,65 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
         // ------------------------------------------------------------------ weight producers
         const int row = threadIdx.x - 32 * PF_W_WARP0, half = row >> 6, rh = row & 63;
         uint8_t *b_ring = smem + PF_OFF_B;
-        BlockAt next = first_block(p);
-        uint4 wn[9];
-        if (total > 0) load_record(p, next, row, wn);
-        for (int it = 0; it < total && !ctl->abort; ++it) {
-            uint4 w[9];
-#pragma unroll
-            for (int i = 0; i < 9; ++i) w[i] = wn[i];
-            const int words = (next.b & 3) + 1;   // this block's operand shift
-            next.advance(p);
-            if (it + 1 < total) load_record(p, next, row, wn);   // in flight while this block is expanded
-            const int u = 2 * it + half;
-            const int sb = u % PF_B_SLOTS;
-            if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
-            PF_MARK0();
-            uint8_t *slot = b_ring + sb * PF_B_SLOT, *wd = smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
-            switch (words) {
-            case 1: expand_weights<1>(w, slot, wd, rh); break;
-            case 2: expand_weights<2>(w, slot, wd, rh); break;
-            case 3: expand_weights<3>(w, slot, wd, rh); break;
-            default: expand_weights<4>(w, slot, wd, rh); break;
+        if constexpr (Q4K) {
+            BlockAt next = first_block(p);
+            uint4 wn[9];
+            if (total > 0) load_record(p, next, row, wn);
+            for (int it = 0; it < total && !ctl->abort; ++it) {
+                uint4 w[9];
+    #pragma unroll
+                for (int i = 0; i < 9; ++i) w[i] = wn[i];
+                const int words = (next.b & 3) + 1;   // this block's operand shift
+                next.advance(p);
+                if (it + 1 < total) load_record(p, next, row, wn);   // in flight while this block is expanded
+                const int u = 2 * it + half;
+                const int sb = u % PF_B_SLOTS;
+                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
+                PF_MARK0();
+                uint8_t *slot = b_ring + sb * PF_B_SLOT, *wd = smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
+                switch (words) {
+                case 1: expand_weights<1>(w, slot, wd, rh); break;
+                case 2: expand_weights<2>(w, slot, wd, rh); break;
+                case 3: expand_weights<3>(w, slot, wd, rh); break;
+                default: expand_weights<4>(w, slot, wd, rh); break;
+                }
+                PF_MARK(4);
+                fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->b_full[sb]);
+                PF_MARK(5);
             }
-            PF_MARK(4);
-            fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->b_full[sb]);
-            PF_MARK(5);
+        } else {
+            BlockAt next = first_block(p);
+            uint32_t pw[5];
+    #pragma unroll
+            for (int i = 0; i < 5; ++i) pw[i] = __ldg(p.powers + i) & 0xffu;
+            uint32_t wn[14];
+            if (total > 0) load_record_tq1(p, next, row, wn);
+            for (int it = 0; it < total && !ctl->abort; ++it) {
+                uint32_t w[14];
+    #pragma unroll
+                for (int i = 0; i < 14; ++i) w[i] = wn[i];
+                const int words = (next.b & 3) + 1;   // this block's operand shift
+                next.advance(p);
+                if (it + 1 < total) load_record_tq1(p, next, row, wn);   // in flight while this block is expanded
+                const int u = 2 * it + half;
+                const int sb = u % PF_B_SLOTS;
+                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
+                PF_MARK0();
+                uint8_t *slot = b_ring + sb * PF_B_SLOT, *wd = smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
+                switch (words) {
+                case 1: expand_tq1<1>(w, pw, slot, wd, rh); break;
+                case 2: expand_tq1<2>(w, pw, slot, wd, rh); break;
+                case 3: expand_tq1<3>(w, pw, slot, wd, rh); break;
+                default: expand_tq1<4>(w, pw, slot, wd, rh); break;
+                }
+                PF_MARK(4);
+                fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->b_full[sb]);
+                PF_MARK(5);
+            }
         }
     } else if (warp >= PF_S_WARP0 && warp < PF_S_WARP0 + PF_S_WARPS) {
         // ------------------------------------------------------------------ scales and bsums of the landed activations
@@ -396,7 +504,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
             at.advance(p);
             if (!PF_TIMED(0, wait_or_abort(&ctl->a_landed[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
             PF_MARK0();
-            build_specials(smem + PF_OFF_A + sa * PF_A_SLOT, shift, smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, ts);
+            build_specials<Q4K>(smem + PF_OFF_A + sa * PF_A_SLOT, shift, smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, ts);
             PF_MARK(4);
             fence_proxy_async();
             __syncwarp();
@@ -422,7 +530,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
     } else if (warp == PF_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
         if (lane == 0) {
-            const uint32_t idesc_q = tc::idesc_i8(PF_BM, 2 * PF_HALF, true, true);
+            const uint32_t idesc_q = tc::idesc_i8(PF_BM, Q4K ? 2 * PF_HALF : PF_HALF, true, true);
             const uint32_t idesc_m = tc::idesc_f16_f32acc(PF_BM, PF_HALF);
             bool ok = true;
             for (int it = 0; it < total && ok && !ctl->abort; ++it) {
@@ -445,7 +553,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
                                    tc::smem_desc_sw128(b_q + (j >> 2) * PF_SLAB + (j & 3) * 32), idesc_q, j > 0);
                     // K bytes 256..287: two 16-byte columns, K-adjacent core matrices one column apart
                     tc::mma_i8(d, tc::smem_desc(a_q + PF_A_THIN, PF_COL, 128), tc::smem_desc(b_q + PF_B_THIN, PF_COL, 128), idesc_q, 1);
-                    tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_q + PF_A_M, 128, 256), tc::smem_desc(b_q + PF_B_M, 128, 256), idesc_m, 0);
+                    if (Q4K) tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_q + PF_A_M, 128, 256), tc::smem_desc(b_q + PF_B_M, 128, 256), idesc_m, 0);
                     tc::commit(&ctl->tmem_full[h]);   // this half's accumulators are complete
                     tc::commit(&ctl->b_empty[sb]);    // and its weight slot may be refilled
                     PF_MARK(4);
@@ -472,6 +580,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
                 const float4 *wd = reinterpret_cast<const float4 *>(smem + PF_OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT);
                 const float xd = reinterpret_cast<const float *>(smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT)[row];
                 PF_MARK0();
+                if constexpr (Q4K) {
 #pragma unroll
                 for (int c = 0; c < PF_HALF / 8; ++c) {
                     uint32_t hi[8], lo[8], mt[8];
@@ -491,6 +600,27 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
                         acc[8 * c + i] += xd * (s2.x * v0 - s2.y * __uint_as_float(mt[i]));
                         acc[8 * c + i + 1] += xd * (s2.z * v1 - s2.w * __uint_as_float(mt[i + 1]));
                     }
+                }
+                } else {
+#pragma unroll
+                for (int c = 0; c < PF_HALF / 16; ++c) {
+                    uint32_t is[16];
+                    tc::tmem_ld16(lane_base + 16 * c, is);
+                    tc::tmem_ld_wait();
+                    if (c == PF_HALF / 16 - 1) {   // last read of this half: hand its columns back to the MMA warp
+                        tc::fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctl->tmem_empty[h]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i += 2) {
+                        const float4 s2 = wd[(16 * c + i) >> 1];
+                        // |isum| <= 256 * 128: exact through the same constant as limbs_to_float
+                        const float v0 = __uint_as_float(is[i] + 0x4b400000u) - 12582912.f, v1 = __uint_as_float(is[i + 1] + 0x4b400000u) - 12582912.f;
+                        acc[16 * c + i] += v0 * (s2.x * xd);
+                        acc[16 * c + i + 1] += v1 * (s2.z * xd);
+                    }
+                }
                 }
                 PF_MARK(4);
             }
@@ -526,22 +656,24 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_q4k_kernel(const PfParams 
 bool prefill_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq) {
     static const bool disabled = getenv("WEFT_B200_NO_TENSOR_PREFILL") != nullptr;
     // K a multiple of 1024: Q8_K rows (292 bytes per 256) are then whole 16-byte multiples, which the TMA box loads need
-    return !disabled && fmt == F_Q4_K && k > 0 && k % 1024 == 0 && n > 0 && m >= 32 &&
-           (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0 &&
+    if (fmt == F_TQ1_0 ? (reinterpret_cast<uintptr_t>(w) & 1u) != 0 : fmt == F_Q4_K ? (reinterpret_cast<uintptr_t>(w) & 15u) != 0 : true) return false;
+    return !disabled && k > 0 && k % 1024 == 0 && n > 0 && m >= 32 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0 &&
            n < (1LL << 31) && m < (1LL << 31);
 }
 
 cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!prefill_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
     PfParams p;
-    p.w = static_cast<const uint8_t *>(a.w); p.y = a.y;
+    p.w = static_cast<const uint8_t *>(a.w); p.powers = a.powers; p.y = a.y;
+    if (a.fmt == F_TQ1_0 && !a.powers) return cudaErrorInvalidValue;
     p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
     p.m_tiles = (int)((a.m + PF_BM - 1) / PF_BM);
     p.n_tiles = (int)((a.n + PF_BN - 1) / PF_BN);
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_q4k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<F_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<F_TQ1_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -554,7 +686,8 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
                         (unsigned long long)p.nb * 292, 4, PF_BM, false);
     if (e != cudaSuccess) return e;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    prefill_q4k_kernel<<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_wide, x_narrow);
+    if (a.fmt == F_Q4_K) prefill_kernel<F_Q4_K><<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_wide, x_narrow);
+    else prefill_kernel<F_TQ1_0><<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_wide, x_narrow);
     return cudaGetLastError();
 }
 
