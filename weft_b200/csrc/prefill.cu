@@ -29,8 +29,8 @@
 // CTA = 128 tokens (TMEM lanes) x 128 weights, persistent over tiles.  The 128 weights are two halves of
 // 64; each half owns 192 TMEM columns ([q*a | q*c | min term]), so the tensor core works on one half
 // while the epilogue drains the other.  Warp roles:
-//   warps 0-7   epilogue, warp = (half, 32-token quarter): tcgen05.ld the accumulators, combine, keep
-//               32 x 64 fp32 in registers across the blocks of a tile
+//   warps 0-7   epilogue, warp = (32-token quarter, 32 of the 64 columns of each half): tcgen05.ld the
+//               accumulators, combine, keep 32 x 64 fp32 in registers across the blocks of a tile
 //   warps 8-11  weight producers, one weight row per thread: the row's Q4_K record is read from global
 //               memory in place (no repack in HBM), one block ahead, and expanded into the shifted
 //               two-limb operand
@@ -112,6 +112,34 @@ __device__ __forceinline__ float limbs_to_float(uint32_t hi, uint32_t lo) {
     const float fh = __uint_as_float(hi + 0x4b400000u) - 12582912.f;
     const float fl = __uint_as_float(lo + 0x4b400000u) - 12582912.f;
     return fmaf(8.f, fh, fl);
+}
+
+// Packed pairs of fp32 (sm_100 executes add / mul / fma on two floats held in a 64-bit register pair with one
+// instruction; each lane of the pair is an ordinary IEEE round-to-nearest operation).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+// the integers of two accumulator columns as floats, exactly (|v| < 2^22, see limbs_to_float)
+__device__ __forceinline__ uint64_t ints_to_float2(uint32_t a, uint32_t b) {
+    return add2(pack2(__uint_as_float(a + 0x4b400000u), __uint_as_float(b + 0x4b400000u)), pack2(-12582912.f, -12582912.f));
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
@@ -229,7 +257,9 @@ __device__ __forceinline__ void load_record(const PfParams &p, const BlockAt &at
 template <int W>
 __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_slot, uint8_t *wd_slot, int rh) {
     const uint4 hd = w[0];
-    reinterpret_cast<float2 *>(wd_slot)[rh] = make_float2(half_bits_to_float(hd.x), half_bits_to_float(hd.x >> 16));
+    // per pair of weights {d, d', -dmin, -dmin'}: the epilogue reads a pair's scales as two packed operands
+    reinterpret_cast<float *>(wd_slot)[4 * (rh >> 1) + (rh & 1)] = half_bits_to_float(hd.x);
+    reinterpret_cast<float *>(wd_slot)[4 * (rh >> 1) + (rh & 1) + 2] = -half_bits_to_float(hd.x >> 16);
     const Q4KScales s = q4k_unpack_scales(hd.y, hd.z, hd.w);
     float mn[8];
 #pragma unroll
@@ -323,7 +353,7 @@ __device__ __forceinline__ void load_record_tq1(const PfParams &p, const BlockAt
 // 240 + 4 n + j (qh).  Stream word g (elements 4g..4g+3) is therefore the digits n of one record word.
 template <int W>
 __device__ __forceinline__ void expand_tq1(const uint32_t (&w)[14], const uint32_t (&pw)[5], uint8_t *b_slot, uint8_t *wd_slot, int rh) {
-    reinterpret_cast<float2 *>(wd_slot)[rh] = make_float2(half_bits_to_float(w[13]), 0.f);
+    reinterpret_cast<float *>(wd_slot)[4 * (rh >> 1) + (rh & 1)] = half_bits_to_float(w[13]);
     const uint32_t base = smem_addr(b_slot) + (uint32_t)(rh >> 3) * 1024u + (uint32_t)(rh & 7) * 128u;
     const uint32_t x7 = (uint32_t)(rh & 7) << 4;
     uint32_t carry[4] = {0, 0, 0, 0};
@@ -414,7 +444,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
     if (threadIdx.x == 0) {
         for (int s = 0; s < PF_A_SLOTS; ++s) { mbar_init(&ctl->a_landed[s], 1); mbar_init(&ctl->a_full[s], PF_S_WARPS); mbar_init(&ctl->a_empty[s], 1); }
         for (int s = 0; s < PF_B_SLOTS; ++s) { mbar_init(&ctl->b_full[s], 2); mbar_init(&ctl->b_empty[s], 1); }
-        for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 4); }
+        for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 8); }
         ctl->abort = 0;
         ctl->tmem_base = 0xffffffffu;
         mbar_fence_init();
@@ -562,79 +592,95 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
             }
         }
     } else if (warp < 8) {
-        // ------------------------------------------------------------------ epilogue: warp = (64-weight half, 32-token quarter)
-        const int quarter = warp & 3, h = warp >> 2;
+        // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, column set)
+        // Every warp takes 32 of the 64 columns of BOTH halves: while it combines its share of one half the
+        // tensor core is already working on the other, so neither waits for a whole half to drain.
+        constexpr int EC = PF_HALF / 2;   // columns of one half per warp
+        const int quarter = warp & 3, cset = warp >> 2;
         const int row = quarter * 32 + lane;   // token row of the tile = TMEM lane
-        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16) + h * PF_HALF_COLS;
-        float acc[PF_HALF];
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16) + cset * EC;
+        uint64_t acc[2][EC / 2];   // packed pairs of fp32
         int it = 0;
         bool ok = true;
         for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
             const int tile = (int)blockIdx.x + t * (int)gridDim.x;
-            const long long n0 = (long long)(tile / p.m_tiles) * PF_BN + h * PF_HALF, m0 = (long long)(tile % p.m_tiles) * PF_BM;
+            const long long n0 = (long long)(tile / p.m_tiles) * PF_BN + cset * EC, m0 = (long long)(tile % p.m_tiles) * PF_BM;
 #pragma unroll
-            for (int i = 0; i < PF_HALF; ++i) acc[i] = 0.f;
-            for (int b = 0; b < nb; ++b, ++it) {
-                if (!PF_TIMED(0, wait_or_abort(&ctl->tmem_full[h], (uint32_t)(it & 1), ctl, p.status))) { ok = false; break; }
-                tc::fence_after_sync();
-                const float4 *wd = reinterpret_cast<const float4 *>(smem + PF_OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT);
-                const float xd = reinterpret_cast<const float *>(smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT)[row];
-                PF_MARK0();
-                if constexpr (Q4K) {
+            for (int i = 0; i < EC / 2; ++i) { acc[0][i] = 0ull; acc[1][i] = 0ull; }
+            for (int b = 0; b < nb && ok; ++b, ++it) {
 #pragma unroll
-                for (int c = 0; c < PF_HALF / 8; ++c) {
-                    uint32_t hi[8], lo[8], mt[8];
-                    tc::tmem_ld8(lane_base + 8 * c, hi);
-                    tc::tmem_ld8(lane_base + PF_HALF + 8 * c, lo);
-                    tc::tmem_ld8(lane_base + 2 * PF_HALF + 8 * c, mt);
-                    tc::tmem_ld_wait();
-                    if (c == PF_HALF / 8 - 1) {   // last read of this half: hand its columns back to the MMA warp
-                        tc::fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&ctl->tmem_empty[h]);
+                for (int h = 0; h < 2; ++h) {
+                    if (!PF_TIMED(0, wait_or_abort(&ctl->tmem_full[h], (uint32_t)(it & 1), ctl, p.status))) { ok = false; break; }
+                    tc::fence_after_sync();
+                    // written before the block's MMAs were issued: visible once their accumulators are
+                    const float xd = reinterpret_cast<const float *>(smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT)[row];
+                    const ulonglong2 *wd = reinterpret_cast<const ulonglong2 *>(smem + PF_OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT) + cset * (EC / 2);
+                    const uint64_t xd2 = pack2(xd, xd);
+                    const uint32_t half_base = lane_base + h * PF_HALF_COLS;
+                    PF_MARK0();
+                    if constexpr (Q4K) {
+#pragma unroll
+                        for (int c = 0; c < EC / 8; ++c) {
+                            uint32_t hi[8], lo[8], mt[8];
+                            tc::tmem_ld8(half_base + 8 * c, hi);
+                            tc::tmem_ld8(half_base + PF_HALF + 8 * c, lo);
+                            tc::tmem_ld8(half_base + 2 * PF_HALF + 8 * c, mt);
+                            tc::tmem_ld_wait();
+                            if (c == EC / 8 - 1) {   // last read of this half: hand its columns back to the MMA warp
+                                tc::fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&ctl->tmem_empty[h]);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 8; i += 2) {
+                                const ulonglong2 s2 = wd[(8 * c + i) >> 1];   // {d, d'}, {-dmin, -dmin'}
+                                // f32(8 hi + lo): both limbs exact as floats, one rounding in the fused multiply-add
+                                const uint64_t v = fma2(pack2(8.f, 8.f), ints_to_float2(hi[i], hi[i + 1]), ints_to_float2(lo[i], lo[i + 1]));
+                                const uint64_t t = fma2(s2.y, pack2(__uint_as_float(mt[i]), __uint_as_float(mt[i + 1])), mul2(s2.x, v));
+                                acc[h][(8 * c + i) >> 1] = fma2(xd2, t, acc[h][(8 * c + i) >> 1]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < EC / 16; ++c) {
+                            uint32_t is[16];
+                            tc::tmem_ld16(half_base + 16 * c, is);
+                            tc::tmem_ld_wait();
+                            if (c == EC / 16 - 1) {
+                                tc::fence_before_sync();
+                                __syncwarp();
+                                if (lane == 0) mbar_arrive(&ctl->tmem_empty[h]);
+                            }
+#pragma unroll
+                            for (int i = 0; i < 16; i += 2) {
+                                const ulonglong2 s2 = wd[(16 * c + i) >> 1];   // {d, d'}
+                                // |isum| <= 256 * 128: exact as a float
+                                acc[h][(16 * c + i) >> 1] = fma2(ints_to_float2(is[i], is[i + 1]), mul2(s2.x, xd2), acc[h][(16 * c + i) >> 1]);
+                            }
+                        }
                     }
-#pragma unroll
-                    for (int i = 0; i < 8; i += 2) {
-                        const float4 s2 = wd[(8 * c + i) >> 1];
-                        const float v0 = limbs_to_float(hi[i], lo[i]), v1 = limbs_to_float(hi[i + 1], lo[i + 1]);
-                        acc[8 * c + i] += xd * (s2.x * v0 - s2.y * __uint_as_float(mt[i]));
-                        acc[8 * c + i + 1] += xd * (s2.z * v1 - s2.w * __uint_as_float(mt[i + 1]));
-                    }
+                    PF_MARK(4);
                 }
-                } else {
-#pragma unroll
-                for (int c = 0; c < PF_HALF / 16; ++c) {
-                    uint32_t is[16];
-                    tc::tmem_ld16(lane_base + 16 * c, is);
-                    tc::tmem_ld_wait();
-                    if (c == PF_HALF / 16 - 1) {   // last read of this half: hand its columns back to the MMA warp
-                        tc::fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&ctl->tmem_empty[h]);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 16; i += 2) {
-                        const float4 s2 = wd[(16 * c + i) >> 1];
-                        // |isum| <= 256 * 128: exact through the same constant as limbs_to_float
-                        const float v0 = __uint_as_float(is[i] + 0x4b400000u) - 12582912.f, v1 = __uint_as_float(is[i + 1] + 0x4b400000u) - 12582912.f;
-                        acc[16 * c + i] += v0 * (s2.x * xd);
-                        acc[16 * c + i + 1] += v1 * (s2.z * xd);
-                    }
-                }
-                }
-                PF_MARK(4);
             }
             if (!ok) break;
             const long long m = m0 + row;
             if (m < p.m) {
-                float *out = p.y + (size_t)m * p.ldy + n0;
-                if (n0 + PF_HALF <= p.n && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) {
 #pragma unroll
-                    for (int i = 0; i < PF_HALF; i += 4) *reinterpret_cast<float4 *>(out + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
-                } else {
+                for (int h = 0; h < 2; ++h) {
+                    const long long nh = n0 + h * PF_HALF;
+                    float *out = p.y + (size_t)m * p.ldy + nh;
+                    if (nh + EC <= p.n && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0)) {
 #pragma unroll
-                    for (int i = 0; i < PF_HALF; ++i)
-                        if (n0 + i < p.n) out[i] = acc[i];
+                        for (int i = 0; i < EC; i += 4) *reinterpret_cast<ulonglong2 *>(out + i) = make_ulonglong2(acc[h][i >> 1], acc[h][(i >> 1) + 1]);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < EC; i += 2) {
+                            float a0, a1;
+                            unpack2(acc[h][i >> 1], a0, a1);
+                            if (nh + i < p.n) out[i] = a0;
+                            if (nh + i + 1 < p.n) out[i + 1] = a1;
+                        }
+                    }
                 }
             }
         }
