@@ -65,25 +65,38 @@ constexpr int PF_A_THIN = 2 * PF_SLAB;                 // three columns: K bytes
 constexpr int PF_A_M = PF_A_THIN + 3 * PF_COL;         // {l, h} f16 per token (128 x 32 bytes)
 constexpr int PF_A_SLOT = PF_A_M + PF_BM * 32;         // 42 KB, one 256-block of activations
 constexpr int PF_A_TMA_BYTES = 2 * PF_SLAB + 3 * PF_COL;
-constexpr int PF_A_SLOTS = 2;
-constexpr int PF_B_THIN = 2 * PF_SLAB;                 // two columns: K bytes 256..287 of [q*a rows 0-63 | q*c rows 64-127]
-constexpr int PF_B_M = PF_B_THIN + 2 * PF_COL;         // {mn, 64 mn} f16 per weight (64 x 32 bytes)
-constexpr int PF_B_SLOT = PF_B_M + PF_HALF * 32;       // 38 KB, one 256-block of one 64-weight half
-constexpr int PF_B_SLOTS = 3;
-constexpr int PF_WD_SLOT = PF_HALF * 8;                // {d, dmin} per weight of one half
+constexpr int PF_WD_SLOT = PF_HALF * 8;                // per pair of weights of one half {d, d', -dmin, -dmin'}
 constexpr int PF_WD_SLOTS = 8;
 constexpr int PF_XD_SLOT = PF_BM * 4;                  // x.ds per token
 constexpr int PF_XD_SLOTS = 4;
 constexpr int PF_CONTROL = 1024;
-constexpr int PF_OFF_A = PF_CONTROL;
-constexpr int PF_OFF_B = PF_OFF_A + PF_A_SLOTS * PF_A_SLOT;
-constexpr int PF_OFF_WD = PF_OFF_B + PF_B_SLOTS * PF_B_SLOT;
-constexpr int PF_OFF_XD = PF_OFF_WD + PF_WD_SLOTS * PF_WD_SLOT;
-constexpr int PF_SMEM = PF_OFF_XD + PF_XD_SLOTS * PF_XD_SLOT;
 constexpr int PF_TMEM_COLS = 512;                      // 2 x 192 used
 constexpr int PF_HALF_COLS = 192;
-static_assert(PF_A_SLOT % 1024 == 0 && PF_B_SLOT % 1024 == 0 && PF_OFF_B % 1024 == 0, "swizzled slabs must stay 1024-byte aligned");
-static_assert(PF_SMEM <= 227 * 1024, "shared memory budget");
+constexpr int PF_MAX_A_SLOTS = 3, PF_MAX_B_SLOTS = 4;
+
+// The weight operand of one 64-weight half and the ring depths, per format.
+//   Q4_K : rows [q*a 0-63 | q*c 64-127], the f16 {mn, 64 mn} rows; 2 activation slots, 3 weight slots
+//   TQ1_0: rows of digits 0-63; 3 activation slots, 4 weight slots
+template <int FMT>
+struct Cfg {
+    static constexpr bool Q4K = FMT == F_Q4_K;
+    static constexpr int B_ROWS = Q4K ? 2 * PF_HALF : PF_HALF;
+    static constexpr int B_SLAB = B_ROWS * 128;            // K bytes 0..127 / 128..255, swizzled
+    static constexpr int B_COL = B_ROWS * 16;              // one 16-byte column
+    static constexpr int B_THIN = 2 * B_SLAB;              // two columns: K bytes 256..287
+    static constexpr int B_M = B_THIN + 2 * B_COL;         // Q4_K: {mn, 64 mn} f16 per weight (64 x 32 bytes)
+    static constexpr int B_SLOT = B_M + (Q4K ? PF_HALF * 32 : 0);   // 38 KB / 18 KB
+    static constexpr int A_SLOTS = Q4K ? 2 : 3;
+    static constexpr int B_SLOTS = Q4K ? 3 : 4;
+    static constexpr int OFF_A = PF_CONTROL;
+    static constexpr int OFF_B = OFF_A + A_SLOTS * PF_A_SLOT;
+    static constexpr int OFF_WD = OFF_B + B_SLOTS * B_SLOT;
+    static constexpr int OFF_XD = OFF_WD + PF_WD_SLOTS * PF_WD_SLOT;
+    static constexpr int SMEM = OFF_XD + PF_XD_SLOTS * PF_XD_SLOT;
+    static_assert(PF_A_SLOT % 1024 == 0 && B_SLOT % 1024 == 0 && OFF_B % 1024 == 0, "swizzled slabs must stay 1024-byte aligned");
+    static_assert(SMEM <= 227 * 1024, "shared memory budget");
+    static_assert(A_SLOTS <= PF_MAX_A_SLOTS && B_SLOTS <= PF_MAX_B_SLOTS, "barrier arrays");
+};
 
 struct PfParams {
     const uint8_t *w;     // (n, k) weight records (Q4_K: 16-byte aligned rows)
@@ -157,8 +170,8 @@ __device__ __forceinline__ void sts_u128(uint32_t addr, uint32_t a, uint32_t b, 
 }
 
 struct Control {
-    uint64_t a_landed[PF_A_SLOTS], a_full[PF_A_SLOTS], a_empty[PF_A_SLOTS];
-    uint64_t b_full[PF_B_SLOTS], b_empty[PF_B_SLOTS];
+    uint64_t a_landed[PF_MAX_A_SLOTS], a_full[PF_MAX_A_SLOTS], a_empty[PF_MAX_A_SLOTS];
+    uint64_t b_full[PF_MAX_B_SLOTS], b_empty[PF_MAX_B_SLOTS];
     uint64_t tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     volatile int abort;
@@ -264,7 +277,7 @@ __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_s
     float mn[8];
 #pragma unroll
     for (int g = 0; g < 8; ++g) mn[g] = (float)byte_of(g < 4 ? s.mn_lo : s.mn_hi, g & 3);
-    uint8_t *bm = b_slot + PF_B_M;
+    uint8_t *bm = b_slot + Cfg<F_Q4_K>::B_M;
     *reinterpret_cast<uint4 *>(bm + core_offset(rh, 0, 2)) =
         make_uint4(pack_half2(mn[0], mn[1]), pack_half2(mn[2], mn[3]), pack_half2(mn[4], mn[5]), pack_half2(mn[6], mn[7]));
     *reinterpret_cast<uint4 *>(bm + core_offset(rh, 1, 2)) =
@@ -303,7 +316,7 @@ __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_s
                 oc[k] = idx < W ? cc[idx < W ? idx : 0] : cur_c[idx < W ? 0 : idx - W];
             }
             const int chunk = 4 * j + q;   // 16-byte K chunk 0..15
-            const uint32_t at = base + (uint32_t)(chunk >> 3) * PF_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7);
+            const uint32_t at = base + (uint32_t)(chunk >> 3) * Cfg<F_Q4_K>::B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7);
             sts_u128(at, oa[0], oa[1], oa[2], oa[3]);
             sts_u128(at + 8192u, oc[0], oc[1], oc[2], oc[3]);
         }
@@ -311,11 +324,11 @@ __device__ __forceinline__ void expand_weights(const uint4 (&w)[9], uint8_t *b_s
         for (int i = 0; i < W; ++i) { ca[i] = cur_a[16 - W + i]; cc[i] = cur_c[16 - W + i]; }
     }
     // K chunk 16: the carried words, then zeros; chunk 17: zeros
-    const uint32_t thin = smem_addr(b_slot) + PF_B_THIN + (uint32_t)rh * 16u;
+    const uint32_t thin = smem_addr(b_slot) + Cfg<F_Q4_K>::B_THIN + (uint32_t)rh * 16u;
     sts_u128(thin, ca[0], W > 1 ? ca[1] : 0u, W > 2 ? ca[2] : 0u, W > 3 ? ca[3] : 0u);
     sts_u128(thin + 1024u, cc[0], W > 1 ? cc[1] : 0u, W > 2 ? cc[2] : 0u, W > 3 ? cc[3] : 0u);
-    sts_u128(thin + PF_COL, 0u, 0u, 0u, 0u);
-    sts_u128(thin + PF_COL + 1024u, 0u, 0u, 0u, 0u);
+    sts_u128(thin + Cfg<F_Q4_K>::B_COL, 0u, 0u, 0u, 0u);
+    sts_u128(thin + Cfg<F_Q4_K>::B_COL + 1024u, 0u, 0u, 0u, 0u);
 }
 
 // ---- TQ1_0 weights (examples/kernels/vec_dot/tq1_0_q8_k.py; GGML ggml-cpu/quants.c:430-480) ---------------------
@@ -377,14 +390,14 @@ __device__ __forceinline__ void expand_tq1(const uint32_t (&w)[14], const uint32
                 o[k] = idx < W ? carry[idx < W ? idx : 0] : cur[idx < W ? 0 : idx - W];
             }
             const int chunk = 4 * j + q;
-            sts_u128(base + (uint32_t)(chunk >> 3) * PF_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7), o[0], o[1], o[2], o[3]);
+            sts_u128(base + (uint32_t)(chunk >> 3) * Cfg<F_TQ1_0>::B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7), o[0], o[1], o[2], o[3]);
         }
 #pragma unroll
         for (int i = 0; i < W; ++i) carry[i] = cur[16 - W + i];
     }
-    const uint32_t thin = smem_addr(b_slot) + PF_B_THIN + (uint32_t)rh * 16u;
+    const uint32_t thin = smem_addr(b_slot) + Cfg<F_TQ1_0>::B_THIN + (uint32_t)rh * 16u;
     sts_u128(thin, carry[0], W > 1 ? carry[1] : 0u, W > 2 ? carry[2] : 0u, W > 3 ? carry[3] : 0u);
-    sts_u128(thin + PF_COL, 0u, 0u, 0u, 0u);
+    sts_u128(thin + Cfg<F_TQ1_0>::B_COL, 0u, 0u, 0u, 0u);
 }
 
 // One thread asks for the tile's Q8_K records of a block: word x0 = 73 b - (b & 3) of each token row is the
@@ -432,7 +445,8 @@ __device__ __forceinline__ void build_specials(uint8_t *a_slot, int shift, uint8
 template <int FMT>
 __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, const __grid_constant__ CUtensorMap x_wide,
                                                                const __grid_constant__ CUtensorMap x_narrow) {
-    constexpr bool Q4K = FMT == F_Q4_K;
+    using C = Cfg<FMT>;
+    constexpr bool Q4K = C::Q4K;
     extern __shared__ __align__(1024) uint8_t smem[];
     Control *ctl = reinterpret_cast<Control *>(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -442,8 +456,8 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
     const int total = my_tiles * nb;   // 256-blocks this CTA works through
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PF_A_SLOTS; ++s) { mbar_init(&ctl->a_landed[s], 1); mbar_init(&ctl->a_full[s], PF_S_WARPS); mbar_init(&ctl->a_empty[s], 1); }
-        for (int s = 0; s < PF_B_SLOTS; ++s) { mbar_init(&ctl->b_full[s], 2); mbar_init(&ctl->b_empty[s], 1); }
+        for (int s = 0; s < C::A_SLOTS; ++s) { mbar_init(&ctl->a_landed[s], 1); mbar_init(&ctl->a_full[s], PF_S_WARPS); mbar_init(&ctl->a_empty[s], 1); }
+        for (int s = 0; s < C::B_SLOTS; ++s) { mbar_init(&ctl->b_full[s], 2); mbar_init(&ctl->b_empty[s], 1); }
         for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 8); }
         ctl->abort = 0;
         ctl->tmem_base = 0xffffffffu;
@@ -464,7 +478,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
     if (warp >= PF_W_WARP0 && warp < PF_W_WARP0 + 4) {
         // ------------------------------------------------------------------ weight producers
         const int row = threadIdx.x - 32 * PF_W_WARP0, half = row >> 6, rh = row & 63;
-        uint8_t *b_ring = smem + PF_OFF_B;
+        uint8_t *b_ring = smem + C::OFF_B;
         if constexpr (Q4K) {
             BlockAt next = first_block(p);
             uint4 wn[9];
@@ -477,10 +491,10 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                 next.advance(p);
                 if (it + 1 < total) load_record(p, next, row, wn);   // in flight while this block is expanded
                 const int u = 2 * it + half;
-                const int sb = u % PF_B_SLOTS;
-                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
+                const int sb = u % C::B_SLOTS;
+                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / C::B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
                 PF_MARK0();
-                uint8_t *slot = b_ring + sb * PF_B_SLOT, *wd = smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
+                uint8_t *slot = b_ring + sb * C::B_SLOT, *wd = smem + C::OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
                 switch (words) {
                 case 1: expand_weights<1>(w, slot, wd, rh); break;
                 case 2: expand_weights<2>(w, slot, wd, rh); break;
@@ -508,10 +522,10 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                 next.advance(p);
                 if (it + 1 < total) load_record_tq1(p, next, row, wn);   // in flight while this block is expanded
                 const int u = 2 * it + half;
-                const int sb = u % PF_B_SLOTS;
-                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / PF_B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
+                const int sb = u % C::B_SLOTS;
+                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / C::B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
                 PF_MARK0();
-                uint8_t *slot = b_ring + sb * PF_B_SLOT, *wd = smem + PF_OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
+                uint8_t *slot = b_ring + sb * C::B_SLOT, *wd = smem + C::OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
                 switch (words) {
                 case 1: expand_tq1<1>(w, pw, slot, wd, rh); break;
                 case 2: expand_tq1<2>(w, pw, slot, wd, rh); break;
@@ -530,11 +544,12 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
         const int ts = threadIdx.x - 32 * PF_S_WARP0;
         BlockAt at = first_block(p);
         for (int it = 0; it < total && !ctl->abort; ++it) {
-            const int sa = it & 1, shift = 4 * (at.b & 3);
+            const int sa = it % C::A_SLOTS, shift = 4 * (at.b & 3);
+            const uint32_t a_phase = (uint32_t)(it / C::A_SLOTS) & 1u;
             at.advance(p);
-            if (!PF_TIMED(0, wait_or_abort(&ctl->a_landed[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
+            if (!PF_TIMED(0, wait_or_abort(&ctl->a_landed[sa], a_phase, ctl, p.status))) break;
             PF_MARK0();
-            build_specials<Q4K>(smem + PF_OFF_A + sa * PF_A_SLOT, shift, smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, ts);
+            build_specials<Q4K>(smem + C::OFF_A + sa * PF_A_SLOT, shift, smem + C::OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, ts);
             PF_MARK(4);
             fence_proxy_async();
             __syncwarp();
@@ -547,15 +562,16 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
             BlockAt at = first_block(p);
             int issued = 0;
             for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
-                const int sa = it & 1;
-                // the slot was last read by the MMAs of block it - 2 (and, before them, by the warps above)
-                if (!PF_TIMED(0, wait_one(&ctl->a_empty[sa], (uint32_t)((it >> 1) & 1) ^ 1u, ctl, p.status))) break;
+                const int sa = it % C::A_SLOTS;
+                const uint32_t a_phase = (uint32_t)(it / C::A_SLOTS) & 1u;
+                // the slot was last read by the MMAs of block it - C::A_SLOTS (and, before them, by the warps above)
+                if (!PF_TIMED(0, wait_one(&ctl->a_empty[sa], a_phase ^ 1u, ctl, p.status))) break;
                 fence_proxy_async();
-                issue_activations(&x_wide, &x_narrow, at, smem + PF_OFF_A + sa * PF_A_SLOT, &ctl->a_landed[sa]);
+                issue_activations(&x_wide, &x_narrow, at, smem + C::OFF_A + sa * PF_A_SLOT, &ctl->a_landed[sa]);
                 issued = it + 1;
             }
             // left early: let the copies in flight land (a phase that has completed already returns at once)
-            for (int j = issued > 2 ? issued - 2 : 0; j < issued; ++j) mbar_wait(&ctl->a_landed[j & 1], (uint32_t)((j >> 1) & 1));
+            for (int j = issued > C::A_SLOTS ? issued - C::A_SLOTS : 0; j < issued; ++j) mbar_wait(&ctl->a_landed[j % C::A_SLOTS], (uint32_t)(j / C::A_SLOTS) & 1u);
         }
     } else if (warp == PF_MMA_WARP) {
         // ------------------------------------------------------------------ MMA issue
@@ -564,26 +580,27 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
             const uint32_t idesc_m = tc::idesc_f16_f32acc(PF_BM, PF_HALF);
             bool ok = true;
             for (int it = 0; it < total && ok && !ctl->abort; ++it) {
-                const int sa = it & 1;
-                if (!PF_TIMED(0, wait_one(&ctl->a_landed[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
-                if (!PF_TIMED(3, wait_one(&ctl->a_full[sa], (uint32_t)((it >> 1) & 1), ctl, p.status))) break;
-                const uint32_t a_q = smem_addr(smem + PF_OFF_A + sa * PF_A_SLOT);
+                const int sa = it % C::A_SLOTS;
+                const uint32_t a_phase = (uint32_t)(it / C::A_SLOTS) & 1u;
+                if (!PF_TIMED(0, wait_one(&ctl->a_landed[sa], a_phase, ctl, p.status))) break;
+                if (!PF_TIMED(3, wait_one(&ctl->a_full[sa], a_phase, ctl, p.status))) break;
+                const uint32_t a_q = smem_addr(smem + C::OFF_A + sa * PF_A_SLOT);
                 for (int h = 0; h < 2; ++h) {
                     const int u = 2 * it + h;
-                    const int sb = u % PF_B_SLOTS;
-                    if (!PF_TIMED(1, wait_one(&ctl->b_full[sb], (uint32_t)((u / PF_B_SLOTS) & 1), ctl, p.status))) { ok = false; break; }
+                    const int sb = u % C::B_SLOTS;
+                    if (!PF_TIMED(1, wait_one(&ctl->b_full[sb], (uint32_t)((u / C::B_SLOTS) & 1), ctl, p.status))) { ok = false; break; }
                     if (!PF_TIMED(2, wait_one(&ctl->tmem_empty[h], (uint32_t)(it & 1) ^ 1u, ctl, p.status))) { ok = false; break; }
                     tc::fence_after_sync();
                     PF_MARK0();
-                    const uint32_t b_q = smem_addr(smem + PF_OFF_B + sb * PF_B_SLOT);
+                    const uint32_t b_q = smem_addr(smem + C::OFF_B + sb * C::B_SLOT);
                     const uint32_t d = tmem + h * PF_HALF_COLS;
 #pragma unroll
                     for (int j = 0; j < 8; ++j)   // K = 32 per instruction: 32 bytes further inside the swizzled row, next slab after 4
                         tc::mma_i8(d, tc::smem_desc_sw128(a_q + (j >> 2) * PF_SLAB + (j & 3) * 32),
-                                   tc::smem_desc_sw128(b_q + (j >> 2) * PF_SLAB + (j & 3) * 32), idesc_q, j > 0);
+                                   tc::smem_desc_sw128(b_q + (j >> 2) * C::B_SLAB + (j & 3) * 32), idesc_q, j > 0);
                     // K bytes 256..287: two 16-byte columns, K-adjacent core matrices one column apart
-                    tc::mma_i8(d, tc::smem_desc(a_q + PF_A_THIN, PF_COL, 128), tc::smem_desc(b_q + PF_B_THIN, PF_COL, 128), idesc_q, 1);
-                    if (Q4K) tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_q + PF_A_M, 128, 256), tc::smem_desc(b_q + PF_B_M, 128, 256), idesc_m, 0);
+                    tc::mma_i8(d, tc::smem_desc(a_q + PF_A_THIN, PF_COL, 128), tc::smem_desc(b_q + C::B_THIN, C::B_COL, 128), idesc_q, 1);
+                    if (Q4K) tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_q + PF_A_M, 128, 256), tc::smem_desc(b_q + C::B_M, 128, 256), idesc_m, 0);
                     tc::commit(&ctl->tmem_full[h]);   // this half's accumulators are complete
                     tc::commit(&ctl->b_empty[sb]);    // and its weight slot may be refilled
                     PF_MARK(4);
@@ -613,8 +630,8 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                     if (!PF_TIMED(0, wait_or_abort(&ctl->tmem_full[h], (uint32_t)(it & 1), ctl, p.status))) { ok = false; break; }
                     tc::fence_after_sync();
                     // written before the block's MMAs were issued: visible once their accumulators are
-                    const float xd = reinterpret_cast<const float *>(smem + PF_OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT)[row];
-                    const ulonglong2 *wd = reinterpret_cast<const ulonglong2 *>(smem + PF_OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT) + cset * (EC / 2);
+                    const float xd = reinterpret_cast<const float *>(smem + C::OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT)[row];
+                    const ulonglong2 *wd = reinterpret_cast<const ulonglong2 *>(smem + C::OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT) + cset * (EC / 2);
                     const uint64_t xd2 = pack2(xd, xd);
                     const uint32_t half_base = lane_base + h * PF_HALF_COLS;
                     PF_MARK0();
@@ -718,8 +735,8 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<F_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<F_TQ1_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<F_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<F_Q4_K>::SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<F_TQ1_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<F_TQ1_0>::SMEM);
         if (e != cudaSuccess) return e;
         configured = true;
     }
@@ -732,8 +749,8 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
                         (unsigned long long)p.nb * 292, 4, PF_BM, false);
     if (e != cudaSuccess) return e;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    if (a.fmt == F_Q4_K) prefill_kernel<F_Q4_K><<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_wide, x_narrow);
-    else prefill_kernel<F_TQ1_0><<<grid, PF_THREADS, PF_SMEM, stream>>>(p, x_wide, x_narrow);
+    if (a.fmt == F_Q4_K) prefill_kernel<F_Q4_K><<<grid, PF_THREADS, Cfg<F_Q4_K>::SMEM, stream>>>(p, x_wide, x_narrow);
+    else prefill_kernel<F_TQ1_0><<<grid, PF_THREADS, Cfg<F_TQ1_0>::SMEM, stream>>>(p, x_wide, x_narrow);
     return cudaGetLastError();
 }
 
