@@ -49,6 +49,23 @@ WORKLOADS = {
     "q4_k_dequantize_14336x4096": ("Q4_K", "dequantize", 14336, 4096, 0),
 }
 DEFAULT_WORKLOAD = "q4_k_decode_14336x4096"
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's dominant kernel, from the ncu
+# captures summarised under profiles/ (a profiler cannot run inside a timed benchmark, so the figures are
+# carried here; a sharded run scales them by the rank's share of the rows).  Writes that are still in L2
+# when the kernel ends are not in these numbers.
+NCU_DRAM_TRAFFIC = {
+    "q4_k_decode_14336x4096": 33_076_480,
+    "iq2_xxs_decode_28672x8192": 60_846_592,
+    "q4_k_prefill_4096x4096": 11_907_328,
+    "tq1_0_prefill_28672x8192": 67_826_432,
+    "q4_k_dequantize_14336x4096": 33_040_000 + 177_400_000,
+}
+
+
+def ncu_traffic(workload: str, share: float):
+    full = NCU_DRAM_TRAFFIC.get(workload)
+    return None if full is None else int(full * share)
 L2_BYTES = 126 * 1024 * 1024
 SEED = 20240611
 
@@ -355,7 +372,7 @@ def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
                        "sharding": f"rows split {world} ways, no collective" if world > 1 else "none",
                        "l2": f"{copies} input copies rotate; the {4 * rows * k / 2**20:.0f} MiB output exceeds L2", "launch": "direct launches", "seed": SEED},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "traffic": None, "peak_source": peaks_kind, "kernel": "dequant kernel (per GPU)", "kernel_ms": ms,
+                         "traffic": ncu_traffic(args.workload, rows / n), "peak_source": peaks_kind, "kernel": "dequant kernel (per GPU)", "kernel_ms": ms,
                          "algorithmic_bytes_per_launch": shard_bytes},
             "clocks": clocks, "gpu_launches": launches,
             "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(shard.nbytes), "d2h_bytes_per_step": int(4 * rows * k),
@@ -586,7 +603,7 @@ def main() -> None:
         shard_bytes = algorithmic_bytes(fmt, n_local, k, m)
         achieved = shard_bytes / (kernel_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "traffic": None, "peak_source": peaks_kind, "kernel": "gemv_kernel (per GPU)", "kernel_ms": kernel_ms,
+                "traffic": ncu_traffic(args.workload, n_local / n), "peak_source": peaks_kind, "kernel": "gemv_kernel (per GPU)", "kernel_ms": kernel_ms,
                 "algorithmic_bytes_per_launch": shard_bytes}
         dtype = "int8 dot (dp4a), f32 accumulate"
     else:
@@ -596,7 +613,7 @@ def main() -> None:
         e2e_value = ops / e2e_s / 1e12
         achieved = 2.0 * m * n_local * k / (kernel_ms * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops"]
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": None,
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": ncu_traffic(args.workload, n_local / n),
                 "peak_source": peaks_kind + " bf16 dense x2 (no int8 entry in MEASURED_PEAKS.json)", "kernel": "prefill kernel (per GPU)",
                 "kernel_ms": kernel_ms}
         dtype = "int8 tensor-core MMA, i32/f32 accumulate"

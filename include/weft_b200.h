@@ -9,9 +9,9 @@
  *   - the reference functions return void; these return int (0 = ok, non-zero = error, message from
  *     weft_b200_last_error()).  A caller that ignores the return value sees the reference behaviour.
  *   - every pointer may be a device pointer or a host pointer.  Device pointers are used in place.
- *     Host pointers are staged through stream-ordered device memory inside the call (inputs copied
- *     in, written arguments copied back) -- the literal drop-in for the reference's host-memory
- *     callers.  Host weights registered with weft_b200_weights_resident() are uploaded once and
+ *     Host pointers are staged through a device-side arena the library keeps and grows on demand
+ *     (inputs copied in, written arguments copied back inside the call) -- the literal drop-in for
+ *     the reference's host-memory callers.  Host weights registered with weft_b200_weights_resident() are uploaded once and
  *     found again by address, so only activations and outputs move per call.
  *
  * Records are the GGML block formats, never repacked: Q4_0 18 B/32, Q8_0 34 B/32, Q4_K 144 B/256,

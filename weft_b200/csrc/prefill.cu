@@ -117,16 +117,6 @@ __device__ __forceinline__ uint32_t core_offset(int row, int chunk, int chunks) 
     return (uint32_t)((row >> 3) * (chunks * 128) + chunk * 128 + (row & 7) * 16);
 }
 
-// f32(8 * hi + lo), rounded to nearest like an int-to-float conversion of the sum, on the full-rate fp32 pipe
-// (the conversion unit runs at a quarter of it): |hi|, |lo| <= 256 * 105 * 128 < 2^22, so adding the integer
-// to the bit pattern of 1.5 * 2^23 and subtracting that constant gives its exact float; 8 * f(hi) + f(lo) is
-// exact before the single rounding of the fused multiply-add.
-__device__ __forceinline__ float limbs_to_float(uint32_t hi, uint32_t lo) {
-    const float fh = __uint_as_float(hi + 0x4b400000u) - 12582912.f;
-    const float fl = __uint_as_float(lo + 0x4b400000u) - 12582912.f;
-    return fmaf(8.f, fh, fl);
-}
-
 // Packed pairs of fp32 (sm_100 executes add / mul / fma on two floats held in a 64-bit register pair with one
 // instruction; each lane of the pair is an ordinary IEEE round-to-nearest operation).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -150,7 +140,9 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
     return r;
 }
-// the integers of two accumulator columns as floats, exactly (|v| < 2^22, see limbs_to_float)
+// The integers of two accumulator columns as floats, exactly, on the full-rate fp32 pipe (the conversion
+// unit runs at a quarter of it): |v| <= 256 * 105 * 128 < 2^22, so adding the integer to the bit pattern of
+// 1.5 * 2^23 and subtracting that constant gives its exact float.
 __device__ __forceinline__ uint64_t ints_to_float2(uint32_t a, uint32_t b) {
     return add2(pack2(__uint_as_float(a + 0x4b400000u), __uint_as_float(b + 0x4b400000u)), pack2(-12582912.f, -12582912.f));
 }
@@ -206,16 +198,6 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, Co
     return ok != 0;
 }
 
-#ifdef WEFT_PF_PROFILE
-__device__ unsigned long long g_pf_prof[16][8];
-#define PF_TIMED(slot, call) ([&] { const long long t_ = clock64(); const bool r_ = (call); prof[slot] += clock64() - t_; return r_; }())
-#define PF_MARK(slot) do { const long long n_ = clock64(); prof[slot] += n_ - mark; mark = n_; } while (0)
-#define PF_MARK0() (mark = clock64())
-#else
-#define PF_TIMED(slot, call) (call)
-#define PF_MARK(slot) do { } while (0)
-#define PF_MARK0() do { } while (0)
-#endif
 
 // Coordinates of one 256-block of this CTA's work list (tiles taken round-robin),
 // advanced incrementally: no division on the critical path of the producer loops.
@@ -469,11 +451,6 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
     __syncthreads();
     tc::fence_after_sync();
     const uint32_t tmem = ctl->tmem_base;
-#ifdef WEFT_PF_PROFILE
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long prof_begin = clock64();
-    long long mark = prof_begin;
-#endif
 
     if (warp >= PF_W_WARP0 && warp < PF_W_WARP0 + 4) {
         // ------------------------------------------------------------------ weight producers
@@ -485,15 +462,14 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
             if (total > 0) load_record(p, next, row, wn);
             for (int it = 0; it < total && !ctl->abort; ++it) {
                 uint4 w[9];
-    #pragma unroll
+#pragma unroll
                 for (int i = 0; i < 9; ++i) w[i] = wn[i];
                 const int words = (next.b & 3) + 1;   // this block's operand shift
                 next.advance(p);
                 if (it + 1 < total) load_record(p, next, row, wn);   // in flight while this block is expanded
                 const int u = 2 * it + half;
                 const int sb = u % C::B_SLOTS;
-                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / C::B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
-                PF_MARK0();
+                if (!wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / C::B_SLOTS) & 1) ^ 1u, ctl, p.status)) break;
                 uint8_t *slot = b_ring + sb * C::B_SLOT, *wd = smem + C::OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
                 switch (words) {
                 case 1: expand_weights<1>(w, slot, wd, rh); break;
@@ -501,30 +477,27 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                 case 3: expand_weights<3>(w, slot, wd, rh); break;
                 default: expand_weights<4>(w, slot, wd, rh); break;
                 }
-                PF_MARK(4);
                 fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->b_full[sb]);
-                PF_MARK(5);
             }
         } else {
             BlockAt next = first_block(p);
             uint32_t pw[5];
-    #pragma unroll
+#pragma unroll
             for (int i = 0; i < 5; ++i) pw[i] = __ldg(p.powers + i) & 0xffu;
             uint32_t wn[14];
             if (total > 0) load_record_tq1(p, next, row, wn);
             for (int it = 0; it < total && !ctl->abort; ++it) {
                 uint32_t w[14];
-    #pragma unroll
+#pragma unroll
                 for (int i = 0; i < 14; ++i) w[i] = wn[i];
                 const int words = (next.b & 3) + 1;   // this block's operand shift
                 next.advance(p);
                 if (it + 1 < total) load_record_tq1(p, next, row, wn);   // in flight while this block is expanded
                 const int u = 2 * it + half;
                 const int sb = u % C::B_SLOTS;
-                if (!PF_TIMED(2, wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / C::B_SLOTS) & 1) ^ 1u, ctl, p.status))) break;
-                PF_MARK0();
+                if (!wait_or_abort(&ctl->b_empty[sb], (uint32_t)((u / C::B_SLOTS) & 1) ^ 1u, ctl, p.status)) break;
                 uint8_t *slot = b_ring + sb * C::B_SLOT, *wd = smem + C::OFF_WD + (u & (PF_WD_SLOTS - 1)) * PF_WD_SLOT;
                 switch (words) {
                 case 1: expand_tq1<1>(w, pw, slot, wd, rh); break;
@@ -532,11 +505,9 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                 case 3: expand_tq1<3>(w, pw, slot, wd, rh); break;
                 default: expand_tq1<4>(w, pw, slot, wd, rh); break;
                 }
-                PF_MARK(4);
                 fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->b_full[sb]);
-                PF_MARK(5);
             }
         }
     } else if (warp >= PF_S_WARP0 && warp < PF_S_WARP0 + PF_S_WARPS) {
@@ -547,14 +518,11 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
             const int sa = it % C::A_SLOTS, shift = 4 * (at.b & 3);
             const uint32_t a_phase = (uint32_t)(it / C::A_SLOTS) & 1u;
             at.advance(p);
-            if (!PF_TIMED(0, wait_or_abort(&ctl->a_landed[sa], a_phase, ctl, p.status))) break;
-            PF_MARK0();
+            if (!wait_or_abort(&ctl->a_landed[sa], a_phase, ctl, p.status)) break;
             build_specials<Q4K>(smem + C::OFF_A + sa * PF_A_SLOT, shift, smem + C::OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT, ts);
-            PF_MARK(4);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->a_full[sa]);
-            PF_MARK(5);
         }
     } else if (warp == PF_TMA_WARP) {
         // ------------------------------------------------------------------ activation copies
@@ -565,7 +533,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                 const int sa = it % C::A_SLOTS;
                 const uint32_t a_phase = (uint32_t)(it / C::A_SLOTS) & 1u;
                 // the slot was last read by the MMAs of block it - C::A_SLOTS (and, before them, by the warps above)
-                if (!PF_TIMED(0, wait_one(&ctl->a_empty[sa], a_phase ^ 1u, ctl, p.status))) break;
+                if (!wait_one(&ctl->a_empty[sa], a_phase ^ 1u, ctl, p.status)) break;
                 fence_proxy_async();
                 issue_activations(&x_wide, &x_narrow, at, smem + C::OFF_A + sa * PF_A_SLOT, &ctl->a_landed[sa]);
                 issued = it + 1;
@@ -582,16 +550,15 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
             for (int it = 0; it < total && ok && !ctl->abort; ++it) {
                 const int sa = it % C::A_SLOTS;
                 const uint32_t a_phase = (uint32_t)(it / C::A_SLOTS) & 1u;
-                if (!PF_TIMED(0, wait_one(&ctl->a_landed[sa], a_phase, ctl, p.status))) break;
-                if (!PF_TIMED(3, wait_one(&ctl->a_full[sa], a_phase, ctl, p.status))) break;
+                if (!wait_one(&ctl->a_landed[sa], a_phase, ctl, p.status)) break;
+                if (!wait_one(&ctl->a_full[sa], a_phase, ctl, p.status)) break;
                 const uint32_t a_q = smem_addr(smem + C::OFF_A + sa * PF_A_SLOT);
                 for (int h = 0; h < 2; ++h) {
                     const int u = 2 * it + h;
                     const int sb = u % C::B_SLOTS;
-                    if (!PF_TIMED(1, wait_one(&ctl->b_full[sb], (uint32_t)((u / C::B_SLOTS) & 1), ctl, p.status))) { ok = false; break; }
-                    if (!PF_TIMED(2, wait_one(&ctl->tmem_empty[h], (uint32_t)(it & 1) ^ 1u, ctl, p.status))) { ok = false; break; }
+                    if (!wait_one(&ctl->b_full[sb], (uint32_t)((u / C::B_SLOTS) & 1), ctl, p.status)) { ok = false; break; }
+                    if (!wait_one(&ctl->tmem_empty[h], (uint32_t)(it & 1) ^ 1u, ctl, p.status)) { ok = false; break; }
                     tc::fence_after_sync();
-                    PF_MARK0();
                     const uint32_t b_q = smem_addr(smem + C::OFF_B + sb * C::B_SLOT);
                     const uint32_t d = tmem + h * PF_HALF_COLS;
 #pragma unroll
@@ -603,7 +570,6 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                     if (Q4K) tc::mma_f16(d + 2 * PF_HALF, tc::smem_desc(a_q + PF_A_M, 128, 256), tc::smem_desc(b_q + C::B_M, 128, 256), idesc_m, 0);
                     tc::commit(&ctl->tmem_full[h]);   // this half's accumulators are complete
                     tc::commit(&ctl->b_empty[sb]);    // and its weight slot may be refilled
-                    PF_MARK(4);
                 }
                 if (ok) tc::commit(&ctl->a_empty[sa]);
             }
@@ -627,14 +593,13 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
             for (int b = 0; b < nb && ok; ++b, ++it) {
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    if (!PF_TIMED(0, wait_or_abort(&ctl->tmem_full[h], (uint32_t)(it & 1), ctl, p.status))) { ok = false; break; }
+                    if (!wait_or_abort(&ctl->tmem_full[h], (uint32_t)(it & 1), ctl, p.status)) { ok = false; break; }
                     tc::fence_after_sync();
                     // written before the block's MMAs were issued: visible once their accumulators are
                     const float xd = reinterpret_cast<const float *>(smem + C::OFF_XD + (it & (PF_XD_SLOTS - 1)) * PF_XD_SLOT)[row];
                     const ulonglong2 *wd = reinterpret_cast<const ulonglong2 *>(smem + C::OFF_WD + ((2 * it + h) & (PF_WD_SLOTS - 1)) * PF_WD_SLOT) + cset * (EC / 2);
                     const uint64_t xd2 = pack2(xd, xd);
                     const uint32_t half_base = lane_base + h * PF_HALF_COLS;
-                    PF_MARK0();
                     if constexpr (Q4K) {
 #pragma unroll
                         for (int c = 0; c < EC / 8; ++c) {
@@ -676,7 +641,6 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
                             }
                         }
                     }
-                    PF_MARK(4);
                 }
             }
             if (!ok) break;
@@ -703,12 +667,6 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const PfParams p, c
         }
     }
 
-#ifdef WEFT_PF_PROFILE
-    if (blockIdx.x == 0 && lane == 0) {
-        prof[7] = clock64() - prof_begin;
-        for (int i = 0; i < 8; ++i) g_pf_prof[warp][i] = (unsigned long long)prof[i];
-    }
-#endif
     tc::fence_before_sync();
     __syncthreads();
     if (warp == PF_MMA_WARP && tmem != 0xffffffffu) tc::tmem_free(tmem, PF_TMEM_COLS);
@@ -754,10 +712,5 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
     return cudaGetLastError();
 }
 
-#ifdef WEFT_PF_PROFILE
-extern "C" int weft_b200_debug_prefill_profile(unsigned long long *out) {
-    return (int)cudaMemcpyFromSymbol(out, g_pf_prof, sizeof(unsigned long long) * 128);
-}
-#endif
 
 }  // namespace weft
