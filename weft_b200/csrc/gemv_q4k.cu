@@ -10,8 +10,8 @@
 // left after the last full round are split evenly over the CTAs, so every CTA streams the same number
 // of bytes to within one row.
 //   * Warp 0 is the producer: one lane streams the CTA's stages into a shared-memory ring with bulk
-//     asynchronous copies (cp.async.bulk + mbarrier complete_tx).  The ring, not the number of loads a
-//     thread can have outstanding, sets the bytes in flight per SM.
+//     asynchronous copies (cp.async.bulk + mbarrier complete_tx), keeping three copies (54 KB per SM, 8 MB
+//     over the GPU) outstanding; the ring of eight slots decouples landing from consumption.
 //   * The other warps are consumers.  Consumer w computes the CTA's rows w, w + W, w + 2W, ...: it waits on
 //     the stage's "full" barrier, computes the row from shared memory and arrives on the stage's "empty"
 //     barrier, which lets the producer refill the slot.
@@ -59,6 +59,7 @@ struct Q4kParams {
     int log_stages;      // ring depth = 1 << log_stages
     int full_rounds;     // rounds in which every CTA owns one full stage
     int tail_rows;       // rows per CTA in the final, partial round
+    int inflight;        // copies the producer keeps outstanding (issued, not yet landed)
     int *status;
 };
 
@@ -189,7 +190,7 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
         bulk_g2s_a(ring_addr + (uint32_t)slot * stage_bytes, p.w + (size_t)row0 * row_bytes, bytes, full_addr + 8 * slot);
     };
     if (warp == 0 && lane == 0) {
-        const int first = min(S, total_stages);
+        const int first = min(min(S, p.inflight), total_stages);
         for (int s = 0; s < first; ++s) issue(s);   // weights do not depend on the activations
         *s_issued = first;
     }
@@ -202,11 +203,21 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
     else q4k_stage_records(p.xq + xq_row, nb, s_xq, s_aux);
     __syncthreads();
 
-    if (warp == 0) {   // producer: refill each slot as soon as its rows have all been consumed
+    if (warp == 0) {
+        // Producer.  Stage s goes out when its slot is free (all rows of the slot's previous stage consumed)
+        // AND stage s - P has landed, i.e. at most P copies are outstanding.  Issuing the whole ring at once
+        // makes every copy of every SM land together, late (measured: first data 3.4 us after the issue, the
+        // consumers idle until then, the rest of the matrix requested only afterwards); with P = 3 the stages
+        // land in order, the first after 2.2 us, and HBM stays busy until the end (7.6 -> 7.1 us).
         if (lane == 0) {
-            for (int s = S; s < total_stages; ++s) {
-                if (!mbar_wait_a(empty_addr + 8 * (s & (S - 1)), (uint32_t)((s >> LS) - 1) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
-                fence_proxy_async();
+            const int P = min(S, p.inflight);
+            for (int s = min(P, total_stages); s < total_stages; ++s) {
+                if (s >= S) {
+                    if (!mbar_wait_a(empty_addr + 8 * (s & (S - 1)), (uint32_t)((s >> LS) - 1) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
+                    fence_proxy_async();
+                }
+                // this thread issued stage s - P itself and has not refilled its slot since: the parity is unambiguous
+                if (!mbar_wait_a(full_addr + 8 * ((s - P) & (S - 1)), (uint32_t)((s - P) >> LS) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
                 issue(s);
                 *s_issued = s + 1;
             }
@@ -302,6 +313,7 @@ const int kQ4kStageBytes = env_or("WEFT_B200_Q4K_STAGE", 18432);
 const int kQ4kMaxStages = env_or("WEFT_B200_Q4K_STAGES", 8);
 const int kQ4kOverlap = env_or("WEFT_B200_Q4K_OVERLAP", 1);
 const int kQ4kSmemCap = env_or("WEFT_B200_Q4K_SMEM_KB", 200);   // per-CTA shared-memory budget tried first
+const int kQ4kInflight = env_or("WEFT_B200_Q4K_INFLIGHT", 3);   // measured: 2 -> 7.8 us, 3 -> 7.05, 4 -> 7.14, 6 -> 7.6, 8 -> 8.1
 
 template <bool QX, bool XREG>
 cudaError_t launch_variant(const Q4kParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
@@ -355,7 +367,7 @@ bool gemv_q4k_supported(const GemvArgs &a) {
 cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream) {
     Q4kParams p;
     p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.x = a.x; p.y = a.y;
-    p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
+    p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status; p.inflight = kQ4kInflight < 1 ? 1 : kQ4kInflight;
     const Q4kPlan plan = plan_q4k(p.nb);
     if (!plan.ok) return cudaErrorInvalidConfiguration;
     p.log_stage_rows = plan.log_stage_rows; p.log_stages = plan.log_stages;

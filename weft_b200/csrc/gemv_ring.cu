@@ -39,6 +39,7 @@ struct RingParams {
     int log_stages;      // ring depth
     int full_rounds;
     int tail_rows;
+    int inflight;        // copies the producer keeps outstanding (issued, not yet landed)
     int *status;
 };
 
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
         bulk_g2s_a(ring_addr + (uint32_t)slot * stage_bytes, p.w + (size_t)row0 * row_bytes, bytes, full_addr + 8 * slot);
     };
     if (warp == 0 && lane == 0) {
-        const int first = min(S, total_stages);
+        const int first = min(min(S, p.inflight), total_stages);
         for (int s = 0; s < first; ++s) issue(s);
         *s_issued = first;
     }
@@ -115,9 +116,15 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int s = S; s < total_stages; ++s) {
-                if (!mbar_wait_a(empty_addr + 8 * (s & (S - 1)), (uint32_t)((s >> LS) - 1) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
-                fence_proxy_async();
+            // stage s goes out when its slot is free and stage s - P has landed (at most P copies outstanding:
+            // issuing the whole ring at once makes every copy land together, late)
+            const int P = min(S, p.inflight);
+            for (int s = min(P, total_stages); s < total_stages; ++s) {
+                if (s >= S) {
+                    if (!mbar_wait_a(empty_addr + 8 * (s & (S - 1)), (uint32_t)((s >> LS) - 1) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
+                    fence_proxy_async();
+                }
+                if (!mbar_wait_a(full_addr + 8 * ((s - P) & (S - 1)), (uint32_t)((s - P) >> LS) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
                 issue(s);
                 *s_issued = s + 1;
             }
@@ -175,6 +182,7 @@ const int kRingConsumers = env_or("WEFT_B200_RING_WARPS", 15);
 const int kRingStageBytes = env_or("WEFT_B200_RING_STAGE", 18432);
 const int kRingMaxStages = env_or("WEFT_B200_RING_STAGES", 8);
 const int kRingOverlap = env_or("WEFT_B200_RING_OVERLAP", 1);
+const int kRingInflight = env_or("WEFT_B200_RING_INFLIGHT", 3);
 
 struct RingPlan { int log_lanes, log_stage_rows, log_stages; size_t smem; bool ok; };
 
@@ -235,7 +243,7 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     RingParams p;
     p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.x = a.x;
     p.grid = a.grid; p.signs = a.signs; p.powers = a.powers; p.y = a.y;
-    p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
+    p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status; p.inflight = kRingInflight < 1 ? 1 : kRingInflight;
     const RingPlan plan = plan_ring(a.fmt, p.nb);
     if (!plan.ok) return cudaErrorInvalidConfiguration;
     p.log_lanes = plan.log_lanes; p.log_stage_rows = plan.log_stage_rows; p.log_stages = plan.log_stages;
