@@ -51,8 +51,9 @@ def test_prefill_q4_k_one_tile(torch, oracle):
     _run(torch, oracle, 128, 128, 256, seed=1)
 
 
-@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 512), (512, 384, 1024), (32, 128, 4096), (200, 1000, 2048)])
+@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 512), (512, 384, 1024), (32, 128, 4096), (200, 1000, 2048), (512, 4736, 1024)])
 def test_prefill_q4_k_shapes(torch, oracle, mnk):
+    """Tiles are 128 x 112 or 128 x 128, whichever leaves the last round of the grid fuller: (512, 4736) takes 128."""
     m, n, k = mnk
     _run(torch, oracle, m, n, k, seed=sum(mnk))
 
@@ -108,7 +109,7 @@ def _run_tq1_0(torch, oracle, m, n, k, seed, column_ranges=None):
         assert reference_tolerance_ok(got[:, lo:hi], want[:, lo:hi])
 
 
-@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 2048), (512, 384, 1024), (32, 130, 4096), (200, 1001, 3072)])
+@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 2048), (512, 384, 1024), (32, 130, 4096), (200, 1001, 3072), (512, 4736, 1024)])
 def test_prefill_tq1_0_shapes(torch, oracle, mnk):
     """K a multiple of 1024 takes the tensor-core kernel; odd N exercises 2-byte-aligned weight rows."""
     m, n, k = mnk
