@@ -42,6 +42,7 @@ WORKLOADS = {
     "q4_k_decode_4096x14336": ("Q4_K", "decode", 4096, 14336, 1),
     "q4_0_decode_4096x4096": ("Q4_0", "decode", 4096, 4096, 1),
     "iq2_xxs_decode_28672x8192": ("IQ2_XXS", "decode", 28672, 8192, 1),
+    "q4k_i16_decode_14336x4096": ("Q4K_I16", "decode", 14336, 4096, 1),   # persistent 16-row interleaved layout
     "q4_k_prefill_14336x4096": ("Q4_K", "prefill", 14336, 4096, 512),
     "q4_k_prefill_4096x4096": ("Q4_K", "prefill", 4096, 4096, 512),
     "q4_k_prefill_4096x14336": ("Q4_K", "prefill", 4096, 14336, 512),
@@ -404,6 +405,9 @@ def main() -> None:
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     fmt, mode, n, k, m = WORKLOADS[args.workload]
+    layout = fmt                      # what the kernel is given
+    if fmt == "Q4K_I16":              # Q4_K records, packed once by the kernel's _W_pack artifact function
+        fmt = "Q4_K"
     if args.impl == "reference":
         reference_arm(args, fmt, mode, n, k, m)
         return
@@ -451,6 +455,14 @@ def main() -> None:
     copies = max(2, -(-2 * L2_BYTES // max(1, shard.nbytes)) + 1)
     copies = min(copies, 64)
     w_dev = [torch.from_numpy(shard).cuda() if c == 0 else None for c in range(copies)]
+    if layout == "Q4K_I16":
+        if n_local % 16:
+            raise SystemExit(f"{n_local} rows per rank are not whole cohorts of 16")
+        packed = torch.empty_like(w_dev[0])
+        lib.q4_k_q8_k_gemv_W_pack.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t]
+        check(lib.q4_k_q8_k_gemv_W_pack(w_dev[0].data_ptr(), packed.data_ptr(), n_local, k))
+        torch.cuda.synchronize()
+        w_dev[0] = packed
     for c in range(1, copies):
         w_dev[c] = w_dev[0].clone()
     x_dev = torch.from_numpy(x_host).cuda()
@@ -459,7 +471,7 @@ def main() -> None:
     grid_dev = torch.from_numpy(grid).cuda()
     signs_dev = torch.from_numpy(signs).cuda()
     powers_dev = torch.tensor(TQ1_POWERS, dtype=torch.int32, device="cuda")
-    fid = FORMAT_IDS[fmt]
+    fid = 1008 if layout == "Q4K_I16" else FORMAT_IDS[fmt]
     mode_id = 0 if mode == "decode" else 1
     shard_fn = lib.weft_b200_mul_mat_shard
     shard_fn.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_size_t] * 4 + [ctypes.c_uint]
@@ -622,7 +634,7 @@ def main() -> None:
         "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype,
         "data": "synthetic",
-        "config": {"workload": args.workload, "format": fmt, "mode": mode, "N": n, "K": k, "M": m,
+        "config": {"workload": args.workload, "format": layout, "mode": mode, "N": n, "K": k, "M": m,
                    "sharding": f"weight rows split {world} ways, fp32 outputs all-gathered (NCCL)" if world > 1 else "none",
                    "l2": f"steps rotate over {copies} weight copies ({copies * shard.nbytes / 2**20:.0f} MiB per GPU > 2 x L2)",
                    "launch": launch_mode, "timed_scope": "activation quantize + mul_mat" + (" + all-gather" if world > 1 else ""), "seed": SEED,

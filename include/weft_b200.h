@@ -121,6 +121,21 @@ int quantized_vec_dot_tq1_0_q8_k_rows(const uint8_t *W, const uint8_t *X, const 
 int q8_0_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 
+/* Persistent interleaved weight layout Q4K_I[16] (examples/formats/ggml.py:286-290): the Q4_K records of each
+ * cohort of 16 rows stored byte-major, byte b of row r of a 256-block at 16 b + r, blocks in (cohort, block)
+ * order (doc/dsl/encoding-and-artifacts.md:209).  Artifact functions as the reference emits them next to every
+ * kernel with a derived-Encoding parameter (lib/Target/Emission/Emitter.h:231-272); rows must be a multiple
+ * of 16 and K of 256 (packed_size returns 0 otherwise, pack fails); the packed object must be 16-byte aligned.
+ * examples/kernels/gemv/q4_k.py:8-26                   q4_k_gemv_runtime.cpp:28-32,243-247 */
+size_t q4_k_q8_k_gemv_W_packed_size(size_t M, size_t K);
+int q4_k_q8_k_gemv_W_pack(const uint8_t *source, uint8_t *target, size_t M, size_t K);
+int q4_k_q8_k_gemv(const uint8_t *W, const uint8_t *X, float *Y, size_t M, size_t K);
+/* examples/kernels/mul_mat/q4_k_persistent.py:9-30     mul_mat_runtime.cpp:337-348,805-810
+ * Extents in the order (M, K, N): the derived Encoding's builder declares M and K first. */
+size_t production_mul_mat_q4_k_persistent_W_packed_size(size_t N, size_t K);
+int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *target, size_t N, size_t K);
+int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N);
+
 /* Row-sharded mul_mat: this process holds weight rows [n0, n0+N_local) of an (N,K) matrix and writes
  * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 8 Q4_K, 15 IQ2_XXS,
  * 20 TQ1_0 (the reference harness numbering).  mode: 0 decode (GEMV), 1 prefill (tensor cores).

@@ -71,6 +71,8 @@ def port() -> ctypes.CDLL:
         lib.wo_f16_to_f32.restype = ctypes.c_float
         lib.wo_f32_to_f16.argtypes = [ctypes.c_float]
         lib.wo_f32_to_f16.restype = ctypes.c_uint16
+        lib.wo_interleave_pack.argtypes = [_u8p, _u8p, ctypes.c_size_t, _i64, _i64, _i64]
+        lib.wo_interleave_unpack.argtypes = [_u8p, _u8p, ctypes.c_size_t, _i64, _i64, _i64]
         lib.wo_max_threads.restype = ctypes.c_int
         lib.wo_set_threads.argtypes = [ctypes.c_int]
         _port = lib
@@ -210,6 +212,19 @@ def ref_iq2xxs_tables():
     signs = np.empty(1024, dtype=np.int8)
     ref().weft_ref_iq2xxs_tables(_ptr(grid, _i8p), _ptr(signs, _i8p))
     return grid, signs
+
+
+def interleave(fmt: int, w: np.ndarray, k: int, rows_per_cohort: int = 16, *, inverse: bool = False) -> np.ndarray:
+    """The persistent interleaved layout ``Family[rows_per_cohort]`` of the (rows, row_bytes) records ``w``
+    (doc/dsl/encoding-and-artifacts.md:209), or back to plain records with ``inverse``.  Same shape and size."""
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    rows = w.shape[0]
+    blocks = k // RECORD_ELEMENTS[fmt]
+    out = np.empty_like(w)
+    move = port().wo_interleave_unpack if inverse else port().wo_interleave_pack
+    if move(_ptr(w, _u8p), _ptr(out, _u8p), RECORD_BYTES[fmt], rows_per_cohort, rows, blocks) != 0:
+        raise ValueError(f"{rows} rows are not whole cohorts of {rows_per_cohort}")
+    return out
 
 
 def host_threads() -> int:

@@ -686,3 +686,32 @@ void wo_iq2_sign_table(int8_t *signs) {
         for (int j = 0; j < 8; ++j) signs[8 * i + j] = (full >> j) & 1 ? -1 : 1;
     }
 }
+
+/* ---- persistent interleaved layout (doc/dsl/encoding-and-artifacts.md:209) ---------------------------------- */
+
+size_t wo_interleave_packed_size(size_t record_bytes, int64_t rows, int64_t blocks) {
+    return (size_t)rows * (size_t)blocks * record_bytes;
+}
+
+static int wo_interleave_move(const uint8_t *source, uint8_t *target, size_t record_bytes, int64_t R, int64_t rows,
+                              int64_t blocks, int pack) {
+    if (R <= 0 || rows < 0 || blocks < 0 || rows % R != 0) return -1;
+    for (int64_t r = 0; r < rows; ++r)
+        for (int64_t k = 0; k < blocks; ++k) {
+            const size_t plain = ((size_t)r * (size_t)blocks + (size_t)k) * record_bytes;
+            const size_t cohort = (((size_t)(r / R) * (size_t)blocks + (size_t)k) * (size_t)R) * record_bytes + (size_t)(r % R);
+            for (size_t b = 0; b < record_bytes; ++b) {
+                if (pack) target[cohort + b * (size_t)R] = source[plain + b];
+                else target[plain + b] = source[cohort + b * (size_t)R];
+            }
+        }
+    return 0;
+}
+
+int wo_interleave_pack(const uint8_t *source, uint8_t *target, size_t record_bytes, int64_t R, int64_t rows, int64_t blocks) {
+    return wo_interleave_move(source, target, record_bytes, R, rows, blocks, 1);
+}
+
+int wo_interleave_unpack(const uint8_t *source, uint8_t *target, size_t record_bytes, int64_t R, int64_t rows, int64_t blocks) {
+    return wo_interleave_move(source, target, record_bytes, R, rows, blocks, 0);
+}

@@ -82,6 +82,16 @@ int wo_mul_mat(int fmt, int rule, const uint8_t *w, const float *x, uint8_t *xq,
 /* sign table in kernel-argument form, derived (7 index bits + even-parity bit) */
 void wo_iq2_sign_table(int8_t *signs /* [128*8] */);
 
+/* Persistent interleaved layout Family[R] of a record format (R rows of one cohort, byte-major): byte b of
+ * the record of row r, block k sits at ((r / R) * blocks + k) * R * record_bytes + b * R + (r % R)
+ * (doc/dsl/encoding-and-artifacts.md:209; record stride record_bytes * R and cohort stride
+ * blocks * record_bytes per row in lib/Target/Emission/Memory.cpp:1344-1348; ABI of the artifact functions
+ * <kernel>_W_packed_size / <kernel>_W_pack in lib/Target/Emission/Emitter.h:231-272).  rows % R must be 0:
+ * returns -1 otherwise (the builder declares no tail cohort). */
+size_t wo_interleave_packed_size(size_t record_bytes, int64_t rows, int64_t blocks);
+int wo_interleave_pack(const uint8_t *source, uint8_t *target, size_t record_bytes, int64_t R, int64_t rows, int64_t blocks);
+int wo_interleave_unpack(const uint8_t *source, uint8_t *target, size_t record_bytes, int64_t R, int64_t rows, int64_t blocks);
+
 int wo_max_threads(void);
 void wo_set_threads(int n);
 

@@ -72,7 +72,7 @@ def test_kernel_abi_follows_the_reference_rules():
     deq = registry.resolve(dequantize.row_dequantize_tq1_0)
     assert [a["encoding"] for a in deq["arguments"]] == ["TQ1_0", "dense.u32", "dense.f32"]
     assert deq["arguments"][1]["shape"] == ["5"] and deq["shape_parameters"] == ["K"]
-    assert len(registry.supported_symbols()) == 34
+    assert len(registry.supported_symbols()) == 36
 
 
 _EXTRA_KERNELS = """
@@ -133,9 +133,27 @@ def test_reference_kernel_files_resolve_unchanged():
         "assert [x['alias_set'] for x in registry.resolve(c.row_dequantize_iq2_xxs)['arguments']] == [0, 0, 0, 1]\n"
         "assert registry.resolve(d.quantized_vec_dot_tq1_0_q8_k)['shape_parameters'] == ['K']\n"
         "assert registry.resolve(e.q8_K_quantize)['arguments'][1]['encoding'] == 'Q8_K'\n"
+        "import kernels.gemv.q4_k as f, kernels.mul_mat.q4_k_persistent as g\n"
+        "r = registry.resolve(f.q4_k_q8_k_gemv); assert r['arguments'][0]['encoding'] == 'Q4K_I[16]' and r['c_dimension_order'] == ['M', 'K'], r\n"
+        "r = registry.resolve(g.production_mul_mat_q4_k_persistent); assert (r['arguments'][0]['storage_bytes'], r['arguments'][0]['record_elements']) == (144, 256)\n"
+        "assert r['shape_parameters'] == ['N', 'K', 'M'] and r['c_dimension_order'] == ['M', 'K', 'N'], r\n"
         "print('ok')\n" % (str(ROOT), str(examples)))
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env={**os.environ, "PYTHONDONTWRITEBYTECODE": "1"})
     assert out.returncode == 0 and "ok" in out.stdout, out.stderr
+
+
+def test_derived_encoding_keeps_its_base_record_geometry():
+    """Q4K_I[16] is Q4_K records, 16 rows interleaved: same storage per record, same alignment (Emitter.h:321-333);
+    the persistent kernel's C symbol takes its extents as (M, K, N) (mul_mat_runtime.cpp:337-348)."""
+    from weft_b200 import registry
+    from weft_b200.kernels import gemv, mul_mat
+
+    abi = registry.resolve(gemv.q4_k_q8_k_gemv)
+    w = abi["arguments"][0]
+    assert (w["encoding"], w["storage_bytes"], w["record_elements"], w["alignment"]) == ("Q4K_I[16]", 144, 256, 2)
+    assert abi["shape_parameters"] == ["M", "K"] and [a["access"] for a in abi["arguments"]] == ["read", "read", "write"]
+    abi = registry.resolve(mul_mat.production_mul_mat_q4_k_persistent)
+    assert abi["shape_parameters"] == ["N", "K", "M"] and abi["c_dimension_order"] == ["M", "K", "N"]
 
 
 # ------------------------------------------------------------------ Buffer and the call checks
@@ -247,7 +265,7 @@ def test_compile_options_keep_the_reference_record():
 
 def _declared_symbols():
     header = (ROOT / "include" / "weft_b200.h").read_text()
-    return sorted(set(re.findall(r"^(?:int|const char \*|unsigned long long)\s*\*?\s*(\w+)\(", header, flags=re.M)))
+    return sorted(set(re.findall(r"^(?:int|size_t|const char \*|unsigned long long)\s*\*?\s*(\w+)\(", header, flags=re.M)))
 
 
 def test_library_exports_every_declared_symbol():
@@ -256,7 +274,8 @@ def test_library_exports_every_declared_symbol():
     library = build.ensure_built()
     lib = ctypes.CDLL(str(library))
     names = _declared_symbols()
-    assert len(names) >= 44 and "production_mul_mat_q4_k_decode" in names and "weft_b200_mul_mat_shard" in names
+    assert len(names) >= 50 and "production_mul_mat_q4_k_decode" in names and "weft_b200_mul_mat_shard" in names
+    assert "q4_k_q8_k_gemv_W_packed_size" in names and "production_mul_mat_q4_k_persistent_W_pack" in names
     for name in names:
         assert hasattr(lib, name), name
 

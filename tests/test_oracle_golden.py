@@ -131,3 +131,19 @@ def test_live_against_compiled_reference(oracle, golden, name):
     y, xq = oracle.mul_mat(fmt, w, x, n, k, m, grid=grid, signs=signs)
     yr, xqr = oracle.ref_mul_mat(fmt, w, x, n, k, m)
     assert np.array_equal(xq, xqr) and np.array_equal(_bits(y), _bits(yr))
+
+
+def test_interleave_follows_the_documented_rule(oracle):
+    """doc/dsl/encoding-and-artifacts.md:209: for every cohort of R rows and every record, byte b of the R rows
+    in row order, then byte b + 1.  Checked against an independent numpy statement of the rule, and that the
+    mul_mat over the unpacked object equals the mul_mat over the source."""
+    rng = np.random.default_rng(7)
+    rows, k, R = 48, 768, 16
+    blocks = k // 256
+    w = rng.integers(0, 256, size=(rows, blocks * 144), dtype=np.uint8)
+    packed = oracle.interleave(oracle.Q4_K, w, k, R)
+    want = w.reshape(rows // R, R, blocks, 144).transpose(0, 2, 3, 1)          # [cohort][block][byte][row]
+    assert np.array_equal(packed.reshape(-1), np.ascontiguousarray(want).reshape(-1))
+    assert np.array_equal(oracle.interleave(oracle.Q4_K, packed, k, R, inverse=True), w)
+    with pytest.raises(ValueError):
+        oracle.interleave(oracle.Q4_K, w[:40], k, R)                            # no tail cohort

@@ -226,6 +226,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     if (check_k(fmt, K) || check_k(act, K)) return 1;
     if (K == 0 || N == 0 || M == 0) return 0;
     if (ldy < N) return fail("Y row pitch %zu is smaller than N = %zu", ldy, N);
+    if (fmt == F_Q4_K_I16 && N % 16 != 0) return fail("Q4K_I[16] holds whole cohorts of 16 rows; N = %zu", N);
     const bool have_xq = vec_dot_only || (flags & 1u);
     Call call;
     void *w, *x = nullptr, *xq, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
@@ -237,7 +238,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     // a host Y with a pitch is staged whole (pitch * M floats); device Y is written in place
     const size_t y_floats = (M - 1) * ldy + N;
     if (call.map(Y, y_floats * sizeof(float), ldy != N, true, &y)) return 1;
-    if ((reinterpret_cast<uintptr_t>(w) & 1u) || (reinterpret_cast<uintptr_t>(xq) & (act == F_Q8_K ? 3u : 1u)) ||
+    if ((reinterpret_cast<uintptr_t>(w) & (fmt == F_Q4_K_I16 ? 15u : 1u)) || (reinterpret_cast<uintptr_t>(xq) & (act == F_Q8_K ? 3u : 1u)) ||
         (reinterpret_cast<uintptr_t>(y) & 3u) || (x && (reinterpret_cast<uintptr_t>(x) & 3u)))
         return fail("a buffer does not meet its Encoding alignment");
     const int sms = g.prop.multiProcessorCount;
@@ -375,10 +376,37 @@ MUL_MAT(production_mul_mat_q4_k_staged, F_Q4_K, 1, NO_TABLES, nullptr, nullptr, 
 MUL_MAT(production_mul_mat_tq1_0, F_TQ1_0, 1, TQ_TABLES, nullptr, nullptr, powers)
 MUL_MAT(production_mul_mat_iq2_xxs_staged, F_IQ2_XXS, 1, IQ_TABLES, grid, signs, nullptr)
 
+// ---- persistent interleaved layout Q4K_I[16]: artifact functions and the kernels that consume it
+static size_t q4ki_packed_size(size_t rows, size_t K) { return K % 256 == 0 && rows % 16 == 0 ? rows * (K / 256) * 144 : 0; }
+static int q4ki_pack(const uint8_t *source, uint8_t *target, size_t rows, size_t K) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (K % 256 != 0) return fail("K = %zu does not hold whole Q4_K records", K);
+    if (rows % 16 != 0) return fail("Q4K_I[16] holds whole cohorts of 16 rows; rows = %zu", rows);
+    if (rows == 0 || K == 0) return 0;
+    Call call;
+    void *src, *dst;
+    const size_t bytes = q4ki_packed_size(rows, K);
+    if (call.map(source, bytes, true, false, &src) || call.map(target, bytes, false, true, &dst)) return 1;
+    if ((reinterpret_cast<uintptr_t>(src) & 1u) || (reinterpret_cast<uintptr_t>(dst) & 15u)) return fail("a buffer does not meet its Encoding alignment");
+    if (launched(launch_interleave_q4k(src, dst, (long long)rows, (long long)K, g.prop.multiProcessorCount, g.stream), "Q4K_I[16] pack")) return 1;
+    return call.finish();
+}
+size_t q4_k_q8_k_gemv_W_packed_size(size_t M, size_t K) { return q4ki_packed_size(M, K); }
+int q4_k_q8_k_gemv_W_pack(const uint8_t *source, uint8_t *target, size_t M, size_t K) { return q4ki_pack(source, target, M, K); }
+int q4_k_q8_k_gemv(const uint8_t *W, const uint8_t *X, float *Y, size_t M, size_t K) {
+    return do_mul_mat(F_Q4_K_I16, 0, W, nullptr, const_cast<uint8_t *>(X), nullptr, nullptr, nullptr, Y, M, K, 1, M, 0, true);
+}
+size_t production_mul_mat_q4_k_persistent_W_packed_size(size_t N, size_t K) { return q4ki_packed_size(N, K); }
+int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *target, size_t N, size_t K) { return q4ki_pack(source, target, N, K); }
+int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N) {
+    return do_mul_mat(F_Q4_K_I16, 0, W, X, Xq, nullptr, nullptr, nullptr, Y, N, K, M, N, 0, false);
+}
+
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags) {
-    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q4_K && format != F_IQ2_XXS && format != F_TQ1_0)
+    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q4_K && format != F_IQ2_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
         return fail("unknown weight format id %d", format);
     if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
     return do_mul_mat(format, mode, W_local, X, Xq, grid, signs, powers, Y_columns, N_local, K, M, ldy, flags, false);

@@ -294,6 +294,7 @@ cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
         return cudaGetLastError();
     }
     if (a.k % 256 != 0 || a.k == 0) return cudaErrorInvalidValue;
+    if (a.fmt == F_Q4_K_I16) return launch_gemv_q4ki(a, sm_count, stream);
     static const bool generic_only = getenv("WEFT_B200_GENERIC_GEMV") != nullptr;
     if (!generic_only && gemv_q4k_supported(a)) return launch_gemv_q4k(a, sm_count, stream);
     if (!generic_only && gemv_ring_supported(a)) return launch_gemv_ring(a, sm_count, stream);

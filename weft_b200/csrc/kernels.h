@@ -34,6 +34,12 @@ cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream
 bool gemv_ring_supported(const GemvArgs &a);
 cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t stream);
 
+// Q4K_I[16]: the same GEMV over 16-row byte-interleaved Q4_K records (n a multiple of 16), and the
+// artifact function that produces that layout from plain records
+bool gemv_q4ki_supported(const GemvArgs &a);
+cudaError_t launch_gemv_q4ki(const GemvArgs &a, int sm_count, cudaStream_t stream);
+cudaError_t launch_interleave_q4k(const void *source, void *target, long long rows, long long k, int sm_count, cudaStream_t stream);
+
 struct PrefillArgs {
     int fmt;
     const void *w;           // (n, k) records

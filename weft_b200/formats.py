@@ -9,7 +9,7 @@ its name and checks the record geometry, not the declaring module.
 from __future__ import annotations
 
 from . import language as wl
-from .api import encoding
+from .api import derive, encoding
 
 _LE = (wl.bitorder.lsb_first, wl.byteorder.little)
 
@@ -79,6 +79,15 @@ class Q8_K:                      # 292 bytes / 256 elements
     ds: wl.f32                   # @0
     q: wl.i8[256]                # @4
     bsum: wl.i16[16]             # @260
+
+
+@derive
+def Q4K_I(W: wl.View[Q4_K, (M, K)], *, rows: wl.static[int]) -> wl.View[Q4K_I[rows], (M, K)]:
+    """Persistent interleaved layout (examples/formats/ggml.py:286-290): every cohort of ``rows`` rows keeps
+    its Q4_K records but stores them byte-major -- byte b of row r of a block at ``rows * b + r``
+    (doc/dsl/encoding-and-artifacts.md:209).  ``Q4K_I[16]`` is the member this build executes; the packed
+    object is produced by the kernels' ``_W_pack`` artifact functions (``weft_b200.artifacts``)."""
+    return wl.interleave(W, rows=rows)
 
 
 #: name -> (storage bytes per record, logical elements per record, alignment)

@@ -75,3 +75,11 @@ def production_mul_mat_iq2_xxs_staged(W: wl.View[ggml.IQ2_XXS, (N, K)], X: wl.Vi
                                       Xq: wl.View[ggml.Q8_K, (M, K)], grid: wl.View[ggml.I8X8, (256, 8)],
                                       signs: wl.View[ggml.I8X8, (128, 8)], Y: wl.View[wl.f32, (M, N)]):
     """Prefill form, IQ2_XXS x Q8_K."""
+
+
+@kernel
+def production_mul_mat_q4_k_persistent(W: wl.View[ggml.Q4K_I[16], (N, K)], X: wl.View[wl.f32, (M, K)],
+                                       Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Q4_K x Q8_K over the persistent interleaved layout (examples/kernels/mul_mat/q4_k_persistent.py:9-30).
+    The C symbol takes its extents as (M, K, N): the derived Encoding's builder declares M and K first
+    (examples/repro/weft/mul_mat_runtime.cpp:337-348)."""

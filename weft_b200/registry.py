@@ -12,7 +12,11 @@ from . import kernels
 from .api import KernelDefinition
 from .signature import kernel_abi
 
-_MODULES = (kernels.vec_dot, kernels.dequantize, kernels.quantize, kernels.mul_mat, kernels.rows)
+_MODULES = (kernels.vec_dot, kernels.dequantize, kernels.quantize, kernels.mul_mat, kernels.gemv, kernels.rows)
+
+#: C symbols whose trailing size_t extents are not in first-appearance order of the signature: the builder of a
+#: derived Encoding declares its own extents first (examples/repro/weft/mul_mat_runtime.cpp:337-348)
+_C_ORDER = {"production_mul_mat_q4_k_persistent": ["M", "K", "N"]}
 
 
 def _access(symbol: str, name: str) -> str:
@@ -78,4 +82,4 @@ def resolve(definition: KernelDefinition) -> dict:
         merged["access"] = mine["access"]
         arguments.append(merged)
     return {"symbol": symbol, "arguments": arguments, "shape_parameters": given["shape_parameters"],
-            "c_dimension_order": [rename[name] for name in known["shape_parameters"]]}
+            "c_dimension_order": [rename[name] for name in _C_ORDER.get(symbol, known["shape_parameters"])]}

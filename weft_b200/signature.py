@@ -79,12 +79,30 @@ def _identity(enc: object) -> tuple[str, int, int, int, str]:
         return enc.__name__, storage, elements, alignment, "uint8_t"
     if isinstance(enc, DerivedEncodingInstance) or (hasattr(enc, "family") and hasattr(enc, "parameters")):
         spelling = f"{enc.family.__name__}[{', '.join(map(str, enc.parameters))}]"
-        return spelling, 0, 0, 0, "uint8_t"
+        # a derived Encoding keeps the record geometry of its base family (Emitter.h:321-333)
+        storage, elements, alignment = _derived_base_facts(enc.family)
+        return spelling, storage, elements, alignment, "uint8_t"
     name, width = getattr(enc, "name", None), getattr(enc, "bits", None)
     if isinstance(name, str) and isinstance(width, int):
         storage = max(8, width) // 8
         return "dense." + name, storage, 1, storage, _C_TYPES.get(name, "uint8_t")
     raise FrontendError(f"{enc!r} is not an Encoding or dtype")
+
+
+def _derived_base_facts(family: object) -> tuple[int, int, int]:
+    function = getattr(family, "python_function", None)
+    if function is None:
+        raise FrontendError(f"derived encoding {getattr(family, '__name__', family)!r} has no builder")
+    parameters = list(family.signature.parameters.values())
+    if not parameters or parameters[0].annotation is parameters[0].empty:
+        raise FrontendError(f"derived encoding {family.__name__} needs a View[base Encoding, shape] source parameter")
+    namespace = dict(function.__globals__)
+    namespace.setdefault(family.__name__, family)
+    base, _ = _view_parts(parameters[0].annotation, namespace)
+    _, storage, elements, alignment, _ = _identity(base)
+    if not storage or not elements:
+        raise FrontendError(f"derived encoding {family.__name__} has no closed storage record")
+    return storage, elements, alignment
 
 
 def _view_parts(annotation: object, namespace: dict) -> tuple[object, tuple]:
