@@ -8,12 +8,13 @@
 // HBM-bound like the plain Q4_K GEMV and streamed the same way: one persistent CTA per SM, a producer lane
 // filling a ring of 18 KB stages with bulk copies, three copies outstanding, bounded waits.  A CTA owns
 // whole cohorts; a stage is eight 256-blocks of one cohort (8 x 2304 bytes, contiguous in this layout).
-// Eight consumer warps take one block of the stage each: the warp transposes its 2304 bytes back into
-// sixteen ordinary 144-byte records in a private scratch (4 x 4 byte transposes with prmt), gives the ring
-// slot back, and then lane (r, h) computes half-record h of row r against the staged activations exactly
-// as the plain kernel does.  Every lane keeps its row's running sum for the whole cohort; at the end the
-// eight warps' partial sums are added in a fixed order (so results do not depend on timing) and 16
-// outputs are written.
+// Two teams of eight consumer warps work on alternate stages of a cohort; a warp takes one block of its
+// team's stage: it transposes the 2304 bytes back into sixteen ordinary 144-byte records in a private
+// scratch (4 x 4 byte transposes with prmt), gives the ring slot back, and then lane (r, h) computes
+// half-record h of row r against the staged activations exactly as the plain kernel does.  Every lane
+// keeps its row's running sum for the whole cohort and hands it to a last warp, which adds the sixteen
+// warps' sums in a fixed order (so results do not depend on timing) and writes the 16 outputs while the
+// consumers are already on the next cohort.
 #include "gemv_units.cuh"
 #include "ring.cuh"
 
@@ -25,10 +26,13 @@ namespace {
 
 constexpr int QI_ROWS = 16;                    // rows per cohort
 constexpr int QI_BLOCK = QI_ROWS * 144;        // bytes of one cohort block
-constexpr int QI_CHUNK = 8;                    // blocks per stage = consumer warps
+constexpr int QI_CHUNK = 8;                    // blocks per stage = warps of one consumer team
+constexpr int QI_TEAMS = 2;                    // teams work on different stages of a cohort at the same time
+constexpr int QI_CONSUMERS = QI_CHUNK * QI_TEAMS;
 constexpr int QI_STAGE = QI_CHUNK * QI_BLOCK;  // 18432
 constexpr int QI_STAGES = 8;
-constexpr int QI_THREADS = 32 * (1 + QI_CHUNK);
+constexpr int QI_PARTIALS = 4;                 // cohorts whose partial sums may be pending at once
+constexpr int QI_THREADS = 32 * (2 + QI_CONSUMERS);   // producer, consumers, one warp that adds the partial sums
 
 struct QiParams {
     const uint8_t *w;
@@ -115,11 +119,12 @@ __global__ void __launch_bounds__(QI_THREADS) gemv_q4ki_kernel(const QiParams p)
     volatile int *s_issued = reinterpret_cast<volatile int *>(smem);
     uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + 16);
     uint64_t *s_empty = s_full + S;
-    float *s_partial = reinterpret_cast<float *>(smem + 256);             // [2][QI_CHUNK][32]
-    uint8_t *s_scratch = smem + 256 + 2 * QI_CHUNK * 32 * 4;              // [QI_CHUNK][16 x 144]
-    uint8_t *s_xq = s_scratch + QI_CHUNK * QI_BLOCK;
+    uint64_t *s_done = s_empty + S, *s_free = s_done + QI_PARTIALS;   // partial sums of a cohort written / consumed
+    float *s_partial = reinterpret_cast<float *>(smem + 256);             // [QI_PARTIALS][QI_CONSUMERS][32]
+    uint8_t *s_scratch = smem + 256 + QI_PARTIALS * QI_CONSUMERS * 32 * 4;          // [QI_CONSUMERS][16 x 144]
+    uint8_t *s_xq = s_scratch + QI_CONSUMERS * QI_BLOCK;
     uint8_t *s_aux = s_xq + (size_t)nb * XQ_PITCH;
-    uint8_t *s_ring = smem + ((256 + 2 * QI_CHUNK * 32 * 4 + QI_CHUNK * QI_BLOCK + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127));
+    uint8_t *s_ring = smem + ((256 + QI_PARTIALS * QI_CONSUMERS * 32 * 4 + QI_CONSUMERS * QI_BLOCK + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127));
     const uint32_t ring_addr = smem_addr(s_ring), full_addr = smem_addr(s_full), empty_addr = smem_addr(s_empty);
 
     const int chunks = (nb + QI_CHUNK - 1) / QI_CHUNK;                    // stages per cohort
@@ -132,7 +137,8 @@ __global__ void __launch_bounds__(QI_THREADS) gemv_q4ki_kernel(const QiParams p)
     asm volatile("griddepcontrol.launch_dependents;");
     if (threadIdx.x < S) {
         mbar_init(s_full + threadIdx.x, 1);
-        mbar_init(s_empty + threadIdx.x, QI_CHUNK);   // every consumer warp arrives once per stage
+        mbar_init(s_empty + threadIdx.x, QI_CHUNK);   // every warp of the stage's team arrives once
+        if (threadIdx.x < QI_PARTIALS) { mbar_init(s_done + threadIdx.x, QI_CONSUMERS); mbar_init(s_free + threadIdx.x, 1); }
         mbar_fence_init();
     }
     if (threadIdx.x == 0) *s_issued = 0;
@@ -175,25 +181,42 @@ __global__ void __launch_bounds__(QI_THREADS) gemv_q4ki_kernel(const QiParams p)
         return;
     }
 
-    const int cw = warp - 1;                            // consumer index = block of the stage
+    const uint32_t done_addr = smem_addr(s_done), free_addr = smem_addr(s_free);
     const int r = lane >> 1, h = lane & 1;              // this lane's row of the cohort and half of the record
+    if (warp == 1 + QI_CONSUMERS) {
+        // the adder: waits for the sixteen partial sums of a cohort, adds them in warp order, writes 16 outputs
+        for (long long ci = 0; ci < my_cohorts; ++ci) {
+            const int ps = (int)(ci % QI_PARTIALS);
+            if (!mbar_wait_a(done_addr + 8 * ps, (uint32_t)(ci / QI_PARTIALS) & 1u, 1u << 24)) { report(p.status, ST_WAIT_TIMEOUT); return; }
+            const float *partial = s_partial + ps * (QI_CONSUMERS * 32);
+            float v = 0.f;
+#pragma unroll
+            for (int w = 0; w < QI_CONSUMERS; ++w) v += partial[w * 32 + lane];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);    // the two halves of a row
+            if (h == 0) y[(b + ci * G) * QI_ROWS + r] = v;
+            __syncwarp();                               // every lane has read its partial sums
+            if (lane == 0) mbar_arrive_a(free_addr + 8 * ps);
+        }
+        return;
+    }
+
+    const int cw = warp - 1, team = cw / QI_CHUNK, bj = cw % QI_CHUNK;   // consumer index, its team, its block of the team's stage
     const uint32_t scratch = smem_addr(s_scratch) + (uint32_t)cw * QI_BLOCK;
     const uint32_t xq_addr = smem_addr(s_xq), aux_addr = smem_addr(s_aux);
-    bool ok = true;
-    for (long long ci = 0; ci < my_cohorts && ok; ++ci) {
+    for (long long ci = 0; ci < my_cohorts; ++ci) {
         float acc = 0.f;
-        for (int q = 0; q < chunks; ++q) {
+        for (int q = team; q < chunks; q += QI_TEAMS) {
             const int s = (int)(ci * chunks + q);
             // A parity wait cannot tell fill n of a slot from fill n-2: first wait until the stage has been issued.
             if (*s_issued <= s) {
                 bool issued = false;
                 for (uint32_t spin = 0; spin < (1u << 24) && !issued; ++spin) issued = *s_issued > s;
-                if (!issued) { report(p.status, ST_WAIT_TIMEOUT); ok = false; break; }
+                if (!issued) { report(p.status, ST_WAIT_TIMEOUT); return; }
             }
-            if (!mbar_wait_a(full_addr + 8 * (s & (S - 1)), (uint32_t)(s / S) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); ok = false; break; }
-            const int kb = q * QI_CHUNK + cw;           // this warp's 256-block of the row
+            if (!mbar_wait_a(full_addr + 8 * (s & (S - 1)), (uint32_t)(s / S) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
+            const int kb = q * QI_CHUNK + bj;           // this warp's 256-block of the row
             const bool mine = kb < nb;
-            if (mine) deinterleave_block(ring_addr + (uint32_t)(s & (S - 1)) * QI_STAGE + (uint32_t)cw * QI_BLOCK, scratch, lane);
+            if (mine) deinterleave_block(ring_addr + (uint32_t)(s & (S - 1)) * QI_STAGE + (uint32_t)bj * QI_BLOCK, scratch, lane);
             __syncwarp();                               // the scratch is complete, the slot no longer needed by this warp
             if (lane == 0) mbar_arrive_a(empty_addr + 8 * (s & (S - 1)));
             if (mine) {
@@ -202,18 +225,12 @@ __global__ void __launch_bounds__(QI_THREADS) gemv_q4ki_kernel(const QiParams p)
             }
             __syncwarp();                               // every lane has read the scratch before the next block overwrites it
         }
-        if (!ok) break;
-        // add the eight warps' sums in a fixed order; two cohorts' partials are kept so that nobody waits twice
-        float *partial = s_partial + (ci & 1) * (QI_CHUNK * 32);
-        partial[cw * 32 + lane] = acc;
-        asm volatile("bar.sync 1, %0;" ::"r"(QI_CHUNK * 32) : "memory");
-        if (cw == 0) {
-            float v = 0.f;
-#pragma unroll
-            for (int w = 0; w < QI_CHUNK; ++w) v += partial[w * 32 + lane];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);    // the two halves of a row
-            if (h == 0) y[(b + ci * G) * QI_ROWS + r] = v;
-        }
+        // hand the cohort's partial sums to the adder; a slot is reused QI_PARTIALS cohorts later, once it has been read
+        const int ps = (int)(ci % QI_PARTIALS);
+        if (ci >= QI_PARTIALS && !mbar_wait_a(free_addr + 8 * ps, (uint32_t)(ci / QI_PARTIALS - 1) & 1u, 1u << 24)) { report(p.status, ST_WAIT_TIMEOUT); return; }
+        s_partial[ps * (QI_CONSUMERS * 32) + cw * 32 + lane] = acc;
+        __syncwarp();                                   // all 32 sums are written before lane 0 says so
+        if (lane == 0) mbar_arrive_a(done_addr + 8 * ps);
     }
 }
 
@@ -263,7 +280,7 @@ cudaError_t launch_variant(const QiParams &p, dim3 grid, size_t smem, cudaStream
 }
 
 size_t q4ki_smem(long long nb) {
-    return ((256 + 2 * QI_CHUNK * 32 * 4 + QI_CHUNK * QI_BLOCK + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127)) + (size_t)QI_STAGES * QI_STAGE;
+    return ((256 + QI_PARTIALS * QI_CONSUMERS * 32 * 4 + QI_CONSUMERS * QI_BLOCK + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127)) + (size_t)QI_STAGES * QI_STAGE;
 }
 
 }  // namespace
