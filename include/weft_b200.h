@@ -15,7 +15,7 @@
  *     found again by address, so only activations and outputs move per call.
  *
  * Records are the GGML block formats, never repacked: Q4_0 18 B/32, Q8_0 34 B/32, Q4_K 144 B/256,
- * Q8_K 292 B/256, IQ2_XXS 66 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
+ * Q6_K 210 B/256, Q8_K 292 B/256, IQ2_XXS 66 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
  * device-pointer arguments: Xq is the caller's written workspace, as in the reference.
  * IQ2_XXS tables arrive as arguments: grid int8[256][8], signs int8[128][8] with entries +1 / -1.
  * TQ1_0 takes powers uint32[5] = {1, 3, 9, 27, 81}.
@@ -121,6 +121,22 @@ int quantized_vec_dot_tq1_0_q8_k_rows(const uint8_t *W, const uint8_t *X, const 
 int q8_0_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 
+/* ------------------------------------------------------------------ Q6_K x Q8_K (ggml-common.h block_q6_K: ql[128], qh[64],
+ * int8 scales[16], f16 d; ggml-quants.c:1881-1910, ggml-cpu/quants.c:800-853).  The reference's Q6_K Encoding
+ * (examples/formats/ggml.py:113-120) states no alignment, so W may start at any byte: a device W at an odd
+ * address is first moved to an aligned slice of the library's arena (one device-to-device copy inside the call).
+ * examples/kernels/vec_dot/q6_k_q8_k.py:39-43          vec_dot_runtime.cpp:263-264 */
+int quantized_vec_dot_q6_k_q8_k(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
+int quantized_vec_dot_q6_k_q8_k_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
+/* examples/kernels/dequantize/q6_k.py:8-15             row_dequantize_runtime.cpp:222,374 */
+int row_dequantize_q6_k(const uint8_t *W, float *Y, size_t K);
+int row_dequantize_q6_k_rows(const uint8_t *W, float *Y, size_t N, size_t K);
+/* examples/kernels/mul_mat/q6_k_decode.py:10-20        mul_mat_runtime.cpp:383-384 */
+int production_mul_mat_q6_k_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/q6_k.py:9-37                mul_mat_runtime.cpp:386-387
+ * (runs the decode GEMV once per activation row: no tensor-core path for this format yet) */
+int production_mul_mat_q6_k(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+
 /* Persistent interleaved weight layout Q4K_I[16] (examples/formats/ggml.py:286-290): the Q4_K records of each
  * cohort of 16 rows stored byte-major, byte b of row r of a 256-block at 16 b + r, blocks in (cohort, block)
  * order (doc/dsl/encoding-and-artifacts.md:209).  Artifact functions as the reference emits them next to every
@@ -137,7 +153,7 @@ int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *ta
 int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N);
 
 /* Row-sharded mul_mat: this process holds weight rows [n0, n0+N_local) of an (N,K) matrix and writes
- * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 8 Q4_K, 15 IQ2_XXS,
+ * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 8 Q4_K, 10 Q6_K, 15 IQ2_XXS,
  * 20 TQ1_0 (the reference harness numbering).  mode: 0 decode (GEMV), 1 prefill (tensor cores).
  * flags bit 0: Xq already holds the quantized activations (X may be NULL). */
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,

@@ -21,11 +21,11 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 
-Q4_0, Q8_0, Q4_K, IQ2_XXS, TQ1_0, Q8_K = 1, 5, 8, 15, 20, 100
-FORMAT_IDS = {"Q4_0": Q4_0, "Q8_0": Q8_0, "Q4_K": Q4_K, "IQ2_XXS": IQ2_XXS, "TQ1_0": TQ1_0, "Q8_K": Q8_K}
-RECORD_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, IQ2_XXS: 66, TQ1_0: 54, Q8_K: 292}
-RECORD_ELEMENTS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, IQ2_XXS: 256, TQ1_0: 256, Q8_K: 256}
-ACTIVATION = {Q4_0: Q8_0, Q8_0: Q8_0, Q4_K: Q8_K, IQ2_XXS: Q8_K, TQ1_0: Q8_K}
+Q4_0, Q8_0, Q4_K, Q6_K, IQ2_XXS, TQ1_0, Q8_K = 1, 5, 8, 10, 15, 20, 100
+FORMAT_IDS = {"Q4_0": Q4_0, "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K, "IQ2_XXS": IQ2_XXS, "TQ1_0": TQ1_0, "Q8_K": Q8_K}
+RECORD_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, IQ2_XXS: 66, TQ1_0: 54, Q8_K: 292}
+RECORD_ELEMENTS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, IQ2_XXS: 256, TQ1_0: 256, Q8_K: 256}
+ACTIVATION = {Q4_0: Q8_0, Q8_0: Q8_0, Q4_K: Q8_K, Q6_K: Q8_K, IQ2_XXS: Q8_K, TQ1_0: Q8_K}
 
 _u8p = ctypes.POINTER(ctypes.c_uint8)
 _i8p = ctypes.POINTER(ctypes.c_int8)

@@ -65,6 +65,7 @@ size_t wo_record_bytes(int fmt) {
     case WO_Q4_0: return 18;
     case WO_Q8_0: return 34;
     case WO_Q4_K: return 144;
+    case WO_Q6_K: return 210;
     case WO_IQ2_XXS: return 66;
     case WO_TQ1_0: return 54;
     case WO_Q8_K: return 292;
@@ -75,7 +76,7 @@ size_t wo_record_bytes(int fmt) {
 size_t wo_record_elements(int fmt) {
     switch (fmt) {
     case WO_Q4_0: case WO_Q8_0: return 32;
-    case WO_Q4_K: case WO_IQ2_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
+    case WO_Q4_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
     default: return 0;
     }
 }
@@ -519,6 +520,7 @@ static void wo_dequantize_range(int64_t begin, int64_t end, void *p) {
         case WO_Q4_0: wo_dequantize_row_q4_0(wr, yr, c->k); break;
         case WO_Q8_0: wo_dequantize_row_q8_0(wr, yr, c->k); break;
         case WO_Q4_K: wo_dequantize_row_q4_K(wr, yr, c->k); break;
+        case WO_Q6_K: wo_dequantize_row_q6_K(wr, yr, c->k); break;
         case WO_IQ2_XXS: wo_dequantize_row_iq2_xxs(wr, c->grid, c->signs, yr, c->k); break;
         case WO_TQ1_0: wo_dequantize_row_tq1_0(wr, yr, c->k); break;
         default: break;
@@ -596,6 +598,46 @@ float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
     return sumf;
 }
 
+/* ---- Q6_K: 210 bytes per 256 weights = ql[128] (low nibbles), qh[64] (high 2 bits), int8 scales[16], f16 d
+ * (ggml/src/ggml-common.h:349-358; examples/formats/ggml.py class Q6_K).  In each half of 128 weights,
+ * weight 32 p + l (p = 0..3, l = 0..31) takes its low nibble from ql[l + 32 (p & 1)] (low half for p < 2, high
+ * half otherwise) and its two high bits from bits 2p, 2p+1 of qh[l]; value = that 6-bit number - 32; its
+ * scale is scales[8 half + 2 p + l / 16]. */
+static int q6k_value(const uint8_t *rec, int e) {
+    const int half = e >> 7, p = (e >> 5) & 3, l = e & 31;
+    const uint8_t lo = rec[64 * half + l + 32 * (p & 1)];
+    const int nib = p < 2 ? (lo & 0x0f) : (lo >> 4);
+    const int hi = (rec[128 + 32 * half + l] >> (2 * p)) & 3;
+    return (int8_t)(nib | (hi << 4)) - 32;
+}
+
+/* ggml/src/ggml-quants.c:1881-1910; examples/kernels/dequantize/q6_k.py:8-14: y = (d * scale) * q */
+void wo_dequantize_row_q6_K(const uint8_t *w, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 210, y += 256) {
+        const float d = wo_f16_to_f32(ld_u16(w + 208));
+        const int8_t *sc = (const int8_t *)(w + 192);
+        for (int e = 0; e < 256; ++e) y[e] = d * sc[e >> 4] * q6k_value(w, e);
+    }
+}
+
+/* ggml/src/ggml-cpu/quants.c:800-853; examples/kernels/vec_dot/q6_k_q8_k.py:8-36: per block eight int32 lane
+ * sums (element index mod 8) of scale * (x * q), each added to its float lane as (d_w * d_x) * sum; the
+ * eight float lanes are added at the end, lane 0 first. */
+float wo_vec_dot_q6_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
+    float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int64_t b = 0; b < k / 256; ++b, w += 210, x += 292) {
+        const int8_t *xq = (const int8_t *)(x + 4);
+        const int8_t *sc = (const int8_t *)(w + 192);
+        int32_t lane_i[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int e = 0; e < 256; ++e) lane_i[e & 7] += sc[e >> 4] * (int16_t)(xq[e] * q6k_value(w, e));
+        const float d = wo_f16_to_f32(ld_u16(w + 208)) * ld_f32(x);
+        for (int l = 0; l < 8; ++l) lanes[l] += d * lane_i[l];
+    }
+    float sumf = 0;
+    for (int l = 0; l < 8; ++l) sumf += lanes[l];
+    return sumf;
+}
+
 /* ggml/src/ggml-cpu/quants.c:855-895; examples/kernels/vec_dot/iq2_xxs_q8_k.py:8-54 */
 float wo_vec_dot_iq2_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k) {
     float sumf = 0.f;
@@ -644,6 +686,7 @@ int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, 
     case WO_Q4_0: *out = wo_vec_dot_q4_0_q8_0(w, x, k); return 0;
     case WO_Q8_0: *out = wo_vec_dot_q8_0_q8_0(w, x, k); return 0;
     case WO_Q4_K: *out = wo_vec_dot_q4_K_q8_K(w, x, k); return 0;
+    case WO_Q6_K: *out = wo_vec_dot_q6_K_q8_K(w, x, k); return 0;
     case WO_IQ2_XXS: *out = wo_vec_dot_iq2_xxs_q8_K(w, x, grid, signs, k); return 0;
     case WO_TQ1_0: *out = wo_vec_dot_tq1_0_q8_K(w, x, k); return 0;
     default: return -1;

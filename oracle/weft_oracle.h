@@ -29,6 +29,7 @@ enum wo_format {
     WO_Q4_0 = 1,
     WO_Q8_0 = 5,
     WO_Q4_K = 8,
+    WO_Q6_K = 10,
     WO_IQ2_XXS = 15,
     WO_TQ1_0 = 20,
     WO_Q8_K = 100
@@ -59,6 +60,7 @@ int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrow
 void wo_dequantize_row_q4_0(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q8_0(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q4_K(const uint8_t *w, float *y, int64_t k);
+void wo_dequantize_row_q6_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_iq2_xxs(const uint8_t *w, const int8_t *grid, const int8_t *signs, float *y, int64_t k);
 void wo_dequantize_row_tq1_0(const uint8_t *w, float *y, int64_t k);
 int wo_dequantize_rows(int fmt, const uint8_t *w, const int8_t *grid, const int8_t *signs,
@@ -70,6 +72,7 @@ float wo_vec_dot_q8_0_q8_0(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_iq2_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k);
 float wo_vec_dot_tq1_0_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
+float wo_vec_dot_q6_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs,
                int64_t k, float *out);
 

@@ -29,9 +29,10 @@ ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 import oracle as o  # noqa: E402
 
-FORMATS = {"q4_0": o.Q4_0, "q8_0": o.Q8_0, "q4_k": o.Q4_K, "iq2_xxs": o.IQ2_XXS, "tq1_0": o.TQ1_0}
-VEC_DOT_IDS = {"q4_0": 1, "q8_0": 5, "q4_k": 8, "iq2_xxs": 15, "tq1_0": 20}    # vec_dot / dequantize harness ids
-MUL_MAT_IDS = {"q4_0": 2, "q8_0": 6, "q4_k": 9, "iq2_xxs": 16, "tq1_0": 21}    # mul_mat harness ids
+# new formats go last: the seeded generator is consumed in this order
+FORMATS = {"q4_0": o.Q4_0, "q8_0": o.Q8_0, "q4_k": o.Q4_K, "iq2_xxs": o.IQ2_XXS, "tq1_0": o.TQ1_0, "q6_k": o.Q6_K}
+VEC_DOT_IDS = {"q4_0": 1, "q8_0": 5, "q4_k": 8, "iq2_xxs": 15, "tq1_0": 20, "q6_k": 10}    # vec_dot / dequantize harness ids
+MUL_MAT_IDS = {"q4_0": 2, "q8_0": 6, "q4_k": 9, "iq2_xxs": 16, "tq1_0": 21, "q6_k": 11}    # mul_mat harness ids
 
 
 def closed_form_weights(count: int, fmt_id: int) -> np.ndarray:

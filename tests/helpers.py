@@ -29,11 +29,20 @@ def random_iq2_xxs(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     return rec.reshape(n, nb * 66)
 
 
+def random_q6_k(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
+    """Random but valid Q6_K records: any ql / qh byte and any int8 scale is legal; d is a small f16."""
+    nb = k // 256
+    rec = rng.integers(0, 256, size=(n, nb, 210), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal((n, nb))) * 1e-4 + 1e-5).astype(np.float16)
+    rec[:, :, 208:210] = d.view(np.uint8).reshape(n, nb, 2)
+    return rec.reshape(n, nb * 210)
+
+
 def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     """Seeded weights of the benchmark distributions, quantized: N(0, 0.02) (scale * {-1,0,+1} for TQ1_0).
 
-    IQ2_XXS goes through the compiled reference quantizer when it is present and falls back to
-    random valid records otherwise (the port has no IQ2_XXS quantizer)."""
+    IQ2_XXS and Q6_K go through the compiled reference quantizer when it is present and fall back to
+    random valid records otherwise (the port has no quantizer for them)."""
     if fmt == o.TQ1_0:
         src = (rng.integers(-1, 2, size=(n, k)) * np.float32(0.02)).astype(np.float32)
         return o.quantize(fmt, src)
@@ -41,6 +50,10 @@ def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
         if o.ref_available() and n * k <= 1 << 22:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
         return random_iq2_xxs(rng, n, k)
+    if fmt == o.Q6_K:
+        if o.ref_available() and n * k <= 1 << 22:
+            return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        return random_q6_k(rng, n, k)
     return o.quantize(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
 
 

@@ -15,7 +15,7 @@ from helpers import TQ1_POWERS, activations, random_iq2_xxs, reference_tolerance
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0"]
+FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k"]
 REL_L2_BOUND = 1e-5
 
 
@@ -133,6 +133,28 @@ def test_row_dequantize_unaligned_views(torch, weft, oracle):
     kernel(Buffer(raw[2:2 + w.size], shape=(n, k), encoding="Q4_K"), Buffer(out[1:1 + n * k], shape=(n, k)))
     assert np.array_equal(out[1:1 + n * k].cpu().numpy().view(np.uint32), want.reshape(-1).view(np.uint32))
     assert out[0] == 0 and out[1 + n * k] == 0
+
+
+def test_q6_k_at_an_odd_address(torch, weft, oracle):
+    """The reference's Q6_K Encoding states no alignment: a weight view may start at any byte."""
+    from weft_b200.kernels import mul_mat, rows
+    from weft_b200.runtime import Buffer
+
+    rng = np.random.default_rng(19)
+    n, k = 37, 1024
+    w = weights(oracle.Q6_K, rng, n, k)
+    x = activations(rng, 2, k)
+    raw = torch.zeros(w.size + 16, dtype=torch.uint8, device="cuda")
+    raw[1:1 + w.size] = dev(torch, w.reshape(-1))
+    view = Buffer(raw[1:1 + w.size], shape=(n, k), encoding="Q6_K")
+    y = torch.empty((n, k), device="cuda")
+    weft.compile(rows.row_dequantize_q6_k_rows)(view, y)
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), oracle.dequantize(oracle.Q6_K, w, k).view(np.uint32))
+    want, want_xq = oracle.mul_mat(oracle.Q6_K, w, x, n, k, 2, rule=1)
+    xq = torch.zeros((2, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
+    out = torch.empty((2, n), device="cuda")
+    weft.compile(mul_mat.production_mul_mat_q6_k)(view, dev(torch, x), Buffer(xq, shape=(2, k), encoding="Q8_K"), out)
+    assert np.array_equal(xq.cpu().numpy(), want_xq) and rel_l2(out.cpu().numpy(), want) <= REL_L2_BOUND
 
 
 # ------------------------------------------------------------------ activation quantize

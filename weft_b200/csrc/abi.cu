@@ -134,18 +134,20 @@ class Call {
         }
         Arg arg;
         arg.user = ptr; arg.bytes = bytes; arg.written = written;
-        const size_t offset = (used_ + 255) & ~size_t(255);
-        wanted_ = ((wanted_ + 255) & ~size_t(255)) + bytes;
-        if (offset + bytes <= g.arena_bytes) {
-            arg.dev = g.arena + offset;
-            used_ = offset + bytes;
-        } else {
-            CU(cudaMalloc(&arg.dev, bytes));
-            arg.overflow = true;
-        }
-        args_.push_back(arg);
+        if (slice(arg)) return 1;
         if (read) CU(cudaMemcpyAsync(arg.dev, ptr, bytes, cudaMemcpyHostToDevice, g.stream));
         *out = arg.dev;
+        return 0;
+    }
+    // A read-only device argument at an address the kernels cannot load from (an Encoding with byte alignment
+    // whose records hold 16-bit fields, at an odd address): move it to an aligned slice.
+    int realign(void **dev, size_t bytes) {
+        Arg arg;
+        arg.bytes = bytes;
+        if (slice(arg)) return 1;
+        any_host_ = true;   // the slice is reused by the next call: end this one with a synchronize
+        CU(cudaMemcpyAsync(arg.dev, *dev, bytes, cudaMemcpyDeviceToDevice, g.stream));
+        *dev = arg.dev;
         return 0;
     }
     // Copy written host arguments back and decide whether to wait.
@@ -168,6 +170,19 @@ class Call {
     }
 
   private:
+    int slice(Arg &arg) {
+        const size_t offset = (used_ + 255) & ~size_t(255);
+        wanted_ = ((wanted_ + 255) & ~size_t(255)) + arg.bytes;
+        if (offset + arg.bytes <= g.arena_bytes) {
+            arg.dev = g.arena + offset;
+            used_ = offset + arg.bytes;
+        } else {
+            CU(cudaMalloc(&arg.dev, arg.bytes));
+            arg.overflow = true;
+        }
+        args_.push_back(arg);
+        return 0;
+    }
     std::vector<Arg> args_;
     size_t used_ = 0, wanted_ = 0;
     bool any_host_ = false;
@@ -193,6 +208,7 @@ int do_dequantize(int fmt, const void *W, const int8_t *grid, const int8_t *sign
     Call call;
     void *w, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
     if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
+    if (fmt == F_Q6_K && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
     if (fmt == F_IQ2_XXS && (call.map(grid, 2048, true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
     if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
     if (call.map(Y, N * K * sizeof(float), false, true, &y)) return 1;
@@ -231,6 +247,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     Call call;
     void *w, *x = nullptr, *xq, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
     if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
+    if (fmt == F_Q6_K && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
     if (!have_xq && call.map(X, M * K * sizeof(float), true, false, &x)) return 1;
     if (call.map(Xq, M * row_bytes(act, K), have_xq, !have_xq, &xq)) return 1;
     if (fmt == F_IQ2_XXS && (call.map(grid, 2048, true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
@@ -341,6 +358,7 @@ int weft_b200_weights_release(const void *host) {
 VEC_DOT(quantized_vec_dot_q4_0_q8_0, F_Q4_0, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_q8_0_q8_0, F_Q8_0, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_q4_k_q8_k, F_Q4_K, NO_TABLES, nullptr, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_q6_k_q8_k, F_Q6_K, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_iq2_xxs_q8_k, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
 VEC_DOT(quantized_vec_dot_tq1_0_q8_k, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
 
@@ -351,6 +369,7 @@ VEC_DOT(quantized_vec_dot_tq1_0_q8_k, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powe
 DEQUANT(row_dequantize_q4_0, F_Q4_0, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_q8_0, F_Q8_0, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_q4_k, F_Q4_K, NO_TABLES, nullptr, nullptr, nullptr)
+DEQUANT(row_dequantize_q6_k, F_Q6_K, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_iq2_xxs, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
 DEQUANT(row_dequantize_tq1_0, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
 
@@ -368,11 +387,13 @@ int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K) { return 
 MUL_MAT(production_mul_mat_q4_0_decode, F_Q4_0, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q8_0_decode, F_Q8_0, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q4_k_decode, F_Q4_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q6_k_decode, F_Q6_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_iq2_xxs_decode, F_IQ2_XXS, 0, IQ_TABLES, grid, signs, nullptr)
 MUL_MAT(production_mul_mat_tq1_0_decode, F_TQ1_0, 0, TQ_TABLES, nullptr, nullptr, powers)
 MUL_MAT(production_mul_mat_q4_0, F_Q4_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q8_0, F_Q8_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q4_k_staged, F_Q4_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q6_k, F_Q6_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_tq1_0, F_TQ1_0, 1, TQ_TABLES, nullptr, nullptr, powers)
 MUL_MAT(production_mul_mat_iq2_xxs_staged, F_IQ2_XXS, 1, IQ_TABLES, grid, signs, nullptr)
 
@@ -406,7 +427,7 @@ int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags) {
-    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q4_K && format != F_IQ2_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
+    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q4_K && format != F_Q6_K && format != F_IQ2_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
         return fail("unknown weight format id %d", format);
     if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
     return do_mul_mat(format, mode, W_local, X, Xq, grid, signs, powers, Y_columns, N_local, K, M, ldy, flags, false);

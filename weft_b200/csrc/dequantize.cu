@@ -11,6 +11,7 @@
 //   Q4_K       (d*sc)*q - (dmin*m)               quantization.py:14-17,                   ggml-quants.c:1471-1493
 //   IQ2_XXS    (d*(0.5+s)*0.25) * (grid*sign)    examples/kernels/dequantize/iq2_xxs.py:9-53, ggml-quants.c:2416-2440
 //   TQ1_0      f32(trit-1) * d                   examples/kernels/dequantize/tq1_0.py:9-46,   ggml-quants.c:2356-2393
+//   Q6_K       (d*scale) * (q6 - 32)             examples/kernels/dequantize/q6_k.py:8-14,    ggml-quants.c:1881-1910
 #include "common.cuh"
 #include "kernels.h"
 
@@ -171,6 +172,35 @@ __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_tq1_0_kernel(const uint
 }
 
 // ---- any alignment of W and Y: one thread per output element (slow path, same op trees)
+// ---- Q6_K (210 bytes, 2-byte aligned: ql[128], qh[64], int8 scales[16], f16 d): lane = (half, pair of l);
+// weight 128 half + 32 p + l has low nibble ql[64 half + l + 32 (p & 1)] (>> 4 for p >= 2), high bits 2p, 2p+1
+// of qh[32 half + l], scale scales[8 half + 2 p + l / 16].  A lane writes two consecutive floats in each of
+// the four quadrants: sixteen lanes cover 128 contiguous bytes per store.
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q6_k_kernel(const uint8_t *__restrict__ w, float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    const int half = lane >> 4, li = lane & 15;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 210;
+        const uint32_t qa = ld_u16(rec + 64 * half + 2 * li), qb = ld_u16(rec + 64 * half + 32 + 2 * li);
+        const uint32_t qh = ld_u16(rec + 128 + 32 * half + 2 * li);
+        const float d = half_bits_to_float(ld_u16(rec + 208));
+        float *out = y + u * 256 + 128 * half + 2 * li;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+            const float ds = __fmul_rn(d, (float)(int)(int8_t)rec[192 + 8 * half + 2 * p + (li >> 3)]);
+            float v[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t lo = ((p & 1) ? qb : qa) >> (8 * j);
+                const uint32_t nib = p < 2 ? (lo & 15u) : ((lo >> 4) & 15u);
+                const uint32_t hi = (qh >> (8 * j + 2 * p)) & 3u;
+                v[j] = __fmul_rn(ds, (float)((int)(nib | (hi << 4)) - 32));
+            }
+            __stcs(reinterpret_cast<float2 *>(out + 32 * p), make_float2(v[0], v[1]));
+        }
+    }
+}
+
 __global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
                                            const int8_t *__restrict__ signs, const uint32_t *__restrict__ powers,
                                            float *__restrict__ y, long long elements) {
@@ -195,6 +225,14 @@ __global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ 
             const float d1 = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)sc);
             const float m1 = __fmul_rn(half_bits_to_float(ld_u16(rec + 2)), (float)mn);
             v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+        } else if (fmt == F_Q6_K) {
+            const uint8_t *rec = w + (i / 256) * 210;
+            const int e = (int)(i % 256), half = e >> 7, p = (e >> 5) & 3, l = e & 31;
+            const uint32_t lo = rec[64 * half + l + 32 * (p & 1)];
+            const uint32_t nib = p < 2 ? (lo & 15u) : (lo >> 4);
+            const uint32_t hi = (rec[128 + 32 * half + l] >> (2 * p)) & 3u;
+            const float ds = __fmul_rn(half_bits_to_float(ld_u16(rec + 208)), (float)(int)(int8_t)rec[192 + (e >> 4)]);
+            v = __fmul_rn(ds, (float)((int)(nib | (hi << 4)) - 32));
         } else if (fmt == F_IQ2_XXS) {
             const uint8_t *rec = w + (i / 256) * 66;
             const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8;
@@ -251,6 +289,11 @@ cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const 
     case F_IQ2_XXS: {
         const long long units = elements / 256;
         dequant_iq2_xxs_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, signs, y, units);
+        break;
+    }
+    case F_Q6_K: {
+        const long long units = elements / 256;
+        dequant_q6_k_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
         break;
     }
     case F_TQ1_0: {

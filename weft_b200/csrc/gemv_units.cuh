@@ -1,8 +1,8 @@
 // Shared pieces of the decode GEMV kernels: the per-format dot product of one 256-element weight unit
 // against one staged activation unit, and the staging of activation records (or of fp32 activations,
 // quantized on the way) into shared memory.
-// (examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q4_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py;
-//  GGML ggml-cpu/quants.c:174-208, 400-428, 645-718, 855-895, 430-480.)
+// (examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q4_k_q8_k,q6_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py;
+//  GGML ggml-cpu/quants.c:174-208, 400-428, 645-718, 800-853, 855-895, 430-480.)
 #pragma once
 
 #include "quantize.cuh"
@@ -11,7 +11,7 @@
 namespace weft {
 
 constexpr int XQ_PITCH = 272;   // 256 code bytes + 16: consecutive units start on different bank groups
-constexpr int XAUX_BYTES = 64;  // per unit: Q8_K {f32 d, i32 total, -, -, i32 pair_sums[8]}; Q8_0 {f32 d[8], i32 sums[8]}
+constexpr int XAUX_BYTES = 80;  // per unit: Q8_K {f32 d, i32 total, -, -, i32 pair_sums[8], i16 sums16[16]}; Q8_0 {f32 d[8], i32 sums[8]}
 
 template <int FMT> struct Unit { static constexpr int BYTES = unit_bytes(FMT); };
 
@@ -64,6 +64,54 @@ __device__ __forceinline__ void dot_q4_k(const uint8_t *const (&wp)[RL], const u
                  + p1.z * (int)byte_of(sc[r].mn_hi, 2) + p1.w * (int)byte_of(sc[r].mn_hi, 3);
         acc[r] += xd_ * (d[r] * (float)isum[r] - dmin[r] * (float)msum);
     }
+}
+
+// One Q6_K record (210 bytes, 2-byte aligned): ql[128] low nibbles, qh[64] high bit pairs, int8 scales[16], f16 d.
+// Weight 128 h + 32 p + l = (nibble p / 2 of ql[64 h + 32 (p & 1) + l]) | (bits 2p, 2p + 1 of qh[32 h + l]) << 4, minus 32,
+// with scale 8 h + 2 p + l / 16.  sum(sc * (q - 32) * x) = sum_g sc_g * (sum(q * x) - 32 * sum16_g): the activation's
+// sums of 16 codes come from the codes themselves, as the reference's loop never reads the record's bsums.
+template <int RL>
+__device__ __forceinline__ void dot_q6_k(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    const uint4 s0 = *reinterpret_cast<const uint4 *>(xaux + 48), s1 = *reinterpret_cast<const uint4 *>(xaux + 64);
+    const uint32_t s16[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    uint32_t scw[RL][4];
+    int isum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<4>(wp[r] + 192, scw[r]); isum[r] = 0; }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        uint32_t ql[RL][16], qh[RL][8];
+#pragma unroll
+        for (int r = 0; r < RL; ++r) { ld_words_a2<16>(wp[r] + 64 * h, ql[r]); ld_words_a2<8>(wp[r] + 128 + 32 * h, qh[r]); }
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {   // 16 weights = one scale
+                const uint4 xv = *reinterpret_cast<const uint4 *>(xq + 128 * h + 32 * p + 16 * c);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                const int g = 8 * h + 2 * p + c;
+                const int xs = (int)(int16_t)(s16[g >> 1] >> (16 * (g & 1)));
+#pragma unroll
+                for (int r = 0; r < RL; ++r) {
+                    int dp = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int w = 4 * c + i;
+                        uint32_t lo = ql[r][8 * (p & 1) + w];
+                        if (p >= 2) lo >>= 4;
+                        const uint32_t hb = qh[r][w];
+                        const uint32_t hi = p == 0 ? hb << 4 : p == 1 ? hb << 2 : p == 2 ? hb : hb >> 2;
+                        dp = dp4a_us((lo & 0x0f0f0f0fu) | (hi & 0x30303030u), xw[i], dp);
+                    }
+                    const int sc = (int)(int8_t)(scw[r][g >> 2] >> (8 * (g & 3)));
+                    isum[r] += sc * (dp - 32 * xs);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r] + 208)) * xd_) * (float)isum[r];
 }
 
 // 8 consecutive Q4_0 records = 144 bytes. Record r starts at byte 18r: f16 d, then 16 nibble bytes.
@@ -295,11 +343,17 @@ __device__ __forceinline__ void dot_tq1_0(const uint8_t *const (&wp)[RL], const 
 
 // ------------------------------------------------------------------ activation staging
 
-// Q8_K records (292 B, 4-byte aligned) -> codes at unit*XQ_PITCH, aux {d, total, pair sums}
+// Q8_K records (292 B, 4-byte aligned) -> codes at unit*XQ_PITCH, aux {d, total, pair sums, sums of 16}
 __device__ inline void stage_q8_k(const uint8_t *xq, int nb, uint8_t *s_q, uint8_t *s_aux) {
     for (int i = threadIdx.x; i < nb * 64; i += blockDim.x) {
         const int u = i >> 6, wd = i & 63;
-        *reinterpret_cast<uint32_t *>(s_q + u * XQ_PITCH + 4 * wd) = *reinterpret_cast<const uint32_t *>(xq + (size_t)u * 292 + 4 + 4 * wd);
+        const uint32_t v = *reinterpret_cast<const uint32_t *>(xq + (size_t)u * 292 + 4 + 4 * wd);
+        *reinterpret_cast<uint32_t *>(s_q + u * XQ_PITCH + 4 * wd) = v;
+        // sums of 16 codes, from the codes (a warp is wholly inside or outside this loop: the bound is a multiple of 64)
+        int s = dp4a_ss(v, 0x01010101u, 0);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        if ((wd & 3) == 0) *reinterpret_cast<int16_t *>(s_aux + u * XAUX_BYTES + 48 + 2 * (wd >> 2)) = (int16_t)s;
     }
     for (int u = threadIdx.x; u < nb; u += blockDim.x) {
         const uint8_t *rec = xq + (size_t)u * 292;
@@ -350,6 +404,7 @@ __device__ inline void quantize_stage_q8_k(const float *x, int nb, uint8_t *s_q,
         for (int o = 4; o < 32; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         int *aux = reinterpret_cast<int *>(s_aux + u * XAUX_BYTES);
         if ((lane & 3) == 0) aux[4 + (lane >> 2)] = s32;
+        if ((lane & 1) == 0) *reinterpret_cast<int16_t *>(s_aux + u * XAUX_BYTES + 48 + lane) = (int16_t)sum16;
         if (lane == 0) { aux[0] = __float_as_int(d); aux[1] = total; }
         if (out) store_q8_k(out + (size_t)u * 292, lane, q0, q1, sum16, d);
     }

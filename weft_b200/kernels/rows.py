@@ -24,6 +24,10 @@ def row_dequantize_q8_0_rows(W: wl.View[ggml.Q8_0, (N, K)], Y: wl.View[wl.f32, (
 def row_dequantize_q4_k_rows(W: wl.View[ggml.Q4_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
 
 
+@kernel
+def row_dequantize_q6_k_rows(W: wl.View[ggml.Q6_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
 @kernel(alias_groups={"Y": "output"})
 def row_dequantize_iq2_xxs_rows(W: wl.View[ggml.IQ2_XXS, (N, K)], grid: wl.View[wl.i8, (2048,)],
                                 signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (N, K)]): ...
@@ -44,6 +48,10 @@ def quantized_vec_dot_q8_0_q8_0_rows(W: wl.View[ggml.Q8_0, (N, K)], X: wl.View[g
 
 @kernel
 def quantized_vec_dot_q4_k_q8_k_rows(W: wl.View[ggml.Q4_K, (N, K)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_q6_k_q8_k_rows(W: wl.View[ggml.Q6_K, (N, K)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (N,)]): ...
 
 
 @kernel
