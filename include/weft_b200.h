@@ -15,7 +15,7 @@
  *     found again by address, so only activations and outputs move per call.
  *
  * Records are the GGML block formats, never repacked: Q4_0 18 B/32, Q8_0 34 B/32, Q4_K 144 B/256,
- * Q6_K 210 B/256, Q8_K 292 B/256, IQ2_XXS 66 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
+ * Q5_K 176 B/256, Q6_K 210 B/256, Q8_K 292 B/256, IQ2_XXS 66 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
  * device-pointer arguments: Xq is the caller's written workspace, as in the reference.
  * IQ2_XXS tables arrive as arguments: grid int8[256][8], signs int8[128][8] with entries +1 / -1.
  * TQ1_0 takes powers uint32[5] = {1, 3, 9, 27, 81}.
@@ -71,8 +71,11 @@ int row_dequantize_iq2_xxs(const uint8_t *W, const int8_t *grid, const int8_t *s
 int row_dequantize_tq1_0(const uint8_t *W, const uint32_t *powers, float *Y, size_t K);
 
 /* ------------------------------------------------------------------ activation quantizers, one row
- * examples/kernels/quantize/q8_0.py:20-23, q8_k.py:32-35   examples/repro/weft/q8_quantize_runtime.cpp:25-26 */
+ * examples/kernels/quantize/q8_0.py:20-23, q8_1.py:28-30, q8_k.py:32-35   examples/repro/weft/q8_quantize_runtime.cpp:13-26
+ * Q8_1 (36 B/32: f16 d, f16 s = f16(sum of codes * d), 32 codes) is the activation format of the *_1 weight
+ * formats; only its quantizer is exported. */
 int q8_0_quantize(const float *X, uint8_t *Y, size_t K);
+int q8_1_quantize(const float *X, uint8_t *Y, size_t K);
 int q8_K_quantize(const float *X, uint8_t *Y, size_t K);
 
 /* ------------------------------------------------------------------ production_mul_mat, decode form (GEMV per activation row)
@@ -119,7 +122,23 @@ int quantized_vec_dot_q4_k_q8_k_rows(const uint8_t *W, const uint8_t *X, float *
 int quantized_vec_dot_iq2_xxs_q8_k_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, const int8_t *signs, float *Y, size_t N, size_t K);
 int quantized_vec_dot_tq1_0_q8_k_rows(const uint8_t *W, const uint8_t *X, const uint32_t *powers, float *Y, size_t N, size_t K);
 int q8_0_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
+int q8_1_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
+
+/* ------------------------------------------------------------------ Q5_K x Q8_K (ggml-common.h block_q5_K: f16 d, f16 dmin,
+ * scales[12] as in Q4_K, qh[32], qs[128]; ggml-quants.c:1673-1698, ggml-cpu/quants.c:720-798; Encoding
+ * examples/formats/ggml.py:100-110, 2-byte aligned).
+ * examples/kernels/vec_dot/q5_k_q8_k.py:34-38          vec_dot_runtime.cpp:255-256 */
+int quantized_vec_dot_q5_k_q8_k(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
+int quantized_vec_dot_q5_k_q8_k_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
+/* examples/kernels/dequantize/q5_k.py:9-15             row_dequantize_runtime.cpp:217,370 */
+int row_dequantize_q5_k(const uint8_t *W, float *Y, size_t K);
+int row_dequantize_q5_k_rows(const uint8_t *W, float *Y, size_t N, size_t K);
+/* examples/kernels/mul_mat/q5_k_decode.py:10-20        mul_mat_runtime.cpp:368-369 */
+int production_mul_mat_q5_k_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/q5_k.py                     mul_mat_runtime.cpp:371-372
+ * (runs the decode GEMV once per activation row: no tensor-core path for this format yet) */
+int production_mul_mat_q5_k(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 
 /* ------------------------------------------------------------------ Q6_K x Q8_K (ggml-common.h block_q6_K: ql[128], qh[64],
  * int8 scales[16], f16 d; ggml-quants.c:1881-1910, ggml-cpu/quants.c:800-853).  The reference's Q6_K Encoding
@@ -153,7 +172,7 @@ int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *ta
 int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N);
 
 /* Row-sharded mul_mat: this process holds weight rows [n0, n0+N_local) of an (N,K) matrix and writes
- * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 8 Q4_K, 10 Q6_K, 15 IQ2_XXS,
+ * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 8 Q4_K, 9 Q5_K, 10 Q6_K, 15 IQ2_XXS,
  * 20 TQ1_0 (the reference harness numbering).  mode: 0 decode (GEMV), 1 prefill (tensor cores).
  * flags bit 0: Xq already holds the quantized activations (X may be NULL). */
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,

@@ -21,11 +21,11 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 
-Q4_0, Q8_0, Q4_K, Q6_K, IQ2_XXS, TQ1_0, Q8_K = 1, 5, 8, 10, 15, 20, 100
-FORMAT_IDS = {"Q4_0": Q4_0, "Q8_0": Q8_0, "Q4_K": Q4_K, "Q6_K": Q6_K, "IQ2_XXS": IQ2_XXS, "TQ1_0": TQ1_0, "Q8_K": Q8_K}
-RECORD_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q6_K: 210, IQ2_XXS: 66, TQ1_0: 54, Q8_K: 292}
-RECORD_ELEMENTS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q6_K: 256, IQ2_XXS: 256, TQ1_0: 256, Q8_K: 256}
-ACTIVATION = {Q4_0: Q8_0, Q8_0: Q8_0, Q4_K: Q8_K, Q6_K: Q8_K, IQ2_XXS: Q8_K, TQ1_0: Q8_K}
+Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ2_XXS, TQ1_0, Q8_K, Q8_1 = 1, 5, 8, 9, 10, 15, 20, 100, 101
+FORMAT_IDS = {"Q4_0": Q4_0, "Q8_0": Q8_0, "Q4_K": Q4_K, "Q5_K": Q5_K, "Q6_K": Q6_K, "IQ2_XXS": IQ2_XXS, "TQ1_0": TQ1_0, "Q8_K": Q8_K, "Q8_1": Q8_1}
+RECORD_BYTES = {Q4_0: 18, Q8_0: 34, Q4_K: 144, Q5_K: 176, Q6_K: 210, IQ2_XXS: 66, TQ1_0: 54, Q8_K: 292, Q8_1: 36}
+RECORD_ELEMENTS = {Q4_0: 32, Q8_0: 32, Q4_K: 256, Q5_K: 256, Q6_K: 256, IQ2_XXS: 256, TQ1_0: 256, Q8_K: 256, Q8_1: 32}
+ACTIVATION = {Q4_0: Q8_0, Q8_0: Q8_0, Q4_K: Q8_K, Q5_K: Q8_K, Q6_K: Q8_K, IQ2_XXS: Q8_K, TQ1_0: Q8_K}
 
 _u8p = ctypes.POINTER(ctypes.c_uint8)
 _i8p = ctypes.POINTER(ctypes.c_int8)
@@ -92,6 +92,7 @@ def ref() -> ctypes.CDLL:
         lib.weft_ref_quantize_weights.argtypes = [ctypes.c_int, _f32p, ctypes.c_void_p, _i64, _i64]
         lib.weft_ref_quantize_q8_0.argtypes = [_f32p, ctypes.c_void_p, _i64]
         lib.weft_ref_quantize_q8_K.argtypes = [_f32p, ctypes.c_void_p, _i64]
+        lib.weft_ref_quantize_q8_1.argtypes = [_f32p, ctypes.c_void_p, _i64]
         lib.weft_ref_dequantize.argtypes = [ctypes.c_int, ctypes.c_void_p, _f32p, _i64]
         lib.weft_ref_vec_dot.argtypes = [ctypes.c_int, _i64, _f32p, ctypes.c_void_p, ctypes.c_void_p]
         lib.weft_ref_mul_mat.argtypes = [ctypes.c_int, ctypes.c_void_p, _f32p, ctypes.c_void_p, _f32p,
@@ -174,7 +175,7 @@ def ref_quantize_activations(fmt: int, x: np.ndarray) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1, x.shape[-1])
     nrows, k = x.shape
     out = np.zeros((nrows, row_bytes(fmt, k)), dtype=np.uint8)
-    fn = ref().weft_ref_quantize_q8_0 if fmt == Q8_0 else ref().weft_ref_quantize_q8_K
+    fn = {Q8_0: ref().weft_ref_quantize_q8_0, Q8_1: ref().weft_ref_quantize_q8_1, Q8_K: ref().weft_ref_quantize_q8_K}[fmt]
     for r in range(nrows):
         fn(_ptr(x[r], _f32p), out[r].ctypes.data, k)
     return out

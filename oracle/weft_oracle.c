@@ -64,7 +64,9 @@ size_t wo_record_bytes(int fmt) {
     switch (fmt) {
     case WO_Q4_0: return 18;
     case WO_Q8_0: return 34;
+    case WO_Q8_1: return 36;
     case WO_Q4_K: return 144;
+    case WO_Q5_K: return 176;
     case WO_Q6_K: return 210;
     case WO_IQ2_XXS: return 66;
     case WO_TQ1_0: return 54;
@@ -75,8 +77,8 @@ size_t wo_record_bytes(int fmt) {
 
 size_t wo_record_elements(int fmt) {
     switch (fmt) {
-    case WO_Q4_0: case WO_Q8_0: return 32;
-    case WO_Q4_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
+    case WO_Q4_0: case WO_Q8_0: case WO_Q8_1: return 32;
+    case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
     default: return 0;
     }
 }
@@ -191,6 +193,44 @@ void wo_quantize_row_q8_0_weft(const float *x, uint8_t *y, int64_t k) {
             r = r < -128.0f ? -128.0f : (r > 127.0f ? 127.0f : r);
             y[2 + j] = (uint8_t)(int8_t)r;
         }
+    }
+}
+
+/* ggml/src/ggml-quants.c quantize_row_q8_1_ref: Q8_0 plus s = f16(sum(q) * d), d the fp32 scale */
+void wo_quantize_row_q8_1(const float *x, uint8_t *y, int64_t k) {
+    for (int64_t b = 0; b < k / 32; ++b, x += 32, y += 36) {
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) amax = amax > fabsf(x[j]) ? amax : fabsf(x[j]);
+        const float d = amax / 127;
+        const float id = d ? 1.0f / d : 0.0f;
+        st_u16(y, wo_f32_to_f16(d));
+        int sum = 0;
+        for (int j = 0; j < 32; ++j) {
+            const int8_t q = (int8_t)roundf(x[j] * id);
+            y[4 + j] = (uint8_t)q;
+            sum += q;
+        }
+        st_u16(y + 2, wo_f32_to_f16(sum * d));
+    }
+}
+
+/* examples/kernels/quantize/q8_1.py:8-20; examples/repro/weft/q8_quantize_runtime.cpp:117-139 (kind 1):
+ * codes rounded to nearest even and clamped, s = f16(f32(sum) * d) */
+void wo_quantize_row_q8_1_weft(const float *x, uint8_t *y, int64_t k) {
+    for (int64_t b = 0; b < k / 32; ++b, x += 32, y += 36) {
+        float amax = 0.0f;
+        for (int j = 0; j < 32; ++j) amax = amax > fabsf(x[j]) ? amax : fabsf(x[j]);
+        const float d = amax / 127.0f;
+        const float id = amax == 0.0f ? 0.0f : 1.0f / d;
+        st_u16(y, wo_f32_to_f16(d));
+        int sum = 0;
+        for (int j = 0; j < 32; ++j) {
+            float r = rintf(x[j] * id);
+            r = r < -128.0f ? -128.0f : (r > 127.0f ? 127.0f : r);
+            y[4 + j] = (uint8_t)(int8_t)r;
+            sum += (int8_t)r;
+        }
+        st_u16(y + 2, wo_f32_to_f16((float)sum * d));
     }
 }
 
@@ -417,6 +457,7 @@ static void wo_quantize_range(int64_t begin, int64_t end, void *p) {
         case WO_Q4_K: wo_quantize_row_q4_K(xr, yr, k); break;
         case WO_TQ1_0: wo_quantize_row_tq1_0(xr, yr, k); break;
         case WO_Q8_0: if (rule) wo_quantize_row_q8_0_weft(xr, yr, k); else wo_quantize_row_q8_0(xr, yr, k); break;
+        case WO_Q8_1: if (rule) wo_quantize_row_q8_1_weft(xr, yr, k); else wo_quantize_row_q8_1(xr, yr, k); break;
         case WO_Q8_K: if (rule) wo_quantize_row_q8_K_weft(xr, yr, k); else wo_quantize_row_q8_K(xr, yr, k); break;
         default: break;
         }
@@ -520,6 +561,7 @@ static void wo_dequantize_range(int64_t begin, int64_t end, void *p) {
         case WO_Q4_0: wo_dequantize_row_q4_0(wr, yr, c->k); break;
         case WO_Q8_0: wo_dequantize_row_q8_0(wr, yr, c->k); break;
         case WO_Q4_K: wo_dequantize_row_q4_K(wr, yr, c->k); break;
+        case WO_Q5_K: wo_dequantize_row_q5_K(wr, yr, c->k); break;
         case WO_Q6_K: wo_dequantize_row_q6_K(wr, yr, c->k); break;
         case WO_IQ2_XXS: wo_dequantize_row_iq2_xxs(wr, c->grid, c->signs, yr, c->k); break;
         case WO_TQ1_0: wo_dequantize_row_tq1_0(wr, yr, c->k); break;
@@ -587,6 +629,52 @@ float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
             q4k_scale_min(w + 4, g, &sc, &mn);
             sum_min += (ld_i16(x + 260 + 4 * g) + ld_i16(x + 260 + 4 * g + 2)) * mn;
             for (int l = 0; l < 32; ++l) lane_i[l & 7] += sc * (int16_t)(xq[32 * g + l] * a[32 * g + l]);
+        }
+        const float xd = ld_f32(x);
+        const float d = wo_f16_to_f32(ld_u16(w)) * xd;
+        for (int l = 0; l < 8; ++l) lanes[l] += d * lane_i[l];
+        const float dmin = wo_f16_to_f32(ld_u16(w + 2)) * xd;
+        sumf -= dmin * sum_min;
+    }
+    for (int l = 0; l < 8; ++l) sumf += lanes[l];
+    return sumf;
+}
+
+/* ---- Q5_K: 176 bytes per 256 weights = f16 d, f16 dmin, the Q4_K 12-byte (scale, min) field, qh[32] (fifth
+ * bits), qs[128] (nibbles, laid out as in Q4_K)  (ggml/src/ggml-common.h block_q5_K; examples/formats/ggml.py
+ * class Q5_K).  Weight 32 g + l (g = 0..7): nibble g & 1 of qs[32 (g / 2) + l], plus 16 when bit g of qh[l] is set. */
+static int q5k_value(const uint8_t *rec, int e) {
+    const int g = e >> 5, l = e & 31;
+    const uint8_t lo = rec[48 + 32 * (g >> 1) + l];
+    return ((g & 1) ? (lo >> 4) : (lo & 0x0f)) + (((rec[16 + l] >> g) & 1) ? 16 : 0);
+}
+
+/* ggml/src/ggml-quants.c:1673-1698; examples/kernels/dequantize/q5_k.py:9-15: (d*sc)*q - (dmin*m) */
+void wo_dequantize_row_q5_K(const uint8_t *w, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 176, y += 256) {
+        const float d = wo_f16_to_f32(ld_u16(w)), dmin = wo_f16_to_f32(ld_u16(w + 2));
+        for (int g = 0; g < 8; ++g) {
+            int sc, mn;
+            q4k_scale_min(w + 4, g, &sc, &mn);
+            const float d1 = d * sc, m1 = dmin * mn;
+            for (int l = 0; l < 32; ++l) y[32 * g + l] = d1 * q5k_value(w, 32 * g + l) - m1;
+        }
+    }
+}
+
+/* ggml/src/ggml-cpu/quants.c:720-798; examples/kernels/vec_dot/q5_k_q8_k.py:8-31: as Q4_K with 5-bit weights */
+float wo_vec_dot_q5_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
+    float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float sumf = 0;
+    for (int64_t b = 0; b < k / 256; ++b, w += 176, x += 292) {
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int32_t lane_i[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        int sum_min = 0;
+        for (int g = 0; g < 8; ++g) {
+            int sc, mn;
+            q4k_scale_min(w + 4, g, &sc, &mn);
+            sum_min += (ld_i16(x + 260 + 4 * g) + ld_i16(x + 260 + 4 * g + 2)) * mn;
+            for (int l = 0; l < 32; ++l) lane_i[l & 7] += sc * (int16_t)(xq[32 * g + l] * q5k_value(w, 32 * g + l));
         }
         const float xd = ld_f32(x);
         const float d = wo_f16_to_f32(ld_u16(w)) * xd;
@@ -686,6 +774,7 @@ int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, 
     case WO_Q4_0: *out = wo_vec_dot_q4_0_q8_0(w, x, k); return 0;
     case WO_Q8_0: *out = wo_vec_dot_q8_0_q8_0(w, x, k); return 0;
     case WO_Q4_K: *out = wo_vec_dot_q4_K_q8_K(w, x, k); return 0;
+    case WO_Q5_K: *out = wo_vec_dot_q5_K_q8_K(w, x, k); return 0;
     case WO_Q6_K: *out = wo_vec_dot_q6_K_q8_K(w, x, k); return 0;
     case WO_IQ2_XXS: *out = wo_vec_dot_iq2_xxs_q8_K(w, x, grid, signs, k); return 0;
     case WO_TQ1_0: *out = wo_vec_dot_tq1_0_q8_K(w, x, k); return 0;

@@ -29,10 +29,12 @@ enum wo_format {
     WO_Q4_0 = 1,
     WO_Q8_0 = 5,
     WO_Q4_K = 8,
+    WO_Q5_K = 9,
     WO_Q6_K = 10,
     WO_IQ2_XXS = 15,
     WO_TQ1_0 = 20,
-    WO_Q8_K = 100
+    WO_Q8_K = 100,
+    WO_Q8_1 = 101   /* activation-only format: local id */
 };
 
 /* record geometry (ggml/src/ggml-common.h:184-189,241-246,266-271,317-328,361-366,371-375) */
@@ -52,6 +54,8 @@ void wo_quantize_row_q8_0(const float *x, uint8_t *y, int64_t k);
 void wo_quantize_row_q8_K(const float *x, uint8_t *y, int64_t k);
 /* activation quantizers, Weft DSL rule (differs from GGML only on exact ties) */
 void wo_quantize_row_q8_0_weft(const float *x, uint8_t *y, int64_t k);
+void wo_quantize_row_q8_1(const float *x, uint8_t *y, int64_t k);
+void wo_quantize_row_q8_1_weft(const float *x, uint8_t *y, int64_t k);
 void wo_quantize_row_q8_K_weft(const float *x, uint8_t *y, int64_t k);
 /* rows [0,nrows) of a row-major matrix, one thread per contiguous row range; rule: 0 = GGML, 1 = Weft (activations only) */
 int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrows, int64_t k);
@@ -60,6 +64,7 @@ int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrow
 void wo_dequantize_row_q4_0(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q8_0(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q4_K(const uint8_t *w, float *y, int64_t k);
+void wo_dequantize_row_q5_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q6_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_iq2_xxs(const uint8_t *w, const int8_t *grid, const int8_t *signs, float *y, int64_t k);
 void wo_dequantize_row_tq1_0(const uint8_t *w, float *y, int64_t k);
@@ -72,6 +77,7 @@ float wo_vec_dot_q8_0_q8_0(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_iq2_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k);
 float wo_vec_dot_tq1_0_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
+float wo_vec_dot_q5_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_q6_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs,
                int64_t k, float *out);

@@ -30,9 +30,9 @@ sys.path.insert(0, str(ROOT))
 import oracle as o  # noqa: E402
 
 # new formats go last: the seeded generator is consumed in this order
-FORMATS = {"q4_0": o.Q4_0, "q8_0": o.Q8_0, "q4_k": o.Q4_K, "iq2_xxs": o.IQ2_XXS, "tq1_0": o.TQ1_0, "q6_k": o.Q6_K}
-VEC_DOT_IDS = {"q4_0": 1, "q8_0": 5, "q4_k": 8, "iq2_xxs": 15, "tq1_0": 20, "q6_k": 10}    # vec_dot / dequantize harness ids
-MUL_MAT_IDS = {"q4_0": 2, "q8_0": 6, "q4_k": 9, "iq2_xxs": 16, "tq1_0": 21, "q6_k": 11}    # mul_mat harness ids
+FORMATS = {"q4_0": o.Q4_0, "q8_0": o.Q8_0, "q4_k": o.Q4_K, "iq2_xxs": o.IQ2_XXS, "tq1_0": o.TQ1_0, "q6_k": o.Q6_K, "q5_k": o.Q5_K}
+VEC_DOT_IDS = {"q4_0": 1, "q8_0": 5, "q4_k": 8, "iq2_xxs": 15, "tq1_0": 20, "q6_k": 10, "q5_k": 9}    # vec_dot / dequantize harness ids
+MUL_MAT_IDS = {"q4_0": 2, "q8_0": 6, "q4_k": 9, "iq2_xxs": 16, "tq1_0": 21, "q6_k": 11, "q5_k": 10}    # mul_mat harness ids
 
 
 def closed_form_weights(count: int, fmt_id: int) -> np.ndarray:
@@ -114,6 +114,8 @@ def main() -> None:
     x31 = x31.reshape(4, 2048)
     out["q8_0_mod31"] = o.ref_quantize_activations(o.Q8_0, x31)
     out["q8_k_mod31"] = o.ref_quantize_activations(o.Q8_K, x31)
+    out["q8_1_mod31"] = o.ref_quantize_activations(o.Q8_1, x31)
+    out["rnd_xq_q8_1"] = o.ref_quantize_activations(o.Q8_1, x_rnd)
 
     path = Path(__file__).with_name("golden.npz")
     np.savez_compressed(path, **out)

@@ -15,7 +15,7 @@ from helpers import TQ1_POWERS, activations, random_iq2_xxs, reference_tolerance
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k"]
+FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k"]
 REL_L2_BOUND = 1e-5
 
 
@@ -159,12 +159,12 @@ def test_q6_k_at_an_odd_address(torch, weft, oracle):
 
 # ------------------------------------------------------------------ activation quantize
 
-@pytest.mark.parametrize("act", ["q8_0", "q8_K"])
+@pytest.mark.parametrize("act", ["q8_0", "q8_1", "q8_K"])
 def test_activation_quantize_bit_exact(torch, weft, oracle, golden, act):
     from weft_b200.kernels import quantize, rows
     from weft_b200.runtime import Buffer
 
-    fmt = oracle.Q8_0 if act == "q8_0" else oracle.Q8_K
+    fmt = {"q8_0": oracle.Q8_0, "q8_1": oracle.Q8_1, "q8_K": oracle.Q8_K}[act]
     enc = act.upper()
     rng = np.random.default_rng(31)
     i = np.arange(128 * 14336, dtype=np.int64)

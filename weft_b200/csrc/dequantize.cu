@@ -11,6 +11,7 @@
 //   Q4_K       (d*sc)*q - (dmin*m)               quantization.py:14-17,                   ggml-quants.c:1471-1493
 //   IQ2_XXS    (d*(0.5+s)*0.25) * (grid*sign)    examples/kernels/dequantize/iq2_xxs.py:9-53, ggml-quants.c:2416-2440
 //   TQ1_0      f32(trit-1) * d                   examples/kernels/dequantize/tq1_0.py:9-46,   ggml-quants.c:2356-2393
+//   Q5_K       (d*sc)*q5 - (dmin*m)              examples/kernels/dequantize/q5_k.py:9-15,    ggml-quants.c:1673-1698
 //   Q6_K       (d*scale) * (q6 - 32)             examples/kernels/dequantize/q6_k.py:8-14,    ggml-quants.c:1881-1910
 #include "common.cuh"
 #include "kernels.h"
@@ -51,6 +52,36 @@ __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q4_k_kernel(const uint8
             const uint32_t b = byte_of(q, i);
             lo[i] = __fsub_rn(__fmul_rn(d1, (float)(b & 15u)), m1);
             hi[i] = __fsub_rn(__fmul_rn(d2, (float)(b >> 4)), m2);
+        }
+        float *out = y + u * 256 + 64 * j + 4 * t;
+        st4(out, lo[0], lo[1], lo[2], lo[3]);
+        st4(out + 32, hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
+// ---- Q5_K (176 bytes: the Q4_K header, qh[32] fifth bits, qs[128]): same lane map as Q4_K; sub-block g of
+// weight byte l takes bit g of qh[l].
+template <bool A4>
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q5_k_kernel(const uint8_t *__restrict__ w, float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    const int j = lane >> 3, t = lane & 7;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 176;
+        const uint32_t dd = ldw<A4>(rec);
+        const Q4KScales s = q4k_unpack_scales(ldw<A4>(rec + 4), ldw<A4>(rec + 8), ldw<A4>(rec + 12));
+        const uint32_t h = ldw<A4>(rec + 16 + 4 * t) >> (2 * j);
+        const uint32_t q = ldw<A4>(rec + 48 + 32 * j + 4 * t);
+        const float d = half_bits_to_float(dd), dmin = half_bits_to_float(dd >> 16);
+        const uint32_t scv = j < 2 ? s.sc_lo : s.sc_hi, mnv = j < 2 ? s.mn_lo : s.mn_hi;
+        const int b0 = (2 * j) & 3;
+        const float d1 = __fmul_rn(d, (float)byte_of(scv, b0)), m1 = __fmul_rn(dmin, (float)byte_of(mnv, b0));
+        const float d2 = __fmul_rn(d, (float)byte_of(scv, b0 + 1)), m2 = __fmul_rn(dmin, (float)byte_of(mnv, b0 + 1));
+        float lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t b = byte_of(q, i), hb = byte_of(h, i);
+            lo[i] = __fsub_rn(__fmul_rn(d1, (float)((b & 15u) | ((hb & 1u) << 4))), m1);
+            hi[i] = __fsub_rn(__fmul_rn(d2, (float)((b >> 4) | ((hb & 2u) << 3))), m2);
         }
         float *out = y + u * 256 + 64 * j + 4 * t;
         st4(out, lo[0], lo[1], lo[2], lo[3]);
@@ -225,6 +256,16 @@ __global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ 
             const float d1 = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)sc);
             const float m1 = __fmul_rn(half_bits_to_float(ld_u16(rec + 2)), (float)mn);
             v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+        } else if (fmt == F_Q5_K) {
+            const uint8_t *rec = w + (i / 256) * 176;
+            const int e = (int)(i % 256), g = e >> 5, l = e & 31;
+            const Q4KScales s = q4k_unpack_scales(ld_u32_a2(rec + 4), ld_u32_a2(rec + 8), ld_u32_a2(rec + 12));
+            const uint32_t sc = byte_of(g < 4 ? s.sc_lo : s.sc_hi, g & 3), mn = byte_of(g < 4 ? s.mn_lo : s.mn_hi, g & 3);
+            const uint32_t b = rec[48 + 32 * (g >> 1) + l];
+            const uint32_t q = ((g & 1) ? (b >> 4) : (b & 15u)) | (((rec[16 + l] >> g) & 1u) << 4);
+            const float d1 = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)sc);
+            const float m1 = __fmul_rn(half_bits_to_float(ld_u16(rec + 2)), (float)mn);
+            v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
         } else if (fmt == F_Q6_K) {
             const uint8_t *rec = w + (i / 256) * 210;
             const int e = (int)(i % 256), half = e >> 7, p = (e >> 5) & 3, l = e & 31;
@@ -274,6 +315,12 @@ cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const 
         const long long units = elements / 256;
         if (a4) dequant_q4_k_kernel<true><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
         else dequant_q4_k_kernel<false><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
+        break;
+    }
+    case F_Q5_K: {
+        const long long units = elements / 256;
+        if (a4) dequant_q5_k_kernel<true><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
+        else dequant_q5_k_kernel<false><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
         break;
     }
     case F_Q4_0: {

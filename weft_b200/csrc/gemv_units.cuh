@@ -1,8 +1,8 @@
 // Shared pieces of the decode GEMV kernels: the per-format dot product of one 256-element weight unit
 // against one staged activation unit, and the staging of activation records (or of fp32 activations,
 // quantized on the way) into shared memory.
-// (examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q4_k_q8_k,q6_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py;
-//  GGML ggml-cpu/quants.c:174-208, 400-428, 645-718, 800-853, 855-895, 430-480.)
+// (examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q4_k_q8_k,q5_k_q8_k,q6_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py;
+//  GGML ggml-cpu/quants.c:174-208, 400-428, 645-718, 720-798, 800-853, 855-895, 430-480.)
 #pragma once
 
 #include "quantize.cuh"
@@ -50,6 +50,64 @@ __device__ __forceinline__ void dot_q4_k(const uint8_t *const (&wp)[RL], const u
             hi = dp4a_us((qa.y >> 4) & M, xc.y, hi); hi = dp4a_us((qa.z >> 4) & M, xc.z, hi); hi = dp4a_us((qa.w >> 4) & M, xc.w, hi);
             hi = dp4a_us((qb.x >> 4) & M, xd.x, hi); hi = dp4a_us((qb.y >> 4) & M, xd.y, hi);
             hi = dp4a_us((qb.z >> 4) & M, xd.z, hi); hi = dp4a_us((qb.w >> 4) & M, xd.w, hi);
+            const uint32_t scv = j < 2 ? sc[r].sc_lo : sc[r].sc_hi;
+            isum[r] += lo * (int)byte_of(scv, (2 * j) & 3) + hi * (int)byte_of(scv, ((2 * j) & 3) + 1);
+        }
+    }
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    const int4 p0 = *reinterpret_cast<const int4 *>(xaux + 16), p1 = *reinterpret_cast<const int4 *>(xaux + 32);
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        int msum = p0.x * (int)byte_of(sc[r].mn_lo, 0) + p0.y * (int)byte_of(sc[r].mn_lo, 1)
+                 + p0.z * (int)byte_of(sc[r].mn_lo, 2) + p0.w * (int)byte_of(sc[r].mn_lo, 3)
+                 + p1.x * (int)byte_of(sc[r].mn_hi, 0) + p1.y * (int)byte_of(sc[r].mn_hi, 1)
+                 + p1.z * (int)byte_of(sc[r].mn_hi, 2) + p1.w * (int)byte_of(sc[r].mn_hi, 3);
+        acc[r] += xd_ * (d[r] * (float)isum[r] - dmin[r] * (float)msum);
+    }
+}
+
+// One Q5_K record (176 bytes, 16-byte aligned in a staged row): the Q4_K header, qh[32] at +16, qs[128] at +48.
+// Sub-block g of weight byte l is nibble g & 1 of qs[32 (g / 2) + l] plus bit g of qh[l] as the fifth bit.
+template <int RL>
+__device__ __forceinline__ void dot_q5_k(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux, float (&acc)[RL]) {
+    Q4KScales sc[RL];
+    float d[RL], dmin[RL];
+    int isum[RL];
+    uint32_t qh[RL][8];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        const uint4 h = *reinterpret_cast<const uint4 *>(wp[r]);
+        d[r] = half_bits_to_float(h.x);
+        dmin[r] = half_bits_to_float(h.x >> 16);
+        sc[r] = q4k_unpack_scales(h.y, h.z, h.w);
+        const uint4 ha = *reinterpret_cast<const uint4 *>(wp[r] + 16), hb = *reinterpret_cast<const uint4 *>(wp[r] + 32);
+        qh[r][0] = ha.x; qh[r][1] = ha.y; qh[r][2] = ha.z; qh[r][3] = ha.w;
+        qh[r][4] = hb.x; qh[r][5] = hb.y; qh[r][6] = hb.z; qh[r][7] = hb.w;
+        isum[r] = 0;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 64 * j);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 64 * j + 16);
+        const uint4 xc = *reinterpret_cast<const uint4 *>(xq + 64 * j + 32);
+        const uint4 xd = *reinterpret_cast<const uint4 *>(xq + 64 * j + 48);
+        const uint32_t xlo[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        const uint32_t xhi[8] = {xc.x, xc.y, xc.z, xc.w, xd.x, xd.y, xd.z, xd.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint4 qa = *reinterpret_cast<const uint4 *>(wp[r] + 48 + 32 * j);
+            const uint4 qb = *reinterpret_cast<const uint4 *>(wp[r] + 64 + 32 * j);
+            const uint32_t qs[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+            int lo = 0, hi = 0;
+#pragma unroll
+            for (int w = 0; w < 8; ++w) {
+                const uint32_t hw = qh[r][w];
+                // bit 2j -> bit 4 of each byte (low sub-block), bit 2j + 1 -> bit 4 (high sub-block)
+                const uint32_t f_lo = j == 0 ? hw << 4 : j == 1 ? hw << 2 : j == 2 ? hw : hw >> 2;
+                const uint32_t f_hi = j == 0 ? hw << 3 : j == 1 ? hw << 1 : j == 2 ? hw >> 1 : hw >> 3;
+                lo = dp4a_us((qs[w] & 0x0f0f0f0fu) | (f_lo & 0x10101010u), xlo[w], lo);
+                hi = dp4a_us(((qs[w] >> 4) & 0x0f0f0f0fu) | (f_hi & 0x10101010u), xhi[w], hi);
+            }
             const uint32_t scv = j < 2 ? sc[r].sc_lo : sc[r].sc_hi;
             isum[r] += lo * (int)byte_of(scv, (2 * j) & 3) + hi * (int)byte_of(scv, ((2 * j) & 3) + 1);
         }

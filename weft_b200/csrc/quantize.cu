@@ -1,4 +1,4 @@
-// Standalone activation quantizers q8_0_quantize / q8_K_quantize (one warp per 256 elements).
+// Standalone activation quantizers q8_0_quantize / q8_1_quantize / q8_K_quantize (one warp per 256 elements).
 // The arithmetic lives in quantize.cuh.  HBM-bound: 4 bytes read per 1.06-1.14 bytes written.
 #include "quantize.cuh"
 #include "kernels.h"
@@ -22,8 +22,8 @@ __global__ void __launch_bounds__(QZ_WARPS * 32) quantize_q8_k_kernel(const floa
     }
 }
 
-// X: `blocks` groups of 32 floats; Y: Q8_0 records of 34 bytes (2-byte aligned). Four lanes per record.
-template <bool A16>
+// X: `blocks` groups of 32 floats; Y: Q8_0 records of 34 bytes or Q8_1 records of 36 (2-byte aligned). Four lanes per record.
+template <bool A16, bool WITH_SUM>
 __global__ void __launch_bounds__(QZ_WARPS * 32) quantize_q8_0_kernel(const float *__restrict__ x, uint8_t *__restrict__ y, long long blocks) {
     const int lane = threadIdx.x & 31;
     const int sub = lane & 3;
@@ -37,7 +37,10 @@ __global__ void __launch_bounds__(QZ_WARPS * 32) quantize_q8_0_kernel(const floa
         int sum32;
         float d;
         q8_0_warp(v, q0, q1, sum32, d);
-        if (live) store_q8_0(y + b * 34, sub, q0, q1, d);
+        if (live) {
+            if (WITH_SUM) store_q8_1(y + b * 36, sub, q0, q1, sum32, d);
+            else store_q8_0(y + b * 34, sub, q0, q1, d);
+        }
     }
 }
 
@@ -53,12 +56,15 @@ cudaError_t launch_quantize(int act_fmt, const float *x, void *y, long long rows
         const int grid = (int)(want > cap ? cap : want);
         if (a16) quantize_q8_k_kernel<true><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
         else quantize_q8_k_kernel<false><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
-    } else if (act_fmt == F_Q8_0) {
+    } else if (act_fmt == F_Q8_0 || act_fmt == F_Q8_1) {
         const long long blocks = elements / 32;
         const long long want = ((blocks + 7) / 8 + QZ_WARPS - 1) / QZ_WARPS;
         const int grid = (int)(want > cap ? cap : want);
-        if (a16) quantize_q8_0_kernel<true><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
-        else quantize_q8_0_kernel<false><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
+        if (act_fmt == F_Q8_1) {
+            if (a16) quantize_q8_0_kernel<true, true><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
+            else quantize_q8_0_kernel<false, true><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
+        } else if (a16) quantize_q8_0_kernel<true, false><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
+        else quantize_q8_0_kernel<false, false><<<grid, QZ_WARPS * 32, 0, stream>>>(x, yb, blocks);
     } else {
         return cudaErrorInvalidValue;
     }

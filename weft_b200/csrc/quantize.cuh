@@ -4,6 +4,7 @@
 // Semantics are the reference DSL's, which its own bit-exact check restates in scalar C++
 // (examples/kernels/quantize/q8_0.py:8-23, q8_k.py:8-35; examples/repro/weft/q8_quantize_runtime.cpp:85-141):
 //   Q8_0: d = amax/127 (stored f16), inverse = amax == 0 ? 0 : 1/d, q = clamp_i8(rne(x*inverse))
+//   Q8_1: Q8_0 with s = f16(f32(sum of codes) * d) after d (q8_1.py:8-20), codes at byte 4
 //   Q8_K: extreme = |max| > |min| ? max : min, inverse = extreme == 0 ? 0 : -127/extreme,
 //         d = inverse == 0 ? 0 : 1/inverse, q = clamp_i8(rne(x*inverse)), bsum[g] = sum of 16 codes
 // GGML's quantize_row_q8_0_ref / quantize_row_q8_K_ref (ggml-quants.c:238-261, 2696-2733) produce the
@@ -88,6 +89,17 @@ __device__ __forceinline__ void store_q8_0(uint8_t *rec, int sub, uint32_t q0, u
     codes[0] = (uint16_t)q0; codes[1] = (uint16_t)(q0 >> 16);
     codes[2] = (uint16_t)q1; codes[3] = (uint16_t)(q1 >> 16);
     if (sub == 0) *reinterpret_cast<__half *>(rec) = __float2half_rn(d);
+}
+
+// Q8_1 record (36 bytes, 2-byte aligned): f16 d, f16 s = f16(f32(sum32) * d) with the fp32 d, 32 codes
+__device__ __forceinline__ void store_q8_1(uint8_t *rec, int sub, uint32_t q0, uint32_t q1, int sum32, float d) {
+    uint16_t *codes = reinterpret_cast<uint16_t *>(rec + 4 + 8 * sub);
+    codes[0] = (uint16_t)q0; codes[1] = (uint16_t)(q0 >> 16);
+    codes[2] = (uint16_t)q1; codes[3] = (uint16_t)(q1 >> 16);
+    if (sub == 0) {
+        *reinterpret_cast<__half *>(rec) = __float2half_rn(d);
+        *reinterpret_cast<__half *>(rec + 2) = __float2half_rn(__fmul_rn((float)sum32, d));
+    }
 }
 
 }  // namespace weft

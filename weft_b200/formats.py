@@ -1,7 +1,7 @@
 """The GGML record layouts on the quantized matrix path, declared with ``@weft.encoding``.
 
 These are the hot-path encodings of the reference's examples/formats/ggml.py (Q4_0 :16-22,
-Q8_0 :56-62, Q4_K :88-97, Q6_K :113-120, IQ2_XXS :164-170, I8X8 :173-178, TQ1_0 :231-238, Q8_K :276-283), byte for
+Q8_0 :56-62, Q4_K :88-97, Q5_K :100-110, Q6_K :113-120, IQ2_XXS :164-170, I8X8 :173-178, TQ1_0 :231-238, Q8_K :276-283), byte for
 byte the block structs of ggml-common.h:184-189,241-246,266-271,317-328,361-366,371-375.  A kernel
 file may use these or the reference's own declarations: ``weft.compile`` identifies an Encoding by
 its name and checks the record geometry, not the declaring module.
@@ -33,6 +33,16 @@ class Q8_0:                      # 34 bytes / 32 elements
 
 
 @encoding
+class Q8_1:                      # 36 bytes / 32 elements (examples/formats/ggml.py:266-273)
+    layout = _LE
+    alignment = 2
+    elements = 32
+    d: wl.f16
+    s: wl.f16                    # f16(sum of codes * d)
+    q: wl.i8[32]
+
+
+@encoding
 class Q4_K:                      # 144 bytes / 256 elements
     layout = _LE
     alignment = 2
@@ -42,6 +52,19 @@ class Q4_K:                      # 144 bytes / 256 elements
     sc: wl.u6[8] @ wl.pack_fields(group=4, fields=2, low_bits=4, order=wl.lo_first)   # @4, 12 bytes shared with m
     m: wl.u6[8] @ wl.pack_fields(group=4, fields=2, low_bits=4, order=wl.lo_first)
     q: wl.u4[256] @ wl.grouped(elements=64) @ wl.bit_layers(elements=32, order=wl.lo_first)   # @16
+
+
+@encoding
+class Q5_K:                      # 176 bytes / 256 elements
+    layout = _LE
+    alignment = 2
+    elements = 256
+    d: wl.f16                    # @0
+    dmin: wl.f16                 # @2
+    sc: wl.u6[8] @ wl.pack_fields(group=4, fields=2, low_bits=4, order=wl.lo_first)   # @4, 12 bytes shared with m
+    m: wl.u6[8] @ wl.pack_fields(group=4, fields=2, low_bits=4, order=wl.lo_first)
+    qh: wl.u1[256] @ wl.grouped(elements=256) @ wl.bit_layers(elements=32, order=wl.lo_first)   # @16
+    q: wl.u4[256] @ wl.grouped(elements=64) @ wl.bit_layers(elements=32, order=wl.lo_first)     # @48
 
 
 @encoding
@@ -101,11 +124,11 @@ def Q4K_I(W: wl.View[Q4_K, (M, K)], *, rows: wl.static[int]) -> wl.View[Q4K_I[ro
 
 
 #: name -> (storage bytes per record, logical elements per record, alignment)
-RECORDS = {"Q4_0": (18, 32, 2), "Q8_0": (34, 32, 2), "Q4_K": (144, 256, 2), "Q6_K": (210, 256, 1), "IQ2_XXS": (66, 256, 2),
+RECORDS = {"Q4_0": (18, 32, 2), "Q8_0": (34, 32, 2), "Q8_1": (36, 32, 2), "Q4_K": (144, 256, 2), "Q5_K": (176, 256, 2), "Q6_K": (210, 256, 1), "IQ2_XXS": (66, 256, 2),
            "TQ1_0": (54, 256, 2), "Q8_K": (292, 256, 4), "I8X8": (8, 8, 8)}
 
 #: numbering of the reference harnesses (examples/repro/weft/vec_dot_runtime.cpp:185-344), used by the C ABI
-FORMAT_IDS = {"Q4_0": 1, "Q8_0": 5, "Q4_K": 8, "Q6_K": 10, "IQ2_XXS": 15, "TQ1_0": 20}
+FORMAT_IDS = {"Q4_0": 1, "Q8_0": 5, "Q4_K": 8, "Q5_K": 9, "Q6_K": 10, "IQ2_XXS": 15, "TQ1_0": 20}
 
 TQ1_POWERS = (1, 3, 9, 27, 81)
 

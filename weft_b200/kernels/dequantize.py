@@ -1,7 +1,7 @@
 """Row dequantizers: K packed elements -> K fp32 values, bit-exact with the reference's GGML semantics.
 
 Signatures follow examples/kernels/dequantize/q4_0.py:9-13, q8_0.py:9-13, q4_k.py:9-20,
-q6_k.py:8-15, iq2_xxs.py:9-53 and tq1_0.py:9-46 of the reference (Y is its own alias group where the reference says so).
+q5_k.py:9-15, q6_k.py:8-15, iq2_xxs.py:9-53 and tq1_0.py:9-46 of the reference (Y is its own alias group where the reference says so).
 """
 from __future__ import annotations
 
@@ -23,6 +23,11 @@ def row_dequantize_q8_0(W: wl.View[ggml.Q8_0, (K,)], Y: wl.View[wl.f32, (K,)]):
 @kernel(alias_groups={"Y": "output"})
 def row_dequantize_q4_k(W: wl.View[ggml.Q4_K, (K,)], Y: wl.View[wl.f32, (K,)]):
     """Y = (d * sc) * q - (dmin * m), three rounded multiplies and one subtract."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_q5_k(W: wl.View[ggml.Q5_K, (K,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * sc) * q5 - (dmin * m)."""
 
 
 @kernel

@@ -24,6 +24,10 @@ def row_dequantize_q8_0_rows(W: wl.View[ggml.Q8_0, (N, K)], Y: wl.View[wl.f32, (
 def row_dequantize_q4_k_rows(W: wl.View[ggml.Q4_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
 
 
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_q5_k_rows(W: wl.View[ggml.Q5_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
 @kernel
 def row_dequantize_q6_k_rows(W: wl.View[ggml.Q6_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
 
@@ -51,6 +55,10 @@ def quantized_vec_dot_q4_k_q8_k_rows(W: wl.View[ggml.Q4_K, (N, K)], X: wl.View[g
 
 
 @kernel
+def quantized_vec_dot_q5_k_q8_k_rows(W: wl.View[ggml.Q5_K, (N, K)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
 def quantized_vec_dot_q6_k_q8_k_rows(W: wl.View[ggml.Q6_K, (N, K)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (N,)]): ...
 
 
@@ -67,6 +75,10 @@ def quantized_vec_dot_tq1_0_q8_k_rows(W: wl.View[ggml.TQ1_0, (N, K)], X: wl.View
 
 @kernel
 def q8_0_quantize_rows(X: wl.View[wl.f32, (M, K)], Y: wl.View[ggml.Q8_0, (M, K)]): ...
+
+
+@kernel
+def q8_1_quantize_rows(X: wl.View[wl.f32, (M, K)], Y: wl.View[ggml.Q8_1, (M, K)]): ...
 
 
 @kernel
