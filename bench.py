@@ -42,6 +42,8 @@ WORKLOADS = {
     "q4_k_decode_4096x14336": ("Q4_K", "decode", 4096, 14336, 1),
     "q4_0_decode_4096x4096": ("Q4_0", "decode", 4096, 4096, 1),
     "iq2_xxs_decode_28672x8192": ("IQ2_XXS", "decode", 28672, 8192, 1),
+    "q2_k_decode_14336x4096": ("Q2_K", "decode", 14336, 4096, 1),
+    "q3_k_decode_14336x4096": ("Q3_K", "decode", 14336, 4096, 1),
     "q5_k_decode_14336x4096": ("Q5_K", "decode", 14336, 4096, 1),
     "q6_k_decode_14336x4096": ("Q6_K", "decode", 14336, 4096, 1),
     "q4k_i16_decode_14336x4096": ("Q4K_I16", "decode", 14336, 4096, 1),   # persistent 16-row interleaved layout
@@ -110,11 +112,11 @@ def make_inputs(fmt: str, n: int, k: int, m: int, seed: int):
             base = rng.integers(0, 256, size=(base_rows, k // 256, 66), dtype=np.uint8)
             base[:, :, 0:2] = (np.abs(rng.standard_normal((base_rows, k // 256))) * 0.01 + 1e-3).astype(np.float16).view(np.uint8).reshape(base_rows, -1, 2)
             base = base.reshape(base_rows, -1)
-    elif fmt in ("Q5_K", "Q6_K"):
+    elif fmt in ("Q2_K", "Q3_K", "Q5_K", "Q6_K"):
         if oracle.ref_available():
             base = oracle.ref_quantize_weights(fid, (rng.standard_normal((base_rows, k)) * 0.02).astype(np.float32))
         else:           # every bit pattern is a valid record once the f16 scales are small finite numbers
-            nbytes, at, count = (176, 0, 2) if fmt == "Q5_K" else (210, 208, 1)
+            nbytes, at, count = {"Q2_K": (84, 80, 2), "Q3_K": (110, 108, 1), "Q5_K": (176, 0, 2), "Q6_K": (210, 208, 1)}[fmt]
             base = rng.integers(0, 256, size=(base_rows, k // 256, nbytes), dtype=np.uint8)
             scales = (np.abs(rng.standard_normal((base_rows, k // 256, count))) * 1e-4 + 1e-5).astype(np.float16)
             base[:, :, at:at + 2 * count] = scales.view(np.uint8).reshape(base_rows, -1, 2 * count)

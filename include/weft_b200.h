@@ -15,7 +15,7 @@
  *     found again by address, so only activations and outputs move per call.
  *
  * Records are the GGML block formats, never repacked: Q4_0 18 B/32, Q8_0 34 B/32, Q4_K 144 B/256,
- * Q5_K 176 B/256, Q6_K 210 B/256, Q8_K 292 B/256, IQ2_XXS 66 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
+ * Q2_K 84 B/256, Q3_K 110 B/256, Q5_K 176 B/256, Q6_K 210 B/256, Q8_K 292 B/256, IQ2_XXS 66 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
  * device-pointer arguments: Xq is the caller's written workspace, as in the reference.
  * IQ2_XXS tables arrive as arguments: grid int8[256][8], signs int8[128][8] with entries +1 / -1.
  * TQ1_0 takes powers uint32[5] = {1, 3, 9, 27, 81}.
@@ -125,6 +125,32 @@ int q8_0_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 int q8_1_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 
+/* ------------------------------------------------------------------ Q2_K x Q8_K (ggml-common.h:288-298 block_q2_K: scales[16],
+ * qs[64], f16 d, f16 dmin; ggml-quants.c:903-933, ggml-cpu/quants.c:514-564; Encoding examples/formats/ggml.py:64-72).
+ * examples/kernels/vec_dot/q2_k_q8_k.py:28-32          vec_dot_runtime.cpp:231-232 */
+int quantized_vec_dot_q2_k_q8_k(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
+int quantized_vec_dot_q2_k_q8_k_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
+/* examples/kernels/dequantize/q2_k.py:8-17             row_dequantize_runtime.cpp:202,358 */
+int row_dequantize_q2_k(const uint8_t *W, float *Y, size_t K);
+int row_dequantize_q2_k_rows(const uint8_t *W, float *Y, size_t N, size_t K);
+/* examples/kernels/mul_mat/q2_k_decode.py:10-20, q2_k.py:9-41     mul_mat_runtime.cpp:292-296
+ * (both run the decode GEMV once per activation row) */
+int production_mul_mat_q2_k_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_q2_k(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+
+/* ------------------------------------------------------------------ Q3_K x Q8_K (ggml-common.h:305-311 block_q3_K: hmask[32],
+ * qs[64], scales[12], f16 d; ggml-quants.c:1247-1294, ggml-cpu/quants.c:566-643; Encoding examples/formats/ggml.py:75-84).
+ * The reference's _predecoded_scales variants (a derived Encoding with widened scales) are not built.
+ * examples/kernels/vec_dot/q3_k_q8_k.py:46-50          vec_dot_runtime.cpp:239-240 */
+int quantized_vec_dot_q3_k_q8_k(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
+int quantized_vec_dot_q3_k_q8_k_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
+/* examples/kernels/dequantize/q3_k.py:8-17             row_dequantize_runtime.cpp:207,362 */
+int row_dequantize_q3_k(const uint8_t *W, float *Y, size_t K);
+int row_dequantize_q3_k_rows(const uint8_t *W, float *Y, size_t N, size_t K);
+/* examples/kernels/mul_mat/q3_k_decode.py:10-20, q3_k.py:9-61     mul_mat_runtime.cpp:311-312,319-320 */
+int production_mul_mat_q3_k_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_q3_k(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+
 /* ------------------------------------------------------------------ Q5_K x Q8_K (ggml-common.h block_q5_K: f16 d, f16 dmin,
  * scales[12] as in Q4_K, qh[32], qs[128]; ggml-quants.c:1673-1698, ggml-cpu/quants.c:720-798; Encoding
  * examples/formats/ggml.py:100-110, 2-byte aligned).
@@ -172,7 +198,7 @@ int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *ta
 int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N);
 
 /* Row-sharded mul_mat: this process holds weight rows [n0, n0+N_local) of an (N,K) matrix and writes
- * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 8 Q4_K, 9 Q5_K, 10 Q6_K, 15 IQ2_XXS,
+ * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 6 Q2_K, 7 Q3_K, 8 Q4_K, 9 Q5_K, 10 Q6_K, 15 IQ2_XXS,
  * 20 TQ1_0 (the reference harness numbering).  mode: 0 decode (GEMV), 1 prefill (tensor cores).
  * flags bit 0: Xq already holds the quantized activations (X may be NULL). */
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,

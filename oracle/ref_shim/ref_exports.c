@@ -49,7 +49,7 @@ __attribute__((constructor)) static void weft_ref_init(void) {
 }
 
 /* format ids follow the reference harnesses (vec_dot_runtime.cpp:185-344) */
-enum { WEFT_Q4_0 = 1, WEFT_Q8_0 = 5, WEFT_Q4_K = 8, WEFT_Q5_K = 9, WEFT_Q6_K = 10, WEFT_IQ2_XXS = 15, WEFT_TQ1_0 = 20,
+enum { WEFT_Q4_0 = 1, WEFT_Q8_0 = 5, WEFT_Q2_K = 6, WEFT_Q3_K = 7, WEFT_Q4_K = 8, WEFT_Q5_K = 9, WEFT_Q6_K = 10, WEFT_IQ2_XXS = 15, WEFT_TQ1_0 = 20,
        WEFT_Q8_K = 100 };
 
 static enum ggml_type to_type(int fmt) {
@@ -57,6 +57,8 @@ static enum ggml_type to_type(int fmt) {
     case WEFT_Q4_0: return GGML_TYPE_Q4_0;
     case WEFT_Q8_0: return GGML_TYPE_Q8_0;
     case WEFT_Q4_K: return GGML_TYPE_Q4_K;
+    case WEFT_Q2_K: return GGML_TYPE_Q2_K;
+    case WEFT_Q3_K: return GGML_TYPE_Q3_K;
     case WEFT_Q5_K: return GGML_TYPE_Q5_K;
     case WEFT_Q6_K: return GGML_TYPE_Q6_K;
     case WEFT_IQ2_XXS: return GGML_TYPE_IQ2_XXS;
@@ -93,6 +95,8 @@ int weft_ref_dequantize(int fmt, const void *w, float *y, int64_t k) {
     case WEFT_Q4_0: dequantize_row_q4_0((const block_q4_0 *)w, y, k); return 0;
     case WEFT_Q8_0: dequantize_row_q8_0((const block_q8_0 *)w, y, k); return 0;
     case WEFT_Q4_K: dequantize_row_q4_K((const block_q4_K *)w, y, k); return 0;
+    case WEFT_Q2_K: dequantize_row_q2_K((const block_q2_K *)w, y, k); return 0;
+    case WEFT_Q3_K: dequantize_row_q3_K((const block_q3_K *)w, y, k); return 0;
     case WEFT_Q5_K: dequantize_row_q5_K((const block_q5_K *)w, y, k); return 0;
     case WEFT_Q6_K: dequantize_row_q6_K((const block_q6_K *)w, y, k); return 0;
     case WEFT_IQ2_XXS: dequantize_row_iq2_xxs((const block_iq2_xxs *)w, y, k); return 0;
@@ -107,6 +111,8 @@ int weft_ref_vec_dot(int fmt, int64_t k, float *s, const void *w, const void *x)
     case WEFT_Q4_0: ggml_vec_dot_q4_0_q8_0((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_Q8_0: ggml_vec_dot_q8_0_q8_0((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_Q4_K: ggml_vec_dot_q4_K_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
+    case WEFT_Q2_K: ggml_vec_dot_q2_K_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
+    case WEFT_Q3_K: ggml_vec_dot_q3_K_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_Q5_K: ggml_vec_dot_q5_K_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_Q6_K: ggml_vec_dot_q6_K_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_IQ2_XXS: ggml_vec_dot_iq2_xxs_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;

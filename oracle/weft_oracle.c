@@ -66,6 +66,8 @@ size_t wo_record_bytes(int fmt) {
     case WO_Q8_0: return 34;
     case WO_Q8_1: return 36;
     case WO_Q4_K: return 144;
+    case WO_Q2_K: return 84;
+    case WO_Q3_K: return 110;
     case WO_Q5_K: return 176;
     case WO_Q6_K: return 210;
     case WO_IQ2_XXS: return 66;
@@ -78,7 +80,7 @@ size_t wo_record_bytes(int fmt) {
 size_t wo_record_elements(int fmt) {
     switch (fmt) {
     case WO_Q4_0: case WO_Q8_0: case WO_Q8_1: return 32;
-    case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
+    case WO_Q2_K: case WO_Q3_K: case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
     default: return 0;
     }
 }
@@ -561,6 +563,8 @@ static void wo_dequantize_range(int64_t begin, int64_t end, void *p) {
         case WO_Q4_0: wo_dequantize_row_q4_0(wr, yr, c->k); break;
         case WO_Q8_0: wo_dequantize_row_q8_0(wr, yr, c->k); break;
         case WO_Q4_K: wo_dequantize_row_q4_K(wr, yr, c->k); break;
+        case WO_Q2_K: wo_dequantize_row_q2_K(wr, yr, c->k); break;
+        case WO_Q3_K: wo_dequantize_row_q3_K(wr, yr, c->k); break;
         case WO_Q5_K: wo_dequantize_row_q5_K(wr, yr, c->k); break;
         case WO_Q6_K: wo_dequantize_row_q6_K(wr, yr, c->k); break;
         case WO_IQ2_XXS: wo_dequantize_row_iq2_xxs(wr, c->grid, c->signs, yr, c->k); break;
@@ -636,6 +640,85 @@ float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
         const float dmin = wo_f16_to_f32(ld_u16(w + 2)) * xd;
         sumf -= dmin * sum_min;
     }
+    for (int l = 0; l < 8; ++l) sumf += lanes[l];
+    return sumf;
+}
+
+/* ---- Q2_K: 84 bytes per 256 weights = scales[16] (low nibble scale, high nibble min, one per 16 weights),
+ * qs[64] (2-bit weights), f16 d, f16 dmin  (ggml/src/ggml-common.h:288-298; examples/formats/ggml.py class Q2_K).
+ * Weight 128 n + 32 j + l is bits 2j, 2j+1 of qs[32 n + l]; its scale byte is scales[e / 16]. */
+static int q2k_value(const uint8_t *rec, int e) {
+    return (rec[16 + 32 * (e >> 7) + (e & 31)] >> (2 * ((e >> 5) & 3))) & 3;
+}
+
+/* ggml/src/ggml-quants.c:903-933; examples/kernels/dequantize/q2_k.py:8-17: (d*sc)*q - (dmin*m) */
+void wo_dequantize_row_q2_K(const uint8_t *w, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 84, y += 256) {
+        const float d = wo_f16_to_f32(ld_u16(w + 80)), dmin = wo_f16_to_f32(ld_u16(w + 82));
+        for (int g = 0; g < 16; ++g) {
+            const float dl = d * (w[g] & 0x0f), ml = dmin * (w[g] >> 4);
+            for (int l = 0; l < 16; ++l) y[16 * g + l] = dl * (int8_t)q2k_value(w, 16 * g + l) - ml;
+        }
+    }
+}
+
+/* ggml/src/ggml-cpu/quants.c:514-564; examples/kernels/vec_dot/q2_k_q8_k.py:8-25:
+ * sumf += (x.d * d) * isum - (x.d * dmin) * sum_g bsums[g] * min_g */
+float wo_vec_dot_q2_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
+    float sumf = 0;
+    for (int64_t b = 0; b < k / 256; ++b, w += 84, x += 292) {
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int summs = 0, isum = 0;
+        for (int g = 0; g < 16; ++g) summs += ld_i16(x + 260 + 2 * g) * (w[g] >> 4);
+        const float xd = ld_f32(x);
+        const float dall = xd * wo_f16_to_f32(ld_u16(w + 80)), dmin = xd * wo_f16_to_f32(ld_u16(w + 82));
+        for (int g = 0; g < 16; ++g) {
+            int part = 0;
+            for (int l = 0; l < 16; ++l) part += xq[16 * g + l] * q2k_value(w, 16 * g + l);
+            isum += (w[g] & 0x0f) * part;
+        }
+        sumf += dall * isum - dmin * summs;
+    }
+    return sumf;
+}
+
+/* ---- Q3_K: 110 bytes per 256 weights = hmask[32] (third bits), qs[64] (low two bits, laid out as Q2_K),
+ * scales[12] (sixteen 6-bit scales), f16 d  (ggml/src/ggml-common.h:305-311; examples/formats/ggml.py class Q3_K).
+ * Weight e = low two bits minus 4 unless bit e / 32 of hmask[e % 32] is set; scale e / 16, stored plus 32:
+ * low nibble from byte g % 8 (high nibble for g >= 8), bits 4-5 from bits 2 (g / 4) of byte 8 + g % 4. */
+static int q3k_value(const uint8_t *rec, int e) {
+    const int low = (rec[32 + 32 * (e >> 7) + (e & 31)] >> (2 * ((e >> 5) & 3))) & 3;
+    return low - (((rec[e & 31] >> (e >> 5)) & 1) ? 0 : 4);
+}
+static int q3k_scale(const uint8_t *s12, int g) {
+    const int low = g < 8 ? (s12[g] & 0x0f) : (s12[g - 8] >> 4);
+    const int high = (s12[8 + (g & 3)] >> (2 * (g >> 2))) & 3;
+    return (int8_t)(low | (high << 4)) - 32;
+}
+
+/* ggml/src/ggml-quants.c:1247-1294; examples/kernels/dequantize/q3_k.py:8-17: (d * scale) * q */
+void wo_dequantize_row_q3_K(const uint8_t *w, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 110, y += 256) {
+        const float d = wo_f16_to_f32(ld_u16(w + 108));
+        for (int g = 0; g < 16; ++g) {
+            const float dl = d * q3k_scale(w + 96, g);
+            for (int l = 0; l < 16; ++l) y[16 * g + l] = dl * q3k_value(w, 16 * g + l);
+        }
+    }
+}
+
+/* ggml/src/ggml-cpu/quants.c:566-643; examples/kernels/vec_dot/q3_k_q8_k.py:8-43: eight int32 lane sums per
+ * block, float lanes, lanes added at the end */
+float wo_vec_dot_q3_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
+    float lanes[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int64_t b = 0; b < k / 256; ++b, w += 110, x += 292) {
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int32_t lane_i[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int e = 0; e < 256; ++e) lane_i[e & 7] += q3k_scale(w + 96, e >> 4) * (int16_t)(xq[e] * (int8_t)q3k_value(w, e));
+        const float d = wo_f16_to_f32(ld_u16(w + 108)) * ld_f32(x);
+        for (int l = 0; l < 8; ++l) lanes[l] += d * lane_i[l];
+    }
+    float sumf = 0;
     for (int l = 0; l < 8; ++l) sumf += lanes[l];
     return sumf;
 }
@@ -774,6 +857,8 @@ int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, 
     case WO_Q4_0: *out = wo_vec_dot_q4_0_q8_0(w, x, k); return 0;
     case WO_Q8_0: *out = wo_vec_dot_q8_0_q8_0(w, x, k); return 0;
     case WO_Q4_K: *out = wo_vec_dot_q4_K_q8_K(w, x, k); return 0;
+    case WO_Q2_K: *out = wo_vec_dot_q2_K_q8_K(w, x, k); return 0;
+    case WO_Q3_K: *out = wo_vec_dot_q3_K_q8_K(w, x, k); return 0;
     case WO_Q5_K: *out = wo_vec_dot_q5_K_q8_K(w, x, k); return 0;
     case WO_Q6_K: *out = wo_vec_dot_q6_K_q8_K(w, x, k); return 0;
     case WO_IQ2_XXS: *out = wo_vec_dot_iq2_xxs_q8_K(w, x, grid, signs, k); return 0;

@@ -29,6 +29,8 @@ enum wo_format {
     WO_Q4_0 = 1,
     WO_Q8_0 = 5,
     WO_Q4_K = 8,
+    WO_Q2_K = 6,
+    WO_Q3_K = 7,
     WO_Q5_K = 9,
     WO_Q6_K = 10,
     WO_IQ2_XXS = 15,
@@ -64,6 +66,8 @@ int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrow
 void wo_dequantize_row_q4_0(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q8_0(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q4_K(const uint8_t *w, float *y, int64_t k);
+void wo_dequantize_row_q2_K(const uint8_t *w, float *y, int64_t k);
+void wo_dequantize_row_q3_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q5_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q6_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_iq2_xxs(const uint8_t *w, const int8_t *grid, const int8_t *signs, float *y, int64_t k);
@@ -77,6 +81,8 @@ float wo_vec_dot_q8_0_q8_0(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_iq2_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k);
 float wo_vec_dot_tq1_0_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
+float wo_vec_dot_q2_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
+float wo_vec_dot_q3_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_q5_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_q6_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs,

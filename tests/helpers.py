@@ -38,6 +38,15 @@ def random_q6_k(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     return rec.reshape(n, nb * 210)
 
 
+def random_k_records(rng: np.random.Generator, n: int, k: int, record_bytes: int, scales_at: int, scales: int) -> np.ndarray:
+    """Random but valid K-family records: every bit pattern is legal once the f16 super-scales are small finite numbers."""
+    nb = k // 256
+    rec = rng.integers(0, 256, size=(n, nb, record_bytes), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal((n, nb, scales))) * 1e-3 + 1e-4).astype(np.float16)
+    rec[:, :, scales_at:scales_at + 2 * scales] = d.view(np.uint8).reshape(n, nb, 2 * scales)
+    return rec.reshape(n, nb * record_bytes)
+
+
 def random_q5_k(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     """Random but valid Q5_K records: every scale / min / bit pattern is legal; d and dmin are small f16."""
     nb = k // 256
@@ -50,7 +59,7 @@ def random_q5_k(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
 def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     """Seeded weights of the benchmark distributions, quantized: N(0, 0.02) (scale * {-1,0,+1} for TQ1_0).
 
-    IQ2_XXS, Q5_K and Q6_K go through the compiled reference quantizer when it is present and fall back to
+    IQ2_XXS, Q2_K, Q3_K, Q5_K and Q6_K go through the compiled reference quantizer when it is present and fall back to
     random valid records otherwise (the port has no quantizer for them)."""
     if fmt == o.TQ1_0:
         src = (rng.integers(-1, 2, size=(n, k)) * np.float32(0.02)).astype(np.float32)
@@ -59,9 +68,13 @@ def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
         if o.ref_available() and n * k <= 1 << 22:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
         return random_iq2_xxs(rng, n, k)
-    if fmt in (o.Q5_K, o.Q6_K):
+    if fmt in (o.Q2_K, o.Q3_K, o.Q5_K, o.Q6_K):
         if o.ref_available() and n * k <= 1 << 22:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        if fmt == o.Q2_K:
+            return random_k_records(rng, n, k, 84, 80, 2)
+        if fmt == o.Q3_K:
+            return random_k_records(rng, n, k, 110, 108, 1)
         return random_q5_k(rng, n, k) if fmt == o.Q5_K else random_q6_k(rng, n, k)
     return o.quantize(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
 

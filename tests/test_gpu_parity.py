@@ -15,7 +15,7 @@ from helpers import TQ1_POWERS, activations, random_iq2_xxs, reference_tolerance
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k"]
+FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k"]
 REL_L2_BOUND = 1e-5
 
 

@@ -9,7 +9,7 @@ from __future__ import annotations
 import numpy as np
 import pytest
 
-FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k"]
+FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k"]
 K = 1024
 
 
@@ -122,7 +122,7 @@ def test_live_against_compiled_reference(oracle, golden, name):
     if name == "tq1_0":
         src = (rng.integers(-1, 2, size=(n, k)) * np.float32(0.031)).astype(np.float32)
     w = oracle.ref_quantize_weights(fmt, src)
-    if name not in ("iq2_xxs", "q6_k", "q5_k"):          # the port has no quantizer for these weight formats
+    if name not in ("iq2_xxs", "q6_k", "q5_k", "q2_k", "q3_k"):          # the port has no quantizer for these weight formats
         assert np.array_equal(oracle.quantize(fmt, src), w)
     grid, signs = oracle.ref_iq2xxs_tables()
     assert np.array_equal(grid, golden["iq2xxs_grid"])

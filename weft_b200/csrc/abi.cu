@@ -358,6 +358,8 @@ int weft_b200_weights_release(const void *host) {
 VEC_DOT(quantized_vec_dot_q4_0_q8_0, F_Q4_0, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_q8_0_q8_0, F_Q8_0, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_q4_k_q8_k, F_Q4_K, NO_TABLES, nullptr, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_q2_k_q8_k, F_Q2_K, NO_TABLES, nullptr, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_q3_k_q8_k, F_Q3_K, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_q5_k_q8_k, F_Q5_K, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_q6_k_q8_k, F_Q6_K, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_iq2_xxs_q8_k, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
@@ -370,6 +372,8 @@ VEC_DOT(quantized_vec_dot_tq1_0_q8_k, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powe
 DEQUANT(row_dequantize_q4_0, F_Q4_0, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_q8_0, F_Q8_0, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_q4_k, F_Q4_K, NO_TABLES, nullptr, nullptr, nullptr)
+DEQUANT(row_dequantize_q2_k, F_Q2_K, NO_TABLES, nullptr, nullptr, nullptr)
+DEQUANT(row_dequantize_q3_k, F_Q3_K, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_q5_k, F_Q5_K, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_q6_k, F_Q6_K, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_iq2_xxs, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
@@ -391,6 +395,8 @@ int q8_K_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K) { return 
 MUL_MAT(production_mul_mat_q4_0_decode, F_Q4_0, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q8_0_decode, F_Q8_0, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q4_k_decode, F_Q4_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q2_k_decode, F_Q2_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q3_k_decode, F_Q3_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q5_k_decode, F_Q5_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q6_k_decode, F_Q6_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_iq2_xxs_decode, F_IQ2_XXS, 0, IQ_TABLES, grid, signs, nullptr)
@@ -398,6 +404,8 @@ MUL_MAT(production_mul_mat_tq1_0_decode, F_TQ1_0, 0, TQ_TABLES, nullptr, nullptr
 MUL_MAT(production_mul_mat_q4_0, F_Q4_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q8_0, F_Q8_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q4_k_staged, F_Q4_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q2_k, F_Q2_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q3_k, F_Q3_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q5_k, F_Q5_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q6_k, F_Q6_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_tq1_0, F_TQ1_0, 1, TQ_TABLES, nullptr, nullptr, powers)
@@ -433,7 +441,7 @@ int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags) {
-    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q4_K && format != F_Q5_K && format != F_Q6_K && format != F_IQ2_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
+    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K && format != F_Q6_K && format != F_IQ2_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
         return fail("unknown weight format id %d", format);
     if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
     return do_mul_mat(format, mode, W_local, X, Xq, grid, signs, powers, Y_columns, N_local, K, M, ldy, flags, false);

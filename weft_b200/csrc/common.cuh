@@ -12,11 +12,11 @@
 
 namespace weft {
 
-enum Format : int { F_Q4_0 = 1, F_Q8_0 = 5, F_Q4_K = 8, F_Q5_K = 9, F_Q6_K = 10, F_IQ2_XXS = 15, F_TQ1_0 = 20, F_Q8_K = 100, F_Q8_1 = 101,
+enum Format : int { F_Q4_0 = 1, F_Q8_0 = 5, F_Q2_K = 6, F_Q3_K = 7, F_Q4_K = 8, F_Q5_K = 9, F_Q6_K = 10, F_IQ2_XXS = 15, F_TQ1_0 = 20, F_Q8_K = 100, F_Q8_1 = 101,
                     F_Q4_K_I16 = 1008 /* Q4_K records, 16 rows byte-interleaved (derived Encoding Q4K_I[16]) */ };
 
 __host__ __device__ constexpr int record_bytes(int fmt) {
-    return fmt == F_Q4_0 ? 18 : fmt == F_Q8_0 ? 34 : (fmt == F_Q4_K || fmt == F_Q4_K_I16) ? 144 : fmt == F_Q5_K ? 176 : fmt == F_Q6_K ? 210 : fmt == F_IQ2_XXS ? 66
+    return fmt == F_Q4_0 ? 18 : fmt == F_Q8_0 ? 34 : (fmt == F_Q4_K || fmt == F_Q4_K_I16) ? 144 : fmt == F_Q2_K ? 84 : fmt == F_Q3_K ? 110 : fmt == F_Q5_K ? 176 : fmt == F_Q6_K ? 210 : fmt == F_IQ2_XXS ? 66
          : fmt == F_TQ1_0 ? 54 : fmt == F_Q8_K ? 292 : fmt == F_Q8_1 ? 36 : 0;
 }
 __host__ __device__ constexpr int record_elements(int fmt) {
@@ -124,6 +124,15 @@ __device__ __forceinline__ Q4KScales q4k_unpack_scales(uint32_t s0, uint32_t s1,
     return r;
 }
 __device__ __forceinline__ uint32_t byte_of(uint32_t v, int i) { return (v >> (8 * i)) & 0xffu; }
+
+// The sixteen 6-bit scales of a Q3_K record (stored plus 32) as four packed byte vectors, scale g in byte g % 4
+// of word g / 4 (ggml-quants.c:1264-1269; same unpack as ggml-cpu/quants.c:620-625).
+__device__ __forceinline__ void q3k_unpack_scales(uint32_t s0, uint32_t s1, uint32_t s2, uint32_t (&out)[4]) {
+    out[0] = (s0 & 0x0f0f0f0fu) | ((s2 & 0x03030303u) << 4);
+    out[1] = (s1 & 0x0f0f0f0fu) | (((s2 >> 2) & 0x03030303u) << 4);
+    out[2] = ((s0 >> 4) & 0x0f0f0f0fu) | (((s2 >> 4) & 0x03030303u) << 4);
+    out[3] = ((s1 >> 4) & 0x0f0f0f0fu) | (((s2 >> 6) & 0x03030303u) << 4);
+}
 
 // One base-3 digit (0 = most significant) of a packed TQ1_0 byte, as -1/0/+1
 // (ggml-quants.c:2369-2371; examples/functions/quantization.py:49-64). `power` is powers[digit]

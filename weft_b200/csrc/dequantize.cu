@@ -11,6 +11,8 @@
 //   Q4_K       (d*sc)*q - (dmin*m)               quantization.py:14-17,                   ggml-quants.c:1471-1493
 //   IQ2_XXS    (d*(0.5+s)*0.25) * (grid*sign)    examples/kernels/dequantize/iq2_xxs.py:9-53, ggml-quants.c:2416-2440
 //   TQ1_0      f32(trit-1) * d                   examples/kernels/dequantize/tq1_0.py:9-46,   ggml-quants.c:2356-2393
+//   Q2_K       (d*sc)*q2 - (dmin*m)              examples/kernels/dequantize/q2_k.py:8-17,    ggml-quants.c:903-933
+//   Q3_K       (d*(scale-32)) * (q3 - 4)         examples/kernels/dequantize/q3_k.py:8-17,    ggml-quants.c:1247-1294
 //   Q5_K       (d*sc)*q5 - (dmin*m)              examples/kernels/dequantize/q5_k.py:9-15,    ggml-quants.c:1673-1698
 //   Q6_K       (d*scale) * (q6 - 32)             examples/kernels/dequantize/q6_k.py:8-14,    ggml-quants.c:1881-1910
 #include "common.cuh"
@@ -86,6 +88,45 @@ __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q5_k_kernel(const uint8
         float *out = y + u * 256 + 64 * j + 4 * t;
         st4(out, lo[0], lo[1], lo[2], lo[3]);
         st4(out + 32, hi[0], hi[1], hi[2], hi[3]);
+    }
+}
+
+// ---- Q2_K (84 bytes: scales[16], qs[64], f16 d, f16 dmin) and Q3_K (110 bytes: hmask[32], qs[64], scales[12], f16 d):
+// both keep the low two bits of weight 128 n + 32 j + l in bits 2j, 2j+1 of qs[32 n + l].  lane = (n, byte pair):
+// a lane writes two consecutive floats in each of the four bit planes; sixteen lanes cover 128 contiguous bytes.
+template <int FMT>
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_q23_k_kernel(const uint8_t *__restrict__ w, float *__restrict__ y, long long units) {
+    constexpr int RB = FMT == F_Q2_K ? 84 : 110, QS = FMT == F_Q2_K ? 16 : 32;
+    const int lane = threadIdx.x & 31;
+    const int n = lane >> 4, li = lane & 15;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * RB;
+        const uint32_t q = ld_u16(rec + QS + 32 * n + 2 * li);
+        float *out = y + u * 256 + 128 * n + 2 * li;
+        if (FMT == F_Q2_K) {
+            const float d = half_bits_to_float(ld_u16(rec + 80)), dmin = half_bits_to_float(ld_u16(rec + 82));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t sc = rec[8 * n + 2 * j + (li >> 3)];
+                const float dl = __fmul_rn(d, (float)(sc & 15u)), ml = __fmul_rn(dmin, (float)(sc >> 4));
+                const float v0 = __fsub_rn(__fmul_rn(dl, (float)((q >> (2 * j)) & 3u)), ml);
+                const float v1 = __fsub_rn(__fmul_rn(dl, (float)((q >> (8 + 2 * j)) & 3u)), ml);
+                __stcs(reinterpret_cast<float2 *>(out + 32 * j), make_float2(v0, v1));
+            }
+        } else {
+            const float d = half_bits_to_float(ld_u16(rec + 108));
+            const uint32_t hm = ld_u16(rec + 2 * li) >> (4 * n);
+            uint32_t sc4[4];
+            q3k_unpack_scales(ld_u32_a2(rec + 96), ld_u32_a2(rec + 100), ld_u32_a2(rec + 104), sc4);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int g = 8 * n + 2 * j + (li >> 3);
+                const float dl = __fmul_rn(d, (float)((int)byte_of(sc4[g >> 2], g & 3) - 32));
+                const int q0 = (int)((q >> (2 * j)) & 3u) - (((hm >> j) & 1u) ? 0 : 4);
+                const int q1 = (int)((q >> (8 + 2 * j)) & 3u) - (((hm >> (8 + j)) & 1u) ? 0 : 4);
+                __stcs(reinterpret_cast<float2 *>(out + 32 * j), make_float2(__fmul_rn(dl, (float)q0), __fmul_rn(dl, (float)q1)));
+            }
+        }
     }
 }
 
@@ -256,6 +297,22 @@ __global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ 
             const float d1 = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)sc);
             const float m1 = __fmul_rn(half_bits_to_float(ld_u16(rec + 2)), (float)mn);
             v = __fsub_rn(__fmul_rn(d1, (float)q), m1);
+        } else if (fmt == F_Q2_K) {
+            const uint8_t *rec = w + (i / 256) * 84;
+            const int e = (int)(i % 256);
+            const uint32_t sc = rec[e >> 4];
+            const uint32_t q = (rec[16 + 32 * (e >> 7) + (e & 31)] >> (2 * ((e >> 5) & 3))) & 3u;
+            const float dl = __fmul_rn(half_bits_to_float(ld_u16(rec + 80)), (float)(sc & 15u));
+            const float ml = __fmul_rn(half_bits_to_float(ld_u16(rec + 82)), (float)(sc >> 4));
+            v = __fsub_rn(__fmul_rn(dl, (float)q), ml);
+        } else if (fmt == F_Q3_K) {
+            const uint8_t *rec = w + (i / 256) * 110;
+            const int e = (int)(i % 256), g = e >> 4;
+            uint32_t sc4[4];
+            q3k_unpack_scales(ld_u32_a2(rec + 96), ld_u32_a2(rec + 100), ld_u32_a2(rec + 104), sc4);
+            const int q = (int)((rec[32 + 32 * (e >> 7) + (e & 31)] >> (2 * ((e >> 5) & 3))) & 3u) - (((rec[e & 31] >> (e >> 5)) & 1u) ? 0 : 4);
+            const float dl = __fmul_rn(half_bits_to_float(ld_u16(rec + 108)), (float)((int)byte_of(sc4[g >> 2], g & 3) - 32));
+            v = __fmul_rn(dl, (float)q);
         } else if (fmt == F_Q5_K) {
             const uint8_t *rec = w + (i / 256) * 176;
             const int e = (int)(i % 256), g = e >> 5, l = e & 31;
@@ -315,6 +372,16 @@ cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const 
         const long long units = elements / 256;
         if (a4) dequant_q4_k_kernel<true><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
         else dequant_q4_k_kernel<false><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
+        break;
+    }
+    case F_Q2_K: {
+        const long long units = elements / 256;
+        dequant_q23_k_kernel<F_Q2_K><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
+        break;
+    }
+    case F_Q3_K: {
+        const long long units = elements / 256;
+        dequant_q23_k_kernel<F_Q3_K><<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, y, units);
         break;
     }
     case F_Q5_K: {

@@ -1,7 +1,7 @@
 // Decode path: Y[m, n] = quantized_vec_dot(W[n], Xq[m]) for every weight row -- the loop the
 // reference's production_mul_mat_*_decode kernels spell out (examples/kernels/mul_mat/q4_k_decode.py:17-20)
-// around the block dots of examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q4_k_q8_k,q5_k_q8_k,q6_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py
-// (GGML: ggml-cpu/quants.c:174-208, 400-428, 645-718, 720-798, 800-853, 855-895, 430-480).
+// around the block dots of examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q2_k_q8_k,q3_k_q8_k,q4_k_q8_k,q5_k_q8_k,q6_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py
+// (GGML: ggml-cpu/quants.c:174-208, 400-428, 514-564, 566-643, 645-718, 720-798, 800-853, 855-895, 430-480).
 //
 // The GEMV is HBM-bound: each weight byte is read exactly once.  One persistent CTA per SM owns a
 // contiguous range of weight rows.  Every warp streams whole rows from HBM into its own shared-memory
@@ -16,7 +16,7 @@
 //   Q4_0  acc += (d_w*d_x) * f32(sum)              Q8_0  acc += f32(sum) * (d_w*d_x)
 //   Q4_K  acc += x.d * (d*f32(isum) - dmin*f32(msum))
 //   IQ2_XXS acc += (d_w*x.d) * f32(bsum), result *= 0.125     TQ1_0 acc += f32(sum) * (d_w*x.d)
-//   Q6_K  acc += (d_w*x.d) * f32(isum)                        Q5_K  as Q4_K
+//   Q6_K  acc += (d_w*x.d) * f32(isum)                        Q5_K, Q2_K  as Q4_K      Q3_K  as Q6_K
 #include "gemv_units.cuh"
 
 #include <climits>
@@ -169,6 +169,8 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
             if (FMT == F_Q4_K) dot_q4_k<RL>(wp, xu, xa, acc);
             else if (FMT == F_Q4_0) dot_q4_0<RL>(wp, xu, xa, acc);
             else if (FMT == F_Q8_0) dot_q8_0<RL>(wp, xu, xa, acc);
+            else if (FMT == F_Q2_K) dot_q2_k<RL>(wp, xu, xa, acc);
+            else if (FMT == F_Q3_K) dot_q3_k<RL>(wp, xu, xa, acc);
             else if (FMT == F_Q5_K) dot_q5_k<RL>(wp, xu, xa, acc);
             else if (FMT == F_Q6_K) dot_q6_k<RL>(wp, xu, xa, acc);
             else if (FMT == F_IQ2_XXS) dot_iq2_xxs<RL>(wp, xu, xa, s_tab0, s_tab1, acc);
@@ -305,6 +307,8 @@ cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
     case F_Q4_0: return launch_fmt<F_Q4_0>(a, sm_count, stream);
     case F_Q8_0: return launch_fmt<F_Q8_0>(a, sm_count, stream);
     case F_Q4_K: return launch_fmt<F_Q4_K>(a, sm_count, stream);
+    case F_Q2_K: return launch_fmt<F_Q2_K>(a, sm_count, stream);
+    case F_Q3_K: return launch_fmt<F_Q3_K>(a, sm_count, stream);
     case F_Q5_K: return launch_fmt<F_Q5_K>(a, sm_count, stream);
     case F_Q6_K: return launch_fmt<F_Q6_K>(a, sm_count, stream);
     case F_IQ2_XXS: return launch_fmt<F_IQ2_XXS>(a, sm_count, stream);

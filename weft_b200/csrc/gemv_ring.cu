@@ -1,5 +1,5 @@
-// Decode GEMV for Q4_0, Q8_0, Q5_K, Q6_K, IQ2_XXS and TQ1_0 weights whose rows are whole 16-byte multiples:
-// Y[m, n] = quantized_vec_dot(W[n], Xq[m])  (examples/kernels/mul_mat/{q4_0,q8_0,q5_k,q6_k,iq2_xxs,tq1_0}_decode.py).
+// Decode GEMV for Q4_0, Q8_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ2_XXS and TQ1_0 weights whose rows are whole 16-byte multiples:
+// Y[m, n] = quantized_vec_dot(W[n], Xq[m])  (examples/kernels/mul_mat/{q4_0,q8_0,q2_k,q3_k,q5_k,q6_k,iq2_xxs,tq1_0}_decode.py).
 //
 // Same streaming scheme as the Q4_K kernel: one persistent CTA per SM, a producer warp that fills a
 // CTA-wide shared-memory ring with bulk asynchronous copies of about 18 KB (copies of a few KB each
@@ -155,6 +155,8 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
             const uint8_t *xu = s_xq + u * XQ_PITCH, *xa = s_aux + u * XAUX_BYTES;
             if (FMT == F_Q4_0) dot_q4_0<2>(wp, xu, xa, acc);
             else if (FMT == F_Q8_0) dot_q8_0<2>(wp, xu, xa, acc);
+            else if (FMT == F_Q2_K) dot_q2_k<2>(wp, xu, xa, acc);
+            else if (FMT == F_Q3_K) dot_q3_k<2>(wp, xu, xa, acc);
             else if (FMT == F_Q5_K) dot_q5_k<2>(wp, xu, xa, acc);
             else if (FMT == F_Q6_K) dot_q6_k<2>(wp, xu, xa, acc);
             else if (FMT == F_IQ2_XXS) { if (own_tables) dot_iq2_xxs_fast<2>(wp, xu, xa, s_sel, acc); else dot_iq2_xxs<2>(wp, xu, xa, s_grid, s_neg, acc); }
@@ -236,7 +238,7 @@ cudaError_t launch_fmt(const RingParams &p, bool qx, dim3 grid, int threads, siz
 }  // namespace
 
 bool gemv_ring_supported(const GemvArgs &a) {
-    if (a.fmt != F_Q4_0 && a.fmt != F_Q8_0 && a.fmt != F_Q5_K && a.fmt != F_Q6_K && a.fmt != F_IQ2_XXS && a.fmt != F_TQ1_0) return false;
+    if (a.fmt != F_Q4_0 && a.fmt != F_Q8_0 && a.fmt != F_Q2_K && a.fmt != F_Q3_K && a.fmt != F_Q5_K && a.fmt != F_Q6_K && a.fmt != F_IQ2_XXS && a.fmt != F_TQ1_0) return false;
     return a.k % 256 == 0 && a.k > 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0 && a.n < (1LL << 30) &&
            plan_ring(a.fmt, a.k / 256).ok;
 }
@@ -263,6 +265,8 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     switch (a.fmt) {
     case F_Q4_0: return launch_fmt<F_Q4_0>(p, qx, grid, threads, plan.smem, stream);
     case F_Q8_0: return launch_fmt<F_Q8_0>(p, qx, grid, threads, plan.smem, stream);
+    case F_Q2_K: return launch_fmt<F_Q2_K>(p, qx, grid, threads, plan.smem, stream);
+    case F_Q3_K: return launch_fmt<F_Q3_K>(p, qx, grid, threads, plan.smem, stream);
     case F_Q5_K: return launch_fmt<F_Q5_K>(p, qx, grid, threads, plan.smem, stream);
     case F_Q6_K: return launch_fmt<F_Q6_K>(p, qx, grid, threads, plan.smem, stream);
     case F_IQ2_XXS: return launch_fmt<F_IQ2_XXS>(p, qx, grid, threads, plan.smem, stream);

@@ -1,8 +1,8 @@
 // Shared pieces of the decode GEMV kernels: the per-format dot product of one 256-element weight unit
 // against one staged activation unit, and the staging of activation records (or of fp32 activations,
 // quantized on the way) into shared memory.
-// (examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q4_k_q8_k,q5_k_q8_k,q6_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py;
-//  GGML ggml-cpu/quants.c:174-208, 400-428, 645-718, 720-798, 800-853, 855-895, 430-480.)
+// (examples/kernels/vec_dot/{q4_0_q8_0,q8_0_q8_0,q2_k_q8_k,q3_k_q8_k,q4_k_q8_k,q5_k_q8_k,q6_k_q8_k,iq2_xxs_q8_k,tq1_0_q8_k}.py;
+//  GGML ggml-cpu/quants.c:174-208, 400-428, 514-564, 566-643, 645-718, 720-798, 800-853, 855-895, 430-480.)
 #pragma once
 
 #include "quantize.cuh"
@@ -11,7 +11,9 @@
 namespace weft {
 
 constexpr int XQ_PITCH = 272;   // 256 code bytes + 16: consecutive units start on different bank groups
-constexpr int XAUX_BYTES = 80;  // per unit: Q8_K {f32 d, i32 total, -, -, i32 pair_sums[8], i16 sums16[16]}; Q8_0 {f32 d[8], i32 sums[8]}
+// per unit: Q8_K {f32 d, i32 total, -, -, i32 pair_sums[8] (of the record's bsums), i16 sums16[16] (of the codes),
+// i16 bsums[16] (as stored)}; Q8_0 {f32 d[8], i32 sums[8]}
+constexpr int XAUX_BYTES = 112;
 
 template <int FMT> struct Unit { static constexpr int BYTES = unit_bytes(FMT); };
 
@@ -64,6 +66,86 @@ __device__ __forceinline__ void dot_q4_k(const uint8_t *const (&wp)[RL], const u
                  + p1.z * (int)byte_of(sc[r].mn_hi, 2) + p1.w * (int)byte_of(sc[r].mn_hi, 3);
         acc[r] += xd_ * (d[r] * (float)isum[r] - dmin[r] * (float)msum);
     }
+}
+
+// One Q2_K record (84 bytes, 2-byte aligned): scales[16] (low nibble scale, high nibble min), qs[64], f16 d, f16 dmin.
+// Weight 128 n + 32 j + l is bits 2j, 2j+1 of qs[32 n + l]; the min term uses the activation record's bsums as stored.
+template <int RL>
+__device__ __forceinline__ void dot_q2_k(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    const uint4 b0 = *reinterpret_cast<const uint4 *>(xaux + 80), b1 = *reinterpret_cast<const uint4 *>(xaux + 96);
+    const uint32_t bs[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    uint32_t wv[RL][21];
+    int isum[RL], msum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        ld_words_a2<21>(wp[r], wv[r]);
+        isum[r] = 0; msum[r] = 0;
+#pragma unroll
+        for (int g = 0; g < 16; ++g)
+            msum[r] += (int)(int16_t)(bs[g >> 1] >> (16 * (g & 1))) * (int)(byte_of(wv[r][g >> 2], g & 3) >> 4);
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const uint4 xv = *reinterpret_cast<const uint4 *>(xq + 128 * n + 32 * j + 16 * c);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                const int g = 8 * n + 2 * j + c;
+#pragma unroll
+                for (int r = 0; r < RL; ++r) {
+                    int dp = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) dp = dp4a_us((wv[r][4 + 8 * n + 4 * c + i] >> (2 * j)) & 0x03030303u, xw[i], dp);
+                    isum[r] += (int)(byte_of(wv[r][g >> 2], g & 3) & 15u) * dp;
+                }
+            }
+#pragma unroll
+    for (int r = 0; r < RL; ++r)
+        acc[r] += xd_ * (half_bits_to_float(wv[r][20]) * (float)isum[r] - half_bits_to_float(wv[r][20] >> 16) * (float)msum[r]);
+}
+
+// One Q3_K record (110 bytes, 2-byte aligned): hmask[32], qs[64] (as Q2_K), scales[12], f16 d.  Weight e is its
+// low two bits plus 4 * (bit e / 32 of hmask[e % 32]) minus 4: sum((u - 4) x) = sum(u x) - 4 * (sum of the 16 codes).
+template <int RL>
+__device__ __forceinline__ void dot_q3_k(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    const uint4 s0 = *reinterpret_cast<const uint4 *>(xaux + 48), s1 = *reinterpret_cast<const uint4 *>(xaux + 64);
+    const uint32_t s16[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    uint32_t wv[RL][27], sc4[RL][4];
+    int isum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        ld_words_a2<27>(wp[r], wv[r]);
+        q3k_unpack_scales(wv[r][24], wv[r][25], wv[r][26], sc4[r]);
+        isum[r] = 0;
+    }
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const uint4 xv = *reinterpret_cast<const uint4 *>(xq + 128 * n + 32 * j + 16 * c);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                const int g = 8 * n + 2 * j + c, bit = 4 * n + j;
+                const int xs = (int)(int16_t)(s16[g >> 1] >> (16 * (g & 1)));
+#pragma unroll
+                for (int r = 0; r < RL; ++r) {
+                    int dp = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t hm = wv[r][4 * c + i];
+                        const uint32_t third = bit < 2 ? hm << (2 - bit) : hm >> (bit - 2);   // mask bit -> bit 2 of each byte
+                        dp = dp4a_us(((wv[r][8 + 8 * n + 4 * c + i] >> (2 * j)) & 0x03030303u) | (third & 0x04040404u), xw[i], dp);
+                    }
+                    isum[r] += ((int)byte_of(sc4[r][g >> 2], g & 3) - 32) * (dp - 4 * xs);
+                }
+            }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r] + 108)) * xd_) * (float)isum[r];
 }
 
 // One Q5_K record (176 bytes, 16-byte aligned in a staged row): the Q4_K header, qh[32] at +16, qs[128] at +48.
@@ -417,6 +499,7 @@ __device__ inline void stage_q8_k(const uint8_t *xq, int nb, uint8_t *s_q, uint8
         const uint8_t *rec = xq + (size_t)u * 292;
         int *aux = reinterpret_cast<int *>(s_aux + u * XAUX_BYTES);
         aux[0] = *reinterpret_cast<const int *>(rec);
+        for (int g = 0; g < 8; ++g) aux[20 + g] = *reinterpret_cast<const int *>(rec + 260 + 4 * g);   // bsums as stored
         int total = 0;
         for (int g = 0; g < 8; ++g) {
             const uint32_t pr = *reinterpret_cast<const uint32_t *>(rec + 260 + 4 * g);
@@ -462,7 +545,10 @@ __device__ inline void quantize_stage_q8_k(const float *x, int nb, uint8_t *s_q,
         for (int o = 4; o < 32; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
         int *aux = reinterpret_cast<int *>(s_aux + u * XAUX_BYTES);
         if ((lane & 3) == 0) aux[4 + (lane >> 2)] = s32;
-        if ((lane & 1) == 0) *reinterpret_cast<int16_t *>(s_aux + u * XAUX_BYTES + 48 + lane) = (int16_t)sum16;
+        if ((lane & 1) == 0) {
+            *reinterpret_cast<int16_t *>(s_aux + u * XAUX_BYTES + 48 + lane) = (int16_t)sum16;
+            *reinterpret_cast<int16_t *>(s_aux + u * XAUX_BYTES + 80 + lane) = (int16_t)sum16;
+        }
         if (lane == 0) { aux[0] = __float_as_int(d); aux[1] = total; }
         if (out) store_q8_k(out + (size_t)u * 292, lane, q0, q1, sum16, d);
     }

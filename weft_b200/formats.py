@@ -1,7 +1,7 @@
 """The GGML record layouts on the quantized matrix path, declared with ``@weft.encoding``.
 
 These are the hot-path encodings of the reference's examples/formats/ggml.py (Q4_0 :16-22,
-Q8_0 :56-62, Q4_K :88-97, Q5_K :100-110, Q6_K :113-120, IQ2_XXS :164-170, I8X8 :173-178, TQ1_0 :231-238, Q8_K :276-283), byte for
+Q8_0 :56-62, Q2_K :64-72, Q3_K :75-84, Q4_K :88-97, Q5_K :100-110, Q6_K :113-120, IQ2_XXS :164-170, I8X8 :173-178, TQ1_0 :231-238, Q8_K :276-283), byte for
 byte the block structs of ggml-common.h:184-189,241-246,266-271,317-328,361-366,371-375.  A kernel
 file may use these or the reference's own declarations: ``weft.compile`` identifies an Encoding by
 its name and checks the record geometry, not the declaring module.
@@ -30,6 +30,29 @@ class Q8_0:                      # 34 bytes / 32 elements
     elements = 32
     d: wl.f16
     q: wl.i8[32]
+
+
+@encoding
+class Q2_K:                      # 84 bytes / 256 elements
+    layout = _LE
+    alignment = 2
+    elements = 256
+    scales: wl.u8[16]            # @0: low nibble scale, high nibble min, one per 16 weights
+    q: wl.u2[256] @ wl.grouped(elements=128) @ wl.bit_layers(elements=32, order=wl.lo_first)   # @16
+    d: wl.f16                    # @80
+    dmin: wl.f16                 # @82
+
+
+@encoding
+class Q3_K:                      # 110 bytes / 256 elements
+    layout = _LE
+    alignment = 2
+    elements = 256
+    hmask: wl.u1[256] @ wl.grouped(elements=256) @ wl.bit_layers(elements=32, order=wl.lo_first)   # @0
+    q: wl.u2[256] @ wl.grouped(elements=128) @ wl.bit_layers(elements=32, order=wl.lo_first)       # @32
+    scale_low: wl.u4[16] @ wl.grouped(elements=16) @ wl.bit_layers(elements=8, order=wl.lo_first)  # @96
+    scale_high: wl.u2[16] @ wl.grouped(elements=16) @ wl.bit_layers(elements=4, order=wl.lo_first) # @104
+    d: wl.f16                    # @108
 
 
 @encoding
@@ -124,11 +147,11 @@ def Q4K_I(W: wl.View[Q4_K, (M, K)], *, rows: wl.static[int]) -> wl.View[Q4K_I[ro
 
 
 #: name -> (storage bytes per record, logical elements per record, alignment)
-RECORDS = {"Q4_0": (18, 32, 2), "Q8_0": (34, 32, 2), "Q8_1": (36, 32, 2), "Q4_K": (144, 256, 2), "Q5_K": (176, 256, 2), "Q6_K": (210, 256, 1), "IQ2_XXS": (66, 256, 2),
+RECORDS = {"Q4_0": (18, 32, 2), "Q8_0": (34, 32, 2), "Q8_1": (36, 32, 2), "Q2_K": (84, 256, 2), "Q3_K": (110, 256, 2), "Q4_K": (144, 256, 2), "Q5_K": (176, 256, 2), "Q6_K": (210, 256, 1), "IQ2_XXS": (66, 256, 2),
            "TQ1_0": (54, 256, 2), "Q8_K": (292, 256, 4), "I8X8": (8, 8, 8)}
 
 #: numbering of the reference harnesses (examples/repro/weft/vec_dot_runtime.cpp:185-344), used by the C ABI
-FORMAT_IDS = {"Q4_0": 1, "Q8_0": 5, "Q4_K": 8, "Q5_K": 9, "Q6_K": 10, "IQ2_XXS": 15, "TQ1_0": 20}
+FORMAT_IDS = {"Q4_0": 1, "Q8_0": 5, "Q2_K": 6, "Q3_K": 7, "Q4_K": 8, "Q5_K": 9, "Q6_K": 10, "IQ2_XXS": 15, "TQ1_0": 20}
 
 TQ1_POWERS = (1, 3, 9, 27, 81)
 

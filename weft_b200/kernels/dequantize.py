@@ -1,7 +1,7 @@
 """Row dequantizers: K packed elements -> K fp32 values, bit-exact with the reference's GGML semantics.
 
 Signatures follow examples/kernels/dequantize/q4_0.py:9-13, q8_0.py:9-13, q4_k.py:9-20,
-q5_k.py:9-15, q6_k.py:8-15, iq2_xxs.py:9-53 and tq1_0.py:9-46 of the reference (Y is its own alias group where the reference says so).
+q2_k.py:8-17, q3_k.py:8-17, q5_k.py:9-15, q6_k.py:8-15, iq2_xxs.py:9-53 and tq1_0.py:9-46 of the reference (Y is its own alias group where the reference says so).
 """
 from __future__ import annotations
 
@@ -23,6 +23,16 @@ def row_dequantize_q8_0(W: wl.View[ggml.Q8_0, (K,)], Y: wl.View[wl.f32, (K,)]):
 @kernel(alias_groups={"Y": "output"})
 def row_dequantize_q4_k(W: wl.View[ggml.Q4_K, (K,)], Y: wl.View[wl.f32, (K,)]):
     """Y = (d * sc) * q - (dmin * m), three rounded multiplies and one subtract."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_q2_k(W: wl.View[ggml.Q2_K, (K,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (scales & 15)) * q2 - (dmin * (scales >> 4))."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_q3_k(W: wl.View[ggml.Q3_K, (K,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (scale - 32)) * (q2 + 4 * hmask - 4)."""
 
 
 @kernel(alias_groups={"Y": "output"})

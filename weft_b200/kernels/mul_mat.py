@@ -1,8 +1,8 @@
 """production_mul_mat_*: quantize X into the Xq workspace, then Y[m, n] = vec_dot(W[n], Xq[m]).
 
 Signatures and alias groups follow the reference: examples/kernels/mul_mat/q4_0_decode.py:10-20,
-q8_0_decode.py, q4_k_decode.py:10-20, q5_k_decode.py:10-20, q6_k_decode.py:10-20, iq2_xxs_decode.py:10-23, tq1_0_decode.py:10-21 (decode: a GEMV
-per activation row) and q4_0.py:9-30, q8_0.py:9-29, q4_k_staged.py:9-37, q5_k.py:9-37, q6_k.py:9-37, tq1_0.py:10-64,
+q8_0_decode.py, q4_k_decode.py:10-20, q2_k_decode.py:10-20, q3_k_decode.py:10-20, q5_k_decode.py:10-20, q6_k_decode.py:10-20, iq2_xxs_decode.py:10-23, tq1_0_decode.py:10-21 (decode: a GEMV
+per activation row) and q4_0.py:9-30, q8_0.py:9-29, q4_k_staged.py:9-37, q2_k.py:9-41, q3_k.py:9-61, q5_k.py:9-37, q6_k.py:9-37, tq1_0.py:10-64,
 iq2_xxs_staged.py:9-97 (prefill: tiled contraction).  The reference's tile symbols NC/MC/MR/NR/KC are
 bound through CompileOptions.meta and are not call parameters.
 """
@@ -29,6 +29,30 @@ def production_mul_mat_q8_0_decode(W: wl.View[ggml.Q8_0, (N, K)], X: wl.View[wl.
 def production_mul_mat_q4_k_decode(W: wl.View[ggml.Q4_K, (N, K)], X: wl.View[wl.f32, (M, K)],
                                    Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
     """Decode GEMV, Q4_K weights x Q8_K activations."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_q2_k_decode(W: wl.View[ggml.Q2_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                   Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, Q2_K weights x Q8_K activations."""
+
+
+@kernel
+def production_mul_mat_q2_k(W: wl.View[ggml.Q2_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                            Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Tiled contraction in the reference; here the decode GEMV per activation row."""
+
+
+@kernel
+def production_mul_mat_q3_k_decode(W: wl.View[ggml.Q3_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                   Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, Q3_K weights x Q8_K activations."""
+
+
+@kernel
+def production_mul_mat_q3_k(W: wl.View[ggml.Q3_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                            Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Tiled contraction in the reference; here the decode GEMV per activation row."""
 
 
 @kernel

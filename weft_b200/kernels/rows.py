@@ -25,6 +25,14 @@ def row_dequantize_q4_k_rows(W: wl.View[ggml.Q4_K, (N, K)], Y: wl.View[wl.f32, (
 
 
 @kernel(alias_groups={"Y": "output"})
+def row_dequantize_q2_k_rows(W: wl.View[ggml.Q2_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_q3_k_rows(W: wl.View[ggml.Q3_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
+@kernel(alias_groups={"Y": "output"})
 def row_dequantize_q5_k_rows(W: wl.View[ggml.Q5_K, (N, K)], Y: wl.View[wl.f32, (N, K)]): ...
 
 
@@ -52,6 +60,14 @@ def quantized_vec_dot_q8_0_q8_0_rows(W: wl.View[ggml.Q8_0, (N, K)], X: wl.View[g
 
 @kernel
 def quantized_vec_dot_q4_k_q8_k_rows(W: wl.View[ggml.Q4_K, (N, K)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_q2_k_q8_k_rows(W: wl.View[ggml.Q2_K, (N, K)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_q3_k_q8_k_rows(W: wl.View[ggml.Q3_K, (N, K)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (N,)]): ...
 
 
 @kernel

@@ -1,7 +1,7 @@
 """Block dot products: one weight row against one activation row, one fp32 result.
 
 Signatures follow examples/kernels/vec_dot/q4_0_q8_0.py:18-23, q8_0_q8_0.py:17-22, q4_k_q8_k.py:31-36,
-q5_k_q8_k.py:34-38, q6_k_q8_k.py:39-43, iq2_xxs_q8_k.py:45-54 and tq1_0_q8_k.py:47-55 of the reference.
+q2_k_q8_k.py:28-32, q3_k_q8_k.py:46-50, q5_k_q8_k.py:34-38, q6_k_q8_k.py:39-43, iq2_xxs_q8_k.py:45-54 and tq1_0_q8_k.py:47-55 of the reference.
 """
 from __future__ import annotations
 
@@ -23,6 +23,16 @@ def quantized_vec_dot_q8_0_q8_0(W: wl.View[ggml.Q8_0, (K,)], X: wl.View[ggml.Q8_
 @kernel
 def quantized_vec_dot_q4_k_q8_k(W: wl.View[ggml.Q4_K, (K,)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (1,)]):
     """Y[0] = sum over 256-blocks of x.ds * (d * sum_g sc_g * dot32_g - dmin * sum_g m_g * (bsum_2g + bsum_2g+1))."""
+
+
+@kernel
+def quantized_vec_dot_q2_k_q8_k(W: wl.View[ggml.Q2_K, (K,)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 256-blocks of x.ds * (d * sum_g (scales_g & 15) * dot16_g - dmin * sum_g (scales_g >> 4) * bsum_g)."""
+
+
+@kernel
+def quantized_vec_dot_q3_k_q8_k(W: wl.View[ggml.Q3_K, (K,)], X: wl.View[ggml.Q8_K, (K,)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 256-blocks of d * x.ds * f32(sum_g (scale_g - 32) * dot16_g(q3 - 4, x))."""
 
 
 @kernel
