@@ -371,6 +371,9 @@ def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_s = float(t.item())
     if not np.array_equal(y_pin[:64].numpy().view(np.uint32), want.view(np.uint32)):
         raise SystemExit("host-buffer dequantize is not bit-exact")
+    if peers is not None:
+        torch.cuda.synchronize()
+        peers.close(dist.barrier)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -414,6 +417,8 @@ def main() -> None:
     parser.add_argument("--impl", default="weft_b200", choices=["weft_b200", "reference"])
     parser.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
+                        help="N > 1: all-gather by the library's own peer-memory kernels (default) or by NCCL")
     parser.add_argument("--no-graph", action="store_true", help="time direct launches instead of a CUDA graph replay")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -490,12 +495,33 @@ def main() -> None:
     shard_fn.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_size_t] * 4 + [ctypes.c_uint]
     gathered = torch.zeros((world * m, n_local), device="cuda") if world > 1 else None
     y_local = torch.zeros((m, n_local), device="cuda") if world > 1 else None
+    # N > 1: the library's own all-gather over NVLink peer memory (peer stores from the GEMV itself and a flag
+    # barrier in the same launch; a push kernel behind the tensor-core prefill), or NCCL with --collective nccl.
+    peers = None
+    collective = "none" if world == 1 else args.collective
+    if world > 1 and collective == "p2p":
+        from weft_b200.peers import SYNC_INTS, PeerBuffers
+
+        try:
+            peers = PeerBuffers(lib, world, rank, [4 * m * n, 4 * m * n, 4 * SYNC_INTS, 16 * min(m * n, 65536)])
+        except RuntimeError as error:
+            sys.stderr.write(f"peer memory unavailable ({error}); using NCCL\n")
+        usable = torch.tensor([1 if peers is not None else 0], device="cuda")
+        dist.all_reduce(usable, op=dist.ReduceOp.MIN)
+        if int(usable.item()) == 0:
+            peers, collective = None, "nccl"
+    gather_fn = lib.weft_b200_mul_mat_shard_gather
+    gather_fn.argtypes = ([ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 6 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+                          + [ctypes.c_size_t] * 5 + [ctypes.c_uint])
 
     def step(i: int, flags: int = 0) -> None:
         wbuf = w_dev[i % copies]
         if world == 1:
             check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
                            powers_dev.data_ptr(), y_dev.data_ptr(), n_local, k, m, n, flags))
+        elif peers is not None:       # consecutive steps alternate between the two output buffers
+            check(gather_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
+                            powers_dev.data_ptr(), peers.tables[i % 2], peers.tables[2], peers.tables[3], world, rank, n0, n_local, n, k, m, flags))
         else:
             check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
                            powers_dev.data_ptr(), y_local.data_ptr(), n_local, k, m, n_local, flags))
@@ -510,7 +536,20 @@ def main() -> None:
     step(0)
     torch.cuda.synchronize()
     check(lib.weft_b200_synchronize())
-    got = (y_dev[:, n0:n1] if world == 1 else y_local).cpu().numpy()
+    if peers is not None:     # the gathered output of this rank: own columns, and a block computed by the next rank
+        full = np.empty((m, n), dtype=np.float32)
+        lib.weft_b200_peer_read.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+        check(lib.weft_b200_peer_read(full.ctypes.data, peers.local[0], full.nbytes))
+        got = full[:, n0:n1]
+        other = (rank + 1) % world
+        o0 = n * other // world
+        span = min(64, n * (other + 1) // world - o0)
+        want_other, _ = oracle.mul_mat(oracle.FORMAT_IDS[fmt], w_host[o0:o0 + span], x_host[:1], span, k, 1, rule=1, grid=grid, signs=signs)
+        err_other = float(np.linalg.norm(full[:1, o0:o0 + span].astype(np.float64) - want_other) / max(np.linalg.norm(want_other.astype(np.float64)), 1e-30))
+        if not err_other <= 1e-5:
+            raise SystemExit(f"gathered columns of rank {other} differ from the oracle on rank {rank}: relative L2 {err_other}")
+    else:
+        got = (y_dev[:, n0:n1] if world == 1 else y_local).cpu().numpy()
     probe = min(n_local, 256)
     want, _ = oracle.mul_mat(oracle.FORMAT_IDS[fmt], shard[:probe], x_host[: min(m, 4)], probe, k, min(m, 4), rule=1, grid=grid, signs=signs)
     err = float(np.linalg.norm(got[: min(m, 4), :probe].astype(np.float64) - want) / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
@@ -648,7 +687,7 @@ def main() -> None:
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype,
         "data": "synthetic",
         "config": {"workload": args.workload, "format": layout, "mode": mode, "N": n, "K": k, "M": m,
-                   "sharding": f"weight rows split {world} ways, fp32 outputs all-gathered (NCCL)" if world > 1 else "none",
+                   "sharding": (f"weight rows split {world} ways, fp32 outputs all-gathered " + ("by peer stores and a flag barrier inside the library's kernels (NVLink, CUDA IPC)" if collective == "p2p" else "(NCCL)")) if world > 1 else "none",
                    "l2": f"steps rotate over {copies} weight copies ({copies * shard.nbytes / 2**20:.0f} MiB per GPU > 2 x L2)",
                    "launch": launch_mode, "timed_scope": "activation quantize + mul_mat" + (" + all-gather" if world > 1 else ""), "seed": SEED,
                    "parity_rel_l2_before_timing": err},

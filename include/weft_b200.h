@@ -205,6 +205,30 @@ int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const 
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags);
 
+/* The same shard with the all-gather done by the library's own kernels over NVLink peer memory instead of a
+ * collective library (the north star's "row-sharded along N ... all-gather of outputs"): every rank owns a full
+ * (M, N) fp32 output and a sync block of 32 ints, both allocated with weft_b200_peer_alloc (zero-filled, exported
+ * as a 64-byte CUDA IPC handle) and opened by every other rank with weft_b200_peer_open.  Y_ranks[r] / sync_ranks[r]
+ * are rank r's buffers as mapped in this process (own buffers at index `rank`).  The call computes columns
+ * [n0, n0 + N_local) and stores them into every rank's output; it returns (or, in async mode, its last kernel
+ * ends) after all ranks' columns have arrived in this rank's output.  All ranks must make the same sequence of
+ * calls; alternate two output buffers between consecutive calls.  stage_ranks (may be NULL) are staging areas of
+ * 2 * 8 * min(M * N, 65536) bytes made and opened the same way: with them, outputs of up to 65536 values (decode)
+ * travel as 8-byte {value, epoch} words that the receiving kernel polls for, with no fence and no barrier (one
+ * launch and one NVLink crossing per step); larger outputs go directly into the peers' output buffers and end with
+ * a flag barrier between the ranks.  Waits on a peer are bounded and surface as a device-side failure.  One
+ * process per GPU. */
+int weft_b200_peer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
+int weft_b200_peer_open(const unsigned char *handle64, void **ptr);
+int weft_b200_peer_close(void *ptr);
+int weft_b200_peer_free(void *ptr);
+/* waits for the library's stream, then copies `bytes` of a buffer made by peer_alloc to host memory */
+int weft_b200_peer_read(void *host, const void *device, size_t bytes);
+int weft_b200_mul_mat_shard_gather(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
+                                   const int8_t *grid, const int8_t *signs, const uint32_t *powers,
+                                   float *const *Y_ranks, int *const *sync_ranks, void *const *stage_ranks, int world, int rank,
+                                   size_t n0, size_t N_local, size_t N, size_t K, size_t M, unsigned flags);
+
 /* ------------------------------------------------------------------ no-allocation variant (no counterpart in the reference)
  * production_mul_mat_q4_k_decode for hosts that cannot allocate device memory once running (all device
  * memory owned by the host's own pool, a frozen memory budget, or a loop that cannot afford the device-wide

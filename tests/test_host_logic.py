@@ -340,6 +340,36 @@ for rows in (n, n - 1):
     y = sharding.sharded_mul_mat(shard, m, local)
     assert tuple(y.shape) == (m, rows)
     assert np.array_equal(y.numpy().view(np.uint32), full[:, :rows].view(np.uint32)), "sharded result differs"
+
+# peer buffer tables: a stand-in for the C library hands out rank-tagged "device pointers" and handles
+from weft_b200 import peers
+class Fn:
+    def __init__(self, call): self.call, self.argtypes = call, None
+    def __call__(self, *a): return self.call(*a)
+class FakeLib:
+    def __init__(self):
+        self.count, self.closed, self.freed = 0, [], []
+        self.weft_b200_peer_alloc, self.weft_b200_peer_open = Fn(self.alloc), Fn(self.open)
+        self.weft_b200_peer_close, self.weft_b200_peer_free = Fn(lambda p: self.closed.append(p.value) or 0), Fn(lambda p: self.freed.append(p.value) or 0)
+    def alloc(self, size, slot, handle):
+        self.count += 1
+        slot._obj.value = 0x100000 * (rank + 1) + 0x100 * self.count
+        handle.raw = (b"rank%d-buffer%d-size%d" % (rank, self.count, size)).ljust(64, b".")
+        return 0
+    def open(self, handle, slot):
+        owner, index = int(handle[4:5]), int(handle.split(b"-")[1][6:])
+        slot._obj.value = 0x900000 + 0x100000 * (owner + 1) + 0x100 * index      # a different mapping of the owner's buffer
+        return 0
+fake = FakeLib()
+group = peers.PeerBuffers(fake, world, rank, [4096, 4096, 4 * peers.SYNC_INTS])
+assert len(group.tables) == 3 and all(len(t) == world for t in group.tables)
+for index, table in enumerate(group.tables):
+    for peer in range(world):
+        want = (0x100000 * (rank + 1) if peer == rank else 0x900000 + 0x100000 * (peer + 1)) + 0x100 * (index + 1)
+        assert table[peer] == want, (index, peer, hex(table[peer] or 0))
+order = []
+group.close(lambda: (order.append(len(fake.closed)), dist.barrier()))
+assert order == [3 * (world - 1)] and len(fake.freed) == 3 and not fake.closed[0] in fake.freed
 dist.destroy_process_group()
 print("rank", rank, "ok")
 """

@@ -235,7 +235,8 @@ int do_quantize(int act, const float *X, uint8_t *Y, size_t M, size_t K) {
 
 // mode 0: GEMV per activation row; mode 1: tensor-core contraction when the shape allows, else GEMV.
 int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const int8_t *grid, const int8_t *signs,
-               const uint32_t *powers, float *Y, size_t N, size_t K, size_t M, size_t ldy, unsigned flags, bool vec_dot_only) {
+               const uint32_t *powers, float *Y, size_t N, size_t K, size_t M, size_t ldy, unsigned flags, bool vec_dot_only,
+               const GatherArgs *gather = nullptr) {
     std::lock_guard<std::recursive_mutex> guard(g.lock);
     if (ensure_init(-1)) return 1;
     const int act = activation_of(fmt);
@@ -268,10 +269,14 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     if (to_prefill) {
         PrefillArgs pa{fmt, w, xq, (const uint32_t *)pw, (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
         if (launched(launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
+        if (gather && launched(launch_gather_push(*gather, (long long)M, (long long)N, (long long)ldy, g.status_dev, sms, g.stream), "peer all-gather")) return 1;
     } else {
         GemvArgs ga{fmt, w, xq, fuse_quantize ? (const float *)x : nullptr, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw,
                     (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
+        const bool fused = gather && gemv_gathers(ga);
+        if (fused) ga.gather = *gather;
         if (launched(launch_gemv(ga, sms, g.stream), "decode mul_mat")) return 1;
+        if (gather && !fused && launched(launch_gather_push(*gather, (long long)M, (long long)N, (long long)ldy, g.status_dev, sms, g.stream), "peer all-gather")) return 1;
     }
     return call.finish();
 }
@@ -436,6 +441,87 @@ size_t production_mul_mat_q4_k_persistent_W_packed_size(size_t N, size_t K) { re
 int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *target, size_t N, size_t K) { return q4ki_pack(source, target, N, K); }
 int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N) {
     return do_mul_mat(F_Q4_K_I16, 0, W, X, Xq, nullptr, nullptr, nullptr, Y, N, K, M, N, 0, false);
+}
+
+// ---- peer memory (CUDA IPC) and the row-sharded mul_mat that gathers through it
+int weft_b200_peer_alloc(size_t bytes, void **ptr, unsigned char *handle) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (!ptr || !handle || !bytes) return fail("peer_alloc needs a size, a pointer slot and a 64-byte handle buffer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void *p = nullptr;
+    CU(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); return fail("peer_alloc: %s", cudaGetErrorString(e)); }
+    memcpy(handle, &h, 64);
+    *ptr = p;
+    return 0;
+}
+
+int weft_b200_peer_open(const unsigned char *handle, void **ptr) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (!ptr || !handle) return fail("peer_open needs a handle and a pointer slot");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    CU(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return 0;
+}
+
+int weft_b200_peer_close(void *ptr) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (!g.ready) return fail("weft_b200 is not initialised");
+    cudaStreamSynchronize(g.stream);
+    CU(cudaIpcCloseMemHandle(ptr));
+    return 0;
+}
+
+int weft_b200_peer_free(void *ptr) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (!g.ready) return fail("weft_b200 is not initialised");
+    cudaStreamSynchronize(g.stream);
+    CU(cudaFree(ptr));
+    return 0;
+}
+
+int weft_b200_peer_read(void *host, const void *device, size_t bytes) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    CU(cudaStreamSynchronize(g.stream));
+    CU(cudaMemcpy(host, device, bytes, cudaMemcpyDeviceToHost));
+    return device_status();
+}
+
+int weft_b200_mul_mat_shard_gather(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
+                                   const int8_t *grid, const int8_t *signs, const uint32_t *powers,
+                                   float *const *Y_ranks, int *const *sync_ranks, void *const *stage_ranks, int world, int rank,
+                                   size_t n0, size_t N_local, size_t N, size_t K, size_t M, unsigned flags) {
+    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K &&
+        format != F_Q6_K && format != F_IQ2_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
+        return fail("unknown weight format id %d", format);
+    if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
+    if (world < 2 || world > GATHER_MAX_RANKS || rank < 0 || rank >= world) return fail("world %d / rank %d out of range (2..%d ranks)", world, rank, GATHER_MAX_RANKS);
+    if (!Y_ranks || !sync_ranks) return fail("the per-rank buffer tables are NULL");
+    if (n0 + N_local > N) return fail("columns [%zu, %zu) exceed N = %zu", n0, n0 + N_local, N);
+    if (!N_local || !K || !M) return fail("every rank must take part in the gather with a non-empty shard");
+    GatherArgs ga{};
+    ga.world = world;
+    ga.rank = rank;
+    ga.n0 = (long long)n0;
+    ga.values = (long long)(M * N);
+    ga.ll = stage_ranks != nullptr && (long long)(M * N) <= GATHER_LL_MAX_VALUES;
+    for (int r = 0; r < world; ++r) {
+        if (!Y_ranks[r] || !sync_ranks[r]) return fail("rank %d has no buffer", r);
+        ga.y[r] = Y_ranks[r] + n0;
+        ga.sync[r] = sync_ranks[r];
+        if (ga.ll) {
+            if (!stage_ranks[r] || (reinterpret_cast<uintptr_t>(stage_ranks[r]) & 7u)) return fail("rank %d has no 8-byte aligned staging area", r);
+            ga.stage[r] = static_cast<uint2 *>(stage_ranks[r]);
+        }
+    }
+    return do_mul_mat(format, mode, W_local, X, Xq, grid, signs, powers, ga.y[rank], N_local, K, M, N, flags, false, &ga);
 }
 
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,

@@ -285,6 +285,16 @@ static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stre
     return cudaGetLastError();
 }
 
+static const bool kGenericOnly = getenv("WEFT_B200_GENERIC_GEMV") != nullptr;
+
+bool gemv_gathers(const GemvArgs &a) {
+    // One activation row only: the grid is then at most one CTA per SM, all resident at once.  A warp that waits
+    // for a peer's values keeps its SM; with more CTAs than SMs two ranks could each hold back the CTAs whose
+    // values the other is waiting for.
+    if (a.k % 256 != 0 || a.k == 0 || a.fmt == F_Q4_K_I16 || kGenericOnly || a.m != 1) return false;
+    return gemv_q4k_supported(a) || gemv_ring_supported(a);
+}
+
 cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
     if (a.n == 0 || a.m == 0) return cudaSuccess;
     if (a.m > 65535) return cudaErrorInvalidValue;
@@ -300,7 +310,7 @@ cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
     }
     if (a.k % 256 != 0 || a.k == 0) return cudaErrorInvalidValue;
     if (a.fmt == F_Q4_K_I16) return launch_gemv_q4ki(a, sm_count, stream);
-    static const bool generic_only = getenv("WEFT_B200_GENERIC_GEMV") != nullptr;
+    const bool generic_only = kGenericOnly;
     if (!generic_only && gemv_q4k_supported(a)) return launch_gemv_q4k(a, sm_count, stream);
     if (!generic_only && gemv_ring_supported(a)) return launch_gemv_ring(a, sm_count, stream);
     switch (a.fmt) {

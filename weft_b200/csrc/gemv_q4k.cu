@@ -61,6 +61,7 @@ struct Q4kParams {
     int tail_rows;       // rows per CTA in the final, partial round
     int inflight;        // copies the producer keeps outstanding (issued, not yet landed)
     int *status;
+    GatherArgs gather;
 };
 
 // One half-record (64 nibble bytes at q0 / q1: two 64-weight groups) of two different rows at once against
@@ -199,6 +200,7 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
     // that precedes it in the stream: wait for that kernel to complete before going on.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    const int epoch = p.gather.world > 1 ? gather_epoch(p.gather) : 0;
     if (QX) q4k_quantize_stage(p.x + (size_t)blockIdx.y * nb * 256, nb, s_xq, s_aux, b == 0 ? const_cast<uint8_t *>(p.xq) + xq_row : nullptr);
     else q4k_stage_records(p.xq + xq_row, nb, s_xq, s_aux);
     __syncthreads();
@@ -298,8 +300,14 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
             const long long grow = ss < p.full_rounds ? ((((long long)ss * G + b) << LSR) + (tt & (SR - 1)))
                                                        : tail_begin + (tt - (p.full_rounds << LSR));
             y[grow] = v;
+            if (p.gather.world > 1) gather_store(p.gather, epoch, blockIdx.y, grow, p.ldy, v);
             mbar_arrive_a(empty_addr + 8 * (ss & (S - 1)));   // after the shuffles: every lane's shared loads have completed
         }
+    }
+    if (p.gather.world > 1) {
+        const int warps = (int)(gridDim.x * gridDim.y) * consumers;
+        gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)(blockIdx.y * gridDim.x + blockIdx.x) * consumers + warp - 1, warps, p.status);
+        gather_finish(p.gather, epoch, p.status, warps);
     }
 }
 
@@ -366,7 +374,7 @@ bool gemv_q4k_supported(const GemvArgs &a) {
 
 cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream) {
     Q4kParams p;
-    p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.x = a.x; p.y = a.y;
+    p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.x = a.x; p.y = a.y; p.gather = a.gather;
     p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status; p.inflight = kQ4kInflight < 1 ? 1 : kQ4kInflight;
     const Q4kPlan plan = plan_q4k(p.nb);
     if (!plan.ok) return cudaErrorInvalidConfiguration;

@@ -41,6 +41,7 @@ struct RingParams {
     int tail_rows;
     int inflight;        // copies the producer keeps outstanding (issued, not yet landed)
     int *status;
+    GatherArgs gather;
 };
 
 template <int FMT, bool QX>
@@ -98,6 +99,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
     // Activations, tables and outputs may belong to the kernel that precedes this one in the stream.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    const int epoch = p.gather.world > 1 ? gather_epoch(p.gather) : 0;
     bool own_tables = false;
     if (FMT == F_IQ2_XXS) own_tables = stage_iq2_tables(p.grid, p.signs, s_grid, s_neg, s_sel);
     uint32_t pw[5] = {1, 3, 9, 27, 81};
@@ -173,8 +175,17 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
             const long long grow = s < p.full_rounds ? ((((long long)s * G + b) << LSR) + in_stage) : tail_begin + (ta - (p.full_rounds << LSR));
             if (live0) y[grow] = v0;
             if (live1) y[grow + 1] = v1;
+            if (p.gather.world > 1) {
+                if (live0) gather_store(p.gather, epoch, blockIdx.y, grow, p.ldy, v0);
+                if (live1) gather_store(p.gather, epoch, blockIdx.y, grow + 1, p.ldy, v1);
+            }
         }
         if (lane == 0) mbar_arrive_a(empty_addr + 8 * (s & (S - 1)));
+    }
+    if (p.gather.world > 1) {
+        const int warps = (int)(gridDim.x * gridDim.y) * consumers;
+        gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)(blockIdx.y * gridDim.x + blockIdx.x) * consumers + warp - 1, warps, p.status);
+        gather_finish(p.gather, epoch, p.status, warps);
     }
 }
 
@@ -247,7 +258,7 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     RingParams p;
     p.w = static_cast<const uint8_t *>(a.w); p.xq = static_cast<const uint8_t *>(a.xq); p.x = a.x;
     p.grid = a.grid; p.signs = a.signs; p.powers = a.powers; p.y = a.y;
-    p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status; p.inflight = kRingInflight < 1 ? 1 : kRingInflight;
+    p.n = a.n; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status; p.gather = a.gather; p.inflight = kRingInflight < 1 ? 1 : kRingInflight;
     const RingPlan plan = plan_ring(a.fmt, p.nb);
     if (!plan.ok) return cudaErrorInvalidConfiguration;
     p.log_lanes = plan.log_lanes; p.log_stage_rows = plan.log_stage_rows; p.log_stages = plan.log_stages;

@@ -5,6 +5,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "gather.cuh"
+
 namespace weft {
 
 // W: `elements` logical values as contiguous records of `fmt`; Y: `elements` floats.
@@ -25,7 +27,10 @@ struct GemvArgs {
     float *y;                // (m, ldy) fp32; column n of row r at y[r * ldy + n]
     long long n, k, m, ldy;
     int *status;             // mapped status word
+    GatherArgs gather;       // world > 1: results also go to every peer's buffer and the launch ends with the ranks' barrier
 };
+// true when the kernel launch_gemv() picks for `a` does the peer stores and the barrier itself
+bool gemv_gathers(const GemvArgs &a);
 cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream);
 // Q4_K x Q8_K specialisation (producer/consumer ring, activations in registers)
 bool gemv_q4k_supported(const GemvArgs &a);
@@ -52,5 +57,9 @@ struct PrefillArgs {
 // tcgen05 int8 tensor-core path; returns cudaErrorNotSupported for shapes it does not take.
 cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stream);
 bool prefill_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
+
+// Push an (m, n_local) column block that this rank has already written into its own buffer (g.y[g.rank], row
+// pitch ldy) to every peer, then run the ranks' barrier: the two-launch form for kernels without fused stores.
+cudaError_t launch_gather_push(const GatherArgs &g, long long m, long long n_local, long long ldy, int *status, int sm_count, cudaStream_t stream);
 
 }  // namespace weft
