@@ -7,8 +7,10 @@ element is computed wholly on one GPU and results are bit-identical for any numb
 
 Rank r of g holds the contiguous row block [N*r/g, N*(r+1)/g) of W -- a contiguous byte range of the
 record array, i.e. a view, not a repack -- and a replica of the (small) activations.  After the local
-mul_mat the fp32 outputs are all-gathered (``torch.distributed.all_gather_into_tensor``; NCCL over
-NVLink on GPUs, gloo in the CPU tests).  One process per GPU.
+mul_mat the fp32 outputs are all-gathered: here with ``torch.distributed.all_gather_into_tensor`` (NCCL over
+NVLink on GPUs, gloo in the CPU tests); ``weft_b200.peers`` + ``weft_b200_mul_mat_shard_gather`` do the same
+gather inside the library's own kernels over peer memory, which is what ``bench.py`` times by default.
+One process per GPU.
 """
 from __future__ import annotations
 
