@@ -22,6 +22,9 @@ namespace {
 
 constexpr int RG_MAX_STAGES = 24;
 constexpr int RG_MAX_THREADS = 512;
+// IQ2_XXS waits on table lookups, needs 64 registers, and gains from twice the warps
+constexpr int ring_max_threads(int fmt) { return fmt == F_IQ2_XXS ? 1024 : RG_MAX_THREADS; }
+constexpr int IQ2_TABLE_BYTES = 49152;   // sixteen bank-striped copies of the grid (32 KB) and of the sign masks (16 KB)
 
 struct RingParams {
     const uint8_t *w;
@@ -45,11 +48,11 @@ struct RingParams {
 };
 
 template <int FMT, bool QX>
-__global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingParams p) {
+__global__ void __launch_bounds__(ring_max_threads(FMT)) gemv_ring_kernel(const RingParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int UB = Unit<FMT>::BYTES;
     constexpr bool ACT_Q8_0 = (FMT == F_Q4_0 || FMT == F_Q8_0);
-    constexpr int TABLE_BYTES = FMT == F_IQ2_XXS ? 4096 : 0;   // grid, sign masks, compressed grid
+    constexpr int TABLE_BYTES = FMT == F_IQ2_XXS ? IQ2_TABLE_BYTES : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = p.nb, LSR = p.log_stage_rows, SR = 1 << LSR, LS = p.log_stages, S = 1 << LS;
     const int LL = p.log_lanes, L = 1 << LL, RPI = 2 * (32 >> LL);   // rows per consumer iteration
@@ -59,7 +62,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
     volatile int *s_issued = reinterpret_cast<volatile int *>(smem);
     uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + 16);
     uint64_t *s_empty = s_full + RG_MAX_STAGES;
-    uint8_t *s_grid = smem + 512, *s_neg = s_grid + 2048, *s_sel = s_neg + 1024;
+    uint8_t *s_grid = smem + 512, *s_neg = s_grid + 32768;
     uint8_t *s_xq = smem + 512 + TABLE_BYTES;
     uint8_t *s_aux = s_xq + (size_t)nb * XQ_PITCH;
     uint8_t *s_ring = smem + ((512 + TABLE_BYTES + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127));
@@ -100,8 +103,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int epoch = p.gather.world > 1 ? gather_epoch(p.gather) : 0;
-    bool own_tables = false;
-    if (FMT == F_IQ2_XXS) own_tables = stage_iq2_tables(p.grid, p.signs, s_grid, s_neg, s_sel);
+    if (FMT == F_IQ2_XXS) stage_iq2_tables_striped(p.grid, p.signs, s_grid, s_neg);
     uint32_t pw[5] = {1, 3, 9, 27, 81};
     if (FMT == F_TQ1_0) {
 #pragma unroll
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(RG_MAX_THREADS) gemv_ring_kernel(const RingPar
             else if (FMT == F_Q3_K) dot_q3_k<2>(wp, xu, xa, acc);
             else if (FMT == F_Q5_K) dot_q5_k<2>(wp, xu, xa, acc);
             else if (FMT == F_Q6_K) dot_q6_k<2>(wp, xu, xa, acc);
-            else if (FMT == F_IQ2_XXS) { if (own_tables) dot_iq2_xxs_fast<2>(wp, xu, xa, s_sel, acc); else dot_iq2_xxs<2>(wp, xu, xa, s_grid, s_neg, acc); }
+            else if (FMT == F_IQ2_XXS) dot_iq2_xxs<2, 128>(wp, xu, xa, s_grid + 8 * (lane & 15), s_neg + 8 * (lane & 15), acc);
             else dot_tq1_0<2>(wp, xu, xa, pw, acc);
         }
         float v0 = acc[0], v1 = acc[1];
@@ -193,7 +195,8 @@ int env_or(const char *name, int fallback) {
     const char *v = getenv(name);
     return v && *v ? atoi(v) : fallback;
 }
-const int kRingConsumers = env_or("WEFT_B200_RING_WARPS", 15);
+const int kRingConsumers = env_or("WEFT_B200_RING_WARPS", 0);   // 0: 15, or kRingIq2Consumers for IQ2_XXS
+const int kRingIq2Consumers = env_or("WEFT_B200_RING_IQ2_WARPS", 27);   // measured 28672 x 8192: 15 -> 29.0 us, 19 -> 28.0, 23 -> 27.1, 27 -> 26.5, 31 -> 26.8
 const int kRingStageBytes = env_or("WEFT_B200_RING_STAGE", 18432);
 const int kRingMaxStages = env_or("WEFT_B200_RING_STAGES", 8);
 const int kRingOverlap = env_or("WEFT_B200_RING_OVERLAP", 1);
@@ -205,7 +208,7 @@ RingPlan plan_ring(int fmt, long long nb) {
     RingPlan plan{0, 0, 0, 0, false};
     const long long row_bytes = nb * unit_bytes(fmt);
     if (row_bytes % 16 != 0 || nb <= 0) return plan;
-    const long long fixed = (512 + (fmt == F_IQ2_XXS ? 4096 : 0) + nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~127LL;
+    const long long fixed = (512 + (fmt == F_IQ2_XXS ? IQ2_TABLE_BYTES : 0) + nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~127LL;
     int ll = 0;
     while ((1 << ll) < 32 && (1 << ll) < nb) ++ll;
     const int log_rpi = 1 + (5 - ll);
@@ -269,7 +272,10 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     p.full_rounds = (int)(a.n / (ctas * stage_rows));
     const long long rest = a.n - (long long)p.full_rounds * ctas * stage_rows;
     p.tail_rows = (int)((rest + ctas - 1) / ctas);
-    int consumers = kRingConsumers < 1 ? 1 : (kRingConsumers > RG_MAX_THREADS / 32 - 1 ? RG_MAX_THREADS / 32 - 1 : kRingConsumers);
+    const int most = ring_max_threads(a.fmt) / 32 - 1;
+    int consumers = kRingConsumers < 1 ? (a.fmt == F_IQ2_XXS ? kRingIq2Consumers : 15) : kRingConsumers;
+    if (consumers > most) consumers = most;
+    if (consumers < 1) consumers = 1;
     const int threads = (consumers + 1) * 32;
     dim3 grid((unsigned)ctas, (unsigned)a.m);
     const bool qx = a.x != nullptr;

@@ -334,7 +334,9 @@ __device__ __forceinline__ void dot_q8_0(const uint8_t *const (&wp)[RL], const u
 
 // One IQ2_XXS record (66 bytes, 2-byte aligned): f16 d, then 8 x {4 grid indices, u32 sign/scale word}.
 // s_grid: int8[256][8]; s_neg: per sign index a byte mask, 0xff where the sign is negative (entries are +1/-1).
-template <int RL>
+// PITCH: bytes between consecutive table entries (8: plain tables; 128: sixteen bank-striped copies, the caller
+// passes the pointers already offset to its lane's copy).
+template <int RL, int PITCH = 8>
 __device__ __forceinline__ void dot_iq2_xxs(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
                                              const uint8_t *s_grid, const uint8_t *s_neg, float (&acc)[RL]) {
     const float xd_ = *reinterpret_cast<const float *>(xaux);
@@ -353,8 +355,8 @@ __device__ __forceinline__ void dot_iq2_xxs(const uint8_t *const (&wp)[RL], cons
             int pos = 0, neg = 0;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + 8 * byte_of(index, e));
-                const uint2 nm = *reinterpret_cast<const uint2 *>(s_neg + 8 * ((meta >> (7 * e)) & 127u));
+                const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + PITCH * byte_of(index, e));
+                const uint2 nm = *reinterpret_cast<const uint2 *>(s_neg + PITCH * ((meta >> (7 * e)) & 127u));
                 pos = dp4a_ss(gv.x, xw[2 * e], pos);
                 pos = dp4a_ss(gv.y, xw[2 * e + 1], pos);
                 neg = dp4a_ss(gv.x & nm.x, xw[2 * e], neg);
@@ -367,75 +369,19 @@ __device__ __forceinline__ void dot_iq2_xxs(const uint8_t *const (&wp)[RL], cons
     for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
 }
 
-// The same record against codebooks in compressed form, usable when the tables passed by the caller are the
-// format's own (every grid byte one of 0x08 / 0x19 / 0x2b; sign row i negative exactly at the set bits of
-// i | parity(i) << 7).  s_sel: per grid entry eight 4-bit selectors into the byte pool {0x08, 0x19, 0x2b},
-// one 32-bit word per entry: a lookup is one 4-byte shared load (random 8-byte loads of the full table
-// serialize on bank conflicts, which is what bounds the uncompressed version) plus two byte permutes.
-// Signs are applied to the grid bytes arithmetically: g' = (g ^ m) + t, t = 0x01 and m = 0xff in negative bytes.
-__device__ __forceinline__ uint32_t iq2_signed4(uint32_t g, uint32_t bits4) {
-    const uint32_t t = (bits4 * 0x00204081u) & 0x01010101u;
-    return (g ^ (t * 0xffu)) + t;
-}
-template <int RL>
-__device__ __forceinline__ void dot_iq2_xxs_fast(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
-                                                  const uint8_t *s_sel, float (&acc)[RL]) {
-    const float xd_ = *reinterpret_cast<const float *>(xaux);
-    uint32_t qw[RL][16];
-    int bsum[RL];
-#pragma unroll
-    for (int r = 0; r < RL; ++r) { ld_words_a2<16>(wp[r] + 2, qw[r]); bsum[r] = 0; }
-    const uint32_t POOL = 0x002b1908u;
-#pragma unroll
-    for (int g = 0; g < 8; ++g) {
-        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
-        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
-        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-#pragma unroll
-        for (int r = 0; r < RL; ++r) {
-            const uint32_t index = qw[r][2 * g], meta = qw[r][2 * g + 1];
-            int sum = 0;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const uint32_t sel = *reinterpret_cast<const uint32_t *>(s_sel + 4 * byte_of(index, e));
-                const uint32_t s7 = (meta >> (7 * e)) & 127u;
-                const uint32_t s8 = s7 | ((__popc(s7) & 1u) << 7);
-                const uint32_t glo = iq2_signed4(__byte_perm(POOL, 0, sel), s8 & 15u);
-                const uint32_t ghi = iq2_signed4(__byte_perm(POOL, 0, sel >> 16), s8 >> 4);
-                sum = dp4a_ss(glo, xw[2 * e], sum);
-                sum = dp4a_ss(ghi, xw[2 * e + 1], sum);
-            }
-            bsum[r] += sum * (int)(2u * (meta >> 28) + 1u);
-        }
+// Stage the IQ2_XXS codebooks as sixteen bank-striped copies: copy c of entry e at e * 128 + c * 8, so copy c lives
+// in banks 2c and 2c + 1 only and a half-warp whose lane l reads copy l % 16 never conflicts, whatever the entries
+// (an 8-byte shared load is served one half-warp at a time).  s_grid: 256 x 128 bytes, s_neg: 128 x 128 bytes.
+__device__ inline void stage_iq2_tables_striped(const int8_t *grid, const int8_t *signs, uint8_t *s_grid, uint8_t *s_neg) {
+    for (int i = threadIdx.x; i < 512 * 16; i += blockDim.x) {       // (entry word, copy)
+        const int word = i >> 4, c = i & 15;
+        reinterpret_cast<uint32_t *>(s_grid)[(word >> 1) * 32 + c * 2 + (word & 1)] = __ldg(reinterpret_cast<const uint32_t *>(grid) + word);
     }
-#pragma unroll
-    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
-}
-
-// Stage the IQ2_XXS codebooks: the full tables (grid bytes, sign masks) and the compressed selectors.
-// Returns (to every thread of the CTA) whether the tables are the format's own.
-__device__ inline bool stage_iq2_tables(const int8_t *grid, const int8_t *signs, uint8_t *s_grid, uint8_t *s_neg, uint8_t *s_sel) {
-    int bad = 0;
-    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-        uint32_t sel = 0;
-        for (int j = 0; j < 8; ++j) {
-            const uint8_t v = (uint8_t)grid[8 * i + j];
-            s_grid[8 * i + j] = v;
-            const uint32_t code = v == 0x08 ? 0u : v == 0x19 ? 1u : v == 0x2b ? 2u : 3u;
-            bad |= code == 3u;
-            sel |= code << (4 * j);
-        }
-        reinterpret_cast<uint32_t *>(s_sel)[i] = sel;
+    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
+        const int word = i >> 4, c = i & 15;
+        const uint32_t s = __ldg(reinterpret_cast<const uint32_t *>(signs) + word);   // four entries of +1 / -1
+        reinterpret_cast<uint32_t *>(s_neg)[(word >> 1) * 32 + c * 2 + (word & 1)] = ((s >> 7) & 0x01010101u) * 0xffu;
     }
-    for (int i = threadIdx.x; i < 128; i += blockDim.x) {
-        const uint32_t s8 = (uint32_t)i | ((__popc((uint32_t)i) & 1u) << 7);
-        for (int j = 0; j < 8; ++j) {
-            const int8_t v = signs[8 * i + j];
-            s_neg[8 * i + j] = v < 0 ? 0xffu : 0u;
-            bad |= v != (((s8 >> j) & 1u) ? -1 : 1);
-        }
-    }
-    return __syncthreads_or(bad) == 0;
 }
 
 // One TQ1_0 record (54 bytes, 2-byte aligned): 32 + 16 bytes of 5 trits, 4 bytes of 4 trits, f16 d.
