@@ -61,7 +61,7 @@ DEFAULT_WORKLOAD = "q4_k_decode_14336x4096"
 # when the kernel ends are not in these numbers.
 NCU_DRAM_TRAFFIC = {
     "q4_k_decode_14336x4096": 33_076_480,
-    "iq2_xxs_decode_28672x8192": 60_846_592,
+    "iq2_xxs_decode_28672x8192": 60_807_168,
     "q4_k_prefill_4096x4096": 11_907_328,
     "tq1_0_prefill_28672x8192": 67_826_432,
     "q4_k_dequantize_14336x4096": 33_040_000 + 177_400_000,
@@ -371,9 +371,6 @@ def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
         t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_s = float(t.item())
     if not np.array_equal(y_pin[:64].numpy().view(np.uint32), want.view(np.uint32)):
         raise SystemExit("host-buffer dequantize is not bit-exact")
-    if peers is not None:
-        torch.cuda.synchronize()
-        peers.close(dist.barrier)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -532,6 +529,20 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    if peers is not None:       # one trial step: if any rank's peer gather fails, every rank goes to NCCL together
+        trial = 1
+        try:
+            step(0)
+            torch.cuda.synchronize()
+            check(lib.weft_b200_synchronize())
+        except SystemExit as error:
+            sys.stderr.write(f"rank {rank}: peer gather failed ({error}); using NCCL\n")
+            trial = 0
+        agreed = torch.tensor([trial], device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            peers, collective = None, "nccl"
+
     # ---- parity spot check before timing (one step against the oracle, rank-local columns)
     step(0)
     torch.cuda.synchronize()
@@ -653,6 +664,9 @@ def main() -> None:
     if e2e_err != 0.0:
         raise SystemExit(f"host-buffer path disagrees with the device-buffer path by {e2e_err}")
 
+    if peers is not None:
+        torch.cuda.synchronize()
+        peers.close(dist.barrier)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
