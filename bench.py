@@ -52,6 +52,7 @@ WORKLOADS = {
     "q4_k_prefill_4096x14336": ("Q4_K", "prefill", 4096, 14336, 512),
     "tq1_0_prefill_28672x8192": ("TQ1_0", "prefill", 28672, 8192, 512),
     "q4_k_dequantize_14336x4096": ("Q4_K", "dequantize", 14336, 4096, 0),
+    "q4_k_layer_decode_llama3_8b": ("Q4_K", "layer", 0, 4096, 1),     # the seven projections of one block, one call per step
 }
 DEFAULT_WORKLOAD = "q4_k_decode_14336x4096"
 
@@ -259,8 +260,36 @@ def reference_arm(args, fmt, mode, n, k, m) -> None:
     import oracle
 
     oracle.build(ref=True)
-    w, x, grid, signs = make_inputs(fmt, n, k, max(m, 1), SEED)
     threads = os.cpu_count() or 1
+    if mode == "layer":         # the seven projections of one block (hidden = k), one after the other
+        kv, ffn = k // 4, k * 7 // 2
+        shapes = [(k, k), (kv, k), (kv, k), (k, k), (ffn, k), (ffn, k), (k, ffn)]
+        runners, total, kind = [], 0, "port"
+        for i, (rows, cols) in enumerate(shapes):
+            w, x, grid, signs = make_inputs(fmt, rows, cols, 1, SEED + i)
+            run, kind = cpu_mul_mat_runner(fmt, rows, cols, 1, w, x, grid, signs, threads)
+            runners.append(run)
+            total += algorithmic_bytes(fmt, rows, cols, 1)
+        times, budget = [], time.perf_counter() + 120.0
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            for run in runners:
+                run()
+            times.append(time.perf_counter() - t0)
+            if time.perf_counter() > budget:
+                break
+        per_step = sum(times) / len(times)
+        value = total / per_step / 1e9
+        print(json.dumps({
+            "impl": "reference", "metric": "mul_mat_decode_algorithmic_gbps", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": len(times), "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8 dot, f32 accumulate", "data": "synthetic",
+            "config": {"workload": args.workload, "format": fmt, "mode": "layer decode", "M": 1, "cpu": oracle.cpu_model(),
+                       "code": "reference GGML C (oracle/_ref)" if kind == "reference" else "C restatement (oracle port)"},
+            "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind, "sample": f"{len(times)} x the seven mul_mats of one block"},
+            "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    w, x, grid, signs = make_inputs(fmt, n, k, max(m, 1), SEED)
     if mode == "dequantize":
         print(json.dumps(cpu_dequantize_line(args, fmt, n, k, w, grid, signs, threads)))
         return
@@ -297,6 +326,130 @@ def reference_arm(args, fmt, mode, n, k, m) -> None:
 
 
 # ------------------------------------------------------------------ GPU side
+
+def gpu_layer_decode(args, lib, check, stream, fmt, hidden, world, rank, local_rank) -> None:
+    """The seven projections of a Llama-3-8B-shaped block at batch 1 (hidden 4096, 8 KV heads of 128, FFN 14336),
+    issued as one weft_b200_mul_mat_chain call per step; a step is one block's worth of weights."""
+    import torch
+
+    import oracle
+    from weft_b200.formats import row_bytes
+    from weft_b200.layers import Projection, ProjectionChain
+
+    if world > 1:
+        raise SystemExit("the layer workload runs on one GPU")
+    kv, ffn = hidden // 4, hidden * 7 // 2
+    shapes = [("attn_q", hidden, hidden, "h", False), ("attn_k", kv, hidden, "h", True), ("attn_v", kv, hidden, "h", True),
+              ("attn_output", hidden, hidden, "a", False), ("ffn_gate", ffn, hidden, "g", False), ("ffn_up", ffn, hidden, "g", True),
+              ("ffn_down", hidden, ffn, "f", False)]
+    rng = np.random.default_rng(SEED)
+    inputs = {"h": hidden, "a": hidden, "g": hidden, "f": ffn}
+    x_host = {key: rng.standard_normal((1, k)).astype(np.float32) for key, k in inputs.items()}
+    x_dev = {key: torch.from_numpy(v).cuda() for key, v in x_host.items()}
+    xq_dev = {key: torch.zeros((1, row_bytes("Q8_K", k)), dtype=torch.uint8, device="cuda") for key, k in inputs.items()}
+    w_host = {name: make_inputs(fmt, n, k, 1, SEED + i)[0] for i, (name, n, k, _, _) in enumerate(shapes)}
+    layer_bytes = sum(w.nbytes for w in w_host.values())
+    copies = max(3, -(-2 * L2_BYTES // layer_bytes) + 1)
+    w_dev = [{name: torch.from_numpy(w).cuda() for name, w in w_host.items()} for _ in range(copies)]
+    y_dev = {name: torch.zeros((1, n), device="cuda") for name, n, _, _, _ in shapes}
+
+    def chain_for(weights, x, xq, y) -> ProjectionChain:
+        return ProjectionChain(lib, [Projection(fmt, weights[name].data_ptr(), x[key].data_ptr(), xq[key].data_ptr(), y[name].data_ptr(), n, k,
+                                                reuse_xq=reuse) for name, n, k, key, reuse in shapes])
+
+    chains = [chain_for(w_dev[c], x_dev, xq_dev, y_dev) for c in range(copies)]
+
+    def step(i: int) -> None:
+        chains[i % copies].run()
+
+    step(0)
+    torch.cuda.synchronize()
+    check(lib.weft_b200_synchronize())
+    worst = 0.0
+    for name, n, k, key, _ in shapes:       # every projection against the oracle (first 128 rows)
+        want, _ = oracle.mul_mat(oracle.FORMAT_IDS[fmt], w_host[name][:128], x_host[key], 128, k, 1, rule=1)
+        got = y_dev[name][:, :128].cpu().numpy().astype(np.float64)
+        worst = max(worst, float(np.linalg.norm(got - want) / max(np.linalg.norm(want.astype(np.float64)), 1e-30)))
+    if not worst <= 1e-5:
+        raise SystemExit(f"parity check failed before timing: relative L2 {worst}")
+
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    launches_before = int(lib.weft_b200_launch_count())
+    side, graph = torch.cuda.Stream(), torch.cuda.CUDAGraph()
+    side.wait_stream(torch.cuda.current_stream())
+    lib.weft_b200_set_stream(ctypes.c_void_p(side.cuda_stream))
+    with torch.cuda.graph(graph, stream=side):
+        for i in range(args.steps):
+            step(args.warmup + i)
+    lib.weft_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
+    launches = int(lib.weft_b200_launch_count()) - launches_before
+    graph.replay()
+    torch.cuda.synchronize()
+    begin.record()
+    graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    ms = begin.elapsed_time(end) / args.steps
+    clocks = sampler.stop()
+
+    # end to end: host (pinned) activations in, host outputs back, weights resident on the device
+    pin = lambda t: t.pin_memory()
+    x_pin = {key: pin(torch.from_numpy(v)) for key, v in x_host.items()}
+    xq_pin = {key: pin(torch.zeros((1, row_bytes("Q8_K", k)), dtype=torch.uint8)) for key, k in inputs.items()}
+    y_pin = {name: pin(torch.zeros((1, n))) for name, n, _, _, _ in shapes}
+    host_chains = [chain_for(w_dev[c], x_pin, xq_pin, y_pin) for c in range(copies)]
+    for i in range(3):
+        host_chains[i % copies].run()
+    torch.cuda.synchronize()
+    e2e_steps = max(3, min(args.steps, 100))
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        host_chains[i % copies].run()
+    check(lib.weft_b200_synchronize())
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    if float((y_pin["ffn_down"] - y_dev["ffn_down"].cpu()).abs().max()) != 0.0:
+        raise SystemExit("host-buffer path disagrees with the device-buffer path")
+
+    peaks, peaks_kind = load_peaks()
+    total = sum(algorithmic_bytes(fmt, n, k, 1) for _, n, k, _, _ in shapes)
+    achieved = total / (ms * 1e-3) / 1e9
+    line = {
+        "metric": "mul_mat_decode_algorithmic_gbps", "value": achieved, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot (dp4a), f32 accumulate",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "format": fmt, "mode": "layer decode", "M": 1,
+                   "projections": {name: [n, k] for name, n, k, _, _ in shapes},
+                   "l2": f"steps rotate over {copies} sets of layer weights ({copies * layer_bytes / 2**20:.0f} MiB > 2 x L2)",
+                   "launch": "cuda graph replay of all steps, one weft_b200_mul_mat_chain call (7 kernels) per step",
+                   "timed_scope": "7 x (activation quantize + mul_mat)", "seed": SEED, "parity_rel_l2_before_timing": worst},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "traffic": None, "peak_source": peaks_kind, "kernel": "gemv kernels of one block, back to back", "kernel_ms": ms,
+                     "algorithmic_bytes_per_launch": total},
+        "clocks": clocks, "gpu_launches": launches,
+        "e2e": {"value": total / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(sum(4 * k for k in inputs.values())),
+                "d2h_bytes_per_step": int(sum(4 * n for _, n, _, _, _ in shapes) + sum(row_bytes("Q8_K", k) for k in inputs.values())),
+                "ms_per_step": e2e_s * 1e3, "what": "weft_b200_mul_mat_chain with host X/Xq/Y (pinned), weights resident in HBM"},
+    }
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        runners = [cpu_mul_mat_runner(fmt, n, k, 1, w_host[name], x_host[key], None, None, threads) for name, n, k, key, _ in shapes]
+        kind = runners[0][1]
+        times, t_end = [], time.perf_counter() + 12.0
+        while time.perf_counter() < t_end and len(times) < 50:
+            t0 = time.perf_counter()
+            for run, _ in runners:
+                run()
+            times.append(time.perf_counter() - t0)
+        per = sum(times) / len(times)
+        line["cpu_baseline"] = {"value": total / per / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
+                                "sample": f"{len(times)} x the seven mul_mats of one block", "cpu": oracle.cpu_model(), "ms_per_step": per * 1e3}
+    print(json.dumps(line))
+
 
 def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank) -> None:
     """row_dequantize over an (n, k) matrix, rows split across ranks (no collective: rows are independent)."""
@@ -459,6 +612,9 @@ def main() -> None:
 
     if mode == "dequantize":
         gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
+        return
+    if mode == "layer":
+        gpu_layer_decode(args, lib, check, stream, fmt, k, world, rank, local_rank)
         return
 
     # ---- inputs, sharded by weight rows

@@ -205,6 +205,25 @@ int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const 
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags);
 
+/* Several decode mul_mats issued back to back in one call, in order, on the library's stream: the projections of
+ * a transformer layer at batch 1 (Q, K, V, O, gate, up, down), as the reference's model-level entry runs them through
+ * llama.cpp (examples/run/ggml.sh:35-43).  Each step is one production_mul_mat_<format>_decode; consecutive kernels
+ * overlap (the next one streams its first weights while the previous one drains).  flags bit 0: Xq of this step
+ * already holds the quantized activations (steps that share an input quantize it once).  grid / signs / powers as
+ * for the single calls, NULL where the format takes none.  Stops at the first failing step. */
+typedef struct weft_b200_mul_mat_step {
+    int format;                  /* harness numbering, as for weft_b200_mul_mat_shard */
+    unsigned flags;
+    const uint8_t *W;            /* (N, K) records */
+    const float *X;              /* (M, K) fp32 */
+    uint8_t *Xq;                 /* (M, K) activation records, written unless flags bit 0 */
+    float *Y;                    /* (M, N) fp32, written */
+    const int8_t *grid, *signs;
+    const uint32_t *powers;
+    size_t N, K, M;
+} weft_b200_mul_mat_step;
+int weft_b200_mul_mat_chain(const weft_b200_mul_mat_step *steps, size_t count);
+
 /* The same shard with the all-gather done by the library's own kernels over NVLink peer memory instead of a
  * collective library (the north star's "row-sharded along N ... all-gather of outputs"): every rank owns a full
  * (M, N) fp32 output and a sync block of 32 ints, both allocated with weft_b200_peer_alloc (zero-filled, exported

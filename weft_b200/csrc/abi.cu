@@ -443,6 +443,19 @@ int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t
     return do_mul_mat(F_Q4_K_I16, 0, W, X, Xq, nullptr, nullptr, nullptr, Y, N, K, M, N, 0, false);
 }
 
+int weft_b200_mul_mat_chain(const weft_b200_mul_mat_step *steps, size_t count) {
+    if (!steps && count) return fail("the step table is NULL");
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    for (size_t i = 0; i < count; ++i) {
+        const weft_b200_mul_mat_step &s = steps[i];
+        if (s.format != F_Q4_0 && s.format != F_Q8_0 && s.format != F_Q2_K && s.format != F_Q3_K && s.format != F_Q4_K && s.format != F_Q5_K &&
+            s.format != F_Q6_K && s.format != F_IQ2_XXS && s.format != F_TQ1_0)
+            return fail("step %zu: unknown weight format id %d", i, s.format);
+        if (do_mul_mat(s.format, 0, s.W, s.X, s.Xq, s.grid, s.signs, s.powers, s.Y, s.N, s.K, s.M, s.N, s.flags, false)) return 1;
+    }
+    return 0;
+}
+
 // ---- peer memory (CUDA IPC) and the row-sharded mul_mat that gathers through it
 int weft_b200_peer_alloc(size_t bytes, void **ptr, unsigned char *handle) {
     std::lock_guard<std::recursive_mutex> guard(g.lock);

@@ -23,7 +23,8 @@ namespace {
 constexpr int RG_MAX_STAGES = 24;
 constexpr int RG_MAX_THREADS = 512;
 // IQ2_XXS waits on table lookups, needs 64 registers, and gains from twice the warps
-constexpr int ring_max_threads(int fmt) { return (fmt == F_IQ2_XXS || fmt == F_Q5_K || fmt == F_Q3_K) ? 1024 : RG_MAX_THREADS; }
+// (Q5_K and Q3_K were tried with the same bound: capped at 64 registers they spill, 10.7 -> 11.0 us and 8.8 -> 11.4 us)
+constexpr int ring_max_threads(int fmt) { return fmt == F_IQ2_XXS ? 1024 : RG_MAX_THREADS; }
 constexpr int IQ2_TABLE_BYTES = 49152;   // sixteen bank-striped copies of the grid (32 KB) and of the sign masks (16 KB)
 
 struct RingParams {
