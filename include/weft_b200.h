@@ -209,7 +209,10 @@ int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const 
  * a transformer layer at batch 1 (Q, K, V, O, gate, up, down), as the reference's model-level entry runs them through
  * llama.cpp (examples/run/ggml.sh:35-43).  Each step is one production_mul_mat_<format>_decode; consecutive kernels
  * overlap (the next one streams its first weights while the previous one drains).  flags bit 0: Xq of this step
- * already holds the quantized activations (steps that share an input quantize it once).  grid / signs / powers as
+ * already holds the quantized activations (steps that share an input quantize it once).  Up to four consecutive
+ * Q4_K steps with one activation row that name the same Xq, the later ones with flags bit 0 set (Q/K/V, gate/up),
+ * run as ONE launch over the concatenated rows when every N is a whole number of the kernel's stages; results are
+ * the same either way.  grid / signs / powers as
  * for the single calls, NULL where the format takes none.  Stops at the first failing step. */
 typedef struct weft_b200_mul_mat_step {
     int format;                  /* harness numbering, as for weft_b200_mul_mat_shard */

@@ -443,11 +443,55 @@ int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t
     return do_mul_mat(F_Q4_K_I16, 0, W, X, Xq, nullptr, nullptr, nullptr, Y, N, K, M, N, 0, false);
 }
 
+// Steps i .. i + count - 1 of a chain as one grouped launch: same activations, same K, one activation row, Q4_K
+// weights already on the device.  Returns -1 when the steps do not qualify (the caller then issues them one by one).
+static int do_mul_mat_group(const weft_b200_mul_mat_step *steps, int count) {
+    if (ensure_init(-1)) return 1;
+    const weft_b200_mul_mat_step &first = steps[0];
+    Call call;
+    GemvArgs ga{};
+    ga.fmt = F_Q4_K; ga.k = (long long)first.K; ga.m = 1; ga.segments = count; ga.status = g.status_dev;
+    for (int i = 0; i < count; ++i) {
+        void *w, *y;
+        if (call.map(steps[i].W, steps[i].N * row_bytes(F_Q4_K, first.K), true, false, &w)) return 1;
+        if (call.map(steps[i].Y, steps[i].N * sizeof(float), false, true, &y)) return 1;
+        ga.seg_w[i] = w; ga.seg_y[i] = static_cast<float *>(y); ga.seg_rows[i] = (long long)steps[i].N;
+        if (reinterpret_cast<uintptr_t>(y) & 3u) return fail("a buffer does not meet its Encoding alignment");
+    }
+    const bool have_xq = (first.flags & 1u) != 0;
+    void *x = nullptr, *xq;
+    if (!have_xq && call.map(first.X, first.K * sizeof(float), true, false, &x)) return 1;
+    if (call.map(first.Xq, row_bytes(F_Q8_K, first.K), have_xq, !have_xq, &xq)) return 1;
+    if ((reinterpret_cast<uintptr_t>(xq) & 3u) || (x && (reinterpret_cast<uintptr_t>(x) & 3u))) return fail("a buffer does not meet its Encoding alignment");
+    const int sms = g.prop.multiProcessorCount;
+    const bool fuse_quantize = !have_xq && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    ga.xq = xq;
+    ga.x = fuse_quantize ? static_cast<const float *>(x) : nullptr;
+    if (!gemv_q4k_groups(ga)) return -1;
+    if (!have_xq && !fuse_quantize &&
+        launched(launch_quantize(F_Q8_K, (const float *)x, xq, 1, (long long)first.K, sms, g.stream), "activation quantize"))
+        return 1;
+    if (launched(launch_gemv(ga, sms, g.stream), "grouped decode mul_mat")) return 1;
+    return call.finish();
+}
+
 int weft_b200_mul_mat_chain(const weft_b200_mul_mat_step *steps, size_t count) {
     if (!steps && count) return fail("the step table is NULL");
     std::lock_guard<std::recursive_mutex> guard(g.lock);
+    static const bool no_groups = getenv("WEFT_B200_CHAIN_NO_GROUPS") != nullptr;
     for (size_t i = 0; i < count; ++i) {
         const weft_b200_mul_mat_step &s = steps[i];
+        // consecutive Q4_K steps on the same activations (the later ones marked as reusing Xq) go out as one launch
+        size_t run = 1;
+        if (!no_groups && s.format == F_Q4_K && s.M == 1 && s.N && s.K && s.K % 256 == 0)
+            while (i + run < count && run < (size_t)GEMV_MAX_SEGMENTS && steps[i + run].format == F_Q4_K && steps[i + run].M == 1 &&
+                   steps[i + run].K == s.K && steps[i + run].Xq == s.Xq && (steps[i + run].flags & 1u) && steps[i + run].N)
+                ++run;
+        if (run > 1) {
+            const int grouped = do_mul_mat_group(steps + i, (int)run);
+            if (grouped > 0) return 1;
+            if (grouped == 0) { i += run - 1; continue; }
+        }
         if (s.format != F_Q4_0 && s.format != F_Q8_0 && s.format != F_Q2_K && s.format != F_Q3_K && s.format != F_Q4_K && s.format != F_Q5_K &&
             s.format != F_Q6_K && s.format != F_IQ2_XXS && s.format != F_TQ1_0)
             return fail("step %zu: unknown weight format id %d", i, s.format);

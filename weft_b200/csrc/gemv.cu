@@ -296,6 +296,7 @@ bool gemv_gathers(const GemvArgs &a) {
 }
 
 cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
+    if (a.segments > 1) return gemv_q4k_groups(a) && !kGenericOnly ? launch_gemv_q4k(a, sm_count, stream) : cudaErrorInvalidValue;
     if (a.n == 0 || a.m == 0) return cudaSuccess;
     if (a.m > 65535) return cudaErrorInvalidValue;
     if ((a.fmt == F_Q4_0 || a.fmt == F_Q8_0) && a.k % 256 != 0) {

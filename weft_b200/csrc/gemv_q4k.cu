@@ -62,7 +62,18 @@ struct Q4kParams {
     int inflight;        // copies the producer keeps outstanding (issued, not yet landed)
     int *status;
     GatherArgs gather;
+    // grouped launch: rows [seg_begin[i], seg_begin[i + 1]) of the row sequence belong to matrix i (whole stages each)
+    int segments;
+    const uint8_t *seg_w[GEMV_MAX_SEGMENTS];
+    float *seg_y[GEMV_MAX_SEGMENTS];
+    long long seg_begin[GEMV_MAX_SEGMENTS + 1];
 };
+
+__device__ __forceinline__ int segment_of(const Q4kParams &p, long long row) {
+    int s = 0;
+    for (int i = 1; i < p.segments; ++i) s += row >= p.seg_begin[i];
+    return s;
+}
 
 // One half-record (64 nibble bytes at q0 / q1: two 64-weight groups) of two different rows at once against
 // the same activations xr[32] (128 codes), scales/mins of sub-blocks 4h..4h+3 from the record headers h0 / h1,
@@ -187,8 +198,13 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
         const bool tail = s >= p.full_rounds;
         const long long row0 = tail ? tail_begin : ((long long)s * G + b) << LSR;
         const uint32_t bytes = tail ? (uint32_t)tail_here * row_bytes : stage_bytes;
+        const uint8_t *src = p.w + (size_t)row0 * row_bytes;
+        if (p.segments > 1) {   // a stage never straddles two matrices
+            const int sg = segment_of(p, row0);
+            src = p.seg_w[sg] + (size_t)(row0 - p.seg_begin[sg]) * row_bytes;
+        }
         mbar_expect_tx_a(full_addr + 8 * slot, bytes);
-        bulk_g2s_a(ring_addr + (uint32_t)slot * stage_bytes, p.w + (size_t)row0 * row_bytes, bytes, full_addr + 8 * slot);
+        bulk_g2s_a(ring_addr + (uint32_t)slot * stage_bytes, src, bytes, full_addr + 8 * slot);
     };
     if (warp == 0 && lane == 0) {
         const int first = min(min(S, p.inflight), total_stages);
@@ -299,7 +315,12 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
             const int tt = upper ? t1 : t, ss = upper ? s1 : s0;
             const long long grow = ss < p.full_rounds ? ((((long long)ss * G + b) << LSR) + (tt & (SR - 1)))
                                                        : tail_begin + (tt - (p.full_rounds << LSR));
-            y[grow] = v;
+            if (p.segments > 1) {
+                const int sg = segment_of(p, grow);
+                p.seg_y[sg][grow - p.seg_begin[sg]] = v;
+            } else {
+                y[grow] = v;
+            }
             if (p.gather.world > 1) gather_store(p.gather, epoch, blockIdx.y, grow, p.ldy, v);
             mbar_arrive_a(empty_addr + 8 * (ss & (S - 1)));   // after the shuffles: every lane's shared loads have completed
         }
@@ -368,8 +389,22 @@ Q4kPlan plan_q4k(long long nb) {
 }  // namespace
 
 bool gemv_q4k_supported(const GemvArgs &a) {
+    if (a.segments > 1) return gemv_q4k_groups(a);
     return a.fmt == F_Q4_K && a.k % 256 == 0 && a.k > 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0 &&
            a.n < (1LL << 30) && plan_q4k(a.k / 256).ok;
+}
+
+bool gemv_q4k_groups(const GemvArgs &a) {
+    if (a.fmt != F_Q4_K || a.segments < 2 || a.segments > GEMV_MAX_SEGMENTS || a.m != 1 || a.k % 256 != 0 || a.k <= 0 || a.gather.world > 1) return false;
+    const Q4kPlan plan = plan_q4k(a.k / 256);
+    if (!plan.ok) return false;
+    long long total = 0;
+    for (int i = 0; i < a.segments; ++i) {
+        if (a.seg_rows[i] <= 0 || a.seg_rows[i] % (1LL << plan.log_stage_rows) != 0) return false;   // whole stages per matrix
+        if ((reinterpret_cast<uintptr_t>(a.seg_w[i]) & 15u) != 0 || !a.seg_y[i]) return false;
+        total += a.seg_rows[i];
+    }
+    return total < (1LL << 30);
 }
 
 cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream) {
@@ -380,15 +415,33 @@ cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream
     if (!plan.ok) return cudaErrorInvalidConfiguration;
     p.log_stage_rows = plan.log_stage_rows; p.log_stages = plan.log_stages;
     const long long stage_rows = 1LL << plan.log_stage_rows;
-    long long ctas = (a.n + stage_rows - 1) / stage_rows;
+    p.segments = a.segments > 1 ? a.segments : 0;
+    if (p.segments) {
+        if (!gemv_q4k_groups(a)) return cudaErrorInvalidConfiguration;
+        p.seg_begin[0] = 0;
+        for (int i = 0; i < p.segments; ++i) {
+            p.seg_w[i] = static_cast<const uint8_t *>(a.seg_w[i]);
+            p.seg_y[i] = a.seg_y[i];
+            p.seg_begin[i + 1] = p.seg_begin[i] + a.seg_rows[i];
+        }
+        p.n = p.seg_begin[p.segments];
+        p.w = p.seg_w[0]; p.y = p.seg_y[0]; p.ldy = p.n;
+    }
+    const long long n = p.n;
+    long long ctas = (n + stage_rows - 1) / stage_rows;
     if (ctas > sm_count) ctas = sm_count;
     if (ctas < 1) ctas = 1;
-    p.full_rounds = (int)(a.n / (ctas * stage_rows));
-    const long long rest = a.n - (long long)p.full_rounds * ctas * stage_rows;
+    p.full_rounds = (int)(n / (ctas * stage_rows));
+    const long long rest = n - (long long)p.full_rounds * ctas * stage_rows;
     p.tail_rows = (int)((rest + ctas - 1) / ctas);
+    if (p.segments) {   // a power of two: the tail chunks then never straddle a matrix boundary (a multiple of the stage)
+        int pow2 = 1;
+        while (pow2 < p.tail_rows) pow2 <<= 1;
+        p.tail_rows = p.tail_rows ? pow2 : 0;
+    }
     int consumers = kQ4kConsumers < 1 ? 1 : (kQ4kConsumers > QK_MAX_THREADS / 32 - 1 ? QK_MAX_THREADS / 32 - 1 : kQ4kConsumers);
     const int threads = (consumers + 1) * 32;
-    dim3 grid((unsigned)ctas, (unsigned)a.m);
+    dim3 grid((unsigned)ctas, (unsigned)(p.segments ? 1 : a.m));
     const bool xreg = 2 * p.nb <= 32;
     if (a.x) return xreg ? launch_variant<true, true>(p, grid, threads, plan.smem, stream) : launch_variant<true, false>(p, grid, threads, plan.smem, stream);
     return xreg ? launch_variant<false, true>(p, grid, threads, plan.smem, stream) : launch_variant<false, false>(p, grid, threads, plan.smem, stream);

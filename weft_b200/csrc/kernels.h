@@ -16,6 +16,8 @@ cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const 
 // X (rows, k) fp32 -> Q8_0 / Q8_K records, Weft rounding and tie rules.
 cudaError_t launch_quantize(int act_fmt, const float *x, void *y, long long rows, long long k, int sm_count, cudaStream_t stream);
 
+constexpr int GEMV_MAX_SEGMENTS = 4;
+
 struct GemvArgs {
     int fmt;                 // weight format
     const void *w;           // (n, k) records
@@ -28,7 +30,15 @@ struct GemvArgs {
     long long n, k, m, ldy;
     int *status;             // mapped status word
     GatherArgs gather;       // world > 1: results also go to every peer's buffer and the launch ends with the ranks' barrier
+    // Several weight matrices against the same activations in one launch (m = 1): matrix i has seg_rows[i] rows at
+    // seg_w[i] and writes seg_y[i]; w / y / n are then unused.  0 or 1: the single matrix w.
+    int segments;
+    const void *seg_w[GEMV_MAX_SEGMENTS];
+    float *seg_y[GEMV_MAX_SEGMENTS];
+    long long seg_rows[GEMV_MAX_SEGMENTS];
 };
+// true when launch_gemv_q4k takes these matrices as one grouped launch
+bool gemv_q4k_groups(const GemvArgs &a);
 // true when the kernel launch_gemv() picks for `a` does the peer stores and the barrier itself
 bool gemv_gathers(const GemvArgs &a);
 cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream);
