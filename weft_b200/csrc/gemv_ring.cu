@@ -24,7 +24,7 @@ constexpr int RG_MAX_STAGES = 24;
 constexpr int RG_MAX_THREADS = 512;
 // IQ2_XXS waits on table lookups, needs 64 registers, and gains from twice the warps
 // (Q5_K and Q3_K were tried with the same bound: capped at 64 registers they spill, 10.7 -> 11.0 us and 8.8 -> 11.4 us)
-constexpr int ring_max_threads(int fmt) { return fmt == F_IQ2_XXS ? 1024 : RG_MAX_THREADS; }
+constexpr int ring_max_threads(int fmt, int rl = 2) { return (fmt == F_IQ2_XXS || rl == 1) ? 1024 : RG_MAX_THREADS; }
 constexpr int IQ2_TABLE_BYTES = 49152;   // sixteen bank-striped copies of the grid (32 KB) and of the sign masks (16 KB)
 
 struct RingParams {
@@ -48,15 +48,15 @@ struct RingParams {
     GatherArgs gather;
 };
 
-template <int FMT, bool QX>
-__global__ void __launch_bounds__(ring_max_threads(FMT)) gemv_ring_kernel(const RingParams p) {
+template <int FMT, bool QX, int RL>
+__global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(const RingParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int UB = Unit<FMT>::BYTES;
     constexpr bool ACT_Q8_0 = (FMT == F_Q4_0 || FMT == F_Q8_0);
     constexpr int TABLE_BYTES = FMT == F_IQ2_XXS ? IQ2_TABLE_BYTES : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = p.nb, LSR = p.log_stage_rows, SR = 1 << LSR, LS = p.log_stages, S = 1 << LS;
-    const int LL = p.log_lanes, L = 1 << LL, RPI = 2 * (32 >> LL);   // rows per consumer iteration
+    const int LL = p.log_lanes, L = 1 << LL, RPI = RL * (32 >> LL);   // rows per consumer iteration
     const uint32_t row_bytes = (uint32_t)nb * UB, stage_bytes = row_bytes << LSR;
     const int G = gridDim.x, b = blockIdx.x;
 
@@ -148,39 +148,44 @@ __global__ void __launch_bounds__(ring_max_threads(FMT)) gemv_ring_kernel(const 
         }
         if (!mbar_wait_a(full_addr + 8 * (s & (S - 1)), (uint32_t)(s >> LS) & 1u)) { report(p.status, ST_WAIT_TIMEOUT); return; }
         const uint8_t *stage = s_ring + (size_t)(s & (S - 1)) * stage_bytes;
-        const int in_stage = (t & (SR - 1)) + 2 * group;
-        const int ta = t + 2 * group;
-        const bool live0 = ta < rows_here, live1 = ta + 1 < rows_here;
-        // rows past the end read row 0 of the stage (always valid) and are dropped
-        const uint8_t *base0 = stage + (size_t)(live0 ? in_stage : 0) * row_bytes;
-        const uint8_t *base1 = stage + (size_t)(live1 ? in_stage + 1 : 0) * row_bytes;
-        float acc[2] = {0.f, 0.f};
+        const int in_stage = (t & (SR - 1)) + RL * group;
+        const int ta = t + RL * group;
+        bool live[RL];
+        const uint8_t *base[RL];
+        float acc[RL];
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {   // rows past the end read row 0 of the stage (always valid) and are dropped
+            live[r] = ta + r < rows_here;
+            base[r] = stage + (size_t)(live[r] ? in_stage + r : 0) * row_bytes;
+            acc[r] = 0.f;
+        }
         for (int u = ul; u < nb; u += L) {
-            const uint8_t *const wp[2] = {base0 + (size_t)u * UB, base1 + (size_t)u * UB};
+            const uint8_t *wp[RL];
+#pragma unroll
+            for (int r = 0; r < RL; ++r) wp[r] = base[r] + (size_t)u * UB;
             const uint8_t *xu = s_xq + u * XQ_PITCH, *xa = s_aux + u * XAUX_BYTES;
-            if (FMT == F_Q4_0) dot_q4_0<2>(wp, xu, xa, acc);
-            else if (FMT == F_Q8_0) dot_q8_0<2>(wp, xu, xa, acc);
-            else if (FMT == F_Q2_K) dot_q2_k<2>(wp, xu, xa, acc);
-            else if (FMT == F_Q3_K) dot_q3_k<2>(wp, xu, xa, acc);
-            else if (FMT == F_Q5_K) dot_q5_k<2>(wp, xu, xa, acc);
-            else if (FMT == F_Q6_K) dot_q6_k<2>(wp, xu, xa, acc);
-            else if (FMT == F_IQ2_XXS) dot_iq2_xxs<2, 128>(wp, xu, xa, s_grid + 8 * (lane & 15), s_neg + 8 * (lane & 15), acc);
-            else dot_tq1_0<2>(wp, xu, xa, pw, acc);
+            if (FMT == F_Q4_0) dot_q4_0<RL>(wp, xu, xa, acc);
+            else if (FMT == F_Q8_0) dot_q8_0<RL>(wp, xu, xa, acc);
+            else if (FMT == F_Q2_K) dot_q2_k<RL>(wp, xu, xa, acc);
+            else if (FMT == F_Q3_K) dot_q3_k<RL>(wp, xu, xa, acc);
+            else if (FMT == F_Q5_K) dot_q5_k<RL>(wp, xu, xa, acc);
+            else if (FMT == F_Q6_K) dot_q6_k<RL>(wp, xu, xa, acc);
+            else if (FMT == F_IQ2_XXS) dot_iq2_xxs<RL, 128>(wp, xu, xa, s_grid + 8 * (lane & 15), s_neg + 8 * (lane & 15), acc);
+            else dot_tq1_0<RL>(wp, xu, xa, pw, acc);
         }
-        float v0 = acc[0], v1 = acc[1];
-        for (int o = L >> 1; o > 0; o >>= 1) {
-            v0 += __shfl_xor_sync(0xffffffffu, v0, o);
-            v1 += __shfl_xor_sync(0xffffffffu, v1, o);
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            for (int o = L >> 1; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
+            if (FMT == F_IQ2_XXS) acc[r] *= 0.125f;
         }
-        if (FMT == F_IQ2_XXS) { v0 *= 0.125f; v1 *= 0.125f; }
         __syncwarp();   // every lane's shared loads of this stage have completed
         if (ul == 0) {
             const long long grow = s < p.full_rounds ? ((((long long)s * G + b) << LSR) + in_stage) : tail_begin + (ta - (p.full_rounds << LSR));
-            if (live0) y[grow] = v0;
-            if (live1) y[grow + 1] = v1;
-            if (p.gather.world > 1) {
-                if (live0) gather_store(p.gather, epoch, blockIdx.y, grow, p.ldy, v0);
-                if (live1) gather_store(p.gather, epoch, blockIdx.y, grow + 1, p.ldy, v1);
+#pragma unroll
+            for (int r = 0; r < RL; ++r) {
+                if (!live[r]) continue;
+                y[grow + r] = acc[r];
+                if (p.gather.world > 1) gather_store(p.gather, epoch, blockIdx.y, grow + r, p.ldy, acc[r]);
             }
         }
         if (lane == 0) mbar_arrive_a(empty_addr + 8 * (s & (S - 1)));
@@ -202,6 +207,8 @@ const int kRingStageBytes = env_or("WEFT_B200_RING_STAGE", 18432);
 const int kRingMaxStages = env_or("WEFT_B200_RING_STAGES", 8);
 const int kRingOverlap = env_or("WEFT_B200_RING_OVERLAP", 1);
 const int kRingInflight = env_or("WEFT_B200_RING_INFLIGHT", 3);
+const int kRingSmemKB = env_or("WEFT_B200_RING_SMEM_KB", 224);
+const int kRingTwoIterations = env_or("WEFT_B200_RING_TWO_ITERATIONS", 1);
 
 struct RingPlan { int log_lanes, log_stage_rows, log_stages; size_t smem; bool ok; };
 
@@ -215,8 +222,12 @@ RingPlan plan_ring(int fmt, long long nb) {
     const int log_rpi = 1 + (5 - ll);
     int lsr = log_rpi;   // at least one consumer iteration per stage
     while (lsr < 8 && (row_bytes << (lsr + 1)) <= kRingStageBytes) ++lsr;
+    const long long cap = (long long)kRingSmemKB * 1024;
+    // A stage that is a single consumer iteration is drained by one warp while the others wait for the next copy:
+    // take two iterations per stage when eight such stages still fit (Q5_K 14336 x 4096: 10.7 -> 8.2 us).
+    if (lsr == log_rpi && kRingTwoIterations && fixed + ((row_bytes << (lsr + 1)) << 3) <= cap) ++lsr;
     int ls = 0;
-    while ((1 << (ls + 1)) <= kRingMaxStages && (1 << (ls + 1)) <= RG_MAX_STAGES && fixed + ((row_bytes << lsr) << (ls + 1)) <= 200LL * 1024) ++ls;
+    while ((1 << (ls + 1)) <= kRingMaxStages && (1 << (ls + 1)) <= RG_MAX_STAGES && fixed + ((row_bytes << lsr) << (ls + 1)) <= cap) ++ls;
     if (ls < 1) return plan;
     plan.log_lanes = ll; plan.log_stage_rows = lsr; plan.log_stages = ls;
     plan.smem = (size_t)(fixed + ((row_bytes << lsr) << ls)) + 16;   // the 2-byte-aligned record loaders read up to 4 bytes past a record
@@ -224,11 +235,11 @@ RingPlan plan_ring(int fmt, long long nb) {
     return plan;
 }
 
-template <int FMT, bool QX>
+template <int FMT, bool QX, int RL>
 cudaError_t launch_variant(const RingParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
     static int smem_set = 0;
     if ((int)smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_ring_kernel<FMT, QX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_ring_kernel<FMT, QX, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         smem_set = (int)smem;
     }
@@ -242,12 +253,14 @@ cudaError_t launch_variant(const RingParams &p, dim3 grid, int threads, size_t s
     attribute[0].val.programmaticStreamSerializationAllowed = kRingOverlap ? 1 : 0;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, gemv_ring_kernel<FMT, QX>, p);
+    return cudaLaunchKernelEx(&config, gemv_ring_kernel<FMT, QX, RL>, p);
 }
 
 template <int FMT>
 cudaError_t launch_fmt(const RingParams &p, bool qx, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
-    return qx ? launch_variant<FMT, true>(p, grid, threads, smem, stream) : launch_variant<FMT, false>(p, grid, threads, smem, stream);
+    // two rows per lane group and iteration; one row (half the registers, up to 31 warps) measured no better:
+    // Q6_K 14336 x 4096 11.0 vs 10.4 us, Q5_K 8.4 vs 8.5, Q3_K 9.1 vs 9.2, Q2_K 7.7 vs 7.7
+    return qx ? launch_variant<FMT, true, 2>(p, grid, threads, smem, stream) : launch_variant<FMT, false, 2>(p, grid, threads, smem, stream);
 }
 
 }  // namespace
