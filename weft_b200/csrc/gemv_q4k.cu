@@ -157,7 +157,9 @@ __device__ void q4k_stage_records(const uint8_t *xq, int nb, uint8_t *s_q, uint8
 
 namespace {
 
-template <bool QX, bool XREG>
+// MODE 0: one matrix; 1: grouped launch over several matrices; 2: one matrix with the peer all-gather.  Separate
+// instantiations, so that the single-matrix kernel carries none of the other two's code.
+template <bool QX, bool XREG, int MODE>
 __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -199,7 +201,7 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
         const long long row0 = tail ? tail_begin : ((long long)s * G + b) << LSR;
         const uint32_t bytes = tail ? (uint32_t)tail_here * row_bytes : stage_bytes;
         const uint8_t *src = p.w + (size_t)row0 * row_bytes;
-        if (p.segments > 1) {   // a stage never straddles two matrices
+        if (MODE == 1) {   // a stage never straddles two matrices
             const int sg = segment_of(p, row0);
             src = p.seg_w[sg] + (size_t)(row0 - p.seg_begin[sg]) * row_bytes;
         }
@@ -216,7 +218,7 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
     // that precedes it in the stream: wait for that kernel to complete before going on.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const int epoch = p.gather.world > 1 ? gather_epoch(p.gather) : 0;
+    const int epoch = MODE == 2 ? gather_epoch(p.gather) : 0;
     if (QX) q4k_quantize_stage(p.x + (size_t)blockIdx.y * nb * 256, nb, s_xq, s_aux, b == 0 ? const_cast<uint8_t *>(p.xq) + xq_row : nullptr);
     else q4k_stage_records(p.xq + xq_row, nb, s_xq, s_aux);
     __syncthreads();
@@ -315,17 +317,17 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
             const int tt = upper ? t1 : t, ss = upper ? s1 : s0;
             const long long grow = ss < p.full_rounds ? ((((long long)ss * G + b) << LSR) + (tt & (SR - 1)))
                                                        : tail_begin + (tt - (p.full_rounds << LSR));
-            if (p.segments > 1) {
+            if (MODE == 1) {
                 const int sg = segment_of(p, grow);
                 p.seg_y[sg][grow - p.seg_begin[sg]] = v;
             } else {
                 y[grow] = v;
             }
-            if (p.gather.world > 1) gather_store(p.gather, epoch, blockIdx.y, grow, p.ldy, v);
+            if (MODE == 2) gather_store(p.gather, epoch, blockIdx.y, grow, p.ldy, v);
             mbar_arrive_a(empty_addr + 8 * (ss & (S - 1)));   // after the shuffles: every lane's shared loads have completed
         }
     }
-    if (p.gather.world > 1) {
+    if (MODE == 2) {
         const int warps = (int)(gridDim.x * gridDim.y) * consumers;
         gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)(blockIdx.y * gridDim.x + blockIdx.x) * consumers + warp - 1, warps, p.status);
         gather_finish(p.gather, epoch, p.status, warps);
@@ -344,11 +346,11 @@ const int kQ4kOverlap = env_or("WEFT_B200_Q4K_OVERLAP", 1);
 const int kQ4kSmemCap = env_or("WEFT_B200_Q4K_SMEM_KB", 200);   // per-CTA shared-memory budget tried first
 const int kQ4kInflight = env_or("WEFT_B200_Q4K_INFLIGHT", 3);   // measured: 2 -> 7.8 us, 3 -> 7.05, 4 -> 7.14, 6 -> 7.6, 8 -> 8.1
 
-template <bool QX, bool XREG>
+template <bool QX, bool XREG, int MODE>
 cudaError_t launch_variant(const Q4kParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
     static int smem_set = 0;
     if ((int)smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_q4k_kernel<QX, XREG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_q4k_kernel<QX, XREG, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         smem_set = (int)smem;
     }
@@ -362,7 +364,7 @@ cudaError_t launch_variant(const Q4kParams &p, dim3 grid, int threads, size_t sm
     attribute[0].val.programmaticStreamSerializationAllowed = kQ4kOverlap ? 1 : 0;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, gemv_q4k_kernel<QX, XREG>, p);
+    return cudaLaunchKernelEx(&config, gemv_q4k_kernel<QX, XREG, MODE>, p);
 }
 
 struct Q4kPlan { int log_stage_rows, log_stages; size_t smem; bool ok; };
@@ -443,8 +445,14 @@ cudaError_t launch_gemv_q4k(const GemvArgs &a, int sm_count, cudaStream_t stream
     const int threads = (consumers + 1) * 32;
     dim3 grid((unsigned)ctas, (unsigned)(p.segments ? 1 : a.m));
     const bool xreg = 2 * p.nb <= 32;
-    if (a.x) return xreg ? launch_variant<true, true>(p, grid, threads, plan.smem, stream) : launch_variant<true, false>(p, grid, threads, plan.smem, stream);
-    return xreg ? launch_variant<false, true>(p, grid, threads, plan.smem, stream) : launch_variant<false, false>(p, grid, threads, plan.smem, stream);
+    const int mode = p.segments ? 1 : p.gather.world > 1 ? 2 : 0;
+#define WEFT_Q4K_LAUNCH(MODE)                                                                                                                  \
+    (a.x ? (xreg ? launch_variant<true, true, MODE>(p, grid, threads, plan.smem, stream) : launch_variant<true, false, MODE>(p, grid, threads, plan.smem, stream)) \
+         : (xreg ? launch_variant<false, true, MODE>(p, grid, threads, plan.smem, stream) : launch_variant<false, false, MODE>(p, grid, threads, plan.smem, stream)))
+    if (mode == 1) return WEFT_Q4K_LAUNCH(1);
+    if (mode == 2) return WEFT_Q4K_LAUNCH(2);
+    return WEFT_Q4K_LAUNCH(0);
+#undef WEFT_Q4K_LAUNCH
 }
 
 }  // namespace weft

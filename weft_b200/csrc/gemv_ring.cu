@@ -48,7 +48,8 @@ struct RingParams {
     GatherArgs gather;
 };
 
-template <int FMT, bool QX, int RL>
+// GATHER: the launch also does the peer all-gather (a separate instantiation: the plain kernel carries none of it)
+template <int FMT, bool QX, int RL, bool GATHER>
 __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(const RingParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int UB = Unit<FMT>::BYTES;
@@ -103,7 +104,7 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
     // Activations, tables and outputs may belong to the kernel that precedes this one in the stream.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    const int epoch = p.gather.world > 1 ? gather_epoch(p.gather) : 0;
+    const int epoch = GATHER ? gather_epoch(p.gather) : 0;
     if (FMT == F_IQ2_XXS) stage_iq2_tables_striped(p.grid, p.signs, s_grid, s_neg);
     uint32_t pw[5] = {1, 3, 9, 27, 81};
     if (FMT == F_TQ1_0) {
@@ -185,12 +186,12 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
             for (int r = 0; r < RL; ++r) {
                 if (!live[r]) continue;
                 y[grow + r] = acc[r];
-                if (p.gather.world > 1) gather_store(p.gather, epoch, blockIdx.y, grow + r, p.ldy, acc[r]);
+                if (GATHER) gather_store(p.gather, epoch, blockIdx.y, grow + r, p.ldy, acc[r]);
             }
         }
         if (lane == 0) mbar_arrive_a(empty_addr + 8 * (s & (S - 1)));
     }
-    if (p.gather.world > 1) {
+    if (GATHER) {
         const int warps = (int)(gridDim.x * gridDim.y) * consumers;
         gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)(blockIdx.y * gridDim.x + blockIdx.x) * consumers + warp - 1, warps, p.status);
         gather_finish(p.gather, epoch, p.status, warps);
@@ -235,11 +236,11 @@ RingPlan plan_ring(int fmt, long long nb) {
     return plan;
 }
 
-template <int FMT, bool QX, int RL>
+template <int FMT, bool QX, int RL, bool GATHER>
 cudaError_t launch_variant(const RingParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
     static int smem_set = 0;
     if ((int)smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_ring_kernel<FMT, QX, RL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_ring_kernel<FMT, QX, RL, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         smem_set = (int)smem;
     }
@@ -253,14 +254,16 @@ cudaError_t launch_variant(const RingParams &p, dim3 grid, int threads, size_t s
     attribute[0].val.programmaticStreamSerializationAllowed = kRingOverlap ? 1 : 0;
     config.attrs = attribute;
     config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, gemv_ring_kernel<FMT, QX, RL>, p);
+    return cudaLaunchKernelEx(&config, gemv_ring_kernel<FMT, QX, RL, GATHER>, p);
 }
 
 template <int FMT>
 cudaError_t launch_fmt(const RingParams &p, bool qx, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
     // two rows per lane group and iteration; one row (half the registers, up to 31 warps) measured no better:
     // Q6_K 14336 x 4096 11.0 vs 10.4 us, Q5_K 8.4 vs 8.5, Q3_K 9.1 vs 9.2, Q2_K 7.7 vs 7.7
-    return qx ? launch_variant<FMT, true, 2>(p, grid, threads, smem, stream) : launch_variant<FMT, false, 2>(p, grid, threads, smem, stream);
+    if (p.gather.world > 1)
+        return qx ? launch_variant<FMT, true, 2, true>(p, grid, threads, smem, stream) : launch_variant<FMT, false, 2, true>(p, grid, threads, smem, stream);
+    return qx ? launch_variant<FMT, true, 2, false>(p, grid, threads, smem, stream) : launch_variant<FMT, false, 2, false>(p, grid, threads, smem, stream);
 }
 
 }  // namespace
