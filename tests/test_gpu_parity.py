@@ -342,6 +342,33 @@ def test_c_abi_with_host_buffers(torch, weft, oracle):
     assert b"records" in lib.weft_b200_last_error()
 
 
+def test_c_abi_with_pinned_host_buffers(torch, weft, oracle):
+    """Pinned (mapped) host arguments are moved by a copy kernel rather than the copy engine: same results, also
+    for sizes that are not whole 16-byte words and for buffers at odd offsets."""
+    from weft_b200.runtime.driver import Toolchain, load_library
+
+    lib = load_library(Toolchain().resolve().compiler)
+    fn = lib.production_mul_mat_q4_k_decode
+    fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_size_t] * 3
+    fn.restype = ctypes.c_int
+    rng = np.random.default_rng(78)
+    for n, k, m, shift in [(1024, 2048, 1, 0), (333, 768, 3, 4), (64, 256, 1, 4)]:
+        w = weights(oracle.Q4_K, rng, n, k)
+        x = activations(rng, m, k)
+        want, want_xq = oracle.mul_mat(oracle.Q4_K, w, x, n, k, m, rule=1)
+        w_dev = dev(torch, w)
+        x_pin = torch.zeros(m * k + 8).pin_memory()
+        x_pin[shift // 4: shift // 4 + m * k] = torch.from_numpy(x.reshape(-1))
+        xq_pin = torch.zeros(want_xq.size + 16, dtype=torch.uint8).pin_memory()
+        y_pin = torch.full((m * n + 8,), float("nan")).pin_memory()
+        x_ptr, xq_ptr, y_ptr = x_pin.data_ptr() + shift, xq_pin.data_ptr() + shift, y_pin.data_ptr() + shift
+        assert fn(w_dev.data_ptr(), x_ptr, xq_ptr, y_ptr, n, k, m) == 0, lib.weft_b200_last_error()
+        got_xq = xq_pin.numpy()[shift: shift + want_xq.size].reshape(want_xq.shape)
+        got = y_pin.numpy()[shift // 4: shift // 4 + m * n].reshape(m, n)
+        assert np.array_equal(got_xq, want_xq) and rel_l2(got, want) <= REL_L2_BOUND, (n, k, m)
+        assert np.isnan(y_pin.numpy()[shift // 4 + m * n:]).all() and (xq_pin.numpy()[shift + want_xq.size:] == 0).all()
+
+
 def test_runtime_errors_match_the_reference(torch, weft, oracle):
     from weft_b200.kernels import rows
     from weft_b200.runtime import Buffer

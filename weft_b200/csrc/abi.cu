@@ -92,9 +92,14 @@ int device_status() {
 struct Arg {
     const void *user = nullptr;
     void *dev = nullptr;
+    void *mapped = nullptr;    // the user's buffer as the device sees it, when it is pinned and mapped host memory
     size_t bytes = 0;
     bool written = false, overflow = false;
 };
+
+// Host arguments up to this size in pinned, mapped memory move by a copy kernel instead of the copy engine.
+constexpr size_t kKernelCopyMax = size_t(1) << 18;
+const bool kKernelCopies = getenv("WEFT_B200_NO_KERNEL_COPIES") == nullptr;
 
 // Host-pointer arguments are staged in one device arena owned by the library (256-byte aligned slices).
 // An argument that does not fit gets a one-off allocation, and the arena is regrown after the call so
@@ -134,8 +139,12 @@ class Call {
         }
         Arg arg;
         arg.user = ptr; arg.bytes = bytes; arg.written = written;
+        if (kKernelCopies && attr.type == cudaMemoryTypeHost && attr.devicePointer && bytes <= kKernelCopyMax) arg.mapped = attr.devicePointer;
         if (slice(arg)) return 1;
-        if (read) CU(cudaMemcpyAsync(arg.dev, ptr, bytes, cudaMemcpyHostToDevice, g.stream));
+        if (read) {
+            if (arg.mapped) CU(launch_copy_bytes(arg.dev, arg.mapped, bytes, g.stream));
+            else CU(cudaMemcpyAsync(arg.dev, ptr, bytes, cudaMemcpyHostToDevice, g.stream));
+        }
         *out = arg.dev;
         return 0;
     }
@@ -153,7 +162,10 @@ class Call {
     // Copy written host arguments back and decide whether to wait.
     int finish() {
         for (Arg &a : args_)
-            if (a.written) CU(cudaMemcpyAsync(const_cast<void *>(a.user), a.dev, a.bytes, cudaMemcpyDeviceToHost, g.stream));
+            if (a.written) {
+                if (a.mapped) CU(launch_copy_bytes(a.mapped, a.dev, a.bytes, g.stream));
+                else CU(cudaMemcpyAsync(const_cast<void *>(a.user), a.dev, a.bytes, cudaMemcpyDeviceToHost, g.stream));
+            }
         if (any_host_ || !g.async) {
             CU(cudaStreamSynchronize(g.stream));
             if (wanted_ > g.arena_bytes) {   // make the next identical call fit

@@ -44,6 +44,27 @@ __global__ void __launch_bounds__(QZ_WARPS * 32) quantize_q8_0_kernel(const floa
     }
 }
 
+// Byte copy for small staged arguments; 16-byte words when both sides allow, whole bytes otherwise.
+__global__ void __launch_bounds__(256) copy_bytes_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src, size_t bytes, int vec) {
+    const size_t stride = (size_t)gridDim.x * 256, first = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (vec) {
+        for (size_t i = first; i < bytes / 16; i += stride) reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
+        for (size_t i = (bytes & ~size_t(15)) + first; i < bytes; i += stride) dst[i] = src[i];
+    } else {
+        for (size_t i = first; i < bytes; i += stride) dst[i] = src[i];
+    }
+}
+
+cudaError_t launch_copy_bytes(void *dst, const void *src, size_t bytes, cudaStream_t stream) {
+    if (!bytes) return cudaSuccess;
+    const int vec = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15u) == 0;
+    size_t ctas = ((vec ? bytes / 16 : bytes) + 255) / 256;
+    if (ctas > 64) ctas = 64;
+    if (ctas < 1) ctas = 1;
+    copy_bytes_kernel<<<(unsigned)ctas, 256, 0, stream>>>(static_cast<uint8_t *>(dst), static_cast<const uint8_t *>(src), bytes, vec);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_quantize(int act_fmt, const float *x, void *y, long long rows, long long k, int sm_count, cudaStream_t stream) {
     const long long elements = rows * k;
     if (elements == 0) return cudaSuccess;
