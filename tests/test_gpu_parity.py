@@ -369,6 +369,41 @@ def test_c_abi_with_pinned_host_buffers(torch, weft, oracle):
         assert np.isnan(y_pin.numpy()[shift // 4 + m * n:]).all() and (xq_pin.numpy()[shift + want_xq.size:] == 0).all()
 
 
+def test_ragged_and_empty_shapes(torch, weft, oracle):
+    """32-element formats whose K is not a multiple of 256, a single row, and empty extents through the C ABI."""
+    from weft_b200.runtime.driver import Toolchain, load_library
+
+    lib = load_library(Toolchain().resolve().compiler)
+    rng = np.random.default_rng(90)
+    for name, fmt in (("q4_0", oracle.Q4_0), ("q8_0", oracle.Q8_0)):
+        fn = getattr(lib, f"production_mul_mat_{name}_decode")
+        fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_size_t] * 3
+        fn.restype = ctypes.c_int
+        for n, k, m in [(5, 96, 1), (37, 288, 2), (1, 32, 1), (130, 4128, 1)]:
+            w = weights(fmt, rng, n, k)
+            x = activations(rng, m, k)
+            want, want_xq = oracle.mul_mat(fmt, w, x, n, k, m, rule=1)
+            xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_0, k)), dtype=torch.uint8, device="cuda")
+            y = torch.full((m, n), float("nan"), device="cuda")
+            assert fn(dev(torch, w).data_ptr(), dev(torch, x).data_ptr(), xq.data_ptr(), y.data_ptr(), n, k, m) == 0, lib.weft_b200_last_error()
+            assert np.array_equal(xq.cpu().numpy(), want_xq) and rel_l2(y.cpu().numpy(), want) <= REL_L2_BOUND, (name, n, k, m)
+    # empty extents: success, nothing written
+    fn = lib.production_mul_mat_q4_k_decode
+    fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_size_t] * 3
+    fn.restype = ctypes.c_int
+    w = dev(torch, weights(oracle.Q4_K, rng, 4, 256))
+    x = dev(torch, activations(rng, 1, 256))
+    xq = torch.full((292,), 7, dtype=torch.uint8, device="cuda")
+    y = torch.full((4,), 5.0, device="cuda")
+    for n, k, m in [(0, 256, 1), (4, 0, 1), (4, 256, 0)]:
+        assert fn(w.data_ptr(), x.data_ptr(), xq.data_ptr(), y.data_ptr(), n, k, m) == 0, lib.weft_b200_last_error()
+    assert bool((y == 5.0).all()) and bool((xq == 7).all())
+    dq = lib.row_dequantize_q4_k_rows
+    dq.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_size_t]
+    assert dq(w.data_ptr(), y.data_ptr(), 0, 256) == 0 and bool((y == 5.0).all())
+    assert dq(w.data_ptr(), y.data_ptr(), 1, 100) != 0 and b"records" in lib.weft_b200_last_error()
+
+
 def test_runtime_errors_match_the_reference(torch, weft, oracle):
     from weft_b200.kernels import rows
     from weft_b200.runtime import Buffer
