@@ -653,10 +653,10 @@ def main() -> None:
     peers = None
     collective = "none" if world == 1 else args.collective
     if world > 1 and collective == "p2p":
-        from weft_b200.peers import SYNC_INTS, PeerBuffers
+        from weft_b200.peers import STAGE_BYTES, SYNC_INTS, PeerBuffers
 
         try:
-            peers = PeerBuffers(lib, world, rank, [4 * m * n, 4 * m * n, 4 * SYNC_INTS, 16 * min(m * n, 65536)])
+            peers = PeerBuffers(lib, world, rank, [4 * m * n, 4 * m * n, 4 * SYNC_INTS, STAGE_BYTES])
         except RuntimeError as error:
             sys.stderr.write(f"peer memory unavailable ({error}); using NCCL\n")
         usable = torch.tensor([1 if peers is not None else 0], device="cuda")

@@ -59,6 +59,9 @@ int quantized_vec_dot_q4_k_q8_k(const uint8_t *W, const uint8_t *X, float *Y, si
 int quantized_vec_dot_iq2_xxs_q8_k(const uint8_t *W, const uint8_t *X, const int8_t *grid, const int8_t *signs, float *Y, size_t K);
 /* examples/kernels/vec_dot/tq1_0_q8_k.py:47-55     vec_dot_runtime.cpp:343 */
 int quantized_vec_dot_tq1_0_q8_k(const uint8_t *W, const uint8_t *X, const uint32_t *powers, float *Y, size_t K);
+/* examples/kernels/vec_dot/tq1_0_q8_k_lane16.py:9-54 (the same dot product written with sixteen-wide partial sums
+ * for the reference's vector target; identical integer sums, so the same kernel serves both names) */
+int quantized_vec_dot_tq1_0_q8_k_lane16(const uint8_t *W, const uint8_t *X, const uint32_t *powers, float *Y, size_t K);
 
 /* ------------------------------------------------------------------ row_dequantize: one row of K elements -> fp32
  * examples/kernels/dequantize/q4_0.py:9-13, q8_0.py:9-13, q4_k.py:9-20   examples/repro/weft/row_dequantize_runtime.cpp:177,197,212 */
@@ -91,6 +94,9 @@ int production_mul_mat_iq2_xxs_decode(const uint8_t *W, const float *X, uint8_t 
 /* examples/kernels/mul_mat/tq1_0_decode.py:10-21     mul_mat_runtime.cpp:534-538 */
 int production_mul_mat_tq1_0_decode(const uint8_t *W, const float *X, uint8_t *Xq, const uint32_t *powers,
                                     float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/tq1_0_lane16_decode.py:10-23 (decode GEMV over the lane16 dot product: same function) */
+int production_mul_mat_tq1_0_lane16_decode(const uint8_t *W, const float *X, uint8_t *Xq, const uint32_t *powers,
+                                           float *Y, size_t N, size_t K, size_t M);
 
 /* ------------------------------------------------------------------ production_mul_mat, prefill form (tiled contraction)
  * Same arguments.  The reference binds its tile sizes (NC/MC/MR/NR/KC) at compile time
@@ -140,7 +146,6 @@ int production_mul_mat_q2_k(const uint8_t *W, const float *X, uint8_t *Xq, float
 
 /* ------------------------------------------------------------------ Q3_K x Q8_K (ggml-common.h:305-311 block_q3_K: hmask[32],
  * qs[64], scales[12], f16 d; ggml-quants.c:1247-1294, ggml-cpu/quants.c:566-643; Encoding examples/formats/ggml.py:75-84).
- * The reference's _predecoded_scales variants (a derived Encoding with widened scales) are not built.
  * examples/kernels/vec_dot/q3_k_q8_k.py:46-50          vec_dot_runtime.cpp:239-240 */
 int quantized_vec_dot_q3_k_q8_k(const uint8_t *W, const uint8_t *X, float *Y, size_t K);
 int quantized_vec_dot_q3_k_q8_k_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
@@ -150,6 +155,11 @@ int row_dequantize_q3_k_rows(const uint8_t *W, float *Y, size_t N, size_t K);
 /* examples/kernels/mul_mat/q3_k_decode.py:10-20, q3_k.py:9-61     mul_mat_runtime.cpp:311-312,319-320 */
 int production_mul_mat_q3_k_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 int production_mul_mat_q3_k(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/q3_k_predecoded_scales_decode.py:10-21, q3_k_predecoded_scales.py:10-61: the same
+ * arguments and results; the reference decodes the sixteen 6-bit scales of a record ahead of its inner loop there,
+ * which these kernels always do. */
+int production_mul_mat_q3_k_predecoded_scales_decode(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_q3_k_predecoded_scales(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 
 /* ------------------------------------------------------------------ Q5_K x Q8_K (ggml-common.h block_q5_K: f16 d, f16 dmin,
  * scales[12] as in Q4_K, qh[32], qs[128]; ggml-quants.c:1673-1698, ggml-cpu/quants.c:720-798; Encoding
@@ -191,6 +201,14 @@ int production_mul_mat_q6_k(const uint8_t *W, const float *X, uint8_t *Xq, float
 size_t q4_k_q8_k_gemv_W_packed_size(size_t M, size_t K);
 int q4_k_q8_k_gemv_W_pack(const uint8_t *source, uint8_t *target, size_t M, size_t K);
 int q4_k_q8_k_gemv(const uint8_t *W, const uint8_t *X, float *Y, size_t M, size_t K);
+/* examples/kernels/gemv/q4_k_groups4.py:8-27, q4_k_contract.py:8-27   q4_k_gemv_runtime.cpp:12-25
+ * (two more statements of the same GEMV for the reference's vector and matrix units: same layout and results) */
+size_t q4_k_q8_k_gemv_groups4_W_packed_size(size_t M, size_t K);
+int q4_k_q8_k_gemv_groups4_W_pack(const uint8_t *source, uint8_t *target, size_t M, size_t K);
+int q4_k_q8_k_gemv_groups4(const uint8_t *W, const uint8_t *X, float *Y, size_t M, size_t K);
+size_t q4_k_q8_k_gemv_contract_W_packed_size(size_t M, size_t K);
+int q4_k_q8_k_gemv_contract_W_pack(const uint8_t *source, uint8_t *target, size_t M, size_t K);
+int q4_k_q8_k_gemv_contract(const uint8_t *W, const uint8_t *X, float *Y, size_t M, size_t K);
 /* examples/kernels/mul_mat/q4_k_persistent.py:9-30     mul_mat_runtime.cpp:337-348,805-810
  * Extents in the order (M, K, N): the derived Encoding's builder declares M and K first. */
 size_t production_mul_mat_q4_k_persistent_W_packed_size(size_t N, size_t K);
@@ -235,11 +253,13 @@ int weft_b200_mul_mat_chain(const weft_b200_mul_mat_step *steps, size_t count);
  * [n0, n0 + N_local) and stores them into every rank's output; it returns (or, in async mode, its last kernel
  * ends) after all ranks' columns have arrived in this rank's output.  All ranks must make the same sequence of
  * calls; alternate two output buffers between consecutive calls.  stage_ranks (may be NULL) are staging areas of
- * 2 * 8 * min(M * N, 65536) bytes made and opened the same way: with them, outputs of up to 65536 values (decode)
+ * WEFT_B200_GATHER_STAGE_BYTES (2 halves x 65536 words of 8 bytes, whatever the call's shape, so that calls of
+ * different shapes can share one area) made and opened the same way: with them, outputs of up to 65536 values (decode)
  * travel as 8-byte {value, epoch} words that the receiving kernel polls for, with no fence and no barrier (one
  * launch and one NVLink crossing per step); larger outputs go directly into the peers' output buffers and end with
  * a flag barrier between the ranks.  Waits on a peer are bounded and surface as a device-side failure.  One
  * process per GPU. */
+#define WEFT_B200_GATHER_STAGE_BYTES (2 * 8 * 65536)
 int weft_b200_peer_alloc(size_t bytes, void **ptr, unsigned char *handle64);
 int weft_b200_peer_open(const unsigned char *handle64, void **ptr);
 int weft_b200_peer_close(void *ptr);

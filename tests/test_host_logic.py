@@ -72,7 +72,7 @@ def test_kernel_abi_follows_the_reference_rules():
     deq = registry.resolve(dequantize.row_dequantize_tq1_0)
     assert [a["encoding"] for a in deq["arguments"]] == ["TQ1_0", "dense.u32", "dense.f32"]
     assert deq["arguments"][1]["shape"] == ["5"] and deq["shape_parameters"] == ["K"]
-    assert len(registry.supported_symbols()) == 62
+    assert len(registry.supported_symbols()) == 68
 
 
 _EXTRA_KERNELS = """
@@ -120,9 +120,10 @@ def test_registry_refuses_what_it_cannot_run(tmp_path):
 
 def test_reference_kernel_files_resolve_unchanged():
     """The reference's own kernel files import against this package and map onto the same C symbols."""
-    examples = Path("/root/reference/examples")
+    root = os.environ.get("WEFT_REFERENCE_ROOT")
+    examples = Path(root) / "examples" if root else ROOT.parent / "reference" / "examples"
     if not examples.exists():
-        pytest.skip("reference tree not present")
+        pytest.skip("reference tree not present (WEFT_REFERENCE_ROOT, or a checkout named reference beside this repository)")
     code = (
         "import sys; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
         "import weft_b200; weft_b200.install_as_weft()\n"
@@ -137,6 +138,14 @@ def test_reference_kernel_files_resolve_unchanged():
         "r = registry.resolve(f.q4_k_q8_k_gemv); assert r['arguments'][0]['encoding'] == 'Q4K_I[16]' and r['c_dimension_order'] == ['M', 'K'], r\n"
         "r = registry.resolve(g.production_mul_mat_q4_k_persistent); assert (r['arguments'][0]['storage_bytes'], r['arguments'][0]['record_elements']) == (144, 256)\n"
         "assert r['shape_parameters'] == ['N', 'K', 'M'] and r['c_dimension_order'] == ['M', 'K', 'N'], r\n"
+        "import kernels.gemv.q4_k_groups4 as h, kernels.gemv.q4_k_contract as i, kernels.vec_dot.tq1_0_q8_k_lane16 as j\n"
+        "import kernels.mul_mat.tq1_0_lane16_decode as k, kernels.mul_mat.q3_k_predecoded_scales_decode as l, kernels.mul_mat.q3_k_predecoded_scales as m\n"
+        "assert registry.resolve(h.q4_k_q8_k_gemv_groups4)['c_dimension_order'] == ['M', 'K']\n"
+        "assert registry.resolve(i.q4_k_q8_k_gemv_contract)['arguments'][0]['encoding'] == 'Q4K_I[16]'\n"
+        "assert [x['name'] for x in registry.resolve(j.quantized_vec_dot_tq1_0_q8_k_lane16)['arguments']] == ['W', 'X', 'powers', 'Y']\n"
+        "assert [x['alias_set'] for x in registry.resolve(k.production_mul_mat_tq1_0_lane16_decode)['arguments']] == [0, 0, 1, 0, 2]\n"
+        "assert registry.resolve(l.production_mul_mat_q3_k_predecoded_scales_decode)['c_dimension_order'] == ['N', 'K', 'M']\n"
+        "assert registry.resolve(m.production_mul_mat_q3_k_predecoded_scales)['c_dimension_order'] == ['N', 'K', 'M']\n"
         "print('ok')\n" % (str(ROOT), str(examples)))
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env={**os.environ, "PYTHONDONTWRITEBYTECODE": "1"})
     assert out.returncode == 0 and "ok" in out.stdout, out.stderr

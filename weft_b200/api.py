@@ -30,7 +30,7 @@ class DefinitionSource:
             lines, first = inspect.getsourcelines(obj)
             filename = inspect.getsourcefile(obj) or "<unknown>"
         except (OSError, TypeError) as error:
-            raise DefinitionError(f"Weft must be able to inspect the {noun}") from error
+            raise DefinitionError(f"the source of this {noun} cannot be read back; definitions must live in a file") from error
         return cls(filename, first, textwrap.dedent("".join(lines)))
 
 
@@ -45,13 +45,13 @@ class KernelDefinition:
 
     def __init__(self, function: Callable, *, alias_groups: Mapping[str, str] | None = None) -> None:
         if not isinstance(function, FunctionType):
-            raise DefinitionError("Weft kernels must decorate a Python function")
+            raise DefinitionError("@kernel goes on a plain Python function (got something else)")
         if alias_groups is not None and not isinstance(alias_groups, Mapping):
-            raise DefinitionError("kernel alias_groups must be a parameter-to-group mapping")
+            raise DefinitionError("alias_groups= takes a mapping {parameter name: group name}")
         groups = dict(alias_groups or {})
         for parameter, group in groups.items():
             if not (isinstance(parameter, str) and parameter and isinstance(group, str) and group):
-                raise DefinitionError("kernel alias_groups maps parameter names to non-empty group names")
+                raise DefinitionError("alias_groups= needs non-empty strings for both the parameter and its group")
         self.python_function = function
         self.alias_groups = groups
         self.source = DefinitionSource.of(function, "decorated DSL kernel")
@@ -71,7 +71,7 @@ class KernelDefinition:
 
     def __call__(self, *args, **kwargs):
         raise LanguageUseError(
-            f"kernel {self.__name__} is a definition; use weft.jit or weft.compile to execute it")
+            f"{self.__name__} only describes a kernel and has no Python behaviour; run it through weft.compile(...) or weft.jit(...)")
 
     def __repr__(self) -> str:
         return f"<weft kernel {self.__module__}.{self.__qualname__}>"
@@ -82,7 +82,7 @@ class EncodingDefinition:
 
     def __init__(self, declaration: type, bindings: dict) -> None:
         if not isinstance(declaration, type):
-            raise DefinitionError("@weft.encoding decorates one class declaration")
+            raise DefinitionError("@encoding goes on a class that declares a record layout")
         self.python_class = declaration
         self.bindings = bindings
         self.source = DefinitionSource.of(declaration, "encoding class")
@@ -113,7 +113,7 @@ class DerivedEncodingDefinition:
 
     def __init__(self, function: Callable) -> None:
         if not isinstance(function, FunctionType):
-            raise DefinitionError("@weft.derive decorates one Python function")
+            raise DefinitionError("@derive goes on a plain Python function")
         self.python_function = function
         self.source = DefinitionSource.of(function, "derived encoding definition")
         _copy_identity(self, function)
@@ -123,12 +123,12 @@ class DerivedEncodingDefinition:
         return inspect.signature(self.python_function, eval_str=False)
 
     def __call__(self, *args, **kwargs):
-        raise LanguageUseError(f"derived encoding {self.__name__} is generated at build time")
+        raise LanguageUseError(f"{self.__name__} names a family of derived Encodings; index it (Family[rows]) instead of calling it")
 
     def __getitem__(self, parameters: object) -> DerivedEncodingInstance:
         values = parameters if isinstance(parameters, tuple) else (parameters,)
         if not values or not all(type(value) is int for value in values):
-            raise TypeError("derived Encoding parameters must be static integers")
+            raise TypeError("a derived Encoding is selected by integer constants, e.g. Family[16]")
         return DerivedEncodingInstance(self, values)
 
 
@@ -141,7 +141,7 @@ class InlineDefinition:
     @classmethod
     def capture(cls, function: Callable) -> "InlineDefinition":
         if not isinstance(function, FunctionType):
-            raise DefinitionError("Weft inline functions must be ordinary Python functions")
+            raise DefinitionError("an overload candidate has to be a plain Python function")
         return cls(function, DefinitionSource.of(function, "inline function"))
 
     @property
@@ -160,7 +160,7 @@ class OverloadSet:
         self.name, self.definitions = name, definitions
 
     def __call__(self, *args, **kwargs):
-        raise LanguageUseError(f"overload set {self.name} is resolved only while lowering a Weft kernel")
+        raise LanguageUseError(f"{self.name} is a set of overloads for use inside kernel bodies; it cannot be called from Python")
 
 
 def kernel(function: Callable | None = None, *, alias_groups: Mapping[str, str] | None = None):
@@ -187,5 +187,5 @@ def derive(function: Callable) -> DerivedEncodingDefinition:
 
 def overloads(name: str, *functions: Callable) -> OverloadSet:
     if not name or not functions:
-        raise DefinitionError("weft.overloads expects a name and at least one function")
+        raise DefinitionError("overloads(name, f, ...) needs a name and one candidate or more")
     return OverloadSet(name, tuple(InlineDefinition.capture(function) for function in functions))

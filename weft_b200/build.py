@@ -64,16 +64,35 @@ def build(verbose: bool = False, extra: list[str] | None = None) -> Path:
             sys.stderr.write(f"--- nvcc {name}\n{out}\n")
     if failed:
         raise RuntimeError("nvcc failed; see the compiler output above")
-    link = [nvcc(), "-shared", "-o", str(LIBRARY), *objects, "-gencode", "arch=compute_100a,code=sm_100a"]
-    subprocess.run(link, check=True)
+    # link under a temporary name and move it into place: a process that loads the library meanwhile sees the old
+    # file or the new one, never a half-written one
+    fresh = LIBRARY.with_suffix(f".so.{os.getpid()}.tmp")
+    link = [nvcc(), "-shared", "-o", str(fresh), *objects, "-gencode", "arch=compute_100a,code=sm_100a"]
+    try:
+        subprocess.run(link, check=True)
+        os.replace(fresh, LIBRARY)
+    finally:
+        fresh.unlink(missing_ok=True)
     return LIBRARY
 
 
-def ensure_built() -> Path:
-    if stale():
-        if os.environ.get("WEFT_B200_NO_BUILD"):
-            raise RuntimeError(f"{LIBRARY} is missing or stale and WEFT_B200_NO_BUILD is set")
-        build()
+def ensure_built(extra: list[str] | None = None) -> Path:
+    """Build when a source is newer than the library.  Several ranks of one job may call this at once: they
+    take a file lock in turn, and all but the first find the library fresh."""
+    if not stale():
+        return LIBRARY
+    if os.environ.get("WEFT_B200_NO_BUILD"):
+        raise RuntimeError(f"{LIBRARY} is missing or stale and WEFT_B200_NO_BUILD is set")
+    import fcntl
+
+    (PACKAGE / "build").mkdir(exist_ok=True)
+    with open(PACKAGE / "build" / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if stale():
+                build(extra=extra)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIBRARY
 
 

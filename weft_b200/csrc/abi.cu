@@ -99,7 +99,6 @@ struct Arg {
 
 // Host arguments up to this size in pinned, mapped memory move by a copy kernel instead of the copy engine.
 constexpr size_t kKernelCopyMax = size_t(1) << 18;
-const bool kKernelCopies = getenv("WEFT_B200_NO_KERNEL_COPIES") == nullptr;
 
 // Host-pointer arguments are staged in one device arena owned by the library (256-byte aligned slices).
 // An argument that does not fit gets a one-off allocation, and the arena is regrown after the call so
@@ -139,7 +138,7 @@ class Call {
         }
         Arg arg;
         arg.user = ptr; arg.bytes = bytes; arg.written = written;
-        if (kKernelCopies && attr.type == cudaMemoryTypeHost && attr.devicePointer && bytes <= kKernelCopyMax) arg.mapped = attr.devicePointer;
+        if (attr.type == cudaMemoryTypeHost && attr.devicePointer && bytes <= kKernelCopyMax) arg.mapped = attr.devicePointer;
         if (slice(arg)) return 1;
         if (read) {
             if (arg.mapped) CU(launch_copy_bytes(arg.dev, arg.mapped, bytes, g.stream));
@@ -381,6 +380,9 @@ VEC_DOT(quantized_vec_dot_q5_k_q8_k, F_Q5_K, NO_TABLES, nullptr, nullptr, nullpt
 VEC_DOT(quantized_vec_dot_q6_k_q8_k, F_Q6_K, NO_TABLES, nullptr, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_iq2_xxs_q8_k, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
 VEC_DOT(quantized_vec_dot_tq1_0_q8_k, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
+// The reference's second statement of the same dot product with sixteen-wide partial sums (a vector-length plan of
+// its target; the integer sum per block, and so every result bit, is the same): examples/kernels/vec_dot/tq1_0_q8_k_lane16.py:9-54
+VEC_DOT(quantized_vec_dot_tq1_0_q8_k_lane16, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
 
 // ---- dequantize
 #define DEQUANT(name, fmt, TABLE_PARAMS, GRID, SIGNS, POWERS)                                                          \
@@ -418,6 +420,11 @@ MUL_MAT(production_mul_mat_q5_k_decode, F_Q5_K, 0, NO_TABLES, nullptr, nullptr, 
 MUL_MAT(production_mul_mat_q6_k_decode, F_Q6_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_iq2_xxs_decode, F_IQ2_XXS, 0, IQ_TABLES, grid, signs, nullptr)
 MUL_MAT(production_mul_mat_tq1_0_decode, F_TQ1_0, 0, TQ_TABLES, nullptr, nullptr, powers)
+// same functions under the names of the reference's alternative lowering plans (examples/kernels/mul_mat/
+// tq1_0_lane16_decode.py:10-23, q3_k_predecoded_scales_decode.py:10-21, q3_k_predecoded_scales.py:10-61)
+MUL_MAT(production_mul_mat_tq1_0_lane16_decode, F_TQ1_0, 0, TQ_TABLES, nullptr, nullptr, powers)
+MUL_MAT(production_mul_mat_q3_k_predecoded_scales_decode, F_Q3_K, 0, NO_TABLES, nullptr, nullptr, nullptr)
+MUL_MAT(production_mul_mat_q3_k_predecoded_scales, F_Q3_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q4_0, F_Q4_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q8_0, F_Q8_0, 1, NO_TABLES, nullptr, nullptr, nullptr)
 MUL_MAT(production_mul_mat_q4_k_staged, F_Q4_K, 1, NO_TABLES, nullptr, nullptr, nullptr)
@@ -449,6 +456,17 @@ int q4_k_q8_k_gemv_W_pack(const uint8_t *source, uint8_t *target, size_t M, size
 int q4_k_q8_k_gemv(const uint8_t *W, const uint8_t *X, float *Y, size_t M, size_t K) {
     return do_mul_mat(F_Q4_K_I16, 0, W, nullptr, const_cast<uint8_t *>(X), nullptr, nullptr, nullptr, Y, M, K, 1, M, 0, true);
 }
+// The reference's two other statements of this GEMV (four 16-bit partial groups per sub-block; a 32-bit contraction
+// per sub-block) differ in the vector plan only: same layout, same integer sums, same float op tree
+// (examples/kernels/gemv/q4_k_groups4.py:8-27, q4_k_contract.py:8-27; examples/repro/weft/q4_k_gemv_runtime.cpp:12-25).
+#define Q4KI_GEMV_ALIAS(name)                                                                                          \
+    size_t name##_W_packed_size(size_t M, size_t K) { return q4ki_packed_size(M, K); }                                \
+    int name##_W_pack(const uint8_t *source, uint8_t *target, size_t M, size_t K) { return q4ki_pack(source, target, M, K); } \
+    int name(const uint8_t *W, const uint8_t *X, float *Y, size_t M, size_t K) {                                       \
+        return do_mul_mat(F_Q4_K_I16, 0, W, nullptr, const_cast<uint8_t *>(X), nullptr, nullptr, nullptr, Y, M, K, 1, M, 0, true); \
+    }
+Q4KI_GEMV_ALIAS(q4_k_q8_k_gemv_groups4)
+Q4KI_GEMV_ALIAS(q4_k_q8_k_gemv_contract)
 size_t production_mul_mat_q4_k_persistent_W_packed_size(size_t N, size_t K) { return q4ki_packed_size(N, K); }
 int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *target, size_t N, size_t K) { return q4ki_pack(source, target, N, K); }
 int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N) {
@@ -490,12 +508,11 @@ static int do_mul_mat_group(const weft_b200_mul_mat_step *steps, int count) {
 int weft_b200_mul_mat_chain(const weft_b200_mul_mat_step *steps, size_t count) {
     if (!steps && count) return fail("the step table is NULL");
     std::lock_guard<std::recursive_mutex> guard(g.lock);
-    static const bool no_groups = getenv("WEFT_B200_CHAIN_NO_GROUPS") != nullptr;
     for (size_t i = 0; i < count; ++i) {
         const weft_b200_mul_mat_step &s = steps[i];
         // consecutive Q4_K steps on the same activations (the later ones marked as reusing Xq) go out as one launch
         size_t run = 1;
-        if (!no_groups && s.format == F_Q4_K && s.M == 1 && s.N && s.K && s.K % 256 == 0)
+        if (s.format == F_Q4_K && s.M == 1 && s.N && s.K && s.K % 256 == 0)
             while (i + run < count && run < (size_t)GEMV_MAX_SEGMENTS && steps[i + run].format == F_Q4_K && steps[i + run].M == 1 &&
                    steps[i + run].K == s.K && steps[i + run].Xq == s.Xq && (steps[i + run].flags & 1u) && steps[i + run].N)
                 ++run;

@@ -47,10 +47,13 @@ int refuse(const char *text) {
     return 1;
 }
 
-bool is_device_pointer(const void *p) {
+// 1: device (or managed) memory usable from `device`; 0: host memory; -1: device memory of another GPU
+int where_is(const void *p, int device) {
     cudaPointerAttributes attr{};
-    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return false; }
-    return attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return 0; }
+    if (attr.type == cudaMemoryTypeManaged) return 1;
+    if (attr.type != cudaMemoryTypeDevice) return 0;
+    return attr.device == device ? 1 : -1;
 }
 
 }  // namespace
@@ -77,14 +80,23 @@ extern "C" int production_mul_mat_q4_k_decode_noalloc(const uint8_t *W, const fl
         g_scratch_on[device] = static_cast<unsigned char *>(address);
         g_sm_count[device] = sms;
     }
-    if (!is_device_pointer(W)) return refuse("W must be device memory for the no-allocation entry point");
+    if (where_is(W, device) != 1) return refuse("W must be memory of the current device for the no-allocation entry point");
+    // extents that could not fit the fixed scratch anyway are refused before any size is multiplied out
+    constexpr size_t kMaxExtent = WEFT_B200_NOALLOC_BYTES / 4;
+    const bool host_x = where_is(X, device) == 0, host_xq = where_is(Xq, device) == 0, host_y = where_is(Y, device) == 0;
+    if (where_is(X, device) < 0 || where_is(Xq, device) < 0 || where_is(Y, device) < 0)
+        return refuse("X, Xq and Y must be host memory or memory of the current device");
+    if ((host_x || host_xq || host_y) && (M > kMaxExtent || K > kMaxExtent || N > kMaxExtent || M * K > kMaxExtent || (host_y && M * N > kMaxExtent))) {
+        snprintf(t_message, sizeof(t_message), "this call needs more staging than the fixed scratch of %d bytes holds; use the regular entry point", WEFT_B200_NOALLOC_BYTES);
+        return 1;
+    }
     if ((reinterpret_cast<uintptr_t>(W) & 15u)) return refuse("W must be 16-byte aligned");
 
     // carve the staged arguments out of the fixed array
     unsigned char *base = g_scratch_on[device];
     size_t used = kControlBytes;
-    auto place = [&](const void *user, size_t bytes, bool &staged) -> void * {
-        staged = !is_device_pointer(user);
+    auto place = [&](const void *user, size_t bytes, bool is_host, bool &staged) -> void * {
+        staged = is_host;
         if (!staged) return const_cast<void *>(user);
         void *slot = base + used;
         used = (used + bytes + 255) & ~size_t(255);
@@ -92,9 +104,9 @@ extern "C" int production_mul_mat_q4_k_decode_noalloc(const uint8_t *W, const fl
     };
     const size_t x_bytes = M * K * sizeof(float), xq_bytes = M * (K / 256) * 292, y_bytes = M * N * sizeof(float);
     bool x_staged, xq_staged, y_staged;
-    float *x = static_cast<float *>(place(X, x_bytes, x_staged));
-    uint8_t *xq = static_cast<uint8_t *>(place(Xq, xq_bytes, xq_staged));
-    float *y = static_cast<float *>(place(Y, y_bytes, y_staged));
+    float *x = static_cast<float *>(place(X, x_bytes, host_x, x_staged));
+    uint8_t *xq = static_cast<uint8_t *>(place(Xq, xq_bytes, host_xq, xq_staged));
+    float *y = static_cast<float *>(place(Y, y_bytes, host_y, y_staged));
     if (used > WEFT_B200_NOALLOC_BYTES) {
         snprintf(t_message, sizeof(t_message), "this call needs %zu bytes of staging, the fixed scratch holds %d; use the regular entry point",
                  used, WEFT_B200_NOALLOC_BYTES);
@@ -115,7 +127,10 @@ extern "C" int production_mul_mat_q4_k_decode_noalloc(const uint8_t *W, const fl
     if (e == cudaSuccess && xq_staged) e = cudaMemcpyAsync(Xq, xq, xq_bytes, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess && y_staged) e = cudaMemcpyAsync(Y, y, y_bytes, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(&device_status, status, sizeof(int), cudaMemcpyDeviceToHost, stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    // Always wait, also after a failed enqueue: copies already in the stream name the caller's host buffers and the
+    // shared scratch, and neither may be touched again while they are in flight.
+    const cudaError_t waited = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess) e = waited;
     if (e != cudaSuccess) { snprintf(t_message, sizeof(t_message), "CUDA call failed: %s", cudaGetErrorString(e)); return 1; }
     if (device_status != 0) return refuse("device-side failure: a bounded wait on an asynchronous copy ran out");
     return 0;

@@ -7,8 +7,10 @@
 //   it computes into every peer's staging area as one 8-byte {value, epoch} word; after its own rows a warp
 //   turns to the words it expects from the other ranks, polls each (bounded) until its epoch shows up, and
 //   writes the value into the local output.  No fence and no barrier: a step costs the GEMV plus one NVLink
-//   crossing.  The epoch (one per launch) alternates between two staging halves; a rank cannot start storing
-//   epoch e + 2 before every peer has finished reading epoch e, because finishing e + 1 needs the peers' e + 1.
+//   crossing.  The epoch (one per launch) alternates between two staging halves of GATHER_LL_MAX_VALUES words each,
+//   whatever the shape of the call (consecutive calls of different shapes may share one staging area); a rank
+//   cannot start storing epoch e + 2 before every peer has finished reading epoch e, because finishing e + 1
+//   needs the peers' e + 1.
 // * Fence and barrier, for large outputs (prefill).  Results go straight into every rank's output buffer; the
 //   last warp of the grid to finish publishes this rank's epoch in every peer's sync block and waits (bounded)
 //   until every peer's epoch has arrived in its own.  Writer warps fence at system scope before they count
@@ -29,7 +31,7 @@ constexpr long long GATHER_LL_MAX_VALUES = 1 << 16;   // flagged-value protocol 
 struct GatherArgs {
     float *y[GATHER_MAX_RANKS];     // per rank: its output buffer, already offset to this rank's first column
     int *sync[GATHER_MAX_RANKS];    // per rank: its sync block
-    uint2 *stage[GATHER_MAX_RANKS]; // per rank: its staging area, 2 x (M * N) words (flagged-value protocol only)
+    uint2 *stage[GATHER_MAX_RANKS]; // per rank: its staging area, 2 x GATHER_LL_MAX_VALUES words (flagged-value protocol only)
     long long n0;                   // this rank's first column
     long long values;               // M * N
     int world;                      // 0 or 1: no gather
@@ -45,7 +47,7 @@ __device__ __forceinline__ int gather_epoch(const GatherArgs &g) {
 // Store one result (output row `row`, column `col` of this rank's block, row pitch ldy = N) for every other rank.
 __device__ __forceinline__ void gather_store(const GatherArgs &g, int epoch, long long row, long long col, long long ldy, float v) {
     if (g.ll) {
-        const size_t slot = (size_t)(epoch & 1) * g.values + (size_t)row * ldy + (size_t)(g.n0 + col);
+        const size_t slot = (size_t)(epoch & 1) * GATHER_LL_MAX_VALUES + (size_t)row * ldy + (size_t)(g.n0 + col);
         for (int r = 0; r < g.world; ++r)   // one 8-byte store: value and tag arrive together
             if (r != g.rank)
                 asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" :: "l"(g.stage[r] + slot), "r"(__float_as_uint(v)), "r"((uint32_t)epoch) : "memory");
@@ -62,7 +64,7 @@ __device__ __forceinline__ void gather_receive(const GatherArgs &g, int epoch, l
     if (!g.ll) return;
     const long long others = ldy - n_local, total = m * others;
     float *out = g.y[g.rank] - g.n0;
-    const uint2 *stage = g.stage[g.rank] + (size_t)(epoch & 1) * g.values;
+    const uint2 *stage = g.stage[g.rank] + (size_t)(epoch & 1) * GATHER_LL_MAX_VALUES;
     for (long long i = (long long)warp_index * 32 + (threadIdx.x & 31); i < total; i += (long long)warps * 32) {
         const long long row = i / others, c = i % others;
         const size_t at = (size_t)row * ldy + (size_t)(c < g.n0 ? c : c + n_local);

@@ -21,6 +21,9 @@
 
 #include <climits>
 #include <cstdlib>
+#include <map>
+#include <mutex>
+#include <utility>
 
 namespace weft {
 
@@ -219,14 +222,26 @@ __global__ void gemv_block32_kernel(const uint8_t *__restrict__ w, const uint8_t
 
 // ------------------------------------------------------------------ launch
 
-static int env_int(const char *name, int fallback) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : fallback;
+cudaError_t grant_dynamic_smem(const void *kernel, int bytes) {
+    static std::mutex lock;
+    static std::map<std::pair<const void *, int>, int> granted;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> guard(lock);
+    int &have = granted[{kernel, device}];
+    if (bytes > have) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) return e;
+        have = bytes;
+    }
+    return cudaSuccess;
 }
-// tuning overrides, read once
-static const int kEnvWarps = env_int("WEFT_B200_GEMV_WARPS", 12);
-static const int kEnvRowsPerLane = env_int("WEFT_B200_GEMV_RL", 1);
-static const int kEnvRingDepth = env_int("WEFT_B200_GEMV_NBUF", 3);
+
+// launch shape (measured on B200)
+constexpr int kEnvWarps = 12;
+constexpr int kEnvRowsPerLane = 1;
+constexpr int kEnvRingDepth = 3;
 
 template <int FMT>
 static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stream) {
@@ -269,12 +284,8 @@ static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stre
 
 #define WEFT_LAUNCH(RLV, BULKV, QXV)                                                                                 \
     do {                                                                                                              \
-        static int smem_set = 0;   /* the attribute sticks to the function: raise it only when a launch needs more */ \
-        if ((int)smem > smem_set) {                                                                                   \
-            cudaError_t e = cudaFuncSetAttribute(gemv_kernel<FMT, RLV, BULKV, QXV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (e != cudaSuccess) return e;                                                                           \
-            smem_set = (int)smem;                                                                                     \
-        }                                                                                                             \
+        cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(gemv_kernel<FMT, RLV, BULKV, QXV>), (int)smem);    \
+        if (e != cudaSuccess) return e;                                                                               \
         gemv_kernel<FMT, RLV, BULKV, QXV><<<grid, warps * 32, smem, stream>>>(p);                                     \
     } while (0)
 #define WEFT_LAUNCH_Q(RLV, BULKV) do { if (qx) WEFT_LAUNCH(RLV, BULKV, true); else WEFT_LAUNCH(RLV, BULKV, false); } while (0)

@@ -334,26 +334,18 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
     }
 }
 
-int env_or(const char *name, int fallback) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : fallback;
-}
 // Measured on B200 for 14336 x 4096: 18 KB stages, 8-deep ring (147 KB in flight per SM), 15 consumer warps.
-const int kQ4kConsumers = env_or("WEFT_B200_Q4K_WARPS", 15);
-const int kQ4kStageBytes = env_or("WEFT_B200_Q4K_STAGE", 18432);
-const int kQ4kMaxStages = env_or("WEFT_B200_Q4K_STAGES", 8);
-const int kQ4kOverlap = env_or("WEFT_B200_Q4K_OVERLAP", 1);
-const int kQ4kSmemCap = env_or("WEFT_B200_Q4K_SMEM_KB", 200);   // per-CTA shared-memory budget tried first
-const int kQ4kInflight = env_or("WEFT_B200_Q4K_INFLIGHT", 3);   // measured: 2 -> 7.8 us, 3 -> 7.05, 4 -> 7.14, 6 -> 7.6, 8 -> 8.1
+constexpr int kQ4kConsumers = 15;
+constexpr int kQ4kStageBytes = 18432;
+constexpr int kQ4kMaxStages = 8;
+constexpr int kQ4kOverlap = 1;
+constexpr int kQ4kSmemCap = 200;   // per-CTA shared-memory budget tried first
+constexpr int kQ4kInflight = 3;   // measured: 2 -> 7.8 us, 3 -> 7.05, 4 -> 7.14, 6 -> 7.6, 8 -> 8.1
 
 template <bool QX, bool XREG, int MODE>
 cudaError_t launch_variant(const Q4kParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
-    static int smem_set = 0;
-    if ((int)smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_q4k_kernel<QX, XREG, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set = (int)smem;
-    }
+    cudaError_t granted = grant_dynamic_smem(reinterpret_cast<const void *>(gemv_q4k_kernel<QX, XREG, MODE>), (int)smem);
+    if (granted != cudaSuccess) return granted;
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = dim3((unsigned)threads);

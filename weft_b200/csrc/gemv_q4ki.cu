@@ -252,20 +252,12 @@ __global__ void interleave_q4k_kernel(const uint8_t *__restrict__ source, uint8_
     }
 }
 
-int env_or(const char *name, int fallback) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : fallback;
-}
-const int kQiInflight = env_or("WEFT_B200_Q4KI_INFLIGHT", 3);
+constexpr int kQiInflight = 3;
 
 template <bool QX>
 cudaError_t launch_variant(const QiParams &p, dim3 grid, size_t smem, cudaStream_t stream) {
-    static int smem_set = 0;
-    if ((int)smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_q4ki_kernel<QX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set = (int)smem;
-    }
+    cudaError_t granted = grant_dynamic_smem(reinterpret_cast<const void *>(gemv_q4ki_kernel<QX>), (int)smem);
+    if (granted != cudaSuccess) return granted;
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = dim3(QI_THREADS);

@@ -198,18 +198,14 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
     }
 }
 
-int env_or(const char *name, int fallback) {
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : fallback;
-}
-const int kRingConsumers = env_or("WEFT_B200_RING_WARPS", 0);   // 0: 15, or kRingIq2Consumers for IQ2_XXS
-const int kRingIq2Consumers = env_or("WEFT_B200_RING_IQ2_WARPS", 27);   // measured 28672 x 8192: 15 -> 29.0 us, 19 -> 28.0, 23 -> 27.1, 27 -> 26.5, 31 -> 26.8
-const int kRingStageBytes = env_or("WEFT_B200_RING_STAGE", 18432);
-const int kRingMaxStages = env_or("WEFT_B200_RING_STAGES", 8);
-const int kRingOverlap = env_or("WEFT_B200_RING_OVERLAP", 1);
-const int kRingInflight = env_or("WEFT_B200_RING_INFLIGHT", 3);
-const int kRingSmemKB = env_or("WEFT_B200_RING_SMEM_KB", 224);
-const int kRingTwoIterations = env_or("WEFT_B200_RING_TWO_ITERATIONS", 1);
+constexpr int kRingConsumers = 0;   // 0: 15, or kRingIq2Consumers for IQ2_XXS
+constexpr int kRingIq2Consumers = 27;   // measured 28672 x 8192: 15 -> 29.0 us, 19 -> 28.0, 23 -> 27.1, 27 -> 26.5, 31 -> 26.8
+constexpr int kRingStageBytes = 18432;
+constexpr int kRingMaxStages = 8;
+constexpr int kRingOverlap = 1;
+constexpr int kRingInflight = 3;
+constexpr int kRingSmemKB = 224;
+constexpr int kRingTwoIterations = 1;
 
 struct RingPlan { int log_lanes, log_stage_rows, log_stages; size_t smem; bool ok; };
 
@@ -238,12 +234,8 @@ RingPlan plan_ring(int fmt, long long nb) {
 
 template <int FMT, bool QX, int RL, bool GATHER>
 cudaError_t launch_variant(const RingParams &p, dim3 grid, int threads, size_t smem, cudaStream_t stream) {
-    static int smem_set = 0;
-    if ((int)smem > smem_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_ring_kernel<FMT, QX, RL, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        smem_set = (int)smem;
-    }
+    cudaError_t granted = grant_dynamic_smem(reinterpret_cast<const void *>(gemv_ring_kernel<FMT, QX, RL, GATHER>), (int)smem);
+    if (granted != cudaSuccess) return granted;
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = dim3((unsigned)threads);

@@ -9,6 +9,10 @@
 
 namespace weft {
 
+// Raises a kernel's dynamic shared-memory limit to at least `bytes` on the CURRENT device.  The attribute belongs
+// to the (function, device) pair, so what was already granted is remembered per device; defined in gemv.cu.
+cudaError_t grant_dynamic_smem(const void *kernel, int bytes);
+
 // W: `elements` logical values as contiguous records of `fmt`; Y: `elements` floats.
 cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                               float *y, long long elements, int sm_count, cudaStream_t stream);

@@ -691,12 +691,10 @@ cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stre
     p.m_tiles = (int)((a.m + PF_BM - 1) / PF_BM);
     p.n_tiles = (int)((a.n + PF_BN - 1) / PF_BN);
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_kernel<F_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<F_Q4_K>::SMEM);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_kernel<F_TQ1_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<F_TQ1_0>::SMEM);
+    {
+        cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_kernel<F_Q4_K>), Cfg<F_Q4_K>::SMEM);
+        if (e == cudaSuccess) e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_kernel<F_TQ1_0>), Cfg<F_TQ1_0>::SMEM);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     // the Q8_K matrix as (m) rows of 73 * nb 32-bit words
     CUtensorMap x_wide, x_narrow;

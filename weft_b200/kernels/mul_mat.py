@@ -93,6 +93,27 @@ def production_mul_mat_tq1_0_decode(W: wl.View[ggml.TQ1_0, (N, K)], X: wl.View[w
     """Decode GEMV, TQ1_0 ternary weights x Q8_K activations."""
 
 
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_tq1_0_lane16_decode(W: wl.View[ggml.TQ1_0, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                           Xq: wl.View[ggml.Q8_K, (M, K)], powers: wl.View[wl.u32, (5,)],
+                                           Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV over the lane16 statement of the TQ1_0 dot product
+    (examples/kernels/mul_mat/tq1_0_lane16_decode.py:10-23): same function as production_mul_mat_tq1_0_decode."""
+
+
+@kernel
+def production_mul_mat_q3_k_predecoded_scales_decode(W: wl.View[ggml.Q3_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                                     Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, Q3_K x Q8_K, under the name of the reference plan that decodes a record's scales ahead of its
+    inner loop (examples/kernels/mul_mat/q3_k_predecoded_scales_decode.py:10-21)."""
+
+
+@kernel
+def production_mul_mat_q3_k_predecoded_scales(W: wl.View[ggml.Q3_K, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                              Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
+    """Tiled form of the same (examples/kernels/mul_mat/q3_k_predecoded_scales.py:10-61)."""
+
+
 @kernel
 def production_mul_mat_q4_0(W: wl.View[ggml.Q4_0, (N, K)], X: wl.View[wl.f32, (M, K)],
                             Xq: wl.View[ggml.Q8_0, (M, K)], Y: wl.View[wl.f32, (M, N)]):

@@ -56,3 +56,10 @@ def quantized_vec_dot_iq2_xxs_q8_k(W: wl.View[ggml.IQ2_XXS, (K,)], X: wl.View[gg
 def quantized_vec_dot_tq1_0_q8_k(W: wl.View[ggml.TQ1_0, (K,)], X: wl.View[ggml.Q8_K, (K,)],
                                  powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (1,)]):
     """Y[0] = sum over 256-blocks of f32(sum((trit - 1) * x)) * (d * x.ds); trits decoded with powers[]."""
+
+
+@kernel
+def quantized_vec_dot_tq1_0_q8_k_lane16(W: wl.View[ggml.TQ1_0, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                        powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (1,)]):
+    """The TQ1_0 dot product as the reference states it for sixteen-wide partial sums
+    (examples/kernels/vec_dot/tq1_0_q8_k_lane16.py:9-54): the per-block integer sum is the same, so is every result."""

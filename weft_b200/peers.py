@@ -12,6 +12,7 @@ import ctypes
 from typing import Callable, Sequence
 
 SYNC_INTS = 32      # the sync block of include/weft_b200.h: int[32], zero-filled by peer_alloc
+STAGE_BYTES = 2 * 8 * 65536   # WEFT_B200_GATHER_STAGE_BYTES: the staging area of the flagged-value protocol, any call shape
 
 
 def exchange_handles(mine: Sequence[bytes], world: int, group=None) -> list[list[bytes]]:

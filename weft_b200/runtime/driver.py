@@ -49,7 +49,7 @@ class Toolchain:
                 if shutil.which(self.cc[0]) is None and not Path("/usr/local/cuda/bin/nvcc").exists():
                     raise CompilationError(f"native toolchain is unavailable: library={library}, CUDA compiler={self.cc[0]}")
                 try:
-                    build.build(extra=list(self.cflags))
+                    build.ensure_built(extra=list(self.cflags))   # file-locked: ranks of one job build once
                 except Exception as error:  # nvcc diagnostics are in the message
                     raise CompilationError(str(error)) from error
         if not library.exists():
