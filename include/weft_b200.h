@@ -43,6 +43,12 @@ int weft_b200_set_stream(void *cuda_stream);         /* NULL = the library's own
 int weft_b200_set_async(int enabled);                /* 1: device-pointer calls return after enqueue */
 int weft_b200_synchronize(void);                     /* wait for the stream and report device-side status */
 unsigned long long weft_b200_launch_count(void);     /* kernels launched by this library so far */
+int weft_b200_peek_status(void);                     /* the raw device status word (0 = none); makes no CUDA call, so it
+                                                        can still be read after the context has reported an error */
+/* Tensor-core issue rate of the bound device, measured: a bare loop of tcgen05.mma instructions (M 128 per SM, N 256)
+ * on every SM, slowest SM's time.  mode 0: kind::i8, K = 32; 1: the same on CTA pairs (cta_group::2); 2: kind::f16,
+ * K = 16.  *tera_ops = 1e12 operations per second.  The roofline denominator of the prefill kernels. */
+int weft_b200_mma_peak(int mode, double *tera_ops);
 /* Keep a device copy of a host weight buffer; later calls that receive an address inside
  * [host, host+bytes) use the copy.  The host bytes must not change while registered. */
 int weft_b200_weights_resident(const void *host, size_t bytes);

@@ -84,6 +84,7 @@ int device_status() {
     const int s = *g.status_host;
     if (s == ST_OK) return 0;
     *g.status_host = 0;
+    if (s & 0x40000000) return fail("device-side failure: tensor memory allocation returned base 0x%08x", (unsigned)(s & 0x3fffffff));
     return fail("device-side failure: %s", s == ST_WAIT_TIMEOUT ? "a bounded wait on an asynchronous copy or MMA ran out"
                                            : s == ST_TMEM_ALLOC ? "tensor memory allocation failed" : "unknown status");
 }
@@ -279,7 +280,8 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
         return 1;
     if (to_prefill) {
         PrefillArgs pa{fmt, w, xq, (const uint32_t *)pw, (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
-        if (launched(launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
+        const bool pair = prefill_pair_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
+        if (launched(pair ? launch_prefill_pair(pa, sms, g.stream) : launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
         if (gather && launched(launch_gather_push(*gather, (long long)M, (long long)N, (long long)ldy, g.status_dev, sms, g.stream), "peer all-gather")) return 1;
     } else {
         GemvArgs ga{fmt, w, xq, fuse_quantize ? (const float *)x : nullptr, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw,
@@ -336,6 +338,8 @@ int weft_b200_synchronize(void) {
 
 unsigned long long weft_b200_launch_count(void) { return g.launches; }
 
+int weft_b200_peek_status(void) { return g.status_host ? *g.status_host : 0; }
+
 int weft_b200_weights_resident(const void *host, size_t bytes) {
     std::lock_guard<std::recursive_mutex> guard(g.lock);
     if (ensure_init(-1)) return 1;
@@ -357,6 +361,32 @@ int weft_b200_weights_release(const void *host) {
     cudaStreamSynchronize(g.stream);
     cudaFree(it->second.device);
     g.resident.erase(it);
+    return 0;
+}
+
+// Tensor-core issue rate of this device: tera-operations per second of a bare tcgen05.mma loop on every SM.
+int weft_b200_mma_peak(int mode, double *tera_ops) {
+    std::lock_guard<std::recursive_mutex> guard(g.lock);
+    if (ensure_init(-1)) return 1;
+    if (mode < 0 || mode > 2 || !tera_ops) return fail("mode must be 0 (int8), 1 (int8, CTA pairs) or 2 (f16), and the result slot non-NULL");
+    const int sms = g.prop.multiProcessorCount, iterations = 8192;
+    unsigned long long *spans = nullptr;
+    CU(cudaMalloc(reinterpret_cast<void **>(&spans), sizeof(unsigned long long) * sms));
+    cudaError_t e = cudaMemsetAsync(spans, 0, sizeof(unsigned long long) * sms, g.stream);
+    double ops = 0.0;
+    for (int pass = 0; pass < 2 && e == cudaSuccess; ++pass)   // the first pass warms the clocks up
+        e = measure_mma_peak(mode, iterations, sms, spans, g.status_dev, g.stream, &ops);
+    std::vector<unsigned long long> host(sms, 0);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
+    if (e == cudaSuccess) e = cudaMemcpy(host.data(), spans, sizeof(unsigned long long) * sms, cudaMemcpyDeviceToHost);
+    cudaFree(spans);
+    if (e != cudaSuccess) return fail("tensor-core peak measurement failed: %s", cudaGetErrorString(e));
+    if (device_status()) return 1;
+    unsigned long long slowest = 0;
+    for (unsigned long long v : host) slowest = v > slowest ? v : slowest;
+    if (!slowest) return fail("tensor-core peak measurement recorded no time");
+    g.launches += 2;
+    *tera_ops = ops / (double)slowest * 1e-3;    // operations per nanosecond = giga-ops; / 1e3 = tera
     return 0;
 }
 

@@ -80,7 +80,7 @@ extern "C" int production_mul_mat_q4_k_decode_noalloc(const uint8_t *W, const fl
         g_scratch_on[device] = static_cast<unsigned char *>(address);
         g_sm_count[device] = sms;
     }
-    if (where_is(W, device) != 1) return refuse("W must be memory of the current device for the no-allocation entry point");
+    if (where_is(W, device) != 1) return refuse("W must be device memory of the current device for the no-allocation entry point");
     // extents that could not fit the fixed scratch anyway are refused before any size is multiplied out
     constexpr size_t kMaxExtent = WEFT_B200_NOALLOC_BYTES / 4;
     const bool host_x = where_is(X, device) == 0, host_xq = where_is(Xq, device) == 0, host_y = where_is(Y, device) == 0;

@@ -75,6 +75,13 @@ struct PrefillArgs {
 // tcgen05 int8 tensor-core path; returns cudaErrorNotSupported for shapes it does not take.
 cudaError_t launch_prefill(const PrefillArgs &a, int sm_count, cudaStream_t stream);
 bool prefill_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
+// The same contraction on CTA pairs (256 tokens per tile, tcgen05 cta_group::2): Q4_K with more than 128 tokens.
+cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream);
+bool prefill_pair_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
+
+// Bare tcgen05.mma issue loop on every SM (mode 0: kind::i8, one CTA per SM; 1: kind::i8 on CTA pairs; 2: kind::f16):
+// spans_dev receives the nanoseconds each issuing CTA took; *ops_per_launch the operations the whole launch performs.
+cudaError_t measure_mma_peak(int mode, int iterations, int sm_count, unsigned long long *spans_dev, int *status, cudaStream_t stream, double *ops_per_launch);
 
 // Push an (m, n_local) column block that this rank has already written into its own buffer (g.y[g.rank], row
 // pitch ldy) to every peer, then run the ranks' barrier: the two-launch form for kernels without fused stores.

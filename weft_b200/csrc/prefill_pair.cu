@@ -1,0 +1,635 @@
+// Prefill contraction for token batches above 128: Q4_K x Q8_K on the int8 tensor cores with CTA PAIRS
+// (tcgen05.mma cta_group::2).  Same function as prefill.cu -- the reference's production_mul_mat_q4_k_staged
+// (examples/kernels/mul_mat/q4_k_staged.py:9-37; per block the math of examples/kernels/vec_dot/q4_k_q8_k.py:8-29,
+// GGML ggml-cpu/quants.c:645-718) -- and the same exact-integer formulation: the 6-bit scale split as 8a + c and
+// folded into two int8 weight limbs, the min term as one K = 16 MMA on exact small f16 integers, activation
+// codes brought in by TMA with the weight operand shifted to meet them (see prefill.cu for the derivation).
+//
+// Tensor-core bound: 2*M*N*K useful integer ops; issued ops are twice that (two limbs).
+//
+// What the pair changes.  A pair of CTAs on the two SMs of a TPC owns a tile of 256 tokens x w weights
+// (w = 16..80 in steps of 16, picked per launch so that the last round of the grid is as full as possible).
+// Each CTA holds its 128 tokens (TMEM lanes, A operand) and expands HALF of the tile's weights: one
+// N = 2w MMA per K step covers both limbs of all w weights, so every Q4_K record is expanded once per 256
+// tokens and the activation slab is read once per block.  Per 256-block and CTA:
+//   raw weights  one TMA box copy of w/2 records (144 B each) into a 4-slot ring, three blocks ahead
+//   activations  five TMA box copies (128 tokens x 304 bytes) into a 3-slot ring
+//   expanders    5 warps, four lanes per weight (lane = one pair of sub-blocks): nibbles -> two scaled limbs,
+//                shifted by the block's operand shift (neighbouring lanes exchange the carried words by
+//                shuffle), written as the K-major 128-byte-swizzled operand; lane layout chosen so that the
+//                16-byte stores of a quarter-warp never meet in a bank
+//   specials     2 warps: x.d of every token to a ring; the bsum pair sums, split as 64 h + l, to f16 in the
+//                two operand columns behind the codes (those bytes only ever meet zero weights in the int8 MMA)
+//   MMA          one lane of the even CTA: 9 int8 K steps (N = 2w) + 1 f16 K = 16 step (N = w), into one of two
+//                TMEM buffers; commits free the operand slots and publish the buffer in BOTH CTAs
+//   epilogue     8 warps = 4 lane quarters x the two halves of the tile's weights; per element
+//                acc += x.d * (d * f32(8 hi + lo) - dmin * msum) in the reference's op order.  The int32
+//                accumulators start at the bit pattern of 1.5 * 2^23 instead of zero (the epilogue writes it
+//                back after every read), so what comes out of TMEM is already the float 1.5 * 2^23 + limb:
+//                one packed subtraction converts two limbs, no integer-to-float instruction is issued.
+// Every wait is bounded; a wait that runs out raises an abort flag in both CTAs, every role leaves its loop,
+// copies in flight are waited for, tensor memory is freed, and the host sees a status code instead of a hang.
+// No copy, store or MMA touches another CTA's shared memory except the 8-byte scale words and the barrier
+// arrivals inside the pair; nothing here reads or writes another GPU's memory.
+#include "prefill_common.cuh"
+#include "kernels.h"
+#include "ring.cuh"
+
+#include <cstddef>
+
+namespace weft {
+
+namespace {
+
+constexpr int PP_TOKENS = 128;                 // tokens per CTA = TMEM lanes; a pair covers 256
+constexpr int PP_RMAX = 80;                    // B rows per CTA at most: [hi limb of w/2 weights | lo limb of w/2 weights]
+constexpr int PP_STAGES = 3;                   // operand slots (activations + expanded weights)
+constexpr int PP_RAW_SLOTS = 4;                // raw-record ring
+constexpr int PP_RING = 8;                     // x.d / weight-scale rings (see the note at their use)
+constexpr int PP_E_WARPS = 8, PP_X_WARPS = 5, PP_X_GROUPS = 1, PP_S_WARPS = 2;   // expander groups take the blocks in turn
+constexpr int PP_X_WARP0 = PP_E_WARPS, PP_S_WARP0 = PP_X_WARP0 + PP_X_GROUPS * PP_X_WARPS;
+constexpr int PP_ATMA_WARP = PP_S_WARP0 + PP_S_WARPS, PP_WTMA_WARP = PP_ATMA_WARP + 1, PP_MMA_WARP = PP_WTMA_WARP + 1;
+constexpr int PP_MMA_WARPS = 2;                 // issuer q takes the blocks with it % 2 == q: one TMEM buffer each
+constexpr int PP_THREADS = 32 * (PP_MMA_WARP + PP_MMA_WARPS);   // 19 warps
+
+// ---- shared memory ---------------------------------------------------------------------------------------
+// A slot: K bytes 0..255 in two 128-byte-swizzled slabs of 128 rows, K bytes 256..303 in three plain 16-byte
+// columns (128 rows x 16 bytes each, i.e. stacked 8 x 16 core matrices).  Columns 1 and 2 are rewritten by the
+// specials warps as the f16 min-term operand {l | h}.
+constexpr int PP_A_SLAB = 128 * 128;
+constexpr int PP_A_COL = 128 * 16;
+constexpr int PP_A_THIN = 2 * PP_A_SLAB;
+constexpr int PP_A_SLOT = PP_A_THIN + 3 * PP_A_COL;          // 38 KB
+// B slot: two swizzled slabs of PP_RMAX rows, two plain columns (the second is always zero), the f16 rows {mn | 64 mn}
+constexpr int PP_B_SLAB = PP_RMAX * 128;
+constexpr int PP_B_COL = PP_RMAX * 16;
+constexpr int PP_B_THIN = 2 * PP_B_SLAB;
+constexpr int PP_B_M = PP_B_THIN + 2 * PP_B_COL;
+constexpr int PP_B_SLOT = 24 * 1024;
+static_assert(PP_B_M + (PP_RMAX / 2) * 32 <= PP_B_SLOT, "B slot");
+constexpr int PP_RAW_HEADS = (PP_RMAX / 2) * 144;            // after the records: the 16-byte headers of the partner's weights
+constexpr int PP_RAW_SLOT = PP_RAW_HEADS + (PP_RMAX / 2) * 16;  // 6400 B
+constexpr int PP_WD_SLOT = 2 * (PP_RMAX / 2) * 8;            // {d, -dmin} per weight of both halves: 640 B
+constexpr int PP_XD_SLOT = PP_TOKENS * 4;
+
+constexpr int PP_CONTROL = 1024;
+constexpr int PP_OFF_A = PP_CONTROL;
+constexpr int PP_OFF_B = PP_OFF_A + PP_STAGES * PP_A_SLOT;
+constexpr int PP_OFF_RAW = PP_OFF_B + PP_STAGES * PP_B_SLOT;
+constexpr int PP_OFF_WD = PP_OFF_RAW + PP_RAW_SLOTS * PP_RAW_SLOT;
+constexpr int PP_OFF_XD = PP_OFF_WD + PP_RING * PP_WD_SLOT;
+constexpr int PP_SMEM = PP_OFF_XD + PP_RING * PP_XD_SLOT;
+static_assert(PP_OFF_A % 1024 == 0 && PP_A_SLOT % 1024 == 0 && PP_OFF_B % 1024 == 0 && PP_B_SLOT % 1024 == 0, "swizzled slabs must stay 1024-byte aligned");
+static_assert(PP_B_SLAB % 1024 == 0 && PP_OFF_RAW % 128 == 0 && PP_RAW_SLOT % 128 == 0, "alignment of the rings");
+static_assert(PP_SMEM <= 227 * 1024, "shared memory budget");
+
+// ---- tensor memory: two buffers of 256 columns; limbs [0, 2w), min term [160, 160 + w) ----------------------
+constexpr int PP_TMEM_COLS = 512;
+constexpr int PP_BUF_COLS = 256;
+constexpr int PP_MIN_COL = 2 * PP_RMAX;
+constexpr uint32_t PP_BIAS = 0x4b400000u;      // bit pattern of 1.5 * 2^23 = 12582912.f
+
+struct PairParams {
+    float *y;              // (m, ldy)
+    long long n, m, ldy;
+    int nb;                // 256-blocks per row
+    int m_tiles, n_tiles;  // tiles of 256 tokens, of w weights
+    int w;                 // weights per tile (multiple of 16, <= PP_RMAX)
+    int *status;
+};
+
+struct PairControl {
+    uint64_t a_landed[PP_STAGES];        // this CTA's activation boxes (transaction bytes)
+    uint64_t raw_full[PP_RAW_SLOTS];     // this CTA's raw records (transaction bytes)
+    uint64_t raw_empty[PP_RAW_SLOTS];    // expander warps of this CTA are done reading the slot
+    uint64_t ab_full[PP_STAGES];         // EVEN CTA's copy is the live one: expander + specials warps of both CTAs
+    uint64_t ab_empty[PP_STAGES];        // both copies live: the MMAs that read the slot have completed
+    uint64_t tmem_full[2];               // both copies live: the buffer's accumulators are complete
+    uint64_t tmem_empty[2];              // EVEN CTA's copy is the live one: epilogue warps of both CTAs
+    uint32_t tmem_base;
+    volatile int abort;
+};
+static_assert(sizeof(PairControl) <= PP_CONTROL, "control block");
+
+// Bounded wait by one thread; gives up as soon as another role (of either CTA) has raised the abort flag.
+__device__ __forceinline__ bool pp_wait_one(uint64_t *bar, uint32_t parity, PairControl *ctl, uint32_t peer_abort, int *status) {
+    const uint32_t addr = smem_addr(bar);
+    for (uint32_t i = 0; i < (1u << 26); ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if ((i & 63u) == 63u && ctl->abort) return false;
+    }
+    ctl->abort = 1;
+    tc::st_cluster_u32(peer_abort, 1u);
+    report(status, ST_WAIT_TIMEOUT);
+    return false;
+}
+// The same for a whole warp: every lane waits on the barrier itself with the suspending form (a waiting warp then
+// takes no issue slots from the working ones; measured 214 -> 159 us per launch against one polling lane per warp).
+__device__ __forceinline__ bool pp_wait_warp(uint64_t *bar, uint32_t parity, PairControl *ctl, uint32_t peer_abort, int *status) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (ctl->abort) return false;
+    }
+    if ((threadIdx.x & 31) == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(status, ST_WAIT_TIMEOUT); }
+    return false;
+}
+
+// Blocks of the pair's work list: tiles round-robin over the pairs; inside a tile the blocks are taken as
+// 0, 4, 8, ..., 1, 5, 9, ..., so that blocks with the same operand shift follow each other and the producers stay
+// in one of their four code variants for a quarter of the tile.
+struct PairAt {
+    long long n0, m0;
+    int b, tile, pairs;
+    __device__ __forceinline__ void set_tile(const PairParams &p, int t) {
+        tile = t;
+        n0 = (long long)(t / p.m_tiles) * p.w;
+        m0 = (long long)(t % p.m_tiles) * (2 * PP_TOKENS);
+    }
+    __device__ __forceinline__ void advance(const PairParams &p) {
+        b += 4;
+        if (b >= p.nb) {
+            b = (b & 3) + 1;
+            if (b == 4) { b = 0; set_tile(p, tile + pairs); }
+        }
+    }
+};
+__device__ __forceinline__ PairAt pair_first(const PairParams &p, int pair, int pairs) {
+    PairAt at;
+    at.b = 0;
+    at.pairs = pairs;
+    at.set_tile(p, pair);
+    return at;
+}
+
+// ---- expanders -----------------------------------------------------------------------------------------------
+// Lane (i8, j): weight i8 = 0..7 of the warp's eight, part j = 0..3 (sub-blocks 2j and 2j+1, weights 64j..64j+63 of
+// the block).  lane = 16 (j >> 1) + 2 i8 + (j & 1): the four parts of the weights in one quarter-warp store to
+// distinct 16-byte bank groups of the swizzled rows.
+// The limb bytes of a block form a stream of 64 words per limb; part j owns stream words 16j..16j+15.  With the
+// operand shift of W words they land at K words 16j + W .., so an output chunk (4 words) takes its first words from
+// the previous part: those W words come over by shuffle.
+template <int W>
+__device__ __forceinline__ void pp_expand(uint32_t raw, uint32_t partner_head, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner, int i, int j, int half_rows, bool active) {
+    const int lane = threadIdx.x & 31;
+    uint4 hd = make_uint4(0, 0, 0, 0), qa = hd, qb = hd;
+    if (active) {
+        hd = lds128(raw);
+        qa = lds128(raw + 16 + 32 * j);
+        qb = lds128(raw + 32 + 32 * j);
+    }
+    const Q4KScales s = q4k_unpack_scales(hd.y, hd.z, hd.w);
+    const uint32_t scv = j < 2 ? s.sc_lo : s.sc_hi;
+    const uint32_t sl = byte_of(scv, (2 * j) & 3), sh = byte_of(scv, ((2 * j) & 3) + 1);
+    const uint32_t al = sl >> 3, cl = sl & 7u, ah = sh >> 3, ch = sh & 7u;
+    uint32_t cur_a[16], cur_c[16];
+    {
+        const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t lo = q[k] & 0x0f0f0f0fu, hi = (q[k] >> 4) & 0x0f0f0f0fu;
+            // every byte product is <= 15 * 7 = 105: one 32-bit multiply scales four weights
+            cur_a[k] = lo * al;      cur_c[k] = lo * cl;
+            cur_a[8 + k] = hi * ah;  cur_c[8 + k] = hi * ch;
+        }
+    }
+    // the last W stream words of the previous part (zeros in front of part 0)
+    const int src = j == 0 ? lane : (16 * ((j - 1) >> 1) + (lane & 14) + ((j - 1) & 1));
+    uint32_t ca[4] = {0, 0, 0, 0}, cc[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int k = 0; k < W; ++k) {
+        const uint32_t va = __shfl_sync(0xffffffffu, cur_a[16 - W + k], src);
+        const uint32_t vc = __shfl_sync(0xffffffffu, cur_c[16 - W + k], src);
+        ca[k] = j == 0 ? 0u : va;
+        cc[k] = j == 0 ? 0u : vc;
+    }
+    if (!active) return;
+    // rows i (hi limb) and half_rows + i (lo limb): same position inside the 8-row group, half_rows * 128 bytes apart
+    const uint32_t base = b_slot + (uint32_t)(i >> 3) * 1024u + (uint32_t)(i & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(i & 7) << 4;
+    const uint32_t lo_limb = (uint32_t)half_rows * 128u;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint32_t oa[4], oc[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int idx = 4 * q + k;
+            oa[k] = idx < W ? ca[idx < W ? idx : 0] : cur_a[idx < W ? 0 : idx - W];
+            oc[k] = idx < W ? cc[idx < W ? idx : 0] : cur_c[idx < W ? 0 : idx - W];
+        }
+        const int chunk = 4 * j + q;   // 16-byte K chunk 0..15
+        const uint32_t at = base + (uint32_t)(chunk >> 3) * PP_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7);
+        sts_u128(at, oa[0], oa[1], oa[2], oa[3]);
+        sts_u128(at + lo_limb, oc[0], oc[1], oc[2], oc[3]);
+    }
+    if (j == 3) {   // K chunk 16: the carried words of the last part, then zeros (chunk 17 stays zero for ever)
+        const uint32_t thin = b_slot + PP_B_THIN + (uint32_t)i * 16u;
+        sts_u128(thin, cur_a[16 - W], W > 1 ? cur_a[17 - W] : 0u, W > 2 ? cur_a[18 - W] : 0u, W > 3 ? cur_a[19 - W] : 0u);
+        sts_u128(thin + (uint32_t)half_rows * 16u, cur_c[16 - W], W > 1 ? cur_c[17 - W] : 0u, W > 2 ? cur_c[18 - W] : 0u, W > 3 ? cur_c[19 - W] : 0u);
+    } else if (j == 0) {   // {mn} and {64 mn} as f16: the min-term rows of this weight
+        const uint32_t bm = b_slot + PP_B_M + core_offset(i, 0, 2);
+        float mn[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) mn[g] = (float)byte_of(g < 4 ? s.mn_lo : s.mn_hi, g & 3);
+        sts_u128(bm, pack_half2(mn[0], mn[1]), pack_half2(mn[2], mn[3]), pack_half2(mn[4], mn[5]), pack_half2(mn[6], mn[7]));
+        sts_u128(bm + 128u, pack_half2(64.f * mn[0], 64.f * mn[1]), pack_half2(64.f * mn[2], 64.f * mn[3]),
+                 pack_half2(64.f * mn[4], 64.f * mn[5]), pack_half2(64.f * mn[6], 64.f * mn[7]));
+    } else {       // {d, -dmin} for the epilogue: part 1 takes this CTA's weight i, part 2 weight i of the partner's half
+        const uint32_t dd = j == 1 ? hd.x : lds_u32(partner_head);
+        const uint32_t d = __float_as_uint(half_bits_to_float(dd)), nm = __float_as_uint(-half_bits_to_float(dd >> 16));
+        // per pair of weights {d, d', -dmin, -dmin'}
+        const uint32_t at = (j == 1 ? wd_mine : wd_partner) + 16u * (uint32_t)(i >> 1) + 4u * (uint32_t)(i & 1);
+        sts_u32(at, d);
+        sts_u32(at + 8u, nm);
+    }
+}
+
+// ---- specials --------------------------------------------------------------------------------------------------
+// One token row per call: x.d to the ring; the eight bsum pair sums s = 64 h + l (l in 0..63) as f16 into operand
+// columns 1 (l) and 2 (h) of the row.  W = (b & 3) + 1: record byte r sits at operand byte r + 4 (W - 1).
+template <int W>
+__device__ __forceinline__ void pp_special_row(uint32_t a_slot, uint32_t xd_slot, int row) {
+    const uint32_t thin = a_slot + PP_A_THIN + (uint32_t)row * 16u;
+    const uint4 c0 = lds128(thin), c1 = lds128(thin + PP_A_COL), c2 = lds128(thin + 2 * PP_A_COL);
+    const uint32_t w[12] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w, c2.x, c2.y, c2.z, c2.w};
+    const uint32_t xd = lds_u32(a_slot + sw128_offset(row, 0) + 4u * (uint32_t)(W - 1));
+    uint32_t l2[4], h2[4];
+#pragma unroll
+    for (int g = 0; g < 8; g += 2) {
+        int s0, s1;   // bsums 2g, 2g+1 are record bytes 260 + 4g ..: operand word 65 + g + (W - 1) = thin word g + W
+        asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(s0) : "r"(w[g + W]), "r"(0x0101u), "r"(0));
+        asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(s1) : "r"(w[g + 1 + W]), "r"(0x0101u), "r"(0));
+        const int l0 = s0 & 63, l1 = s1 & 63;
+        l2[g >> 1] = (uint32_t)__half_as_ushort(__int2half_rn(l0)) | ((uint32_t)__half_as_ushort(__int2half_rn(l1)) << 16);
+        h2[g >> 1] = (uint32_t)__half_as_ushort(__int2half_rn((s0 - l0) >> 6)) | ((uint32_t)__half_as_ushort(__int2half_rn((s1 - l1) >> 6)) << 16);
+    }
+    sts_u128(thin + PP_A_COL, l2[0], l2[1], l2[2], l2[3]);
+    sts_u128(thin + 2 * PP_A_COL, h2[0], h2[1], h2[2], h2[3]);
+    sts_u32(xd_slot + 4u * (uint32_t)row, xd);
+}
+
+__device__ __forceinline__ void pp_issue_activations(const CUtensorMap *wide, const CUtensorMap *narrow, int b, int m0, uint8_t *slot, uint64_t *bar) {
+    // word x0 = 73 b - (b & 3) of a token row is the 16-byte boundary at or before record b
+    const int x0 = 73 * b - (b & 3);
+    mbar_expect_tx(bar, PP_A_SLOT);
+    tma_load_2d(slot, wide, x0, m0, bar);
+    tma_load_2d(slot + PP_A_SLAB, wide, x0 + 32, m0, bar);
+    tma_load_2d(slot + PP_A_THIN, narrow, x0 + 64, m0, bar);
+    tma_load_2d(slot + PP_A_THIN + PP_A_COL, narrow, x0 + 68, m0, bar);
+    tma_load_2d(slot + PP_A_THIN + 2 * PP_A_COL, narrow, x0 + 72, m0, bar);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PP_THREADS, 1)
+prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap x_wide, const __grid_constant__ CUtensorMap x_narrow,
+                        const __grid_constant__ CUtensorMap w_rows, const __grid_constant__ CUtensorMap w_heads) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    PairControl *ctl = reinterpret_cast<PairControl *>(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();          // 0: issues the MMAs; 1: partner
+    const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int nb = p.nb;
+    const int my_tiles = (tiles - pair + pairs - 1) / pairs;
+    const int total = my_tiles * nb;                      // 256-blocks the pair works through
+    const int half_rows = p.w >> 1;                       // weights this CTA expands per block = rows per limb
+    const int R = p.w;                                    // B rows per CTA
+
+    // where the partner and the even CTA keep their copies of the control block
+    const uint32_t ctl_addr = smem_addr(ctl);
+    const uint32_t ctl_even = tc::map_to_cta(ctl_addr, 0), ctl_peer = tc::map_to_cta(ctl_addr, rank ^ 1u);
+    const uint32_t peer_abort = ctl_peer + (uint32_t)offsetof(PairControl, abort);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PP_STAGES; ++s) {
+            mbar_init(&ctl->a_landed[s], 1);
+            mbar_init(&ctl->ab_full[s], 2 * (PP_X_WARPS + PP_S_WARPS));
+            mbar_init(&ctl->ab_empty[s], 1);
+        }
+        for (int s = 0; s < PP_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 1); mbar_init(&ctl->raw_empty[s], PP_X_WARPS); }
+        for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 2 * PP_E_WARPS); }
+        ctl->abort = 0;
+        ctl->tmem_base = 0xffffffffu;
+        mbar_fence_init();
+    }
+    // K chunk 17 of every weight slot (operand bytes 272..287) is zero for the whole kernel
+    for (int i = threadIdx.x; i < PP_STAGES * PP_RMAX * 4; i += PP_THREADS) {
+        const int s = i / (PP_RMAX * 4), r = i % (PP_RMAX * 4);
+        reinterpret_cast<uint32_t *>(smem + PP_OFF_B + s * PP_B_SLOT + PP_B_THIN + PP_B_COL)[r] = 0u;
+    }
+    fence_proxy_async();
+    __syncthreads();
+    // Each CTA allocates its own tensor memory (cta_group::1: no pair-wide allocation protocol); the pair's MMAs then
+    // use the same columns in both.
+    if (warp == PP_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PP_TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync_all();          // barriers of both CTAs are initialised before anyone arrives on the partner's
+    tc::fence_after_sync();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&ctl->tmem_base);
+    // The pair asked for all 512 columns, so the only valid base is lane 0, column 0; anything else means the allocation
+    // went wrong: say so and take no role (the partner's waits are bounded).
+    const bool tmem_ok = tmem == 0u;
+    if (!tmem_ok && threadIdx.x == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(p.status, 0x40000000 | (int)(tmem & 0xffffu) | (int)((tmem >> 16) & 0x3fffu) << 16); }
+    if (!tmem_ok) {
+        // nothing: fall through to the common exit
+    } else if (warp >= PP_X_WARP0 && warp < PP_X_WARP0 + PP_X_GROUPS * PP_X_WARPS) {
+        // ------------------------------------------------------------------ expanders
+        const int xw = (warp - PP_X_WARP0) % PP_X_WARPS, xg = (warp - PP_X_WARP0) / PP_X_WARPS;
+        const int i8 = (lane >> 1) & 7, j = (lane & 1) | ((lane >> 4) << 1);
+        const int i = 8 * xw + i8;
+        const bool active = i < half_rows;
+        PairAt at = pair_first(p, pair, pairs);
+        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
+        for (int skip = 0; skip < xg && skip < total; ++skip) at.advance(p);
+        for (int it = xg; it < total && !ctl->abort; it += PP_X_GROUPS) {
+            const int words = (at.b & 3) + 1;
+            for (int skip = 0; skip < PP_X_GROUPS; ++skip) at.advance(p);
+            const int s = it % PP_STAGES, rs = it % PP_RAW_SLOTS;
+            if (!pp_wait_warp(&ctl->raw_full[rs], (uint32_t)(it / PP_RAW_SLOTS) & 1u, ctl, peer_abort, p.status)) break;
+            if (!pp_wait_warp(&ctl->ab_empty[s], ((uint32_t)(it / PP_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+            const uint32_t raw_slot = smem_addr(smem + PP_OFF_RAW + rs * PP_RAW_SLOT);
+            const uint32_t raw = raw_slot + (uint32_t)i * 144u, partner_head = raw_slot + PP_RAW_HEADS + (uint32_t)i * 16u;
+            const uint32_t b_slot = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
+            // the scales of the tile's weights, this CTA's half and the partner's, in the order of the tile
+            const uint32_t wd_slot = smem_addr(smem + PP_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT);
+            const uint32_t wd_mine = wd_slot + rank * (uint32_t)(PP_WD_SLOT / 2), wd_partner = wd_slot + (rank ^ 1u) * (uint32_t)(PP_WD_SLOT / 2);
+            switch (words) {
+            case 1: pp_expand<1>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
+            case 2: pp_expand<2>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
+            case 3: pp_expand<3>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
+            default: pp_expand<4>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
+            }
+            fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&ctl->raw_empty[rs]);
+                tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
+            }
+        }
+    } else if (warp >= PP_S_WARP0 && warp < PP_S_WARP0 + PP_S_WARPS) {
+        // ------------------------------------------------------------------ x.d and the min-term operand of the landed activations
+        const int ts = threadIdx.x - 32 * PP_S_WARP0;   // 0..63, rows ts and ts + 64
+        PairAt at = pair_first(p, pair, pairs);
+        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
+        for (int it = 0; it < total && !ctl->abort; ++it) {
+            const int words = (at.b & 3) + 1;
+            at.advance(p);
+            const int s = it % PP_STAGES;
+            if (!pp_wait_warp(&ctl->a_landed[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+            const uint32_t a_slot = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT);
+            const uint32_t xd_slot = smem_addr(smem + PP_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int row = ts + 64 * k;
+                switch (words) {
+                case 1: pp_special_row<1>(a_slot, xd_slot, row); break;
+                case 2: pp_special_row<2>(a_slot, xd_slot, row); break;
+                case 3: pp_special_row<3>(a_slot, xd_slot, row); break;
+                default: pp_special_row<4>(a_slot, xd_slot, row); break;
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
+        }
+    } else if (warp == PP_ATMA_WARP) {
+        // ------------------------------------------------------------------ activation copies (this CTA's 128 tokens)
+        if (lane == 0) {
+            PairAt at = pair_first(p, pair, pairs);
+            int issued = 0;
+            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
+                const int s = it % PP_STAGES;
+                const uint32_t phase = (uint32_t)(it / PP_STAGES) & 1u;
+                // the slot was last read by the MMAs of block it - PP_STAGES (and, before them, by the specials warps)
+                if (!pp_wait_one(&ctl->ab_empty[s], phase ^ 1u, ctl, peer_abort, p.status)) break;
+                fence_proxy_async();
+                pp_issue_activations(&x_wide, &x_narrow, at.b, (int)at.m0 + (int)rank * PP_TOKENS, smem + PP_OFF_A + s * PP_A_SLOT, &ctl->a_landed[s]);
+                issued = it + 1;
+            }
+            // left early: let the copies in flight land (a phase that has completed already returns at once)
+            for (int k = issued > PP_STAGES ? issued - PP_STAGES : 0; k < issued; ++k) mbar_wait(&ctl->a_landed[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u);
+            // The even CTA's commits arrive on this CTA's barriers when the MMAs complete, whoever still waits for them:
+            // stay until the last ones have landed, so that none can reach a CTA that has already left the SM.
+            for (int k = total > PP_STAGES ? total - PP_STAGES : 0; k < total && !ctl->abort; ++k)
+                if (!pp_wait_one(&ctl->ab_empty[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+        }
+    } else if (warp == PP_WTMA_WARP) {
+        // ------------------------------------------------------------------ raw weight records (this CTA's half of the tile's weights)
+        if (lane == 0) {
+            PairAt at = pair_first(p, pair, pairs);
+            int issued = 0;
+            const uint32_t bytes = (uint32_t)half_rows * 160u;   // this CTA's records and the 16-byte headers of the partner's
+            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
+                const int rs = it % PP_RAW_SLOTS;
+                if (!pp_wait_one(&ctl->raw_empty[rs], ((uint32_t)(it / PP_RAW_SLOTS) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+                mbar_expect_tx(&ctl->raw_full[rs], bytes);
+                // rows past N read as zero records (d = dmin = 0: they contribute nothing and are never stored)
+                tma_load_2d(smem + PP_OFF_RAW + rs * PP_RAW_SLOT, &w_rows, 36 * at.b, (int)at.n0 + (int)rank * half_rows, &ctl->raw_full[rs]);
+                tma_load_2d(smem + PP_OFF_RAW + rs * PP_RAW_SLOT + PP_RAW_HEADS, &w_heads, 36 * at.b, (int)at.n0 + (int)(rank ^ 1u) * half_rows, &ctl->raw_full[rs]);
+                issued = it + 1;
+            }
+            for (int k = issued > PP_RAW_SLOTS ? issued - PP_RAW_SLOTS : 0; k < issued; ++k) mbar_wait(&ctl->raw_full[k % PP_RAW_SLOTS], (uint32_t)(k / PP_RAW_SLOTS) & 1u);
+        }
+    } else if (warp >= PP_MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issue (even CTA only), two issuers
+        // One thread's wait / issue / commit sequence takes longer than the MMAs of a block run, so two threads take the
+        // blocks in turn; each owns one TMEM buffer, and a commit covers the issuing thread's own MMAs only.
+        const int q = warp - PP_MMA_WARP;
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc_q = tc::idesc_i8(2 * PP_TOKENS, 2 * R, true, true);
+            const uint32_t idesc_m = tc::idesc_f16_f32acc(2 * PP_TOKENS, R);
+            const uint32_t full_mine = smem_addr(&ctl->tmem_full[q]), full_peer = ctl_peer + (uint32_t)offsetof(PairControl, tmem_full) + 8u * (uint32_t)q;
+            const uint32_t empty_peer = ctl_peer + (uint32_t)offsetof(PairControl, ab_empty);
+            const uint32_t d = tmem + (uint32_t)q * PP_BUF_COLS;
+            int last = -1;
+            for (int it = q; it < total && !ctl->abort; it += PP_MMA_WARPS) {
+                const int s = it % PP_STAGES;
+                if (!pp_wait_one(&ctl->ab_full[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                // arrival n on tmem_empty: n = 0 the initial fill, n >= 1 after the epilogue of the buffer's n-th use
+                if (!pp_wait_one(&ctl->tmem_empty[q], (uint32_t)(it >> 1) & 1u, ctl, peer_abort, p.status)) break;
+                tc::fence_after_sync();
+                const uint32_t a_q = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT), b_q = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
+                const uint64_t a0 = tc::smem_desc_sw128(a_q), b0 = tc::smem_desc_sw128(b_q);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)   // K = 32 per instruction: 32 bytes further inside the swizzled row, next slab after 4 (address field in 16-byte units)
+                    tc::mma_i8_pair(d, a0 + (uint64_t)(((k >> 2) * PP_A_SLAB + (k & 3) * 32) >> 4), b0 + (uint64_t)(((k >> 2) * PP_B_SLAB + (k & 3) * 32) >> 4), idesc_q, 1);
+                // K bytes 256..287: two 16-byte columns, K-adjacent core matrices one column apart
+                tc::mma_i8_pair(d, tc::smem_desc(a_q + PP_A_THIN, PP_A_COL, 128), tc::smem_desc(b_q + PP_B_THIN, PP_B_COL, 128), idesc_q, 1);
+                // min term: A = {l | h} in operand columns 1 and 2, B = {mn | 64 mn}
+                tc::mma_f16_pair(d + PP_MIN_COL, tc::smem_desc(a_q + PP_A_THIN + PP_A_COL, PP_A_COL, 128), tc::smem_desc(b_q + PP_B_M, 128, 256), idesc_m, 0);
+                tc::commit_pair(full_mine);
+                tc::commit_pair(full_peer);
+                tc::commit_pair(smem_addr(&ctl->ab_empty[s]));
+                tc::commit_pair(empty_peer + 8u * (uint32_t)s);
+                last = it;
+            }
+            // the epilogues of both CTAs arrive once more after the last use of the buffer: receive those arrivals
+            // before this CTA may leave
+            if (last >= 0 && !ctl->abort) pp_wait_one(&ctl->tmem_empty[q], ((uint32_t)(last >> 1) + 1u) & 1u, ctl, peer_abort, p.status);
+        }
+    } else if (warp < PP_E_WARPS) {
+        // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, half of the tile's weights)
+        const int quarter = warp & 3, grp = warp >> 2;
+        const int row = quarter * 32 + lane;               // token row of this CTA = TMEM lane
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t empty_even = ctl_even + (uint32_t)offsetof(PairControl, tmem_empty);
+        const int chunks = half_rows >> 3;                  // groups of 8 weights
+        // accumulators start at the bit pattern of 1.5 * 2^23
+        for (int buf = 0; buf < 2; ++buf) {
+            for (int c = 0; c < 2 * chunks; ++c) tc::tmem_st8_fill(lane_base + (uint32_t)(buf * PP_BUF_COLS + grp * R + 8 * c), PP_BIAS);
+            tc::tmem_st_wait();
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
+        }
+        uint64_t acc[PP_RMAX / 4];   // packed pairs of fp32: up to 40 weights
+        const uint64_t bias2 = pack2(-12582912.f, -12582912.f), eight2 = pack2(8.f, 8.f);
+        int it = 0;
+        bool ok = true;
+        for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
+            const int tile = pair + t * pairs;
+            const long long n0 = (long long)(tile / p.m_tiles) * p.w + grp * half_rows;
+            const long long m = (long long)(tile % p.m_tiles) * (2 * PP_TOKENS) + (long long)rank * PP_TOKENS + row;
+#pragma unroll
+            for (int k = 0; k < PP_RMAX / 4; ++k) acc[k] = 0ull;
+            for (int b = 0; b < nb && ok; ++b, ++it) {
+                const int buf = it & 1;
+                if (!pp_wait_warp(&ctl->tmem_full[buf], (uint32_t)(it >> 1) & 1u, ctl, peer_abort, p.status)) { ok = false; break; }
+                tc::fence_after_sync();
+                // The rings are PP_RING deep: the slot of block it is rewritten for block it + PP_RING, whose producers run
+                // only after the MMAs of block it + PP_RING - PP_STAGES, and those need this epilogue to have freed the buffer.
+                const float xd = reinterpret_cast<const float *>(smem + PP_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT)[row];
+                const ulonglong2 *wd = reinterpret_cast<const ulonglong2 *>(smem + PP_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT + grp * (PP_WD_SLOT / 2));
+                const uint64_t xd2 = pack2(xd, xd);
+                const uint32_t limb = lane_base + (uint32_t)(buf * PP_BUF_COLS + grp * R);
+                const uint32_t mins = lane_base + (uint32_t)(buf * PP_BUF_COLS + PP_MIN_COL + grp * half_rows);
+#pragma unroll
+                for (int c = 0; c < PP_RMAX / 16; ++c) {
+                    if (c < chunks) {
+                        uint32_t hi[8], lo[8], mt[8];
+                        tc::tmem_ld8(limb + 8 * c, hi);
+                        tc::tmem_ld8(limb + half_rows + 8 * c, lo);
+                        tc::tmem_ld8(mins + 8 * c, mt);
+                        tc::tmem_ld_wait();
+                        tc::tmem_st8_fill(limb + 8 * c, PP_BIAS);
+                        tc::tmem_st8_fill(limb + half_rows + 8 * c, PP_BIAS);
+#pragma unroll
+                        for (int k = 0; k < 8; k += 2) {
+                            const ulonglong2 s2 = wd[(8 * c + k) >> 1];   // {d, d'}, {-dmin, -dmin'}
+                            // limbs arrive as 1.5 * 2^23 + integer: subtracting the constant is exact; f32(8 hi + lo) rounds once
+                            const uint64_t fh = add2(pack2(__uint_as_float(hi[k]), __uint_as_float(hi[k + 1])), bias2);
+                            const uint64_t fl = add2(pack2(__uint_as_float(lo[k]), __uint_as_float(lo[k + 1])), bias2);
+                            const uint64_t v = fma2(eight2, fh, fl);
+                            const uint64_t u = fma2(s2.y, pack2(__uint_as_float(mt[k]), __uint_as_float(mt[k + 1])), mul2(s2.x, v));
+                            acc[(8 * c + k) >> 1] = fma2(xd2, u, acc[(8 * c + k) >> 1]);
+                        }
+                    }
+                }
+                tc::tmem_st_wait();
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
+            }
+            if (!ok) break;
+            if (m < p.m) {
+                float *out = p.y + (size_t)m * p.ldy + n0;
+                const bool vec = (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+#pragma unroll
+                for (int k = 0; k < PP_RMAX / 2; k += 4) {
+                    if (k < half_rows) {
+                        if (vec && n0 + k + 4 <= p.n) {
+                            *reinterpret_cast<ulonglong2 *>(out + k) = make_ulonglong2(acc[k >> 1], acc[(k >> 1) + 1]);
+                        } else {
+                            float a0, a1, a2, a3;
+                            unpack2(acc[k >> 1], a0, a1);
+                            unpack2(acc[(k >> 1) + 1], a2, a3);
+                            if (n0 + k < p.n) out[k] = a0;
+                            if (n0 + k + 1 < p.n) out[k + 1] = a1;
+                            if (n0 + k + 2 < p.n) out[k + 2] = a2;
+                            if (n0 + k + 3 < p.n) out[k + 3] = a3;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync_all();      // neither CTA leaves, or frees tensor memory, while the other may still use the pair's resources
+    if (warp == PP_MMA_WARP) {
+        __syncwarp();
+        if (tmem_ok) tc::tmem_free(tmem, PP_TMEM_COLS);
+    }
+}
+
+// w in {16, 32, 48, 64, 80}.  A block costs a fixed part (hand-offs, activations, the per-token work) plus a part that
+// grows with w; measured, the fixed part is about the size of the variable part at w = 80.  Pick the w that minimises
+// (rounds of the grid) x (80 + w), ties to the wider tile.
+int pick_tile_width(long long n, int m_tiles, int pairs) {
+    int best = 16;
+    long long best_cost = -1;
+    for (int w = 16; w <= PP_RMAX; w += 16) {
+        const long long tiles = (long long)m_tiles * ((n + w - 1) / w);
+        const long long cost = ((tiles + pairs - 1) / pairs) * (80 + w);
+        if (best_cost < 0 || cost <= best_cost) { best = w; best_cost = cost; }
+    }
+    return best;
+}
+
+}  // namespace
+
+bool prefill_pair_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq) {
+    // above 128 tokens a pair's second CTA has work; K a multiple of 1024 keeps every Q8_K row a whole number of 16-byte
+    // units (TMA boxes), and Q4_K rows of 16-byte multiples at a 16-byte aligned base let TMA fetch the raw records
+    return fmt == F_Q4_K && m > PP_TOKENS && k > 0 && k % 1024 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
+           (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
+}
+
+cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
+    if (!prefill_pair_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
+    cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_SMEM);
+    if (e != cudaSuccess) return e;
+    // how many pairs the device can hold at once (one CTA per SM: the shared memory of a CTA fills an SM)
+    int pairs = 0;
+    {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3((unsigned)sm_count & ~1u);
+        probe.blockDim = dim3(PP_THREADS);
+        probe.dynamicSmemBytes = PP_SMEM;
+        if (cudaOccupancyMaxActiveClusters(&pairs, prefill_pair_q4k_kernel, &probe) != cudaSuccess) { cudaGetLastError(); pairs = sm_count / 2; }
+        if (pairs < 1) return cudaErrorNotSupported;
+        if (pairs > sm_count / 2) pairs = sm_count / 2;
+    }
+    PairParams p;
+    p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
+    p.m_tiles = (int)((a.m + 2 * PP_TOKENS - 1) / (2 * PP_TOKENS));
+    p.w = pick_tile_width(a.n, p.m_tiles, pairs);
+    p.n_tiles = (int)((a.n + p.w - 1) / p.w);
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles < pairs) pairs = (int)tiles;
+    // the Q8_K matrix as (m) rows of 73 * nb 32-bit words; the weight matrix as (n) rows of 36 * nb words
+    CUtensorMap x_wide, x_narrow, w_rows;
+    e = encode_tile_map(&x_wide, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
+                        (unsigned long long)p.nb * 292, 32, PP_TOKENS, true);
+    if (e == cudaSuccess)
+        e = encode_tile_map(&x_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
+                            (unsigned long long)p.nb * 292, 4, PP_TOKENS, false);
+    if (e == cudaSuccess)
+        e = encode_tile_map(&w_rows, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.w, (unsigned long long)p.nb * 36, (unsigned long long)a.n,
+                            (unsigned long long)p.nb * 144, 36, (unsigned)(p.w / 2), false);
+    CUtensorMap w_heads;
+    if (e == cudaSuccess)
+        e = encode_tile_map(&w_heads, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.w, (unsigned long long)p.nb * 36, (unsigned long long)a.n,
+                            (unsigned long long)p.nb * 144, 4, (unsigned)(p.w / 2), false);
+    if (e != cudaSuccess) return e;
+    prefill_pair_q4k_kernel<<<2 * pairs, PP_THREADS, PP_SMEM, stream>>>(p, x_wide, x_narrow, w_rows, w_heads);
+    return cudaGetLastError();
+}
+
+}  // namespace weft
