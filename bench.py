@@ -451,8 +451,9 @@ def gpu_layer_decode(args, lib, check, stream, fmt, hidden, world, rank, local_r
     print(json.dumps(line))
 
 
-def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank) -> None:
-    """row_dequantize over an (n, k) matrix, rows split across ranks (no collective: rows are independent)."""
+def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank, *, extras: bool = True):
+    """row_dequantize over an (n, k) matrix, rows split across ranks (no collective: rows are independent).
+    Returns the JSON record on rank 0, None on the others; extras = False leaves out the end-to-end and CPU legs."""
     import torch
     import torch.distributed as dist
 
@@ -498,65 +499,73 @@ def gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
     if rank == 0:
         sampler.start()
     before = lib.weft_b200_launch_count()
-    begin.record()
-    for i in range(args.steps):
-        step(args.warmup + i)
-    end.record()
-    barrier()
-    launches = int(lib.weft_b200_launch_count() - before)
-    ms = begin.elapsed_time(end) / args.steps
+    times = []
+    for r in range(max(1, args.replays)):       # each timing: `steps` direct launches between two events
+        barrier()
+        begin.record()
+        for i in range(args.steps):
+            step(args.warmup + r * args.steps + i)
+        end.record()
+        barrier()
+        times.append(begin.elapsed_time(end) / args.steps)
+    launches = int(lib.weft_b200_launch_count() - before) // max(1, args.replays)
     clocks = sampler.stop() if rank == 0 else None
     if world > 1:
-        t = torch.tensor([ms], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+        t = torch.tensor(times, device="cuda", dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); times = [float(v) for v in t.tolist()]
         lt = torch.tensor([launches], device="cuda"); dist.all_reduce(lt); launches = int(lt.item())
-    # end to end: host record bytes in, host fp32 out (pinned), copies inside the timed region
-    w_pin = torch.from_numpy(shard).pin_memory()
-    y_pin = torch.empty((rows, k), dtype=torch.float32).pin_memory()
-    e2e_steps = max(3, min(args.steps, 10))
-    call(w_pin.data_ptr(), y_pin.data_ptr())
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
+    ms = statistics.median(times)
+    e2e_s = None
+    if extras:
+        # end to end: host record bytes in, host fp32 out (pinned), copies inside the timed region
+        w_pin = torch.from_numpy(shard).pin_memory()
+        y_pin = torch.empty((rows, k), dtype=torch.float32).pin_memory()
+        e2e_steps = max(3, min(args.steps, 10))
         call(w_pin.data_ptr(), y_pin.data_ptr())
-    torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_s = float(t.item())
-    if not np.array_equal(y_pin[:64].numpy().view(np.uint32), want.view(np.uint32)):
-        raise SystemExit("host-buffer dequantize is not bit-exact")
-    if rank != 0:
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            call(w_pin.data_ptr(), y_pin.data_ptr())
+        torch.cuda.synchronize()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
         if world > 1:
-            dist.destroy_process_group()
-        return
+            t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64); dist.all_reduce(t, op=dist.ReduceOp.MAX); e2e_s = float(t.item())
+        if not np.array_equal(y_pin[:64].numpy().view(np.uint32), want.view(np.uint32)):
+            raise SystemExit("host-buffer dequantize is not bit-exact")
+    del w_dev, y_dev
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
     peaks, peaks_kind = load_peaks()
     total_bytes = n * row_bytes(fmt, k) + 4 * n * k
     shard_bytes = rows * row_bytes(fmt, k) + 4 * rows * k
     achieved = shard_bytes / (ms * 1e-3) / 1e9
+    workload = next((name for name, spec in WORKLOADS.items() if spec[:4] == (fmt, "dequantize", n, k)), args.workload)
     line = {"metric": "row_dequantize_algorithmic_gbps", "value": total_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32 (bit-exact)", "data": "synthetic",
-            "config": {"workload": args.workload, "format": fmt, "mode": "dequantize", "N": n, "K": k,
+            "config": {"workload": workload, "format": fmt, "mode": "dequantize", "N": n, "K": k,
                        "sharding": f"rows split {world} ways, no collective" if world > 1 else "none",
-                       "l2": f"{copies} input copies rotate; the {4 * rows * k / 2**20:.0f} MiB output exceeds L2", "launch": "direct launches", "seed": SEED},
+                       "l2": f"{copies} input copies rotate; the {4 * rows * k / 2**20:.0f} MiB output exceeds L2", "launch": "direct launches",
+                       "timing": f"median of {len(times)} timings of {args.steps} launches, max over ranks",
+                       "replay_spread": (max(times) - min(times)) / ms if len(times) > 1 else 0.0, "seed": SEED, "parity_rel_l2_before_timing": 0.0},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "traffic": ncu_traffic(args.workload, rows / n), "peak_source": peaks_kind, "kernel": "dequant kernel (per GPU)", "kernel_ms": ms,
+                         "traffic": ncu_traffic(workload, rows / n), "peak_source": peaks_kind, "kernel": "dequant kernel (per GPU)", "kernel_ms": ms,
                          "algorithmic_bytes_per_launch": shard_bytes},
-            "clocks": clocks, "gpu_launches": launches,
-            "e2e": {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(shard.nbytes), "d2h_bytes_per_step": int(4 * rows * k),
-                    "ms_per_step": e2e_s * 1e3, "what": "row_dequantize_*_rows with host W and Y (pinned)"}}
-    if not args.no_cpu_baseline and world == 1:
+            "clocks": clocks, "gpu_launches": launches}
+    if e2e_s is not None:
+        line["e2e"] = {"value": total_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(shard.nbytes), "d2h_bytes_per_step": int(4 * rows * k),
+                       "ms_per_step": e2e_s * 1e3, "what": "row_dequantize_*_rows with host W and Y (pinned)"}
+    if extras and not args.no_cpu_baseline and world == 1:
         threads = os.cpu_count() or 1
         run, kind = cpu_dequantize(fmt, n, k, w_host, threads)
         run()
-        times, t_end = [], time.perf_counter() + 10.0
-        while time.perf_counter() < t_end and len(times) < 100:
-            t0 = time.perf_counter(); run(); times.append(time.perf_counter() - t0)
-        per = sum(times) / len(times)
+        cpu_times, t_end = [], time.perf_counter() + 10.0
+        while time.perf_counter() < t_end and len(cpu_times) < 100:
+            t0 = time.perf_counter(); run(); cpu_times.append(time.perf_counter() - t0)
+        per = sum(cpu_times) / len(cpu_times)
         line["cpu_baseline"] = {"value": total_bytes / per / 1e9, "unit": "GB/s", "cores": threads, "kind": kind,
-                                "sample": f"{len(times)} x full {n} x {k} dequantize", "cpu": oracle.cpu_model(), "ms_per_step": per * 1e3}
-    print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+                                "sample": f"{len(cpu_times)} x full {n} x {k} dequantize", "cpu": oracle.cpu_model(), "ms_per_step": per * 1e3}
+    return line
 
 
 def main() -> None:
@@ -570,6 +579,8 @@ def main() -> None:
     parser.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
                         help="N > 1: all-gather by the library's own peer-memory kernels (default) or by NCCL")
     parser.add_argument("--no-graph", action="store_true", help="time direct launches instead of a CUDA graph replay")
+    parser.add_argument("--replays", type=int, default=5, help="timings taken of the K steps; the median is reported")
+    parser.add_argument("--no-also", action="store_true", help="default workload only: leave out the compact records of the other configurations")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3)
     fmt, mode, n, k, m = WORKLOADS[args.workload]
@@ -611,11 +622,39 @@ def main() -> None:
             raise SystemExit("weft_b200 call failed: " + last_error(lib))
 
     if mode == "dequantize":
-        gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
+        line = gpu_dequantize(args, lib, check, stream, fmt, n, k, world, rank, local_rank)
+        if line is not None:
+            print(json.dumps(line))
+        if world > 1:
+            dist.destroy_process_group()
         return
     if mode == "layer":
         gpu_layer_decode(args, lib, check, stream, fmt, k, world, rank, local_rank)
         return
+    line = run_mul_mat(args, lib, check, stream, args.workload, world, rank, local_rank)
+    if args.workload == DEFAULT_WORKLOAD and not args.no_also:
+        records = also_records(args, lib, check, stream, world, rank, local_rank)
+        if line is not None:
+            line["also"] = records
+    if line is not None:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_mul_mat(args, lib, check, stream, workload: str, world: int, rank: int, local_rank: int, *, extras: bool = True):
+    """One mul_mat workload (decode or prefill), weight rows sharded over the ranks.  Returns the JSON record on rank 0,
+    None on the others.  extras = False leaves out the end-to-end and CPU legs (the compact records of the default run)."""
+    import torch
+    import torch.distributed as dist
+
+    import oracle
+    from weft_b200.formats import FORMAT_IDS, TQ1_POWERS, row_bytes
+
+    fmt, mode, n, k, m = WORKLOADS[workload]
+    layout = fmt                      # what the kernel is given
+    if fmt == "Q4K_I16":              # Q4_K records, packed once by the kernel's _W_pack artifact function
+        fmt = "Q4_K"
 
     # ---- inputs, sharded by weight rows
     act = "Q8_0" if fmt in ("Q4_0", "Q8_0") else "Q8_K"
@@ -662,21 +701,29 @@ def main() -> None:
         usable = torch.tensor([1 if peers is not None else 0], device="cuda")
         dist.all_reduce(usable, op=dist.ReduceOp.MIN)
         if int(usable.item()) == 0:
+            if peers is not None:
+                peers.close(dist.barrier)
             peers, collective = None, "nccl"
     gather_fn = lib.weft_b200_mul_mat_shard_gather
     gather_fn.argtypes = ([ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 6 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
                           + [ctypes.c_size_t] * 5 + [ctypes.c_uint])
+    lib.weft_b200_peer_read.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
+    calls = [0]                       # gathers made so far: consecutive ones alternate between the two output buffers
 
-    def step(i: int, flags: int = 0) -> None:
+    def step(i: int, flags: int = 0, x_ptr=None, xq_ptr=None) -> None:
         wbuf = w_dev[i % copies]
+        x_ptr = x_dev.data_ptr() if x_ptr is None else x_ptr
+        xq_ptr = xq_dev.data_ptr() if xq_ptr is None else xq_ptr
         if world == 1:
-            check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
+            check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_ptr, xq_ptr, grid_dev.data_ptr(), signs_dev.data_ptr(),
                            powers_dev.data_ptr(), y_dev.data_ptr(), n_local, k, m, n, flags))
-        elif peers is not None:       # consecutive steps alternate between the two output buffers
-            check(gather_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
-                            powers_dev.data_ptr(), peers.tables[i % 2], peers.tables[2], peers.tables[3], world, rank, n0, n_local, n, k, m, flags))
+        elif peers is not None:
+            out = calls[0] % 2
+            calls[0] += 1
+            check(gather_fn(fid, mode_id, wbuf.data_ptr(), x_ptr, xq_ptr, grid_dev.data_ptr(), signs_dev.data_ptr(),
+                            powers_dev.data_ptr(), peers.tables[out], peers.tables[2], peers.tables[3], world, rank, n0, n_local, n, k, m, flags))
         else:
-            check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_dev.data_ptr(), xq_dev.data_ptr(), grid_dev.data_ptr(), signs_dev.data_ptr(),
+            check(shard_fn(fid, mode_id, wbuf.data_ptr(), x_ptr, xq_ptr, grid_dev.data_ptr(), signs_dev.data_ptr(),
                            powers_dev.data_ptr(), y_local.data_ptr(), n_local, k, m, n_local, flags))
             dist.all_gather_into_tensor(gathered, y_local)
 
@@ -697,6 +744,7 @@ def main() -> None:
         agreed = torch.tensor([trial], device="cuda")
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
         if int(agreed.item()) == 0:
+            peers.close(dist.barrier)
             peers, collective = None, "nccl"
 
     # ---- parity spot check before timing (one step against the oracle, rank-local columns)
@@ -705,8 +753,7 @@ def main() -> None:
     check(lib.weft_b200_synchronize())
     if peers is not None:     # the gathered output of this rank: own columns, and a block computed by the next rank
         full = np.empty((m, n), dtype=np.float32)
-        lib.weft_b200_peer_read.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t]
-        check(lib.weft_b200_peer_read(full.ctypes.data, peers.local[0], full.nbytes))
+        check(lib.weft_b200_peer_read(full.ctypes.data, peers.local[(calls[0] - 1) % 2], full.nbytes))
         got = full[:, n0:n1]
         other = (rank + 1) % world
         o0 = n * other // world
@@ -721,15 +768,17 @@ def main() -> None:
     want, _ = oracle.mul_mat(oracle.FORMAT_IDS[fmt], shard[:probe], x_host[: min(m, 4)], probe, k, min(m, 4), rule=1, grid=grid, signs=signs)
     err = float(np.linalg.norm(got[: min(m, 4), :probe].astype(np.float64) - want) / max(np.linalg.norm(want.astype(np.float64)), 1e-30))
     if not err <= 1e-5:
-        raise SystemExit(f"parity check failed before timing: relative L2 {err}")
+        raise SystemExit(f"parity check failed before timing ({workload}): relative L2 {err}")
 
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    replays = max(1, args.replays)
 
-    def run_timed(fn, steps: int, first: int) -> tuple[float, str]:
-        """Device time of `steps` consecutive calls of fn.  The calls are captured once into a CUDA graph and
-        the graph is replayed between the two events, so host launch cost (Python + ctypes, several
-        microseconds per call, comparable to the kernel itself) stays out of the measurement.  Falls back to
-        direct launches when capture is refused."""
+    def run_timed(fn, steps: int, first: int) -> tuple[list[float], str]:
+        """Device times (ms) of `steps` consecutive calls of fn, taken `replays` times.  The calls are captured once
+        into a CUDA graph and each timing is one replay of that graph between two events on the launching stream, so
+        host launch cost (Python + ctypes, several microseconds per call, comparable to the kernel itself) stays out of
+        the measurement.  An even number of steps keeps the two alternating gather buffers in step from replay to
+        replay.  Falls back to direct launches when capture is refused."""
         if not args.no_graph:
             side = torch.cuda.Stream()
             graph = torch.cuda.CUDAGraph()
@@ -741,43 +790,56 @@ def main() -> None:
                         fn(first + i)
                 lib.weft_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
                 graph.replay()          # untimed: first replay uploads the graph
-                barrier()
-                begin.record()
-                graph.replay()
-                end.record()
-                barrier()
-                return begin.elapsed_time(end), "cuda graph replay of all steps"
+                times = []
+                for _ in range(replays):
+                    barrier()
+                    begin.record()
+                    graph.replay()
+                    end.record()
+                    barrier()
+                    times.append(begin.elapsed_time(end))
+                return times, "cuda graph replay of all steps"
             except Exception as error:  # capture refused: measure direct launches instead
                 lib.weft_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
                 torch.cuda.synchronize()
                 sys.stderr.write(f"graph capture unavailable ({error}); timing direct launches\n")
-        barrier()
-        begin.record()
-        for i in range(steps):
-            fn(first + i)
-        end.record()
-        barrier()
-        return begin.elapsed_time(end), "direct launches"
+        times = []
+        for _ in range(replays):
+            barrier()
+            begin.record()
+            for i in range(steps):
+                fn(first + i)
+            end.record()
+            barrier()
+            times.append(begin.elapsed_time(end))
+        return times, "direct launches"
 
-    # ---- timed region: K steps on the device
-    for i in range(args.warmup):
+    def over_ranks(values: list[float]) -> list[float]:
+        if world == 1:
+            return values
+        t = torch.tensor(values, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    steps = args.steps + (args.steps % 2 if peers is not None else 0)
+
+    # ---- timed region: K steps on the device, `replays` times
+    for i in range(args.warmup + (args.warmup + calls[0]) % 2 if peers is not None else args.warmup):
         step(i)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches_before = lib.weft_b200_launch_count()
-    elapsed_ms, launch_mode = run_timed(step, args.steps, args.warmup)
-    launches = int(lib.weft_b200_launch_count() - launches_before)
+    step_times, launch_mode = run_timed(step, steps, args.warmup)
+    launches = int(lib.weft_b200_launch_count() - launches_before)     # kernels captured for one pass over the steps
     check(lib.weft_b200_synchronize())
+    step_times = over_ranks(step_times)
     if world > 1:
-        t = torch.tensor([elapsed_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
         lt = torch.tensor([launches], device="cuda")
         dist.all_reduce(lt)
         launches = int(lt.item())
-    ms_per_step = elapsed_ms / args.steps
+    ms_per_step = statistics.median(step_times) / steps
 
     # ---- the dominant kernel alone (activations already quantized, no collective): average launch duration
     def kernel_step(i: int) -> None:
@@ -788,85 +850,125 @@ def main() -> None:
     for i in range(args.warmup):
         kernel_step(i)
     barrier()
-    kernel_total_ms, _ = run_timed(kernel_step, args.steps, args.warmup)
-    kernel_ms = kernel_total_ms / args.steps
+    kernel_times, _ = run_timed(kernel_step, steps, args.warmup)
+    kernel_times = over_ranks(kernel_times)
+    kernel_ms = statistics.median(kernel_times) / steps
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- end to end through the C ABI with host buffers (weights resident on the device)
-    x_pin = torch.from_numpy(x_host).pin_memory()
-    xq_pin = torch.zeros((m, row_bytes(act, k)), dtype=torch.uint8).pin_memory()
-    y_pin = torch.zeros((m, n_local), dtype=torch.float32).pin_memory()
-    grid_pin, signs_pin = torch.from_numpy(grid).pin_memory(), torch.from_numpy(signs).pin_memory()
-    powers_pin = torch.tensor(TQ1_POWERS, dtype=torch.int32).pin_memory()
+    e2e = None
+    if extras:
+        # ---- end to end through the C ABI with host buffers (weights resident on the device): pinned X in, the FULL
+        # (m, n) output back on the host.  One GPU: the plain entry point with host X / Xq / Y.  Several GPUs: the
+        # gathering entry point with host X, then the gathered output read back from this rank's buffer.
+        x_pin = torch.from_numpy(x_host).pin_memory()
+        xq_pin = torch.zeros((m, row_bytes(act, k)), dtype=torch.uint8).pin_memory()
+        y_pin = torch.zeros((m, n), dtype=torch.float32).pin_memory()
+        grid_pin, signs_pin = torch.from_numpy(grid).pin_memory(), torch.from_numpy(signs).pin_memory()
+        powers_pin = torch.tensor(TQ1_POWERS, dtype=torch.int32).pin_memory()
+        y_page = np.zeros((m, n), dtype=np.float32)      # pageable memory, what a plain numpy caller of the reference passes
+        x_page, xq_page = x_host.copy(), np.zeros((m, row_bytes(act, k)), dtype=np.uint8)
 
-    def e2e_step(i: int) -> None:
-        check(shard_fn(fid, mode_id, w_dev[i % copies].data_ptr(), x_pin.data_ptr(), xq_pin.data_ptr(), grid_pin.data_ptr(),
-                       signs_pin.data_ptr(), powers_pin.data_ptr(), y_pin.data_ptr(), n_local, k, m, n_local, 0))
+        def e2e_step(i: int, pinned: bool = True) -> None:
+            if world == 1:
+                xs = (x_pin.data_ptr(), xq_pin.data_ptr(), y_pin.data_ptr()) if pinned else (x_page.ctypes.data, xq_page.ctypes.data, y_page.ctypes.data)
+                check(shard_fn(fid, mode_id, w_dev[i % copies].data_ptr(), xs[0], xs[1], grid_pin.data_ptr(),
+                               signs_pin.data_ptr(), powers_pin.data_ptr(), xs[2], n_local, k, m, n, 0))
+            elif peers is not None:
+                step(i, 0, x_pin.data_ptr(), None)
+                check(lib.weft_b200_peer_read(y_pin.data_ptr(), peers.local[(calls[0] - 1) % 2], 4 * m * n))
+            else:
+                step(i, 0, x_pin.data_ptr(), None)
+                torch.cuda.synchronize()
+                y_pin.view(m, world, n_local).copy_(gathered.view(world, m, n_local).permute(1, 0, 2))
 
-    e2e_steps = max(3, min(args.steps, 200))
-    for i in range(3):
-        e2e_step(i)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        e2e_step(3 + i)
-    torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_err = float(np.abs(y_pin.numpy()[: min(m, 4), :probe] - got[: min(m, 4), :probe]).max())
-    if e2e_err != 0.0:
-        raise SystemExit(f"host-buffer path disagrees with the device-buffer path by {e2e_err}")
+        lib.weft_b200_set_async(0 if world == 1 else 1)
+        e2e_steps = max(3, min(args.steps, 200))
+
+        def e2e_time(pinned: bool) -> float:
+            for i in range(3):
+                e2e_step(i, pinned)
+            barrier()
+            t0 = time.perf_counter()
+            for i in range(e2e_steps):
+                e2e_step(3 + i, pinned)
+            torch.cuda.synchronize()
+            seconds = (time.perf_counter() - t0) / e2e_steps
+            if world > 1:
+                t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                seconds = float(t.item())
+            return seconds
+
+        e2e_s = e2e_time(True)
+        e2e_err = float(np.abs(y_pin.numpy()[: min(m, 4), n0:n0 + probe] - got[: min(m, 4), :probe]).max())
+        if e2e_err != 0.0:
+            raise SystemExit(f"host-buffer path disagrees with the device-buffer path by {e2e_err}")
+        e2e_pageable_s = e2e_time(False) if world == 1 else None
+        lib.weft_b200_set_async(1)
+        e2e = {"seconds": e2e_s, "pageable_seconds": e2e_pageable_s, "h2d": int(x_pin.numel() * 4),
+               "d2h": int(4 * m * n + (xq_pin.numel() if world == 1 else 0))}
 
     if peers is not None:
         torch.cuda.synchronize()
         peers.close(dist.barrier)
+    del w_dev, x_dev, xq_dev, y_dev, gathered, y_local
+    torch.cuda.empty_cache()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     peaks, peaks_kind = load_peaks()
     total_bytes = algorithmic_bytes(fmt, n, k, m)
+    spread = (max(step_times) - min(step_times)) / statistics.median(step_times) if len(step_times) > 1 else 0.0
+    kernel_spread = (max(kernel_times) - min(kernel_times)) / statistics.median(kernel_times) if len(kernel_times) > 1 else 0.0
     if mode == "decode":
         metric, unit = "mul_mat_decode_algorithmic_gbps", "GB/s"
         value = total_bytes / (ms_per_step * 1e-3) / 1e9
-        e2e_value = total_bytes / e2e_s / 1e9
+        e2e_value = total_bytes / e2e["seconds"] / 1e9 if e2e else None
+        e2e_pageable = total_bytes / e2e["pageable_seconds"] / 1e9 if e2e and e2e["pageable_seconds"] else None
         shard_bytes = algorithmic_bytes(fmt, n_local, k, m)
         achieved = shard_bytes / (kernel_ms * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "traffic": ncu_traffic(args.workload, n_local / n), "peak_source": peaks_kind, "kernel": "gemv_kernel (per GPU)", "kernel_ms": kernel_ms,
-                "algorithmic_bytes_per_launch": shard_bytes}
+                "traffic": ncu_traffic(workload, n_local / n), "peak_source": peaks_kind, "kernel": "gemv_kernel (per GPU)", "kernel_ms": kernel_ms,
+                "kernel_ms_spread": kernel_spread, "algorithmic_bytes_per_launch": shard_bytes}
         dtype = "int8 dot (dp4a), f32 accumulate"
     else:
         metric, unit = "mul_mat_prefill_int8_tops", "TOP/s"
         ops = 2.0 * m * n * k
         value = ops / (ms_per_step * 1e-3) / 1e12
-        e2e_value = ops / e2e_s / 1e12
+        e2e_value = ops / e2e["seconds"] / 1e12 if e2e else None
+        e2e_pageable = ops / e2e["pageable_seconds"] / 1e12 if e2e and e2e["pageable_seconds"] else None
         achieved = 2.0 * m * n_local * k / (kernel_ms * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops"]
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": ncu_traffic(args.workload, n_local / n),
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak, "traffic": ncu_traffic(workload, n_local / n),
                 "peak_source": peaks_kind + " bf16 dense x2 (no int8 entry in MEASURED_PEAKS.json)", "kernel": "prefill kernel (per GPU)",
-                "kernel_ms": kernel_ms}
+                "kernel_ms": kernel_ms, "kernel_ms_spread": kernel_spread}
+        int8_peak = measured_int8_peak(lib)
+        if int8_peak:
+            roof["int8_issue_peak"] = int8_peak
+            roof["frac_of_int8_issue_peak"] = achieved / int8_peak
         dtype = "int8 tensor-core MMA, i32/f32 accumulate"
 
     line = {
-        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype,
         "data": "synthetic",
-        "config": {"workload": args.workload, "format": layout, "mode": mode, "N": n, "K": k, "M": m,
+        "config": {"workload": workload, "format": layout, "mode": mode, "N": n, "K": k, "M": m,
                    "sharding": (f"weight rows split {world} ways, fp32 outputs all-gathered " + ("by peer stores and a flag barrier inside the library's kernels (NVLink, CUDA IPC)" if collective == "p2p" else "(NCCL)")) if world > 1 else "none",
                    "l2": f"steps rotate over {copies} weight copies ({copies * shard.nbytes / 2**20:.0f} MiB per GPU > 2 x L2)",
-                   "launch": launch_mode, "timed_scope": "activation quantize + mul_mat" + (" + all-gather" if world > 1 else ""), "seed": SEED,
+                   "launch": launch_mode, "timing": f"median of {len(step_times)} replays of {steps} steps, max over ranks",
+                   "replay_spread": spread, "timed_scope": "activation quantize + mul_mat" + (" + all-gather" if world > 1 else ""), "seed": SEED,
                    "parity_rel_l2_before_timing": err},
         "roofline": roof, "clocks": clocks, "gpu_launches": launches,
-        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": int(x_pin.numel() * 4),
-                "d2h_bytes_per_step": int(y_pin.numel() * 4 + xq_pin.numel()), "ms_per_step": e2e_s * 1e3,
-                "what": "weft_b200_mul_mat_shard with host X/Xq/Y (pinned), weights resident in HBM"},
     }
-    if not args.no_cpu_baseline and world == 1:
+    if e2e:
+        line["e2e"] = {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                       "ms_per_step": e2e["seconds"] * 1e3,
+                       "what": ("weft_b200_mul_mat_shard with host X/Xq/Y (pinned), weights resident in HBM" if world == 1 else
+                                "weft_b200_mul_mat_shard_gather with host X (pinned) and the gathered (M, N) output read back to the host, weights resident in HBM")}
+        if e2e_pageable:
+            line["e2e"]["pageable"] = {"value": e2e_pageable, "ms_per_step": e2e["pageable_seconds"] * 1e3,
+                                       "what": "the same call with pageable (plain numpy) X / Xq / Y, as the reference's FFI passes them"}
+    if extras and not args.no_cpu_baseline and world == 1:
         threads = os.cpu_count() or 1
         sample_m = m if mode == "decode" else min(m, 2)
         run, kind = cpu_mul_mat_runner(fmt, n, k, sample_m, w_host, x_host[:sample_m], grid, signs, threads)
@@ -879,10 +981,81 @@ def main() -> None:
         line["cpu_baseline"] = {"value": cpu_value, "unit": unit, "cores": threads, "kind": kind,
                                 "sample": f"{len(times)} x full mul_mat N={n} K={k} M={sample_m}" + ("" if sample_m == m else f" of M={m}"),
                                 "cpu": oracle.cpu_model(), "ms_per_step": per * 1e3 * (m / sample_m)}
-    print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+        single = cpu_single_thread(fmt, n, k, sample_m, w_host, x_host[:sample_m], grid, signs)
+        if single:
+            single["value"] = (algorithmic_bytes(fmt, n, k, m) / single["seconds"] / 1e9) if mode == "decode" else (2.0 * sample_m * n * k / single["seconds"] / 1e12)
+            single["unit"] = unit
+            line["cpu_baseline"]["single_thread"] = single
+    return line
 
+
+_INT8_PEAK = []
+
+
+def measured_int8_peak(lib):
+    """TOP/s of a bare tcgen05.mma kind::i8 issue loop on every SM (weft_b200_mma_peak), measured once per process."""
+    if not _INT8_PEAK:
+        lib.weft_b200_mma_peak.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double)]
+        value = ctypes.c_double()
+        _INT8_PEAK.append(float(value.value) if lib.weft_b200_mma_peak(0, ctypes.byref(value)) == 0 else None)
+    return _INT8_PEAK[0]
+
+
+def cpu_single_thread(fmt, n, k, m, w, x, grid, signs):
+    """The reference's own protocol for its CPU numbers (doc/experiments/protocol.md:33-59): one pinned thread, a 64 MiB
+    buffer rewritten between repetitions so that every repetition starts cold, median of the repetitions.  Bounded to a
+    few seconds: at most 4096 weight rows per repetition."""
+    import oracle
+
+    rows = min(n, 4096)
+    run, kind = cpu_mul_mat_runner(fmt, rows, k, m, np.ascontiguousarray(w[:rows]), x, grid, signs, 1)
+    try:
+        previous = os.sched_getaffinity(0)
+        os.sched_setaffinity(0, {sorted(previous)[0]})
+    except (AttributeError, OSError):
+        previous = None
+    evict = np.zeros(64 << 20, dtype=np.uint8)
+    try:
+        run()
+        times, t_end = [], time.perf_counter() + 6.0
+        while time.perf_counter() < t_end and len(times) < 10:
+            evict += 1
+            t0 = time.perf_counter(); run(); times.append(time.perf_counter() - t0)
+    finally:
+        if previous is not None:
+            os.sched_setaffinity(0, previous)
+    return {"seconds": statistics.median(times) * (n / rows), "kind": kind, "cores": 1,
+            "sample": f"median of {len(times)} cold repetitions of {rows} of {n} rows, one pinned thread, 64 MiB rewritten between repetitions"}
+
+
+#: the other configurations of the headline metric, reported as compact records beside the default line
+ALSO_WORKLOADS = ["q4_0_decode_4096x4096", "q4_k_dequantize_14336x4096", "q4_k_decode_4096x4096", "q4_k_decode_4096x14336",
+                  "q4_k_prefill_4096x4096", "q4_k_prefill_14336x4096", "q4_k_prefill_4096x14336", "iq2_xxs_decode_28672x8192",
+                  "tq1_0_prefill_28672x8192"]
+#: the ones the metric shards over several GPUs (prefill with N = 14336; the 28672 x 8192 layer)
+ALSO_SHARDED = ["q4_k_prefill_14336x4096", "iq2_xxs_decode_28672x8192", "tq1_0_prefill_28672x8192"]
+
+
+def also_records(args, lib, check, stream, world, rank, local_rank) -> list[dict]:
+    """One compact record per further configuration of the metric, measured like the default line (median of the
+    replays of `steps` graph-captured steps, weights rotating through more than twice the L2, parity checked first)."""
+    import copy
+
+    quick = copy.copy(args)
+    quick.steps, quick.warmup = max(2, min(args.steps, 10)), 3
+    records = []
+    for workload in (ALSO_WORKLOADS if world == 1 else ALSO_SHARDED):
+        fmt, mode, n, k, _ = WORKLOADS[workload]
+        if mode == "dequantize":
+            line = gpu_dequantize(quick, lib, check, stream, fmt, n, k, world, rank, local_rank, extras=False)
+        else:
+            line = run_mul_mat(quick, lib, check, stream, workload, world, rank, local_rank, extras=False)
+        if line is not None:
+            records.append({"workload": workload, "n_gpus": world, "ms_per_step": line["ms_per_step"], "value": line["value"], "unit": line["unit"],
+                            "frac": line["roofline"]["frac"], "bound": line["roofline"]["bound"], "kernel_ms": line["roofline"]["kernel_ms"],
+                            "parity_rel_l2": line["config"].get("parity_rel_l2_before_timing", 0.0), "replays": args.replays,
+                            "replay_spread": line["config"].get("replay_spread"), "steps": line["steps"]})
+    return records
 
 if __name__ == "__main__":
     main()
