@@ -112,7 +112,9 @@ class Call {
             if (a.overflow && a.dev) { cudaStreamSynchronize(g.stream); cudaFree(a.dev); }
     }
     // Returns the device address for `ptr` (bytes long). read: copy in when host; written: copy back.
-    int map(const void *ptr, size_t bytes, bool read, bool written, void **out) {
+    // direct: a written host argument in pinned, mapped memory that the kernels only ever store to (never read back)
+    // is handed to them as it is -- their stores go to the caller's buffer, no staging slice and no copy back.
+    int map(const void *ptr, size_t bytes, bool read, bool written, void **out, bool direct = false) {
         *out = nullptr;
         if (bytes == 0) { *out = const_cast<void *>(ptr); return 0; }
         if (!ptr) return fail("a required buffer is NULL");
@@ -140,6 +142,7 @@ class Call {
         Arg arg;
         arg.user = ptr; arg.bytes = bytes; arg.written = written;
         if (attr.type == cudaMemoryTypeHost && attr.devicePointer && bytes <= kKernelCopyMax) arg.mapped = attr.devicePointer;
+        if (direct && written && !read && arg.mapped) { *out = arg.mapped; return 0; }
         if (slice(arg)) return 1;
         if (read) {
             if (arg.mapped) CU(launch_copy_bytes(arg.dev, arg.mapped, bytes, g.stream));
@@ -262,12 +265,16 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
     if (fmt == F_Q6_K && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
     if (!have_xq && call.map(X, M * K * sizeof(float), true, false, &x)) return 1;
-    if (call.map(Xq, M * row_bytes(act, K), have_xq, !have_xq, &xq)) return 1;
+    // Decode quantizes X inside the GEMV (its first CTA stores the records, nobody loads them again), so a pinned Xq can
+    // be written in place; a call that may take the tensor-core path or the separate quantize kernel reads Xq back.
+    const bool may_contract = mode == 1 && M >= 32 && K % 1024 == 0;
+    const bool xq_in_place = !have_xq && !may_contract && K % 256 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+    if (call.map(Xq, M * row_bytes(act, K), have_xq, !have_xq, &xq, xq_in_place)) return 1;
     if (fmt == F_IQ2_XXS && (call.map(grid, 2048, true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
     if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
-    // a host Y with a pitch is staged whole (pitch * M floats); device Y is written in place
+    // a host Y with a pitch is staged whole (pitch * M floats); device Y is written in place; a small pinned Y too
     const size_t y_floats = (M - 1) * ldy + N;
-    if (call.map(Y, y_floats * sizeof(float), ldy != N, true, &y)) return 1;
+    if (call.map(Y, y_floats * sizeof(float), ldy != N, true, &y, ldy == N && gather == nullptr)) return 1;
     if ((reinterpret_cast<uintptr_t>(w) & (fmt == F_Q4_K_I16 ? 15u : 1u)) || (reinterpret_cast<uintptr_t>(xq) & (act == F_Q8_K ? 3u : 1u)) ||
         (reinterpret_cast<uintptr_t>(y) & 3u) || (x && (reinterpret_cast<uintptr_t>(x) & 3u)))
         return fail("a buffer does not meet its Encoding alignment");

@@ -46,6 +46,9 @@ __global__ void __launch_bounds__(QZ_WARPS * 32) quantize_q8_0_kernel(const floa
 
 // Byte copy for small staged arguments; 16-byte words when both sides allow, whole bytes otherwise.
 __global__ void __launch_bounds__(256) copy_bytes_kernel(uint8_t *__restrict__ dst, const uint8_t *__restrict__ src, size_t bytes, int vec) {
+    // The kernel behind this one may start its own prologue now (programmatic dependent launch); it waits for this
+    // grid to complete before it touches what is copied here.
+    asm volatile("griddepcontrol.launch_dependents;");
     const size_t stride = (size_t)gridDim.x * 256, first = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (vec) {
         for (size_t i = first; i < bytes / 16; i += stride) reinterpret_cast<uint4 *>(dst)[i] = reinterpret_cast<const uint4 *>(src)[i];
