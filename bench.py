@@ -51,6 +51,9 @@ WORKLOADS = {
     "q4_k_prefill_4096x4096": ("Q4_K", "prefill", 4096, 4096, 512),
     "q4_k_prefill_4096x14336": ("Q4_K", "prefill", 4096, 14336, 512),
     "tq1_0_prefill_28672x8192": ("TQ1_0", "prefill", 28672, 8192, 512),
+    "q4_0_prefill_4096x4096": ("Q4_0", "prefill", 4096, 4096, 512),
+    "q8_0_prefill_4096x4096": ("Q8_0", "prefill", 4096, 4096, 512),
+    "iq2_xxs_prefill_4096x4096": ("IQ2_XXS", "prefill", 4096, 4096, 512),
     "q4_k_dequantize_14336x4096": ("Q4_K", "dequantize", 14336, 4096, 0),
     "q4_k_layer_decode_llama3_8b": ("Q4_K", "layer", 0, 4096, 1),     # the seven projections of one block, one call per step
 }

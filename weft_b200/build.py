@@ -15,7 +15,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 CSRC = PACKAGE / "csrc"
 LIBRARY = PACKAGE / "libweft_b200.so"
-SOURCES = ["abi.cu", "abi_noalloc.cu", "dequantize.cu", "quantize.cu", "gemv.cu", "gemv_q4k.cu", "gemv_ring.cu", "gemv_q4ki.cu", "prefill.cu", "prefill_pair.cu", "mma_peak.cu", "gather.cu"]
+SOURCES = ["abi.cu", "abi_noalloc.cu", "dequantize.cu", "quantize.cu", "gemv.cu", "gemv_q4k.cu", "gemv_ring.cu", "gemv_q4ki.cu", "prefill.cu", "prefill_pair.cu", "prefill_blocks.cu", "mma_peak.cu", "gather.cu"]
 HEADERS = ["common.cuh", "quantize.cuh", "kernels.h", "gemv_units.cuh", "ring.cuh", "tcgen05.cuh", "tensormap.cuh", "prefill_common.cuh", "gather.cuh", "../../include/weft_b200.h"]
 
 NVCC_FLAGS = [

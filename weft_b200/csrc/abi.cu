@@ -267,7 +267,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     if (!have_xq && call.map(X, M * K * sizeof(float), true, false, &x)) return 1;
     // Decode quantizes X inside the GEMV (its first CTA stores the records, nobody loads them again), so a pinned Xq can
     // be written in place; a call that may take the tensor-core path or the separate quantize kernel reads Xq back.
-    const bool may_contract = mode == 1 && M >= 32 && K % 1024 == 0;
+    const bool may_contract = mode == 1 && M >= 32 && K % 256 == 0;
     const bool xq_in_place = !have_xq && !may_contract && K % 256 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     if (call.map(Xq, M * row_bytes(act, K), have_xq, !have_xq, &xq, xq_in_place)) return 1;
     if (fmt == F_IQ2_XXS && (call.map(grid, 2048, true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
@@ -279,7 +279,8 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
         (reinterpret_cast<uintptr_t>(y) & 3u) || (x && (reinterpret_cast<uintptr_t>(x) & 3u)))
         return fail("a buffer does not meet its Encoding alignment");
     const int sms = g.prop.multiProcessorCount;
-    const bool to_prefill = mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
+    const bool by_blocks = mode == 1 && prefill_blocks_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
+    const bool to_prefill = by_blocks || (mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq));
     // decode: the GEMV's own prologue quantizes X (one launch) when the fp32 rows allow 16-byte loads
     const bool fuse_quantize = !have_xq && !to_prefill && K % 256 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     if (!have_xq && !fuse_quantize &&
@@ -288,7 +289,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     if (to_prefill) {
         PrefillArgs pa{fmt, w, xq, (const uint32_t *)pw, (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
         const bool pair = prefill_pair_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
-        if (launched(pair ? launch_prefill_pair(pa, sms, g.stream) : launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
+        if (launched(by_blocks ? launch_prefill_blocks(pa, sms, g.stream) : pair ? launch_prefill_pair(pa, sms, g.stream) : launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
         if (gather && launched(launch_gather_push(*gather, (long long)M, (long long)N, (long long)ldy, g.status_dev, sms, g.stream), "peer all-gather")) return 1;
     } else {
         GemvArgs ga{fmt, w, xq, fuse_quantize ? (const float *)x : nullptr, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw,

@@ -79,6 +79,11 @@ bool prefill_supported(int fmt, long long n, long long k, long long m, const voi
 cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream);
 bool prefill_pair_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
 
+// Q4_0 / Q8_0 x Q8_0 with more than a few tokens: one K = 32 contraction per 32-element block (both operands carry a
+// scale per block), accumulators rotating through tensor memory, scales applied in the epilogue.
+cudaError_t launch_prefill_blocks(const PrefillArgs &a, int sm_count, cudaStream_t stream);
+bool prefill_blocks_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
+
 // Bare tcgen05.mma issue loop on every SM (mode 0: kind::i8, one CTA per SM; 1: kind::i8 on CTA pairs; 2: kind::f16):
 // spans_dev receives the nanoseconds each issuing CTA took; *ops_per_launch the operations the whole launch performs.
 cudaError_t measure_mma_peak(int mode, int iterations, int sm_count, unsigned long long *spans_dev, int *status, cudaStream_t stream, double *ops_per_launch);
