@@ -107,14 +107,18 @@ int production_mul_mat_tq1_0_lane16_decode(const uint8_t *W, const float *X, uin
 /* ------------------------------------------------------------------ production_mul_mat, prefill form (tiled contraction)
  * Same arguments.  The reference binds its tile sizes (NC/MC/MR/NR/KC) at compile time
  * (Emitter.h:505-510), so they are not C parameters here either.
- * examples/kernels/mul_mat/q4_0.py:9-30, q8_0.py:9-29, q4_k_staged.py:9-37   mul_mat_runtime.cpp:217-221,277-281,350-357 */
+ * examples/kernels/mul_mat/q4_0.py:9-30, q8_0.py:9-29, q4_k_staged.py:9-37   mul_mat_runtime.cpp:217-221,277-281,350-357
+ * From 32 tokens on these run on the int8 tensor cores (Q4_K: two scaled limbs per 256-block, CTA pairs above 128
+ * tokens; Q4_0 / Q8_0: one contraction per 32-element block); smaller batches run the decode GEMV per token row. */
 int production_mul_mat_q4_0(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 int production_mul_mat_q8_0(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 int production_mul_mat_q4_k_staged(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 /* examples/kernels/mul_mat/tq1_0.py:10-64            mul_mat_runtime.cpp:534-538 */
 int production_mul_mat_tq1_0(const uint8_t *W, const float *X, uint8_t *Xq, const uint32_t *powers,
                              float *Y, size_t N, size_t K, size_t M);
-/* examples/kernels/mul_mat/iq2_xxs_staged.py:9-97    mul_mat_runtime.cpp:458-473 */
+/* examples/kernels/mul_mat/iq2_xxs_staged.py:9-97    mul_mat_runtime.cpp:458-473
+ * (from 32 tokens on, K a multiple of 1024: one tensor-core contraction per 32-element group, integer group scales
+ * combined in the epilogue) */
 int production_mul_mat_iq2_xxs_staged(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, const int8_t *signs,
                                       float *Y, size_t N, size_t K, size_t M);
 

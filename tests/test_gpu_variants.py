@@ -58,10 +58,12 @@ def _mul_mat(torch, oracle, golden, symbol, fmt_name, m, n, k, seed):
 
 @pytest.mark.parametrize("symbol,fmt", [("production_mul_mat_q4_0", "Q4_0"), ("production_mul_mat_q8_0", "Q8_0"),
                                         ("production_mul_mat_iq2_xxs_staged", "IQ2_XXS")])
-@pytest.mark.parametrize("mnk", [(3, 200, 1024), (128, 384, 2048), (128, 1000, 1024), (40, 64, 256)])
+@pytest.mark.parametrize("mnk", [(3, 200, 1024), (128, 384, 2048), (128, 1000, 1024), (40, 64, 256), (512, 1000, 2048), (300, 77, 3072)])
 def test_prefill_form_of_small_block_and_codebook_formats(torch, oracle, golden, symbol, fmt, mnk):
-    """examples/kernels/mul_mat/q4_0.py:9-30, q8_0.py:9-29, iq2_xxs_staged.py:9-97: token batches below and at the
-    tensor-core threshold, N that is not a whole tile, and a K (256) that only the row-by-row path takes."""
+    """examples/kernels/mul_mat/q4_0.py:9-30, q8_0.py:9-29, iq2_xxs_staged.py:9-97: token batches below the tensor-core
+    threshold (32 tokens: row-by-row GEMV) and above it (one contraction per 32-element block or group), token and
+    weight counts that are not whole tiles, K = 256 (one unit; the codebook format then takes the row-by-row path,
+    its activation rows are whole 16-byte multiples only for K % 1024 = 0)."""
     m, n, k = mnk
     _mul_mat(torch, oracle, golden, symbol, fmt, m, n, k, seed=sum(mnk) + len(symbol))
 

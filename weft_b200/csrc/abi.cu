@@ -280,7 +280,8 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
         return fail("a buffer does not meet its Encoding alignment");
     const int sms = g.prop.multiProcessorCount;
     const bool by_blocks = mode == 1 && prefill_blocks_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
-    const bool to_prefill = by_blocks || (mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq));
+    const bool by_codebook = mode == 1 && gr && sg && prefill_codebook_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
+    const bool to_prefill = by_blocks || by_codebook || (mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq));
     // decode: the GEMV's own prologue quantizes X (one launch) when the fp32 rows allow 16-byte loads
     const bool fuse_quantize = !have_xq && !to_prefill && K % 256 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     if (!have_xq && !fuse_quantize &&
@@ -289,7 +290,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     if (to_prefill) {
         PrefillArgs pa{fmt, w, xq, (const uint32_t *)pw, (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
         const bool pair = prefill_pair_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
-        if (launched(by_blocks ? launch_prefill_blocks(pa, sms, g.stream) : pair ? launch_prefill_pair(pa, sms, g.stream) : launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
+        if (launched(by_codebook ? launch_prefill_codebook(pa, (const int8_t *)gr, (const int8_t *)sg, sms, g.stream) : by_blocks ? launch_prefill_blocks(pa, sms, g.stream) : pair ? launch_prefill_pair(pa, sms, g.stream) : launch_prefill(pa, sms, g.stream), "prefill mul_mat")) return 1;
         if (gather && launched(launch_gather_push(*gather, (long long)M, (long long)N, (long long)ldy, g.status_dev, sms, g.stream), "peer all-gather")) return 1;
     } else {
         GemvArgs ga{fmt, w, xq, fuse_quantize ? (const float *)x : nullptr, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw,

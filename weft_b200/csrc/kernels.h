@@ -84,6 +84,11 @@ bool prefill_pair_supported(int fmt, long long n, long long k, long long m, cons
 cudaError_t launch_prefill_blocks(const PrefillArgs &a, int sm_count, cudaStream_t stream);
 bool prefill_blocks_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
 
+// IQ2_XXS x Q8_K with more than a few tokens: one contraction per 32-element group (integer scale 2 s + 1 per group),
+// combined in integers in the epilogue; grid int8[256][8] and signs int8[128][8] (+1 / -1) in device memory.
+cudaError_t launch_prefill_codebook(const PrefillArgs &a, const int8_t *grid, const int8_t *signs, int sm_count, cudaStream_t stream);
+bool prefill_codebook_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
+
 // Bare tcgen05.mma issue loop on every SM (mode 0: kind::i8, one CTA per SM; 1: kind::i8 on CTA pairs; 2: kind::f16):
 // spans_dev receives the nanoseconds each issuing CTA took; *ops_per_launch the operations the whole launch performs.
 cudaError_t measure_mma_peak(int mode, int iterations, int sm_count, unsigned long long *spans_dev, int *status, cudaStream_t stream, double *ops_per_launch);

@@ -368,6 +368,266 @@ __global__ void __launch_bounds__(PB_THREADS, 1) prefill_blocks_kernel(const Blo
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// IQ2_XXS x Q8_K (production_mul_mat_iq2_xxs_staged, examples/kernels/mul_mat/iq2_xxs_staged.py:9-97; per block the math
+// of examples/kernels/vec_dot/iq2_xxs_q8_k.py:8-54, GGML ggml-cpu/quants.c:855-895).  A 32-element group has its own
+// integer scale 2 s + 1 (up to 31) on codebook values of up to 43: the product does not fit int8, so the groups are
+// contracted one by one like the blocks above (two K = 32 steps against a 64-byte row, codes at the operand shift of
+// the Q8_K record, accumulator g of 8) and combined in integers in the epilogue:
+//   isum = sum_g (2 s_g + 1) * D_g;   acc += (d * x.d) * f32(isum);   Y = 0.125 * acc.
+// The weight operand holds grid[index] * sign per element, built from the caller's two tables (staged in shared memory,
+// the sign table as byte masks).  Records are 66 bytes at 2-byte alignment: the expanders read them from global memory
+// with 16-bit loads, one unit ahead.  Activations as in prefill.cu: Q8_K records by TMA, codes at operand byte 4 W.
+constexpr int PC_A_SLOT = PB_A_THIN + 3 * PB_A_COL;           // 38 KB: two slabs and three plain columns
+constexpr int PC_LS_SLOT = 8 * PB_NT * 4;                      // 2 s + 1 per (group, weight)
+constexpr int PC_DW_SLOT = PB_NT * 4;
+constexpr int PC_XD_SLOT = PB_TOKENS * 4;
+constexpr int PC_OFF_A = PB_CONTROL;
+constexpr int PC_OFF_B = PC_OFF_A + PB_STAGES * PC_A_SLOT;
+constexpr int PC_OFF_GRID = PC_OFF_B + PB_STAGES * PB_B_SLOT;  // int8[256][8]
+constexpr int PC_OFF_NEG = PC_OFF_GRID + 2048;                 // per sign index 8 byte masks (0xff where the sign is -1)
+constexpr int PC_OFF_LS = PC_OFF_NEG + 1024;
+constexpr int PC_OFF_DW = PC_OFF_LS + PB_RING * PC_LS_SLOT;
+constexpr int PC_OFF_XD = PC_OFF_DW + PB_RING * PC_DW_SLOT;
+constexpr int PC_SMEM = PC_OFF_XD + PB_RING * PC_XD_SLOT;
+static_assert(PC_A_SLOT % 1024 == 0 && PC_OFF_B % 1024 == 0 && PC_SMEM <= 227 * 1024, "codebook kernel shared memory");
+
+struct CodebookParams {
+    const uint8_t *w;          // (n, k) IQ2_XXS records
+    const int8_t *grid, *signs;
+    float *y;
+    long long n, m, ldy;
+    int units, m_tiles, n_tiles;
+    int *status;
+};
+
+// the 16 bytes {index, meta} x 2 of groups 2x and 2x + 1 of one record, by 16-bit loads (records are 2-byte aligned)
+__device__ __forceinline__ void pc_load_groups(const uint8_t *rec, int x, bool valid, uint32_t (&q)[4], uint32_t &d_bits) {
+    if (valid) {
+        const unsigned short *h = reinterpret_cast<const unsigned short *>(rec);
+        d_bits = __ldg(h);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = (uint32_t)__ldg(h + 1 + 8 * x + 2 * i) | ((uint32_t)__ldg(h + 2 + 8 * x + 2 * i) << 16);
+    } else {
+        d_bits = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) q[i] = 0;
+    }
+}
+
+// one group's 64-byte row: the 32 signed codebook values at word W (operand byte 4 W), zeros around them
+template <int W>
+__device__ __forceinline__ void pc_expand_group(uint32_t index, uint32_t meta, uint32_t grid, uint32_t neg, uint32_t row) {
+    uint32_t v[8];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        uint2 gv, nm;
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(gv.x), "=r"(gv.y) : "r"(grid + 8u * byte_of(index, e)));
+        asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(nm.x), "=r"(nm.y) : "r"(neg + 8u * ((meta >> (7 * e)) & 127u)));
+        // negate the bytes under the mask: ~g + 1 per byte; g <= 43, so no carry leaves a byte
+        v[2 * e] = (gv.x ^ nm.x) + (nm.x & 0x01010101u);
+        v[2 * e + 1] = (gv.y ^ nm.y) + (nm.y & 0x01010101u);
+    }
+    uint32_t out[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) out[i] = (i >= W && i < W + 8) ? v[(i >= W && i < W + 8) ? i - W : 0] : 0u;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) sts_u128(row + 128u * c, out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+}
+
+__global__ void __launch_bounds__(PB_THREADS, 1) prefill_codebook_kernel(const CodebookParams p, const __grid_constant__ CUtensorMap x_wide,
+                                                                          const __grid_constant__ CUtensorMap x_narrow) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    BlockControl *ctl = reinterpret_cast<BlockControl *>(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int my_tiles = (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int units = p.units, total = my_tiles * units;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PB_STAGES; ++s) {
+            mbar_init(&ctl->a_landed[s], 1);
+            mbar_init(&ctl->ab_full[s], PB_X_WARPS + PB_S_WARPS); mbar_init(&ctl->ab_empty[s], 1);
+        }
+        for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], PB_E_WARPS); }
+        ctl->abort = 0;
+        ctl->tmem_base = 0xffffffffu;
+        mbar_fence_init();
+    }
+    // the caller's tables: the grid as it is, the signs (+1 / -1 per element) as byte masks
+    for (int i = threadIdx.x; i < 512; i += PB_THREADS) reinterpret_cast<uint32_t *>(smem + PC_OFF_GRID)[i] = __ldg(reinterpret_cast<const uint32_t *>(p.grid) + i);
+    for (int i = threadIdx.x; i < 256; i += PB_THREADS)
+        reinterpret_cast<uint32_t *>(smem + PC_OFF_NEG)[i] = ((__ldg(reinterpret_cast<const uint32_t *>(p.signs) + i) >> 7) & 0x01010101u) * 0xffu;
+    __syncthreads();
+    if (warp == PB_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PB_TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = ctl->tmem_base;
+    auto tile_of = [&](int it) { return (int)blockIdx.x + (it / units) * (int)gridDim.x; };
+
+    if (warp >= PB_X_WARP0 && warp < PB_X_WARP0 + PB_X_WARPS) {
+        // ------------------------------------------------------------------ expanders: warp x = groups 2x, 2x + 1; lane = weight
+        const int x = warp - PB_X_WARP0;
+        const uint32_t grid = smem_addr(smem + PC_OFF_GRID), neg = smem_addr(smem + PC_OFF_NEG);
+        auto record = [&](int it, bool &valid) {
+            const int tile = tile_of(it);
+            const long long n = (long long)(tile / p.m_tiles) * PB_NT + lane;
+            valid = n < p.n;
+            return p.w + ((size_t)(valid ? n : 0) * units + (it % units)) * 66;
+        };
+        uint32_t qn[4], dn;
+        bool valid = false;
+        if (total > 0) { const uint8_t *rec = record(0, valid); pc_load_groups(rec, x, valid, qn, dn); }
+        for (int it = 0; it < total && !ctl->abort; ++it) {
+            uint32_t q[4] = {qn[0], qn[1], qn[2], qn[3]};
+            const uint32_t d_bits = dn;
+            if (it + 1 < total) { const uint8_t *rec = record(it + 1, valid); pc_load_groups(rec, x, valid, qn, dn); }   // in flight while this unit is expanded
+            const int s = it % PB_STAGES, words = ((it % units) & 3) + 1;
+            if (!pb_wait(&ctl->ab_empty[s], ((uint32_t)(it / PB_STAGES) & 1u) ^ 1u, ctl, p.status)) break;
+            const uint32_t b_slot = smem_addr(smem + PC_OFF_B + s * PB_B_SLOT);
+            const uint32_t row0 = b_slot + (uint32_t)(2 * x) * PB_B_BLOCK + (uint32_t)(lane >> 3) * 512u + (uint32_t)(lane & 7) * 16u;
+            switch (words) {
+            case 1: pc_expand_group<1>(q[0], q[1], grid, neg, row0); pc_expand_group<1>(q[2], q[3], grid, neg, row0 + PB_B_BLOCK); break;
+            case 2: pc_expand_group<2>(q[0], q[1], grid, neg, row0); pc_expand_group<2>(q[2], q[3], grid, neg, row0 + PB_B_BLOCK); break;
+            case 3: pc_expand_group<3>(q[0], q[1], grid, neg, row0); pc_expand_group<3>(q[2], q[3], grid, neg, row0 + PB_B_BLOCK); break;
+            default: pc_expand_group<4>(q[0], q[1], grid, neg, row0); pc_expand_group<4>(q[2], q[3], grid, neg, row0 + PB_B_BLOCK); break;
+            }
+            int *ls = reinterpret_cast<int *>(smem + PC_OFF_LS + (it & (PB_RING - 1)) * PC_LS_SLOT);
+            ls[(2 * x) * PB_NT + lane] = (int)(2u * (q[1] >> 28) + 1u);
+            ls[(2 * x + 1) * PB_NT + lane] = (int)(2u * (q[3] >> 28) + 1u);
+            if (x == 0) reinterpret_cast<float *>(smem + PC_OFF_DW + (it & (PB_RING - 1)) * PC_DW_SLOT)[lane] = half_bits_to_float(d_bits);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->ab_full[s]);
+        }
+    } else if (warp >= PB_S_WARP0 && warp < PB_S_WARP0 + PB_S_WARPS) {
+        // ------------------------------------------------------------------ x.d of every token (record byte 0 = operand byte 4 (W - 1))
+        const int ts = threadIdx.x - 32 * PB_S_WARP0;
+        for (int it = 0; it < total && !ctl->abort; ++it) {
+            const int s = it % PB_STAGES, shift = 4 * ((it % units) & 3);
+            if (!pb_wait(&ctl->a_landed[s], (uint32_t)(it / PB_STAGES) & 1u, ctl, p.status)) break;
+            const uint32_t a_slot = smem_addr(smem + PC_OFF_A + s * PC_A_SLOT);
+            const uint32_t xd_slot = smem_addr(smem + PC_OFF_XD + (it & (PB_RING - 1)) * PC_XD_SLOT);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int row = ts + 64 * k;
+                sts_u32(xd_slot + 4u * (uint32_t)row, lds32(a_slot + sw128_offset(row, 0) + (uint32_t)shift));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->ab_full[s]);
+        }
+    } else if (warp == PB_TMA_WARP) {
+        // ------------------------------------------------------------------ activation boxes
+        if (lane == 0) {
+            int issued = 0;
+            for (int it = 0; it < total && !ctl->abort; ++it) {
+                const int s = it % PB_STAGES, b = it % units, tile = tile_of(it);
+                const int m0 = (tile % p.m_tiles) * PB_TOKENS;
+                if (!pb_wait(&ctl->ab_empty[s], ((uint32_t)(it / PB_STAGES) & 1u) ^ 1u, ctl, p.status)) break;
+                fence_proxy_async();
+                uint8_t *slot = smem + PC_OFF_A + s * PC_A_SLOT;
+                const int x0 = 73 * b - (b & 3);       // the 16-byte boundary at or before record b of a token row, in words
+                mbar_expect_tx(&ctl->a_landed[s], PC_A_SLOT);
+                tma_load_2d(slot, &x_wide, x0, m0, &ctl->a_landed[s]);
+                tma_load_2d(slot + PB_A_SLAB, &x_wide, x0 + 32, m0, &ctl->a_landed[s]);
+                tma_load_2d(slot + PB_A_THIN, &x_narrow, x0 + 64, m0, &ctl->a_landed[s]);
+                tma_load_2d(slot + PB_A_THIN + PB_A_COL, &x_narrow, x0 + 68, m0, &ctl->a_landed[s]);
+                tma_load_2d(slot + PB_A_THIN + 2 * PB_A_COL, &x_narrow, x0 + 72, m0, &ctl->a_landed[s]);
+                issued = it + 1;
+            }
+            for (int k = issued > PB_STAGES ? issued - PB_STAGES : 0; k < issued; ++k) mbar_wait(&ctl->a_landed[k % PB_STAGES], (uint32_t)(k / PB_STAGES) & 1u);
+        }
+    } else if (warp == PB_MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t idesc = tc::idesc_i8(PB_TOKENS, PB_NT, true, true);
+            for (int it = 0; it < total && !ctl->abort; ++it) {
+                const int s = it % PB_STAGES, buf = it & 1;
+                if (!pb_wait(&ctl->ab_full[s], (uint32_t)(it / PB_STAGES) & 1u, ctl, p.status)) break;
+                if (!pb_wait(&ctl->tmem_empty[buf], ((uint32_t)(it >> 1) & 1u) ^ 1u, ctl, p.status)) break;
+                tc::fence_after_sync();
+                const uint32_t a_q = smem_addr(smem + PC_OFF_A + s * PC_A_SLOT), b_q = smem_addr(smem + PC_OFF_B + s * PB_B_SLOT);
+                const uint64_t a0 = tc::smem_desc_sw128(a_q);
+                const uint64_t a_thin = tc::smem_desc(a_q + PB_A_THIN, PB_A_COL, 128);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const uint32_t d = tmem + (uint32_t)(buf * PB_BUF_COLS + g * PB_NT);
+                    const uint32_t bg = b_q + (uint32_t)g * PB_B_BLOCK;
+                    tc::mma_i8(d, a0 + (uint64_t)(((g >> 2) * PB_A_SLAB + (g & 3) * 32) >> 4), tc::smem_desc(bg, 128, 512), idesc, 0);
+                    if (g < 7) tc::mma_i8(d, a0 + (uint64_t)((((g + 1) >> 2) * PB_A_SLAB + ((g + 1) & 3) * 32) >> 4), tc::smem_desc(bg + 256, 128, 512), idesc, 1);
+                    else tc::mma_i8(d, a_thin, tc::smem_desc(bg + 256, 128, 512), idesc, 1);
+                }
+                tc::commit(&ctl->tmem_full[buf]);
+                tc::commit(&ctl->ab_empty[s]);
+            }
+        }
+    } else if (warp < PB_E_WARPS) {
+        // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, 16 of the 32 weights)
+        const int quarter = warp & 3, half = warp >> 2;
+        const int row = quarter * 32 + lane;
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * 16);
+        float acc[16];
+        int it = 0;
+        bool ok = true;
+        for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
+            const int tile = (int)blockIdx.x + t * (int)gridDim.x;
+            const long long n0 = (long long)(tile / p.m_tiles) * PB_NT + half * 16, m = (long long)(tile % p.m_tiles) * PB_TOKENS + row;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+            for (int u = 0; u < units && ok; ++u, ++it) {
+                const int buf = it & 1;
+                if (!pb_wait(&ctl->tmem_full[buf], (uint32_t)(it >> 1) & 1u, ctl, p.status)) { ok = false; break; }
+                tc::fence_after_sync();
+                const float xd = reinterpret_cast<const float *>(smem + PC_OFF_XD + (it & (PB_RING - 1)) * PC_XD_SLOT)[row];
+                const float *dw = reinterpret_cast<const float *>(smem + PC_OFF_DW + (it & (PB_RING - 1)) * PC_DW_SLOT) + half * 16;
+                const int4 *ls = reinterpret_cast<const int4 *>(smem + PC_OFF_LS + (it & (PB_RING - 1)) * PC_LS_SLOT) + half * 4;
+                const uint32_t cols = lane_base + (uint32_t)(buf * PB_BUF_COLS);
+                uint32_t cur[16], nxt[16];
+                int isum[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) isum[i] = 0;
+                tc::tmem_ld16(cols, cur);
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    tc::tmem_ld_wait();
+                    if (g < 7) tc::tmem_ld16(cols + (uint32_t)((g + 1) * PB_NT), nxt);   // in flight while group g is combined
+#pragma unroll
+                    for (int i = 0; i < 16; i += 4) {
+                        const int4 l = ls[g * (PB_NT / 4) + (i >> 2)];
+                        isum[i] += (int)cur[i] * l.x; isum[i + 1] += (int)cur[i + 1] * l.y;
+                        isum[i + 2] += (int)cur[i + 2] * l.z; isum[i + 3] += (int)cur[i + 3] * l.w;
+                    }
+                    if (g < 7) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) cur[i] = nxt[i];
+                    }
+                }
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->tmem_empty[buf]);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[i] += (dw[i] * xd) * (float)isum[i];
+            }
+            if (!ok) break;
+            if (m < p.m) {
+                float *out = p.y + (size_t)m * p.ldy + n0;
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    if (n0 + i < p.n) out[i] = 0.125f * acc[i];
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    if (warp == PB_MMA_WARP) {
+        __syncwarp();
+        if (tmem != 0xffffffffu) tc::tmem_free(tmem, PB_TMEM_COLS);
+    }
+}
+
 }  // namespace
 
 bool prefill_blocks_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq) {
@@ -375,6 +635,34 @@ bool prefill_blocks_supported(int fmt, long long n, long long k, long long m, co
     // which the TMA box copies of activations and raw weights need; both bases 16-byte aligned
     return (fmt == F_Q4_0 || fmt == F_Q8_0) && m >= 32 && k > 0 && k % 256 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
            (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
+}
+
+bool prefill_codebook_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq) {
+    // K a multiple of 1024: Q8_K rows (292 bytes per 256) are then whole 16-byte multiples, which the TMA box loads need
+    return fmt == F_IQ2_XXS && m >= 32 && k > 0 && k % 1024 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
+           (reinterpret_cast<uintptr_t>(w) & 1u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
+}
+
+cudaError_t launch_prefill_codebook(const PrefillArgs &a, const int8_t *grid, const int8_t *signs, int sm_count, cudaStream_t stream) {
+    if (!prefill_codebook_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq) || !grid || !signs) return cudaErrorNotSupported;
+    if ((reinterpret_cast<uintptr_t>(grid) & 3u) || (reinterpret_cast<uintptr_t>(signs) & 3u)) return cudaErrorNotSupported;
+    CodebookParams p;
+    p.w = static_cast<const uint8_t *>(a.w); p.grid = grid; p.signs = signs;
+    p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.units = (int)(a.k / 256); p.status = a.status;
+    p.m_tiles = (int)((a.m + PB_TOKENS - 1) / PB_TOKENS);
+    p.n_tiles = (int)((a.n + PB_NT - 1) / PB_NT);
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    CUtensorMap x_wide, x_narrow;
+    cudaError_t e = encode_tile_map(&x_wide, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.units * 73, (unsigned long long)a.m,
+                                    (unsigned long long)p.units * 292, 32, PB_TOKENS, true);
+    if (e == cudaSuccess)
+        e = encode_tile_map(&x_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.units * 73, (unsigned long long)a.m,
+                            (unsigned long long)p.units * 292, 4, PB_TOKENS, false);
+    if (e == cudaSuccess) e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_codebook_kernel), PC_SMEM);
+    if (e != cudaSuccess) return e;
+    const int grid_size = (int)(tiles < sm_count ? tiles : sm_count);
+    prefill_codebook_kernel<<<grid_size, PB_THREADS, PC_SMEM, stream>>>(p, x_wide, x_narrow);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_prefill_blocks(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
