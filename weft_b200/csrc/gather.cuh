@@ -57,6 +57,23 @@ __device__ __forceinline__ void gather_store(const GatherArgs &g, int epoch, lon
     }
 }
 
+// The same for a group of lanes that all hold the result: lane `sub` of the group stores to ONE peer (the peers' stores
+// leave together instead of one after the other from a single lane).  Lanes with sub >= world - 1 do nothing.
+__device__ __forceinline__ void gather_store_spread(const GatherArgs &g, int epoch, long long row, long long col, long long ldy, float v, int sub) {
+    if (sub >= g.world - 1) return;
+    const int r = sub + (sub >= g.rank ? 1 : 0);
+    if (g.ll) {
+        const size_t slot = (size_t)(epoch & 1) * GATHER_LL_MAX_VALUES + (size_t)row * ldy + (size_t)(g.n0 + col);
+        asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" :: "l"(g.stage[r] + slot), "r"(__float_as_uint(v)), "r"((uint32_t)epoch) : "memory");
+    } else {
+        g.y[r][(size_t)row * ldy + col] = v;
+    }
+}
+
+// How many CTAs of a fused GEMV take the receiving side.  The others leave as soon as their rows are stored, so the
+// next launch in the stream finds free SMs and streams its first weights while the values are still crossing NVLink.
+constexpr int GATHER_RECV_CTAS = 12;
+
 // Flagged-value protocol: this warp's share (`warp_index` of `warps`) of the values the other ranks send;
 // n_local = columns this rank computes, ldy = N, m = output rows.
 __device__ __forceinline__ void gather_receive(const GatherArgs &g, int epoch, long long m, long long n_local, long long ldy,

@@ -323,13 +323,20 @@ __global__ void __launch_bounds__(QK_MAX_THREADS) gemv_q4k_kernel(const Q4kParam
             } else {
                 y[grow] = v;
             }
-            if (MODE == 2) gather_store(p.gather, epoch, blockIdx.y, grow, p.ldy, v);
             mbar_arrive_a(empty_addr + 8 * (ss & (S - 1)));   // after the shuffles: every lane's shared loads have completed
+        }
+        if (MODE == 2 && (!upper || two)) {   // every lane of a half-warp holds its row's sum: lane i stores to peer i
+            const int tt = upper ? t1 : t, ss = upper ? s1 : s0;
+            const long long grow = ss < p.full_rounds ? ((((long long)ss * G + b) << LSR) + (tt & (SR - 1)))
+                                                       : tail_begin + (tt - (p.full_rounds << LSR));
+            gather_store_spread(p.gather, epoch, blockIdx.y, grow, p.ldy, v, lane & 15);
         }
     }
     if (MODE == 2) {
-        const int warps = (int)(gridDim.x * gridDim.y) * consumers;
-        gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)(blockIdx.y * gridDim.x + blockIdx.x) * consumers + warp - 1, warps, p.status);
+        // a few CTAs receive for the whole grid; the others are done
+        const int recv = min((int)gridDim.x, GATHER_RECV_CTAS), warps = (int)(gridDim.x * gridDim.y) * consumers;
+        if ((int)blockIdx.x < recv && blockIdx.y == 0)
+            gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)blockIdx.x * consumers + warp - 1, recv * consumers, p.status);
         gather_finish(p.gather, epoch, p.status, warps);
     }
 }

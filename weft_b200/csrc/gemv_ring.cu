@@ -192,8 +192,10 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
         if (lane == 0) mbar_arrive_a(empty_addr + 8 * (s & (S - 1)));
     }
     if (GATHER) {
-        const int warps = (int)(gridDim.x * gridDim.y) * consumers;
-        gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)(blockIdx.y * gridDim.x + blockIdx.x) * consumers + warp - 1, warps, p.status);
+        // a few CTAs receive for the whole grid; the others are done
+        const int recv = min((int)gridDim.x, GATHER_RECV_CTAS), warps = (int)(gridDim.x * gridDim.y) * consumers;
+        if ((int)blockIdx.x < recv && blockIdx.y == 0)
+            gather_receive(p.gather, epoch, gridDim.y, p.n, p.ldy, (int)blockIdx.x * consumers + warp - 1, recv * consumers, p.status);
         gather_finish(p.gather, epoch, p.status, warps);
     }
 }
