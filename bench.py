@@ -64,11 +64,13 @@ DEFAULT_WORKLOAD = "q4_k_decode_14336x4096"
 # carried here; a sharded run scales them by the rank's share of the rows).  Writes that are still in L2
 # when the kernel ends are not in these numbers.
 NCU_DRAM_TRAFFIC = {
-    "q4_k_decode_14336x4096": 33_076_480,
-    "iq2_xxs_decode_28672x8192": 60_807_168,
-    "q4_k_prefill_4096x4096": 11_907_328,
+    "q4_k_decode_14336x4096": 33_078_272,
+    "iq2_xxs_decode_28672x8192": 60_635_904,
+    "q4_k_prefill_4096x4096": 11_908_608,
+    "q8_0_prefill_4096x4096": 20_104_448,
+    "iq2_xxs_prefill_4096x4096": 6_777_344,
     "tq1_0_prefill_28672x8192": 67_826_432,
-    "q4_k_dequantize_14336x4096": 33_040_000 + 177_400_000,
+    "q4_k_dequantize_14336x4096": 33_041_920 + 177_308_928,
 }
 
 
