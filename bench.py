@@ -873,11 +873,17 @@ def run_mul_mat(args, lib, check, stream, workload: str, world: int, rank: int, 
         y_page = np.zeros((m, n), dtype=np.float32)      # pageable memory, what a plain numpy caller of the reference passes
         x_page, xq_page = x_host.copy(), np.zeros((m, row_bytes(act, k)), dtype=np.uint8)
 
+        # addresses taken once: a C caller of the entry point has them at hand, the interpreter would spend 2 us per step on them
+        w_ptrs = [w.data_ptr() for w in w_dev]
+        host_ptrs = {True: (x_pin.data_ptr(), xq_pin.data_ptr(), y_pin.data_ptr()),
+                     False: (x_page.ctypes.data, xq_page.ctypes.data, y_page.ctypes.data)}
+        table_ptrs = (grid_pin.data_ptr(), signs_pin.data_ptr(), powers_pin.data_ptr())
+
         def e2e_step(i: int, pinned: bool = True) -> None:
             if world == 1:
-                xs = (x_pin.data_ptr(), xq_pin.data_ptr(), y_pin.data_ptr()) if pinned else (x_page.ctypes.data, xq_page.ctypes.data, y_page.ctypes.data)
-                check(shard_fn(fid, mode_id, w_dev[i % copies].data_ptr(), xs[0], xs[1], grid_pin.data_ptr(),
-                               signs_pin.data_ptr(), powers_pin.data_ptr(), xs[2], n_local, k, m, n, 0))
+                xs = host_ptrs[pinned]
+                check(shard_fn(fid, mode_id, w_ptrs[i % copies], xs[0], xs[1], table_ptrs[0], table_ptrs[1], table_ptrs[2],
+                               xs[2], n_local, k, m, n, 0))
             elif peers is not None:
                 step(i, 0, x_pin.data_ptr(), None)
                 check(lib.weft_b200_peer_read(y_pin.data_ptr(), peers.local[(calls[0] - 1) % 2], 4 * m * n))

@@ -352,7 +352,9 @@ def test_c_abi_with_pinned_host_buffers(torch, weft, oracle):
     fn.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_size_t] * 3
     fn.restype = ctypes.c_int
     rng = np.random.default_rng(78)
-    for n, k, m, shift in [(1024, 2048, 1, 0), (333, 768, 3, 4), (64, 256, 1, 4)]:
+    # the larger cases: every CTA collects several rounds of rows and a ragged tail before it stores them to the host;
+    # the last one has more rows per CTA than the kernel collects, so every row is stored as it completes
+    for n, k, m, shift in [(1024, 2048, 1, 0), (333, 768, 3, 4), (64, 256, 1, 4), (14336, 4096, 1, 0), (5003, 1024, 2, 4), (90000, 256, 1, 0)]:
         w = weights(oracle.Q4_K, rng, n, k)
         x = activations(rng, m, k)
         want, want_xq = oracle.mul_mat(oracle.Q4_K, w, x, n, k, m, rule=1)

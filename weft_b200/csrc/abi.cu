@@ -116,6 +116,7 @@ class Call {
     // is handed to them as it is -- their stores go to the caller's buffer, no staging slice and no copy back.
     int map(const void *ptr, size_t bytes, bool read, bool written, void **out, bool direct = false) {
         *out = nullptr;
+        direct_ = false;
         if (bytes == 0) { *out = const_cast<void *>(ptr); return 0; }
         if (!ptr) return fail("a required buffer is NULL");
         cudaPointerAttributes attr{};
@@ -142,7 +143,7 @@ class Call {
         Arg arg;
         arg.user = ptr; arg.bytes = bytes; arg.written = written;
         if (attr.type == cudaMemoryTypeHost && attr.devicePointer && bytes <= kKernelCopyMax) arg.mapped = attr.devicePointer;
-        if (direct && written && !read && arg.mapped) { *out = arg.mapped; return 0; }
+        if (direct && written && !read && arg.mapped) { *out = arg.mapped; direct_ = true; return 0; }
         if (slice(arg)) return 1;
         if (read) {
             if (arg.mapped) CU(launch_copy_bytes(arg.dev, arg.mapped, bytes, g.stream));
@@ -184,7 +185,11 @@ class Call {
         return 0;
     }
 
+    // true when the latest map() handed the caller's pinned buffer to the kernels as it is
+    bool direct() const { return direct_; }
+
   private:
+    bool direct_ = false;
     int slice(Arg &arg) {
         const size_t offset = (used_ + 255) & ~size_t(255);
         wanted_ = ((wanted_ + 255) & ~size_t(255)) + arg.bytes;
@@ -275,6 +280,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     // a host Y with a pitch is staged whole (pitch * M floats); device Y is written in place; a small pinned Y too
     const size_t y_floats = (M - 1) * ldy + N;
     if (call.map(Y, y_floats * sizeof(float), ldy != N, true, &y, ldy == N && gather == nullptr)) return 1;
+    const bool y_on_host = call.direct();
     if ((reinterpret_cast<uintptr_t>(w) & (fmt == F_Q4_K_I16 ? 15u : 1u)) || (reinterpret_cast<uintptr_t>(xq) & (act == F_Q8_K ? 3u : 1u)) ||
         (reinterpret_cast<uintptr_t>(y) & 3u) || (x && (reinterpret_cast<uintptr_t>(x) & 3u)))
         return fail("a buffer does not meet its Encoding alignment");
@@ -294,7 +300,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
         if (gather && launched(launch_gather_push(*gather, (long long)M, (long long)N, (long long)ldy, g.status_dev, sms, g.stream), "peer all-gather")) return 1;
     } else {
         GemvArgs ga{fmt, w, xq, fuse_quantize ? (const float *)x : nullptr, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw,
-                    (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
+                    (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev, y_on_host};
         const bool fused = gather && gemv_gathers(ga);
         if (fused) ga.gather = *gather;
         if (launched(launch_gemv(ga, sms, g.stream), "decode mul_mat")) return 1;

@@ -37,6 +37,7 @@ struct GemvArgs {
     float *y;                // (m, ldy) fp32; column n of row r at y[r * ldy + n]
     long long n, k, m, ldy;
     int *status;             // mapped status word
+    bool y_on_host;          // y is pinned host memory seen through its device mapping: store it in few, wide pieces
     GatherArgs gather;       // world > 1: results also go to every peer's buffer and the launch ends with the ranks' barrier
     // Several weight matrices against the same activations in one launch (m = 1): matrix i has seg_rows[i] rows at
     // seg_w[i] and writes seg_y[i]; w / y / n are then unused.  0 or 1: the single matrix w.
