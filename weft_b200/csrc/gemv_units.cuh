@@ -82,8 +82,11 @@ __device__ __forceinline__ void dot_q2_k(const uint8_t *const (&wp)[RL], const u
         ld_words_a2<21>(wp[r], wv[r]);
         isum[r] = 0; msum[r] = 0;
 #pragma unroll
-        for (int g = 0; g < 16; ++g)
-            msum[r] += (int)(int16_t)(bs[g >> 1] >> (16 * (g & 1))) * (int)(byte_of(wv[r][g >> 2], g & 3) >> 4);
+        for (int q = 0; q < 4; ++q) {   // four mins as bytes against two pairs of 16-bit sums: two dp2a
+            const int mins4 = (int)((wv[r][q] >> 4) & 0x0f0f0f0fu);
+            msum[r] = __dp2a_lo((int)bs[2 * q], mins4, msum[r]);
+            msum[r] = __dp2a_hi((int)bs[2 * q + 1], mins4, msum[r]);
+        }
     }
 #pragma unroll
     for (int n = 0; n < 2; ++n)
@@ -96,10 +99,11 @@ __device__ __forceinline__ void dot_q2_k(const uint8_t *const (&wp)[RL], const u
                 const int g = 8 * n + 2 * j + c;
 #pragma unroll
                 for (int r = 0; r < RL; ++r) {
+                    // the 2-bit plane is masked where it lies: the sum comes out times 4^j (bytes up to 192, exact)
                     int dp = 0;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) dp = dp4a_us((wv[r][4 + 8 * n + 4 * c + i] >> (2 * j)) & 0x03030303u, xw[i], dp);
-                    isum[r] += (int)(byte_of(wv[r][g >> 2], g & 3) & 15u) * dp;
+                    for (int i = 0; i < 4; ++i) dp = dp4a_us(wv[r][4 + 8 * n + 4 * c + i] & (0x03030303u << (2 * j)), xw[i], dp);
+                    isum[r] += (int)(byte_of(wv[r][g >> 2], g & 3) & 15u) * (dp >> (2 * j));
                 }
             }
 #pragma unroll
