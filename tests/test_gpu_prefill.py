@@ -84,6 +84,40 @@ def test_prefill_matches_decode_path(torch, oracle):
     assert rel_l2(outs[0], outs[1]) <= 1e-5
 
 
+@pytest.mark.parametrize("m", [64, 300])
+def test_prefill_q4_k_saturated_records(torch, oracle, m):
+    """Every weight nibble 15, every 6-bit scale and min 63, every activation code +-127: the largest sums a block can
+    produce (limb sums of 3.4 million, min-term sums of 2 million), through the single-CTA (64 tokens) and the
+    CTA-pair (300 tokens) kernels.  The integer part must still be exact."""
+    import weft_b200 as weft
+    from weft_b200.kernels import mul_mat
+    from weft_b200.runtime import Buffer
+
+    n, k = 176, 2048
+    record = np.full(144, 0xFF, dtype=np.uint8)
+    record[0:2] = np.frombuffer(np.float16(0.5).tobytes(), dtype=np.uint8)
+    record[2:4] = np.frombuffer(np.float16(0.25).tobytes(), dtype=np.uint8)
+    w = np.tile(record, (n, k // 256))
+    # rows of all-positive, all-negative and alternating extremes; the block maximum sits on every element
+    x = np.empty((m, k), dtype=np.float32)
+    x[0::3] = 3.0
+    x[1::3] = -3.0
+    x[2::3] = np.where(np.arange(k) % 2 == 0, 3.0, -3.0)
+    xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
+    y = torch.full((m, n), float("nan"), device="cuda")
+    weft.compile(mul_mat.production_mul_mat_q4_k_staged)(
+        Buffer(torch.from_numpy(w).cuda(), shape=(n, k), encoding="Q4_K"), torch.from_numpy(x).cuda(),
+        Buffer(xq, shape=(m, k), encoding="Q8_K"), y)
+    want_xq = oracle.quantize(oracle.Q8_K, x, rule=1)
+    assert np.array_equal(xq.cpu().numpy(), want_xq)
+    codes = want_xq.reshape(m, k // 256, 292)[:, :, 4:260].view(np.int8)
+    assert int(np.abs(codes).min()) == 127
+    want, _ = oracle.mul_mat(oracle.Q4_K, w, None, n, k, m, xq=want_xq)
+    got = y.cpu().numpy()
+    assert rel_l2(got, want) <= 1e-6, rel_l2(got, want)
+    assert reference_tolerance_ok(got, want)
+
+
 def _run_tq1_0(torch, oracle, m, n, k, seed, column_ranges=None):
     import weft_b200 as weft
     from weft_b200.kernels import mul_mat
