@@ -117,31 +117,54 @@ __device__ __forceinline__ void half_record2(uint32_t q0, uint32_t q1, const uin
     r1 = half_bits_to_float(h1.x) * (float)i1 - half_bits_to_float(h1.x >> 16) * (float)m1;
 }
 
-// fp32 row -> staged Q8_K records (codes at u*QK_XQ_PITCH, aux {d, pair sums}); optionally also to global
-__device__ void q4k_quantize_stage(const float *x, int nb, uint8_t *s_q, uint8_t *s_aux, uint8_t *out) {
-    const int lane = threadIdx.x & 31;
-    for (int u = threadIdx.x >> 5; u < nb; u += blockDim.x >> 5) {
-        float v[8];
-        load8<true>(x + u * 256 + 8 * lane, v);
-        uint32_t q0, q1;
-        int sum16;
-        float d;
-        q8_k_warp(v, q0, q1, sum16, d);
-        *reinterpret_cast<uint2 *>(s_q + u * QK_XQ_PITCH + 8 * lane) = make_uint2(q0, q1);
-        const int s32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
-        int *aux = reinterpret_cast<int *>(s_aux + u * QK_XAUX);
-        if ((lane & 3) == 0) aux[4 + (lane >> 2)] = s32;
-        if (lane == 0) aux[0] = __float_as_int(d);
-        if (out) store_q8_k(out + (size_t)u * 292, lane, q0, q1, sum16, d);
+// fp32 row -> staged Q8_K records (codes at u*QK_XQ_PITCH, aux {d, pair sums}); optionally also to global.
+// A warp's blocks are u = warp, warp + warps, ...; the loads of four of them are issued before the first is worked on
+// (a load from L2 takes longer than quantizing a block; 9.54 -> 9.41 us per step for K = 14336).
+__device__ void q4k_quantize_stage(const float *__restrict__ x, int nb, uint8_t *s_q, uint8_t *s_aux, uint8_t *out) {
+    const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    constexpr int B = 4;
+    for (int u0 = threadIdx.x >> 5; u0 < nb; u0 += B * warps) {
+        float v[B][8];
+#pragma unroll
+        for (int i = 0; i < B; ++i)
+            if (u0 + i * warps < nb) load8<true>(x + (u0 + i * warps) * 256 + 8 * lane, v[i]);
+#pragma unroll
+        for (int i = 0; i < B; ++i) {
+            const int u = u0 + i * warps;
+            if (u < nb) {
+                uint32_t q0, q1;
+                int sum16;
+                float d;
+                q8_k_warp(v[i], q0, q1, sum16, d);
+                *reinterpret_cast<uint2 *>(s_q + u * QK_XQ_PITCH + 8 * lane) = make_uint2(q0, q1);
+                const int s32 = sum16 + __shfl_xor_sync(0xffffffffu, sum16, 2);
+                int *aux = reinterpret_cast<int *>(s_aux + u * QK_XAUX);
+                if ((lane & 3) == 0) aux[4 + (lane >> 2)] = s32;
+                if (lane == 0) aux[0] = __float_as_int(d);
+                if (out) store_q8_k(out + (size_t)u * 292, lane, q0, q1, sum16, d);
+            }
+        }
     }
 }
 
-__device__ void q4k_stage_records(const uint8_t *xq, int nb, uint8_t *s_q, uint8_t *s_aux) {
-    for (int i = threadIdx.x; i < nb * 64; i += blockDim.x) {
-        const int u = i >> 6, wd = i & 63;
-        *reinterpret_cast<uint32_t *>(s_q + u * QK_XQ_PITCH + 4 * wd) = *reinterpret_cast<const uint32_t *>(xq + (size_t)u * 292 + 4 + 4 * wd);
+// Q8_K records -> the same staged form, four loads in flight per thread
+__device__ void q4k_stage_records(const uint8_t *__restrict__ xq, int nb, uint8_t *s_q, uint8_t *s_aux) {
+    constexpr int B = 4;
+    const int threads = blockDim.x;
+    for (int i0 = threadIdx.x; i0 < nb * 64; i0 += B * threads) {
+        uint32_t w[B];
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            const int i = i0 + j * threads;
+            if (i < nb * 64) w[j] = *reinterpret_cast<const uint32_t *>(xq + (size_t)(i >> 6) * 292 + 4 + 4 * (i & 63));
+        }
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            const int i = i0 + j * threads;
+            if (i < nb * 64) *reinterpret_cast<uint32_t *>(s_q + (i >> 6) * QK_XQ_PITCH + 4 * (i & 63)) = w[j];
+        }
     }
-    for (int i = threadIdx.x; i < nb * 9; i += blockDim.x) {
+    for (int i = threadIdx.x; i < nb * 9; i += threads) {
         const int u = i / 9, f = i % 9;
         const uint8_t *rec = xq + (size_t)u * 292;
         int *aux = reinterpret_cast<int *>(s_aux + u * QK_XAUX);
