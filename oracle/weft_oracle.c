@@ -71,6 +71,8 @@ size_t wo_record_bytes(int fmt) {
     case WO_Q5_K: return 176;
     case WO_Q6_K: return 210;
     case WO_IQ2_XXS: return 66;
+    case WO_IQ2_XS: return 74;
+    case WO_IQ3_XXS: return 98;
     case WO_TQ1_0: return 54;
     case WO_Q8_K: return 292;
     default: return 0;
@@ -80,7 +82,7 @@ size_t wo_record_bytes(int fmt) {
 size_t wo_record_elements(int fmt) {
     switch (fmt) {
     case WO_Q4_0: case WO_Q8_0: case WO_Q8_1: return 32;
-    case WO_Q2_K: case WO_Q3_K: case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
+    case WO_Q2_K: case WO_Q3_K: case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_IQ2_XS: case WO_IQ3_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
     default: return 0;
     }
 }
@@ -468,7 +470,7 @@ static void wo_quantize_range(int64_t begin, int64_t end, void *p) {
 
 int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrows, int64_t k) {
     wo_quant_ctx c = {fmt, rule, x, y, k, wo_row_bytes(fmt, k)};
-    if (!c.rb || fmt == WO_IQ2_XXS) return -1;
+    if (!c.rb || fmt == WO_IQ2_XXS || fmt == WO_IQ2_XS || fmt == WO_IQ3_XXS) return -1;
     wo_parallel_for(nrows, wo_quantize_range, &c);
     return 0;
 }
@@ -531,6 +533,46 @@ void wo_dequantize_row_iq2_xxs(const uint8_t *w, const int8_t *grid, const int8_
     }
 }
 
+/* ggml/src/ggml-quants.c:2444-2468; examples/kernels/dequantize/iq2_xs.py:9-68.
+ * Record (74 bytes): f16 d @0, 32 u16 codes @2 (grid index in bits 0-8, sign index in bits 9-15, one code per 8
+ * weights), 8 scale bytes @66 (low nibble: first 16 weights of a 32-group, high nibble: the other 16). */
+void wo_dequantize_row_iq2_xs(const uint8_t *w, const int8_t *grid, const int8_t *signs, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 74) {
+        const float d = wo_f16_to_f32(ld_u16(w));
+        for (int g = 0; g < 8; ++g) {
+            const uint8_t sc = w[66 + g];
+            const float db[2] = {d * (0.5f + (float)(sc & 15)) * 0.25f, d * (0.5f + (float)(sc >> 4)) * 0.25f};
+            for (int e = 0; e < 4; ++e) {
+                const uint16_t code = ld_u16(w + 2 + 2 * (4 * g + e));
+                const int8_t *gv = grid + 8 * (code & 511);
+                const int8_t *sv = signs + 8 * (code >> 9);
+                for (int j = 0; j < 8; ++j) *y++ = db[e >> 1] * (float)(uint8_t)gv[j] * (float)sv[j];
+            }
+        }
+    }
+}
+
+/* ggml/src/ggml-quants.c:2506-2536; examples/kernels/dequantize/iq3_xxs.py.
+ * Record (98 bytes): f16 d @0, 64 grid-index bytes @2 (one per 4 weights), 8 u32 @66: four 7-bit sign indices (one per
+ * 8 weights) and a 4-bit scale in bits 28-31, one word per 32 weights. */
+void wo_dequantize_row_iq3_xxs(const uint8_t *w, const int8_t *grid, const int8_t *signs, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 98) {
+        const float d = wo_f16_to_f32(ld_u16(w));
+        for (int g = 0; g < 8; ++g) {
+            uint32_t meta;
+            memcpy(&meta, w + 66 + 4 * g, 4);
+            const float db = d * (0.5f + (float)(meta >> 28)) * 0.5f;
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *sv = signs + 8 * ((meta >> (7 * e)) & 127);
+                const int8_t *g1 = grid + 4 * w[2 + 8 * g + 2 * e], *g2 = grid + 4 * w[2 + 8 * g + 2 * e + 1];
+                for (int j = 0; j < 4; ++j) y[j] = db * (float)(uint8_t)g1[j] * (float)sv[j];
+                for (int j = 0; j < 4; ++j) y[4 + j] = db * (float)(uint8_t)g2[j] * (float)sv[4 + j];
+                y += 8;
+            }
+        }
+    }
+}
+
 /* one base-3 digit of a packed byte, digit 0 = most significant:
  * ggml/src/ggml-quants.c:2369-2371; examples/functions/quantization.py:49-64 */
 static inline int tq1_digit(uint8_t packed, int n) {
@@ -568,6 +610,8 @@ static void wo_dequantize_range(int64_t begin, int64_t end, void *p) {
         case WO_Q5_K: wo_dequantize_row_q5_K(wr, yr, c->k); break;
         case WO_Q6_K: wo_dequantize_row_q6_K(wr, yr, c->k); break;
         case WO_IQ2_XXS: wo_dequantize_row_iq2_xxs(wr, c->grid, c->signs, yr, c->k); break;
+        case WO_IQ2_XS: wo_dequantize_row_iq2_xs(wr, c->grid, c->signs, yr, c->k); break;
+        case WO_IQ3_XXS: wo_dequantize_row_iq3_xxs(wr, c->grid, c->signs, yr, c->k); break;
         case WO_TQ1_0: wo_dequantize_row_tq1_0(wr, yr, c->k); break;
         default: break;
         }
@@ -834,6 +878,61 @@ float wo_vec_dot_iq2_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *
     return 0.125f * sumf;
 }
 
+/* ggml/src/ggml-cpu/quants.c (ggml_vec_dot_iq2_xs_q8_K_generic); examples/kernels/vec_dot/iq2_xs_q8_k.py:9-39,
+ * examples/functions/quantization.py:71-83: per 16 weights an odd integer scale 2 s + 1, result times 0.125 */
+float wo_vec_dot_iq2_xs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k) {
+    float sumf = 0.f;
+    for (int64_t b = 0; b < k / 256; ++b, w += 74, x += 292) {
+        const float d = wo_f16_to_f32(ld_u16(w)) * ld_f32(x);
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int32_t bsum = 0;
+        for (int g = 0; g < 8; ++g) {
+            const uint8_t sc = w[66 + g];
+            for (int half = 0; half < 2; ++half) {
+                const int32_t ls = 2 * (half ? sc >> 4 : sc & 15) + 1;
+                int32_t sumi = 0;
+                for (int e = 2 * half; e < 2 * half + 2; ++e) {
+                    const uint16_t code = ld_u16(w + 2 + 2 * (4 * g + e));
+                    const int8_t *gv = grid + 8 * (code & 511);
+                    const int8_t *sv = signs + 8 * (code >> 9);
+                    for (int j = 0; j < 8; ++j) sumi += (int)(uint8_t)gv[j] * xq[32 * g + 8 * e + j] * sv[j];
+                }
+                bsum += sumi * ls;
+            }
+        }
+        sumf += d * bsum;
+    }
+    return 0.125f * sumf;
+}
+
+/* ggml/src/ggml-cpu/quants.c (ggml_vec_dot_iq3_xxs_q8_K_generic); examples/kernels/vec_dot/iq3_xxs_q8_k.py:8-75:
+ * per 32 weights an odd integer scale, result times 0.25 */
+float wo_vec_dot_iq3_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k) {
+    float sumf = 0.f;
+    for (int64_t b = 0; b < k / 256; ++b, w += 98, x += 292) {
+        const float d = wo_f16_to_f32(ld_u16(w)) * ld_f32(x);
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int32_t bsum = 0;
+        for (int g = 0; g < 8; ++g) {
+            uint32_t meta;
+            memcpy(&meta, w + 66 + 4 * g, 4);
+            const int32_t ls = (int32_t)(2 * (meta >> 28) + 1);
+            int32_t sumi = 0;
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *sv = signs + 8 * ((meta >> (7 * e)) & 127);
+                const int8_t *g1 = grid + 4 * w[2 + 8 * g + 2 * e], *g2 = grid + 4 * w[2 + 8 * g + 2 * e + 1];
+                for (int j = 0; j < 4; ++j) {
+                    sumi += (int)(uint8_t)g1[j] * xq[32 * g + 8 * e + j] * sv[j];
+                    sumi += (int)(uint8_t)g2[j] * xq[32 * g + 8 * e + 4 + j] * sv[4 + j];
+                }
+            }
+            bsum += sumi * ls;
+        }
+        sumf += d * bsum;
+    }
+    return 0.25f * sumf;
+}
+
 /* ggml/src/ggml-cpu/quants.c:430-480; examples/kernels/vec_dot/tq1_0_q8_k.py:9-55 */
 float wo_vec_dot_tq1_0_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
     float sumf = 0.0f;
@@ -862,6 +961,8 @@ int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, 
     case WO_Q5_K: *out = wo_vec_dot_q5_K_q8_K(w, x, k); return 0;
     case WO_Q6_K: *out = wo_vec_dot_q6_K_q8_K(w, x, k); return 0;
     case WO_IQ2_XXS: *out = wo_vec_dot_iq2_xxs_q8_K(w, x, grid, signs, k); return 0;
+    case WO_IQ2_XS: *out = wo_vec_dot_iq2_xs_q8_K(w, x, grid, signs, k); return 0;
+    case WO_IQ3_XXS: *out = wo_vec_dot_iq3_xxs_q8_K(w, x, grid, signs, k); return 0;
     case WO_TQ1_0: *out = wo_vec_dot_tq1_0_q8_K(w, x, k); return 0;
     default: return -1;
     }

@@ -29,6 +29,24 @@ def random_iq2_xxs(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     return rec.reshape(n, nb * 66)
 
 
+def random_iq2_xs(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
+    """Random but valid IQ2_XS records: any 9-bit grid index, sign index and scale nibble is legal; d is a small f16."""
+    nb = k // 256
+    rec = rng.integers(0, 256, size=(n, nb, 74), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal((n, nb))) * 0.01 + 1e-3).astype(np.float16)
+    rec[:, :, 0:2] = d.view(np.uint8).reshape(n, nb, 2)
+    return rec.reshape(n, nb * 74)
+
+
+def random_iq3_xxs(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
+    """Random but valid IQ3_XXS records: any grid index byte, sign index and 4-bit scale is legal; d is a small f16."""
+    nb = k // 256
+    rec = rng.integers(0, 256, size=(n, nb, 98), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal((n, nb))) * 0.01 + 1e-3).astype(np.float16)
+    rec[:, :, 0:2] = d.view(np.uint8).reshape(n, nb, 2)
+    return rec.reshape(n, nb * 98)
+
+
 def random_q6_k(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     """Random but valid Q6_K records: any ql / qh byte and any int8 scale is legal; d is a small f16."""
     nb = k // 256
@@ -68,6 +86,10 @@ def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
         if o.ref_available() and n * k <= 1 << 22:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
         return random_iq2_xxs(rng, n, k)
+    if fmt in (o.IQ2_XS, o.IQ3_XXS):
+        if o.ref_available() and n * k <= 1 << 21:
+            return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        return random_iq2_xs(rng, n, k) if fmt == o.IQ2_XS else random_iq3_xxs(rng, n, k)
     if fmt in (o.Q2_K, o.Q3_K, o.Q5_K, o.Q6_K):
         if o.ref_available() and n * k <= 1 << 22:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
@@ -83,5 +105,7 @@ def activations(rng: np.random.Generator, m: int, k: int) -> np.ndarray:
     return rng.standard_normal((m, k)).astype(np.float32)
 
 
-def tables(golden: dict):
-    return golden["iq2xxs_grid"], golden["iq2xxs_signs"]
+def tables(golden: dict, name: str = "iq2_xxs"):
+    """The codebook and the sign table a format's kernels take as arguments (the sign table is the same for all three)."""
+    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid"}.get(name.lower(), "iq2xxs_grid")
+    return golden[grid], golden["iq2xxs_signs"]

@@ -15,7 +15,9 @@ from helpers import TQ1_POWERS, activations, random_iq2_xxs, reference_tolerance
 
 pytestmark = pytest.mark.gpu
 
-FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k"]
+DECODE_FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k"]   # have a production_mul_mat_<fmt>_decode
+FORMATS = DECODE_FORMATS + ["iq2_xs", "iq3_xxs"]
+CODEBOOKS = {"iq2_xxs": (256, 8, "I8X8"), "iq2_xs": (512, 8, "I8X8"), "iq3_xxs": (256, 4, "I8X4")}
 REL_L2_BOUND = 1e-5
 
 
@@ -44,8 +46,8 @@ def _fmt(oracle, name):
 
 
 def _table_args(torch, golden, name):
-    grid, signs = tables(golden)
-    if name == "iq2_xxs":
+    grid, signs = tables(golden, name)
+    if name in CODEBOOKS:
         return [dev(torch, grid), dev(torch, signs)]
     if name == "tq1_0":
         return [dev(torch, TQ1_POWERS.view(np.int32)).view(torch.int32)]
@@ -55,10 +57,11 @@ def _table_args(torch, golden, name):
 def _wrap_tables(weft, name, tensors, dequant=False):
     from weft_b200.runtime import Buffer
 
-    if name == "iq2_xxs":
+    if name in CODEBOOKS:
         if dequant:
             return tensors
-        return [Buffer(tensors[0], shape=(256, 8), encoding="I8X8"), Buffer(tensors[1], shape=(128, 8), encoding="I8X8")]
+        entries, width, encoding = CODEBOOKS[name]
+        return [Buffer(tensors[0], shape=(entries, width), encoding=encoding), Buffer(tensors[1], shape=(128, 8), encoding="I8X8")]
     if name == "tq1_0":
         return [Buffer(tensors[0], shape=(5,), encoding="dense.u32")]
     return []
@@ -76,7 +79,7 @@ def test_row_dequantize_bit_exact(torch, weft, oracle, golden, name):
     from weft_b200.runtime import Buffer
 
     fmt = _fmt(oracle, name)
-    grid, signs = tables(golden)
+    grid, signs = tables(golden, name)
     rng = np.random.default_rng(100 + fmt)
     cases = [
         (golden[f"rnd_w_{name}"], 8, 1024),                                              # reference-made golden bytes
@@ -230,7 +233,7 @@ def test_vec_dot_rows_against_oracle(torch, weft, oracle, golden, name, shape):
     rng = np.random.default_rng(1000 * fmt + n + k)
     w = weights(fmt, rng, n, k)
     xq = oracle.quantize(act_fmt, activations(rng, 1, k))
-    grid, signs = tables(golden)
+    grid, signs = tables(golden, name)
     want, _ = oracle.mul_mat(fmt, w, None, n, k, 1, xq=xq, grid=grid, signs=signs)
     kernel = weft.compile(getattr(rows, f"quantized_vec_dot_{name}_{act.lower()}_rows"))
     y = torch.full((n,), float("nan"), device="cuda")
@@ -243,7 +246,35 @@ def test_vec_dot_rows_against_oracle(torch, weft, oracle, golden, name, shape):
 
 # ------------------------------------------------------------------ mul_mat (decode)
 
-@pytest.mark.parametrize("name", FORMATS)
+@pytest.mark.parametrize("symbol", ["production_mul_mat_iq2_xs", "production_mul_mat_iq2_xs_staged", "production_mul_mat_iq3_xxs", "production_mul_mat_iq2_xxs"])
+@pytest.mark.parametrize("mnk", [(1, 512, 2048), (3, 200, 1024), (40, 96, 4096), (1, 4096, 4096)])
+def test_mul_mat_codebook_formats(torch, weft, oracle, golden, symbol, mnk):
+    """The mul_mat symbols of IQ2_XS, IQ3_XXS and the unstaged IQ2_XXS name: K = 1024 leaves rows that are not whole
+    16-byte multiples (per-warp copies), K = 2048 and 4096 take the ring kernel with bank-striped tables."""
+    from weft_b200.kernels import mul_mat
+    from weft_b200.runtime import Buffer
+
+    name = "iq3_xxs" if "iq3" in symbol else "iq2_xs" if "iq2_xs" in symbol else "iq2_xxs"
+    fmt = _fmt(oracle, name)
+    m, n, k = mnk
+    rng = np.random.default_rng(11 * fmt + m + n + k)
+    w = weights(fmt, rng, n, k)
+    x = activations(rng, m, k)
+    grid, signs = tables(golden, name)
+    want, want_xq = oracle.mul_mat(fmt, w, x, n, k, m, rule=1, grid=grid, signs=signs)
+    xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
+    y = torch.full((m, n), float("nan"), device="cuda")
+    table_tensors = _table_args(torch, golden, name)
+    wrapped = table_tensors if symbol.endswith("iq2_xs_staged") else _wrap_tables(weft, name, table_tensors)   # flat int8 arrays there
+    weft.compile(getattr(mul_mat, symbol))(Buffer(dev(torch, w), shape=(n, k), encoding=name.upper()), dev(torch, x),
+                                           Buffer(xq, shape=(m, k), encoding="Q8_K"), *wrapped, y)
+    assert np.array_equal(xq.cpu().numpy(), want_xq)
+    got = y.cpu().numpy()
+    assert rel_l2(got, want) <= REL_L2_BOUND, (symbol, mnk, rel_l2(got, want))
+    assert reference_tolerance_ok(got, want)
+
+
+@pytest.mark.parametrize("name", DECODE_FORMATS)
 @pytest.mark.parametrize("mnk", [(1, 512, 1024), (3, 200, 2048), (1, 4096, 4096)])
 def test_mul_mat_decode(torch, weft, oracle, golden, name, mnk):
     from weft_b200.kernels import mul_mat

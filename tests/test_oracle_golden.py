@@ -9,7 +9,12 @@ from __future__ import annotations
 import numpy as np
 import pytest
 
-FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k"]
+FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k", "iq2_xs", "iq3_xxs"]
+
+
+def _tables(golden, name):
+    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid"}.get(name, "iq2xxs_grid")
+    return golden[grid], golden["iq2xxs_signs"]
 K = 1024
 
 
@@ -41,6 +46,8 @@ def test_sign_table_is_seven_bits_plus_parity(oracle, golden):
     assert np.array_equal(oracle.sign_table(), golden["iq2xxs_signs"])
     grid = golden["iq2xxs_grid"]
     assert grid.shape == (2048,) and set(np.unique(grid)) <= {8, 25, 43}
+    assert golden["iq2xs_grid"].shape == (4096,) and set(np.unique(golden["iq2xs_grid"])) <= {8, 25, 43}
+    assert golden["iq3xxs_grid"].shape == (1024,) and int(golden["iq3xxs_grid"].min()) >= 4 and int(golden["iq3xxs_grid"].max()) <= 62
 
 
 @pytest.mark.parametrize("name", ["q4_0", "q8_0", "q4_k", "tq1_0"])
@@ -78,7 +85,7 @@ def test_weft_activation_rule_differs_only_by_sign_on_ties(oracle):
 @pytest.mark.parametrize("name", FORMATS)
 def test_dequantize_bit_exact(oracle, golden, name):
     fmt = _fmt(oracle, name)
-    grid, signs = golden["iq2xxs_grid"], golden["iq2xxs_signs"]
+    grid, signs = _tables(golden, name)
     got = oracle.dequantize(fmt, golden[f"rnd_w_{name}"], K, grid, signs)
     assert np.array_equal(_bits(got), _bits(golden[f"rnd_deq_{name}"]))
     # the reference's random-byte record (row_dequantize_runtime.cpp:145-164)
@@ -90,8 +97,8 @@ def test_dequantize_bit_exact(oracle, golden, name):
 @pytest.mark.parametrize("name", FORMATS)
 def test_mul_mat_bit_exact(oracle, golden, name):
     fmt = _fmt(oracle, name)
-    y, xq = oracle.mul_mat(fmt, golden[f"rnd_w_{name}"], golden["rnd_x"], 8, K, 3,
-                           grid=golden["iq2xxs_grid"], signs=golden["iq2xxs_signs"])
+    grid, signs = _tables(golden, name)
+    y, xq = oracle.mul_mat(fmt, golden[f"rnd_w_{name}"], golden["rnd_x"], 8, K, 3, grid=grid, signs=signs)
     act = "q8_0" if name in ("q4_0", "q8_0") else "q8_k"
     assert np.array_equal(xq, golden[f"rnd_xq_{act}"])
     assert np.array_equal(_bits(y), _bits(golden[f"rnd_y_{name}"]))
@@ -106,7 +113,7 @@ def test_closed_form_known_answers(oracle, golden, name, tag):
     w_row = np.tile(golden[f"kat_{tag}_w_{name}"], reps)
     x_rec = golden[f"kat_{tag}_x_{name}"]
     x_row = np.tile(x_rec, reps) if tag == "vd" else x_rec
-    got = oracle.vec_dot(fmt, w_row, x_row, 4096, golden["iq2xxs_grid"], golden["iq2xxs_signs"])
+    got = oracle.vec_dot(fmt, w_row, x_row, 4096, *_tables(golden, name))
     assert np.float32(got).view(np.uint32) == golden[f"kat_{tag}_row_{name}"].view(np.uint32)
     assert np.isfinite(got)
 
@@ -122,10 +129,12 @@ def test_live_against_compiled_reference(oracle, golden, name):
     if name == "tq1_0":
         src = (rng.integers(-1, 2, size=(n, k)) * np.float32(0.031)).astype(np.float32)
     w = oracle.ref_quantize_weights(fmt, src)
-    if name not in ("iq2_xxs", "q6_k", "q5_k", "q2_k", "q3_k"):          # the port has no quantizer for these weight formats
+    if name not in ("iq2_xxs", "q6_k", "q5_k", "q2_k", "q3_k", "iq2_xs", "iq3_xxs"):   # the port has no quantizer for these weight formats
         assert np.array_equal(oracle.quantize(fmt, src), w)
     grid, signs = oracle.ref_iq2xxs_tables()
     assert np.array_equal(grid, golden["iq2xxs_grid"])
+    assert np.array_equal(oracle.ref_iq2xs_grid(), golden["iq2xs_grid"]) and np.array_equal(oracle.ref_iq3xxs_grid(), golden["iq3xxs_grid"])
+    grid, signs = _tables(golden, name)
     x = rng.standard_normal((m, k)).astype(np.float32)
     assert np.array_equal(_bits(oracle.dequantize(fmt, w, k, grid, signs)), _bits(oracle.ref_dequantize(fmt, w, k)))
     y, xq = oracle.mul_mat(fmt, w, x, n, k, m, grid=grid, signs=signs)

@@ -205,6 +205,64 @@ __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq2_xxs_kernel(const ui
     }
 }
 
+// ---- IQ2_XS (examples/kernels/dequantize/iq2_xs.py:9-68, ggml-quants.c:2444-2468): (d*(0.5+s)*0.25) * (grid*sign), s the
+//      low scale nibble for the first 16 weights of a 32-group and the high nibble for the rest; lane = (group g, entry e)
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq2_xs_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                                                        const int8_t *__restrict__ signs, float *__restrict__ y, long long units) {
+    __shared__ __align__(8) int8_t s_grid[4096];
+    __shared__ __align__(8) int8_t s_signs[1024];
+    for (int i = threadIdx.x; i < 4096; i += blockDim.x) s_grid[i] = grid[i];
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) s_signs[i] = signs[i];
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, e = lane & 3;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 74;
+        const float d = half_bits_to_float(ld_u16(rec));
+        const uint32_t code = ld_u16(rec + 2 + 2 * (4 * g + e));
+        const uint32_t sc = rec[66 + g];
+        const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(e < 2 ? sc & 15u : sc >> 4))), 0.25f);
+        const int8_t *gv = s_grid + 8 * (code & 511u);
+        const int8_t *sv = s_signs + 8 * (code >> 9);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(__fmul_rn(db, (float)gv[i]), (float)sv[i]);
+        float *out = y + u * 256 + 32 * g + 8 * e;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
+// ---- IQ3_XXS (examples/kernels/dequantize/iq3_xxs.py, ggml-quants.c:2506-2536): (d*(0.5+s)*0.5) * (grid*sign); a grid
+//      entry holds 4 weights, a sign entry 8; lane = (group g, entry e) produces 8 consecutive outputs
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq3_xxs_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                                                         const int8_t *__restrict__ signs, float *__restrict__ y, long long units) {
+    __shared__ __align__(8) int8_t s_grid[1024];
+    __shared__ __align__(8) int8_t s_signs[1024];
+    for (int i = threadIdx.x; i < 1024; i += blockDim.x) { s_grid[i] = grid[i]; s_signs[i] = signs[i]; }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, e = lane & 3;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 98;
+        const float d = half_bits_to_float(ld_u16(rec));
+        const uint32_t meta = ld_u32_a2(rec + 66 + 4 * g);
+        const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(meta >> 28))), 0.5f);
+        const uint8_t *g1 = reinterpret_cast<const uint8_t *>(s_grid) + 4 * rec[2 + 8 * g + 2 * e];
+        const uint8_t *g2 = reinterpret_cast<const uint8_t *>(s_grid) + 4 * rec[2 + 8 * g + 2 * e + 1];
+        const int8_t *sv = s_signs + 8 * ((meta >> (7 * e)) & 127u);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[i] = __fmul_rn(__fmul_rn(db, (float)g1[i]), (float)sv[i]);
+            v[4 + i] = __fmul_rn(__fmul_rn(db, (float)g2[i]), (float)sv[4 + i]);
+        }
+        float *out = y + u * 256 + 32 * g + 8 * e;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
 // ---- TQ1_0: every lane produces 8 consecutive outputs; lanes 0-19 region 0 (5 digits x 32 bytes),
 //      20-29 region 1 (5 digits x 16 bytes), 30-31 region 2 (4 digits x 4 bytes)
 __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_tq1_0_kernel(const uint8_t *__restrict__ w, const uint32_t *__restrict__ powers,
@@ -338,6 +396,20 @@ __global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ 
             const float db = __fmul_rn(__fmul_rn(half_bits_to_float(ld_u16(rec)), __fadd_rn(0.5f, (float)(meta >> 28))), 0.25f);
             const int gv = grid[8 * rec[2 + 8 * g + en] + l], sv = signs[8 * ((meta >> (7 * en)) & 127u) + l];
             v = __fmul_rn(__fmul_rn(db, (float)gv), (float)sv);
+        } else if (fmt == F_IQ2_XS) {
+            const uint8_t *rec = w + (i / 256) * 74;
+            const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8;
+            const uint32_t code = ld_u16(rec + 2 + 2 * (4 * g + en)), sc = rec[66 + g];
+            const float db = __fmul_rn(__fmul_rn(half_bits_to_float(ld_u16(rec)), __fadd_rn(0.5f, (float)(en < 2 ? sc & 15u : sc >> 4))), 0.25f);
+            const int gv = grid[8 * (code & 511u) + l], sv = signs[8 * (code >> 9) + l];
+            v = __fmul_rn(__fmul_rn(db, (float)gv), (float)sv);
+        } else if (fmt == F_IQ3_XXS) {
+            const uint8_t *rec = w + (i / 256) * 98;
+            const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8;
+            const uint32_t meta = ld_u32_a2(rec + 66 + 4 * g);
+            const float db = __fmul_rn(__fmul_rn(half_bits_to_float(ld_u16(rec)), __fadd_rn(0.5f, (float)(meta >> 28))), 0.5f);
+            const int gv = (int)(uint8_t)grid[4 * rec[2 + 8 * g + 2 * en + (l >> 2)] + (l & 3)], sv = signs[8 * ((meta >> (7 * en)) & 127u) + l];
+            v = __fmul_rn(__fmul_rn(db, (float)gv), (float)sv);
         } else if (fmt == F_TQ1_0) {
             const uint8_t *rec = w + (i / 256) * 54;
             const int e = (int)(i % 256);
@@ -403,6 +475,16 @@ cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const 
     case F_IQ2_XXS: {
         const long long units = elements / 256;
         dequant_iq2_xxs_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, signs, y, units);
+        break;
+    }
+    case F_IQ2_XS: {
+        const long long units = elements / 256;
+        dequant_iq2_xs_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, signs, y, units);
+        break;
+    }
+    case F_IQ3_XXS: {
+        const long long units = elements / 256;
+        dequant_iq3_xxs_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, signs, y, units);
         break;
     }
     case F_Q6_K: {

@@ -1,4 +1,4 @@
-// Decode GEMV for Q4_0, Q8_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ2_XXS and TQ1_0 weights whose rows are whole 16-byte multiples:
+// Decode GEMV for Q4_0, Q8_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ2_XXS, IQ2_XS, IQ3_XXS and TQ1_0 weights whose rows are whole 16-byte multiples:
 // Y[m, n] = quantized_vec_dot(W[n], Xq[m])  (examples/kernels/mul_mat/{q4_0,q8_0,q2_k,q3_k,q5_k,q6_k,iq2_xxs,tq1_0}_decode.py).
 //
 // Same streaming scheme as the Q4_K kernel: one persistent CTA per SM, a producer warp that fills a
@@ -24,8 +24,12 @@ constexpr int RG_MAX_STAGES = 24;
 constexpr int RG_MAX_THREADS = 512;
 // IQ2_XXS waits on table lookups, needs 64 registers, and gains from twice the warps
 // (Q5_K and Q3_K were tried with the same bound: capped at 64 registers they spill, 10.7 -> 11.0 us and 8.8 -> 11.4 us)
-constexpr int ring_max_threads(int fmt, int rl = 2) { return (fmt == F_IQ2_XXS || rl == 1) ? 1024 : RG_MAX_THREADS; }
-constexpr int IQ2_TABLE_BYTES = 49152;   // sixteen bank-striped copies of the grid (32 KB) and of the sign masks (16 KB)
+__host__ __device__ constexpr bool is_codebook(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS; }
+constexpr int ring_max_threads(int fmt, int rl = 2) { return (is_codebook(fmt) || rl == 1) ? 1024 : RG_MAX_THREADS; }
+// bank-striped copies of the grid (IQ2_XXS: 256 entries x 128 bytes; IQ2_XS: 512 x 128; IQ3_XXS: 256 x 128), then of the
+// sign masks (128 x 128 bytes)
+__host__ __device__ constexpr int codebook_grid_bytes(int fmt) { return fmt == F_IQ2_XS ? 65536 : is_codebook(fmt) ? 32768 : 0; }
+__host__ __device__ constexpr int codebook_table_bytes(int fmt) { return is_codebook(fmt) ? codebook_grid_bytes(fmt) + 16384 : 0; }
 
 struct RingParams {
     const uint8_t *w;
@@ -54,7 +58,7 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int UB = Unit<FMT>::BYTES;
     constexpr bool ACT_Q8_0 = (FMT == F_Q4_0 || FMT == F_Q8_0);
-    constexpr int TABLE_BYTES = FMT == F_IQ2_XXS ? IQ2_TABLE_BYTES : 0;
+    constexpr int TABLE_BYTES = codebook_table_bytes(FMT);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = p.nb, LSR = p.log_stage_rows, SR = 1 << LSR, LS = p.log_stages, S = 1 << LS;
     const int LL = p.log_lanes, L = 1 << LL, RPI = RL * (32 >> LL);   // rows per consumer iteration
@@ -64,7 +68,7 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
     volatile int *s_issued = reinterpret_cast<volatile int *>(smem);
     uint64_t *s_full = reinterpret_cast<uint64_t *>(smem + 16);
     uint64_t *s_empty = s_full + RG_MAX_STAGES;
-    uint8_t *s_grid = smem + 512, *s_neg = s_grid + 32768;
+    uint8_t *s_grid = smem + 512, *s_neg = s_grid + codebook_grid_bytes(FMT);
     uint8_t *s_xq = smem + 512 + TABLE_BYTES;
     uint8_t *s_aux = s_xq + (size_t)nb * XQ_PITCH;
     uint8_t *s_ring = smem + ((512 + TABLE_BYTES + (size_t)nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~size_t(127));
@@ -106,6 +110,8 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
 
     const int epoch = GATHER ? gather_epoch(p.gather) : 0;
     if (FMT == F_IQ2_XXS) stage_iq2_tables_striped(p.grid, p.signs, s_grid, s_neg);
+    if (FMT == F_IQ2_XS) { stage_striped8(p.grid, 512, s_grid, false); stage_striped8(p.signs, 128, s_neg, true); }
+    if (FMT == F_IQ3_XXS) { stage_striped4(p.grid, 256, s_grid); stage_striped8(p.signs, 128, s_neg, true); }
     uint32_t pw[5] = {1, 3, 9, 27, 81};
     if (FMT == F_TQ1_0) {
 #pragma unroll
@@ -172,12 +178,15 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
             else if (FMT == F_Q5_K) dot_q5_k<RL>(wp, xu, xa, acc);
             else if (FMT == F_Q6_K) dot_q6_k<RL>(wp, xu, xa, acc);
             else if (FMT == F_IQ2_XXS) dot_iq2_xxs<RL, 128>(wp, xu, xa, s_grid + 8 * (lane & 15), s_neg + 8 * (lane & 15), acc);
+            else if (FMT == F_IQ2_XS) dot_iq2_xs<RL, 128>(wp, xu, xa, s_grid + 8 * (lane & 15), s_neg + 8 * (lane & 15), acc);
+            else if (FMT == F_IQ3_XXS) dot_iq3_xxs<RL, 128, 128>(wp, xu, xa, s_grid + 4 * lane, s_neg + 8 * (lane & 15), acc);
             else dot_tq1_0<RL>(wp, xu, xa, pw, acc);
         }
 #pragma unroll
         for (int r = 0; r < RL; ++r) {
             for (int o = L >> 1; o > 0; o >>= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
-            if (FMT == F_IQ2_XXS) acc[r] *= 0.125f;
+            if (FMT == F_IQ2_XXS || FMT == F_IQ2_XS) acc[r] *= 0.125f;
+            if (FMT == F_IQ3_XXS) acc[r] *= 0.25f;
         }
         __syncwarp();   // every lane's shared loads of this stage have completed
         if (ul == 0) {
@@ -215,7 +224,7 @@ RingPlan plan_ring(int fmt, long long nb) {
     RingPlan plan{0, 0, 0, 0, false};
     const long long row_bytes = nb * unit_bytes(fmt);
     if (row_bytes % 16 != 0 || nb <= 0) return plan;
-    const long long fixed = (512 + (fmt == F_IQ2_XXS ? IQ2_TABLE_BYTES : 0) + nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~127LL;
+    const long long fixed = (512 + codebook_table_bytes(fmt) + nb * (XQ_PITCH + XAUX_BYTES) + 127) & ~127LL;
     int ll = 0;
     while ((1 << ll) < 32 && (1 << ll) < nb) ++ll;
     const int log_rpi = 1 + (5 - ll);
@@ -263,7 +272,7 @@ cudaError_t launch_fmt(const RingParams &p, bool qx, dim3 grid, int threads, siz
 }  // namespace
 
 bool gemv_ring_supported(const GemvArgs &a) {
-    if (a.fmt != F_Q4_0 && a.fmt != F_Q8_0 && a.fmt != F_Q2_K && a.fmt != F_Q3_K && a.fmt != F_Q5_K && a.fmt != F_Q6_K && a.fmt != F_IQ2_XXS && a.fmt != F_TQ1_0) return false;
+    if (a.fmt != F_Q4_0 && a.fmt != F_Q8_0 && a.fmt != F_Q2_K && a.fmt != F_Q3_K && a.fmt != F_Q5_K && a.fmt != F_Q6_K && a.fmt != F_IQ2_XXS && a.fmt != F_IQ2_XS && a.fmt != F_IQ3_XXS && a.fmt != F_TQ1_0) return false;
     return a.k % 256 == 0 && a.k > 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0 && a.n < (1LL << 30) &&
            plan_ring(a.fmt, a.k / 256).ok;
 }
@@ -284,7 +293,7 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     const long long rest = a.n - (long long)p.full_rounds * ctas * stage_rows;
     p.tail_rows = (int)((rest + ctas - 1) / ctas);
     const int most = ring_max_threads(a.fmt) / 32 - 1;
-    int consumers = kRingConsumers < 1 ? (a.fmt == F_IQ2_XXS ? kRingIq2Consumers : 15) : kRingConsumers;
+    int consumers = kRingConsumers < 1 ? (is_codebook(a.fmt) ? kRingIq2Consumers : 15) : kRingConsumers;
     if (consumers > most) consumers = most;
     if (consumers < 1) consumers = 1;
     const int threads = (consumers + 1) * 32;
@@ -298,6 +307,8 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     case F_Q5_K: return launch_fmt<F_Q5_K>(p, qx, grid, threads, plan.smem, stream);
     case F_Q6_K: return launch_fmt<F_Q6_K>(p, qx, grid, threads, plan.smem, stream);
     case F_IQ2_XXS: return launch_fmt<F_IQ2_XXS>(p, qx, grid, threads, plan.smem, stream);
+    case F_IQ2_XS: return launch_fmt<F_IQ2_XS>(p, qx, grid, threads, plan.smem, stream);
+    case F_IQ3_XXS: return launch_fmt<F_IQ3_XXS>(p, qx, grid, threads, plan.smem, stream);
     default: return launch_fmt<F_TQ1_0>(p, qx, grid, threads, plan.smem, stream);
     }
 }

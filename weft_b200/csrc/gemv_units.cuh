@@ -373,19 +373,107 @@ __device__ __forceinline__ void dot_iq2_xxs(const uint8_t *const (&wp)[RL], cons
     for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
 }
 
-// Stage the IQ2_XXS codebooks as sixteen bank-striped copies: copy c of entry e at e * 128 + c * 8, so copy c lives
-// in banks 2c and 2c + 1 only and a half-warp whose lane l reads copy l % 16 never conflicts, whatever the entries
-// (an 8-byte shared load is served one half-warp at a time).  s_grid: 256 x 128 bytes, s_neg: 128 x 128 bytes.
+// One IQ2_XS record (74 bytes, 2-byte aligned): f16 d, 32 u16 codes (grid index in bits 0-8, sign index in bits 9-15,
+// one code per 8 weights), 8 scale bytes (low nibble: first 16 weights of a 32-group, high nibble: the other 16)
+// (examples/kernels/vec_dot/iq2_xs_q8_k.py:9-39, examples/functions/quantization.py:71-83; GGML
+// ggml_vec_dot_iq2_xs_q8_K_generic).  s_grid: int8[512][8]; s_neg and PITCH as for IQ2_XXS.
+template <int RL, int PITCH = 8>
+__device__ __forceinline__ void dot_iq2_xs(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                            const uint8_t *s_grid, const uint8_t *s_neg, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    uint32_t qw[RL][18];
+    int bsum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<18>(wp[r] + 2, qw[r]); bsum[r] = 0; }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t sc = byte_of(qw[r][16 + (g >> 2)], g & 3);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const uint32_t codes = qw[r][2 * g + half];
+                int pos = 0, neg = 0;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t code = e ? codes >> 16 : codes & 0xffffu;
+                    const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + PITCH * (code & 511u));
+                    const uint2 nm = *reinterpret_cast<const uint2 *>(s_neg + PITCH * (code >> 9));
+                    pos = dp4a_ss(gv.x, xw[4 * half + 2 * e], pos);
+                    pos = dp4a_ss(gv.y, xw[4 * half + 2 * e + 1], pos);
+                    neg = dp4a_ss(gv.x & nm.x, xw[4 * half + 2 * e], neg);
+                    neg = dp4a_ss(gv.y & nm.y, xw[4 * half + 2 * e + 1], neg);
+                }
+                bsum[r] += (pos - 2 * neg) * (int)(2u * (half ? sc >> 4 : sc & 15u) + 1u);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
+}
+
+// One IQ3_XXS record (98 bytes, 2-byte aligned): f16 d, 64 grid-index bytes (one per 4 weights), 8 u32 (four 7-bit sign
+// indices, one per 8 weights, and a 4-bit scale in bits 28-31; one word per 32 weights)
+// (examples/kernels/vec_dot/iq3_xxs_q8_k.py:8-75; GGML ggml_vec_dot_iq3_xxs_q8_K_generic).  s_grid: int8[256][4] with
+// GP bytes between entries (4: plain; 128: thirty-two bank-striped copies); s_neg / SP as for IQ2_XXS.
+template <int RL, int GP = 4, int SP = 8>
+__device__ __forceinline__ void dot_iq3_xxs(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                             const uint8_t *s_grid, const uint8_t *s_neg, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    uint32_t qw[RL][24];
+    int bsum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<24>(wp[r] + 2, qw[r]); bsum[r] = 0; }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t meta = qw[r][16 + g];
+            int pos = 0, neg = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t pair = qw[r][2 * g + (e >> 1)] >> (16 * (e & 1));   // index bytes 2e and 2e + 1 of the group
+                const uint32_t g1 = *reinterpret_cast<const uint32_t *>(s_grid + GP * (pair & 0xffu));
+                const uint32_t g2 = *reinterpret_cast<const uint32_t *>(s_grid + GP * ((pair >> 8) & 0xffu));
+                const uint2 nm = *reinterpret_cast<const uint2 *>(s_neg + SP * ((meta >> (7 * e)) & 127u));
+                pos = dp4a_ss(g1, xw[2 * e], pos);
+                pos = dp4a_ss(g2, xw[2 * e + 1], pos);
+                neg = dp4a_ss(g1 & nm.x, xw[2 * e], neg);
+                neg = dp4a_ss(g2 & nm.y, xw[2 * e + 1], neg);
+            }
+            bsum[r] += (pos - 2 * neg) * (int)(2u * (meta >> 28) + 1u);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
+}
+
+// Bank-striped copies of a codebook: with 8-byte entries, copy c (of sixteen) of entry e sits at e * 128 + c * 8, so copy
+// c lives in banks 2c and 2c + 1 only and a half-warp whose lane l reads copy l % 16 never conflicts, whatever the
+// entries (an 8-byte shared load is served one half-warp at a time); with 4-byte entries, copy c (of thirty-two) at
+// e * 128 + c * 4, one per lane.  `masks`: store 0xff where the entry is negative, 0 elsewhere (the sign tables).
+__device__ inline void stage_striped8(const int8_t *table, int entries, uint8_t *dst, bool masks) {
+    for (int i = threadIdx.x; i < entries * 2 * 16; i += blockDim.x) {       // (entry word, copy)
+        const int word = i >> 4, c = i & 15;
+        uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(table) + word);
+        if (masks) v = ((v >> 7) & 0x01010101u) * 0xffu;
+        reinterpret_cast<uint32_t *>(dst)[(word >> 1) * 32 + c * 2 + (word & 1)] = v;
+    }
+}
+__device__ inline void stage_striped4(const int8_t *table, int entries, uint8_t *dst) {
+    for (int i = threadIdx.x; i < entries * 32; i += blockDim.x)
+        reinterpret_cast<uint32_t *>(dst)[i] = __ldg(reinterpret_cast<const uint32_t *>(table) + (i >> 5));
+}
+// IQ2_XXS: s_grid 256 x 128 bytes, s_neg 128 x 128 bytes
 __device__ inline void stage_iq2_tables_striped(const int8_t *grid, const int8_t *signs, uint8_t *s_grid, uint8_t *s_neg) {
-    for (int i = threadIdx.x; i < 512 * 16; i += blockDim.x) {       // (entry word, copy)
-        const int word = i >> 4, c = i & 15;
-        reinterpret_cast<uint32_t *>(s_grid)[(word >> 1) * 32 + c * 2 + (word & 1)] = __ldg(reinterpret_cast<const uint32_t *>(grid) + word);
-    }
-    for (int i = threadIdx.x; i < 256 * 16; i += blockDim.x) {
-        const int word = i >> 4, c = i & 15;
-        const uint32_t s = __ldg(reinterpret_cast<const uint32_t *>(signs) + word);   // four entries of +1 / -1
-        reinterpret_cast<uint32_t *>(s_neg)[(word >> 1) * 32 + c * 2 + (word & 1)] = ((s >> 7) & 0x01010101u) * 0xffu;
-    }
+    stage_striped8(grid, 256, s_grid, false);
+    stage_striped8(signs, 128, s_neg, true);
 }
 
 // One TQ1_0 record (54 bytes, 2-byte aligned): 32 + 16 bytes of 5 trits, 4 bytes of 4 trits, f16 d.

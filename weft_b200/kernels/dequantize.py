@@ -51,6 +51,18 @@ def row_dequantize_iq2_xxs(W: wl.View[ggml.IQ2_XXS, (K,)], grid: wl.View[wl.i8, 
     """Y = (d * (0.5 + s) * 0.25) * (grid[idx] * signs[sidx])."""
 
 
+@kernel
+def row_dequantize_iq2_xs(W: wl.View[ggml.IQ2_XS, (K,)], grid: wl.View[wl.i8, (4096,)],
+                          signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (0.5 + s) * 0.25) * (grid[idx] * signs[sidx]), s per 16 elements (examples/kernels/dequantize/iq2_xs.py:9-68)."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq3_xxs(W: wl.View[ggml.IQ3_XXS, (K,)], grid: wl.View[wl.i8, (1024,)],
+                           signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (0.5 + s) * 0.5) * (grid[idx] * signs[sidx]) (examples/kernels/dequantize/iq3_xxs.py:9-14)."""
+
+
 @kernel(alias_groups={"Y": "output"})
 def row_dequantize_tq1_0(W: wl.View[ggml.TQ1_0, (K,)], powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (K,)]):
     """Y = f32(trit - 1) * d, digit-major within each of the record's three regions."""

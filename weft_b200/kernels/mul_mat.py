@@ -147,6 +147,34 @@ def production_mul_mat_iq2_xxs_staged(W: wl.View[ggml.IQ2_XXS, (N, K)], X: wl.Vi
 
 
 @kernel
+def production_mul_mat_iq2_xxs(W: wl.View[ggml.IQ2_XXS, (N, K)], X: wl.View[wl.f32, (M, K)],
+                               Xq: wl.View[ggml.Q8_K, (M, K)], grid: wl.View[ggml.I8X8, (256, 8)],
+                               signs: wl.View[ggml.I8X8, (128, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """IQ2_XXS x Q8_K mul_mat (examples/kernels/mul_mat/iq2_xxs.py:10-17): the function of the staged form."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq2_xs(W: wl.View[ggml.IQ2_XS, (N, K)], X: wl.View[wl.f32, (M, K)],
+                              Xq: wl.View[ggml.Q8_K, (M, K)], grid: wl.View[ggml.I8X8, (512, 8)],
+                              signs: wl.View[ggml.I8X8, (128, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """IQ2_XS x Q8_K mul_mat (examples/kernels/mul_mat/iq2_xs.py:26-33)."""
+
+
+@kernel
+def production_mul_mat_iq2_xs_staged(W: wl.View[ggml.IQ2_XS, (N, K)], X: wl.View[wl.f32, (M, K)],
+                                     Xq: wl.View[ggml.Q8_K, (M, K)], grid: wl.View[wl.i8, (4096,)],
+                                     signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (M, N)]):
+    """The same with the tables as flat byte arrays (examples/kernels/mul_mat/iq2_xs_staged.py:29-36)."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq3_xxs(W: wl.View[ggml.IQ3_XXS, (N, K)], X: wl.View[wl.f32, (M, K)],
+                               Xq: wl.View[ggml.Q8_K, (M, K)], grid: wl.View[ggml.I8X4, (256, 4)],
+                               signs: wl.View[ggml.I8X8, (128, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """IQ3_XXS x Q8_K mul_mat (examples/kernels/mul_mat/iq3_xxs.py:10-17)."""
+
+
+@kernel
 def production_mul_mat_q4_k_persistent(W: wl.View[ggml.Q4K_I[16], (N, K)], X: wl.View[wl.f32, (M, K)],
                                        Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
     """Q4_K x Q8_K over the persistent interleaved layout (examples/kernels/mul_mat/q4_k_persistent.py:9-30).

@@ -45,6 +45,16 @@ def row_dequantize_iq2_xxs_rows(W: wl.View[ggml.IQ2_XXS, (N, K)], grid: wl.View[
                                 signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (N, K)]): ...
 
 
+@kernel
+def row_dequantize_iq2_xs_rows(W: wl.View[ggml.IQ2_XS, (N, K)], grid: wl.View[wl.i8, (4096,)],
+                               signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq3_xxs_rows(W: wl.View[ggml.IQ3_XXS, (N, K)], grid: wl.View[wl.i8, (1024,)],
+                                signs: wl.View[wl.i8, (1024,)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
 @kernel(alias_groups={"Y": "output"})
 def row_dequantize_tq1_0_rows(W: wl.View[ggml.TQ1_0, (N, K)], powers: wl.View[wl.u32, (5,)],
                               Y: wl.View[wl.f32, (N, K)]): ...
@@ -81,6 +91,18 @@ def quantized_vec_dot_q6_k_q8_k_rows(W: wl.View[ggml.Q6_K, (N, K)], X: wl.View[g
 @kernel
 def quantized_vec_dot_iq2_xxs_q8_k_rows(W: wl.View[ggml.IQ2_XXS, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
                                         grid: wl.View[ggml.I8X8, (256, 8)], signs: wl.View[ggml.I8X8, (128, 8)],
+                                        Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_iq2_xs_q8_k_rows(W: wl.View[ggml.IQ2_XS, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
+                                       grid: wl.View[ggml.I8X8, (512, 8)], signs: wl.View[ggml.I8X8, (128, 8)],
+                                       Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_iq3_xxs_q8_k_rows(W: wl.View[ggml.IQ3_XXS, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
+                                        grid: wl.View[ggml.I8X4, (256, 4)], signs: wl.View[ggml.I8X8, (128, 8)],
                                         Y: wl.View[wl.f32, (N,)]): ...
 
 

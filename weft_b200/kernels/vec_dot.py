@@ -53,6 +53,22 @@ def quantized_vec_dot_iq2_xxs_q8_k(W: wl.View[ggml.IQ2_XXS, (K,)], X: wl.View[gg
 
 
 @kernel
+def quantized_vec_dot_iq2_xs_q8_k(W: wl.View[ggml.IQ2_XS, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                  grid: wl.View[ggml.I8X8, (512, 8)], signs: wl.View[ggml.I8X8, (128, 8)],
+                                  Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = 0.125 * sum over 256-blocks of d * x.ds * sum over 16-element halves (2 s + 1) * dot(grid[idx] * signs[sidx], x)
+    (examples/kernels/vec_dot/iq2_xs_q8_k.py:9-39)."""
+
+
+@kernel
+def quantized_vec_dot_iq3_xxs_q8_k(W: wl.View[ggml.IQ3_XXS, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                   grid: wl.View[ggml.I8X4, (256, 4)], signs: wl.View[ggml.I8X8, (128, 8)],
+                                   Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = 0.25 * sum over 256-blocks of d * x.ds * sum_g (2 s_g + 1) * dot(grid[idx] * signs[sidx], x)
+    (examples/kernels/vec_dot/iq3_xxs_q8_k.py:70-76)."""
+
+
+@kernel
 def quantized_vec_dot_tq1_0_q8_k(W: wl.View[ggml.TQ1_0, (K,)], X: wl.View[ggml.Q8_K, (K,)],
                                  powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (1,)]):
     """Y[0] = sum over 256-blocks of f32(sum((trit - 1) * x)) * (d * x.ds); trits decoded with powers[]."""
