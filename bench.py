@@ -42,6 +42,8 @@ WORKLOADS = {
     "q4_k_decode_4096x14336": ("Q4_K", "decode", 4096, 14336, 1),
     "q4_0_decode_4096x4096": ("Q4_0", "decode", 4096, 4096, 1),
     "iq2_xxs_decode_28672x8192": ("IQ2_XXS", "decode", 28672, 8192, 1),
+    "iq2_xs_decode_28672x8192": ("IQ2_XS", "decode", 28672, 8192, 1),
+    "iq3_xxs_decode_28672x8192": ("IQ3_XXS", "decode", 28672, 8192, 1),
     "q2_k_decode_14336x4096": ("Q2_K", "decode", 14336, 4096, 1),
     "q3_k_decode_14336x4096": ("Q3_K", "decode", 14336, 4096, 1),
     "q5_k_decode_14336x4096": ("Q5_K", "decode", 14336, 4096, 1),
@@ -105,17 +107,17 @@ def make_inputs(fmt: str, n: int, k: int, m: int, seed: int):
     rng = np.random.default_rng(seed)
     fid = oracle.FORMAT_IDS[fmt]
     golden = np.load(ROOT / "tests" / "golden" / "golden.npz")
-    grid, signs = golden["iq2xxs_grid"], golden["iq2xxs_signs"]
+    grid, signs = golden[{"IQ2_XS": "iq2xs_grid", "IQ3_XXS": "iq3xxs_grid"}.get(fmt, "iq2xxs_grid")], golden["iq2xxs_signs"]
     base_rows = min(n, 1024)            # quantize 1024 distinct rows, rotate them to fill the matrix (timing is data-independent)
     if fmt == "TQ1_0":
         src = (rng.integers(-1, 2, size=(base_rows, k)) * np.float32(0.02)).astype(np.float32)
         base = oracle.quantize(fid, src)
-    elif fmt == "IQ2_XXS":
+    elif fmt in ("IQ2_XXS", "IQ2_XS", "IQ3_XXS"):
         if oracle.ref_available():
             base_rows = min(n, 128)
             base = oracle.ref_quantize_weights(fid, (rng.standard_normal((base_rows, k)) * 0.02).astype(np.float32))
-        else:
-            base = rng.integers(0, 256, size=(base_rows, k // 256, 66), dtype=np.uint8)
+        else:           # any index, sign index and scale is a valid record once the f16 scale is a small finite number
+            base = rng.integers(0, 256, size=(base_rows, k // 256, oracle.RECORD_BYTES[fid]), dtype=np.uint8)
             base[:, :, 0:2] = (np.abs(rng.standard_normal((base_rows, k // 256))) * 0.01 + 1e-3).astype(np.float16).view(np.uint8).reshape(base_rows, -1, 2)
             base = base.reshape(base_rows, -1)
     elif fmt in ("Q2_K", "Q3_K", "Q5_K", "Q6_K"):
