@@ -44,6 +44,8 @@ WORKLOADS = {
     "iq2_xxs_decode_28672x8192": ("IQ2_XXS", "decode", 28672, 8192, 1),
     "iq2_xs_decode_28672x8192": ("IQ2_XS", "decode", 28672, 8192, 1),
     "iq3_xxs_decode_28672x8192": ("IQ3_XXS", "decode", 28672, 8192, 1),
+    "iq2_s_decode_28672x8192": ("IQ2_S", "decode", 28672, 8192, 1),
+    "iq3_s_decode_28672x8192": ("IQ3_S", "decode", 28672, 8192, 1),
     "q2_k_decode_14336x4096": ("Q2_K", "decode", 14336, 4096, 1),
     "q3_k_decode_14336x4096": ("Q3_K", "decode", 14336, 4096, 1),
     "q5_k_decode_14336x4096": ("Q5_K", "decode", 14336, 4096, 1),
@@ -107,12 +109,12 @@ def make_inputs(fmt: str, n: int, k: int, m: int, seed: int):
     rng = np.random.default_rng(seed)
     fid = oracle.FORMAT_IDS[fmt]
     golden = np.load(ROOT / "tests" / "golden" / "golden.npz")
-    grid, signs = golden[{"IQ2_XS": "iq2xs_grid", "IQ3_XXS": "iq3xxs_grid"}.get(fmt, "iq2xxs_grid")], golden["iq2xxs_signs"]
+    grid, signs = golden[{"IQ2_XS": "iq2xs_grid", "IQ3_XXS": "iq3xxs_grid", "IQ2_S": "iq2s_grid", "IQ3_S": "iq3s_grid"}.get(fmt, "iq2xxs_grid")], golden["iq2xxs_signs"]
     base_rows = min(n, 1024)            # quantize 1024 distinct rows, rotate them to fill the matrix (timing is data-independent)
     if fmt == "TQ1_0":
         src = (rng.integers(-1, 2, size=(base_rows, k)) * np.float32(0.02)).astype(np.float32)
         base = oracle.quantize(fid, src)
-    elif fmt in ("IQ2_XXS", "IQ2_XS", "IQ3_XXS"):
+    elif fmt in ("IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ2_S", "IQ3_S"):
         if oracle.ref_available():
             base_rows = min(n, 128)
             base = oracle.ref_quantize_weights(fid, (rng.standard_normal((base_rows, k)) * 0.02).astype(np.float32))

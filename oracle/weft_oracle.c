@@ -72,6 +72,8 @@ size_t wo_record_bytes(int fmt) {
     case WO_Q6_K: return 210;
     case WO_IQ2_XXS: return 66;
     case WO_IQ2_XS: return 74;
+    case WO_IQ2_S: return 82;
+    case WO_IQ3_S: return 110;
     case WO_IQ3_XXS: return 98;
     case WO_TQ1_0: return 54;
     case WO_Q8_K: return 292;
@@ -82,7 +84,7 @@ size_t wo_record_bytes(int fmt) {
 size_t wo_record_elements(int fmt) {
     switch (fmt) {
     case WO_Q4_0: case WO_Q8_0: case WO_Q8_1: return 32;
-    case WO_Q2_K: case WO_Q3_K: case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_IQ2_XS: case WO_IQ3_XXS: case WO_TQ1_0: case WO_Q8_K: return 256;
+    case WO_Q2_K: case WO_Q3_K: case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_IQ2_XS: case WO_IQ3_XXS: case WO_IQ2_S: case WO_IQ3_S: case WO_TQ1_0: case WO_Q8_K: return 256;
     default: return 0;
     }
 }
@@ -470,7 +472,7 @@ static void wo_quantize_range(int64_t begin, int64_t end, void *p) {
 
 int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrows, int64_t k) {
     wo_quant_ctx c = {fmt, rule, x, y, k, wo_row_bytes(fmt, k)};
-    if (!c.rb || fmt == WO_IQ2_XXS || fmt == WO_IQ2_XS || fmt == WO_IQ3_XXS) return -1;
+    if (!c.rb || fmt == WO_IQ2_XXS || fmt == WO_IQ2_XS || fmt == WO_IQ3_XXS || fmt == WO_IQ2_S || fmt == WO_IQ3_S) return -1;
     wo_parallel_for(nrows, wo_quantize_range, &c);
     return 0;
 }
@@ -573,6 +575,50 @@ void wo_dequantize_row_iq3_xxs(const uint8_t *w, const int8_t *grid, const int8_
     }
 }
 
+/* ggml/src/ggml-quants.c (dequantize_row_iq2_s); examples/kernels/dequantize/iq2_s.py.
+ * Record (82 bytes): f16 d @0; 32 bytes @2: the low 8 bits of the grid index of every 8 weights; 32 bytes @34: their
+ * sign bits (bit j set: weight j negative); 8 bytes @66: per 32 weights four 2-bit pairs, index bits 8-9; 8 scale
+ * bytes @74 (low nibble: first 16 weights of the 32, high nibble: the other 16). */
+static inline int iq2s_index(const uint8_t *w, int g, int e) { return w[2 + 4 * g + e] | ((w[66 + g] << (8 - 2 * e)) & 0x300); }
+
+void wo_dequantize_row_iq2_s(const uint8_t *w, const int8_t *grid, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 82) {
+        const float d = wo_f16_to_f32(ld_u16(w));
+        for (int g = 0; g < 8; ++g) {
+            const uint8_t sc = w[74 + g];
+            const float db[2] = {d * (0.5f + (float)(sc & 15)) * 0.25f, d * (0.5f + (float)(sc >> 4)) * 0.25f};
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *gv = grid + 8 * iq2s_index(w, g, e);
+                const uint8_t sb = w[34 + 4 * g + e];
+                for (int j = 0; j < 8; ++j) *y++ = db[e >> 1] * (float)(uint8_t)gv[j] * ((sb >> j) & 1 ? -1.f : 1.f);
+            }
+        }
+    }
+}
+
+/* ggml/src/ggml-quants.c (dequantize_row_iq3_s); examples/kernels/dequantize/iq3_s.py.
+ * Record (110 bytes): f16 d @0; 64 bytes @2: the low 8 bits of the grid index of every 4 weights; 8 bytes @66: bit e of
+ * byte g is bit 8 of index e of 32-group g; 32 sign bytes @74 (one per 8 weights); 4 scale bytes @106 (nibble per 32
+ * weights, low nibble first).  Scale d * (1 + 2 s). */
+static inline int iq3s_index(const uint8_t *w, int g, int e) { return w[2 + 8 * g + e] | (((w[66 + g] >> e) & 1) << 8); }
+
+void wo_dequantize_row_iq3_s(const uint8_t *w, const int8_t *grid, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 110) {
+        const float d = wo_f16_to_f32(ld_u16(w));
+        for (int g = 0; g < 8; ++g) {
+            const uint8_t sc = w[106 + (g >> 1)];
+            const float db = d * (float)(1 + 2 * (g & 1 ? sc >> 4 : sc & 15));
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *g1 = grid + 4 * iq3s_index(w, g, 2 * e), *g2 = grid + 4 * iq3s_index(w, g, 2 * e + 1);
+                const uint8_t sb = w[74 + 4 * g + e];
+                for (int j = 0; j < 4; ++j) y[j] = db * (float)(uint8_t)g1[j] * ((sb >> j) & 1 ? -1.f : 1.f);
+                for (int j = 0; j < 4; ++j) y[4 + j] = db * (float)(uint8_t)g2[j] * ((sb >> (4 + j)) & 1 ? -1.f : 1.f);
+                y += 8;
+            }
+        }
+    }
+}
+
 /* one base-3 digit of a packed byte, digit 0 = most significant:
  * ggml/src/ggml-quants.c:2369-2371; examples/functions/quantization.py:49-64 */
 static inline int tq1_digit(uint8_t packed, int n) {
@@ -612,6 +658,8 @@ static void wo_dequantize_range(int64_t begin, int64_t end, void *p) {
         case WO_IQ2_XXS: wo_dequantize_row_iq2_xxs(wr, c->grid, c->signs, yr, c->k); break;
         case WO_IQ2_XS: wo_dequantize_row_iq2_xs(wr, c->grid, c->signs, yr, c->k); break;
         case WO_IQ3_XXS: wo_dequantize_row_iq3_xxs(wr, c->grid, c->signs, yr, c->k); break;
+        case WO_IQ2_S: wo_dequantize_row_iq2_s(wr, c->grid, yr, c->k); break;
+        case WO_IQ3_S: wo_dequantize_row_iq3_s(wr, c->grid, yr, c->k); break;
         case WO_TQ1_0: wo_dequantize_row_tq1_0(wr, yr, c->k); break;
         default: break;
         }
@@ -933,6 +981,57 @@ float wo_vec_dot_iq3_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *
     return 0.25f * sumf;
 }
 
+/* ggml/src/ggml-cpu/quants.c (ggml_vec_dot_iq2_s_q8_K_generic); examples/kernels/vec_dot/iq2_s_q8_k.py:68-73 */
+float wo_vec_dot_iq2_s_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k) {
+    float sumf = 0.f;
+    for (int64_t b = 0; b < k / 256; ++b, w += 82, x += 292) {
+        const float d = wo_f16_to_f32(ld_u16(w)) * ld_f32(x);
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int32_t bsum = 0;
+        for (int g = 0; g < 8; ++g) {
+            const uint8_t sc = w[74 + g];
+            for (int half = 0; half < 2; ++half) {
+                const int32_t ls = 1 + 2 * (half ? sc >> 4 : sc & 15);
+                int32_t sumi = 0;
+                for (int e = 2 * half; e < 2 * half + 2; ++e) {
+                    const int8_t *gv = grid + 8 * iq2s_index(w, g, e);
+                    const uint8_t sb = w[34 + 4 * g + e];
+                    for (int j = 0; j < 8; ++j) sumi += xq[32 * g + 8 * e + j] * (int)(uint8_t)gv[j] * ((sb >> j) & 1 ? -1 : 1);
+                }
+                bsum += ls * sumi;
+            }
+        }
+        sumf += d * bsum;
+    }
+    return 0.125f * sumf;
+}
+
+/* ggml/src/ggml-cpu/quants.c (ggml_vec_dot_iq3_s_q8_K_generic); examples/kernels/vec_dot/iq3_s_q8_k.py:67-72 */
+float wo_vec_dot_iq3_s_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k) {
+    float sumf = 0.f;
+    for (int64_t b = 0; b < k / 256; ++b, w += 110, x += 292) {
+        const float d = wo_f16_to_f32(ld_u16(w)) * ld_f32(x);
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int32_t bsum = 0;
+        for (int g = 0; g < 8; ++g) {
+            const uint8_t sc = w[106 + (g >> 1)];
+            const int32_t ls = 2 * (g & 1 ? sc >> 4 : sc & 15) + 1;
+            int32_t sumi = 0;
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *g1 = grid + 4 * iq3s_index(w, g, 2 * e), *g2 = grid + 4 * iq3s_index(w, g, 2 * e + 1);
+                const uint8_t sb = w[74 + 4 * g + e];
+                for (int j = 0; j < 4; ++j) {
+                    sumi += (int)(uint8_t)g1[j] * xq[32 * g + 8 * e + j] * ((sb >> j) & 1 ? -1 : 1);
+                    sumi += (int)(uint8_t)g2[j] * xq[32 * g + 8 * e + 4 + j] * ((sb >> (4 + j)) & 1 ? -1 : 1);
+                }
+            }
+            bsum += sumi * ls;
+        }
+        sumf += d * bsum;
+    }
+    return sumf;
+}
+
 /* ggml/src/ggml-cpu/quants.c:430-480; examples/kernels/vec_dot/tq1_0_q8_k.py:9-55 */
 float wo_vec_dot_tq1_0_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
     float sumf = 0.0f;
@@ -963,6 +1062,8 @@ int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, 
     case WO_IQ2_XXS: *out = wo_vec_dot_iq2_xxs_q8_K(w, x, grid, signs, k); return 0;
     case WO_IQ2_XS: *out = wo_vec_dot_iq2_xs_q8_K(w, x, grid, signs, k); return 0;
     case WO_IQ3_XXS: *out = wo_vec_dot_iq3_xxs_q8_K(w, x, grid, signs, k); return 0;
+    case WO_IQ2_S: *out = wo_vec_dot_iq2_s_q8_K(w, x, grid, k); return 0;
+    case WO_IQ3_S: *out = wo_vec_dot_iq3_s_q8_K(w, x, grid, k); return 0;
     case WO_TQ1_0: *out = wo_vec_dot_tq1_0_q8_K(w, x, k); return 0;
     default: return -1;
     }

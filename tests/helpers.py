@@ -38,6 +38,15 @@ def random_iq2_xs(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     return rec.reshape(n, nb * 74)
 
 
+def random_codebook_records(rng: np.random.Generator, n: int, k: int, record_bytes: int) -> np.ndarray:
+    """Random but valid IQ2_S / IQ3_S records: every index, sign and scale bit pattern is legal; d (the first two bytes) is a small f16."""
+    nb = k // 256
+    rec = rng.integers(0, 256, size=(n, nb, record_bytes), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal((n, nb))) * 0.01 + 1e-3).astype(np.float16)
+    rec[:, :, 0:2] = d.view(np.uint8).reshape(n, nb, 2)
+    return rec.reshape(n, nb * record_bytes)
+
+
 def random_iq3_xxs(rng: np.random.Generator, n: int, k: int) -> np.ndarray:
     """Random but valid IQ3_XXS records: any grid index byte, sign index and 4-bit scale is legal; d is a small f16."""
     nb = k // 256
@@ -86,9 +95,11 @@ def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
         if o.ref_available() and n * k <= 1 << 22:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
         return random_iq2_xxs(rng, n, k)
-    if fmt in (o.IQ2_XS, o.IQ3_XXS):
+    if fmt in (o.IQ2_XS, o.IQ3_XXS, o.IQ2_S, o.IQ3_S):
         if o.ref_available() and n * k <= 1 << 21:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
+        if fmt in (o.IQ2_S, o.IQ3_S):
+            return random_codebook_records(rng, n, k, o.RECORD_BYTES[fmt])
         return random_iq2_xs(rng, n, k) if fmt == o.IQ2_XS else random_iq3_xxs(rng, n, k)
     if fmt in (o.Q2_K, o.Q3_K, o.Q5_K, o.Q6_K):
         if o.ref_available() and n * k <= 1 << 22:
@@ -107,5 +118,5 @@ def activations(rng: np.random.Generator, m: int, k: int) -> np.ndarray:
 
 def tables(golden: dict, name: str = "iq2_xxs"):
     """The codebook and the sign table a format's kernels take as arguments (the sign table is the same for all three)."""
-    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid"}.get(name.lower(), "iq2xxs_grid")
+    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid", "iq2_s": "iq2s_grid", "iq3_s": "iq3s_grid"}.get(name.lower(), "iq2xxs_grid")
     return golden[grid], golden["iq2xxs_signs"]

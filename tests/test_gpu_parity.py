@@ -16,8 +16,9 @@ from helpers import TQ1_POWERS, activations, random_iq2_xxs, reference_tolerance
 pytestmark = pytest.mark.gpu
 
 DECODE_FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k"]   # have a production_mul_mat_<fmt>_decode
-FORMATS = DECODE_FORMATS + ["iq2_xs", "iq3_xxs"]
-CODEBOOKS = {"iq2_xxs": (256, 8, "I8X8"), "iq2_xs": (512, 8, "I8X8"), "iq3_xxs": (256, 4, "I8X4")}
+FORMATS = DECODE_FORMATS + ["iq2_xs", "iq3_xxs", "iq2_s", "iq3_s"]
+CODEBOOKS = {"iq2_xxs": (256, 8, "I8X8"), "iq2_xs": (512, 8, "I8X8"), "iq3_xxs": (256, 4, "I8X4"), "iq2_s": (1024, 8, "I8X8"), "iq3_s": (512, 4, "I8X4")}
+SIGN_TABLE = ("iq2_xxs", "iq2_xs", "iq3_xxs")     # the other codebook formats carry their sign bits in the record
 REL_L2_BOUND = 1e-5
 
 
@@ -48,7 +49,7 @@ def _fmt(oracle, name):
 def _table_args(torch, golden, name):
     grid, signs = tables(golden, name)
     if name in CODEBOOKS:
-        return [dev(torch, grid), dev(torch, signs)]
+        return [dev(torch, grid), dev(torch, signs)] if name in SIGN_TABLE else [dev(torch, grid)]
     if name == "tq1_0":
         return [dev(torch, TQ1_POWERS.view(np.int32)).view(torch.int32)]
     return []
@@ -61,7 +62,8 @@ def _wrap_tables(weft, name, tensors, dequant=False):
         if dequant:
             return tensors
         entries, width, encoding = CODEBOOKS[name]
-        return [Buffer(tensors[0], shape=(entries, width), encoding=encoding), Buffer(tensors[1], shape=(128, 8), encoding="I8X8")]
+        wrapped = [Buffer(tensors[0], shape=(entries, width), encoding=encoding)]
+        return wrapped + ([Buffer(tensors[1], shape=(128, 8), encoding="I8X8")] if name in SIGN_TABLE else [])
     if name == "tq1_0":
         return [Buffer(tensors[0], shape=(5,), encoding="dense.u32")]
     return []
@@ -246,7 +248,8 @@ def test_vec_dot_rows_against_oracle(torch, weft, oracle, golden, name, shape):
 
 # ------------------------------------------------------------------ mul_mat (decode)
 
-@pytest.mark.parametrize("symbol", ["production_mul_mat_iq2_xs", "production_mul_mat_iq2_xs_staged", "production_mul_mat_iq3_xxs", "production_mul_mat_iq2_xxs"])
+@pytest.mark.parametrize("symbol", ["production_mul_mat_iq2_xs", "production_mul_mat_iq2_xs_staged", "production_mul_mat_iq3_xxs", "production_mul_mat_iq2_xxs",
+                                    "production_mul_mat_iq2_s", "production_mul_mat_iq2_s_staged", "production_mul_mat_iq3_s"])
 @pytest.mark.parametrize("mnk", [(1, 512, 2048), (3, 200, 1024), (40, 96, 4096), (1, 4096, 4096)])
 def test_mul_mat_codebook_formats(torch, weft, oracle, golden, symbol, mnk):
     """The mul_mat symbols of IQ2_XS, IQ3_XXS and the unstaged IQ2_XXS name: K = 1024 leaves rows that are not whole
@@ -254,7 +257,7 @@ def test_mul_mat_codebook_formats(torch, weft, oracle, golden, symbol, mnk):
     from weft_b200.kernels import mul_mat
     from weft_b200.runtime import Buffer
 
-    name = "iq3_xxs" if "iq3" in symbol else "iq2_xs" if "iq2_xs" in symbol else "iq2_xxs"
+    name = symbol[len("production_mul_mat_"):].removesuffix("_staged")
     fmt = _fmt(oracle, name)
     m, n, k = mnk
     rng = np.random.default_rng(11 * fmt + m + n + k)
@@ -265,7 +268,7 @@ def test_mul_mat_codebook_formats(torch, weft, oracle, golden, symbol, mnk):
     xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
     y = torch.full((m, n), float("nan"), device="cuda")
     table_tensors = _table_args(torch, golden, name)
-    wrapped = table_tensors if symbol.endswith("iq2_xs_staged") else _wrap_tables(weft, name, table_tensors)   # flat int8 arrays there
+    wrapped = table_tensors if symbol.endswith(("iq2_xs_staged", "iq2_s_staged")) else _wrap_tables(weft, name, table_tensors)   # flat int8 arrays there
     weft.compile(getattr(mul_mat, symbol))(Buffer(dev(torch, w), shape=(n, k), encoding=name.upper()), dev(torch, x),
                                            Buffer(xq, shape=(m, k), encoding="Q8_K"), *wrapped, y)
     assert np.array_equal(xq.cpu().numpy(), want_xq)

@@ -223,7 +223,9 @@ int launched(cudaError_t e, const char *what, unsigned count = 1) {
 
 // bytes of the codebook a format's kernels take as an argument (int8[256][8], int8[512][8], int8[256][4]); the sign
 // table is int8[128][8] for all three
-size_t codebook_bytes(int fmt) { return fmt == F_IQ2_XXS ? 2048 : fmt == F_IQ2_XS ? 4096 : fmt == F_IQ3_XXS ? 1024 : 0; }
+size_t codebook_bytes(int fmt) { return fmt == F_IQ2_XXS ? 2048 : fmt == F_IQ2_XS ? 4096 : fmt == F_IQ3_XXS ? 1024 : fmt == F_IQ2_S ? 8192 : fmt == F_IQ3_S ? 2048 : 0; }
+// IQ2_S and IQ3_S carry their sign bits in the record
+bool has_sign_table(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS; }
 
 int do_dequantize(int fmt, const void *W, const int8_t *grid, const int8_t *signs, const uint32_t *powers, float *Y, size_t N, size_t K) {
     std::lock_guard<std::recursive_mutex> guard(g.lock);
@@ -233,7 +235,7 @@ int do_dequantize(int fmt, const void *W, const int8_t *grid, const int8_t *sign
     void *w, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
     if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
     if (fmt == F_Q6_K && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
-    if (codebook_bytes(fmt) && (call.map(grid, codebook_bytes(fmt), true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
+    if (codebook_bytes(fmt) && (call.map(grid, codebook_bytes(fmt), true, false, &gr) || (has_sign_table(fmt) && call.map(signs, 1024, true, false, &sg)))) return 1;
     if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
     if (call.map(Y, N * K * sizeof(float), false, true, &y)) return 1;
     if (launched(launch_dequantize(fmt, w, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw, (float *)y,
@@ -279,7 +281,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     const bool may_contract = mode == 1 && M >= 32 && K % 256 == 0;
     const bool xq_in_place = !have_xq && !may_contract && K % 256 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     if (call.map(Xq, M * row_bytes(act, K), have_xq, !have_xq, &xq, xq_in_place)) return 1;
-    if (codebook_bytes(fmt) && (call.map(grid, codebook_bytes(fmt), true, false, &gr) || call.map(signs, 1024, true, false, &sg))) return 1;
+    if (codebook_bytes(fmt) && (call.map(grid, codebook_bytes(fmt), true, false, &gr) || (has_sign_table(fmt) && call.map(signs, 1024, true, false, &sg)))) return 1;
     if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
     // a host Y with a pitch is staged whole (pitch * M floats); device Y is written in place; a small pinned Y too
     const size_t y_floats = (M - 1) * ldy + N;
@@ -430,6 +432,9 @@ VEC_DOT(quantized_vec_dot_q6_k_q8_k, F_Q6_K, NO_TABLES, nullptr, nullptr, nullpt
 VEC_DOT(quantized_vec_dot_iq2_xxs_q8_k, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
 VEC_DOT(quantized_vec_dot_iq2_xs_q8_k, F_IQ2_XS, IQ_TABLES, grid, signs, nullptr)
 VEC_DOT(quantized_vec_dot_iq3_xxs_q8_k, F_IQ3_XXS, IQ_TABLES, grid, signs, nullptr)
+#define GRID_ONLY , const int8_t *grid
+VEC_DOT(quantized_vec_dot_iq2_s_q8_k, F_IQ2_S, GRID_ONLY, grid, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_iq3_s_q8_k, F_IQ3_S, GRID_ONLY, grid, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_tq1_0_q8_k, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
 // The reference's second statement of the same dot product with sixteen-wide partial sums (a vector-length plan of
 // its target; the integer sum per block, and so every result bit, is the same): examples/kernels/vec_dot/tq1_0_q8_k_lane16.py:9-54
@@ -449,6 +454,8 @@ DEQUANT(row_dequantize_q6_k, F_Q6_K, NO_TABLES, nullptr, nullptr, nullptr)
 DEQUANT(row_dequantize_iq2_xxs, F_IQ2_XXS, IQ_TABLES, grid, signs, nullptr)
 DEQUANT(row_dequantize_iq2_xs, F_IQ2_XS, IQ_TABLES, grid, signs, nullptr)
 DEQUANT(row_dequantize_iq3_xxs, F_IQ3_XXS, IQ_TABLES, grid, signs, nullptr)
+DEQUANT(row_dequantize_iq2_s, F_IQ2_S, GRID_ONLY, grid, nullptr, nullptr)
+DEQUANT(row_dequantize_iq3_s, F_IQ3_S, GRID_ONLY, grid, nullptr, nullptr)
 DEQUANT(row_dequantize_tq1_0, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
 
 // ---- quantize
@@ -493,6 +500,10 @@ MUL_MAT(production_mul_mat_iq2_xxs, F_IQ2_XXS, 1, IQ_TABLES, grid, signs, nullpt
 MUL_MAT(production_mul_mat_iq2_xs, F_IQ2_XS, 1, IQ_TABLES, grid, signs, nullptr)
 MUL_MAT(production_mul_mat_iq2_xs_staged, F_IQ2_XS, 1, IQ_TABLES, grid, signs, nullptr)
 MUL_MAT(production_mul_mat_iq3_xxs, F_IQ3_XXS, 1, IQ_TABLES, grid, signs, nullptr)
+// IQ2_S (examples/kernels/mul_mat/iq2_s.py:10-16, iq2_s_staged.py:29-35) and IQ3_S (iq3_s.py:10-16): one table argument
+MUL_MAT(production_mul_mat_iq2_s, F_IQ2_S, 1, GRID_ONLY, grid, nullptr, nullptr)
+MUL_MAT(production_mul_mat_iq2_s_staged, F_IQ2_S, 1, GRID_ONLY, grid, nullptr, nullptr)
+MUL_MAT(production_mul_mat_iq3_s, F_IQ3_S, 1, GRID_ONLY, grid, nullptr, nullptr)
 
 // ---- persistent interleaved layout Q4K_I[16]: artifact functions and the kernels that consume it
 static size_t q4ki_packed_size(size_t rows, size_t K) { return K % 256 == 0 && rows % 16 == 0 ? rows * (K / 256) * 144 : 0; }
@@ -644,7 +655,7 @@ int weft_b200_mul_mat_shard_gather(int format, int mode, const uint8_t *W_local,
                                    float *const *Y_ranks, int *const *sync_ranks, void *const *stage_ranks, int world, int rank,
                                    size_t n0, size_t N_local, size_t N, size_t K, size_t M, unsigned flags) {
     if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K &&
-        format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
+        format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_IQ2_S && format != F_IQ3_S && format != F_TQ1_0 && format != F_Q4_K_I16)
         return fail("unknown weight format id %d", format);
     if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
     if (world < 2 || world > GATHER_MAX_RANKS || rank < 0 || rank >= world) return fail("world %d / rank %d out of range (2..%d ranks)", world, rank, GATHER_MAX_RANKS);
@@ -672,7 +683,7 @@ int weft_b200_mul_mat_shard_gather(int format, int mode, const uint8_t *W_local,
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags) {
-    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K && format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_TQ1_0 && format != F_Q4_K_I16)
+    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K && format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_IQ2_S && format != F_IQ3_S && format != F_TQ1_0 && format != F_Q4_K_I16)
         return fail("unknown weight format id %d", format);
     if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
     return do_mul_mat(format, mode, W_local, X, Xq, grid, signs, powers, Y_columns, N_local, K, M, ldy, flags, false);

@@ -263,6 +263,57 @@ __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq3_xxs_kernel(const ui
     }
 }
 
+// ---- IQ2_S (examples/kernels/dequantize/iq2_s.py, GGML dequantize_row_iq2_s): as IQ2_XS with 10-bit grid indices (low
+//      byte + two bits of qh) and explicit sign bits; lane = (group g, entry e).  The 8 KB grid is read through the
+//      read-only cache.
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq2_s_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                                                       float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, e = lane & 3;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 82;
+        const float d = half_bits_to_float(ld_u16(rec));
+        const uint32_t index = rec[2 + 4 * g + e] | (((uint32_t)rec[66 + g] << (8 - 2 * e)) & 0x300u);
+        const uint32_t sb = rec[34 + 4 * g + e], sc = rec[74 + g];
+        const float db = __fmul_rn(__fmul_rn(d, __fadd_rn(0.5f, (float)(e < 2 ? sc & 15u : sc >> 4))), 0.25f);
+        const uint2 gv = __ldg(reinterpret_cast<const uint2 *>(grid) + index);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float q = (float)(((i < 4 ? gv.x : gv.y) >> (8 * (i & 3))) & 0xffu);
+            v[i] = __fmul_rn(__fmul_rn(db, q), (sb >> i) & 1u ? -1.f : 1.f);
+        }
+        float *out = y + u * 256 + 32 * g + 8 * e;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
+// ---- IQ3_S (examples/kernels/dequantize/iq3_s.py, GGML dequantize_row_iq3_s): (d * (1 + 2 s)) * (grid * sign), 9-bit grid
+//      indices (low byte + one bit of qh), explicit sign bits; lane = (group g, entry e) produces 8 consecutive outputs
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq3_s_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                                                       float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, e = lane & 3;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 110;
+        const float d = half_bits_to_float(ld_u16(rec));
+        const uint32_t high = rec[66 + g], sb = rec[74 + 4 * g + e], sc = rec[106 + (g >> 1)];
+        const float db = __fmul_rn(d, (float)(1 + 2 * (int)(g & 1 ? sc >> 4 : sc & 15u)));
+        const uint32_t i1 = rec[2 + 8 * g + 2 * e] | (((high >> (2 * e)) & 1u) << 8), i2 = rec[2 + 8 * g + 2 * e + 1] | (((high >> (2 * e + 1)) & 1u) << 8);
+        const uint32_t g1 = __ldg(reinterpret_cast<const uint32_t *>(grid) + i1), g2 = __ldg(reinterpret_cast<const uint32_t *>(grid) + i2);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float q = (float)(((i < 4 ? g1 : g2) >> (8 * (i & 3))) & 0xffu);
+            v[i] = __fmul_rn(__fmul_rn(db, q), (sb >> i) & 1u ? -1.f : 1.f);
+        }
+        float *out = y + u * 256 + 32 * g + 8 * e;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
 // ---- TQ1_0: every lane produces 8 consecutive outputs; lanes 0-19 region 0 (5 digits x 32 bytes),
 //      20-29 region 1 (5 digits x 16 bytes), 30-31 region 2 (4 digits x 4 bytes)
 __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_tq1_0_kernel(const uint8_t *__restrict__ w, const uint32_t *__restrict__ powers,
@@ -410,6 +461,19 @@ __global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ 
             const float db = __fmul_rn(__fmul_rn(half_bits_to_float(ld_u16(rec)), __fadd_rn(0.5f, (float)(meta >> 28))), 0.5f);
             const int gv = (int)(uint8_t)grid[4 * rec[2 + 8 * g + 2 * en + (l >> 2)] + (l & 3)], sv = signs[8 * ((meta >> (7 * en)) & 127u) + l];
             v = __fmul_rn(__fmul_rn(db, (float)gv), (float)sv);
+        } else if (fmt == F_IQ2_S) {
+            const uint8_t *rec = w + (i / 256) * 82;
+            const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8;
+            const uint32_t index = rec[2 + 4 * g + en] | (((uint32_t)rec[66 + g] << (8 - 2 * en)) & 0x300u), sc = rec[74 + g];
+            const float db = __fmul_rn(__fmul_rn(half_bits_to_float(ld_u16(rec)), __fadd_rn(0.5f, (float)(en < 2 ? sc & 15u : sc >> 4))), 0.25f);
+            v = __fmul_rn(__fmul_rn(db, (float)(int)(uint8_t)grid[8 * index + l]), (rec[34 + 4 * g + en] >> l) & 1 ? -1.f : 1.f);
+        } else if (fmt == F_IQ3_S) {
+            const uint8_t *rec = w + (i / 256) * 110;
+            const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8, ix = 2 * en + (l >> 2);
+            const uint32_t sc = rec[106 + (g >> 1)];
+            const float db = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)(1 + 2 * (int)(g & 1 ? sc >> 4 : sc & 15u)));
+            const uint32_t index = rec[2 + 8 * g + ix] | ((((uint32_t)rec[66 + g] >> ix) & 1u) << 8);
+            v = __fmul_rn(__fmul_rn(db, (float)(int)(uint8_t)grid[4 * index + (l & 3)]), (rec[74 + 4 * g + en] >> l) & 1 ? -1.f : 1.f);
         } else if (fmt == F_TQ1_0) {
             const uint8_t *rec = w + (i / 256) * 54;
             const int e = (int)(i % 256);
@@ -485,6 +549,16 @@ cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const 
     case F_IQ3_XXS: {
         const long long units = elements / 256;
         dequant_iq3_xxs_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, signs, y, units);
+        break;
+    }
+    case F_IQ2_S: {
+        const long long units = elements / 256;
+        dequant_iq2_s_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, y, units);
+        break;
+    }
+    case F_IQ3_S: {
+        const long long units = elements / 256;
+        dequant_iq3_s_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, y, units);
         break;
     }
     case F_Q6_K: {

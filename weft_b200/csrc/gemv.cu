@@ -64,8 +64,9 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
     uint8_t *cursor = smem + 16 + 48 * warps;
     uint8_t *s_tab0 = cursor, *s_tab1 = cursor;
     // codebook formats: the grid as given, then the sign table as byte masks (1 KB)
-    constexpr int GRID_BYTES = FMT == F_IQ2_XXS ? 2048 : FMT == F_IQ2_XS ? 4096 : FMT == F_IQ3_XXS ? 1024 : 0;
-    if (GRID_BYTES) { s_tab1 = cursor + GRID_BYTES; cursor += GRID_BYTES + 1024; }
+    constexpr int GRID_BYTES = FMT == F_IQ2_XXS ? 2048 : FMT == F_IQ2_XS ? 4096 : FMT == F_IQ3_XXS ? 1024 : FMT == F_IQ2_S ? 8192 : FMT == F_IQ3_S ? 2048 : 0;
+    constexpr bool SIGN_TABLE = FMT == F_IQ2_XXS || FMT == F_IQ2_XS || FMT == F_IQ3_XXS;
+    if (GRID_BYTES) { s_tab1 = cursor + GRID_BYTES; cursor += GRID_BYTES + (SIGN_TABLE ? 1024 : 0); }
     uint8_t *s_xq = cursor;
     cursor += nb * XQ_PITCH;
     uint8_t *s_xaux = cursor;
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
     // stage tables and activations
     if (GRID_BYTES) {
         for (int i = threadIdx.x; i < GRID_BYTES; i += blockDim.x) s_tab0[i] = (uint8_t)p.grid[i];
-        for (int i = threadIdx.x; i < 1024; i += blockDim.x) s_tab1[i] = p.signs[i] < 0 ? 0xffu : 0u;
+        if (SIGN_TABLE) for (int i = threadIdx.x; i < 1024; i += blockDim.x) s_tab1[i] = p.signs[i] < 0 ? 0xffu : 0u;
     }
     uint32_t pw[5] = {1, 3, 9, 27, 81};
     if (FMT == F_TQ1_0) {
@@ -181,13 +182,15 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
             else if (FMT == F_IQ2_XXS) dot_iq2_xxs<RL>(wp, xu, xa, s_tab0, s_tab1, acc);
             else if (FMT == F_IQ2_XS) dot_iq2_xs<RL>(wp, xu, xa, s_tab0, s_tab1, acc);
             else if (FMT == F_IQ3_XXS) dot_iq3_xxs<RL>(wp, xu, xa, s_tab0, s_tab1, acc);
+            else if (FMT == F_IQ2_S) dot_iq2_s<RL>(wp, xu, xa, s_tab0, acc);
+            else if (FMT == F_IQ3_S) dot_iq3_s<RL>(wp, xu, xa, s_tab0, acc);
             else dot_tq1_0<RL>(wp, xu, xa, pw, acc);
         }
 #pragma unroll
         for (int r = 0; r < RL; ++r) {
             float v = acc[r];
             for (int o = L >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (FMT == F_IQ2_XXS || FMT == F_IQ2_XS) v *= 0.125f;
+            if (FMT == F_IQ2_XXS || FMT == F_IQ2_XS || FMT == F_IQ2_S) v *= 0.125f;
             if (FMT == F_IQ3_XXS) v *= 0.25f;
             if (ul == 0 && live[r]) y[r_begin + cur + slot * RL + r] = v;
         }
@@ -260,7 +263,7 @@ static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stre
     int warps = kEnvWarps;
     warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
     int rl = kEnvRowsPerLane;
-    const long long x_bytes = (long long)nb * (XQ_PITCH + XAUX_BYTES) + (FMT == F_IQ2_XXS ? 3072 : FMT == F_IQ2_XS ? 5120 : FMT == F_IQ3_XXS ? 2048 : 0) + 16 + 48 * 16;
+    const long long x_bytes = (long long)nb * (XQ_PITCH + XAUX_BYTES) + (FMT == F_IQ2_XXS ? 3072 : FMT == F_IQ2_XS ? 5120 : FMT == F_IQ3_XXS ? 2048 : FMT == F_IQ2_S ? 8192 : FMT == F_IQ3_S ? 2048 : 0) + 16 + 48 * 16;
     int nbuf = kEnvRingDepth;
     nbuf = nbuf < 2 ? 2 : (nbuf > 4 ? 4 : nbuf);
     auto ring = [&](int w_, int rl_) { return (long long)w_ * nbuf * (((32 / L) * rl_ * row_bytes + 31) / 16 * 16); };
@@ -341,6 +344,8 @@ cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
     case F_IQ2_XXS: return launch_fmt<F_IQ2_XXS>(a, sm_count, stream);
     case F_IQ2_XS: return launch_fmt<F_IQ2_XS>(a, sm_count, stream);
     case F_IQ3_XXS: return launch_fmt<F_IQ3_XXS>(a, sm_count, stream);
+    case F_IQ2_S: return launch_fmt<F_IQ2_S>(a, sm_count, stream);
+    case F_IQ3_S: return launch_fmt<F_IQ3_S>(a, sm_count, stream);
     case F_TQ1_0: return launch_fmt<F_TQ1_0>(a, sm_count, stream);
     default: return cudaErrorInvalidValue;
     }

@@ -454,6 +454,99 @@ __device__ __forceinline__ void dot_iq3_xxs(const uint8_t *const (&wp)[RL], cons
     for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
 }
 
+// Eight sign bits (bit j set: weight j negative) as two words of byte masks, 0xff where negative
+__device__ __forceinline__ void sign_bits_to_masks(uint32_t bits, uint32_t &m0, uint32_t &m1) {
+    // x * 0x00204081 puts bit i of a nibble at bit 8 i; the other product bits are masked away
+    m0 = (((bits & 15u) * 0x00204081u) & 0x01010101u) * 0xffu;
+    m1 = ((((bits >> 4) & 15u) * 0x00204081u) & 0x01010101u) * 0xffu;
+}
+
+// One IQ2_S record (82 bytes, 2-byte aligned): f16 d; 32 bytes: low 8 bits of the grid index of every 8 weights; 32 sign
+// bytes; 8 bytes: per 32 weights four 2-bit pairs, index bits 8-9; 8 scale bytes as IQ2_XS
+// (examples/kernels/vec_dot/iq2_s_q8_k.py:68-73; GGML ggml_vec_dot_iq2_s_q8_K_generic).  s_grid: int8[1024][8], PITCH bytes
+// between entries (the caller passes the pointer already offset to its lane's copy).
+template <int RL, int PITCH = 8>
+__device__ __forceinline__ void dot_iq2_s(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                           const uint8_t *s_grid, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    uint32_t qw[RL][20];
+    int bsum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<20>(wp[r] + 2, qw[r]); bsum[r] = 0; }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t low = qw[r][g], sgn = qw[r][8 + g];
+            const uint32_t high = byte_of(qw[r][16 + (g >> 2)], g & 3), sc = byte_of(qw[r][18 + (g >> 2)], g & 3);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                int pos = 0, neg = 0;
+#pragma unroll
+                for (int ee = 0; ee < 2; ++ee) {
+                    const int e = 2 * half + ee;
+                    const uint32_t index = byte_of(low, e) | ((high << (8 - 2 * e)) & 0x300u);
+                    const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + PITCH * index);
+                    uint32_t m0, m1;
+                    sign_bits_to_masks(byte_of(sgn, e), m0, m1);
+                    pos = dp4a_ss(gv.x, xw[2 * e], pos);
+                    pos = dp4a_ss(gv.y, xw[2 * e + 1], pos);
+                    neg = dp4a_ss(gv.x & m0, xw[2 * e], neg);
+                    neg = dp4a_ss(gv.y & m1, xw[2 * e + 1], neg);
+                }
+                bsum[r] += (pos - 2 * neg) * (int)(2u * (half ? sc >> 4 : sc & 15u) + 1u);
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
+}
+
+// One IQ3_S record (110 bytes, 2-byte aligned): f16 d; 64 bytes: low 8 bits of the grid index of every 4 weights; 8 bytes:
+// bit e of byte g is index bit 8 of entry e of 32-group g; 32 sign bytes; 4 scale bytes (nibble per 32 weights)
+// (examples/kernels/vec_dot/iq3_s_q8_k.py:67-72; GGML ggml_vec_dot_iq3_s_q8_K_generic).  s_grid: int8[512][4], GP bytes
+// between entries.  No factor on the result.
+template <int RL, int GP = 4>
+__device__ __forceinline__ void dot_iq3_s(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                           const uint8_t *s_grid, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    uint32_t qw[RL][27];
+    int bsum[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<27>(wp[r] + 2, qw[r]); bsum[r] = 0; }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t high = byte_of(qw[r][16 + (g >> 2)], g & 3), sgn = qw[r][18 + g];
+            const uint32_t sc = byte_of(qw[r][26], g >> 1);
+            int pos = 0, neg = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint32_t pair = qw[r][2 * g + (e >> 1)] >> (16 * (e & 1));   // index bytes 2e and 2e + 1 of the group
+                const uint32_t i1 = (pair & 0xffu) | (((high >> (2 * e)) & 1u) << 8), i2 = ((pair >> 8) & 0xffu) | (((high >> (2 * e + 1)) & 1u) << 8);
+                const uint32_t g1 = *reinterpret_cast<const uint32_t *>(s_grid + GP * i1);
+                const uint32_t g2 = *reinterpret_cast<const uint32_t *>(s_grid + GP * i2);
+                uint32_t m0, m1;
+                sign_bits_to_masks(byte_of(sgn, e), m0, m1);
+                pos = dp4a_ss(g1, xw[2 * e], pos);
+                pos = dp4a_ss(g2, xw[2 * e + 1], pos);
+                neg = dp4a_ss(g1 & m0, xw[2 * e], neg);
+                neg = dp4a_ss(g2 & m1, xw[2 * e + 1], neg);
+            }
+            bsum[r] += (pos - 2 * neg) * (int)(2u * (g & 1 ? sc >> 4 : sc & 15u) + 1u);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
+}
+
 // Bank-striped copies of a codebook: with 8-byte entries, copy c (of sixteen) of entry e sits at e * 128 + c * 8, so copy
 // c lives in banks 2c and 2c + 1 only and a half-warp whose lane l reads copy l % 16 never conflicts, whatever the
 // entries (an 8-byte shared load is served one half-warp at a time); with 4-byte entries, copy c (of thirty-two) at
@@ -464,6 +557,13 @@ __device__ inline void stage_striped8(const int8_t *table, int entries, uint8_t 
         uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(table) + word);
         if (masks) v = ((v >> 7) & 0x01010101u) * 0xffu;
         reinterpret_cast<uint32_t *>(dst)[(word >> 1) * 32 + c * 2 + (word & 1)] = v;
+    }
+}
+// four copies of 8-byte entries (a table too large for sixteen): copy c of entry e at e * 32 + c * 8; lane l reads copy l % 4
+__device__ inline void stage_striped8x4(const int8_t *table, int entries, uint8_t *dst) {
+    for (int i = threadIdx.x; i < entries * 2 * 4; i += blockDim.x) {
+        const int word = i >> 2, c = i & 3;
+        reinterpret_cast<uint32_t *>(dst)[(word >> 1) * 8 + c * 2 + (word & 1)] = __ldg(reinterpret_cast<const uint32_t *>(table) + word);
     }
 }
 __device__ inline void stage_striped4(const int8_t *table, int entries, uint8_t *dst) {

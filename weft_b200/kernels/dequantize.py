@@ -64,5 +64,15 @@ def row_dequantize_iq3_xxs(W: wl.View[ggml.IQ3_XXS, (K,)], grid: wl.View[wl.i8, 
 
 
 @kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq2_s(W: wl.View[ggml.IQ2_S, (K,)], grid: wl.View[wl.i8, (8192,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (0.5 + s) * 0.25) * (grid[idx] * sign), s per 16 elements (examples/kernels/dequantize/iq2_s.py:9-13)."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq3_s(W: wl.View[ggml.IQ3_S, (K,)], grid: wl.View[wl.i8, (2048,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (1 + 2 s)) * (grid[idx] * sign), s per 32 elements (examples/kernels/dequantize/iq3_s.py:9-13)."""
+
+
+@kernel(alias_groups={"Y": "output"})
 def row_dequantize_tq1_0(W: wl.View[ggml.TQ1_0, (K,)], powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (K,)]):
     """Y = f32(trit - 1) * d, digit-major within each of the record's three regions."""

@@ -175,6 +175,24 @@ def production_mul_mat_iq3_xxs(W: wl.View[ggml.IQ3_XXS, (N, K)], X: wl.View[wl.f
 
 
 @kernel
+def production_mul_mat_iq2_s(W: wl.View[ggml.IQ2_S, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                             grid: wl.View[ggml.I8X8, (1024, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """IQ2_S x Q8_K mul_mat (examples/kernels/mul_mat/iq2_s.py:10-16)."""
+
+
+@kernel
+def production_mul_mat_iq2_s_staged(W: wl.View[ggml.IQ2_S, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                                    grid: wl.View[wl.i8, (8192,)], Y: wl.View[wl.f32, (M, N)]):
+    """The same with the grid as a flat byte array (examples/kernels/mul_mat/iq2_s_staged.py:29-35)."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq3_s(W: wl.View[ggml.IQ3_S, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                             grid: wl.View[ggml.I8X4, (512, 4)], Y: wl.View[wl.f32, (M, N)]):
+    """IQ3_S x Q8_K mul_mat (examples/kernels/mul_mat/iq3_s.py:10-16)."""
+
+
+@kernel
 def production_mul_mat_q4_k_persistent(W: wl.View[ggml.Q4K_I[16], (N, K)], X: wl.View[wl.f32, (M, K)],
                                        Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):
     """Q4_K x Q8_K over the persistent interleaved layout (examples/kernels/mul_mat/q4_k_persistent.py:9-30).

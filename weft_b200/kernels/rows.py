@@ -56,6 +56,14 @@ def row_dequantize_iq3_xxs_rows(W: wl.View[ggml.IQ3_XXS, (N, K)], grid: wl.View[
 
 
 @kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq2_s_rows(W: wl.View[ggml.IQ2_S, (N, K)], grid: wl.View[wl.i8, (8192,)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq3_s_rows(W: wl.View[ggml.IQ3_S, (N, K)], grid: wl.View[wl.i8, (2048,)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
+@kernel(alias_groups={"Y": "output"})
 def row_dequantize_tq1_0_rows(W: wl.View[ggml.TQ1_0, (N, K)], powers: wl.View[wl.u32, (5,)],
                               Y: wl.View[wl.f32, (N, K)]): ...
 
@@ -104,6 +112,16 @@ def quantized_vec_dot_iq2_xs_q8_k_rows(W: wl.View[ggml.IQ2_XS, (N, K)], X: wl.Vi
 def quantized_vec_dot_iq3_xxs_q8_k_rows(W: wl.View[ggml.IQ3_XXS, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
                                         grid: wl.View[ggml.I8X4, (256, 4)], signs: wl.View[ggml.I8X8, (128, 8)],
                                         Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_iq2_s_q8_k_rows(W: wl.View[ggml.IQ2_S, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
+                                      grid: wl.View[ggml.I8X8, (1024, 8)], Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_iq3_s_q8_k_rows(W: wl.View[ggml.IQ3_S, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
+                                      grid: wl.View[ggml.I8X4, (512, 4)], Y: wl.View[wl.f32, (N,)]): ...
 
 
 @kernel

@@ -69,6 +69,19 @@ def quantized_vec_dot_iq3_xxs_q8_k(W: wl.View[ggml.IQ3_XXS, (K,)], X: wl.View[gg
 
 
 @kernel
+def quantized_vec_dot_iq2_s_q8_k(W: wl.View[ggml.IQ2_S, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                 grid: wl.View[ggml.I8X8, (1024, 8)], Y: wl.View[wl.f32, (1,)]):
+    """As IQ2_XS with 10-bit grid indices and sign bits stored in the record (examples/kernels/vec_dot/iq2_s_q8_k.py:68-73)."""
+
+
+@kernel
+def quantized_vec_dot_iq3_s_q8_k(W: wl.View[ggml.IQ3_S, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                 grid: wl.View[ggml.I8X4, (512, 4)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 256-blocks of d * x.ds * sum_g (2 s_g + 1) * dot(grid[idx] * sign, x)
+    (examples/kernels/vec_dot/iq3_s_q8_k.py:67-72)."""
+
+
+@kernel
 def quantized_vec_dot_tq1_0_q8_k(W: wl.View[ggml.TQ1_0, (K,)], X: wl.View[ggml.Q8_K, (K,)],
                                  powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (1,)]):
     """Y[0] = sum over 256-blocks of f32(sum((trit - 1) * x)) * (d * x.ds); trits decoded with powers[]."""
