@@ -15,10 +15,10 @@
  *     found again by address, so only activations and outputs move per call.
  *
  * Records are the GGML block formats, never repacked: Q4_0 18 B/32, Q8_0 34 B/32, Q4_K 144 B/256,
- * Q2_K 84 B/256, Q3_K 110 B/256, Q5_K 176 B/256, Q6_K 210 B/256, Q8_K 292 B/256, IQ2_XXS 66 B/256, IQ2_XS 74 B/256, IQ2_S 82 B/256, IQ3_XXS 98 B/256, IQ3_S 110 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
+ * Q2_K 84 B/256, Q3_K 110 B/256, Q5_K 176 B/256, Q6_K 210 B/256, Q8_K 292 B/256, IQ2_XXS 66 B/256, IQ1_S 50 B/256, IQ1_M 56 B/256, IQ2_XS 74 B/256, IQ2_S 82 B/256, IQ3_XXS 98 B/256, IQ3_S 110 B/256, TQ1_0 54 B/256.  No entry point allocates a hidden workspace for
  * device-pointer arguments: Xq is the caller's written workspace, as in the reference.
  * Codebook tables arrive as arguments: grid int8[256][8] (IQ2_XXS), int8[512][8] (IQ2_XS), int8[256][4] (IQ3_XXS, values
- * 4..62), int8[1024][8] (IQ2_S), int8[512][4] (IQ3_S); signs int8[128][8] with entries +1 / -1 (IQ2_S and IQ3_S carry
+ * 4..62), int8[1024][8] (IQ2_S), int8[512][4] (IQ3_S), int8[2048][8] with values -1 / 0 / +1 (IQ1_S, IQ1_M); signs int8[128][8] with entries +1 / -1 (IQ2_S and IQ3_S carry
  * their sign bits in the record and take no sign table).
  * TQ1_0 takes powers uint32[5] = {1, 3, 9, 27, 81}.
  *
@@ -73,6 +73,12 @@ int quantized_vec_dot_iq3_xxs_q8_k(const uint8_t *W, const uint8_t *X, const int
 int quantized_vec_dot_iq2_s_q8_k(const uint8_t *W, const uint8_t *X, const int8_t *grid, float *Y, size_t K);
 /* examples/kernels/vec_dot/iq3_s_q8_k.py:67-72     vec_dot_runtime.cpp:305-312 */
 int quantized_vec_dot_iq3_s_q8_k(const uint8_t *W, const uint8_t *X, const int8_t *grid, float *Y, size_t K);
+/* examples/kernels/vec_dot/iq1_s_q8_k.py:51-56     vec_dot_runtime.cpp:265-272 */
+int quantized_vec_dot_iq1_s_q8_k(const uint8_t *W, const uint8_t *X, const int8_t *grid, float *Y, size_t K);
+/* examples/kernels/vec_dot/iq1_m_q8_k.py:73-79, iq1_m_q8_k_lane16.py:85-91   vec_dot_runtime.cpp:273-280
+ * (f16_bits: float[65536], entry b the value of the f16 bit pattern b, as the reference's harness builds it) */
+int quantized_vec_dot_iq1_m_q8_k(const uint8_t *W, const uint8_t *X, const int8_t *grid, const float *f16_bits, float *Y, size_t K);
+int quantized_vec_dot_iq1_m_q8_k_lane16(const uint8_t *W, const uint8_t *X, const int8_t *grid, const float *f16_bits, float *Y, size_t K);
 /* examples/kernels/vec_dot/tq1_0_q8_k.py:47-55     vec_dot_runtime.cpp:343 */
 int quantized_vec_dot_tq1_0_q8_k(const uint8_t *W, const uint8_t *X, const uint32_t *powers, float *Y, size_t K);
 /* examples/kernels/vec_dot/tq1_0_q8_k_lane16.py:9-54 (the same dot product written with sixteen-wide partial sums
@@ -94,6 +100,9 @@ int row_dequantize_iq3_xxs(const uint8_t *W, const int8_t *grid, const int8_t *s
 int row_dequantize_iq2_s(const uint8_t *W, const int8_t *grid, float *Y, size_t K);
 /* examples/kernels/dequantize/iq3_s.py:9-13; grid int8[2048]    row_dequantize_runtime.cpp:249-252 */
 int row_dequantize_iq3_s(const uint8_t *W, const int8_t *grid, float *Y, size_t K);
+/* examples/kernels/dequantize/iq1_s.py:9-13, iq1_m.py:18-23; grid int8[16384] */
+int row_dequantize_iq1_s(const uint8_t *W, const int8_t *grid, float *Y, size_t K);
+int row_dequantize_iq1_m(const uint8_t *W, const int8_t *grid, const float *f16_bits, float *Y, size_t K);
 /* examples/kernels/dequantize/tq1_0.py:9-46        row_dequantize_runtime.cpp:272 */
 int row_dequantize_tq1_0(const uint8_t *W, const uint32_t *powers, float *Y, size_t K);
 
@@ -156,6 +165,13 @@ int production_mul_mat_iq3_xxs(const uint8_t *W, const float *X, uint8_t *Xq, co
 int production_mul_mat_iq2_s(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, float *Y, size_t N, size_t K, size_t M);
 int production_mul_mat_iq2_s_staged(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, float *Y, size_t N, size_t K, size_t M);
 int production_mul_mat_iq3_s(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, float *Y, size_t N, size_t K, size_t M);
+/* examples/kernels/mul_mat/iq1_s.py:9-15, iq1_s_decode.py:10-16           mul_mat_runtime.cpp:389-401;
+ * examples/kernels/mul_mat/iq1_m.py:10-17, iq1_m_decode.py:10-17, iq1_m_lane16_decode.py:10-17   mul_mat_runtime.cpp:404-416 */
+int production_mul_mat_iq1_s(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_iq1_s_decode(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_iq1_m(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, const float *f16_bits, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_iq1_m_decode(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, const float *f16_bits, float *Y, size_t N, size_t K, size_t M);
+int production_mul_mat_iq1_m_lane16_decode(const uint8_t *W, const float *X, uint8_t *Xq, const int8_t *grid, const float *f16_bits, float *Y, size_t N, size_t K, size_t M);
 
 /* ------------------------------------------------------------------ whole-matrix forms (no reference counterpart)
  * The reference's standalone symbols above take one row and its harness loops rows on the host
@@ -169,6 +185,8 @@ int row_dequantize_iq2_xs_rows(const uint8_t *W, const int8_t *grid, const int8_
 int row_dequantize_iq3_xxs_rows(const uint8_t *W, const int8_t *grid, const int8_t *signs, float *Y, size_t N, size_t K);
 int row_dequantize_iq2_s_rows(const uint8_t *W, const int8_t *grid, float *Y, size_t N, size_t K);
 int row_dequantize_iq3_s_rows(const uint8_t *W, const int8_t *grid, float *Y, size_t N, size_t K);
+int row_dequantize_iq1_s_rows(const uint8_t *W, const int8_t *grid, float *Y, size_t N, size_t K);
+int row_dequantize_iq1_m_rows(const uint8_t *W, const int8_t *grid, const float *f16_bits, float *Y, size_t N, size_t K);
 int row_dequantize_tq1_0_rows(const uint8_t *W, const uint32_t *powers, float *Y, size_t N, size_t K);
 /* Y[n] = vec_dot(W[n], X) for n < N; X one row of activation records */
 int quantized_vec_dot_q4_0_q8_0_rows(const uint8_t *W, const uint8_t *X, float *Y, size_t N, size_t K);
@@ -179,6 +197,9 @@ int quantized_vec_dot_iq2_xs_q8_k_rows(const uint8_t *W, const uint8_t *X, const
 int quantized_vec_dot_iq3_xxs_q8_k_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, const int8_t *signs, float *Y, size_t N, size_t K);
 int quantized_vec_dot_iq2_s_q8_k_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, float *Y, size_t N, size_t K);
 int quantized_vec_dot_iq3_s_q8_k_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, float *Y, size_t N, size_t K);
+int quantized_vec_dot_iq1_s_q8_k_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, float *Y, size_t N, size_t K);
+int quantized_vec_dot_iq1_m_q8_k_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, const float *f16_bits, float *Y, size_t N, size_t K);
+int quantized_vec_dot_iq1_m_q8_k_lane16_rows(const uint8_t *W, const uint8_t *X, const int8_t *grid, const float *f16_bits, float *Y, size_t N, size_t K);
 int quantized_vec_dot_tq1_0_q8_k_rows(const uint8_t *W, const uint8_t *X, const uint32_t *powers, float *Y, size_t N, size_t K);
 int q8_0_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
 int q8_1_quantize_rows(const float *X, uint8_t *Y, size_t M, size_t K);
@@ -269,7 +290,7 @@ int production_mul_mat_q4_k_persistent_W_pack(const uint8_t *source, uint8_t *ta
 int production_mul_mat_q4_k_persistent(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t M, size_t K, size_t N);
 
 /* Row-sharded mul_mat: this process holds weight rows [n0, n0+N_local) of an (N,K) matrix and writes
- * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 6 Q2_K, 7 Q3_K, 8 Q4_K, 9 Q5_K, 10 Q6_K, 13 IQ2_S, 14 IQ2_XS, 15 IQ2_XXS, 16 IQ3_S, 17 IQ3_XXS,
+ * columns n0.. of Y, whose rows are ldy floats apart.  format: 1 Q4_0, 5 Q8_0, 6 Q2_K, 7 Q3_K, 8 Q4_K, 9 Q5_K, 10 Q6_K, 11 IQ1_S, 12 IQ1_M, 13 IQ2_S, 14 IQ2_XS, 15 IQ2_XXS, 16 IQ3_S, 17 IQ3_XXS,
  * 20 TQ1_0 (the reference harness numbering).  mode: 0 decode (GEMV), 1 prefill (tensor cores).
  * flags bit 0: Xq already holds the quantized activations (X may be NULL). */
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,

@@ -21,11 +21,11 @@ import numpy as np
 
 HERE = Path(__file__).resolve().parent
 
-Q4_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ2_S, IQ2_XS, IQ2_XXS, IQ3_S, IQ3_XXS, TQ1_0, Q8_K, Q8_1 = 1, 5, 6, 7, 8, 9, 10, 13, 14, 15, 16, 17, 20, 100, 101
-FORMAT_IDS = {"Q4_0": Q4_0, "Q8_0": Q8_0, "Q2_K": Q2_K, "Q3_K": Q3_K, "Q4_K": Q4_K, "Q5_K": Q5_K, "Q6_K": Q6_K, "IQ2_XXS": IQ2_XXS, "IQ2_XS": IQ2_XS, "IQ3_XXS": IQ3_XXS, "IQ2_S": IQ2_S, "IQ3_S": IQ3_S, "TQ1_0": TQ1_0, "Q8_K": Q8_K, "Q8_1": Q8_1}
-RECORD_BYTES = {Q4_0: 18, Q8_0: 34, Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210, IQ2_XXS: 66, IQ2_XS: 74, IQ3_XXS: 98, IQ2_S: 82, IQ3_S: 110, TQ1_0: 54, Q8_K: 292, Q8_1: 36}
-RECORD_ELEMENTS = {Q4_0: 32, Q8_0: 32, Q2_K: 256, Q3_K: 256, Q4_K: 256, Q5_K: 256, Q6_K: 256, IQ2_XXS: 256, IQ2_XS: 256, IQ3_XXS: 256, IQ2_S: 256, IQ3_S: 256, TQ1_0: 256, Q8_K: 256, Q8_1: 32}
-ACTIVATION = {Q4_0: Q8_0, Q8_0: Q8_0, Q2_K: Q8_K, Q3_K: Q8_K, Q4_K: Q8_K, Q5_K: Q8_K, Q6_K: Q8_K, IQ2_XXS: Q8_K, IQ2_XS: Q8_K, IQ3_XXS: Q8_K, IQ2_S: Q8_K, IQ3_S: Q8_K, TQ1_0: Q8_K}
+Q4_0, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K, IQ1_S, IQ1_M, IQ2_S, IQ2_XS, IQ2_XXS, IQ3_S, IQ3_XXS, TQ1_0, Q8_K, Q8_1 = 1, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 20, 100, 101
+FORMAT_IDS = {"Q4_0": Q4_0, "Q8_0": Q8_0, "Q2_K": Q2_K, "Q3_K": Q3_K, "Q4_K": Q4_K, "Q5_K": Q5_K, "Q6_K": Q6_K, "IQ2_XXS": IQ2_XXS, "IQ2_XS": IQ2_XS, "IQ3_XXS": IQ3_XXS, "IQ2_S": IQ2_S, "IQ3_S": IQ3_S, "IQ1_S": IQ1_S, "IQ1_M": IQ1_M, "TQ1_0": TQ1_0, "Q8_K": Q8_K, "Q8_1": Q8_1}
+RECORD_BYTES = {Q4_0: 18, Q8_0: 34, Q2_K: 84, Q3_K: 110, Q4_K: 144, Q5_K: 176, Q6_K: 210, IQ2_XXS: 66, IQ2_XS: 74, IQ3_XXS: 98, IQ2_S: 82, IQ3_S: 110, IQ1_S: 50, IQ1_M: 56, TQ1_0: 54, Q8_K: 292, Q8_1: 36}
+RECORD_ELEMENTS = {Q4_0: 32, Q8_0: 32, Q2_K: 256, Q3_K: 256, Q4_K: 256, Q5_K: 256, Q6_K: 256, IQ2_XXS: 256, IQ2_XS: 256, IQ3_XXS: 256, IQ2_S: 256, IQ3_S: 256, IQ1_S: 256, IQ1_M: 256, TQ1_0: 256, Q8_K: 256, Q8_1: 32}
+ACTIVATION = {Q4_0: Q8_0, Q8_0: Q8_0, Q2_K: Q8_K, Q3_K: Q8_K, Q4_K: Q8_K, Q5_K: Q8_K, Q6_K: Q8_K, IQ2_XXS: Q8_K, IQ2_XS: Q8_K, IQ3_XXS: Q8_K, IQ2_S: Q8_K, IQ3_S: Q8_K, IQ1_S: Q8_K, IQ1_M: Q8_K, TQ1_0: Q8_K}
 
 _u8p = ctypes.POINTER(ctypes.c_uint8)
 _i8p = ctypes.POINTER(ctypes.c_int8)
@@ -102,6 +102,7 @@ def ref() -> ctypes.CDLL:
         lib.weft_ref_iq3xxs_grid.argtypes = [_i8p]
         lib.weft_ref_iq2s_grid.argtypes = [_i8p]
         lib.weft_ref_iq3s_grid.argtypes = [_i8p]
+        lib.weft_ref_iq1s_grid.argtypes = [_i8p]
         _ref = lib
     return _ref
 
@@ -240,6 +241,12 @@ def ref_iq2s_grid():
 def ref_iq3s_grid():
     grid = np.empty(2048, dtype=np.int8)
     ref().weft_ref_iq3s_grid(_ptr(grid, _i8p))
+    return grid
+
+
+def ref_iq1s_grid():
+    grid = np.empty(16384, dtype=np.int8)
+    ref().weft_ref_iq1s_grid(_ptr(grid, _i8p))
     return grid
 
 

@@ -49,7 +49,7 @@ __attribute__((constructor)) static void weft_ref_init(void) {
 }
 
 /* format ids follow the reference harnesses (vec_dot_runtime.cpp:185-344) */
-enum { WEFT_Q4_0 = 1, WEFT_Q8_0 = 5, WEFT_Q2_K = 6, WEFT_Q3_K = 7, WEFT_Q4_K = 8, WEFT_Q5_K = 9, WEFT_Q6_K = 10, WEFT_IQ2_S = 13, WEFT_IQ2_XS = 14, WEFT_IQ2_XXS = 15, WEFT_IQ3_S = 16, WEFT_IQ3_XXS = 17, WEFT_TQ1_0 = 20,
+enum { WEFT_Q4_0 = 1, WEFT_Q8_0 = 5, WEFT_Q2_K = 6, WEFT_Q3_K = 7, WEFT_Q4_K = 8, WEFT_Q5_K = 9, WEFT_Q6_K = 10, WEFT_IQ1_S = 11, WEFT_IQ1_M = 12, WEFT_IQ2_S = 13, WEFT_IQ2_XS = 14, WEFT_IQ2_XXS = 15, WEFT_IQ3_S = 16, WEFT_IQ3_XXS = 17, WEFT_TQ1_0 = 20,
        WEFT_Q8_K = 100 };
 
 static enum ggml_type to_type(int fmt) {
@@ -65,6 +65,8 @@ static enum ggml_type to_type(int fmt) {
     case WEFT_IQ2_XS: return GGML_TYPE_IQ2_XS;
     case WEFT_IQ3_XXS: return GGML_TYPE_IQ3_XXS;
     case WEFT_IQ2_S: return GGML_TYPE_IQ2_S;
+    case WEFT_IQ1_S: return GGML_TYPE_IQ1_S;
+    case WEFT_IQ1_M: return GGML_TYPE_IQ1_M;
     case WEFT_IQ3_S: return GGML_TYPE_IQ3_S;
     case WEFT_TQ1_0: return GGML_TYPE_TQ1_0;
     case WEFT_Q8_K: return GGML_TYPE_Q8_K;
@@ -107,6 +109,8 @@ int weft_ref_dequantize(int fmt, const void *w, float *y, int64_t k) {
     case WEFT_IQ2_XS: dequantize_row_iq2_xs((const block_iq2_xs *)w, y, k); return 0;
     case WEFT_IQ3_XXS: dequantize_row_iq3_xxs((const block_iq3_xxs *)w, y, k); return 0;
     case WEFT_IQ2_S: dequantize_row_iq2_s((const block_iq2_s *)w, y, k); return 0;
+    case WEFT_IQ1_S: dequantize_row_iq1_s((const block_iq1_s *)w, y, k); return 0;
+    case WEFT_IQ1_M: dequantize_row_iq1_m((const block_iq1_m *)w, y, k); return 0;
     case WEFT_IQ3_S: dequantize_row_iq3_s((const block_iq3_s *)w, y, k); return 0;
     case WEFT_TQ1_0: dequantize_row_tq1_0((const block_tq1_0 *)w, y, k); return 0;
     default: return -1;
@@ -127,6 +131,8 @@ int weft_ref_vec_dot(int fmt, int64_t k, float *s, const void *w, const void *x)
     case WEFT_IQ2_XS: ggml_vec_dot_iq2_xs_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_IQ3_XXS: ggml_vec_dot_iq3_xxs_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_IQ2_S: ggml_vec_dot_iq2_s_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
+    case WEFT_IQ1_S: ggml_vec_dot_iq1_s_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
+    case WEFT_IQ1_M: ggml_vec_dot_iq1_m_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_IQ3_S: ggml_vec_dot_iq3_s_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     case WEFT_TQ1_0: ggml_vec_dot_tq1_0_q8_K((int)k, s, 0, w, 0, x, 0, 1); return 0;
     default: return -1;
@@ -187,5 +193,12 @@ void weft_ref_iq3s_grid(int8_t *grid) {
     for (int i = 0; i < 512; ++i) {
         const uint8_t *g = (const uint8_t *)(iq3s_grid + i);
         for (int j = 0; j < 4; ++j) grid[i * 4 + j] = (int8_t)g[j];
+    }
+}
+/* iq1s_grid as int8[2048][8] (vec_dot_runtime.cpp:436) */
+void weft_ref_iq1s_grid(int8_t *grid) {
+    for (int i = 0; i < 2048; ++i) {
+        const int8_t *g = (const int8_t *)(iq1s_grid + i);
+        for (int j = 0; j < 8; ++j) grid[i * 8 + j] = g[j];
     }
 }

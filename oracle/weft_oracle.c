@@ -73,6 +73,8 @@ size_t wo_record_bytes(int fmt) {
     case WO_IQ2_XXS: return 66;
     case WO_IQ2_XS: return 74;
     case WO_IQ2_S: return 82;
+    case WO_IQ1_S: return 50;
+    case WO_IQ1_M: return 56;
     case WO_IQ3_S: return 110;
     case WO_IQ3_XXS: return 98;
     case WO_TQ1_0: return 54;
@@ -84,7 +86,7 @@ size_t wo_record_bytes(int fmt) {
 size_t wo_record_elements(int fmt) {
     switch (fmt) {
     case WO_Q4_0: case WO_Q8_0: case WO_Q8_1: return 32;
-    case WO_Q2_K: case WO_Q3_K: case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_IQ2_XS: case WO_IQ3_XXS: case WO_IQ2_S: case WO_IQ3_S: case WO_TQ1_0: case WO_Q8_K: return 256;
+    case WO_Q2_K: case WO_Q3_K: case WO_Q4_K: case WO_Q5_K: case WO_Q6_K: case WO_IQ2_XXS: case WO_IQ2_XS: case WO_IQ3_XXS: case WO_IQ2_S: case WO_IQ3_S: case WO_IQ1_S: case WO_IQ1_M: case WO_TQ1_0: case WO_Q8_K: return 256;
     default: return 0;
     }
 }
@@ -472,7 +474,7 @@ static void wo_quantize_range(int64_t begin, int64_t end, void *p) {
 
 int wo_quantize_rows(int fmt, int rule, const float *x, uint8_t *y, int64_t nrows, int64_t k) {
     wo_quant_ctx c = {fmt, rule, x, y, k, wo_row_bytes(fmt, k)};
-    if (!c.rb || fmt == WO_IQ2_XXS || fmt == WO_IQ2_XS || fmt == WO_IQ3_XXS || fmt == WO_IQ2_S || fmt == WO_IQ3_S) return -1;
+    if (!c.rb || fmt == WO_IQ2_XXS || fmt == WO_IQ2_XS || fmt == WO_IQ3_XXS || fmt == WO_IQ2_S || fmt == WO_IQ3_S || fmt == WO_IQ1_S || fmt == WO_IQ1_M) return -1;
     wo_parallel_for(nrows, wo_quantize_range, &c);
     return 0;
 }
@@ -619,6 +621,51 @@ void wo_dequantize_row_iq3_s(const uint8_t *w, const int8_t *grid, float *y, int
     }
 }
 
+/* ggml/src/ggml-quants.c (dequantize_row_iq1_s); examples/kernels/dequantize/iq1_s.py.
+ * Record (50 bytes): f16 d @0; 32 bytes @2: low 8 bits of the grid index of every 8 weights; 8 u16 @34, one per 32 weights:
+ * bits 0-11 four 3-bit index tops, bits 12-14 scale, bit 15 the sign of the shift 0.125.  Grid values are -1, 0, +1. */
+void wo_dequantize_row_iq1_s(const uint8_t *w, const int8_t *grid, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 50) {
+        const float d = wo_f16_to_f32(ld_u16(w));
+        for (int g = 0; g < 8; ++g) {
+            const uint16_t qh = ld_u16(w + 34 + 2 * g);
+            const float dl = d * (float)(2 * ((qh >> 12) & 7) + 1);
+            const float delta = qh & 0x8000 ? -0.125f : 0.125f;
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *gv = grid + 8 * (w[2 + 4 * g + e] | (((qh >> (3 * e)) & 7) << 8));
+                for (int j = 0; j < 8; ++j) *y++ = dl * ((float)gv[j] + delta);
+            }
+        }
+    }
+}
+
+/* IQ1_M (56 bytes, no d field): 32 index bytes @0; 16 bytes @32, one per 16 weights: low nibble {3 index bits, shift
+ * sign} of the first 8 weights, high nibble of the other 8; 8 bytes @48 read as four u16: bits 0-11 four 3-bit scales
+ * (one per 16 weights), bits 12-15 a nibble of the record's f16 scale.  ggml/src/ggml-quants.c (dequantize_row_iq1_m). */
+static inline float iq1m_scale(const uint8_t *w) {
+    const uint16_t s0 = ld_u16(w + 48), s1 = ld_u16(w + 50), s2 = ld_u16(w + 52), s3 = ld_u16(w + 54);
+    return wo_f16_to_f32((uint16_t)((s0 >> 12) | ((s1 >> 8) & 0x00f0) | ((s2 >> 4) & 0x0f00) | (s3 & 0xf000)));
+}
+static inline int iq1m_index(const uint8_t *w, int g, int e) {
+    const uint8_t qh = w[32 + 2 * g + (e >> 1)];
+    return w[4 * g + e] | (((e & 1 ? qh >> 4 : qh) & 7) << 8);
+}
+static inline int iq1m_negative(const uint8_t *w, int g, int e) { return (w[32 + 2 * g + (e >> 1)] >> (e & 1 ? 7 : 3)) & 1; }
+static inline int iq1m_sub_scale(const uint8_t *w, int g, int half) { return (ld_u16(w + 48 + 2 * (g >> 1)) >> (6 * (g & 1) + 3 * half)) & 7; }
+
+void wo_dequantize_row_iq1_m(const uint8_t *w, const int8_t *grid, float *y, int64_t k) {
+    for (int64_t b = 0; b < k / 256; ++b, w += 56) {
+        const float d = iq1m_scale(w);
+        for (int g = 0; g < 8; ++g)
+            for (int e = 0; e < 4; ++e) {
+                const float dl = d * (float)(2 * iq1m_sub_scale(w, g, e >> 1) + 1);
+                const float delta = iq1m_negative(w, g, e) ? -0.125f : 0.125f;
+                const int8_t *gv = grid + 8 * iq1m_index(w, g, e);
+                for (int j = 0; j < 8; ++j) *y++ = dl * ((float)gv[j] + delta);
+            }
+    }
+}
+
 /* one base-3 digit of a packed byte, digit 0 = most significant:
  * ggml/src/ggml-quants.c:2369-2371; examples/functions/quantization.py:49-64 */
 static inline int tq1_digit(uint8_t packed, int n) {
@@ -659,6 +706,8 @@ static void wo_dequantize_range(int64_t begin, int64_t end, void *p) {
         case WO_IQ2_XS: wo_dequantize_row_iq2_xs(wr, c->grid, c->signs, yr, c->k); break;
         case WO_IQ3_XXS: wo_dequantize_row_iq3_xxs(wr, c->grid, c->signs, yr, c->k); break;
         case WO_IQ2_S: wo_dequantize_row_iq2_s(wr, c->grid, yr, c->k); break;
+        case WO_IQ1_S: wo_dequantize_row_iq1_s(wr, c->grid, yr, c->k); break;
+        case WO_IQ1_M: wo_dequantize_row_iq1_m(wr, c->grid, yr, c->k); break;
         case WO_IQ3_S: wo_dequantize_row_iq3_s(wr, c->grid, yr, c->k); break;
         case WO_TQ1_0: wo_dequantize_row_tq1_0(wr, yr, c->k); break;
         default: break;
@@ -1032,6 +1081,54 @@ float wo_vec_dot_iq3_s_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *gr
     return sumf;
 }
 
+/* ggml/src/ggml-cpu/quants.c (ggml_vec_dot_iq1_s_q8_K_generic); examples/kernels/vec_dot/iq1_s_q8_k.py:51-56: the shift
+ * term uses the activation record's stored sums of 16 */
+float wo_vec_dot_iq1_s_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k) {
+    float sumf = 0.f;
+    for (int64_t b = 0; b < k / 256; ++b, w += 50, x += 292) {
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int sumi = 0, sumi1 = 0;
+        for (int g = 0; g < 8; ++g) {
+            const uint16_t qh = ld_u16(w + 34 + 2 * g);
+            const int ls = 2 * ((qh >> 12) & 7) + 1, delta = qh & 0x8000 ? -1 : 1;
+            int lsum = 0;
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *gv = grid + 8 * (w[2 + 4 * g + e] | (((qh >> (3 * e)) & 7) << 8));
+                for (int j = 0; j < 8; ++j) lsum += xq[32 * g + 8 * e + j] * gv[j];
+            }
+            sumi += ls * lsum;
+            sumi1 += ls * delta * (ld_i16(x + 260 + 4 * g) + ld_i16(x + 260 + 4 * g + 2));
+        }
+        sumf += wo_f16_to_f32(ld_u16(w)) * ld_f32(x) * ((float)sumi + 0.125f * (float)sumi1);
+    }
+    return sumf;
+}
+
+/* ggml/src/ggml-cpu/quants.c (ggml_vec_dot_iq1_m_q8_K_generic); examples/kernels/vec_dot/iq1_m_q8_k.py:73-79: the shift term
+ * uses sums of 8 codes, computed here */
+float wo_vec_dot_iq1_m_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k) {
+    float sumf = 0.f;
+    for (int64_t b = 0; b < k / 256; ++b, w += 56, x += 292) {
+        const int8_t *xq = (const int8_t *)(x + 4);
+        int sumi1 = 0, sumi2 = 0;
+        for (int g = 0; g < 8; ++g) {
+            int sum1[2] = {0, 0}, sum2[2] = {0, 0};
+            for (int e = 0; e < 4; ++e) {
+                const int8_t *gv = grid + 8 * iq1m_index(w, g, e);
+                int lsum1 = 0, lsum2 = 0;
+                for (int j = 0; j < 8; ++j) { lsum1 += xq[32 * g + 8 * e + j] * gv[j]; lsum2 += xq[32 * g + 8 * e + j]; }
+                sum1[e >> 1] += lsum1;
+                sum2[e >> 1] += lsum2 * (iq1m_negative(w, g, e) ? -1 : 1);
+            }
+            const int ls1 = 2 * iq1m_sub_scale(w, g, 0) + 1, ls2 = 2 * iq1m_sub_scale(w, g, 1) + 1;
+            sumi1 += sum1[0] * ls1 + sum1[1] * ls2;
+            sumi2 += sum2[0] * ls1 + sum2[1] * ls2;
+        }
+        sumf += iq1m_scale(w) * ld_f32(x) * ((float)sumi1 + 0.125f * (float)sumi2);
+    }
+    return sumf;
+}
+
 /* ggml/src/ggml-cpu/quants.c:430-480; examples/kernels/vec_dot/tq1_0_q8_k.py:9-55 */
 float wo_vec_dot_tq1_0_q8_K(const uint8_t *w, const uint8_t *x, int64_t k) {
     float sumf = 0.0f;
@@ -1063,6 +1160,8 @@ int wo_vec_dot(int fmt, const uint8_t *w, const uint8_t *x, const int8_t *grid, 
     case WO_IQ2_XS: *out = wo_vec_dot_iq2_xs_q8_K(w, x, grid, signs, k); return 0;
     case WO_IQ3_XXS: *out = wo_vec_dot_iq3_xxs_q8_K(w, x, grid, signs, k); return 0;
     case WO_IQ2_S: *out = wo_vec_dot_iq2_s_q8_K(w, x, grid, k); return 0;
+    case WO_IQ1_S: *out = wo_vec_dot_iq1_s_q8_K(w, x, grid, k); return 0;
+    case WO_IQ1_M: *out = wo_vec_dot_iq1_m_q8_K(w, x, grid, k); return 0;
     case WO_IQ3_S: *out = wo_vec_dot_iq3_s_q8_K(w, x, grid, k); return 0;
     case WO_TQ1_0: *out = wo_vec_dot_tq1_0_q8_K(w, x, k); return 0;
     default: return -1;

@@ -33,6 +33,8 @@ enum wo_format {
     WO_Q3_K = 7,
     WO_Q5_K = 9,
     WO_Q6_K = 10,
+    WO_IQ1_S = 11,
+    WO_IQ1_M = 12,
     WO_IQ2_S = 13,
     WO_IQ2_XS = 14,
     WO_IQ2_XXS = 15,
@@ -76,6 +78,8 @@ void wo_dequantize_row_q5_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_q6_K(const uint8_t *w, float *y, int64_t k);
 void wo_dequantize_row_iq2_xxs(const uint8_t *w, const int8_t *grid, const int8_t *signs, float *y, int64_t k);
 void wo_dequantize_row_iq2_xs(const uint8_t *w, const int8_t *grid /* [512*8] */, const int8_t *signs, float *y, int64_t k);
+void wo_dequantize_row_iq1_s(const uint8_t *w, const int8_t *grid /* [2048*8] */, float *y, int64_t k);
+void wo_dequantize_row_iq1_m(const uint8_t *w, const int8_t *grid /* [2048*8] */, float *y, int64_t k);
 void wo_dequantize_row_iq2_s(const uint8_t *w, const int8_t *grid /* [1024*8] */, float *y, int64_t k);
 void wo_dequantize_row_iq3_s(const uint8_t *w, const int8_t *grid /* [512*4] */, float *y, int64_t k);
 void wo_dequantize_row_iq3_xxs(const uint8_t *w, const int8_t *grid /* [256*4] */, const int8_t *signs, float *y, int64_t k);
@@ -89,6 +93,8 @@ float wo_vec_dot_q8_0_q8_0(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_q4_K_q8_K(const uint8_t *w, const uint8_t *x, int64_t k);
 float wo_vec_dot_iq2_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k);
 float wo_vec_dot_iq2_xs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k);
+float wo_vec_dot_iq1_s_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k);
+float wo_vec_dot_iq1_m_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k);
 float wo_vec_dot_iq2_s_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k);
 float wo_vec_dot_iq3_s_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, int64_t k);
 float wo_vec_dot_iq3_xxs_q8_K(const uint8_t *w, const uint8_t *x, const int8_t *grid, const int8_t *signs, int64_t k);

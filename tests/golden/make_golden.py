@@ -30,9 +30,9 @@ sys.path.insert(0, str(ROOT))
 import oracle as o  # noqa: E402
 
 # new formats go last: the seeded generator is consumed in this order
-FORMATS = {"q4_0": o.Q4_0, "q8_0": o.Q8_0, "q4_k": o.Q4_K, "iq2_xxs": o.IQ2_XXS, "tq1_0": o.TQ1_0, "q6_k": o.Q6_K, "q5_k": o.Q5_K, "q2_k": o.Q2_K, "q3_k": o.Q3_K, "iq2_xs": o.IQ2_XS, "iq3_xxs": o.IQ3_XXS, "iq2_s": o.IQ2_S, "iq3_s": o.IQ3_S}
-VEC_DOT_IDS = {"q4_0": 1, "q8_0": 5, "q4_k": 8, "iq2_xxs": 15, "tq1_0": 20, "q6_k": 10, "q5_k": 9, "q2_k": 6, "q3_k": 7, "iq2_xs": 14, "iq3_xxs": 17, "iq2_s": 13, "iq3_s": 16}    # vec_dot / dequantize harness ids
-MUL_MAT_IDS = {"q4_0": 2, "q8_0": 6, "q4_k": 9, "iq2_xxs": 16, "tq1_0": 21, "q6_k": 11, "q5_k": 10, "q2_k": 7, "q3_k": 8, "iq2_xs": 15, "iq3_xxs": 18, "iq2_s": 14, "iq3_s": 17}    # mul_mat harness ids
+FORMATS = {"q4_0": o.Q4_0, "q8_0": o.Q8_0, "q4_k": o.Q4_K, "iq2_xxs": o.IQ2_XXS, "tq1_0": o.TQ1_0, "q6_k": o.Q6_K, "q5_k": o.Q5_K, "q2_k": o.Q2_K, "q3_k": o.Q3_K, "iq2_xs": o.IQ2_XS, "iq3_xxs": o.IQ3_XXS, "iq2_s": o.IQ2_S, "iq3_s": o.IQ3_S, "iq1_s": o.IQ1_S, "iq1_m": o.IQ1_M}
+VEC_DOT_IDS = {"q4_0": 1, "q8_0": 5, "q4_k": 8, "iq2_xxs": 15, "tq1_0": 20, "q6_k": 10, "q5_k": 9, "q2_k": 6, "q3_k": 7, "iq2_xs": 14, "iq3_xxs": 17, "iq2_s": 13, "iq3_s": 16, "iq1_s": 11, "iq1_m": 12}    # vec_dot / dequantize harness ids
+MUL_MAT_IDS = {"q4_0": 2, "q8_0": 6, "q4_k": 9, "iq2_xxs": 16, "tq1_0": 21, "q6_k": 11, "q5_k": 10, "q2_k": 7, "q3_k": 8, "iq2_xs": 15, "iq3_xxs": 18, "iq2_s": 14, "iq3_s": 17, "iq1_s": 12, "iq1_m": 13}    # mul_mat harness ids
 
 
 def closed_form_weights(count: int, fmt_id: int) -> np.ndarray:
@@ -61,6 +61,7 @@ def main() -> None:
     out["iq3xxs_grid"] = o.ref_iq3xxs_grid()
     out["iq2s_grid"] = o.ref_iq2s_grid()
     out["iq3s_grid"] = o.ref_iq3s_grid()
+    out["iq1s_grid"] = o.ref_iq1s_grid()
     check = np.random.MT19937(); check._legacy_seeding(5489)
     assert int(check.random_raw(1)[0]) == 3499211612
 

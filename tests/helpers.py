@@ -95,10 +95,14 @@ def weights(fmt: int, rng: np.random.Generator, n: int, k: int) -> np.ndarray:
         if o.ref_available() and n * k <= 1 << 22:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
         return random_iq2_xxs(rng, n, k)
-    if fmt in (o.IQ2_XS, o.IQ3_XXS, o.IQ2_S, o.IQ3_S):
+    if fmt in (o.IQ2_XS, o.IQ3_XXS, o.IQ2_S, o.IQ3_S, o.IQ1_S, o.IQ1_M):
         if o.ref_available() and n * k <= 1 << 21:
             return o.ref_quantize_weights(fmt, (rng.standard_normal((n, k)) * 0.02).astype(np.float32))
-        if fmt in (o.IQ2_S, o.IQ3_S):
+        if fmt == o.IQ1_M:          # the f16 scale is spread over the top nibbles of the last eight bytes: 0x2xxx is a small normal number
+            rec = rng.integers(0, 256, size=(n, k // 256, 56), dtype=np.uint8)
+            rec[:, :, 55] = (rec[:, :, 55] & 0x0f) | 0x20
+            return rec.reshape(n, -1)
+        if fmt in (o.IQ2_S, o.IQ3_S, o.IQ1_S):
             return random_codebook_records(rng, n, k, o.RECORD_BYTES[fmt])
         return random_iq2_xs(rng, n, k) if fmt == o.IQ2_XS else random_iq3_xxs(rng, n, k)
     if fmt in (o.Q2_K, o.Q3_K, o.Q5_K, o.Q6_K):
@@ -118,5 +122,5 @@ def activations(rng: np.random.Generator, m: int, k: int) -> np.ndarray:
 
 def tables(golden: dict, name: str = "iq2_xxs"):
     """The codebook and the sign table a format's kernels take as arguments (the sign table is the same for all three)."""
-    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid", "iq2_s": "iq2s_grid", "iq3_s": "iq3s_grid"}.get(name.lower(), "iq2xxs_grid")
+    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid", "iq2_s": "iq2s_grid", "iq3_s": "iq3s_grid", "iq1_s": "iq1s_grid", "iq1_m": "iq1s_grid"}.get(name.lower(), "iq2xxs_grid")
     return golden[grid], golden["iq2xxs_signs"]

@@ -16,8 +16,9 @@ from helpers import TQ1_POWERS, activations, random_iq2_xxs, reference_tolerance
 pytestmark = pytest.mark.gpu
 
 DECODE_FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k"]   # have a production_mul_mat_<fmt>_decode
-FORMATS = DECODE_FORMATS + ["iq2_xs", "iq3_xxs", "iq2_s", "iq3_s"]
-CODEBOOKS = {"iq2_xxs": (256, 8, "I8X8"), "iq2_xs": (512, 8, "I8X8"), "iq3_xxs": (256, 4, "I8X4"), "iq2_s": (1024, 8, "I8X8"), "iq3_s": (512, 4, "I8X4")}
+FORMATS = DECODE_FORMATS + ["iq2_xs", "iq3_xxs", "iq2_s", "iq3_s", "iq1_s", "iq1_m"]
+CODEBOOKS = {"iq2_xxs": (256, 8, "I8X8"), "iq2_xs": (512, 8, "I8X8"), "iq3_xxs": (256, 4, "I8X4"), "iq2_s": (1024, 8, "I8X8"), "iq3_s": (512, 4, "I8X4"),
+             "iq1_s": (2048, 8, "I8X8"), "iq1_m": (2048, 8, "I8X8")}
 SIGN_TABLE = ("iq2_xxs", "iq2_xs", "iq3_xxs")     # the other codebook formats carry their sign bits in the record
 REL_L2_BOUND = 1e-5
 
@@ -48,6 +49,9 @@ def _fmt(oracle, name):
 
 def _table_args(torch, golden, name):
     grid, signs = tables(golden, name)
+    if name == "iq1_m":      # the reference passes the f16 -> f32 conversion as a table of 65536 floats
+        f16_bits = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float32)
+        return [dev(torch, grid), dev(torch, f16_bits)]
     if name in CODEBOOKS:
         return [dev(torch, grid), dev(torch, signs)] if name in SIGN_TABLE else [dev(torch, grid)]
     if name == "tq1_0":
@@ -63,6 +67,8 @@ def _wrap_tables(weft, name, tensors, dequant=False):
             return tensors
         entries, width, encoding = CODEBOOKS[name]
         wrapped = [Buffer(tensors[0], shape=(entries, width), encoding=encoding)]
+        if name == "iq1_m":
+            return wrapped + [tensors[1]]
         return wrapped + ([Buffer(tensors[1], shape=(128, 8), encoding="I8X8")] if name in SIGN_TABLE else [])
     if name == "tq1_0":
         return [Buffer(tensors[0], shape=(5,), encoding="dense.u32")]
@@ -249,7 +255,9 @@ def test_vec_dot_rows_against_oracle(torch, weft, oracle, golden, name, shape):
 # ------------------------------------------------------------------ mul_mat (decode)
 
 @pytest.mark.parametrize("symbol", ["production_mul_mat_iq2_xs", "production_mul_mat_iq2_xs_staged", "production_mul_mat_iq3_xxs", "production_mul_mat_iq2_xxs",
-                                    "production_mul_mat_iq2_s", "production_mul_mat_iq2_s_staged", "production_mul_mat_iq3_s"])
+                                    "production_mul_mat_iq2_s", "production_mul_mat_iq2_s_staged", "production_mul_mat_iq3_s",
+                                    "production_mul_mat_iq1_s", "production_mul_mat_iq1_s_decode", "production_mul_mat_iq1_m",
+                                    "production_mul_mat_iq1_m_decode", "production_mul_mat_iq1_m_lane16_decode"])
 @pytest.mark.parametrize("mnk", [(1, 512, 2048), (3, 200, 1024), (40, 96, 4096), (1, 4096, 4096)])
 def test_mul_mat_codebook_formats(torch, weft, oracle, golden, symbol, mnk):
     """The mul_mat symbols of IQ2_XS, IQ3_XXS and the unstaged IQ2_XXS name: K = 1024 leaves rows that are not whole
@@ -257,7 +265,7 @@ def test_mul_mat_codebook_formats(torch, weft, oracle, golden, symbol, mnk):
     from weft_b200.kernels import mul_mat
     from weft_b200.runtime import Buffer
 
-    name = symbol[len("production_mul_mat_"):].removesuffix("_staged")
+    name = symbol[len("production_mul_mat_"):].removesuffix("_staged").removesuffix("_decode").removesuffix("_lane16")
     fmt = _fmt(oracle, name)
     m, n, k = mnk
     rng = np.random.default_rng(11 * fmt + m + n + k)

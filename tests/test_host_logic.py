@@ -72,7 +72,7 @@ def test_kernel_abi_follows_the_reference_rules():
     deq = registry.resolve(dequantize.row_dequantize_tq1_0)
     assert [a["encoding"] for a in deq["arguments"]] == ["TQ1_0", "dense.u32", "dense.f32"]
     assert deq["arguments"][1]["shape"] == ["5"] and deq["shape_parameters"] == ["K"]
-    assert len(registry.supported_symbols()) == 91
+    assert len(registry.supported_symbols()) == 105
 
 
 _EXTRA_KERNELS = """

@@ -9,11 +9,11 @@ from __future__ import annotations
 import numpy as np
 import pytest
 
-FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k", "iq2_xs", "iq3_xxs", "iq2_s", "iq3_s"]
+FORMATS = ["q4_0", "q8_0", "q4_k", "iq2_xxs", "tq1_0", "q6_k", "q5_k", "q2_k", "q3_k", "iq2_xs", "iq3_xxs", "iq2_s", "iq3_s", "iq1_s", "iq1_m"]
 
 
 def _tables(golden, name):
-    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid", "iq2_s": "iq2s_grid", "iq3_s": "iq3s_grid"}.get(name, "iq2xxs_grid")
+    grid = {"iq2_xs": "iq2xs_grid", "iq3_xxs": "iq3xxs_grid", "iq2_s": "iq2s_grid", "iq3_s": "iq3s_grid", "iq1_s": "iq1s_grid", "iq1_m": "iq1s_grid"}.get(name, "iq2xxs_grid")
     return golden[grid], golden["iq2xxs_signs"]
 K = 1024
 
@@ -129,12 +129,13 @@ def test_live_against_compiled_reference(oracle, golden, name):
     if name == "tq1_0":
         src = (rng.integers(-1, 2, size=(n, k)) * np.float32(0.031)).astype(np.float32)
     w = oracle.ref_quantize_weights(fmt, src)
-    if name not in ("iq2_xxs", "q6_k", "q5_k", "q2_k", "q3_k", "iq2_xs", "iq3_xxs", "iq2_s", "iq3_s"):   # the port has no quantizer for these weight formats
+    if name not in ("iq2_xxs", "q6_k", "q5_k", "q2_k", "q3_k", "iq2_xs", "iq3_xxs", "iq2_s", "iq3_s", "iq1_s", "iq1_m"):   # the port has no quantizer for these weight formats
         assert np.array_equal(oracle.quantize(fmt, src), w)
     grid, signs = oracle.ref_iq2xxs_tables()
     assert np.array_equal(grid, golden["iq2xxs_grid"])
     assert np.array_equal(oracle.ref_iq2xs_grid(), golden["iq2xs_grid"]) and np.array_equal(oracle.ref_iq3xxs_grid(), golden["iq3xxs_grid"])
     assert np.array_equal(oracle.ref_iq2s_grid(), golden["iq2s_grid"]) and np.array_equal(oracle.ref_iq3s_grid(), golden["iq3s_grid"])
+    assert np.array_equal(oracle.ref_iq1s_grid(), golden["iq1s_grid"])
     grid, signs = _tables(golden, name)
     x = rng.standard_normal((m, k)).astype(np.float32)
     assert np.array_equal(_bits(oracle.dequantize(fmt, w, k, grid, signs)), _bits(oracle.ref_dequantize(fmt, w, k)))

@@ -223,7 +223,7 @@ int launched(cudaError_t e, const char *what, unsigned count = 1) {
 
 // bytes of the codebook a format's kernels take as an argument (int8[256][8], int8[512][8], int8[256][4]); the sign
 // table is int8[128][8] for all three
-size_t codebook_bytes(int fmt) { return fmt == F_IQ2_XXS ? 2048 : fmt == F_IQ2_XS ? 4096 : fmt == F_IQ3_XXS ? 1024 : fmt == F_IQ2_S ? 8192 : fmt == F_IQ3_S ? 2048 : 0; }
+size_t codebook_bytes(int fmt) { return fmt == F_IQ2_XXS ? 2048 : fmt == F_IQ2_XS ? 4096 : fmt == F_IQ3_XXS ? 1024 : fmt == F_IQ2_S ? 8192 : fmt == F_IQ3_S ? 2048 : (fmt == F_IQ1_S || fmt == F_IQ1_M) ? 16384 : 0; }
 // IQ2_S and IQ3_S carry their sign bits in the record
 bool has_sign_table(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS; }
 
@@ -234,9 +234,10 @@ int do_dequantize(int fmt, const void *W, const int8_t *grid, const int8_t *sign
     Call call;
     void *w, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
     if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
-    if (fmt == F_Q6_K && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
+    if ((fmt == F_Q6_K || fmt == F_IQ1_M) && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
     if (codebook_bytes(fmt) && (call.map(grid, codebook_bytes(fmt), true, false, &gr) || (has_sign_table(fmt) && call.map(signs, 1024, true, false, &sg)))) return 1;
     if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
+    if (fmt == F_IQ1_M && call.map(powers, 65536 * sizeof(float), true, false, &pw)) return 1;   // the caller's float[65536] table of f16 bit patterns
     if (call.map(Y, N * K * sizeof(float), false, true, &y)) return 1;
     if (launched(launch_dequantize(fmt, w, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw, (float *)y,
                                    (long long)(N * K), g.prop.multiProcessorCount, g.stream), "row_dequantize"))
@@ -274,7 +275,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     Call call;
     void *w, *x = nullptr, *xq, *y, *gr = nullptr, *sg = nullptr, *pw = nullptr;
     if (call.map(W, N * row_bytes(fmt, K), true, false, &w)) return 1;
-    if (fmt == F_Q6_K && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
+    if ((fmt == F_Q6_K || fmt == F_IQ1_M) && (reinterpret_cast<uintptr_t>(w) & 1u) && call.realign(&w, N * row_bytes(fmt, K))) return 1;
     if (!have_xq && call.map(X, M * K * sizeof(float), true, false, &x)) return 1;
     // Decode quantizes X inside the GEMV (its first CTA stores the records, nobody loads them again), so a pinned Xq can
     // be written in place; a call that may take the tensor-core path or the separate quantize kernel reads Xq back.
@@ -283,6 +284,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     if (call.map(Xq, M * row_bytes(act, K), have_xq, !have_xq, &xq, xq_in_place)) return 1;
     if (codebook_bytes(fmt) && (call.map(grid, codebook_bytes(fmt), true, false, &gr) || (has_sign_table(fmt) && call.map(signs, 1024, true, false, &sg)))) return 1;
     if (fmt == F_TQ1_0 && call.map(powers, 20, true, false, &pw)) return 1;
+    if (fmt == F_IQ1_M && call.map(powers, 65536 * sizeof(float), true, false, &pw)) return 1;   // the caller's float[65536] table of f16 bit patterns
     // a host Y with a pitch is staged whole (pitch * M floats); device Y is written in place; a small pinned Y too
     const size_t y_floats = (M - 1) * ldy + N;
     if (call.map(Y, y_floats * sizeof(float), ldy != N, true, &y, ldy == N && gather == nullptr)) return 1;
@@ -435,6 +437,11 @@ VEC_DOT(quantized_vec_dot_iq3_xxs_q8_k, F_IQ3_XXS, IQ_TABLES, grid, signs, nullp
 #define GRID_ONLY , const int8_t *grid
 VEC_DOT(quantized_vec_dot_iq2_s_q8_k, F_IQ2_S, GRID_ONLY, grid, nullptr, nullptr)
 VEC_DOT(quantized_vec_dot_iq3_s_q8_k, F_IQ3_S, GRID_ONLY, grid, nullptr, nullptr)
+VEC_DOT(quantized_vec_dot_iq1_s_q8_k, F_IQ1_S, GRID_ONLY, grid, nullptr, nullptr)
+// IQ1_M: the reference passes a float[65536] table of f16 bit patterns; it travels in the slot of the TQ1_0 powers
+#define IQ1M_TABLES , const int8_t *grid, const float *f16_bits
+VEC_DOT(quantized_vec_dot_iq1_m_q8_k, F_IQ1_M, IQ1M_TABLES, grid, nullptr, reinterpret_cast<const uint32_t *>(f16_bits))
+VEC_DOT(quantized_vec_dot_iq1_m_q8_k_lane16, F_IQ1_M, IQ1M_TABLES, grid, nullptr, reinterpret_cast<const uint32_t *>(f16_bits))
 VEC_DOT(quantized_vec_dot_tq1_0_q8_k, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
 // The reference's second statement of the same dot product with sixteen-wide partial sums (a vector-length plan of
 // its target; the integer sum per block, and so every result bit, is the same): examples/kernels/vec_dot/tq1_0_q8_k_lane16.py:9-54
@@ -456,6 +463,8 @@ DEQUANT(row_dequantize_iq2_xs, F_IQ2_XS, IQ_TABLES, grid, signs, nullptr)
 DEQUANT(row_dequantize_iq3_xxs, F_IQ3_XXS, IQ_TABLES, grid, signs, nullptr)
 DEQUANT(row_dequantize_iq2_s, F_IQ2_S, GRID_ONLY, grid, nullptr, nullptr)
 DEQUANT(row_dequantize_iq3_s, F_IQ3_S, GRID_ONLY, grid, nullptr, nullptr)
+DEQUANT(row_dequantize_iq1_s, F_IQ1_S, GRID_ONLY, grid, nullptr, nullptr)
+DEQUANT(row_dequantize_iq1_m, F_IQ1_M, IQ1M_TABLES, grid, nullptr, reinterpret_cast<const uint32_t *>(f16_bits))
 DEQUANT(row_dequantize_tq1_0, F_TQ1_0, TQ_TABLES, nullptr, nullptr, powers)
 
 // ---- quantize
@@ -504,6 +513,13 @@ MUL_MAT(production_mul_mat_iq3_xxs, F_IQ3_XXS, 1, IQ_TABLES, grid, signs, nullpt
 MUL_MAT(production_mul_mat_iq2_s, F_IQ2_S, 1, GRID_ONLY, grid, nullptr, nullptr)
 MUL_MAT(production_mul_mat_iq2_s_staged, F_IQ2_S, 1, GRID_ONLY, grid, nullptr, nullptr)
 MUL_MAT(production_mul_mat_iq3_s, F_IQ3_S, 1, GRID_ONLY, grid, nullptr, nullptr)
+// IQ1_S (examples/kernels/mul_mat/iq1_s.py:9-15, iq1_s_decode.py:10-16) and IQ1_M (iq1_m.py:10-17, iq1_m_decode.py:10-17,
+// iq1_m_lane16_decode.py:10-17)
+MUL_MAT(production_mul_mat_iq1_s, F_IQ1_S, 1, GRID_ONLY, grid, nullptr, nullptr)
+MUL_MAT(production_mul_mat_iq1_s_decode, F_IQ1_S, 0, GRID_ONLY, grid, nullptr, nullptr)
+MUL_MAT(production_mul_mat_iq1_m, F_IQ1_M, 1, IQ1M_TABLES, grid, nullptr, reinterpret_cast<const uint32_t *>(f16_bits))
+MUL_MAT(production_mul_mat_iq1_m_decode, F_IQ1_M, 0, IQ1M_TABLES, grid, nullptr, reinterpret_cast<const uint32_t *>(f16_bits))
+MUL_MAT(production_mul_mat_iq1_m_lane16_decode, F_IQ1_M, 0, IQ1M_TABLES, grid, nullptr, reinterpret_cast<const uint32_t *>(f16_bits))
 
 // ---- persistent interleaved layout Q4K_I[16]: artifact functions and the kernels that consume it
 static size_t q4ki_packed_size(size_t rows, size_t K) { return K % 256 == 0 && rows % 16 == 0 ? rows * (K / 256) * 144 : 0; }
@@ -655,7 +671,7 @@ int weft_b200_mul_mat_shard_gather(int format, int mode, const uint8_t *W_local,
                                    float *const *Y_ranks, int *const *sync_ranks, void *const *stage_ranks, int world, int rank,
                                    size_t n0, size_t N_local, size_t N, size_t K, size_t M, unsigned flags) {
     if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K &&
-        format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_IQ2_S && format != F_IQ3_S && format != F_TQ1_0 && format != F_Q4_K_I16)
+        format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_IQ2_S && format != F_IQ3_S && format != F_IQ1_S && format != F_IQ1_M && format != F_TQ1_0 && format != F_Q4_K_I16)
         return fail("unknown weight format id %d", format);
     if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
     if (world < 2 || world > GATHER_MAX_RANKS || rank < 0 || rank >= world) return fail("world %d / rank %d out of range (2..%d ranks)", world, rank, GATHER_MAX_RANKS);
@@ -683,7 +699,7 @@ int weft_b200_mul_mat_shard_gather(int format, int mode, const uint8_t *W_local,
 int weft_b200_mul_mat_shard(int format, int mode, const uint8_t *W_local, const float *X, uint8_t *Xq,
                             const int8_t *grid, const int8_t *signs, const uint32_t *powers,
                             float *Y_columns, size_t N_local, size_t K, size_t M, size_t ldy, unsigned flags) {
-    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K && format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_IQ2_S && format != F_IQ3_S && format != F_TQ1_0 && format != F_Q4_K_I16)
+    if (format != F_Q4_0 && format != F_Q8_0 && format != F_Q2_K && format != F_Q3_K && format != F_Q4_K && format != F_Q5_K && format != F_Q6_K && format != F_IQ2_XXS && format != F_IQ2_XS && format != F_IQ3_XXS && format != F_IQ2_S && format != F_IQ3_S && format != F_IQ1_S && format != F_IQ1_M && format != F_TQ1_0 && format != F_Q4_K_I16)
         return fail("unknown weight format id %d", format);
     if (mode != 0 && mode != 1) return fail("mode must be 0 (decode) or 1 (prefill)");
     return do_mul_mat(format, mode, W_local, X, Xq, grid, signs, powers, Y_columns, N_local, K, M, ldy, flags, false);

@@ -12,11 +12,11 @@
 
 namespace weft {
 
-enum Format : int { F_Q4_0 = 1, F_Q8_0 = 5, F_Q2_K = 6, F_Q3_K = 7, F_Q4_K = 8, F_Q5_K = 9, F_Q6_K = 10, F_IQ2_S = 13, F_IQ2_XS = 14, F_IQ2_XXS = 15, F_IQ3_S = 16, F_IQ3_XXS = 17, F_TQ1_0 = 20, F_Q8_K = 100, F_Q8_1 = 101,
+enum Format : int { F_Q4_0 = 1, F_Q8_0 = 5, F_Q2_K = 6, F_Q3_K = 7, F_Q4_K = 8, F_Q5_K = 9, F_Q6_K = 10, F_IQ1_S = 11, F_IQ1_M = 12, F_IQ2_S = 13, F_IQ2_XS = 14, F_IQ2_XXS = 15, F_IQ3_S = 16, F_IQ3_XXS = 17, F_TQ1_0 = 20, F_Q8_K = 100, F_Q8_1 = 101,
                     F_Q4_K_I16 = 1008 /* Q4_K records, 16 rows byte-interleaved (derived Encoding Q4K_I[16]) */ };
 
 __host__ __device__ constexpr int record_bytes(int fmt) {
-    return fmt == F_Q4_0 ? 18 : fmt == F_Q8_0 ? 34 : (fmt == F_Q4_K || fmt == F_Q4_K_I16) ? 144 : fmt == F_Q2_K ? 84 : fmt == F_Q3_K ? 110 : fmt == F_Q5_K ? 176 : fmt == F_Q6_K ? 210 : fmt == F_IQ2_XXS ? 66 : fmt == F_IQ2_XS ? 74 : fmt == F_IQ3_XXS ? 98 : fmt == F_IQ2_S ? 82 : fmt == F_IQ3_S ? 110
+    return fmt == F_Q4_0 ? 18 : fmt == F_Q8_0 ? 34 : (fmt == F_Q4_K || fmt == F_Q4_K_I16) ? 144 : fmt == F_Q2_K ? 84 : fmt == F_Q3_K ? 110 : fmt == F_Q5_K ? 176 : fmt == F_Q6_K ? 210 : fmt == F_IQ2_XXS ? 66 : fmt == F_IQ2_XS ? 74 : fmt == F_IQ3_XXS ? 98 : fmt == F_IQ2_S ? 82 : fmt == F_IQ3_S ? 110 : fmt == F_IQ1_S ? 50 : fmt == F_IQ1_M ? 56
          : fmt == F_TQ1_0 ? 54 : fmt == F_Q8_K ? 292 : fmt == F_Q8_1 ? 36 : 0;
 }
 __host__ __device__ constexpr int record_elements(int fmt) {

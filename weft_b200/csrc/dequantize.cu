@@ -314,6 +314,52 @@ __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq3_s_kernel(const uint
     }
 }
 
+// ---- IQ1_S (examples/kernels/dequantize/iq1_s.py, GGML dequantize_row_iq1_s): (d * (2 s + 1)) * (grid + delta), delta = +-0.125
+//      per 32 weights; lane = (group g, entry e); the 16 KB grid (values -1, 0, +1) is read through the read-only cache
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq1_s_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                                                       float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, e = lane & 3;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 50;
+        const uint32_t qh = ld_u16(rec + 34 + 2 * g);
+        const float dl = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)(int)(2u * ((qh >> 12) & 7u) + 1u));
+        const float delta = qh & 0x8000u ? -0.125f : 0.125f;
+        const uint2 gv = __ldg(reinterpret_cast<const uint2 *>(grid) + (rec[2 + 4 * g + e] | (((qh >> (3 * e)) & 7u) << 8)));
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(dl, __fadd_rn((float)(int)(int8_t)((i < 4 ? gv.x : gv.y) >> (8 * (i & 3))), delta));
+        float *out = y + u * 256 + 32 * g + 8 * e;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
+// ---- IQ1_M (examples/kernels/dequantize/iq1_m.py:18-23, GGML dequantize_row_iq1_m): as IQ1_S with a scale per 16 weights, a
+//      shift sign per 8 and the record's f16 scale spread over the top nibbles of four u16; f16_table is the caller's
+//      float[65536] table of f16 bit patterns
+__global__ void __launch_bounds__(DQ_WARPS * 32) dequant_iq1_m_kernel(const uint8_t *__restrict__ w, const int8_t *__restrict__ grid,
+                                                                       const float *__restrict__ f16_table, float *__restrict__ y, long long units) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2, e = lane & 3;
+    for (long long u = (long long)blockIdx.x * DQ_WARPS + (threadIdx.x >> 5); u < units; u += (long long)gridDim.x * DQ_WARPS) {
+        const uint8_t *rec = w + u * 56;
+        const uint32_t s0 = ld_u16(rec + 48), s1 = ld_u16(rec + 50), s2 = ld_u16(rec + 52), s3 = ld_u16(rec + 54);
+        const float d = __ldg(f16_table + ((s0 >> 12) | ((s1 >> 8) & 0x00f0u) | ((s2 >> 4) & 0x0f00u) | (s3 & 0xf000u)));
+        const uint32_t sc = ld_u16(rec + 48 + 2 * (g >> 1)), qh = rec[32 + 2 * g + (e >> 1)];
+        const uint32_t nib = e & 1 ? qh >> 4 : qh & 15u;
+        const float dl = __fmul_rn(d, (float)(int)(2u * ((sc >> (6 * (g & 1) + 3 * (e >> 1))) & 7u) + 1u));
+        const float delta = nib & 8u ? -0.125f : 0.125f;
+        const uint2 gv = __ldg(reinterpret_cast<const uint2 *>(grid) + (rec[4 * g + e] | ((nib & 7u) << 8)));
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __fmul_rn(dl, __fadd_rn((float)(int)(int8_t)((i < 4 ? gv.x : gv.y) >> (8 * (i & 3))), delta));
+        float *out = y + u * 256 + 32 * g + 8 * e;
+        st4(out, v[0], v[1], v[2], v[3]);
+        st4(out + 4, v[4], v[5], v[6], v[7]);
+    }
+}
+
 // ---- TQ1_0: every lane produces 8 consecutive outputs; lanes 0-19 region 0 (5 digits x 32 bytes),
 //      20-29 region 1 (5 digits x 16 bytes), 30-31 region 2 (4 digits x 4 bytes)
 __global__ void __launch_bounds__(DQ_WARPS * 32) dequant_tq1_0_kernel(const uint8_t *__restrict__ w, const uint32_t *__restrict__ powers,
@@ -474,6 +520,23 @@ __global__ void dequant_elementwise_kernel(int fmt, const uint8_t *__restrict__ 
             const float db = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)(1 + 2 * (int)(g & 1 ? sc >> 4 : sc & 15u)));
             const uint32_t index = rec[2 + 8 * g + ix] | ((((uint32_t)rec[66 + g] >> ix) & 1u) << 8);
             v = __fmul_rn(__fmul_rn(db, (float)(int)(uint8_t)grid[4 * index + (l & 3)]), (rec[74 + 4 * g + en] >> l) & 1 ? -1.f : 1.f);
+        } else if (fmt == F_IQ1_S) {
+            const uint8_t *rec = w + (i / 256) * 50;
+            const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8;
+            const uint32_t qh = ld_u16(rec + 34 + 2 * g);
+            const float dl = __fmul_rn(half_bits_to_float(ld_u16(rec)), (float)(int)(2u * ((qh >> 12) & 7u) + 1u));
+            const int gvl = grid[8 * (rec[2 + 4 * g + en] | (((qh >> (3 * en)) & 7u) << 8)) + l];
+            v = __fmul_rn(dl, __fadd_rn((float)gvl, qh & 0x8000u ? -0.125f : 0.125f));
+        } else if (fmt == F_IQ1_M) {
+            const uint8_t *rec = w + (i / 256) * 56;
+            const int e = (int)(i % 256), g = e / 32, en = (e % 32) / 8, l = e % 8;
+            const uint32_t s0 = rec[48] | (rec[49] << 8), s1 = rec[50] | (rec[51] << 8), s2 = rec[52] | (rec[53] << 8), s3 = rec[54] | (rec[55] << 8);
+            const float d = reinterpret_cast<const float *>(powers)[(s0 >> 12) | ((s1 >> 8) & 0x00f0u) | ((s2 >> 4) & 0x0f00u) | (s3 & 0xf000u)];
+            const uint32_t sc = rec[48 + 2 * (g >> 1)] | (rec[49 + 2 * (g >> 1)] << 8), qh = rec[32 + 2 * g + (en >> 1)];
+            const uint32_t nib = en & 1 ? qh >> 4 : qh & 15u;
+            const float dl = __fmul_rn(d, (float)(int)(2u * ((sc >> (6 * (g & 1) + 3 * (en >> 1))) & 7u) + 1u));
+            const int gvl = grid[8 * (rec[4 * g + en] | ((nib & 7u) << 8)) + l];
+            v = __fmul_rn(dl, __fadd_rn((float)gvl, nib & 8u ? -0.125f : 0.125f));
         } else if (fmt == F_TQ1_0) {
             const uint8_t *rec = w + (i / 256) * 54;
             const int e = (int)(i % 256);
@@ -559,6 +622,16 @@ cudaError_t launch_dequantize(int fmt, const void *w, const int8_t *grid, const 
     case F_IQ3_S: {
         const long long units = elements / 256;
         dequant_iq3_s_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, y, units);
+        break;
+    }
+    case F_IQ1_S: {
+        const long long units = elements / 256;
+        dequant_iq1_s_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, y, units);
+        break;
+    }
+    case F_IQ1_M: {
+        const long long units = elements / 256;
+        dequant_iq1_m_kernel<<<dq_grid(units, sm_count), DQ_WARPS * 32, 0, stream>>>(wb, grid, reinterpret_cast<const float *>(powers), y, units);
         break;
     }
     case F_Q6_K: {

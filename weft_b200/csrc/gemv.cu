@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
     uint8_t *cursor = smem + 16 + 48 * warps;
     uint8_t *s_tab0 = cursor, *s_tab1 = cursor;
     // codebook formats: the grid as given, then the sign table as byte masks (1 KB)
-    constexpr int GRID_BYTES = FMT == F_IQ2_XXS ? 2048 : FMT == F_IQ2_XS ? 4096 : FMT == F_IQ3_XXS ? 1024 : FMT == F_IQ2_S ? 8192 : FMT == F_IQ3_S ? 2048 : 0;
+    constexpr int GRID_BYTES = FMT == F_IQ2_XXS ? 2048 : FMT == F_IQ2_XS ? 4096 : FMT == F_IQ3_XXS ? 1024 : FMT == F_IQ2_S ? 8192 : FMT == F_IQ3_S ? 2048 : (FMT == F_IQ1_S || FMT == F_IQ1_M) ? 16384 : 0;
     constexpr bool SIGN_TABLE = FMT == F_IQ2_XXS || FMT == F_IQ2_XS || FMT == F_IQ3_XXS;
     if (GRID_BYTES) { s_tab1 = cursor + GRID_BYTES; cursor += GRID_BYTES + (SIGN_TABLE ? 1024 : 0); }
     uint8_t *s_xq = cursor;
@@ -184,6 +184,8 @@ __global__ void __launch_bounds__(512) gemv_kernel(const GemvParams p) {
             else if (FMT == F_IQ3_XXS) dot_iq3_xxs<RL>(wp, xu, xa, s_tab0, s_tab1, acc);
             else if (FMT == F_IQ2_S) dot_iq2_s<RL>(wp, xu, xa, s_tab0, acc);
             else if (FMT == F_IQ3_S) dot_iq3_s<RL>(wp, xu, xa, s_tab0, acc);
+            else if (FMT == F_IQ1_S) dot_iq1_s<RL>(wp, xu, xa, s_tab0, acc);
+            else if (FMT == F_IQ1_M) dot_iq1_m<RL>(wp, xu, xa, s_tab0, reinterpret_cast<const float *>(p.powers), acc);
             else dot_tq1_0<RL>(wp, xu, xa, pw, acc);
         }
 #pragma unroll
@@ -263,7 +265,7 @@ static cudaError_t launch_fmt(const GemvArgs &a, int sm_count, cudaStream_t stre
     int warps = kEnvWarps;
     warps = warps < 1 ? 1 : (warps > 16 ? 16 : warps);
     int rl = kEnvRowsPerLane;
-    const long long x_bytes = (long long)nb * (XQ_PITCH + XAUX_BYTES) + (FMT == F_IQ2_XXS ? 3072 : FMT == F_IQ2_XS ? 5120 : FMT == F_IQ3_XXS ? 2048 : FMT == F_IQ2_S ? 8192 : FMT == F_IQ3_S ? 2048 : 0) + 16 + 48 * 16;
+    const long long x_bytes = (long long)nb * (XQ_PITCH + XAUX_BYTES) + (FMT == F_IQ2_XXS ? 3072 : FMT == F_IQ2_XS ? 5120 : FMT == F_IQ3_XXS ? 2048 : FMT == F_IQ2_S ? 8192 : FMT == F_IQ3_S ? 2048 : (FMT == F_IQ1_S || FMT == F_IQ1_M) ? 16384 : 0) + 16 + 48 * 16;
     int nbuf = kEnvRingDepth;
     nbuf = nbuf < 2 ? 2 : (nbuf > 4 ? 4 : nbuf);
     auto ring = [&](int w_, int rl_) { return (long long)w_ * nbuf * (((32 / L) * rl_ * row_bytes + 31) / 16 * 16); };
@@ -346,6 +348,8 @@ cudaError_t launch_gemv(const GemvArgs &a, int sm_count, cudaStream_t stream) {
     case F_IQ3_XXS: return launch_fmt<F_IQ3_XXS>(a, sm_count, stream);
     case F_IQ2_S: return launch_fmt<F_IQ2_S>(a, sm_count, stream);
     case F_IQ3_S: return launch_fmt<F_IQ3_S>(a, sm_count, stream);
+    case F_IQ1_S: return launch_fmt<F_IQ1_S>(a, sm_count, stream);
+    case F_IQ1_M: return launch_fmt<F_IQ1_M>(a, sm_count, stream);
     case F_TQ1_0: return launch_fmt<F_TQ1_0>(a, sm_count, stream);
     default: return cudaErrorInvalidValue;
     }

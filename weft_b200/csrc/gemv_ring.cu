@@ -1,4 +1,4 @@
-// Decode GEMV for Q4_0, Q8_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S and TQ1_0 weights whose rows are whole 16-byte multiples:
+// Decode GEMV for Q4_0, Q8_0, Q2_K, Q3_K, Q5_K, Q6_K, IQ1_S, IQ1_M, IQ2_XXS, IQ2_XS, IQ2_S, IQ3_XXS, IQ3_S and TQ1_0 weights whose rows are whole 16-byte multiples:
 // Y[m, n] = quantized_vec_dot(W[n], Xq[m])  (examples/kernels/mul_mat/{q4_0,q8_0,q2_k,q3_k,q5_k,q6_k,iq2_xxs,tq1_0}_decode.py).
 //
 // Same streaming scheme as the Q4_K kernel: one persistent CTA per SM, a producer warp that fills a
@@ -24,12 +24,12 @@ constexpr int RG_MAX_STAGES = 24;
 constexpr int RG_MAX_THREADS = 512;
 // IQ2_XXS waits on table lookups, needs 64 registers, and gains from twice the warps
 // (Q5_K and Q3_K were tried with the same bound: capped at 64 registers they spill, 10.7 -> 11.0 us and 8.8 -> 11.4 us)
-__host__ __device__ constexpr bool is_codebook(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS || fmt == F_IQ2_S || fmt == F_IQ3_S; }
+__host__ __device__ constexpr bool is_codebook(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS || fmt == F_IQ2_S || fmt == F_IQ3_S || fmt == F_IQ1_S || fmt == F_IQ1_M; }
 __host__ __device__ constexpr bool has_sign_table(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS; }
 constexpr int ring_max_threads(int fmt, int rl = 2) { return (is_codebook(fmt) || rl == 1) ? 1024 : RG_MAX_THREADS; }
 // bank-striped copies of the grid (IQ2_XXS: 256 entries x 128 bytes; IQ2_XS: 512 x 128; IQ3_XXS: 256 x 128; IQ2_S: 1024
-// entries x 32 bytes, four copies; IQ3_S: 512 x 128), then, where the format has a sign table, of the sign masks (128 x 128)
-__host__ __device__ constexpr int codebook_grid_bytes(int fmt) { return (fmt == F_IQ2_XS || fmt == F_IQ3_S) ? 65536 : is_codebook(fmt) ? 32768 : 0; }
+// entries x 32 bytes, four copies; IQ3_S: 512 x 128; IQ1_S / IQ1_M: the 16 KB grid as it is), then, where the format has a sign table, of the sign masks (128 x 128)
+__host__ __device__ constexpr int codebook_grid_bytes(int fmt) { return (fmt == F_IQ2_XS || fmt == F_IQ3_S) ? 65536 : (fmt == F_IQ1_S || fmt == F_IQ1_M) ? 16384 : is_codebook(fmt) ? 32768 : 0; }
 __host__ __device__ constexpr int codebook_table_bytes(int fmt) { return is_codebook(fmt) ? codebook_grid_bytes(fmt) + (has_sign_table(fmt) ? 16384 : 0) : 0; }
 
 struct RingParams {
@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
     if (FMT == F_IQ3_XXS) { stage_striped4(p.grid, 256, s_grid); stage_striped8(p.signs, 128, s_neg, true); }
     if (FMT == F_IQ2_S) stage_striped8x4(p.grid, 1024, s_grid);
     if (FMT == F_IQ3_S) stage_striped4(p.grid, 512, s_grid);
+    if (FMT == F_IQ1_S || FMT == F_IQ1_M)
+        for (int i = threadIdx.x; i < 4096; i += blockDim.x) reinterpret_cast<uint32_t *>(s_grid)[i] = __ldg(reinterpret_cast<const uint32_t *>(p.grid) + i);
     uint32_t pw[5] = {1, 3, 9, 27, 81};
     if (FMT == F_TQ1_0) {
 #pragma unroll
@@ -185,6 +187,8 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
             else if (FMT == F_IQ3_XXS) dot_iq3_xxs<RL, 128, 128>(wp, xu, xa, s_grid + 4 * lane, s_neg + 8 * (lane & 15), acc);
             else if (FMT == F_IQ2_S) dot_iq2_s<RL, 32>(wp, xu, xa, s_grid + 8 * (lane & 3), acc);
             else if (FMT == F_IQ3_S) dot_iq3_s<RL, 128>(wp, xu, xa, s_grid + 4 * lane, acc);
+            else if (FMT == F_IQ1_S) dot_iq1_s<RL>(wp, xu, xa, s_grid, acc);
+            else if (FMT == F_IQ1_M) dot_iq1_m<RL>(wp, xu, xa, s_grid, reinterpret_cast<const float *>(p.powers), acc);
             else dot_tq1_0<RL>(wp, xu, xa, pw, acc);
         }
 #pragma unroll
@@ -277,7 +281,7 @@ cudaError_t launch_fmt(const RingParams &p, bool qx, dim3 grid, int threads, siz
 }  // namespace
 
 bool gemv_ring_supported(const GemvArgs &a) {
-    if (a.fmt != F_Q4_0 && a.fmt != F_Q8_0 && a.fmt != F_Q2_K && a.fmt != F_Q3_K && a.fmt != F_Q5_K && a.fmt != F_Q6_K && a.fmt != F_IQ2_XXS && a.fmt != F_IQ2_XS && a.fmt != F_IQ3_XXS && a.fmt != F_IQ2_S && a.fmt != F_IQ3_S && a.fmt != F_TQ1_0) return false;
+    if (a.fmt != F_Q4_0 && a.fmt != F_Q8_0 && a.fmt != F_Q2_K && a.fmt != F_Q3_K && a.fmt != F_Q5_K && a.fmt != F_Q6_K && a.fmt != F_IQ2_XXS && a.fmt != F_IQ2_XS && a.fmt != F_IQ3_XXS && a.fmt != F_IQ2_S && a.fmt != F_IQ3_S && a.fmt != F_IQ1_S && a.fmt != F_IQ1_M && a.fmt != F_TQ1_0) return false;
     return a.k % 256 == 0 && a.k > 0 && (reinterpret_cast<uintptr_t>(a.w) & 15u) == 0 && a.n < (1LL << 30) &&
            plan_ring(a.fmt, a.k / 256).ok;
 }
@@ -316,6 +320,8 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     case F_IQ3_XXS: return launch_fmt<F_IQ3_XXS>(p, qx, grid, threads, plan.smem, stream);
     case F_IQ2_S: return launch_fmt<F_IQ2_S>(p, qx, grid, threads, plan.smem, stream);
     case F_IQ3_S: return launch_fmt<F_IQ3_S>(p, qx, grid, threads, plan.smem, stream);
+    case F_IQ1_S: return launch_fmt<F_IQ1_S>(p, qx, grid, threads, plan.smem, stream);
+    case F_IQ1_M: return launch_fmt<F_IQ1_M>(p, qx, grid, threads, plan.smem, stream);
     default: return launch_fmt<F_TQ1_0>(p, qx, grid, threads, plan.smem, stream);
     }
 }

@@ -547,6 +547,94 @@ __device__ __forceinline__ void dot_iq3_s(const uint8_t *const (&wp)[RL], const 
     for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * (float)bsum[r];
 }
 
+// One IQ1_S record (50 bytes, 2-byte aligned): f16 d; 32 bytes: low 8 bits of the grid index of every 8 weights; 8 u16, one per
+// 32 weights: four 3-bit index tops, a 3-bit scale, the sign of the shift 0.125
+// (examples/kernels/vec_dot/iq1_s_q8_k.py:51-56; GGML ggml_vec_dot_iq1_s_q8_K_generic).  s_grid: int8[2048][8] with values
+// -1, 0, +1.  The shift term multiplies the activation record's stored sums of 32.
+template <int RL>
+__device__ __forceinline__ void dot_iq1_s(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                           const uint8_t *s_grid, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    const int *pair_sums = reinterpret_cast<const int *>(xaux + 16);
+    uint32_t qw[RL][12];
+    int sumi[RL], sumi1[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<12>(wp[r] + 2, qw[r]); sumi[r] = 0; sumi1[r] = 0; }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        const int ps = pair_sums[g];
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t low = qw[r][g], qh = (qw[r][8 + (g >> 1)] >> (16 * (g & 1))) & 0xffffu;
+            int lsum = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + 8 * (byte_of(low, e) | (((qh >> (3 * e)) & 7u) << 8)));
+                lsum = dp4a_ss(gv.x, xw[2 * e], lsum);
+                lsum = dp4a_ss(gv.y, xw[2 * e + 1], lsum);
+            }
+            const int ls = (int)(2u * ((qh >> 12) & 7u) + 1u);
+            sumi[r] += ls * lsum;
+            sumi1[r] += (qh & 0x8000u) ? -ls * ps : ls * ps;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) acc[r] += (half_bits_to_float(ld_u16(wp[r])) * xd_) * ((float)sumi[r] + 0.125f * (float)sumi1[r]);
+}
+
+// One IQ1_M record (56 bytes, no d field, 2-byte aligned here): 32 index bytes; 16 bytes, one per 16 weights: low nibble
+// {3 index bits, shift sign} of the first 8 weights, high nibble of the other 8; four u16: bits 0-11 four 3-bit scales (one
+// per 16 weights), bits 12-15 a nibble of the record's f16 scale (examples/kernels/vec_dot/iq1_m_q8_k.py:73-79; GGML
+// ggml_vec_dot_iq1_m_q8_K_generic).  f16_table: the caller's float[65536] table of f16 bit patterns, as the reference
+// kernel takes it.  The shift term needs sums of 8 activation codes: computed with dp4a against ones.
+template <int RL>
+__device__ __forceinline__ void dot_iq1_m(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
+                                           const uint8_t *s_grid, const float *f16_table, float (&acc)[RL]) {
+    const float xd_ = *reinterpret_cast<const float *>(xaux);
+    uint32_t qw[RL][14];
+    int sumi1[RL], sumi2[RL];
+#pragma unroll
+    for (int r = 0; r < RL; ++r) { ld_words_a2<14>(wp[r], qw[r]); sumi1[r] = 0; sumi2[r] = 0; }
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const uint4 xa = *reinterpret_cast<const uint4 *>(xq + 32 * g);
+        const uint4 xb = *reinterpret_cast<const uint4 *>(xq + 32 * g + 16);
+        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        int s8[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s8[e] = dp4a_ss(0x01010101u, xw[2 * e + 1], dp4a_ss(0x01010101u, xw[2 * e], 0));
+#pragma unroll
+        for (int r = 0; r < RL; ++r) {
+            const uint32_t low = qw[r][g], qh = (qw[r][8 + (g >> 1)] >> (16 * (g & 1))) & 0xffffu;     // two qh bytes of the group
+            const uint32_t sc = (qw[r][12 + (g >> 2)] >> (16 * ((g >> 1) & 1))) & 0xffffu;           // the u16 that holds the group's scales
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                int sum1 = 0, sum2 = 0;
+#pragma unroll
+                for (int ee = 0; ee < 2; ++ee) {
+                    const int e = 2 * half + ee;
+                    const uint32_t nib = (qh >> (4 * e)) & 15u;      // byte e >> 1, nibble e & 1
+                    const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + 8 * (byte_of(low, e) | ((nib & 7u) << 8)));
+                    sum1 = dp4a_ss(gv.x, xw[2 * e], sum1);
+                    sum1 = dp4a_ss(gv.y, xw[2 * e + 1], sum1);
+                    sum2 += (nib & 8u) ? -s8[e] : s8[e];
+                }
+                const int ls = (int)(2u * ((sc >> (6 * (g & 1) + 3 * half)) & 7u) + 1u);
+                sumi1[r] += sum1 * ls;
+                sumi2[r] += sum2 * ls;
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < RL; ++r) {
+        const uint32_t bits = (qw[r][12] >> 12 & 0xfu) | (qw[r][12] >> 24 & 0xf0u) | (qw[r][13] >> 4 & 0xf00u) | (qw[r][13] >> 16 & 0xf000u);
+        acc[r] += (__ldg(f16_table + bits) * xd_) * ((float)sumi1[r] + 0.125f * (float)sumi2[r]);
+    }
+}
+
 // Bank-striped copies of a codebook: with 8-byte entries, copy c (of sixteen) of entry e sits at e * 128 + c * 8, so copy
 // c lives in banks 2c and 2c + 1 only and a half-warp whose lane l reads copy l % 16 never conflicts, whatever the
 // entries (an 8-byte shared load is served one half-warp at a time); with 4-byte entries, copy c (of thirty-two) at

@@ -1,7 +1,7 @@
 """The GGML record layouts on the quantized matrix path, declared with ``@weft.encoding``.
 
 These are the hot-path encodings of the reference's examples/formats/ggml.py (Q4_0 :16-22,
-Q8_0 :56-62, Q2_K :64-72, Q3_K :75-84, Q4_K :88-97, Q5_K :100-110, Q6_K :113-120, IQ2_S :142-151, IQ2_XS :154-161, IQ3_S :189-198, IQ2_XXS :164-170, I8X8 :173-178, I8X4 :181-186, IQ3_XXS :201-208, TQ1_0 :231-238, Q8_K :276-283), byte for
+Q8_0 :56-62, Q2_K :64-72, Q3_K :75-84, Q4_K :88-97, Q5_K :100-110, Q6_K :113-120, IQ1_S :123-130, IQ1_M :133-139, IQ2_S :142-151, IQ2_XS :154-161, IQ3_S :189-198, IQ2_XXS :164-170, I8X8 :173-178, I8X4 :181-186, IQ3_XXS :201-208, TQ1_0 :231-238, Q8_K :276-283), byte for
 byte the block structs of ggml-common.h:184-189,241-246,266-271,317-328,361-366,371-375.  A kernel
 file may use these or the reference's own declarations: ``weft.compile`` identifies an Encoding by
 its name and checks the record geometry, not the declaring module.
@@ -130,6 +130,25 @@ class IQ3_XXS:                   # 98 bytes / 256 elements
 
 
 @encoding
+class IQ1_S:                     # 50 bytes / 256 elements
+    layout = _LE
+    alignment = 2
+    elements = 256
+    d: wl.f16
+    q: wl.u8[32]                 # low 8 bits of the grid index of every 8 elements
+    qh: wl.u16[8]                # per 32 elements: four 3-bit index tops, 3-bit scale, sign of the shift
+
+
+@encoding
+class IQ1_M:                     # 56 bytes / 256 elements, no d field
+    layout = _LE
+    elements = 256
+    q: wl.u8[32]
+    qh: wl.u8[16]                # per 16 elements: two nibbles {3 index bits, shift sign}
+    scales: wl.u8[8]             # four u16: 3-bit scales per 16 elements, top nibbles form the record's f16 scale
+
+
+@encoding
 class IQ2_S:                     # 82 bytes / 256 elements
     layout = _LE
     alignment = 2
@@ -199,11 +218,11 @@ def Q4K_I(W: wl.View[Q4_K, (M, K)], *, rows: wl.static[int]) -> wl.View[Q4K_I[ro
 
 
 #: name -> (storage bytes per record, logical elements per record, alignment)
-RECORDS = {"Q4_0": (18, 32, 2), "Q8_0": (34, 32, 2), "Q8_1": (36, 32, 2), "Q2_K": (84, 256, 2), "Q3_K": (110, 256, 2), "Q4_K": (144, 256, 2), "Q5_K": (176, 256, 2), "Q6_K": (210, 256, 1), "IQ2_XXS": (66, 256, 2), "IQ2_XS": (74, 256, 2), "IQ3_XXS": (98, 256, 2), "IQ2_S": (82, 256, 2), "IQ3_S": (110, 256, 2),
+RECORDS = {"Q4_0": (18, 32, 2), "Q8_0": (34, 32, 2), "Q8_1": (36, 32, 2), "Q2_K": (84, 256, 2), "Q3_K": (110, 256, 2), "Q4_K": (144, 256, 2), "Q5_K": (176, 256, 2), "Q6_K": (210, 256, 1), "IQ2_XXS": (66, 256, 2), "IQ2_XS": (74, 256, 2), "IQ3_XXS": (98, 256, 2), "IQ2_S": (82, 256, 2), "IQ3_S": (110, 256, 2), "IQ1_S": (50, 256, 2), "IQ1_M": (56, 256, 1),
            "TQ1_0": (54, 256, 2), "Q8_K": (292, 256, 4), "I8X8": (8, 8, 8), "I8X4": (4, 4, 4)}
 
 #: numbering of the reference harnesses (examples/repro/weft/vec_dot_runtime.cpp:185-344), used by the C ABI
-FORMAT_IDS = {"Q4_0": 1, "Q8_0": 5, "Q2_K": 6, "Q3_K": 7, "Q4_K": 8, "Q5_K": 9, "Q6_K": 10, "IQ2_S": 13, "IQ2_XS": 14, "IQ2_XXS": 15, "IQ3_S": 16, "IQ3_XXS": 17, "TQ1_0": 20}
+FORMAT_IDS = {"Q4_0": 1, "Q8_0": 5, "Q2_K": 6, "Q3_K": 7, "Q4_K": 8, "Q5_K": 9, "Q6_K": 10, "IQ1_S": 11, "IQ1_M": 12, "IQ2_S": 13, "IQ2_XS": 14, "IQ2_XXS": 15, "IQ3_S": 16, "IQ3_XXS": 17, "TQ1_0": 20}
 
 TQ1_POWERS = (1, 3, 9, 27, 81)
 

@@ -29,7 +29,7 @@ GGML_TYPES = {
     0: ("dense.f32", 4, 1), 1: ("dense.f16", 2, 1),
     2: ("Q4_0", 18, 32), 8: ("Q8_0", 34, 32), 9: ("Q8_1", 36, 32),
     10: ("Q2_K", 84, 256), 11: ("Q3_K", 110, 256), 12: ("Q4_K", 144, 256), 13: ("Q5_K", 176, 256), 14: ("Q6_K", 210, 256),
-    15: ("Q8_K", 292, 256), 16: ("IQ2_XXS", 66, 256), 17: ("IQ2_XS", 74, 256), 18: ("IQ3_XXS", 98, 256), 21: ("IQ3_S", 110, 256), 22: ("IQ2_S", 82, 256), 34: ("TQ1_0", 54, 256),
+    15: ("Q8_K", 292, 256), 16: ("IQ2_XXS", 66, 256), 17: ("IQ2_XS", 74, 256), 18: ("IQ3_XXS", 98, 256), 19: ("IQ1_S", 50, 256), 21: ("IQ3_S", 110, 256), 22: ("IQ2_S", 82, 256), 29: ("IQ1_M", 56, 256), 34: ("TQ1_0", 54, 256),
 }
 TYPE_IDS = {name: type_id for type_id, (name, _, _) in GGML_TYPES.items()}
 

@@ -74,5 +74,16 @@ def row_dequantize_iq3_s(W: wl.View[ggml.IQ3_S, (K,)], grid: wl.View[wl.i8, (204
 
 
 @kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq1_s(W: wl.View[ggml.IQ1_S, (K,)], grid: wl.View[wl.i8, (16384,)], Y: wl.View[wl.f32, (K,)]):
+    """Y = (d * (2 s + 1)) * (grid[idx] + delta), delta = +-0.125 per 32 elements (examples/kernels/dequantize/iq1_s.py:9-13)."""
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq1_m(W: wl.View[ggml.IQ1_M, (K,)], grid: wl.View[wl.i8, (16384,)], f16_bits: wl.View[wl.f32, (65536,)],
+                         Y: wl.View[wl.f32, (K,)]):
+    """As IQ1_S with per-16 scales, per-8 shift signs and the scale looked up in f16_bits (examples/kernels/dequantize/iq1_m.py:18-23)."""
+
+
+@kernel(alias_groups={"Y": "output"})
 def row_dequantize_tq1_0(W: wl.View[ggml.TQ1_0, (K,)], powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (K,)]):
     """Y = f32(trit - 1) * d, digit-major within each of the record's three regions."""

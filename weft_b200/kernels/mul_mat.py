@@ -192,6 +192,36 @@ def production_mul_mat_iq3_s(W: wl.View[ggml.IQ3_S, (N, K)], X: wl.View[wl.f32, 
     """IQ3_S x Q8_K mul_mat (examples/kernels/mul_mat/iq3_s.py:10-16)."""
 
 
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq1_s(W: wl.View[ggml.IQ1_S, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                             grid: wl.View[ggml.I8X8, (2048, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """IQ1_S x Q8_K mul_mat (examples/kernels/mul_mat/iq1_s.py:9-15)."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq1_s_decode(W: wl.View[ggml.IQ1_S, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                                    grid: wl.View[ggml.I8X8, (2048, 8)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, IQ1_S (examples/kernels/mul_mat/iq1_s_decode.py:10-16)."""
+
+
+@kernel
+def production_mul_mat_iq1_m(W: wl.View[ggml.IQ1_M, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                             grid: wl.View[ggml.I8X8, (2048, 8)], f16_bits: wl.View[wl.f32, (65536,)], Y: wl.View[wl.f32, (M, N)]):
+    """IQ1_M x Q8_K mul_mat (examples/kernels/mul_mat/iq1_m.py:10-17)."""
+
+
+@kernel(alias_groups={"Xq": "workspace", "Y": "output"})
+def production_mul_mat_iq1_m_decode(W: wl.View[ggml.IQ1_M, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                                    grid: wl.View[ggml.I8X8, (2048, 8)], f16_bits: wl.View[wl.f32, (65536,)], Y: wl.View[wl.f32, (M, N)]):
+    """Decode GEMV, IQ1_M (examples/kernels/mul_mat/iq1_m_decode.py:10-17)."""
+
+
+@kernel
+def production_mul_mat_iq1_m_lane16_decode(W: wl.View[ggml.IQ1_M, (N, K)], X: wl.View[wl.f32, (M, K)], Xq: wl.View[ggml.Q8_K, (M, K)],
+                                           grid: wl.View[ggml.I8X8, (2048, 8)], f16_bits: wl.View[wl.f32, (65536,)], Y: wl.View[wl.f32, (M, N)]):
+    """The same under the name of the reference's sixteen-wide plan (examples/kernels/mul_mat/iq1_m_lane16_decode.py:10-17)."""
+
+
 @kernel
 def production_mul_mat_q4_k_persistent(W: wl.View[ggml.Q4K_I[16], (N, K)], X: wl.View[wl.f32, (M, K)],
                                        Xq: wl.View[ggml.Q8_K, (M, K)], Y: wl.View[wl.f32, (M, N)]):

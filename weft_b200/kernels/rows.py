@@ -64,6 +64,15 @@ def row_dequantize_iq3_s_rows(W: wl.View[ggml.IQ3_S, (N, K)], grid: wl.View[wl.i
 
 
 @kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq1_s_rows(W: wl.View[ggml.IQ1_S, (N, K)], grid: wl.View[wl.i8, (16384,)], Y: wl.View[wl.f32, (N, K)]): ...
+
+
+@kernel(alias_groups={"Y": "output"})
+def row_dequantize_iq1_m_rows(W: wl.View[ggml.IQ1_M, (N, K)], grid: wl.View[wl.i8, (16384,)], f16_bits: wl.View[wl.f32, (65536,)],
+                              Y: wl.View[wl.f32, (N, K)]): ...
+
+
+@kernel(alias_groups={"Y": "output"})
 def row_dequantize_tq1_0_rows(W: wl.View[ggml.TQ1_0, (N, K)], powers: wl.View[wl.u32, (5,)],
                               Y: wl.View[wl.f32, (N, K)]): ...
 
@@ -122,6 +131,17 @@ def quantized_vec_dot_iq2_s_q8_k_rows(W: wl.View[ggml.IQ2_S, (N, K)], X: wl.View
 @kernel
 def quantized_vec_dot_iq3_s_q8_k_rows(W: wl.View[ggml.IQ3_S, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
                                       grid: wl.View[ggml.I8X4, (512, 4)], Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_iq1_s_q8_k_rows(W: wl.View[ggml.IQ1_S, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
+                                      grid: wl.View[ggml.I8X8, (2048, 8)], Y: wl.View[wl.f32, (N,)]): ...
+
+
+@kernel
+def quantized_vec_dot_iq1_m_q8_k_rows(W: wl.View[ggml.IQ1_M, (N, K)], X: wl.View[ggml.Q8_K, (K,)],
+                                      grid: wl.View[ggml.I8X8, (2048, 8)], f16_bits: wl.View[wl.f32, (65536,)],
+                                      Y: wl.View[wl.f32, (N,)]): ...
 
 
 @kernel

@@ -82,6 +82,28 @@ def quantized_vec_dot_iq3_s_q8_k(W: wl.View[ggml.IQ3_S, (K,)], X: wl.View[ggml.Q
 
 
 @kernel
+def quantized_vec_dot_iq1_s_q8_k(W: wl.View[ggml.IQ1_S, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                 grid: wl.View[ggml.I8X8, (2048, 8)], Y: wl.View[wl.f32, (1,)]):
+    """Y[0] = sum over 256-blocks of d * x.ds * (sum_g (2 s_g + 1) dot(grid[idx], x) + 0.125 sum_g (2 s_g + 1) (+-1) bsum32_g)
+    (examples/kernels/vec_dot/iq1_s_q8_k.py:51-56)."""
+
+
+@kernel
+def quantized_vec_dot_iq1_m_q8_k(W: wl.View[ggml.IQ1_M, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                 grid: wl.View[ggml.I8X8, (2048, 8)], f16_bits: wl.View[wl.f32, (65536,)],
+                                 Y: wl.View[wl.f32, (1,)]):
+    """As IQ1_S with a scale per 16 weights, a shift sign per 8 and the record's f16 scale spread over four u16
+    (examples/kernels/vec_dot/iq1_m_q8_k.py:73-79)."""
+
+
+@kernel
+def quantized_vec_dot_iq1_m_q8_k_lane16(W: wl.View[ggml.IQ1_M, (K,)], X: wl.View[ggml.Q8_K, (K,)],
+                                        grid: wl.View[ggml.I8X8, (2048, 8)], f16_bits: wl.View[wl.f32, (65536,)],
+                                        Y: wl.View[wl.f32, (1,)]):
+    """The same dot product under the name of the reference's sixteen-wide plan (examples/kernels/vec_dot/iq1_m_q8_k_lane16.py:85-91)."""
+
+
+@kernel
 def quantized_vec_dot_tq1_0_q8_k(W: wl.View[ggml.TQ1_0, (K,)], X: wl.View[ggml.Q8_K, (K,)],
                                  powers: wl.View[wl.u32, (5,)], Y: wl.View[wl.f32, (1,)]):
     """Y[0] = sum over 256-blocks of f32(sum((trit - 1) * x)) * (d * x.ds); trits decoded with powers[]."""
