@@ -46,6 +46,8 @@ WORKLOADS = {
     "iq3_xxs_decode_28672x8192": ("IQ3_XXS", "decode", 28672, 8192, 1),
     "iq2_s_decode_28672x8192": ("IQ2_S", "decode", 28672, 8192, 1),
     "iq3_s_decode_28672x8192": ("IQ3_S", "decode", 28672, 8192, 1),
+    "iq1_s_decode_28672x8192": ("IQ1_S", "decode", 28672, 8192, 1),
+    "iq1_m_decode_28672x8192": ("IQ1_M", "decode", 28672, 8192, 1),
     "q2_k_decode_14336x4096": ("Q2_K", "decode", 14336, 4096, 1),
     "q3_k_decode_14336x4096": ("Q3_K", "decode", 14336, 4096, 1),
     "q5_k_decode_14336x4096": ("Q5_K", "decode", 14336, 4096, 1),
@@ -109,17 +111,19 @@ def make_inputs(fmt: str, n: int, k: int, m: int, seed: int):
     rng = np.random.default_rng(seed)
     fid = oracle.FORMAT_IDS[fmt]
     golden = np.load(ROOT / "tests" / "golden" / "golden.npz")
-    grid, signs = golden[{"IQ2_XS": "iq2xs_grid", "IQ3_XXS": "iq3xxs_grid", "IQ2_S": "iq2s_grid", "IQ3_S": "iq3s_grid"}.get(fmt, "iq2xxs_grid")], golden["iq2xxs_signs"]
+    grid, signs = golden[{"IQ2_XS": "iq2xs_grid", "IQ3_XXS": "iq3xxs_grid", "IQ2_S": "iq2s_grid", "IQ3_S": "iq3s_grid", "IQ1_S": "iq1s_grid", "IQ1_M": "iq1s_grid"}.get(fmt, "iq2xxs_grid")], golden["iq2xxs_signs"]
     base_rows = min(n, 1024)            # quantize 1024 distinct rows, rotate them to fill the matrix (timing is data-independent)
     if fmt == "TQ1_0":
         src = (rng.integers(-1, 2, size=(base_rows, k)) * np.float32(0.02)).astype(np.float32)
         base = oracle.quantize(fid, src)
-    elif fmt in ("IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ2_S", "IQ3_S"):
+    elif fmt in ("IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ2_S", "IQ3_S", "IQ1_S", "IQ1_M"):
         if oracle.ref_available():
             base_rows = min(n, 128)
             base = oracle.ref_quantize_weights(fid, (rng.standard_normal((base_rows, k)) * 0.02).astype(np.float32))
         else:           # any index, sign index and scale is a valid record once the f16 scale is a small finite number
             base = rng.integers(0, 256, size=(base_rows, k // 256, oracle.RECORD_BYTES[fid]), dtype=np.uint8)
+            if fmt == "IQ1_M":          # its f16 scale is spread over the top nibbles of the last eight bytes: keep it a small normal number
+                base[:, :, 55] = (base[:, :, 55] & 0x0f) | 0x20
             base[:, :, 0:2] = (np.abs(rng.standard_normal((base_rows, k // 256))) * 0.01 + 1e-3).astype(np.float16).view(np.uint8).reshape(base_rows, -1, 2)
             base = base.reshape(base_rows, -1)
     elif fmt in ("Q2_K", "Q3_K", "Q5_K", "Q6_K"):
@@ -689,7 +693,9 @@ def run_mul_mat(args, lib, check, stream, workload: str, world: int, rank: int, 
     y_dev = torch.zeros((m, n), device="cuda")
     grid_dev = torch.from_numpy(grid).cuda()
     signs_dev = torch.from_numpy(signs).cuda()
-    powers_dev = torch.tensor(TQ1_POWERS, dtype=torch.int32, device="cuda")
+    # the third table slot: the TQ1_0 powers, or for IQ1_M the float[65536] table of f16 bit patterns its reference kernel takes
+    f16_table = np.arange(65536, dtype=np.uint16).view(np.float16).astype(np.float32)
+    powers_dev = torch.from_numpy(f16_table).cuda() if fmt == "IQ1_M" else torch.tensor(TQ1_POWERS, dtype=torch.int32, device="cuda")
     fid = 1008 if layout == "Q4K_I16" else FORMAT_IDS[fmt]
     mode_id = 0 if mode == "decode" else 1
     shard_fn = lib.weft_b200_mul_mat_shard
@@ -873,7 +879,7 @@ def run_mul_mat(args, lib, check, stream, workload: str, world: int, rank: int, 
         xq_pin = torch.zeros((m, row_bytes(act, k)), dtype=torch.uint8).pin_memory()
         y_pin = torch.zeros((m, n), dtype=torch.float32).pin_memory()
         grid_pin, signs_pin = torch.from_numpy(grid).pin_memory(), torch.from_numpy(signs).pin_memory()
-        powers_pin = torch.tensor(TQ1_POWERS, dtype=torch.int32).pin_memory()
+        powers_pin = powers_dev if fmt == "IQ1_M" else torch.tensor(TQ1_POWERS, dtype=torch.int32).pin_memory()   # 256 KB: kept on the device
         y_page = np.zeros((m, n), dtype=np.float32)      # pageable memory, what a plain numpy caller of the reference passes
         x_page, xq_page = x_host.copy(), np.zeros((m, row_bytes(act, k)), dtype=np.uint8)
 
