@@ -26,10 +26,14 @@ constexpr int RG_MAX_THREADS = 512;
 // (Q5_K and Q3_K were tried with the same bound: capped at 64 registers they spill, 10.7 -> 11.0 us and 8.8 -> 11.4 us)
 __host__ __device__ constexpr bool is_codebook(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS || fmt == F_IQ2_S || fmt == F_IQ3_S || fmt == F_IQ1_S || fmt == F_IQ1_M; }
 __host__ __device__ constexpr bool has_sign_table(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ2_XS || fmt == F_IQ3_XXS; }
-constexpr int ring_max_threads(int fmt, int rl = 2) { return (is_codebook(fmt) || rl == 1) ? 1024 : RG_MAX_THREADS; }
+// the codebook formats whose two rows of record words fit in 64 registers run twice the warps; the others (20 to 27 words per
+// row) spill at that bound and keep 128 registers and fifteen consumer warps (28672 x 8192: IQ2_XS 42.2 -> 31.2 us, IQ2_S
+// 49.0 -> 36.8, IQ3_XXS 46.5 -> 33.8, IQ3_S 62.2 -> 46.9; twenty-three warps at 80 registers: 34.1 / 41.1 / 36.6 / 52.4)
+__host__ __device__ constexpr bool many_warps(int fmt) { return fmt == F_IQ2_XXS || fmt == F_IQ1_S || fmt == F_IQ1_M; }
+constexpr int ring_max_threads(int fmt, int rl = 2) { return (many_warps(fmt) || rl == 1) ? 1024 : RG_MAX_THREADS; }
 // bank-striped copies of the grid (IQ2_XXS: 256 entries x 128 bytes; IQ2_XS: 512 x 128; IQ3_XXS: 256 x 128; IQ2_S: 1024
-// entries x 32 bytes, four copies; IQ3_S: 512 x 128; IQ1_S / IQ1_M: the 16 KB grid as it is), then, where the format has a sign table, of the sign masks (128 x 128)
-__host__ __device__ constexpr int codebook_grid_bytes(int fmt) { return (fmt == F_IQ2_XS || fmt == F_IQ3_S) ? 65536 : (fmt == F_IQ1_S || fmt == F_IQ1_M) ? 16384 : is_codebook(fmt) ? 32768 : 0; }
+// entries x 32 bytes, four copies; IQ3_S: 512 x 128; IQ1_S / IQ1_M: 2048 entries x 32 bytes, four copies: IQ1_S 31.6 -> 30.6 us against the plain 16 KB table), then, where the format has a sign table, of the sign masks (128 x 128)
+__host__ __device__ constexpr int codebook_grid_bytes(int fmt) { return (fmt == F_IQ2_XS || fmt == F_IQ3_S || fmt == F_IQ1_S || fmt == F_IQ1_M) ? 65536 : is_codebook(fmt) ? 32768 : 0; }
 __host__ __device__ constexpr int codebook_table_bytes(int fmt) { return is_codebook(fmt) ? codebook_grid_bytes(fmt) + (has_sign_table(fmt) ? 16384 : 0) : 0; }
 
 struct RingParams {
@@ -115,8 +119,7 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
     if (FMT == F_IQ3_XXS) { stage_striped4(p.grid, 256, s_grid); stage_striped8(p.signs, 128, s_neg, true); }
     if (FMT == F_IQ2_S) stage_striped8x4(p.grid, 1024, s_grid);
     if (FMT == F_IQ3_S) stage_striped4(p.grid, 512, s_grid);
-    if (FMT == F_IQ1_S || FMT == F_IQ1_M)
-        for (int i = threadIdx.x; i < 4096; i += blockDim.x) reinterpret_cast<uint32_t *>(s_grid)[i] = __ldg(reinterpret_cast<const uint32_t *>(p.grid) + i);
+    if (FMT == F_IQ1_S || FMT == F_IQ1_M) stage_striped8x4(p.grid, 2048, s_grid);
     uint32_t pw[5] = {1, 3, 9, 27, 81};
     if (FMT == F_TQ1_0) {
 #pragma unroll
@@ -187,8 +190,8 @@ __global__ void __launch_bounds__(ring_max_threads(FMT, RL)) gemv_ring_kernel(co
             else if (FMT == F_IQ3_XXS) dot_iq3_xxs<RL, 128, 128>(wp, xu, xa, s_grid + 4 * lane, s_neg + 8 * (lane & 15), acc);
             else if (FMT == F_IQ2_S) dot_iq2_s<RL, 32>(wp, xu, xa, s_grid + 8 * (lane & 3), acc);
             else if (FMT == F_IQ3_S) dot_iq3_s<RL, 128>(wp, xu, xa, s_grid + 4 * lane, acc);
-            else if (FMT == F_IQ1_S) dot_iq1_s<RL>(wp, xu, xa, s_grid, acc);
-            else if (FMT == F_IQ1_M) dot_iq1_m<RL>(wp, xu, xa, s_grid, reinterpret_cast<const float *>(p.powers), acc);
+            else if (FMT == F_IQ1_S) dot_iq1_s<RL, 32>(wp, xu, xa, s_grid + 8 * (lane & 3), acc);
+            else if (FMT == F_IQ1_M) dot_iq1_m<RL, 32>(wp, xu, xa, s_grid + 8 * (lane & 3), reinterpret_cast<const float *>(p.powers), acc);
             else dot_tq1_0<RL>(wp, xu, xa, pw, acc);
         }
 #pragma unroll
@@ -302,7 +305,7 @@ cudaError_t launch_gemv_ring(const GemvArgs &a, int sm_count, cudaStream_t strea
     const long long rest = a.n - (long long)p.full_rounds * ctas * stage_rows;
     p.tail_rows = (int)((rest + ctas - 1) / ctas);
     const int most = ring_max_threads(a.fmt) / 32 - 1;
-    int consumers = kRingConsumers < 1 ? (is_codebook(a.fmt) ? kRingIq2Consumers : 15) : kRingConsumers;
+    int consumers = kRingConsumers < 1 ? (many_warps(a.fmt) ? kRingIq2Consumers : 15) : kRingConsumers;
     if (consumers > most) consumers = most;
     if (consumers < 1) consumers = 1;
     const int threads = (consumers + 1) * 32;

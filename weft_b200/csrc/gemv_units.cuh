@@ -550,8 +550,8 @@ __device__ __forceinline__ void dot_iq3_s(const uint8_t *const (&wp)[RL], const 
 // One IQ1_S record (50 bytes, 2-byte aligned): f16 d; 32 bytes: low 8 bits of the grid index of every 8 weights; 8 u16, one per
 // 32 weights: four 3-bit index tops, a 3-bit scale, the sign of the shift 0.125
 // (examples/kernels/vec_dot/iq1_s_q8_k.py:51-56; GGML ggml_vec_dot_iq1_s_q8_K_generic).  s_grid: int8[2048][8] with values
-// -1, 0, +1.  The shift term multiplies the activation record's stored sums of 32.
-template <int RL>
+// -1, 0, +1, PITCH bytes between entries.  The shift term multiplies the activation record's stored sums of 32.
+template <int RL, int PITCH = 8>
 __device__ __forceinline__ void dot_iq1_s(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
                                            const uint8_t *s_grid, float (&acc)[RL]) {
     const float xd_ = *reinterpret_cast<const float *>(xaux);
@@ -572,7 +572,7 @@ __device__ __forceinline__ void dot_iq1_s(const uint8_t *const (&wp)[RL], const 
             int lsum = 0;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + 8 * (byte_of(low, e) | (((qh >> (3 * e)) & 7u) << 8)));
+                const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + PITCH * (byte_of(low, e) | (((qh >> (3 * e)) & 7u) << 8)));
                 lsum = dp4a_ss(gv.x, xw[2 * e], lsum);
                 lsum = dp4a_ss(gv.y, xw[2 * e + 1], lsum);
             }
@@ -590,7 +590,7 @@ __device__ __forceinline__ void dot_iq1_s(const uint8_t *const (&wp)[RL], const 
 // per 16 weights), bits 12-15 a nibble of the record's f16 scale (examples/kernels/vec_dot/iq1_m_q8_k.py:73-79; GGML
 // ggml_vec_dot_iq1_m_q8_K_generic).  f16_table: the caller's float[65536] table of f16 bit patterns, as the reference
 // kernel takes it.  The shift term needs sums of 8 activation codes: computed with dp4a against ones.
-template <int RL>
+template <int RL, int PITCH = 8>
 __device__ __forceinline__ void dot_iq1_m(const uint8_t *const (&wp)[RL], const uint8_t *xq, const uint8_t *xaux,
                                            const uint8_t *s_grid, const float *f16_table, float (&acc)[RL]) {
     const float xd_ = *reinterpret_cast<const float *>(xaux);
@@ -617,7 +617,7 @@ __device__ __forceinline__ void dot_iq1_m(const uint8_t *const (&wp)[RL], const 
                 for (int ee = 0; ee < 2; ++ee) {
                     const int e = 2 * half + ee;
                     const uint32_t nib = (qh >> (4 * e)) & 15u;      // byte e >> 1, nibble e & 1
-                    const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + 8 * (byte_of(low, e) | ((nib & 7u) << 8)));
+                    const uint2 gv = *reinterpret_cast<const uint2 *>(s_grid + PITCH * (byte_of(low, e) | ((nib & 7u) << 8)));
                     sum1 = dp4a_ss(gv.x, xw[2 * e], sum1);
                     sum1 = dp4a_ss(gv.y, xw[2 * e + 1], sum1);
                     sum2 += (nib & 8u) ? -s8[e] : s8[e];
