@@ -143,9 +143,11 @@ def _run_tq1_0(torch, oracle, m, n, k, seed, column_ranges=None):
         assert reference_tolerance_ok(got[:, lo:hi], want[:, lo:hi])
 
 
-@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 2048), (512, 384, 1024), (32, 130, 4096), (200, 1001, 3072), (512, 4736, 1024)])
+@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 2048), (512, 384, 1024), (32, 130, 4096), (200, 1001, 3072), (512, 4736, 1024),
+                                 (300, 77, 4096), (512, 1000, 2048), (256, 160, 2048), (129, 33, 6144), (700, 2000, 4096)])
 def test_prefill_tq1_0_shapes(torch, oracle, mnk):
-    """K a multiple of 1024 takes the tensor-core kernel; odd N exercises 2-byte-aligned weight rows."""
+    """K a multiple of 1024 takes the tensor-core kernels (above 128 tokens and with K a multiple of 2048 the CTA-pair
+    kernel, whose tiles are 32 to 160 weights wide); odd N exercises 2-byte-aligned weight rows and ragged last tiles."""
     m, n, k = mnk
     _run_tq1_0(torch, oracle, m, n, k, seed=sum(mnk))
 

@@ -104,8 +104,8 @@ struct PairControl {
     uint64_t raw_empty[PP_RAW_SLOTS];    // expander warps of this CTA are done reading the slot
     uint64_t ab_full[PP_STAGES];         // EVEN CTA's copy is the live one: expander + specials warps of both CTAs
     uint64_t ab_empty[PP_STAGES];        // both copies live: the MMAs that read the slot have completed
-    uint64_t tmem_full[2];               // both copies live: the buffer's accumulators are complete
-    uint64_t tmem_empty[2];              // EVEN CTA's copy is the live one: epilogue warps of both CTAs
+    uint64_t tmem_full[3];               // both copies live: the buffer's accumulators are complete (Q4_K uses two buffers, TQ1_0 three)
+    uint64_t tmem_empty[3];              // EVEN CTA's copy is the live one: epilogue warps of both CTAs
     uint32_t tmem_base;
     volatile int abort;
 };
@@ -135,6 +135,18 @@ __device__ __forceinline__ bool pp_wait_warp(uint64_t *bar, uint32_t parity, Pai
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (ctl->abort) return false;
+    }
+    if ((threadIdx.x & 31) == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(status, ST_WAIT_TIMEOUT); }
+    return false;
+}
+
+// For a role with slack (the TQ1_0 epilogue, three accumulator buffers deep): sleep between polls, leaving the issue slots to the
+// expanders (measured 429 -> 412 us with the arithmetic decode)
+__device__ __forceinline__ bool pp_wait_warp_relaxed(uint64_t *bar, uint32_t parity, PairControl *ctl, uint32_t peer_abort, int *status) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (ctl->abort) return false;
+        __nanosleep(200);
     }
     if ((threadIdx.x & 31) == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(status, ST_WAIT_TIMEOUT); }
     return false;
@@ -568,6 +580,378 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
     }
 }
 
+// ================================================================================================================
+// TQ1_0 x Q8_K on CTA pairs (production_mul_mat_tq1_0, examples/kernels/mul_mat/tq1_0.py; per block the math of
+// examples/kernels/vec_dot/tq1_0_q8_k.py:9-55, GGML ggml-cpu/quants.c:430-480).  Same pipeline as the Q4_K kernel above with
+// what the format makes simpler: the weight operand is the base-3 digits minus one (one limb, no min term), so a tile
+// is 256 tokens x w weights with w up to 160 (each CTA expands w/2 weights into w/2 operand rows, N = w), an accumulator
+// buffer is w <= 160 columns and THREE of them fit in tensor memory, the per-token warps only copy x.d, and the
+// epilogue is acc += f32(isum) * (d * x.d) on one column per weight.  Sixteen epilogue warps (lane quarter x quarter of
+// the tile's weights, at most 40 accumulators per thread) and ten expander warps, 32 warps at 64 registers per thread.
+// The expansion is what the kernel waits for: turning 54 bytes into 256 int8 digits is bound by the integer pipe, so the
+// digits come from a table (see pt_expand_lut) rather than from the multiplications of the decode kernels.
+// 512 x 28672 x 8192: 318 us (the single-CTA kernel of prefill.cu: 582 us; this kernel with the arithmetic decode: 421 us).
+// Raw records: 54 bytes, rows of K/256 * 54 bytes (a multiple of 16 when K % 2048 == 0).  Record b of a row starts
+// (54 b) % 16 bytes past a 16-byte boundary; an 80-byte box from that boundary holds it whole.  Its f16 d (bytes 52, 53)
+// lies inside the 16-byte box at (54 b + 52) rounded down to 16: that box is fetched for the PARTNER's weights, so each
+// CTA has the scales of all w weights without touching the partner's shared memory.
+constexpr int PT_E_WARPS = 16, PT_X_WARPS = 10, PT_S_WARPS = 2;
+constexpr int PT_X_WARP0 = PT_E_WARPS, PT_S_WARP0 = PT_X_WARP0 + PT_X_WARPS;
+constexpr int PT_ATMA_WARP = PT_S_WARP0 + PT_S_WARPS, PT_WTMA_WARP = PT_ATMA_WARP + 1, PT_MMA_WARP = PT_WTMA_WARP + 1;
+constexpr int PT_THREADS = 32 * (PT_MMA_WARP + PP_MMA_WARPS);   // 32 warps
+constexpr int PT_BUFS = 3, PT_BUF_COLS = 160;
+constexpr int PT_RAW_BOX = 80;                                  // bytes per record box
+constexpr int PT_RAW_HEADS = PP_RMAX * PT_RAW_BOX;              // after the record boxes: the 16-byte boxes with the partner's d
+constexpr int PT_RAW_SLOT = PT_RAW_HEADS + PP_RMAX * 16;        // 7680 B
+constexpr int PT_RAW_SLOTS = 3;
+constexpr int PT_OFF_WD = PP_OFF_RAW + PT_RAW_SLOTS * PT_RAW_SLOT;
+constexpr int PT_OFF_XD = PT_OFF_WD + PP_RING * PP_WD_SLOT;     // d of the pair's 2 x 80 weights: 640 B per slot
+constexpr int PT_OFF_LUT = PT_OFF_XD + PP_RING * PP_XD_SLOT;    // digits of every byte value, two copies interleaved
+constexpr int PT_LUT_COPIES = 4;
+constexpr int PT_SMEM = PT_OFF_LUT + 256 * 8 * PT_LUT_COPIES;
+static_assert(PT_SMEM <= 227 * 1024 && PT_RAW_SLOT % 128 == 0, "shared memory budget of the TQ1_0 kernel");
+
+// Table form.  Entry v of the table (built from the caller's powers when the kernel starts) holds the five digits of byte value v,
+// minus one, as int8: bytes 0..3 digits 0..3, byte 4 digit 4.  A task takes four bytes of each of its record words, looks them up and
+// transposes the 4 x 5 digits into five stream words with byte permutes: about 4 integer instructions per stream word where the
+// arithmetic form needs 10 (the expansion is bound by the integer pipe).  Stream word g goes to operand word g + W by a 4-byte
+// store; PART 3 also writes the zeros in front of stream word 0 and behind stream word 63.
+// PART 0: record words 0..3 (stream words 8 n + s), 1: words 4..7, 2: words 8..11 (40 + 4 n + s - 8), 3: the qh word (60 + n).
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+template <int W>
+__device__ __forceinline__ void pt_store_word(uint32_t base, uint32_t x7, int g, uint32_t v) {   // g: stream word index, compile time
+    const int pos = g + W, chunk = pos >> 2;
+    const uint32_t at = chunk < 16 ? base + (uint32_t)(chunk >> 3) * PP_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7) + 4u * (uint32_t)(pos & 3) : 0u;
+    if (chunk < 16) sts_u32(at, v);
+}
+template <int W, int PART>
+__device__ __forceinline__ void pt_expand_lut(uint32_t rec, uint32_t lut, uint32_t b_slot, int row) {
+    const uint32_t base = b_slot + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(row & 7) << 4;
+    const uint32_t thin = b_slot + PP_B_THIN + (uint32_t)row * 16u;
+    constexpr int NW = PART == 3 ? 1 : 4;            // record words of this task
+    // the task's record words: aligned 4-byte loads and a 16-bit funnel shift when the record starts in the middle of a word
+    const uint32_t first = rec + 16u * (uint32_t)PART, aligned = first & ~3u;
+    uint32_t raw[NW + 1], w[NW];
+#pragma unroll
+    for (int i = 0; i <= NW; ++i) raw[i] = lds_u32(aligned + 4u * (uint32_t)i);
+#pragma unroll
+    for (int i = 0; i < NW; ++i) w[i] = (first & 2u) ? __funnelshift_r(raw[i], raw[i + 1], 16) : raw[i];
+    uint32_t thin_words[4] = {0u, 0u, 0u, 0u};      // operand words 64..67 (PART 3)
+#pragma unroll
+    for (int s = 0; s < NW; ++s) {
+        uint32_t x[4], y[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t at = lut + prmt(w[s], 0u, 0x4440u + (uint32_t)i) * (8u * PT_LUT_COPIES);   // the copies of a value's 8-byte entry lie side by side
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(x[i]), "=r"(y[i]) : "r"(at));
+        }
+        const uint32_t t0 = prmt(x[0], x[1], 0x5140u), t1 = prmt(x[0], x[1], 0x7362u);
+        const uint32_t t2 = prmt(x[2], x[3], 0x5140u), t3 = prmt(x[2], x[3], 0x7362u);
+        uint32_t digit[5];
+        digit[0] = prmt(t0, t2, 0x5410u); digit[1] = prmt(t0, t2, 0x7632u);
+        digit[2] = prmt(t1, t3, 0x5410u); digit[3] = prmt(t1, t3, 0x7632u);
+        digit[4] = prmt(prmt(y[0], y[1], 0x0040u), prmt(y[2], y[3], 0x0040u), 0x5410u);
+#pragma unroll
+        for (int n = 0; n < (PART == 3 ? 4 : 5); ++n) {
+            const int g = PART < 2 ? 8 * n + 4 * PART + s : PART == 2 ? 40 + 4 * n + s : 60 + n;
+            if (g + W < 64) pt_store_word<W>(base, x7, g, digit[n]);
+            else thin_words[g + W - 64] = digit[n];
+        }
+    }
+    if (PART == 3) {
+        // zeros in front of the first stream word, the carried words and zeros in the thin chunk
+#pragma unroll
+        for (int k = 0; k < W; ++k) sts_u32(base + (((uint32_t)0 << 4) ^ x7) + 4u * (uint32_t)k, 0u);
+        sts_u128(thin, thin_words[0], thin_words[1], thin_words[2], thin_words[3]);
+    }
+}
+template <int W>
+__device__ __forceinline__ void pt_expand_lut_part(uint32_t rec, uint32_t lut, uint32_t b_slot, int row, int part) {
+    if (part == 0) pt_expand_lut<W, 0>(rec, lut, b_slot, row);
+    else if (part == 1) pt_expand_lut<W, 1>(rec, lut, b_slot, row);
+    else if (part == 2) pt_expand_lut<W, 2>(rec, lut, b_slot, row);
+    else pt_expand_lut<W, 3>(rec, lut, b_slot, row);
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PT_THREADS, 1)
+prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid_constant__ CUtensorMap x_wide, const __grid_constant__ CUtensorMap x_narrow,
+                        const __grid_constant__ CUtensorMap w_rows, const __grid_constant__ CUtensorMap w_heads) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    PairControl *ctl = reinterpret_cast<PairControl *>(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();
+    const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int nb = p.nb;
+    const int my_tiles = (tiles - pair + pairs - 1) / pairs;
+    const int total = my_tiles * nb;
+    const int R = p.w >> 1;                                // weights this CTA expands per block = its B rows
+
+    const uint32_t ctl_addr = smem_addr(ctl);
+    const uint32_t ctl_even = tc::map_to_cta(ctl_addr, 0), ctl_peer = tc::map_to_cta(ctl_addr, rank ^ 1u);
+    const uint32_t peer_abort = ctl_peer + (uint32_t)offsetof(PairControl, abort);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PP_STAGES; ++s) {
+            mbar_init(&ctl->a_landed[s], 1);
+            mbar_init(&ctl->ab_full[s], 2 * (PT_X_WARPS + PT_S_WARPS));
+            mbar_init(&ctl->ab_empty[s], 1);
+        }
+        for (int s = 0; s < PT_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 1); mbar_init(&ctl->raw_empty[s], PT_X_WARPS); }
+        for (int h = 0; h < PT_BUFS; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 2 * PT_E_WARPS); }
+        ctl->abort = 0;
+        ctl->tmem_base = 0xffffffffu;
+        mbar_fence_init();
+    }
+    // K chunk 17 of every weight slot (operand bytes 272..287) is zero for the whole kernel
+    for (int i = threadIdx.x; i < PP_STAGES * PP_RMAX * 4; i += PT_THREADS) {
+        const int s = i / (PP_RMAX * 4), r = i % (PP_RMAX * 4);
+        reinterpret_cast<uint32_t *>(smem + PP_OFF_B + s * PP_B_SLOT + PP_B_THIN + PP_B_COL)[r] = 0u;
+    }
+    // the digit table, from the caller's powers: entry v = digits 0..4 of byte value v minus one, as int8
+    for (int v = threadIdx.x; v < 256; v += PT_THREADS) {
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int n = 0; n < 5; ++n) {
+            const uint32_t q = ((uint32_t)v * (__ldg(powers + n) & 0xffu)) & 0xffu;
+            const uint32_t digit_minus_one = (((q * 3u) >> 8) + 0xffu) & 0xffu;
+            if (n < 4) lo |= digit_minus_one << (8 * n); else hi = digit_minus_one;
+        }
+#pragma unroll
+        for (int c = 0; c < PT_LUT_COPIES; ++c) reinterpret_cast<uint2 *>(smem + PT_OFF_LUT)[v * PT_LUT_COPIES + c] = make_uint2(lo, hi);
+    }
+    fence_proxy_async();
+    __syncthreads();
+    if (warp == PT_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PP_TMEM_COLS);   // per CTA, see the Q4_K kernel
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync_all();
+    tc::fence_after_sync();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&ctl->tmem_base);
+    const bool tmem_ok = tmem == 0u;
+    if (!tmem_ok && threadIdx.x == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(p.status, 0x40000000 | (int)(tmem & 0xffffu) | (int)((tmem >> 16) & 0x3fffu) << 16); }
+    if (!tmem_ok) {
+        // nothing: fall through to the common exit
+    } else if (warp >= PT_X_WARP0 && warp < PT_X_WARP0 + PT_X_WARPS) {
+        // ------------------------------------------------------------------ expanders: four tasks per weight row (tasks [part R, (part + 1) R)
+        // are part `part` of the rows: a warp is of one part except where it straddles a multiple of R)
+        const int task = 32 * (warp - PT_X_WARP0) + lane;
+        const int part = task / R, row = task - part * R;       // tasks [part R, (part + 1) R) are part `part` of the rows
+        const bool active = task < 4 * R;
+        const uint32_t lut = smem_addr(smem + PT_OFF_LUT) + 8u * (uint32_t)(lane & (PT_LUT_COPIES - 1));
+        PairAt at = pair_first(p, pair, pairs);
+        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
+        for (int it = 0; it < total && !ctl->abort; ++it) {
+            const int b = at.b, words = (b & 3) + 1;
+            at.advance(p);
+            const int s = it % PP_STAGES, rs = it % PT_RAW_SLOTS;
+            if (!pp_wait_warp(&ctl->raw_full[rs], (uint32_t)(it / PT_RAW_SLOTS) & 1u, ctl, peer_abort, p.status)) break;
+            if (!pp_wait_warp(&ctl->ab_empty[s], ((uint32_t)(it / PP_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+            if (active) {
+                const uint32_t raw_slot = smem_addr(smem + PP_OFF_RAW + rs * PT_RAW_SLOT);
+                const uint32_t b_slot = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
+                const uint32_t rec = raw_slot + (uint32_t)row * PT_RAW_BOX + ((54u * (uint32_t)b) & 15u);
+                switch (words) {
+                case 1: pt_expand_lut_part<1>(rec, lut, b_slot, row, part); break;
+                case 2: pt_expand_lut_part<2>(rec, lut, b_slot, row, part); break;
+                case 3: pt_expand_lut_part<3>(rec, lut, b_slot, row, part); break;
+                default: pt_expand_lut_part<4>(rec, lut, b_slot, row, part); break;
+                }
+                // d of the pair's weights for the epilogue: part 0 this CTA's weight, part 1 the partner's (from its d box)
+                if (part < 2) {
+                    const uint32_t at_d = part ? raw_slot + PT_RAW_HEADS + (uint32_t)row * 16u + ((54u * (uint32_t)b + 52u) & 15u) : rec + 52u;
+                    const uint32_t dbits = lds_u32(at_d & ~3u) >> (8u * (at_d & 2u));
+                    const uint32_t wd_slot = smem_addr(smem + PT_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT);
+                    sts_u32(wd_slot + ((part ? rank ^ 1u : rank) * (uint32_t)(PP_WD_SLOT / 2)) + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(dbits)));
+                }
+            }
+            fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&ctl->raw_empty[rs]);
+                tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
+            }
+        }
+    } else if (warp >= PT_S_WARP0 && warp < PT_S_WARP0 + PT_S_WARPS) {
+        // ------------------------------------------------------------------ x.d of the landed activations to a ring for the epilogue
+        const int ts = threadIdx.x - 32 * PT_S_WARP0;   // 0..63, rows ts and ts + 64
+        PairAt at = pair_first(p, pair, pairs);
+        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
+        for (int it = 0; it < total && !ctl->abort; ++it) {
+            const int words = (at.b & 3) + 1;
+            at.advance(p);
+            const int s = it % PP_STAGES;
+            if (!pp_wait_warp(&ctl->a_landed[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+            const uint32_t a_slot = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT);
+            const uint32_t xd_slot = smem_addr(smem + PT_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT);
+            // record byte r sits at operand byte r + 4 (W - 1): x.d is the first word of the record
+            sts_u32(xd_slot + 4u * (uint32_t)ts, lds_u32(a_slot + sw128_offset(ts, 0) + 4u * (uint32_t)(words - 1)));
+            sts_u32(xd_slot + 4u * (uint32_t)(ts + 64), lds_u32(a_slot + sw128_offset(ts + 64, 0) + 4u * (uint32_t)(words - 1)));
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
+        }
+    } else if (warp == PT_ATMA_WARP) {
+        // ------------------------------------------------------------------ activation copies (this CTA's 128 tokens)
+        if (lane == 0) {
+            PairAt at = pair_first(p, pair, pairs);
+            int issued = 0;
+            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
+                const int s = it % PP_STAGES;
+                const uint32_t phase = (uint32_t)(it / PP_STAGES) & 1u;
+                if (!pp_wait_one(&ctl->ab_empty[s], phase ^ 1u, ctl, peer_abort, p.status)) break;
+                fence_proxy_async();
+                pp_issue_activations(&x_wide, &x_narrow, at.b, (int)at.m0 + (int)rank * PP_TOKENS, smem + PP_OFF_A + s * PP_A_SLOT, &ctl->a_landed[s]);
+                issued = it + 1;
+            }
+            for (int k = issued > PP_STAGES ? issued - PP_STAGES : 0; k < issued; ++k) mbar_wait(&ctl->a_landed[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u);
+            // stay until the even CTA's last commits have arrived on this CTA's barriers
+            for (int k = total > PP_STAGES ? total - PP_STAGES : 0; k < total && !ctl->abort; ++k)
+                if (!pp_wait_one(&ctl->ab_empty[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+        }
+    } else if (warp == PT_WTMA_WARP) {
+        // ------------------------------------------------------------------ raw weight records: this CTA's boxes and the partner's d boxes
+        if (lane == 0) {
+            PairAt at = pair_first(p, pair, pairs);
+            int issued = 0;
+            const uint32_t bytes = (uint32_t)R * (PT_RAW_BOX + 16u);
+            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
+                const int rs = it % PT_RAW_SLOTS;
+                if (!pp_wait_one(&ctl->raw_empty[rs], ((uint32_t)(it / PT_RAW_SLOTS) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+                mbar_expect_tx(&ctl->raw_full[rs], bytes);
+                // rows past N and bytes past the end of a row read as zero (digits -1 times d = 0: never stored)
+                tma_load_2d(smem + PP_OFF_RAW + rs * PT_RAW_SLOT, &w_rows, (54 * at.b) & ~15, (int)at.n0 + (int)rank * R, &ctl->raw_full[rs]);
+                tma_load_2d(smem + PP_OFF_RAW + rs * PT_RAW_SLOT + PT_RAW_HEADS, &w_heads, (54 * at.b + 52) & ~15, (int)at.n0 + (int)(rank ^ 1u) * R, &ctl->raw_full[rs]);
+                issued = it + 1;
+            }
+            for (int k = issued > PT_RAW_SLOTS ? issued - PT_RAW_SLOTS : 0; k < issued; ++k) mbar_wait(&ctl->raw_full[k % PT_RAW_SLOTS], (uint32_t)(k / PT_RAW_SLOTS) & 1u);
+        }
+    } else if (warp >= PT_MMA_WARP) {
+        // ------------------------------------------------------------------ MMA issue (even CTA only), two issuers taking the blocks in turn
+        const int q = warp - PT_MMA_WARP;
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc_q = tc::idesc_i8(2 * PP_TOKENS, 2 * R, true, true);
+            const uint32_t empty_peer = ctl_peer + (uint32_t)offsetof(PairControl, ab_empty);
+            for (int it = q; it < total && !ctl->abort; it += PP_MMA_WARPS) {
+                const int s = it % PP_STAGES, buf = it % PT_BUFS;
+                if (!pp_wait_one(&ctl->ab_full[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                if (!pp_wait_one(&ctl->tmem_empty[buf], (uint32_t)(it / PT_BUFS) & 1u, ctl, peer_abort, p.status)) break;
+                tc::fence_after_sync();
+                const uint32_t d = tmem + (uint32_t)buf * PT_BUF_COLS;
+                const uint32_t a_q = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT), b_q = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
+                const uint64_t a0 = tc::smem_desc_sw128(a_q), b0 = tc::smem_desc_sw128(b_q);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)   // the first instruction of a block overwrites the accumulators
+                    tc::mma_i8_pair(d, a0 + (uint64_t)(((k >> 2) * PP_A_SLAB + (k & 3) * 32) >> 4), b0 + (uint64_t)(((k >> 2) * PP_B_SLAB + (k & 3) * 32) >> 4), idesc_q, k > 0 ? 1u : 0u);
+                tc::mma_i8_pair(d, tc::smem_desc(a_q + PP_A_THIN, PP_A_COL, 128), tc::smem_desc(b_q + PP_B_THIN, PP_B_COL, 128), idesc_q, 1);
+                tc::commit_pair(smem_addr(&ctl->tmem_full[buf]));
+                tc::commit_pair(ctl_peer + (uint32_t)offsetof(PairControl, tmem_full) + 8u * (uint32_t)buf);
+                tc::commit_pair(smem_addr(&ctl->ab_empty[s]));
+                tc::commit_pair(empty_peer + 8u * (uint32_t)s);
+            }
+            // the epilogues of both CTAs arrive once more after the last use of every buffer: receive those arrivals
+            // before this CTA may leave (issuer 0 waits for all three buffers)
+            if (q == 0 && !ctl->abort)
+                for (int buf = 0; buf < PT_BUFS && buf < total; ++buf) {
+                    const int uses = (total - buf + PT_BUFS - 1) / PT_BUFS;
+                    if (!pp_wait_one(&ctl->tmem_empty[buf], (uint32_t)uses & 1u, ctl, peer_abort, p.status)) break;
+                }
+        }
+    } else if (warp < PT_E_WARPS) {
+        // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, quarter of the tile's weights)
+        const int quarter = warp & 3, grp = warp >> 2;       // grp = 2 (CTA whose weights these are) + (half of that CTA's weights)
+        const int half = grp >> 1, sub = grp & 1;
+        const int row = quarter * 32 + lane;                 // token row of this CTA = TMEM lane
+        const int cols = R >> 1, chunks = cols >> 3;         // this warp's weights, in chunks of eight
+        const int col0 = half * R + sub * cols;
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col0;
+        const uint32_t empty_even = ctl_even + (uint32_t)offsetof(PairControl, tmem_empty);
+        __syncwarp();
+        if (lane == 0)
+            for (int buf = 0; buf < PT_BUFS; ++buf) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);   // all buffers start free
+        uint64_t acc[PP_RMAX / 4];   // packed pairs of fp32: up to 40 weights
+        int it = 0;
+        bool ok = true;
+        for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
+            const int tile = pair + t * pairs;
+            const long long n0 = (long long)(tile / p.m_tiles) * p.w + col0;
+            const long long m = (long long)(tile % p.m_tiles) * (2 * PP_TOKENS) + (long long)rank * PP_TOKENS + row;
+#pragma unroll
+            for (int k = 0; k < PP_RMAX / 4; ++k) acc[k] = 0ull;
+            for (int b = 0; b < nb && ok; ++b, ++it) {
+                const int buf = it % PT_BUFS;
+                if (!pp_wait_warp_relaxed(&ctl->tmem_full[buf], (uint32_t)(it / PT_BUFS) & 1u, ctl, peer_abort, p.status)) { ok = false; break; }
+                tc::fence_after_sync();
+                const float xd = reinterpret_cast<const float *>(smem + PT_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT)[row];
+                const uint64_t *wd = reinterpret_cast<const uint64_t *>(smem + PT_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT + half * (PP_WD_SLOT / 2)) + sub * (cols >> 1);
+                const uint64_t xd2 = pack2(xd, xd);
+                const uint32_t from = lane_base + (uint32_t)(buf * PT_BUF_COLS);
+#pragma unroll
+                for (int c = 0; c < PP_RMAX / 16; ++c) {
+                    if (c < chunks) {
+                        uint32_t v[8];
+                        tc::tmem_ld8(from + 8 * c, v);
+                        tc::tmem_ld_wait();
+                        if (c + 1 == chunks) {   // everything is read: the buffer goes back before the last arithmetic
+                            tc::fence_before_sync();
+                            __syncwarp();
+                            if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
+                        }
+#pragma unroll
+                        for (int k = 0; k < 8; k += 2)   // acc += f32(isum) * (d * x.d)
+                            acc[(8 * c + k) >> 1] = fma2(ints_to_float2(v[k], v[k + 1]), mul2(wd[(8 * c + k) >> 1], xd2), acc[(8 * c + k) >> 1]);
+                    }
+                }
+            }
+            if (!ok) break;
+            if (m < p.m) {
+                float *out = p.y + (size_t)m * p.ldy + n0;
+                const bool vec = (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+#pragma unroll
+                for (int k = 0; k < PP_RMAX / 2; k += 4) {
+                    if (k < cols) {
+                        if (vec && n0 + k + 4 <= p.n) {
+                            *reinterpret_cast<ulonglong2 *>(out + k) = make_ulonglong2(acc[k >> 1], acc[(k >> 1) + 1]);
+                        } else {
+                            float a0, a1, a2, a3;
+                            unpack2(acc[k >> 1], a0, a1);
+                            unpack2(acc[(k >> 1) + 1], a2, a3);
+                            if (n0 + k < p.n) out[k] = a0;
+                            if (n0 + k + 1 < p.n) out[k + 1] = a1;
+                            if (n0 + k + 2 < p.n) out[k + 2] = a2;
+                            if (n0 + k + 3 < p.n) out[k + 3] = a3;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync_all();
+    if (warp == PT_MMA_WARP) {
+        __syncwarp();
+        if (tmem_ok) tc::tmem_free(tmem, PP_TMEM_COLS);
+    }
+}
+
+// w in {32, 64, 96, 128, 160} for TQ1_0: minimise (rounds of the grid) x (fixed part + w), ties to the wider tile
+int pick_tile_width_tq1(long long n, int m_tiles, int pairs) {
+    int best = 32;
+    long long best_cost = -1;
+    for (int w = 32; w <= 2 * PP_RMAX; w += 32) {
+        const long long tiles = (long long)m_tiles * ((n + w - 1) / w);
+        const long long cost = ((tiles + pairs - 1) / pairs) * (160 + w);
+        if (best_cost < 0 || cost <= best_cost) { best = w; best_cost = cost; }
+    }
+    return best;
+}
+
 // w in {16, 32, 48, 64, 80}.  A block costs a fixed part (hand-offs, activations, the per-token work) plus a part that
 // grows with w; measured, the fixed part is about the size of the variable part at w = 80.  Pick the w that minimises
 // (rounds of the grid) x (80 + w), ties to the wider tile.
@@ -585,14 +969,58 @@ int pick_tile_width(long long n, int m_tiles, int pairs) {
 }  // namespace
 
 bool prefill_pair_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq) {
+    // TQ1_0: K a multiple of 2048 makes the weight rows whole 16-byte multiples (TMA boxes over the raw records)
+    if (fmt == F_TQ1_0)
+        return m > PP_TOKENS && k > 0 && k % 2048 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
+               (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
     // above 128 tokens a pair's second CTA has work; K a multiple of 1024 keeps every Q8_K row a whole number of 16-byte
     // units (TMA boxes), and Q4_K rows of 16-byte multiples at a 16-byte aligned base let TMA fetch the raw records
     return fmt == F_Q4_K && m > PP_TOKENS && k > 0 && k % 1024 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
            (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
 }
 
+static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
+    if (!a.powers) return cudaErrorInvalidValue;
+    cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_tq1_kernel), PT_SMEM);
+    if (e != cudaSuccess) return e;
+    int pairs = 0;
+    {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3((unsigned)sm_count & ~1u);
+        probe.blockDim = dim3(PT_THREADS);
+        probe.dynamicSmemBytes = PT_SMEM;
+        if (cudaOccupancyMaxActiveClusters(&pairs, prefill_pair_tq1_kernel, &probe) != cudaSuccess) { cudaGetLastError(); pairs = sm_count / 2; }
+        if (pairs < 1) return cudaErrorNotSupported;
+        if (pairs > sm_count / 2) pairs = sm_count / 2;
+    }
+    PairParams p;
+    p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
+    p.m_tiles = (int)((a.m + 2 * PP_TOKENS - 1) / (2 * PP_TOKENS));
+    p.w = pick_tile_width_tq1(a.n, p.m_tiles, pairs);
+    p.n_tiles = (int)((a.n + p.w - 1) / p.w);
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles < pairs) pairs = (int)tiles;
+    CUtensorMap x_wide, x_narrow, w_rows, w_heads;
+    e = encode_tile_map(&x_wide, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
+                        (unsigned long long)p.nb * 292, 32, PP_TOKENS, true);
+    if (e == cudaSuccess)
+        e = encode_tile_map(&x_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
+                            (unsigned long long)p.nb * 292, 4, PP_TOKENS, false);
+    // the weight matrix as (n) rows of 54 * nb bytes
+    if (e == cudaSuccess)
+        e = encode_tile_map(&w_rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.w, (unsigned long long)p.nb * 54, (unsigned long long)a.n,
+                            (unsigned long long)p.nb * 54, PT_RAW_BOX, (unsigned)(p.w / 2), false);
+    if (e == cudaSuccess)
+        e = encode_tile_map(&w_heads, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.w, (unsigned long long)p.nb * 54, (unsigned long long)a.n,
+                            (unsigned long long)p.nb * 54, 16, (unsigned)(p.w / 2), false);
+    if (e != cudaSuccess) return e;
+    prefill_pair_tq1_kernel<<<2 * pairs, PT_THREADS, PT_SMEM, stream>>>(p, a.powers, x_wide, x_narrow, w_rows, w_heads);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!prefill_pair_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
+    if (a.fmt == F_TQ1_0) return launch_prefill_pair_tq1(a, sm_count, stream);
     cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_SMEM);
     if (e != cudaSuccess) return e;
     // how many pairs the device can hold at once (one CTA per SM: the shared memory of a CTA fills an SM)
