@@ -140,7 +140,8 @@ int production_mul_mat_tq1_0_lane16_decode(const uint8_t *W, const float *X, uin
 int production_mul_mat_q4_0(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 int production_mul_mat_q8_0(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
 int production_mul_mat_q4_k_staged(const uint8_t *W, const float *X, uint8_t *Xq, float *Y, size_t N, size_t K, size_t M);
-/* examples/kernels/mul_mat/tq1_0.py:10-64            mul_mat_runtime.cpp:534-538 */
+/* examples/kernels/mul_mat/tq1_0.py:10-64            mul_mat_runtime.cpp:534-538
+ * (tensor cores from 32 tokens on when K is a multiple of 1024; CTA pairs above 128 tokens when K is a multiple of 2048) */
 int production_mul_mat_tq1_0(const uint8_t *W, const float *X, uint8_t *Xq, const uint32_t *powers,
                              float *Y, size_t N, size_t K, size_t M);
 /* examples/kernels/mul_mat/iq2_xxs_staged.py:9-97    mul_mat_runtime.cpp:458-473
