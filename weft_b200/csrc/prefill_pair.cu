@@ -104,25 +104,21 @@ struct PairControl {
     uint64_t raw_empty[PP_RAW_SLOTS];    // expander warps of this CTA are done reading the slot
     uint64_t ab_full[PP_STAGES];         // EVEN CTA's copy is the live one: expander + specials warps of both CTAs
     uint64_t ab_empty[PP_STAGES];        // both copies live: the MMAs that read the slot have completed
-    uint64_t tmem_full[3];               // both copies live: the buffer's accumulators are complete (Q4_K uses two buffers, TQ1_0 three)
-    uint64_t tmem_empty[3];              // EVEN CTA's copy is the live one: epilogue warps of both CTAs
+    uint64_t tmem_full[2];               // both copies live: the buffer's accumulators are complete
+    uint64_t tmem_empty[2];              // EVEN CTA's copy is the live one: epilogue warps of both CTAs
     uint32_t tmem_base;
     volatile int abort;
 };
 static_assert(sizeof(PairControl) <= PP_CONTROL, "control block");
 
-// Bounded wait by one thread; gives up as soon as another role (of either CTA) has raised the abort flag.
-__device__ __forceinline__ bool pp_wait_one(uint64_t *bar, uint32_t parity, PairControl *ctl, uint32_t peer_abort, int *status) {
-    const uint32_t addr = smem_addr(bar);
-    for (uint32_t i = 0; i < (1u << 26); ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-        if (done) return true;
-        if ((i & 63u) == 63u && ctl->abort) return false;
+// Bounded wait by one thread; gives up as soon as another role (of either CTA) has raised the abort flag.  The suspending
+// form of the wait: a lane that spins on test_wait issues an instruction every few cycles and takes a third of its
+// scheduler's issue slots from the warps that work.
+template <class Control>
+__device__ __forceinline__ bool pp_wait_one(uint64_t *bar, uint32_t parity, Control *ctl, uint32_t peer_abort, int *status) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 15u) == 15u && ctl->abort) return false;
     }
     ctl->abort = 1;
     tc::st_cluster_u32(peer_abort, 1u);
@@ -131,21 +127,22 @@ __device__ __forceinline__ bool pp_wait_one(uint64_t *bar, uint32_t parity, Pair
 }
 // The same for a whole warp: every lane waits on the barrier itself with the suspending form (a waiting warp then
 // takes no issue slots from the working ones; measured 214 -> 159 us per launch against one polling lane per warp).
-__device__ __forceinline__ bool pp_wait_warp(uint64_t *bar, uint32_t parity, PairControl *ctl, uint32_t peer_abort, int *status) {
+template <class Control>
+__device__ __forceinline__ bool pp_wait_warp(uint64_t *bar, uint32_t parity, Control *ctl, uint32_t peer_abort, int *status) {
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (ctl->abort) return false;
+        if ((i & 7u) == 7u && ctl->abort) return false;
     }
     if ((threadIdx.x & 31) == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(status, ST_WAIT_TIMEOUT); }
     return false;
 }
 
-// For a role with slack (the TQ1_0 epilogue, three accumulator buffers deep): sleep between polls, leaving the issue slots to the
-// expanders (measured 429 -> 412 us with the arithmetic decode)
-__device__ __forceinline__ bool pp_wait_warp_relaxed(uint64_t *bar, uint32_t parity, PairControl *ctl, uint32_t peer_abort, int *status) {
+// For a role with slack: sleep between polls, leaving the issue slots to the roles that the kernel waits for
+template <class Control>
+__device__ __forceinline__ bool pp_wait_warp_relaxed(uint64_t *bar, uint32_t parity, Control *ctl, uint32_t peer_abort, int *status) {
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (ctl->abort) return false;
+        if ((i & 7u) == 7u && ctl->abort) return false;
         __nanosleep(200);
     }
     if ((threadIdx.x & 31) == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(status, ST_WAIT_TIMEOUT); }
@@ -582,107 +579,245 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
 
 // ================================================================================================================
 // TQ1_0 x Q8_K on CTA pairs (production_mul_mat_tq1_0, examples/kernels/mul_mat/tq1_0.py; per block the math of
-// examples/kernels/vec_dot/tq1_0_q8_k.py:9-55, GGML ggml-cpu/quants.c:430-480).  Same pipeline as the Q4_K kernel above with
-// what the format makes simpler: the weight operand is the base-3 digits minus one (one limb, no min term), so a tile
-// is 256 tokens x w weights with w up to 160 (each CTA expands w/2 weights into w/2 operand rows, N = w), an accumulator
-// buffer is w <= 160 columns and THREE of them fit in tensor memory, the per-token warps only copy x.d, and the
-// epilogue is acc += f32(isum) * (d * x.d) on one column per weight.  Sixteen epilogue warps (lane quarter x quarter of
-// the tile's weights, at most 40 accumulators per thread) and ten expander warps, 32 warps at 64 registers per thread.
-// The expansion is what the kernel waits for: turning 54 bytes into 256 int8 digits is bound by the integer pipe, so the
-// digits come from a table (see pt_expand_lut) rather than from the multiplications of the decode kernels.
-// 512 x 28672 x 8192: 318 us (the single-CTA kernel of prefill.cu: 582 us; this kernel with the arithmetic decode: 421 us).
+// examples/kernels/vec_dot/tq1_0_q8_k.py:9-55, GGML ggml-cpu/quants.c:430-480).  The weight operand is the base-3 digits
+// minus one (one limb, no min term): a tile is 256 tokens x w weights with w up to 160 (each CTA expands w/2 weights into
+// w/2 operand rows, N = w), an accumulator buffer is w <= 160 columns and THREE of them fit in tensor memory; the epilogue
+// is acc += f32(isum) * (d * x.d) on one column per weight.
+//
+// Activations come from PLANES that a small kernel makes of the Q8_K records before this one runs: the codes as an
+// (M, K) int8 matrix, x.d as an (K/256, M) float matrix.  The codes of a block are then 256 aligned bytes per token --
+// two 128-byte-swizzled TMA boxes, eight K = 32 MMAs, nothing shifted -- and the expanded weights are written as whole
+// 16-byte operand chunks.  (The Q8_K records themselves start every block at a different offset from a 16-byte
+// boundary, which the Q4_K kernel above meets by shifting the weight operand.)
+//
+// Per 256-block and CTA:
+//   raw weights  two TMA box copies (w/2 records in 80-byte boxes; the 16-byte boxes with the partner's d) into a ring
+//   activations  two TMA box copies (128 tokens x 128 bytes) into a ring of their own; the odd CTA's MMA warp forwards
+//                the landing of its boxes to the even CTA's barrier
+//   expanders    12 warps, four tasks per weight: bytes 0-15, 16-31, 32-47 of the record (16 table lookups, five operand
+//                chunks each) and the qh word with the two scales.  A warp is of one task kind; the lanes of a quarter
+//                warp store their 16-byte chunks to eight different rows, whose swizzled positions never meet in a bank.
+//                The digits come from a table in shared memory (entry v = the five digits of byte value v, built from the
+//                caller's powers), sixteen copies so that the lookups of a half warp fall into different banks: the
+//                expansion is bound by shared-memory wavefronts and by the integer pipe, not by latency.
+//   MMA          one lane of the even CTA (two issuers taking the blocks in turn): 8 int8 K = 32 steps, N = w
+//   epilogue     16 warps = 4 lane quarters x 4 quarters of the tile's weights, up to 40 accumulators per thread; x.d by
+//                one global load per thread and block, issued a block ahead
 // Raw records: 54 bytes, rows of K/256 * 54 bytes (a multiple of 16 when K % 2048 == 0).  Record b of a row starts
-// (54 b) % 16 bytes past a 16-byte boundary; an 80-byte box from that boundary holds it whole.  Its f16 d (bytes 52, 53)
+// O = (54 b) % 16 bytes past a 16-byte boundary; an 80-byte box from that boundary holds it whole.  Its f16 d (bytes 52, 53)
 // lies inside the 16-byte box at (54 b + 52) rounded down to 16: that box is fetched for the PARTNER's weights, so each
-// CTA has the scales of all w weights without touching the partner's shared memory.
-constexpr int PT_E_WARPS = 16, PT_X_WARPS = 10, PT_S_WARPS = 2;
-constexpr int PT_X_WARP0 = PT_E_WARPS, PT_S_WARP0 = PT_X_WARP0 + PT_X_WARPS;
-constexpr int PT_ATMA_WARP = PT_S_WARP0 + PT_S_WARPS, PT_WTMA_WARP = PT_ATMA_WARP + 1, PT_MMA_WARP = PT_WTMA_WARP + 1;
+// CTA has the scales of all w weights without touching the partner's shared memory.  O takes eight values (b % 8); the
+// blocks of a tile are taken as 0, 8, 16, ..., 1, 9, ... so that the expanders stay in one of their eight code variants.
+constexpr int PT_E_WARPS = 16, PT_X_WARPS = 12;
+constexpr int PT_X_WARP0 = PT_E_WARPS;
+constexpr int PT_ATMA_WARP = PT_X_WARP0 + PT_X_WARPS, PT_WTMA_WARP = PT_ATMA_WARP + 1, PT_MMA_WARP = PT_WTMA_WARP + 1;
 constexpr int PT_THREADS = 32 * (PT_MMA_WARP + PP_MMA_WARPS);   // 32 warps
+constexpr int PT_A_STAGES = 3, PT_B_STAGES = 3, PT_RAW_SLOTS = 3, PT_RING = 8;
 constexpr int PT_BUFS = 3, PT_BUF_COLS = 160;
+// Registers: the kernel starts with 64 per thread (1024 threads); the roles then trade them in whole warp groups of four
+// warps: the epilogue (warps 0-15) holds 40 accumulators and 16 columns in flight, the copy and MMA lanes need few.
+constexpr int PT_E_REGS = 88, PT_X_REGS = 40, PT_IO_REGS = 24;
+static_assert(32 * (PT_E_WARPS * PT_E_REGS + PT_X_WARPS * PT_X_REGS + 4 * PT_IO_REGS) <= 65536 && PT_E_WARPS % 4 == 0 && PT_X_WARPS % 4 == 0, "register trade between the warp groups");
+constexpr int PT_A_SLAB = 128 * 128, PT_A_SLOT = 2 * PT_A_SLAB;            // 32 KB
+constexpr int PT_B_SLAB = PP_RMAX * 128, PT_B_SLOT = 2 * PT_B_SLAB;        // 20 KB
 constexpr int PT_RAW_BOX = 80;                                  // bytes per record box
 constexpr int PT_RAW_HEADS = PP_RMAX * PT_RAW_BOX;              // after the record boxes: the 16-byte boxes with the partner's d
 constexpr int PT_RAW_SLOT = PT_RAW_HEADS + PP_RMAX * 16;        // 7680 B
-constexpr int PT_RAW_SLOTS = 3;
-constexpr int PT_OFF_WD = PP_OFF_RAW + PT_RAW_SLOTS * PT_RAW_SLOT;
-constexpr int PT_OFF_XD = PT_OFF_WD + PP_RING * PP_WD_SLOT;     // d of the pair's 2 x 80 weights: 640 B per slot
-constexpr int PT_OFF_LUT = PT_OFF_XD + PP_RING * PP_XD_SLOT;    // digits of every byte value, two copies interleaved
-constexpr int PT_LUT_COPIES = 4;
+constexpr int PT_WD_SLOT = 2 * PP_RMAX * 4;                     // d of the pair's 2 x 80 weights as floats
+constexpr int PT_LUT_COPIES = 16;
+constexpr int PT_OFF_A = 1024;
+constexpr int PT_OFF_B = PT_OFF_A + PT_A_STAGES * PT_A_SLOT;
+constexpr int PT_OFF_RAW = PT_OFF_B + PT_B_STAGES * PT_B_SLOT;
+constexpr int PT_OFF_WD = PT_OFF_RAW + PT_RAW_SLOTS * PT_RAW_SLOT;
+constexpr int PT_OFF_LUT = PT_OFF_WD + PT_RING * PT_WD_SLOT;
 constexpr int PT_SMEM = PT_OFF_LUT + 256 * 8 * PT_LUT_COPIES;
-static_assert(PT_SMEM <= 227 * 1024 && PT_RAW_SLOT % 128 == 0, "shared memory budget of the TQ1_0 kernel");
+static_assert(PT_SMEM <= 227 * 1024 && PT_RAW_SLOT % 128 == 0 && PT_B_SLAB % 1024 == 0 && PT_OFF_B % 1024 == 0 && PT_OFF_LUT % 128 == 0,
+              "shared memory of the TQ1_0 kernel");
+static_assert(PT_RING > PT_B_STAGES + PT_BUFS, "the expanders run at most B slots + accumulator buffers ahead of the epilogue");
 
-// Table form.  Entry v of the table (built from the caller's powers when the kernel starts) holds the five digits of byte value v,
-// minus one, as int8: bytes 0..3 digits 0..3, byte 4 digit 4.  A task takes four bytes of each of its record words, looks them up and
-// transposes the 4 x 5 digits into five stream words with byte permutes: about 4 integer instructions per stream word where the
-// arithmetic form needs 10 (the expansion is bound by the integer pipe).  Stream word g goes to operand word g + W by a 4-byte
-// store; PART 3 also writes the zeros in front of stream word 0 and behind stream word 63.
-// PART 0: record words 0..3 (stream words 8 n + s), 1: words 4..7, 2: words 8..11 (40 + 4 n + s - 8), 3: the qh word (60 + n).
+struct TqParams {
+    float *y;              // (m, ldy)
+    long long n, m, ldy;
+    int nb;                // 256-blocks per row
+    int m_tiles, n_tiles;  // tiles of 256 tokens, of w weights
+    int w;                 // weights per tile (multiple of 32, <= 2 * PP_RMAX)
+    const float *xd;       // (nb, xd_pitch): x.d of every token and block
+    long long xd_pitch;
+    int *status;
+};
+
+struct TqControl {
+    uint64_t a_full[PT_A_STAGES];        // this CTA's activation boxes (transaction bytes)
+    uint64_t a_peer[PT_A_STAGES];        // EVEN CTA's copy is the live one: the odd CTA's boxes have landed
+    uint64_t a_empty[PT_A_STAGES];       // both copies live: the MMAs that read the slot have completed
+    uint64_t raw_full[PT_RAW_SLOTS];     // this CTA's raw records (transaction bytes)
+    uint64_t raw_empty[PT_RAW_SLOTS];    // expander warps of this CTA are done reading the slot
+    uint64_t b_full[PT_B_STAGES];        // EVEN CTA's copy is the live one: expander warps of both CTAs
+    uint64_t b_empty[PT_B_STAGES];       // both copies live
+    uint64_t tmem_full[PT_BUFS];         // both copies live: the buffer's accumulators are complete
+    uint64_t tmem_empty[PT_BUFS];        // EVEN CTA's copy is the live one: epilogue warps of both CTAs
+    uint32_t tmem_base;
+    volatile int abort;
+};
+static_assert(sizeof(TqControl) <= PT_OFF_A, "control block");
+
+// Blocks of the pair's work list: tiles round-robin over the pairs; inside a tile the blocks go 0, 8, 16, ..., 1, 9, ...
+struct TqAt {
+    int n0, m0;          // first weight and first token of the tile (both below 2^31)
+    int b, tile, pairs;
+    __device__ __forceinline__ void set_tile(const TqParams &p, int t) {
+        tile = t;
+        n0 = (t / p.m_tiles) * p.w;
+        m0 = (t % p.m_tiles) * (2 * PP_TOKENS);
+    }
+    __device__ __forceinline__ void advance(const TqParams &p) {
+        b += 8;
+        if (b >= p.nb) {
+            b = (b & 7) + 1;
+            if (b == 8) { b = 0; set_tile(p, tile + pairs); }
+        }
+    }
+};
+__device__ __forceinline__ TqAt tq_first(const TqParams &p, int pair, int pairs) {
+    TqAt at;
+    at.b = 0;
+    at.pairs = pairs;
+    at.set_tile(p, pair);
+    return at;
+}
+
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
 }
-template <int W>
-__device__ __forceinline__ void pt_store_word(uint32_t base, uint32_t x7, int g, uint32_t v) {   // g: stream word index, compile time
-    const int pos = g + W, chunk = pos >> 2;
-    const uint32_t at = chunk < 16 ? base + (uint32_t)(chunk >> 3) * PP_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7) + 4u * (uint32_t)(pos & 3) : 0u;
-    if (chunk < 16) sts_u32(at, v);
+// Table entry of byte i of a record word: {digits 0..3 minus one as int8, digit 4 minus one}.  `lut` already points at the
+// lane's copy; the copies of a value's 8-byte entry lie side by side.
+__device__ __forceinline__ void tq_lookup(uint32_t lut, uint32_t word, int i, uint32_t &x, uint32_t &y) {
+    const uint32_t at = lut + prmt(word, 0u, 0x4440u + (uint32_t)i) * (8u * PT_LUT_COPIES);
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(x), "=r"(y) : "r"(at));
 }
-template <int W, int PART>
-__device__ __forceinline__ void pt_expand_lut(uint32_t rec, uint32_t lut, uint32_t b_slot, int row) {
-    const uint32_t base = b_slot + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
-    const uint32_t x7 = (uint32_t)(row & 7) << 4;
-    const uint32_t thin = b_slot + PP_B_THIN + (uint32_t)row * 16u;
-    constexpr int NW = PART == 3 ? 1 : 4;            // record words of this task
-    // the task's record words: aligned 4-byte loads and a 16-bit funnel shift when the record starts in the middle of a word
-    const uint32_t first = rec + 16u * (uint32_t)PART, aligned = first & ~3u;
-    uint32_t raw[NW + 1], w[NW];
+// The four record words that start O + 16 PART bytes into the row's box (O even, compile time): two aligned 16-byte loads
+// (a quarter warp's rows are 80 bytes apart: eight different bank groups) and 16-bit funnel shifts.
+template <int O>
+__device__ __forceinline__ void tq_record_words(uint32_t src, uint32_t (&w)[4]) {
+    const uint4 lo = lds128(src), hi = lds128(src + 16u);
+    const uint32_t r[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+    constexpr int j = O >> 2;
 #pragma unroll
-    for (int i = 0; i <= NW; ++i) raw[i] = lds_u32(aligned + 4u * (uint32_t)i);
+    for (int i = 0; i < 4; ++i) w[i] = (O & 2) ? __funnelshift_r(r[j + i], r[j + i + 1], 16) : r[j + i];
+}
+// Heavy task: record bytes 16 PART .. 16 PART + 15 -> five operand chunks (digit n of those sixteen weights' bytes:
+// elements 32 n + 16 PART + [0, 16) for PART 0 and 1, 160 + 16 n + [0, 16) for PART 2).
+template <int PART, int O>
+__device__ __forceinline__ void tq_expand_heavy(uint32_t box, uint32_t lut, uint32_t b_slot, int row) {
+    uint32_t w[4];
+    tq_record_words<O>(box + 16u * (uint32_t)PART, w);
+    uint32_t digit[5][4];
 #pragma unroll
-    for (int i = 0; i < NW; ++i) w[i] = (first & 2u) ? __funnelshift_r(raw[i], raw[i + 1], 16) : raw[i];
-    uint32_t thin_words[4] = {0u, 0u, 0u, 0u};      // operand words 64..67 (PART 3)
-#pragma unroll
-    for (int s = 0; s < NW; ++s) {
+    for (int s = 0; s < 4; ++s) {
         uint32_t x[4], y[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t at = lut + prmt(w[s], 0u, 0x4440u + (uint32_t)i) * (8u * PT_LUT_COPIES);   // the copies of a value's 8-byte entry lie side by side
-            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(x[i]), "=r"(y[i]) : "r"(at));
-        }
+        for (int i = 0; i < 4; ++i) tq_lookup(lut, w[s], i, x[i], y[i]);
         const uint32_t t0 = prmt(x[0], x[1], 0x5140u), t1 = prmt(x[0], x[1], 0x7362u);
         const uint32_t t2 = prmt(x[2], x[3], 0x5140u), t3 = prmt(x[2], x[3], 0x7362u);
-        uint32_t digit[5];
-        digit[0] = prmt(t0, t2, 0x5410u); digit[1] = prmt(t0, t2, 0x7632u);
-        digit[2] = prmt(t1, t3, 0x5410u); digit[3] = prmt(t1, t3, 0x7632u);
-        digit[4] = prmt(prmt(y[0], y[1], 0x0040u), prmt(y[2], y[3], 0x0040u), 0x5410u);
-#pragma unroll
-        for (int n = 0; n < (PART == 3 ? 4 : 5); ++n) {
-            const int g = PART < 2 ? 8 * n + 4 * PART + s : PART == 2 ? 40 + 4 * n + s : 60 + n;
-            if (g + W < 64) pt_store_word<W>(base, x7, g, digit[n]);
-            else thin_words[g + W - 64] = digit[n];
-        }
+        digit[0][s] = prmt(t0, t2, 0x5410u); digit[1][s] = prmt(t0, t2, 0x7632u);
+        digit[2][s] = prmt(t1, t3, 0x5410u); digit[3][s] = prmt(t1, t3, 0x7632u);
+        digit[4][s] = prmt(prmt(y[0], y[1], 0x0040u), prmt(y[2], y[3], 0x0040u), 0x5410u);
     }
-    if (PART == 3) {
-        // zeros in front of the first stream word, the carried words and zeros in the thin chunk
+    const uint32_t base = b_slot + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(row & 7) << 4;
 #pragma unroll
-        for (int k = 0; k < W; ++k) sts_u32(base + (((uint32_t)0 << 4) ^ x7) + 4u * (uint32_t)k, 0u);
-        sts_u128(thin, thin_words[0], thin_words[1], thin_words[2], thin_words[3]);
+    for (int n = 0; n < 5; ++n) {
+        const int chunk = PART < 2 ? 2 * n + PART : 10 + n;
+        sts_u128(base + (uint32_t)(chunk >> 3) * PT_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7), digit[n][0], digit[n][1], digit[n][2], digit[n][3]);
     }
 }
-template <int W>
-__device__ __forceinline__ void pt_expand_lut_part(uint32_t rec, uint32_t lut, uint32_t b_slot, int row, int part) {
-    if (part == 0) pt_expand_lut<W, 0>(rec, lut, b_slot, row);
-    else if (part == 1) pt_expand_lut<W, 1>(rec, lut, b_slot, row);
-    else if (part == 2) pt_expand_lut<W, 2>(rec, lut, b_slot, row);
-    else pt_expand_lut<W, 3>(rec, lut, b_slot, row);
+// Light task: the qh word (record bytes 48..51: digit n of byte m is element 240 + 4 n + m, operand chunk 15) and the two
+// scales for the epilogue: this weight's d (record bytes 52, 53) and the d of the partner's weight of the same index.
+template <int O>
+__device__ __forceinline__ void tq_expand_light(uint32_t box, uint32_t head, uint32_t lut, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner, int row) {
+    constexpr int at_qh = O + 48, at_d = O + 52, at_pd = (O + 52) & 15;
+    const uint32_t q0 = lds_u32(box + (uint32_t)(at_qh & ~3)), q1 = lds_u32(box + (uint32_t)(at_qh & ~3) + 4u);
+    const uint32_t qh = (at_qh & 2) ? __funnelshift_r(q0, q1, 16) : q0;
+    const uint32_t d_mine = (at_d & 2) ? q1 >> 16 : q1;     // bytes O + 52, 53: the half word after qh
+    const uint32_t d_partner = lds_u32(head + (uint32_t)(at_pd & ~3)) >> (8 * (at_pd & 2));
+    uint32_t x[4], y[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) tq_lookup(lut, qh, i, x[i], y[i]);
+    const uint32_t t0 = prmt(x[0], x[1], 0x5140u), t1 = prmt(x[0], x[1], 0x7362u);
+    const uint32_t t2 = prmt(x[2], x[3], 0x5140u), t3 = prmt(x[2], x[3], 0x7362u);
+    const uint32_t base = b_slot + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(row & 7) << 4;
+    sts_u128(base + PT_B_SLAB + ((7u << 4) ^ x7), prmt(t0, t2, 0x5410u), prmt(t0, t2, 0x7632u), prmt(t1, t3, 0x5410u), prmt(t1, t3, 0x7632u));
+    sts_u32(wd_mine + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(d_mine & 0xffffu)));
+    sts_u32(wd_partner + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(d_partner & 0xffffu)));
+}
+template <int O>
+__device__ __forceinline__ void tq_expand(int part, uint32_t box, uint32_t head, uint32_t lut, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner, int row) {
+    if (part == 0) tq_expand_heavy<0, O>(box, lut, b_slot, row);
+    else if (part == 1) tq_expand_heavy<1, O>(box, lut, b_slot, row);
+    else if (part == 2) tq_expand_heavy<2, O>(box, lut, b_slot, row);
+    else tq_expand_light<O>(box, head, lut, b_slot, wd_mine, wd_partner, row);
 }
 
+// Epilogue pieces.  Columns [g, g + 16) of the warp's accumulators (eight when the warp has only eight left) into v.
+__device__ __forceinline__ void tq_load_columns(uint32_t from, int g, int cols, uint32_t (&v)[16]) {
+    if (g + 16 <= cols) tc::tmem_ld16(from + (uint32_t)g, v);
+    else {
+        uint32_t v8[8];
+        tc::tmem_ld8(from + (uint32_t)g, v8);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { v[k] = v8[k]; v[8 + k] = 0u; }
+    }
+}
+__device__ __forceinline__ void tq_release(uint32_t empty_bar, int lane) {
+    tc::fence_before_sync();
+    __syncwarp();
+    if (lane == 0) tc::mbar_arrive_cluster(empty_bar);
+}
+// acc += f32(isum) * (d * x.d) for columns [G, G + 16) (or [G, G + 8)); wd: the weights' d as floats in shared memory
+template <int G>
+__device__ __forceinline__ void tq_scale_add(uint64_t (&acc)[PP_RMAX / 4], const uint32_t (&v)[16], int cols, uint32_t wd, uint64_t xd2) {
+    const bool wide = G + 16 <= cols;
+#pragma unroll
+    for (int k = 0; k < 16; k += 4) {
+        if (G + k < PP_RMAX / 2 && (wide || k < 8)) {
+            const uint4 s4 = lds128(wd + 4u * (uint32_t)(G + k));
+            acc[(G + k) >> 1] = fma2(ints_to_float2(v[k], v[k + 1]), mul2(pack2(__uint_as_float(s4.x), __uint_as_float(s4.y)), xd2), acc[(G + k) >> 1]);
+            acc[((G + k) >> 1) + 1] = fma2(ints_to_float2(v[k + 2], v[k + 3]), mul2(pack2(__uint_as_float(s4.z), __uint_as_float(s4.w)), xd2), acc[((G + k) >> 1) + 1]);
+        }
+    }
+}
+
+// Q8_K records -> planes: codes (m, k) int8 and x.d (k / 256, pitch) float.  One thread per 16 codes.
+__global__ void __launch_bounds__(256) q8k_planes_kernel(const uint8_t *__restrict__ xq, int8_t *__restrict__ codes, float *__restrict__ xd, long long m, int nb, long long pitch) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long record = idx >> 4;
+    const int c = (int)(idx & 15);
+    if (record >= m * nb) return;
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + record * 292);   // records are 4-byte aligned
+    const uint4 v = make_uint4(src[1 + 4 * c], src[2 + 4 * c], src[3 + 4 * c], src[4 + 4 * c]);
+    *reinterpret_cast<uint4 *>(codes + record * 256 + 16 * c) = v;
+    if (c == 0) {
+        const long long t = record / nb;
+        xd[(record - t * nb) * pitch + t] = __uint_as_float(src[0]);
+    }
+}
+
+#ifdef PT_TRACE
+__device__ unsigned long long pt_trace[2][32][96][4];
+__device__ __forceinline__ unsigned long long pt_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TR(slot) do { if (pair == 0 && (threadIdx.x & 31) == 0 && it >= 32 && it < 128) pt_trace[rank][threadIdx.x >> 5][it - 32][slot] = pt_now(); } while (0)
+#else
+#define TR(slot) do { } while (0)
+#endif
+
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PT_THREADS, 1)
-prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid_constant__ CUtensorMap x_wide, const __grid_constant__ CUtensorMap x_narrow,
+prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_constant__ CUtensorMap x_codes,
                         const __grid_constant__ CUtensorMap w_rows, const __grid_constant__ CUtensorMap w_heads) {
     extern __shared__ __align__(1024) uint8_t smem[];
-    PairControl *ctl = reinterpret_cast<PairControl *>(smem);
+    TqControl *ctl = reinterpret_cast<TqControl *>(smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = tc::cluster_ctarank();
     const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
@@ -694,24 +829,16 @@ prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid
 
     const uint32_t ctl_addr = smem_addr(ctl);
     const uint32_t ctl_even = tc::map_to_cta(ctl_addr, 0), ctl_peer = tc::map_to_cta(ctl_addr, rank ^ 1u);
-    const uint32_t peer_abort = ctl_peer + (uint32_t)offsetof(PairControl, abort);
+    const uint32_t peer_abort = ctl_peer + (uint32_t)offsetof(TqControl, abort);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < PP_STAGES; ++s) {
-            mbar_init(&ctl->a_landed[s], 1);
-            mbar_init(&ctl->ab_full[s], 2 * (PT_X_WARPS + PT_S_WARPS));
-            mbar_init(&ctl->ab_empty[s], 1);
-        }
+        for (int s = 0; s < PT_A_STAGES; ++s) { mbar_init(&ctl->a_full[s], 1); mbar_init(&ctl->a_peer[s], 1); mbar_init(&ctl->a_empty[s], 1); }
         for (int s = 0; s < PT_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 1); mbar_init(&ctl->raw_empty[s], PT_X_WARPS); }
+        for (int s = 0; s < PT_B_STAGES; ++s) { mbar_init(&ctl->b_full[s], 2 * PT_X_WARPS); mbar_init(&ctl->b_empty[s], 1); }
         for (int h = 0; h < PT_BUFS; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 2 * PT_E_WARPS); }
         ctl->abort = 0;
         ctl->tmem_base = 0xffffffffu;
         mbar_fence_init();
-    }
-    // K chunk 17 of every weight slot (operand bytes 272..287) is zero for the whole kernel
-    for (int i = threadIdx.x; i < PP_STAGES * PP_RMAX * 4; i += PT_THREADS) {
-        const int s = i / (PP_RMAX * 4), r = i % (PP_RMAX * 4);
-        reinterpret_cast<uint32_t *>(smem + PP_OFF_B + s * PP_B_SLOT + PP_B_THIN + PP_B_COL)[r] = 0u;
     }
     // the digit table, from the caller's powers: entry v = digits 0..4 of byte value v minus one, as int8
     for (int v = threadIdx.x; v < 256; v += PT_THREADS) {
@@ -725,7 +852,6 @@ prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid
 #pragma unroll
         for (int c = 0; c < PT_LUT_COPIES; ++c) reinterpret_cast<uint2 *>(smem + PT_OFF_LUT)[v * PT_LUT_COPIES + c] = make_uint2(lo, hi);
     }
-    fence_proxy_async();
     __syncthreads();
     if (warp == PT_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PP_TMEM_COLS);   // per CTA, see the Q4_K kernel
     tc::fence_before_sync();
@@ -738,36 +864,37 @@ prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid
     if (!tmem_ok) {
         // nothing: fall through to the common exit
     } else if (warp >= PT_X_WARP0 && warp < PT_X_WARP0 + PT_X_WARPS) {
-        // ------------------------------------------------------------------ expanders: four tasks per weight row (tasks [part R, (part + 1) R)
-        // are part `part` of the rows: a warp is of one part except where it straddles a multiple of R)
-        const int task = 32 * (warp - PT_X_WARP0) + lane;
-        const int part = task / R, row = task - part * R;       // tasks [part R, (part + 1) R) are part `part` of the rows
-        const bool active = task < 4 * R;
+        // ------------------------------------------------------------------ expanders: three warps per task kind
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PT_X_REGS));
+        const int xw = warp - PT_X_WARP0;
+        const int part = xw / 3, row = 32 * (xw - 3 * part) + lane;
+        const bool active = row < R;
         const uint32_t lut = smem_addr(smem + PT_OFF_LUT) + 8u * (uint32_t)(lane & (PT_LUT_COPIES - 1));
-        PairAt at = pair_first(p, pair, pairs);
-        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
+        TqAt at = tq_first(p, pair, pairs);
+        const uint32_t full_even = ctl_even + (uint32_t)offsetof(TqControl, b_full);
         for (int it = 0; it < total && !ctl->abort; ++it) {
-            const int b = at.b, words = (b & 3) + 1;
+            const int b = at.b;
             at.advance(p);
-            const int s = it % PP_STAGES, rs = it % PT_RAW_SLOTS;
+            const int s = it % PT_B_STAGES, rs = it % PT_RAW_SLOTS;
             if (!pp_wait_warp(&ctl->raw_full[rs], (uint32_t)(it / PT_RAW_SLOTS) & 1u, ctl, peer_abort, p.status)) break;
-            if (!pp_wait_warp(&ctl->ab_empty[s], ((uint32_t)(it / PP_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+            TR(0);
+            if (!pp_wait_warp(&ctl->b_empty[s], ((uint32_t)(it / PT_B_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+            TR(1);
             if (active) {
-                const uint32_t raw_slot = smem_addr(smem + PP_OFF_RAW + rs * PT_RAW_SLOT);
-                const uint32_t b_slot = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
-                const uint32_t rec = raw_slot + (uint32_t)row * PT_RAW_BOX + ((54u * (uint32_t)b) & 15u);
-                switch (words) {
-                case 1: pt_expand_lut_part<1>(rec, lut, b_slot, row, part); break;
-                case 2: pt_expand_lut_part<2>(rec, lut, b_slot, row, part); break;
-                case 3: pt_expand_lut_part<3>(rec, lut, b_slot, row, part); break;
-                default: pt_expand_lut_part<4>(rec, lut, b_slot, row, part); break;
-                }
-                // d of the pair's weights for the epilogue: part 0 this CTA's weight, part 1 the partner's (from its d box)
-                if (part < 2) {
-                    const uint32_t at_d = part ? raw_slot + PT_RAW_HEADS + (uint32_t)row * 16u + ((54u * (uint32_t)b + 52u) & 15u) : rec + 52u;
-                    const uint32_t dbits = lds_u32(at_d & ~3u) >> (8u * (at_d & 2u));
-                    const uint32_t wd_slot = smem_addr(smem + PT_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT);
-                    sts_u32(wd_slot + ((part ? rank ^ 1u : rank) * (uint32_t)(PP_WD_SLOT / 2)) + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(dbits)));
+                const uint32_t raw_slot = smem_addr(smem + PT_OFF_RAW + rs * PT_RAW_SLOT);
+                const uint32_t b_slot = smem_addr(smem + PT_OFF_B + s * PT_B_SLOT);
+                const uint32_t box = raw_slot + (uint32_t)row * PT_RAW_BOX, head = raw_slot + PT_RAW_HEADS + (uint32_t)row * 16u;
+                const uint32_t wd_slot = smem_addr(smem + PT_OFF_WD + (it & (PT_RING - 1)) * PT_WD_SLOT);
+                const uint32_t wd_mine = wd_slot + rank * (uint32_t)(PT_WD_SLOT / 2), wd_partner = wd_slot + (rank ^ 1u) * (uint32_t)(PT_WD_SLOT / 2);
+                switch (b & 7) {   // O = (54 b) % 16
+                case 0: tq_expand<0>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                case 1: tq_expand<6>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                case 2: tq_expand<12>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                case 3: tq_expand<2>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                case 4: tq_expand<8>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                case 5: tq_expand<14>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                case 6: tq_expand<4>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                default: tq_expand<10>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
                 }
             }
             fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
@@ -776,82 +903,82 @@ prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid
                 mbar_arrive(&ctl->raw_empty[rs]);
                 tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
             }
-        }
-    } else if (warp >= PT_S_WARP0 && warp < PT_S_WARP0 + PT_S_WARPS) {
-        // ------------------------------------------------------------------ x.d of the landed activations to a ring for the epilogue
-        const int ts = threadIdx.x - 32 * PT_S_WARP0;   // 0..63, rows ts and ts + 64
-        PairAt at = pair_first(p, pair, pairs);
-        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
-        for (int it = 0; it < total && !ctl->abort; ++it) {
-            const int words = (at.b & 3) + 1;
-            at.advance(p);
-            const int s = it % PP_STAGES;
-            if (!pp_wait_warp(&ctl->a_landed[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
-            const uint32_t a_slot = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT);
-            const uint32_t xd_slot = smem_addr(smem + PT_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT);
-            // record byte r sits at operand byte r + 4 (W - 1): x.d is the first word of the record
-            sts_u32(xd_slot + 4u * (uint32_t)ts, lds_u32(a_slot + sw128_offset(ts, 0) + 4u * (uint32_t)(words - 1)));
-            sts_u32(xd_slot + 4u * (uint32_t)(ts + 64), lds_u32(a_slot + sw128_offset(ts + 64, 0) + 4u * (uint32_t)(words - 1)));
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
+            TR(2);
         }
     } else if (warp == PT_ATMA_WARP) {
         // ------------------------------------------------------------------ activation copies (this CTA's 128 tokens)
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PT_IO_REGS));
         if (lane == 0) {
-            PairAt at = pair_first(p, pair, pairs);
+            TqAt at = tq_first(p, pair, pairs);
             int issued = 0;
             for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
-                const int s = it % PP_STAGES;
-                const uint32_t phase = (uint32_t)(it / PP_STAGES) & 1u;
-                if (!pp_wait_one(&ctl->ab_empty[s], phase ^ 1u, ctl, peer_abort, p.status)) break;
-                fence_proxy_async();
-                pp_issue_activations(&x_wide, &x_narrow, at.b, (int)at.m0 + (int)rank * PP_TOKENS, smem + PP_OFF_A + s * PP_A_SLOT, &ctl->a_landed[s]);
+                const int s = it % PT_A_STAGES;
+                if (!pp_wait_one(&ctl->a_empty[s], ((uint32_t)(it / PT_A_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+                TR(0);
+                uint8_t *slot = smem + PT_OFF_A + s * PT_A_SLOT;
+                mbar_expect_tx(&ctl->a_full[s], PT_A_SLOT);
+                // tokens past M read as zero
+                tma_load_2d(slot, &x_codes, 256 * at.b, at.m0 + (int)rank * PP_TOKENS, &ctl->a_full[s]);
+                tma_load_2d(slot + PT_A_SLAB, &x_codes, 256 * at.b + 128, (int)at.m0 + (int)rank * PP_TOKENS, &ctl->a_full[s]);
                 issued = it + 1;
             }
-            for (int k = issued > PP_STAGES ? issued - PP_STAGES : 0; k < issued; ++k) mbar_wait(&ctl->a_landed[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u);
-            // stay until the even CTA's last commits have arrived on this CTA's barriers
-            for (int k = total > PP_STAGES ? total - PP_STAGES : 0; k < total && !ctl->abort; ++k)
-                if (!pp_wait_one(&ctl->ab_empty[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+            // left early: let the copies in flight land (a phase that has completed already returns at once)
+            for (int k = issued > PT_A_STAGES ? issued - PT_A_STAGES : 0; k < issued; ++k) mbar_wait(&ctl->a_full[k % PT_A_STAGES], (uint32_t)(k / PT_A_STAGES) & 1u);
+            // The even CTA's commits arrive on this CTA's barriers when the MMAs complete, whoever still waits for them:
+            // stay until the last ones have landed, so that none can reach a CTA that has already left the SM.
+            for (int k = total > PT_A_STAGES ? total - PT_A_STAGES : 0; k < total && !ctl->abort; ++k)
+                if (!pp_wait_one(&ctl->a_empty[k % PT_A_STAGES], (uint32_t)(k / PT_A_STAGES) & 1u, ctl, peer_abort, p.status)) break;
         }
     } else if (warp == PT_WTMA_WARP) {
         // ------------------------------------------------------------------ raw weight records: this CTA's boxes and the partner's d boxes
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PT_IO_REGS));
         if (lane == 0) {
-            PairAt at = pair_first(p, pair, pairs);
+            TqAt at = tq_first(p, pair, pairs);
             int issued = 0;
             const uint32_t bytes = (uint32_t)R * (PT_RAW_BOX + 16u);
             for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
                 const int rs = it % PT_RAW_SLOTS;
                 if (!pp_wait_one(&ctl->raw_empty[rs], ((uint32_t)(it / PT_RAW_SLOTS) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+                TR(0);
                 mbar_expect_tx(&ctl->raw_full[rs], bytes);
                 // rows past N and bytes past the end of a row read as zero (digits -1 times d = 0: never stored)
-                tma_load_2d(smem + PP_OFF_RAW + rs * PT_RAW_SLOT, &w_rows, (54 * at.b) & ~15, (int)at.n0 + (int)rank * R, &ctl->raw_full[rs]);
-                tma_load_2d(smem + PP_OFF_RAW + rs * PT_RAW_SLOT + PT_RAW_HEADS, &w_heads, (54 * at.b + 52) & ~15, (int)at.n0 + (int)(rank ^ 1u) * R, &ctl->raw_full[rs]);
+                tma_load_2d(smem + PT_OFF_RAW + rs * PT_RAW_SLOT, &w_rows, (54 * at.b) & ~15, (int)at.n0 + (int)rank * R, &ctl->raw_full[rs]);
+                tma_load_2d(smem + PT_OFF_RAW + rs * PT_RAW_SLOT + PT_RAW_HEADS, &w_heads, (54 * at.b + 52) & ~15, (int)at.n0 + (int)(rank ^ 1u) * R, &ctl->raw_full[rs]);
                 issued = it + 1;
             }
             for (int k = issued > PT_RAW_SLOTS ? issued - PT_RAW_SLOTS : 0; k < issued; ++k) mbar_wait(&ctl->raw_full[k % PT_RAW_SLOTS], (uint32_t)(k / PT_RAW_SLOTS) & 1u);
+            // the last commits on this CTA's b_empty barriers (see the activation warp)
+            for (int k = total > PT_B_STAGES ? total - PT_B_STAGES : 0; k < total && !ctl->abort; ++k)
+                if (!pp_wait_one(&ctl->b_empty[k % PT_B_STAGES], (uint32_t)(k / PT_B_STAGES) & 1u, ctl, peer_abort, p.status)) break;
         }
     } else if (warp >= PT_MMA_WARP) {
-        // ------------------------------------------------------------------ MMA issue (even CTA only), two issuers taking the blocks in turn
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PT_IO_REGS));
         const int q = warp - PT_MMA_WARP;
         if (lane == 0 && rank == 0) {
+            // -------------------------------------------------------------- MMA issue (even CTA), two issuers taking the blocks in turn
             const uint32_t idesc_q = tc::idesc_i8(2 * PP_TOKENS, 2 * R, true, true);
-            const uint32_t empty_peer = ctl_peer + (uint32_t)offsetof(PairControl, ab_empty);
             for (int it = q; it < total && !ctl->abort; it += PP_MMA_WARPS) {
-                const int s = it % PP_STAGES, buf = it % PT_BUFS;
-                if (!pp_wait_one(&ctl->ab_full[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                const int sa = it % PT_A_STAGES, sb = it % PT_B_STAGES, buf = it % PT_BUFS;
+                if (!pp_wait_one(&ctl->a_full[sa], (uint32_t)(it / PT_A_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                TR(0);
+                if (!pp_wait_one(&ctl->a_peer[sa], (uint32_t)(it / PT_A_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                TR(1);
+                if (!pp_wait_one(&ctl->b_full[sb], (uint32_t)(it / PT_B_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                TR(2);
                 if (!pp_wait_one(&ctl->tmem_empty[buf], (uint32_t)(it / PT_BUFS) & 1u, ctl, peer_abort, p.status)) break;
+                TR(3);
                 tc::fence_after_sync();
                 const uint32_t d = tmem + (uint32_t)buf * PT_BUF_COLS;
-                const uint32_t a_q = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT), b_q = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
-                const uint64_t a0 = tc::smem_desc_sw128(a_q), b0 = tc::smem_desc_sw128(b_q);
+                const uint64_t a0 = tc::smem_desc_sw128(smem_addr(smem + PT_OFF_A + sa * PT_A_SLOT)), b0 = tc::smem_desc_sw128(smem_addr(smem + PT_OFF_B + sb * PT_B_SLOT));
 #pragma unroll
                 for (int k = 0; k < 8; ++k)   // the first instruction of a block overwrites the accumulators
-                    tc::mma_i8_pair(d, a0 + (uint64_t)(((k >> 2) * PP_A_SLAB + (k & 3) * 32) >> 4), b0 + (uint64_t)(((k >> 2) * PP_B_SLAB + (k & 3) * 32) >> 4), idesc_q, k > 0 ? 1u : 0u);
-                tc::mma_i8_pair(d, tc::smem_desc(a_q + PP_A_THIN, PP_A_COL, 128), tc::smem_desc(b_q + PP_B_THIN, PP_B_COL, 128), idesc_q, 1);
+                    tc::mma_i8_pair(d, a0 + (uint64_t)(((k >> 2) * PT_A_SLAB + (k & 3) * 32) >> 4), b0 + (uint64_t)(((k >> 2) * PT_B_SLAB + (k & 3) * 32) >> 4), idesc_q, k > 0 ? 1u : 0u);
                 tc::commit_pair(smem_addr(&ctl->tmem_full[buf]));
-                tc::commit_pair(ctl_peer + (uint32_t)offsetof(PairControl, tmem_full) + 8u * (uint32_t)buf);
-                tc::commit_pair(smem_addr(&ctl->ab_empty[s]));
-                tc::commit_pair(empty_peer + 8u * (uint32_t)s);
+                tc::commit_pair(ctl_peer + (uint32_t)offsetof(TqControl, tmem_full) + 8u * (uint32_t)buf);
+                tc::commit_pair(smem_addr(&ctl->a_empty[sa]));
+                tc::commit_pair(ctl_peer + (uint32_t)offsetof(TqControl, a_empty) + 8u * (uint32_t)sa);
+                tc::commit_pair(smem_addr(&ctl->b_empty[sb]));
+                tc::commit_pair(ctl_peer + (uint32_t)offsetof(TqControl, b_empty) + 8u * (uint32_t)sb);
             }
             // the epilogues of both CTAs arrive once more after the last use of every buffer: receive those arrivals
             // before this CTA may leave (issuer 0 waits for all three buffers)
@@ -860,52 +987,74 @@ prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid
                     const int uses = (total - buf + PT_BUFS - 1) / PT_BUFS;
                     if (!pp_wait_one(&ctl->tmem_empty[buf], (uint32_t)uses & 1u, ctl, peer_abort, p.status)) break;
                 }
+        } else if (lane == 0 && rank == 1 && q == 0) {
+            // -------------------------------------------------------------- odd CTA: tell the even CTA that this CTA's activations have landed
+            const uint32_t peer_even = ctl_even + (uint32_t)offsetof(TqControl, a_peer);
+            for (int it = 0; it < total && !ctl->abort; ++it) {
+                const int sa = it % PT_A_STAGES;
+                if (!pp_wait_one(&ctl->a_full[sa], (uint32_t)(it / PT_A_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                tc::mbar_arrive_cluster(peer_even + 8u * (uint32_t)sa);
+                TR(0);
+            }
         }
     } else if (warp < PT_E_WARPS) {
         // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, quarter of the tile's weights)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PT_E_REGS));
         const int quarter = warp & 3, grp = warp >> 2;       // grp = 2 (CTA whose weights these are) + (half of that CTA's weights)
         const int half = grp >> 1, sub = grp & 1;
         const int row = quarter * 32 + lane;                 // token row of this CTA = TMEM lane
-        const int cols = R >> 1, chunks = cols >> 3;         // this warp's weights, in chunks of eight
+        const int cols = R >> 1;                             // this warp's weights: 8, 16, 24, 32 or 40
         const int col0 = half * R + sub * cols;
         const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)col0;
-        const uint32_t empty_even = ctl_even + (uint32_t)offsetof(PairControl, tmem_empty);
+        const uint32_t empty_even = ctl_even + (uint32_t)offsetof(TqControl, tmem_empty);
         __syncwarp();
         if (lane == 0)
             for (int buf = 0; buf < PT_BUFS; ++buf) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);   // all buffers start free
         uint64_t acc[PP_RMAX / 4];   // packed pairs of fp32: up to 40 weights
+        TqAt at = tq_first(p, pair, pairs);
         int it = 0;
         bool ok = true;
+        int m = at.m0 + (int)rank * PP_TOKENS + row;
+        float xd_next = m < p.m ? __ldg(p.xd + (long long)at.b * p.xd_pitch + m) : 0.f;
         for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
-            const int tile = pair + t * pairs;
-            const long long n0 = (long long)(tile / p.m_tiles) * p.w + col0;
-            const long long m = (long long)(tile % p.m_tiles) * (2 * PP_TOKENS) + (long long)rank * PP_TOKENS + row;
+            const int n0 = at.n0 + col0;
+            m = at.m0 + (int)rank * PP_TOKENS + row;
 #pragma unroll
             for (int k = 0; k < PP_RMAX / 4; ++k) acc[k] = 0ull;
-            for (int b = 0; b < nb && ok; ++b, ++it) {
+            for (int blk = 0; blk < nb && ok; ++blk, ++it) {
                 const int buf = it % PT_BUFS;
-                if (!pp_wait_warp_relaxed(&ctl->tmem_full[buf], (uint32_t)(it / PT_BUFS) & 1u, ctl, peer_abort, p.status)) { ok = false; break; }
+                const float xd = xd_next;
+                at.advance(p);
+                if (it + 1 < total) {   // x.d of the next block (of the next tile's tokens after the last block of a tile)
+                    const int mn = at.m0 + (int)rank * PP_TOKENS + row;
+                    xd_next = mn < p.m ? __ldg(p.xd + (long long)at.b * p.xd_pitch + mn) : 0.f;
+                }
+                TR(0);
+                if (!pp_wait_warp(&ctl->tmem_full[buf], (uint32_t)(it / PT_BUFS) & 1u, ctl, peer_abort, p.status)) { ok = false; break; }
+                TR(1);
                 tc::fence_after_sync();
-                const float xd = reinterpret_cast<const float *>(smem + PT_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT)[row];
-                const uint64_t *wd = reinterpret_cast<const uint64_t *>(smem + PT_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT + half * (PP_WD_SLOT / 2)) + sub * (cols >> 1);
+                const uint32_t wd = smem_addr(smem + PT_OFF_WD + (it & (PT_RING - 1)) * PT_WD_SLOT) + (uint32_t)half * (PT_WD_SLOT / 2) + 4u * (uint32_t)(sub * cols);
                 const uint64_t xd2 = pack2(xd, xd);
                 const uint32_t from = lane_base + (uint32_t)(buf * PT_BUF_COLS);
-#pragma unroll
-                for (int c = 0; c < PP_RMAX / 16; ++c) {
-                    if (c < chunks) {
-                        uint32_t v[8];
-                        tc::tmem_ld8(from + 8 * c, v);
-                        tc::tmem_ld_wait();
-                        if (c + 1 == chunks) {   // everything is read: the buffer goes back before the last arithmetic
-                            tc::fence_before_sync();
-                            __syncwarp();
-                            if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
-                        }
-#pragma unroll
-                        for (int k = 0; k < 8; k += 2)   // acc += f32(isum) * (d * x.d)
-                            acc[(8 * c + k) >> 1] = fma2(ints_to_float2(v[k], v[k + 1]), mul2(wd[(8 * c + k) >> 1], xd2), acc[(8 * c + k) >> 1]);
-                    }
+                // read-out sixteen columns at a time, the next load in flight while the previous columns are scaled and added
+                uint32_t va[16], vb[16];
+                tq_load_columns(from, 0, cols, va);
+                tc::tmem_ld_wait();
+                if (cols > 16) tq_load_columns(from, 16, cols, vb);
+                else tq_release(empty_even + 8u * (uint32_t)buf, lane);      // everything is read: the buffer goes back before the arithmetic
+                tq_scale_add<0>(acc, va, cols, wd, xd2);
+                if (cols > 16) {
+                    tc::tmem_ld_wait();
+                    if (cols > 32) tq_load_columns(from, 32, cols, va);
+                    else tq_release(empty_even + 8u * (uint32_t)buf, lane);
+                    tq_scale_add<16>(acc, vb, cols, wd, xd2);
                 }
+                if (cols > 32) {
+                    tc::tmem_ld_wait();
+                    tq_release(empty_even + 8u * (uint32_t)buf, lane);
+                    tq_scale_add<32>(acc, va, cols, wd, xd2);
+                }
+                TR(2);
             }
             if (!ok) break;
             if (m < p.m) {
@@ -979,6 +1128,29 @@ bool prefill_pair_supported(int fmt, long long n, long long k, long long m, cons
            (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
 }
 
+// The planes of the latest TQ1_0 call: one device allocation that only ever grows.  Calls are serialised by the
+// library and run on one stream, so the next call's plane kernel starts after this call's contraction has ended.  A
+// larger request gets a new allocation; the previous ones stay until the process ends, because work already queued (or a
+// captured graph) may still name them.
+struct PlaneScratch {
+    uint8_t *base = nullptr;
+    size_t bytes = 0;
+};
+static PlaneScratch g_planes;
+
+static cudaError_t reserve_planes(size_t bytes, uint8_t **out) {
+    if (bytes > g_planes.bytes) {
+        uint8_t *fresh = nullptr;
+        const size_t want = (bytes + bytes / 4 + 255) & ~size_t(255);
+        const cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&fresh), want);
+        if (e != cudaSuccess) return e;
+        g_planes.base = fresh;
+        g_planes.bytes = want;
+    }
+    *out = g_planes.base;
+    return cudaSuccess;
+}
+
 static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!a.powers) return cudaErrorInvalidValue;
     cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_tq1_kernel), PT_SMEM);
@@ -993,19 +1165,30 @@ static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, c
         if (pairs < 1) return cudaErrorNotSupported;
         if (pairs > sm_count / 2) pairs = sm_count / 2;
     }
-    PairParams p;
+    TqParams p;
     p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
     p.m_tiles = (int)((a.m + 2 * PP_TOKENS - 1) / (2 * PP_TOKENS));
     p.w = pick_tile_width_tq1(a.n, p.m_tiles, pairs);
     p.n_tiles = (int)((a.n + p.w - 1) / p.w);
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     if (tiles < pairs) pairs = (int)tiles;
-    CUtensorMap x_wide, x_narrow, w_rows, w_heads;
-    e = encode_tile_map(&x_wide, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
-                        (unsigned long long)p.nb * 292, 32, PP_TOKENS, true);
-    if (e == cudaSuccess)
-        e = encode_tile_map(&x_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
-                            (unsigned long long)p.nb * 292, 4, PP_TOKENS, false);
+    // planes: codes (m, k) int8, then x.d (nb, pitch) float
+    p.xd_pitch = (a.m + 63) & ~63LL;
+    const size_t code_bytes = ((size_t)a.m * (size_t)a.k + 255) & ~size_t(255);
+    uint8_t *planes = nullptr;
+    e = reserve_planes(code_bytes + (size_t)p.nb * (size_t)p.xd_pitch * sizeof(float), &planes);
+    if (e != cudaSuccess) return e;
+    p.xd = reinterpret_cast<const float *>(planes + code_bytes);
+    {
+        const long long threads = a.m * p.nb * 16;
+        q8k_planes_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(static_cast<const uint8_t *>(a.xq), reinterpret_cast<int8_t *>(planes),
+                                                                                   reinterpret_cast<float *>(planes + code_bytes), a.m, p.nb, p.xd_pitch);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    CUtensorMap x_codes, w_rows, w_heads;
+    e = encode_tile_map(&x_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, planes, (unsigned long long)a.k, (unsigned long long)a.m,
+                        (unsigned long long)a.k, 128, PP_TOKENS, true);
     // the weight matrix as (n) rows of 54 * nb bytes
     if (e == cudaSuccess)
         e = encode_tile_map(&w_rows, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.w, (unsigned long long)p.nb * 54, (unsigned long long)a.n,
@@ -1014,9 +1197,13 @@ static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, c
         e = encode_tile_map(&w_heads, CU_TENSOR_MAP_DATA_TYPE_UINT8, a.w, (unsigned long long)p.nb * 54, (unsigned long long)a.n,
                             (unsigned long long)p.nb * 54, 16, (unsigned)(p.w / 2), false);
     if (e != cudaSuccess) return e;
-    prefill_pair_tq1_kernel<<<2 * pairs, PT_THREADS, PT_SMEM, stream>>>(p, a.powers, x_wide, x_narrow, w_rows, w_heads);
+    prefill_pair_tq1_kernel<<<2 * pairs, PT_THREADS, PT_SMEM, stream>>>(p, a.powers, x_codes, w_rows, w_heads);
     return cudaGetLastError();
 }
+
+#ifdef PT_TRACE
+extern "C" int weft_b200_debug_trace_read(void *host, size_t bytes) { return (int)cudaMemcpyFromSymbol(host, pt_trace, bytes); }
+#endif
 
 cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!prefill_pair_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
