@@ -114,11 +114,16 @@ static_assert(sizeof(PairControl) <= PP_CONTROL, "control block");
 // Bounded wait by one thread; gives up as soon as another role (of either CTA) has raised the abort flag.  The suspending
 // form of the wait: a lane that spins on test_wait issues an instruction every few cycles and takes a third of its
 // scheduler's issue slots from the warps that work.
+// Sleep between failed polls (ns): single lanes that wait for a copy or for tensor memory, and whole warps.  A waiting
+// warp that polls without pause issues an instruction every few cycles; with these pauses the Q4_K kernel went from
+// 134 to 124 us on 512 x 14336 x 4096 (the TQ1_0 kernel did not change).
+constexpr uint32_t PP_LANE_NAP = 300, PP_WARP_NAP = 100;
 template <class Control>
 __device__ __forceinline__ bool pp_wait_one(uint64_t *bar, uint32_t parity, Control *ctl, uint32_t peer_abort, int *status) {
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 15u) == 15u && ctl->abort) return false;
+        __nanosleep(PP_LANE_NAP);
     }
     ctl->abort = 1;
     tc::st_cluster_u32(peer_abort, 1u);
@@ -132,6 +137,7 @@ __device__ __forceinline__ bool pp_wait_warp(uint64_t *bar, uint32_t parity, Con
     for (uint32_t i = 0; i < (1u << 22); ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 7u) == 7u && ctl->abort) return false;
+        __nanosleep(PP_WARP_NAP);
     }
     if ((threadIdx.x & 31) == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(status, ST_WAIT_TIMEOUT); }
     return false;
@@ -609,6 +615,7 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
 // CTA has the scales of all w weights without touching the partner's shared memory.  O takes eight values (b % 8); the
 // blocks of a tile are taken as 0, 8, 16, ..., 1, 9, ... so that the expanders stay in one of their eight code variants.
 constexpr int PT_E_WARPS = 16, PT_X_WARPS = 12;
+constexpr int PT_X_GROUPS = 1;                                 // expander groups taking the blocks in turn (two measured the same as one)
 constexpr int PT_X_WARP0 = PT_E_WARPS;
 constexpr int PT_ATMA_WARP = PT_X_WARP0 + PT_X_WARPS, PT_WTMA_WARP = PT_ATMA_WARP + 1, PT_MMA_WARP = PT_WTMA_WARP + 1;
 constexpr int PT_THREADS = 32 * (PT_MMA_WARP + PP_MMA_WARPS);   // 32 warps
@@ -753,12 +760,20 @@ __device__ __forceinline__ void tq_expand_light(uint32_t box, uint32_t head, uin
     sts_u32(wd_mine + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(d_mine & 0xffffu)));
     sts_u32(wd_partner + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(d_partner & 0xffffu)));
 }
+// The jobs of one warp for one block: job j = first_job + k * (12 / PT_X_GROUPS) is task kind j / 3 on rows 32 (j % 3) + lane
 template <int O>
-__device__ __forceinline__ void tq_expand(int part, uint32_t box, uint32_t head, uint32_t lut, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner, int row) {
-    if (part == 0) tq_expand_heavy<0, O>(box, lut, b_slot, row);
-    else if (part == 1) tq_expand_heavy<1, O>(box, lut, b_slot, row);
-    else if (part == 2) tq_expand_heavy<2, O>(box, lut, b_slot, row);
-    else tq_expand_light<O>(box, head, lut, b_slot, wd_mine, wd_partner, row);
+__device__ __forceinline__ void tq_expand_jobs(int first_job, int lane, int R, uint32_t raw_slot, uint32_t lut, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner) {
+#pragma unroll 1
+    for (int job = first_job; job < PT_X_WARPS; job += PT_X_WARPS / PT_X_GROUPS) {
+        const int part = job / 3, row = 32 * (job - 3 * part) + lane;
+        if (row < R) {
+            const uint32_t box = raw_slot + (uint32_t)row * PT_RAW_BOX, head = raw_slot + PT_RAW_HEADS + (uint32_t)row * 16u;
+            if (part == 0) tq_expand_heavy<0, O>(box, lut, b_slot, row);
+            else if (part == 1) tq_expand_heavy<1, O>(box, lut, b_slot, row);
+            else if (part == 2) tq_expand_heavy<2, O>(box, lut, b_slot, row);
+            else tq_expand_light<O>(box, head, lut, b_slot, wd_mine, wd_partner, row);
+        }
+    }
 }
 
 // Epilogue pieces.  Columns [g, g + 16) of the warp's accumulators (eight when the warp has only eight left) into v.
@@ -776,16 +791,25 @@ __device__ __forceinline__ void tq_release(uint32_t empty_bar, int lane) {
     __syncwarp();
     if (lane == 0) tc::mbar_arrive_cluster(empty_bar);
 }
-// acc += f32(isum) * (d * x.d) for columns [G, G + 16) (or [G, G + 8)); wd: the weights' d as floats in shared memory
+// Two accumulator integers as a packed pair of floats, exactly (|v| < 2^22): v + bits(1.5 * 2^23) is the float
+// 1.5 * 2^23 + v; the halves are written straight into the 64-bit register that the packed subtraction reads.
+__device__ __forceinline__ uint64_t tq_ints_to_float2(uint32_t a, uint32_t b) {
+    uint64_t biased;
+    asm("{\n\t.reg .b32 lo, hi;\n\tadd.u32 lo, %1, 0x4b400000;\n\tadd.u32 hi, %2, 0x4b400000;\n\tmov.b64 %0, {lo, hi};\n\t}" : "=l"(biased) : "r"(a), "r"(b));
+    return add2(biased, pack2(-12582912.f, -12582912.f));
+}
+// acc += f32(isum) * (d * x.d) for columns [G, G + 16) (or [G, G + 8)); wd: the weights' d as floats in shared memory,
+// read as 64-bit pairs so that no move stands between the load and the packed multiply
 template <int G>
 __device__ __forceinline__ void tq_scale_add(uint64_t (&acc)[PP_RMAX / 4], const uint32_t (&v)[16], int cols, uint32_t wd, uint64_t xd2) {
     const bool wide = G + 16 <= cols;
 #pragma unroll
     for (int k = 0; k < 16; k += 4) {
         if (G + k < PP_RMAX / 2 && (wide || k < 8)) {
-            const uint4 s4 = lds128(wd + 4u * (uint32_t)(G + k));
-            acc[(G + k) >> 1] = fma2(ints_to_float2(v[k], v[k + 1]), mul2(pack2(__uint_as_float(s4.x), __uint_as_float(s4.y)), xd2), acc[(G + k) >> 1]);
-            acc[((G + k) >> 1) + 1] = fma2(ints_to_float2(v[k + 2], v[k + 3]), mul2(pack2(__uint_as_float(s4.z), __uint_as_float(s4.w)), xd2), acc[((G + k) >> 1) + 1]);
+            uint64_t s01, s23;
+            asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(s01), "=l"(s23) : "r"(wd + 4u * (uint32_t)(G + k)));
+            acc[(G + k) >> 1] = fma2(tq_ints_to_float2(v[k], v[k + 1]), mul2(s01, xd2), acc[(G + k) >> 1]);
+            acc[((G + k) >> 1) + 1] = fma2(tq_ints_to_float2(v[k + 2], v[k + 3]), mul2(s23, xd2), acc[((G + k) >> 1) + 1]);
         }
     }
 }
@@ -804,14 +828,6 @@ __global__ void __launch_bounds__(256) q8k_planes_kernel(const uint8_t *__restri
         xd[(record - t * nb) * pitch + t] = __uint_as_float(src[0]);
     }
 }
-
-#ifdef PT_TRACE
-__device__ unsigned long long pt_trace[2][32][96][4];
-__device__ __forceinline__ unsigned long long pt_now() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define TR(slot) do { if (pair == 0 && (threadIdx.x & 31) == 0 && it >= 32 && it < 128) pt_trace[rank][threadIdx.x >> 5][it - 32][slot] = pt_now(); } while (0)
-#else
-#define TR(slot) do { } while (0)
-#endif
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PT_THREADS, 1)
 prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_constant__ CUtensorMap x_codes,
@@ -833,8 +849,8 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PT_A_STAGES; ++s) { mbar_init(&ctl->a_full[s], 1); mbar_init(&ctl->a_peer[s], 1); mbar_init(&ctl->a_empty[s], 1); }
-        for (int s = 0; s < PT_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 1); mbar_init(&ctl->raw_empty[s], PT_X_WARPS); }
-        for (int s = 0; s < PT_B_STAGES; ++s) { mbar_init(&ctl->b_full[s], 2 * PT_X_WARPS); mbar_init(&ctl->b_empty[s], 1); }
+        for (int s = 0; s < PT_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 1); mbar_init(&ctl->raw_empty[s], PT_X_WARPS / PT_X_GROUPS); }
+        for (int s = 0; s < PT_B_STAGES; ++s) { mbar_init(&ctl->b_full[s], 2 * PT_X_WARPS / PT_X_GROUPS); mbar_init(&ctl->b_empty[s], 1); }
         for (int h = 0; h < PT_BUFS; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 2 * PT_E_WARPS); }
         ctl->abort = 0;
         ctl->tmem_base = 0xffffffffu;
@@ -866,35 +882,37 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
     } else if (warp >= PT_X_WARP0 && warp < PT_X_WARP0 + PT_X_WARPS) {
         // ------------------------------------------------------------------ expanders: three warps per task kind
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PT_X_REGS));
+        // The twelve warps form PT_X_GROUPS groups that take the blocks in turn; a warp of a group does PT_X_GROUPS of the
+        // twelve jobs (job j: task kind j / 3, rows 32 (j % 3) ..) of its block one after the other.  What a block costs an
+        // expander is mostly waiting (the records' way through shared memory, the fence before the hand-over), so two
+        // blocks in flight nearly double what the expanders deliver.
         const int xw = warp - PT_X_WARP0;
-        const int part = xw / 3, row = 32 * (xw - 3 * part) + lane;
-        const bool active = row < R;
+        const int group = xw % PT_X_GROUPS, first_job = xw / PT_X_GROUPS;
         const uint32_t lut = smem_addr(smem + PT_OFF_LUT) + 8u * (uint32_t)(lane & (PT_LUT_COPIES - 1));
         TqAt at = tq_first(p, pair, pairs);
+        for (int k = 0; k < group; ++k) at.advance(p);
         const uint32_t full_even = ctl_even + (uint32_t)offsetof(TqControl, b_full);
-        for (int it = 0; it < total && !ctl->abort; ++it) {
+        for (int it = group; it < total && !ctl->abort; it += PT_X_GROUPS) {
             const int b = at.b;
-            at.advance(p);
+#pragma unroll
+            for (int k = 0; k < PT_X_GROUPS; ++k) at.advance(p);
             const int s = it % PT_B_STAGES, rs = it % PT_RAW_SLOTS;
             if (!pp_wait_warp(&ctl->raw_full[rs], (uint32_t)(it / PT_RAW_SLOTS) & 1u, ctl, peer_abort, p.status)) break;
-            TR(0);
             if (!pp_wait_warp(&ctl->b_empty[s], ((uint32_t)(it / PT_B_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
-            TR(1);
-            if (active) {
+            {
                 const uint32_t raw_slot = smem_addr(smem + PT_OFF_RAW + rs * PT_RAW_SLOT);
                 const uint32_t b_slot = smem_addr(smem + PT_OFF_B + s * PT_B_SLOT);
-                const uint32_t box = raw_slot + (uint32_t)row * PT_RAW_BOX, head = raw_slot + PT_RAW_HEADS + (uint32_t)row * 16u;
                 const uint32_t wd_slot = smem_addr(smem + PT_OFF_WD + (it & (PT_RING - 1)) * PT_WD_SLOT);
                 const uint32_t wd_mine = wd_slot + rank * (uint32_t)(PT_WD_SLOT / 2), wd_partner = wd_slot + (rank ^ 1u) * (uint32_t)(PT_WD_SLOT / 2);
                 switch (b & 7) {   // O = (54 b) % 16
-                case 0: tq_expand<0>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
-                case 1: tq_expand<6>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
-                case 2: tq_expand<12>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
-                case 3: tq_expand<2>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
-                case 4: tq_expand<8>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
-                case 5: tq_expand<14>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
-                case 6: tq_expand<4>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
-                default: tq_expand<10>(part, box, head, lut, b_slot, wd_mine, wd_partner, row); break;
+                case 0: tq_expand_jobs<0>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
+                case 1: tq_expand_jobs<6>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
+                case 2: tq_expand_jobs<12>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
+                case 3: tq_expand_jobs<2>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
+                case 4: tq_expand_jobs<8>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
+                case 5: tq_expand_jobs<14>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
+                case 6: tq_expand_jobs<4>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
+                default: tq_expand_jobs<10>(first_job, lane, R, raw_slot, lut, b_slot, wd_mine, wd_partner); break;
                 }
             }
             fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
@@ -903,7 +921,6 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
                 mbar_arrive(&ctl->raw_empty[rs]);
                 tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
             }
-            TR(2);
         }
     } else if (warp == PT_ATMA_WARP) {
         // ------------------------------------------------------------------ activation copies (this CTA's 128 tokens)
@@ -914,7 +931,6 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
             for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
                 const int s = it % PT_A_STAGES;
                 if (!pp_wait_one(&ctl->a_empty[s], ((uint32_t)(it / PT_A_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
-                TR(0);
                 uint8_t *slot = smem + PT_OFF_A + s * PT_A_SLOT;
                 mbar_expect_tx(&ctl->a_full[s], PT_A_SLOT);
                 // tokens past M read as zero
@@ -939,7 +955,6 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
             for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
                 const int rs = it % PT_RAW_SLOTS;
                 if (!pp_wait_one(&ctl->raw_empty[rs], ((uint32_t)(it / PT_RAW_SLOTS) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
-                TR(0);
                 mbar_expect_tx(&ctl->raw_full[rs], bytes);
                 // rows past N and bytes past the end of a row read as zero (digits -1 times d = 0: never stored)
                 tma_load_2d(smem + PT_OFF_RAW + rs * PT_RAW_SLOT, &w_rows, (54 * at.b) & ~15, (int)at.n0 + (int)rank * R, &ctl->raw_full[rs]);
@@ -960,13 +975,9 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
             for (int it = q; it < total && !ctl->abort; it += PP_MMA_WARPS) {
                 const int sa = it % PT_A_STAGES, sb = it % PT_B_STAGES, buf = it % PT_BUFS;
                 if (!pp_wait_one(&ctl->a_full[sa], (uint32_t)(it / PT_A_STAGES) & 1u, ctl, peer_abort, p.status)) break;
-                TR(0);
                 if (!pp_wait_one(&ctl->a_peer[sa], (uint32_t)(it / PT_A_STAGES) & 1u, ctl, peer_abort, p.status)) break;
-                TR(1);
                 if (!pp_wait_one(&ctl->b_full[sb], (uint32_t)(it / PT_B_STAGES) & 1u, ctl, peer_abort, p.status)) break;
-                TR(2);
                 if (!pp_wait_one(&ctl->tmem_empty[buf], (uint32_t)(it / PT_BUFS) & 1u, ctl, peer_abort, p.status)) break;
-                TR(3);
                 tc::fence_after_sync();
                 const uint32_t d = tmem + (uint32_t)buf * PT_BUF_COLS;
                 const uint64_t a0 = tc::smem_desc_sw128(smem_addr(smem + PT_OFF_A + sa * PT_A_SLOT)), b0 = tc::smem_desc_sw128(smem_addr(smem + PT_OFF_B + sb * PT_B_SLOT));
@@ -994,7 +1005,6 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
                 const int sa = it % PT_A_STAGES;
                 if (!pp_wait_one(&ctl->a_full[sa], (uint32_t)(it / PT_A_STAGES) & 1u, ctl, peer_abort, p.status)) break;
                 tc::mbar_arrive_cluster(peer_even + 8u * (uint32_t)sa);
-                TR(0);
             }
         }
     } else if (warp < PT_E_WARPS) {
@@ -1029,9 +1039,7 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
                     const int mn = at.m0 + (int)rank * PP_TOKENS + row;
                     xd_next = mn < p.m ? __ldg(p.xd + (long long)at.b * p.xd_pitch + mn) : 0.f;
                 }
-                TR(0);
                 if (!pp_wait_warp(&ctl->tmem_full[buf], (uint32_t)(it / PT_BUFS) & 1u, ctl, peer_abort, p.status)) { ok = false; break; }
-                TR(1);
                 tc::fence_after_sync();
                 const uint32_t wd = smem_addr(smem + PT_OFF_WD + (it & (PT_RING - 1)) * PT_WD_SLOT) + (uint32_t)half * (PT_WD_SLOT / 2) + 4u * (uint32_t)(sub * cols);
                 const uint64_t xd2 = pack2(xd, xd);
@@ -1054,7 +1062,6 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
                     tq_release(empty_even + 8u * (uint32_t)buf, lane);
                     tq_scale_add<32>(acc, va, cols, wd, xd2);
                 }
-                TR(2);
             }
             if (!ok) break;
             if (m < p.m) {
@@ -1200,10 +1207,6 @@ static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, c
     prefill_pair_tq1_kernel<<<2 * pairs, PT_THREADS, PT_SMEM, stream>>>(p, a.powers, x_codes, w_rows, w_heads);
     return cudaGetLastError();
 }
-
-#ifdef PT_TRACE
-extern "C" int weft_b200_debug_trace_read(void *host, size_t bytes) { return (int)cudaMemcpyFromSymbol(host, pt_trace, bytes); }
-#endif
 
 cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!prefill_pair_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
