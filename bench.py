@@ -75,7 +75,7 @@ NCU_DRAM_TRAFFIC = {
     "q4_k_prefill_4096x4096": 11_908_608,
     "q8_0_prefill_4096x4096": 20_104_448,
     "iq2_xxs_prefill_4096x4096": 6_777_344,
-    "tq1_0_prefill_28672x8192": 67_826_432,
+    "tq1_0_prefill_28672x8192": 69_316_352,
     "q4_k_dequantize_14336x4096": 33_041_920 + 177_308_928,
 }
 
