@@ -604,11 +604,14 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
 //                chunks each) and the qh word with the two scales.  A warp is of one task kind; the lanes of a quarter
 //                warp store their 16-byte chunks to eight different rows, whose swizzled positions never meet in a bank.
 //                The digits come from a table in shared memory (entry v = the five digits of byte value v, built from the
-//                caller's powers), sixteen copies so that the lookups of a half warp fall into different banks: the
-//                expansion is bound by shared-memory wavefronts and by the integer pipe, not by latency.
+//                caller's powers), sixteen copies so that the lookups of a half warp fall into different banks.
 //   MMA          one lane of the even CTA (two issuers taking the blocks in turn): 8 int8 K = 32 steps, N = w
-//   epilogue     16 warps = 4 lane quarters x 4 quarters of the tile's weights, up to 40 accumulators per thread; x.d by
-//                one global load per thread and block, issued a block ahead
+//   epilogue     16 warps = 4 lane quarters x 4 quarters of the tile's weights, up to 40 accumulators per thread; sixteen
+//                columns per tensor-memory load, the next load in flight during the arithmetic; x.d by one global load per
+//                thread and block, issued a block ahead
+// 512 x 28672 x 8192: 231 us per step (321 us on the first pair kernel, which read the records as they lie; 582 us on the
+// single-CTA kernel of prefill.cu).  With the expanders and the epilogue arithmetic switched off the kernel still takes
+// 146 us: 0.9 us per block of hand-overs between the roles against 0.36 us of tensor work.
 // Raw records: 54 bytes, rows of K/256 * 54 bytes (a multiple of 16 when K % 2048 == 0).  Record b of a row starts
 // O = (54 b) % 16 bytes past a 16-byte boundary; an 80-byte box from that boundary holds it whole.  Its f16 d (bytes 52, 53)
 // lies inside the 16-byte box at (54 b + 52) rounded down to 16: that box is fetched for the PARTNER's weights, so each
@@ -1044,19 +1047,15 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
                 const uint32_t wd = smem_addr(smem + PT_OFF_WD + (it & (PT_RING - 1)) * PT_WD_SLOT) + (uint32_t)half * (PT_WD_SLOT / 2) + 4u * (uint32_t)(sub * cols);
                 const uint64_t xd2 = pack2(xd, xd);
                 const uint32_t from = lane_base + (uint32_t)(buf * PT_BUF_COLS);
-                // read-out sixteen columns at a time, the next load in flight while the previous columns are scaled and added
+                // read-out: the first 32 columns by two loads in flight together, the last eight during the arithmetic
                 uint32_t va[16], vb[16];
                 tq_load_columns(from, 0, cols, va);
-                tc::tmem_ld_wait();
                 if (cols > 16) tq_load_columns(from, 16, cols, vb);
-                else tq_release(empty_even + 8u * (uint32_t)buf, lane);      // everything is read: the buffer goes back before the arithmetic
+                tc::tmem_ld_wait();
+                if (cols <= 32) tq_release(empty_even + 8u * (uint32_t)buf, lane);   // everything is read: the buffer goes back before the arithmetic
                 tq_scale_add<0>(acc, va, cols, wd, xd2);
-                if (cols > 16) {
-                    tc::tmem_ld_wait();
-                    if (cols > 32) tq_load_columns(from, 32, cols, va);
-                    else tq_release(empty_even + 8u * (uint32_t)buf, lane);
-                    tq_scale_add<16>(acc, vb, cols, wd, xd2);
-                }
+                if (cols > 32) tq_load_columns(from, 32, cols, va);
+                if (cols > 16) tq_scale_add<16>(acc, vb, cols, wd, xd2);
                 if (cols > 32) {
                     tc::tmem_ld_wait();
                     tq_release(empty_even + 8u * (uint32_t)buf, lane);
