@@ -626,8 +626,12 @@ constexpr int PT_A_STAGES = 3, PT_B_STAGES = 3, PT_RAW_SLOTS = 3, PT_RING = 8;
 constexpr int PT_BUFS = 3, PT_BUF_COLS = 160;
 // Registers: the kernel starts with 64 per thread (1024 threads); the roles then trade them in whole warp groups of four
 // warps: the epilogue (warps 0-15) holds 40 accumulators and 16 columns in flight, the copy and MMA lanes need few.
-constexpr int PT_E_REGS = 88, PT_X_REGS = 40, PT_IO_REGS = 24;
-static_assert(32 * (PT_E_WARPS * PT_E_REGS + PT_X_WARPS * PT_X_REGS + 4 * PT_IO_REGS) <= 65536 && PT_E_WARPS % 4 == 0 && PT_X_WARPS % 4 == 0, "register trade between the warp groups");
+// A group can only take what other groups of the same CTA have given back (registers the CTA never had stay out of reach:
+// a kernel whose groups ask for more than the others release waits in setmaxnreg for ever).
+constexpr int PT_LAUNCH_REGS = 64, PT_E_REGS = 88, PT_X_REGS = 40, PT_IO_REGS = 24;
+static_assert(PT_E_WARPS * (PT_E_REGS - PT_LAUNCH_REGS) <= PT_X_WARPS * (PT_LAUNCH_REGS - PT_X_REGS) + 4 * (PT_LAUNCH_REGS - PT_IO_REGS) &&
+              PT_E_WARPS % 4 == 0 && PT_X_WARPS % 4 == 0 && 32 * PT_LAUNCH_REGS * (PT_E_WARPS + PT_X_WARPS + 4) <= 65536,
+              "register trade between the warp groups");
 constexpr int PT_A_SLAB = 128 * 128, PT_A_SLOT = 2 * PT_A_SLAB;            // 32 KB
 constexpr int PT_B_SLAB = PP_RMAX * 128, PT_B_SLOT = 2 * PT_B_SLAB;        // 20 KB
 constexpr int PT_RAW_BOX = 80;                                  // bytes per record box
@@ -1157,9 +1161,18 @@ static cudaError_t reserve_planes(size_t bytes, uint8_t **out) {
     return cudaSuccess;
 }
 
+// The register trade assumes the allocation the kernel was compiled with: a build with another one must not run
+static cudaError_t check_launch_registers(const void *kernel, int expected) {
+    cudaFuncAttributes attr;
+    const cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+    if (e != cudaSuccess) return e;
+    return attr.numRegs == expected ? cudaSuccess : cudaErrorInvalidConfiguration;
+}
+
 static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!a.powers) return cudaErrorInvalidValue;
     cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_tq1_kernel), PT_SMEM);
+    if (e == cudaSuccess) e = check_launch_registers(reinterpret_cast<const void *>(prefill_pair_tq1_kernel), PT_LAUNCH_REGS);
     if (e != cudaSuccess) return e;
     int pairs = 0;
     {
