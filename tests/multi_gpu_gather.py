@@ -29,6 +29,7 @@ CASES = [
     ("Q4_0", 0, 1024, 4096, 1),
     ("TQ1_0", 0, 512, 1024, 1),      # rows of 216 bytes: fallback GEMV + push kernel
     ("Q4_K", 1, 1024, 2048, 128),    # tensor-core prefill + push kernel
+    ("TQ1_0", 1, 640, 2048, 300),    # CTA-pair prefill on activation planes + push kernel
 ]
 
 

@@ -156,3 +156,35 @@ def test_prefill_tq1_0_benchmark_shape(torch, oracle):
     """Config 5b: M = 512 tokens, (N, K) = (28672, 8192); three column bands against the oracle."""
     n, k = 28672, 8192
     _run_tq1_0(torch, oracle, 512, n, k, seed=5, column_ranges=[(0, 128), (n // 2 - 60, n // 2 + 70), (n - 128, n)])
+
+
+def test_prefill_tq1_0_given_records_and_plane_reuse(torch, oracle):
+    """The CTA-pair kernel reads planes that a kernel of its own makes of the Q8_K records.  With flags bit 0 the records
+    are the caller's (X is not read); a small call after a large one reuses the larger plane allocation.  Every result
+    must equal, bit for bit, what the same call computes when it quantizes X itself."""
+    import ctypes
+
+    from weft_b200.runtime.driver import Toolchain, last_error, load_library
+
+    lib = load_library(Toolchain().resolve().compiler)
+    assert lib.weft_b200_init(0) == 0, last_error(lib)
+    fn = lib.weft_b200_mul_mat_shard
+    fn.argtypes = [ctypes.c_int, ctypes.c_int] + [ctypes.c_void_p] * 7 + [ctypes.c_size_t] * 4 + [ctypes.c_uint]
+    powers = torch.tensor([1, 3, 9, 27, 81], dtype=torch.int32, device="cuda")
+    for m, n, k in [(512, 640, 4096), (130, 96, 2048), (300, 333, 2048)]:
+        rng = np.random.default_rng(m + n + k)
+        w = torch.from_numpy(weights(oracle.TQ1_0, rng, n, k)).cuda()
+        x_host = activations(rng, m, k)
+        x = torch.from_numpy(x_host).cuda()
+        xq = torch.zeros((m, oracle.row_bytes(oracle.Q8_K, k)), dtype=torch.uint8, device="cuda")
+        y0 = torch.full((m, n), float("nan"), device="cuda")
+        y1 = torch.full((m, n), float("nan"), device="cuda")
+        assert fn(oracle.TQ1_0, 1, w.data_ptr(), x.data_ptr(), xq.data_ptr(), None, None, powers.data_ptr(), y0.data_ptr(), n, k, m, n, 0) == 0, last_error(lib)
+        given = torch.from_numpy(oracle.quantize(oracle.Q8_K, x_host, rule=1)).cuda()
+        assert torch.equal(given, xq)
+        assert fn(oracle.TQ1_0, 1, w.data_ptr(), None, given.data_ptr(), None, None, powers.data_ptr(), y1.data_ptr(), n, k, m, n, 1) == 0, last_error(lib)
+        torch.cuda.synchronize()
+        assert torch.isfinite(y0).all()
+        assert torch.equal(y0, y1), (m, n, k)
+        want, _ = oracle.mul_mat(oracle.TQ1_0, w.cpu().numpy(), None, n, k, m, xq=given.cpu().numpy())
+        assert rel_l2(y1.cpu().numpy(), want) <= 1e-5
