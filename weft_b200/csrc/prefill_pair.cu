@@ -14,7 +14,8 @@
 // tokens and the activation slab is read once per block.  Per 256-block and CTA:
 //   raw weights  one TMA box copy of w/2 records (144 B each) into a 4-slot ring, three blocks ahead
 //   activations  five TMA box copies (128 tokens x 304 bytes) into a 3-slot ring
-//   expanders    5 warps, four lanes per weight (lane = one pair of sub-blocks): nibbles -> two scaled limbs,
+//   expanders    two groups of 5 warps that take the blocks in turn, four lanes per weight (lane = one pair of
+//                sub-blocks): nibbles -> two scaled limbs,
 //                shifted by the block's operand shift (neighbouring lanes exchange the carried words by
 //                shuffle), written as the K-major 128-byte-swizzled operand; lane layout chosen so that the
 //                16-byte stores of a quarter-warp never meet in a bank
@@ -46,11 +47,16 @@ constexpr int PP_RMAX = 80;                    // B rows per CTA at most: [hi li
 constexpr int PP_STAGES = 3;                   // operand slots (activations + expanded weights)
 constexpr int PP_RAW_SLOTS = 4;                // raw-record ring
 constexpr int PP_RING = 8;                     // x.d / weight-scale rings (see the note at their use)
-constexpr int PP_E_WARPS = 8, PP_X_WARPS = 5, PP_X_GROUPS = 1, PP_S_WARPS = 2;   // expander groups take the blocks in turn
+constexpr int PP_E_WARPS = 8, PP_X_WARPS = 5, PP_X_GROUPS = 2, PP_S_WARPS = 2;   // expander groups take the blocks in turn
 constexpr int PP_X_WARP0 = PP_E_WARPS, PP_S_WARP0 = PP_X_WARP0 + PP_X_GROUPS * PP_X_WARPS;
 constexpr int PP_ATMA_WARP = PP_S_WARP0 + PP_S_WARPS, PP_WTMA_WARP = PP_ATMA_WARP + 1, PP_MMA_WARP = PP_WTMA_WARP + 1;
 constexpr int PP_MMA_WARPS = 2;                 // issuer q takes the blocks with it % 2 == q: one TMEM buffer each
-constexpr int PP_THREADS = 32 * (PP_MMA_WARP + PP_MMA_WARPS);   // 19 warps
+constexpr int PP_THREADS = 32 * (PP_MMA_WARP + PP_MMA_WARPS);   // 24 warps
+// Registers: 80 per thread at launch; the epilogue (warp groups 0 and 1) takes sixteen more from what the copy and MMA
+// lanes (group 5) give back.  A group can only take what other groups of the same CTA have released.
+constexpr int PP_LAUNCH_REGS = 80, PP_E_REGS = 96, PP_IO_REGS = 24;
+static_assert(PP_THREADS == 768 && PP_E_WARPS == 8 && PP_X_GROUPS * PP_X_WARPS + PP_S_WARPS == 12, "warp groups of four: epilogue 0-1, expanders and per-token warps 2-4, copy and MMA lanes 5");
+static_assert(PP_E_WARPS * (PP_E_REGS - PP_LAUNCH_REGS) <= 4 * (PP_LAUNCH_REGS - PP_IO_REGS), "register trade between the warp groups");
 
 // ---- shared memory ---------------------------------------------------------------------------------------
 // A slot: K bytes 0..255 in two 128-byte-swizzled slabs of 128 rows, K bytes 256..303 in three plain 16-byte
@@ -413,6 +419,7 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
             if (lane == 0) tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
         }
     } else if (warp == PP_ATMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PP_IO_REGS));
         // ------------------------------------------------------------------ activation copies (this CTA's 128 tokens)
         if (lane == 0) {
             PairAt at = pair_first(p, pair, pairs);
@@ -434,6 +441,7 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
                 if (!pp_wait_one(&ctl->ab_empty[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
         }
     } else if (warp == PP_WTMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PP_IO_REGS));
         // ------------------------------------------------------------------ raw weight records (this CTA's half of the tile's weights)
         if (lane == 0) {
             PairAt at = pair_first(p, pair, pairs);
@@ -451,6 +459,7 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
             for (int k = issued > PP_RAW_SLOTS ? issued - PP_RAW_SLOTS : 0; k < issued; ++k) mbar_wait(&ctl->raw_full[k % PP_RAW_SLOTS], (uint32_t)(k / PP_RAW_SLOTS) & 1u);
         }
     } else if (warp >= PP_MMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PP_IO_REGS));
         // ------------------------------------------------------------------ MMA issue (even CTA only), two issuers
         // One thread's wait / issue / commit sequence takes longer than the MMAs of a block run, so two threads take the
         // blocks in turn; each owns one TMEM buffer, and a commit covers the issuing thread's own MMAs only.
@@ -488,6 +497,7 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
             if (last >= 0 && !ctl->abort) pp_wait_one(&ctl->tmem_empty[q], ((uint32_t)(last >> 1) + 1u) & 1u, ctl, peer_abort, p.status);
         }
     } else if (warp < PP_E_WARPS) {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PP_E_REGS));
         // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, half of the tile's weights)
         const int quarter = warp & 3, grp = warp >> 2;
         const int row = quarter * 32 + lane;               // token row of this CTA = TMEM lane
@@ -1224,6 +1234,7 @@ cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t
     if (!prefill_pair_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
     if (a.fmt == F_TQ1_0) return launch_prefill_pair_tq1(a, sm_count, stream);
     cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_SMEM);
+    if (e == cudaSuccess) e = check_launch_registers(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_LAUNCH_REGS);
     if (e != cudaSuccess) return e;
     // how many pairs the device can hold at once (one CTA per SM: the shared memory of a CTA fills an SM)
     int pairs = 0;
