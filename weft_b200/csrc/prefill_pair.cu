@@ -611,7 +611,7 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
 //   activations  two TMA box copies (128 tokens x 128 bytes) into a ring of their own; the odd CTA's MMA warp forwards
 //                the landing of its boxes to the even CTA's barrier
 //   expanders    12 warps, four tasks per weight: bytes 0-15, 16-31, 32-47 of the record (16 table lookups, five operand
-//                chunks each) and the qh word with the two scales.  A warp is of one task kind; the lanes of a quarter
+//                chunks each, in the operand order described at tq_operand_element) and the qh word with the two scales.  A warp is of one task kind; the lanes of a quarter
 //                warp store their 16-byte chunks to eight different rows, whose swizzled positions never meet in a bank.
 //                The digits come from a table in shared memory (entry v = the five digits of byte value v, built from the
 //                caller's powers), sixteen copies so that the lookups of a half warp fall into different banks.
@@ -619,7 +619,7 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
 //   epilogue     16 warps = 4 lane quarters x 4 quarters of the tile's weights, up to 40 accumulators per thread; sixteen
 //                columns per tensor-memory load, the next load in flight during the arithmetic; x.d by one global load per
 //                thread and block, issued a block ahead
-// 512 x 28672 x 8192: 231 us per step (321 us on the first pair kernel, which read the records as they lie; 582 us on the
+// 512 x 28672 x 8192: 214 us per step (321 us on the first pair kernel, which read the records as they lie; 582 us on the
 // single-CTA kernel of prefill.cu).  With the expanders and the epilogue arithmetic switched off the kernel still takes
 // 146 us: 0.9 us per block of hand-overs between the roles against 0.36 us of tensor work.
 // Raw records: 54 bytes, rows of K/256 * 54 bytes (a multiple of 16 when K % 2048 == 0).  Record b of a row starts
@@ -731,34 +731,45 @@ __device__ __forceinline__ void tq_record_words(uint32_t src, uint32_t (&w)[4]) 
 #pragma unroll
     for (int i = 0; i < 4; ++i) w[i] = (O & 2) ? __funnelshift_r(r[j + i], r[j + i + 1], 16) : r[j + i];
 }
-// Heavy task: record bytes 16 PART .. 16 PART + 15 -> five operand chunks (digit n of those sixteen weights' bytes:
-// elements 32 n + 16 PART + [0, 16) for PART 0 and 1, 160 + 16 n + [0, 16) for PART 2).
+// Operand order inside a block.  A dot product does not care in which order its 256 terms are taken, as long as both
+// operands use the same one, and the plane kernel writes the activation codes in any order for free.  So the weights
+// are laid out the way the table delivers them, without transposing digits: with x(j) = digits 0..3 of record byte j
+// (one table word) and y(j) = its digit 4,
+//   chunks 5 p + s (p = 0..2, s = 0..3):  x(16 p + 4 s), x(16 p + 4 s + 1), x(16 p + 4 s + 2), x(16 p + 4 s + 3)
+//   chunk  5 p + 4:                        y(16 p), y(16 p + 1), ..., y(16 p + 15)
+//   chunk  15:                             x(48), x(49), x(50), x(51)      (the qh bytes: four digits each)
+// tq_operand_element() gives the block element (the reference's order) that sits at operand position k.
+__host__ __device__ constexpr int tq_element_of(int j, int n) {   // digit n of record byte j (qs 0..47, qh 48..51)
+    return j < 32 ? 32 * n + j : j < 48 ? 160 + 16 * n + (j - 32) : 240 + 4 * n + (j - 48);
+}
+__host__ __device__ constexpr int tq_operand_element(int k) {
+    if (k >= 240) return tq_element_of(48 + (k - 240) / 4, (k - 240) % 4);
+    const int p = k / 80, r = k % 80;
+    return r < 64 ? tq_element_of(16 * p + r / 4, r % 4) : tq_element_of(16 * p + (r - 64), 4);
+}
+// Heavy task: record bytes 16 PART .. 16 PART + 15 -> operand chunks 5 PART .. 5 PART + 4
 template <int PART, int O>
 __device__ __forceinline__ void tq_expand_heavy(uint32_t box, uint32_t lut, uint32_t b_slot, int row) {
     uint32_t w[4];
     tq_record_words<O>(box + 16u * (uint32_t)PART, w);
-    uint32_t digit[5][4];
+    const uint32_t base = b_slot + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(row & 7) << 4;
+    uint32_t last[4];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
         uint32_t x[4], y[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) tq_lookup(lut, w[s], i, x[i], y[i]);
-        const uint32_t t0 = prmt(x[0], x[1], 0x5140u), t1 = prmt(x[0], x[1], 0x7362u);
-        const uint32_t t2 = prmt(x[2], x[3], 0x5140u), t3 = prmt(x[2], x[3], 0x7362u);
-        digit[0][s] = prmt(t0, t2, 0x5410u); digit[1][s] = prmt(t0, t2, 0x7632u);
-        digit[2][s] = prmt(t1, t3, 0x5410u); digit[3][s] = prmt(t1, t3, 0x7632u);
-        digit[4][s] = prmt(prmt(y[0], y[1], 0x0040u), prmt(y[2], y[3], 0x0040u), 0x5410u);
+        constexpr int first = 5 * PART;
+        const int chunk = first + s;
+        sts_u128(base + (uint32_t)(chunk >> 3) * PT_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7), x[0], x[1], x[2], x[3]);
+        last[s] = prmt(prmt(y[0], y[1], 0x0040u), prmt(y[2], y[3], 0x0040u), 0x5410u);
     }
-    const uint32_t base = b_slot + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
-    const uint32_t x7 = (uint32_t)(row & 7) << 4;
-#pragma unroll
-    for (int n = 0; n < 5; ++n) {
-        const int chunk = PART < 2 ? 2 * n + PART : 10 + n;
-        sts_u128(base + (uint32_t)(chunk >> 3) * PT_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7), digit[n][0], digit[n][1], digit[n][2], digit[n][3]);
-    }
+    constexpr int chunk4 = 5 * PART + 4;
+    sts_u128(base + (uint32_t)(chunk4 >> 3) * PT_B_SLAB + (((uint32_t)(chunk4 & 7) << 4) ^ x7), last[0], last[1], last[2], last[3]);
 }
-// Light task: the qh word (record bytes 48..51: digit n of byte m is element 240 + 4 n + m, operand chunk 15) and the two
-// scales for the epilogue: this weight's d (record bytes 52, 53) and the d of the partner's weight of the same index.
+// Light task: the qh word (record bytes 48..51, operand chunk 15) and the two scales for the epilogue: this weight's d
+// (record bytes 52, 53) and the d of the partner's weight of the same index.
 template <int O>
 __device__ __forceinline__ void tq_expand_light(uint32_t box, uint32_t head, uint32_t lut, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner, int row) {
     constexpr int at_qh = O + 48, at_d = O + 52, at_pd = (O + 52) & 15;
@@ -769,11 +780,9 @@ __device__ __forceinline__ void tq_expand_light(uint32_t box, uint32_t head, uin
     uint32_t x[4], y[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) tq_lookup(lut, qh, i, x[i], y[i]);
-    const uint32_t t0 = prmt(x[0], x[1], 0x5140u), t1 = prmt(x[0], x[1], 0x7362u);
-    const uint32_t t2 = prmt(x[2], x[3], 0x5140u), t3 = prmt(x[2], x[3], 0x7362u);
     const uint32_t base = b_slot + (uint32_t)(row >> 3) * 1024u + (uint32_t)(row & 7) * 128u;
     const uint32_t x7 = (uint32_t)(row & 7) << 4;
-    sts_u128(base + PT_B_SLAB + ((7u << 4) ^ x7), prmt(t0, t2, 0x5410u), prmt(t0, t2, 0x7632u), prmt(t1, t3, 0x5410u), prmt(t1, t3, 0x7632u));
+    sts_u128(base + PT_B_SLAB + ((7u << 4) ^ x7), x[0], x[1], x[2], x[3]);
     sts_u32(wd_mine + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(d_mine & 0xffffu)));
     sts_u32(wd_partner + 4u * (uint32_t)row, __float_as_uint(half_bits_to_float(d_partner & 0xffffu)));
 }
@@ -831,19 +840,42 @@ __device__ __forceinline__ void tq_scale_add(uint64_t (&acc)[PP_RMAX / 4], const
     }
 }
 
-// Q8_K records -> planes: codes (m, k) int8 and x.d (k / 256, pitch) float.  One thread per 16 codes.
+// Q8_K records -> planes: codes (m, k) int8, every block in the operand order of tq_operand_element(), and x.d
+// (k / 256, pitch) float.  A CTA takes sixteen records: their codes go through shared memory, one thread per 16 output bytes.
 __global__ void __launch_bounds__(256) q8k_planes_kernel(const uint8_t *__restrict__ xq, int8_t *__restrict__ codes, float *__restrict__ xd, long long m, int nb, long long pitch) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    const long long record = idx >> 4;
-    const int c = (int)(idx & 15);
-    if (record >= m * nb) return;
-    const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + record * 292);   // records are 4-byte aligned
-    const uint4 v = make_uint4(src[1 + 4 * c], src[2 + 4 * c], src[3 + 4 * c], src[4 + 4 * c]);
-    *reinterpret_cast<uint4 *>(codes + record * 256 + 16 * c) = v;
-    if (c == 0) {
-        const long long t = record / nb;
-        xd[(record - t * nb) * pitch + t] = __uint_as_float(src[0]);
+    __shared__ __align__(16) uint8_t s_codes[16][256 + 16];   // + 16: the records of a CTA start in different banks
+    const int r = threadIdx.x >> 4, c = threadIdx.x & 15;
+    const long long record = (long long)blockIdx.x * 16 + r;
+    const bool live = record < m * nb;
+    if (live) {
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + record * 292);   // records are 4-byte aligned
+        *reinterpret_cast<uint4 *>(&s_codes[r][16 * c]) = make_uint4(src[1 + 4 * c], src[2 + 4 * c], src[3 + 4 * c], src[4 + 4 * c]);
+        if (c == 0) {
+            const long long t = record / nb;
+            xd[(record - t * nb) * pitch + t] = __uint_as_float(src[0]);
+        }
     }
+    __syncthreads();
+    if (!live) return;
+    uint32_t out[4];
+#pragma unroll
+    for (int wd = 0; wd < 4; ++wd) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            // the element at operand position 16 c + 4 wd + i (tq_operand_element, spelled with run-time c)
+            int e;
+            if (c == 15) e = 240 + 4 * i + wd;                        // x(48 + wd): digit i -> element 240 + 4 i + wd
+            else {
+                const int p = c / 5, s = c - 5 * p;
+                if (s < 4) { const int j = 16 * p + 4 * s + wd; e = p < 2 ? 32 * i + j : 160 + 16 * i + (j - 32); }
+                else { const int j = 16 * p + 4 * wd + i; e = p < 2 ? 128 + j : 224 + (j - 32); }
+            }
+            v |= (uint32_t)s_codes[r][e] << (8 * i);
+        }
+        out[wd] = v;
+    }
+    *reinterpret_cast<uint4 *>(codes + record * 256 + 16 * c) = make_uint4(out[0], out[1], out[2], out[3]);
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PT_THREADS, 1)
@@ -1209,8 +1241,8 @@ static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, c
     if (e != cudaSuccess) return e;
     p.xd = reinterpret_cast<const float *>(planes + code_bytes);
     {
-        const long long threads = a.m * p.nb * 16;
-        q8k_planes_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(static_cast<const uint8_t *>(a.xq), reinterpret_cast<int8_t *>(planes),
+        const long long records = a.m * p.nb;
+        q8k_planes_kernel<<<(unsigned)((records + 15) / 16), 256, 0, stream>>>(static_cast<const uint8_t *>(a.xq), reinterpret_cast<int8_t *>(planes),
                                                                                    reinterpret_cast<float *>(planes + code_bytes), a.m, p.nb, p.xd_pitch);
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
