@@ -305,7 +305,7 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
         PrefillArgs pa{fmt, w, xq, (const uint32_t *)pw, (float *)y, (long long)N, (long long)K, (long long)M, (long long)ldy, g.status_dev};
         const bool pair = prefill_pair_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
         if (launched(by_codebook ? launch_prefill_codebook(pa, (const int8_t *)gr, (const int8_t *)sg, sms, g.stream) : by_blocks ? launch_prefill_blocks(pa, sms, g.stream) : pair ? launch_prefill_pair(pa, sms, g.stream) : launch_prefill(pa, sms, g.stream), "prefill mul_mat",
-                     pair && fmt == F_TQ1_0 ? 2 : 1)) return 1;   // the TQ1_0 pair path launches its plane kernel first
+                     pair ? prefill_pair_launches(fmt) : 1)) return 1;   // the pair paths launch their plane kernel first
         if (gather && launched(launch_gather_push(*gather, (long long)M, (long long)N, (long long)ldy, g.status_dev, sms, g.stream), "peer all-gather")) return 1;
     } else {
         GemvArgs ga{fmt, w, xq, fuse_quantize ? (const float *)x : nullptr, (const int8_t *)gr, (const int8_t *)sg, (const uint32_t *)pw,

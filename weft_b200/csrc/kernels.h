@@ -79,6 +79,7 @@ bool prefill_supported(int fmt, long long n, long long k, long long m, const voi
 // The same contraction on CTA pairs (256 tokens per tile, tcgen05 cta_group::2): Q4_K with more than 128 tokens.
 cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream);
 bool prefill_pair_supported(int fmt, long long n, long long k, long long m, const void *w, const void *xq);
+int prefill_pair_launches(int fmt);   // kernels one launch_prefill_pair call puts on the stream (the plane kernel counts)
 
 // Q4_0 / Q8_0 x Q8_0 with more than a few tokens: one K = 32 contraction per 32-element block (both operands carry a
 // scale per block), accumulators rotating through tensor memory, scales applied in the epilogue.

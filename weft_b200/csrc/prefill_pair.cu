@@ -1141,6 +1141,385 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
     }
 }
 
+// ================================================================================================================
+// Q4_K x Q8_K on CTA pairs, reading activation PLANES (the arrangement of the TQ1_0 kernel above applied to the Q4_K
+// kernel at the top of this file; same exact-integer formulation, same tile and epilogue).  `q8k_planes_q4k_kernel`
+// turns the Q8_K records into the codes as an (M, K) int8 matrix, x.d as a (K/256, M) float matrix and, per token and
+// block, the min-term operand {l_0..l_7 | h_0..h_7} as sixteen f16 (bsum pair sums split as 64 h + l).  What that
+// removes from the contraction kernel: the operand shift and its four code variants in the expanders (no carried words,
+// no shuffles), the thin K chunk (eight K = 32 MMAs per block instead of nine), the three 16-byte activation columns and
+// the two per-token warps (the min-term operand arrives by TMA ready to use, x.d comes to the epilogue by a global load
+// issued a block ahead).
+constexpr int PQ_E_WARPS = 8, PQ_X_WARPS = 5, PQ_X_GROUPS = 2;
+constexpr int PQ_X_WARP0 = PQ_E_WARPS, PQ_PAD_WARP0 = PQ_X_WARP0 + PQ_X_GROUPS * PQ_X_WARPS;   // 18, 19: complete the fifth group of four
+constexpr int PQ_ATMA_WARP = 20, PQ_WTMA_WARP = 21, PQ_MMA_WARP = 22;
+constexpr int PQ_THREADS = 32 * 24;
+constexpr int PQ_LAUNCH_REGS = 80, PQ_E_REGS = 96, PQ_IO_REGS = 24;
+static_assert(PQ_PAD_WARP0 == 18 && PQ_E_WARPS * (PQ_E_REGS - PQ_LAUNCH_REGS) <= 4 * (PQ_LAUNCH_REGS - PQ_IO_REGS), "warp groups and their register trade");
+constexpr int PQ_STAGES = 3, PQ_RAW_SLOTS = 4, PQ_RING = 8;
+constexpr int PQ_A_SLAB = 128 * 128, PQ_A_MIN = 2 * PQ_A_SLAB, PQ_A_COL = 128 * 16, PQ_A_SLOT = PQ_A_MIN + 2 * PQ_A_COL;   // 36 KB
+constexpr int PQ_B_SLAB = PP_RMAX * 128, PQ_B_M = 2 * PQ_B_SLAB, PQ_B_SLOT = 22 * 1024;
+static_assert(PQ_B_M + (PP_RMAX / 2) * 32 <= PQ_B_SLOT && PQ_A_SLOT % 1024 == 0, "operand slots");
+constexpr int PQ_OFF_A = 1024;
+constexpr int PQ_OFF_B = PQ_OFF_A + PQ_STAGES * PQ_A_SLOT;
+constexpr int PQ_OFF_RAW = PQ_OFF_B + PQ_STAGES * PQ_B_SLOT;
+constexpr int PQ_OFF_WD = PQ_OFF_RAW + PQ_RAW_SLOTS * PP_RAW_SLOT;
+constexpr int PQ_SMEM = PQ_OFF_WD + PQ_RING * PP_WD_SLOT;
+static_assert(PQ_SMEM <= 227 * 1024 && PQ_OFF_B % 1024 == 0 && PQ_OFF_RAW % 128 == 0, "shared memory of the Q4_K plane kernel");
+
+struct QpControl {
+    uint64_t a_full[PQ_STAGES];          // this CTA's activation boxes (transaction bytes)
+    uint64_t a_peer[PQ_STAGES];          // EVEN CTA's copy is the live one: the odd CTA's boxes have landed
+    uint64_t raw_full[PQ_RAW_SLOTS];
+    uint64_t raw_empty[PQ_RAW_SLOTS];
+    uint64_t b_full[PQ_STAGES];          // EVEN CTA's copy is the live one: expander warps of both CTAs
+    uint64_t ab_empty[PQ_STAGES];        // both copies live: the MMAs that read the slots have completed
+    uint64_t tmem_full[2];               // both copies live
+    uint64_t tmem_empty[2];              // EVEN CTA's copy is the live one: epilogue warps of both CTAs
+    uint32_t tmem_base;
+    volatile int abort;
+};
+static_assert(sizeof(QpControl) <= PQ_OFF_A, "control block");
+
+struct QpAt {   // blocks in order, tiles round-robin over the pairs
+    int n0, m0, b, tile, pairs;
+    __device__ __forceinline__ void set_tile(const TqParams &p, int t) {
+        tile = t;
+        n0 = (t / p.m_tiles) * p.w;
+        m0 = (t % p.m_tiles) * (2 * PP_TOKENS);
+    }
+    __device__ __forceinline__ void advance(const TqParams &p) {
+        if (++b == p.nb) { b = 0; set_tile(p, tile + pairs); }
+    }
+};
+__device__ __forceinline__ QpAt qp_first(const TqParams &p, int pair, int pairs) {
+    QpAt at;
+    at.b = 0;
+    at.pairs = pairs;
+    at.set_tile(p, pair);
+    return at;
+}
+
+// Lane (i8, j) as in pp_expand: weight i8 of the warp's eight, part j (sub-blocks 2j and 2j+1, weights 64j..64j+63): two
+// scaled limbs into operand chunks 4j..4j+3 of rows i (hi) and half_rows + i (lo); part 0 also writes the min-term rows,
+// parts 1 and 2 the {d, -dmin} of this CTA's and of the partner's weight for the epilogue.
+__device__ __forceinline__ void pq_expand(uint32_t raw, uint32_t partner_head, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner, int i, int j, int half_rows) {
+    const uint4 hd = lds128(raw), qa = lds128(raw + 16 + 32 * j), qb = lds128(raw + 32 + 32 * j);
+    const Q4KScales s = q4k_unpack_scales(hd.y, hd.z, hd.w);
+    const uint32_t scv = j < 2 ? s.sc_lo : s.sc_hi;
+    const uint32_t sl = byte_of(scv, (2 * j) & 3), sh = byte_of(scv, ((2 * j) & 3) + 1);
+    const uint32_t al = sl >> 3, cl = sl & 7u, ah = sh >> 3, ch = sh & 7u;
+    const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+    const uint32_t base = b_slot + (uint32_t)(i >> 3) * 1024u + (uint32_t)(i & 7) * 128u;
+    const uint32_t x7 = (uint32_t)(i & 7) << 4;
+    const uint32_t lo_limb = (uint32_t)half_rows * 128u;
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {   // low nibbles: weights 64j..64j+31 (chunks 4j, 4j+1), high nibbles: 64j+32.. (chunks 4j+2, 4j+3)
+        uint32_t va[8], vc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t nib = (g ? q[k] >> 4 : q[k]) & 0x0f0f0f0fu;
+            // every byte product is <= 15 * 7 = 105: one 32-bit multiply scales four weights
+            va[k] = nib * (g ? ah : al);
+            vc[k] = nib * (g ? ch : cl);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int chunk = 4 * j + 2 * g + h;
+            const uint32_t at = base + (uint32_t)(chunk >> 3) * PQ_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7);
+            sts_u128(at, va[4 * h], va[4 * h + 1], va[4 * h + 2], va[4 * h + 3]);
+            sts_u128(at + lo_limb, vc[4 * h], vc[4 * h + 1], vc[4 * h + 2], vc[4 * h + 3]);
+        }
+    }
+    if (j == 0) {   // {mn} and {64 mn} as f16: the min-term rows of this weight
+        const uint32_t bm = b_slot + PQ_B_M + core_offset(i, 0, 2);
+        float mn[8];
+#pragma unroll
+        for (int g = 0; g < 8; ++g) mn[g] = (float)byte_of(g < 4 ? s.mn_lo : s.mn_hi, g & 3);
+        sts_u128(bm, pack_half2(mn[0], mn[1]), pack_half2(mn[2], mn[3]), pack_half2(mn[4], mn[5]), pack_half2(mn[6], mn[7]));
+        sts_u128(bm + 128u, pack_half2(64.f * mn[0], 64.f * mn[1]), pack_half2(64.f * mn[2], 64.f * mn[3]),
+                 pack_half2(64.f * mn[4], 64.f * mn[5]), pack_half2(64.f * mn[6], 64.f * mn[7]));
+    } else if (j < 3) {   // {d, -dmin} for the epilogue: part 1 takes this CTA's weight i, part 2 weight i of the partner's half
+        const uint32_t dd = j == 1 ? hd.x : lds_u32(partner_head);
+        const uint32_t d = __float_as_uint(half_bits_to_float(dd)), nm = __float_as_uint(-half_bits_to_float(dd >> 16));
+        const uint32_t at = (j == 1 ? wd_mine : wd_partner) + 16u * (uint32_t)(i >> 1) + 4u * (uint32_t)(i & 1);
+        sts_u32(at, d);
+        sts_u32(at + 8u, nm);
+    }
+}
+
+// Q8_K records -> planes for the Q4_K kernel: codes (m, k) int8 in the records' own order, x.d (k / 256, pitch) float, and the
+// min-term operand (m, k / 256 * 16) f16: per block the eight bsum pair sums s = 64 h + l (l in 0..63) as {l_0..l_7 | h_0..h_7}.
+__global__ void __launch_bounds__(256) q8k_planes_q4k_kernel(const uint8_t *__restrict__ xq, int8_t *__restrict__ codes, float *__restrict__ xd, __half *__restrict__ mins,
+                                                             long long m, int nb, long long pitch) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long record = idx >> 4;
+    const int c = (int)(idx & 15);
+    if (record >= m * nb) return;
+    const uint32_t *src = reinterpret_cast<const uint32_t *>(xq + record * 292);   // records are 4-byte aligned
+    *reinterpret_cast<uint4 *>(codes + record * 256 + 16 * c) = make_uint4(src[1 + 4 * c], src[2 + 4 * c], src[3 + 4 * c], src[4 + 4 * c]);
+    if (c < 8) {   // bsums 2c, 2c+1 are the two halves of record word 65 + c
+        int sum;
+        asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(sum) : "r"(src[65 + c]), "r"(0x0101u), "r"(0));
+        const int l = sum & 63;
+        mins[record * 16 + c] = __int2half_rn(l);
+        mins[record * 16 + 8 + c] = __int2half_rn((sum - l) >> 6);
+    } else if (c == 8) {
+        const long long t = record / nb;
+        xd[(record - t * nb) * pitch + t] = __uint_as_float(src[0]);
+    }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PQ_THREADS, 1)
+prefill_pair_q4k_planes_kernel(const TqParams p, const __grid_constant__ CUtensorMap x_codes, const __grid_constant__ CUtensorMap x_mins,
+                               const __grid_constant__ CUtensorMap w_rows, const __grid_constant__ CUtensorMap w_heads) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    QpControl *ctl = reinterpret_cast<QpControl *>(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = tc::cluster_ctarank();
+    const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
+    const int tiles = p.m_tiles * p.n_tiles;
+    const int nb = p.nb;
+    const int my_tiles = (tiles - pair + pairs - 1) / pairs;
+    const int total = my_tiles * nb;
+    const int half_rows = p.w >> 1;                       // weights this CTA expands per block = rows per limb
+    const int R = p.w;                                    // B rows per CTA
+
+    const uint32_t ctl_addr = smem_addr(ctl);
+    const uint32_t ctl_even = tc::map_to_cta(ctl_addr, 0), ctl_peer = tc::map_to_cta(ctl_addr, rank ^ 1u);
+    const uint32_t peer_abort = ctl_peer + (uint32_t)offsetof(QpControl, abort);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PQ_STAGES; ++s) {
+            mbar_init(&ctl->a_full[s], 1);
+            mbar_init(&ctl->a_peer[s], 1);
+            mbar_init(&ctl->b_full[s], 2 * PQ_X_WARPS);
+            mbar_init(&ctl->ab_empty[s], 1);
+        }
+        for (int s = 0; s < PQ_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 1); mbar_init(&ctl->raw_empty[s], PQ_X_WARPS); }
+        for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 2 * PQ_E_WARPS); }
+        ctl->abort = 0;
+        ctl->tmem_base = 0xffffffffu;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == PQ_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PP_TMEM_COLS);
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync_all();
+    tc::fence_after_sync();
+    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&ctl->tmem_base);
+    const bool tmem_ok = tmem == 0u;
+    if (!tmem_ok && threadIdx.x == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(p.status, 0x40000000 | (int)(tmem & 0xffffu) | (int)((tmem >> 16) & 0x3fffu) << 16); }
+    if (!tmem_ok) {
+        // nothing: fall through to the common exit
+    } else if (warp >= PQ_X_WARP0 && warp < PQ_PAD_WARP0) {
+        // ------------------------------------------------------------------ expanders: two groups taking the blocks in turn
+        const int xw = (warp - PQ_X_WARP0) % PQ_X_WARPS, xg = (warp - PQ_X_WARP0) / PQ_X_WARPS;
+        const int i8 = (lane >> 1) & 7, j = (lane & 1) | ((lane >> 4) << 1);
+        const int i = 8 * xw + i8;
+        const bool active = i < half_rows;
+        const uint32_t full_even = ctl_even + (uint32_t)offsetof(QpControl, b_full);
+        for (int it = xg; it < total && !ctl->abort; it += PQ_X_GROUPS) {
+            const int s = it % PQ_STAGES, rs = it % PQ_RAW_SLOTS;
+            if (!pp_wait_warp(&ctl->raw_full[rs], (uint32_t)(it / PQ_RAW_SLOTS) & 1u, ctl, peer_abort, p.status)) break;
+            if (!pp_wait_warp(&ctl->ab_empty[s], ((uint32_t)(it / PQ_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+            if (active) {
+                const uint32_t raw_slot = smem_addr(smem + PQ_OFF_RAW + rs * PP_RAW_SLOT);
+                const uint32_t wd_slot = smem_addr(smem + PQ_OFF_WD + (it & (PQ_RING - 1)) * PP_WD_SLOT);
+                pq_expand(raw_slot + (uint32_t)i * 144u, raw_slot + PP_RAW_HEADS + (uint32_t)i * 16u, smem_addr(smem + PQ_OFF_B + s * PQ_B_SLOT),
+                          wd_slot + rank * (uint32_t)(PP_WD_SLOT / 2), wd_slot + (rank ^ 1u) * (uint32_t)(PP_WD_SLOT / 2), i, j, half_rows);
+            }
+            fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&ctl->raw_empty[rs]);
+                tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
+            }
+        }
+    } else if (warp == PQ_ATMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PQ_IO_REGS));
+        // ------------------------------------------------------------------ activation copies (this CTA's 128 tokens)
+        if (lane == 0) {
+            QpAt at = qp_first(p, pair, pairs);
+            int issued = 0;
+            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
+                const int s = it % PQ_STAGES;
+                if (!pp_wait_one(&ctl->ab_empty[s], ((uint32_t)(it / PQ_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+                uint8_t *slot = smem + PQ_OFF_A + s * PQ_A_SLOT;
+                const int m0 = at.m0 + (int)rank * PP_TOKENS;
+                mbar_expect_tx(&ctl->a_full[s], PQ_A_SLOT);
+                // tokens past M read as zero
+                tma_load_2d(slot, &x_codes, 256 * at.b, m0, &ctl->a_full[s]);
+                tma_load_2d(slot + PQ_A_SLAB, &x_codes, 256 * at.b + 128, m0, &ctl->a_full[s]);
+                tma_load_2d(slot + PQ_A_MIN, &x_mins, 32 * at.b, m0, &ctl->a_full[s]);                // {l}: 16 bytes per token
+                tma_load_2d(slot + PQ_A_MIN + PQ_A_COL, &x_mins, 32 * at.b + 16, m0, &ctl->a_full[s]);  // {h}
+                issued = it + 1;
+            }
+            for (int k = issued > PQ_STAGES ? issued - PQ_STAGES : 0; k < issued; ++k) mbar_wait(&ctl->a_full[k % PQ_STAGES], (uint32_t)(k / PQ_STAGES) & 1u);
+            // stay until the even CTA's last commits have arrived on this CTA's barriers
+            for (int k = total > PQ_STAGES ? total - PQ_STAGES : 0; k < total && !ctl->abort; ++k)
+                if (!pp_wait_one(&ctl->ab_empty[k % PQ_STAGES], (uint32_t)(k / PQ_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+        }
+    } else if (warp == PQ_WTMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PQ_IO_REGS));
+        // ------------------------------------------------------------------ raw weight records (this CTA's half of the tile's weights)
+        if (lane == 0) {
+            QpAt at = qp_first(p, pair, pairs);
+            int issued = 0;
+            const uint32_t bytes = (uint32_t)half_rows * 160u;   // this CTA's records and the 16-byte headers of the partner's
+            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
+                const int rs = it % PQ_RAW_SLOTS;
+                if (!pp_wait_one(&ctl->raw_empty[rs], ((uint32_t)(it / PQ_RAW_SLOTS) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
+                mbar_expect_tx(&ctl->raw_full[rs], bytes);
+                tma_load_2d(smem + PQ_OFF_RAW + rs * PP_RAW_SLOT, &w_rows, 36 * at.b, at.n0 + (int)rank * half_rows, &ctl->raw_full[rs]);
+                tma_load_2d(smem + PQ_OFF_RAW + rs * PP_RAW_SLOT + PP_RAW_HEADS, &w_heads, 36 * at.b, at.n0 + (int)(rank ^ 1u) * half_rows, &ctl->raw_full[rs]);
+                issued = it + 1;
+            }
+            for (int k = issued > PQ_RAW_SLOTS ? issued - PQ_RAW_SLOTS : 0; k < issued; ++k) mbar_wait(&ctl->raw_full[k % PQ_RAW_SLOTS], (uint32_t)(k / PQ_RAW_SLOTS) & 1u);
+        }
+    } else if (warp >= PQ_MMA_WARP) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PQ_IO_REGS));
+        const int q = warp - PQ_MMA_WARP;
+        if (lane == 0 && rank == 0) {
+            // -------------------------------------------------------------- MMA issue (even CTA), two issuers, one TMEM buffer each
+            const uint32_t idesc_q = tc::idesc_i8(2 * PP_TOKENS, 2 * R, true, true);
+            const uint32_t idesc_m = tc::idesc_f16_f32acc(2 * PP_TOKENS, R);
+            const uint32_t full_mine = smem_addr(&ctl->tmem_full[q]), full_peer = ctl_peer + (uint32_t)offsetof(QpControl, tmem_full) + 8u * (uint32_t)q;
+            const uint32_t empty_peer = ctl_peer + (uint32_t)offsetof(QpControl, ab_empty);
+            const uint32_t d = tmem + (uint32_t)q * PP_BUF_COLS;
+            int last = -1;
+            for (int it = q; it < total && !ctl->abort; it += 2) {
+                const int s = it % PQ_STAGES;
+                if (!pp_wait_one(&ctl->a_full[s], (uint32_t)(it / PQ_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                if (!pp_wait_one(&ctl->a_peer[s], (uint32_t)(it / PQ_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                if (!pp_wait_one(&ctl->b_full[s], (uint32_t)(it / PQ_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                if (!pp_wait_one(&ctl->tmem_empty[q], (uint32_t)(it >> 1) & 1u, ctl, peer_abort, p.status)) break;
+                tc::fence_after_sync();
+                const uint32_t a_q = smem_addr(smem + PQ_OFF_A + s * PQ_A_SLOT), b_q = smem_addr(smem + PQ_OFF_B + s * PQ_B_SLOT);
+                const uint64_t a0 = tc::smem_desc_sw128(a_q), b0 = tc::smem_desc_sw128(b_q);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    tc::mma_i8_pair(d, a0 + (uint64_t)(((k >> 2) * PQ_A_SLAB + (k & 3) * 32) >> 4), b0 + (uint64_t)(((k >> 2) * PQ_B_SLAB + (k & 3) * 32) >> 4), idesc_q, 1);
+                // min term: A = {l | h} (two 16-byte columns), B = {mn | 64 mn}
+                tc::mma_f16_pair(d + PP_MIN_COL, tc::smem_desc(a_q + PQ_A_MIN, PQ_A_COL, 128), tc::smem_desc(b_q + PQ_B_M, 128, 256), idesc_m, 0);
+                tc::commit_pair(full_mine);
+                tc::commit_pair(full_peer);
+                tc::commit_pair(smem_addr(&ctl->ab_empty[s]));
+                tc::commit_pair(empty_peer + 8u * (uint32_t)s);
+                last = it;
+            }
+            if (last >= 0 && !ctl->abort) pp_wait_one(&ctl->tmem_empty[q], ((uint32_t)(last >> 1) + 1u) & 1u, ctl, peer_abort, p.status);
+        } else if (lane == 0 && rank == 1 && q == 0) {
+            // -------------------------------------------------------------- odd CTA: tell the even CTA that this CTA's activations have landed
+            const uint32_t peer_even = ctl_even + (uint32_t)offsetof(QpControl, a_peer);
+            for (int it = 0; it < total && !ctl->abort; ++it) {
+                const int s = it % PQ_STAGES;
+                if (!pp_wait_one(&ctl->a_full[s], (uint32_t)(it / PQ_STAGES) & 1u, ctl, peer_abort, p.status)) break;
+                tc::mbar_arrive_cluster(peer_even + 8u * (uint32_t)s);
+            }
+        }
+    } else if (warp < PQ_E_WARPS) {
+        // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, half of the tile's weights)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PQ_E_REGS));
+        const int quarter = warp & 3, grp = warp >> 2;
+        const int row = quarter * 32 + lane;               // token row of this CTA = TMEM lane
+        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t empty_even = ctl_even + (uint32_t)offsetof(QpControl, tmem_empty);
+        const int chunks = half_rows >> 3;                  // groups of 8 weights
+        // accumulators start at the bit pattern of 1.5 * 2^23
+        for (int buf = 0; buf < 2; ++buf) {
+            for (int c = 0; c < 2 * chunks; ++c) tc::tmem_st8_fill(lane_base + (uint32_t)(buf * PP_BUF_COLS + grp * R + 8 * c), PP_BIAS);
+            tc::tmem_st_wait();
+            tc::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
+        }
+        uint64_t acc[PP_RMAX / 4];   // packed pairs of fp32: up to 40 weights
+        const uint64_t bias2 = pack2(-12582912.f, -12582912.f), eight2 = pack2(8.f, 8.f);
+        QpAt at = qp_first(p, pair, pairs);
+        int it = 0;
+        bool ok = true;
+        int m = at.m0 + (int)rank * PP_TOKENS + row;
+        float xd_next = m < p.m ? __ldg(p.xd + (long long)at.b * p.xd_pitch + m) : 0.f;
+        for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
+            const long long n0 = (long long)at.n0 + grp * half_rows;
+            m = at.m0 + (int)rank * PP_TOKENS + row;
+#pragma unroll
+            for (int k = 0; k < PP_RMAX / 4; ++k) acc[k] = 0ull;
+            for (int b = 0; b < nb && ok; ++b, ++it) {
+                const int buf = it & 1;
+                const float xd = xd_next;
+                at.advance(p);
+                if (it + 1 < total) {   // x.d of the next block (of the next tile's tokens after the last block of a tile)
+                    const int mn = at.m0 + (int)rank * PP_TOKENS + row;
+                    xd_next = mn < p.m ? __ldg(p.xd + (long long)at.b * p.xd_pitch + mn) : 0.f;
+                }
+                if (!pp_wait_warp(&ctl->tmem_full[buf], (uint32_t)(it >> 1) & 1u, ctl, peer_abort, p.status)) { ok = false; break; }
+                tc::fence_after_sync();
+                const ulonglong2 *wd = reinterpret_cast<const ulonglong2 *>(smem + PQ_OFF_WD + (it & (PQ_RING - 1)) * PP_WD_SLOT + grp * (PP_WD_SLOT / 2));
+                const uint64_t xd2 = pack2(xd, xd);
+                const uint32_t limb = lane_base + (uint32_t)(buf * PP_BUF_COLS + grp * R);
+                const uint32_t mins = lane_base + (uint32_t)(buf * PP_BUF_COLS + PP_MIN_COL + grp * half_rows);
+#pragma unroll
+                for (int c = 0; c < PP_RMAX / 16; ++c) {
+                    if (c < chunks) {
+                        uint32_t hi[8], lo[8], mt[8];
+                        tc::tmem_ld8(limb + 8 * c, hi);
+                        tc::tmem_ld8(limb + half_rows + 8 * c, lo);
+                        tc::tmem_ld8(mins + 8 * c, mt);
+                        tc::tmem_ld_wait();
+                        tc::tmem_st8_fill(limb + 8 * c, PP_BIAS);
+                        tc::tmem_st8_fill(limb + half_rows + 8 * c, PP_BIAS);
+#pragma unroll
+                        for (int k = 0; k < 8; k += 2) {
+                            const ulonglong2 s2 = wd[(8 * c + k) >> 1];   // {d, d'}, {-dmin, -dmin'}
+                            const uint64_t fh = add2(pack2(__uint_as_float(hi[k]), __uint_as_float(hi[k + 1])), bias2);
+                            const uint64_t fl = add2(pack2(__uint_as_float(lo[k]), __uint_as_float(lo[k + 1])), bias2);
+                            const uint64_t v = fma2(eight2, fh, fl);
+                            const uint64_t u = fma2(s2.y, pack2(__uint_as_float(mt[k]), __uint_as_float(mt[k + 1])), mul2(s2.x, v));
+                            acc[(8 * c + k) >> 1] = fma2(xd2, u, acc[(8 * c + k) >> 1]);
+                        }
+                    }
+                }
+                tc::tmem_st_wait();
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
+            }
+            if (!ok) break;
+            if (m < p.m) {
+                float *out = p.y + (size_t)m * p.ldy + n0;
+                const bool vec = (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+#pragma unroll
+                for (int k = 0; k < PP_RMAX / 2; k += 4) {
+                    if (k < half_rows) {
+                        if (vec && n0 + k + 4 <= p.n) {
+                            *reinterpret_cast<ulonglong2 *>(out + k) = make_ulonglong2(acc[k >> 1], acc[(k >> 1) + 1]);
+                        } else {
+                            float a0, a1, a2, a3;
+                            unpack2(acc[k >> 1], a0, a1);
+                            unpack2(acc[(k >> 1) + 1], a2, a3);
+                            if (n0 + k < p.n) out[k] = a0;
+                            if (n0 + k + 1 < p.n) out[k + 1] = a1;
+                            if (n0 + k + 2 < p.n) out[k + 2] = a2;
+                            if (n0 + k + 3 < p.n) out[k + 3] = a3;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::cluster_sync_all();
+    if (warp == PQ_MMA_WARP) {
+        __syncwarp();
+        if (tmem_ok) tc::tmem_free(tmem, PP_TMEM_COLS);
+    }
+}
+
 // w in {32, 64, 96, 128, 160} for TQ1_0: minimise (rounds of the grid) x (fixed part + w), ties to the wider tile
 int pick_tile_width_tq1(long long n, int m_tiles, int pairs) {
     int best = 32;
@@ -1262,9 +1641,69 @@ static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, c
     return cudaGetLastError();
 }
 
+constexpr bool kQ4kOnPlanes = true;   // the Q4_K pair kernel that reads activation planes (false: the one that reads the Q8_K records as they lie)
+
+static cudaError_t launch_prefill_pair_q4k_planes(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
+    cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_q4k_planes_kernel), PQ_SMEM);
+    if (e == cudaSuccess) e = check_launch_registers(reinterpret_cast<const void *>(prefill_pair_q4k_planes_kernel), PQ_LAUNCH_REGS);
+    if (e != cudaSuccess) return e;
+    int pairs = 0;
+    {
+        cudaLaunchConfig_t probe = {};
+        probe.gridDim = dim3((unsigned)sm_count & ~1u);
+        probe.blockDim = dim3(PQ_THREADS);
+        probe.dynamicSmemBytes = PQ_SMEM;
+        if (cudaOccupancyMaxActiveClusters(&pairs, prefill_pair_q4k_planes_kernel, &probe) != cudaSuccess) { cudaGetLastError(); pairs = sm_count / 2; }
+        if (pairs < 1) return cudaErrorNotSupported;
+        if (pairs > sm_count / 2) pairs = sm_count / 2;
+    }
+    TqParams p;
+    p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
+    p.m_tiles = (int)((a.m + 2 * PP_TOKENS - 1) / (2 * PP_TOKENS));
+    p.w = pick_tile_width(a.n, p.m_tiles, pairs);
+    p.n_tiles = (int)((a.n + p.w - 1) / p.w);
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    if (tiles < pairs) pairs = (int)tiles;
+    // planes: codes (m, k) int8, x.d (nb, pitch) float, min-term operand (m, nb * 16) f16
+    p.xd_pitch = (a.m + 63) & ~63LL;
+    const size_t code_bytes = ((size_t)a.m * (size_t)a.k + 255) & ~size_t(255);
+    const size_t xd_bytes = ((size_t)p.nb * (size_t)p.xd_pitch * sizeof(float) + 255) & ~size_t(255);
+    uint8_t *planes = nullptr;
+    e = reserve_planes(code_bytes + xd_bytes + (size_t)a.m * (size_t)p.nb * 32, &planes);
+    if (e != cudaSuccess) return e;
+    p.xd = reinterpret_cast<const float *>(planes + code_bytes);
+    uint8_t *mins = planes + code_bytes + xd_bytes;
+    {
+        const long long threads = a.m * p.nb * 16;
+        q8k_planes_q4k_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(static_cast<const uint8_t *>(a.xq), reinterpret_cast<int8_t *>(planes),
+                                                                                       reinterpret_cast<float *>(planes + code_bytes), reinterpret_cast<__half *>(mins), a.m, p.nb, p.xd_pitch);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    CUtensorMap x_codes, x_mins, w_rows, w_heads;
+    e = encode_tile_map(&x_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, planes, (unsigned long long)a.k, (unsigned long long)a.m,
+                        (unsigned long long)a.k, 128, PP_TOKENS, true);
+    if (e == cudaSuccess)
+        e = encode_tile_map(&x_mins, CU_TENSOR_MAP_DATA_TYPE_UINT8, mins, (unsigned long long)p.nb * 32, (unsigned long long)a.m,
+                            (unsigned long long)p.nb * 32, 16, PP_TOKENS, false);
+    // the weight matrix as (n) rows of 36 * nb words
+    if (e == cudaSuccess)
+        e = encode_tile_map(&w_rows, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.w, (unsigned long long)p.nb * 36, (unsigned long long)a.n,
+                            (unsigned long long)p.nb * 144, 36, (unsigned)(p.w / 2), false);
+    if (e == cudaSuccess)
+        e = encode_tile_map(&w_heads, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.w, (unsigned long long)p.nb * 36, (unsigned long long)a.n,
+                            (unsigned long long)p.nb * 144, 4, (unsigned)(p.w / 2), false);
+    if (e != cudaSuccess) return e;
+    prefill_pair_q4k_planes_kernel<<<2 * pairs, PQ_THREADS, PQ_SMEM, stream>>>(p, x_codes, x_mins, w_rows, w_heads);
+    return cudaGetLastError();
+}
+
+int prefill_pair_launches(int fmt) { return fmt == F_TQ1_0 || kQ4kOnPlanes ? 2 : 1; }
+
 cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!prefill_pair_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
     if (a.fmt == F_TQ1_0) return launch_prefill_pair_tq1(a, sm_count, stream);
+    if (kQ4kOnPlanes) return launch_prefill_pair_q4k_planes(a, sm_count, stream);
     cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_SMEM);
     if (e == cudaSuccess) e = check_launch_registers(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_LAUNCH_REGS);
     if (e != cudaSuccess) return e;
