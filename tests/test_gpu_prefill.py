@@ -51,9 +51,11 @@ def test_prefill_q4_k_one_tile(torch, oracle):
     _run(torch, oracle, 128, 128, 256, seed=1)
 
 
-@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 512), (512, 384, 1024), (32, 128, 4096), (200, 1000, 2048), (512, 4736, 1024)])
+@pytest.mark.parametrize("mnk", [(128, 128, 1024), (130, 200, 512), (512, 384, 1024), (32, 128, 4096), (200, 1000, 2048), (512, 4736, 1024),
+                                 (300, 77, 768), (257, 1001, 1280), (129, 16, 256)])
 def test_prefill_q4_k_shapes(torch, oracle, mnk):
-    """Tiles are 128 x 112 or 128 x 128, whichever leaves the last round of the grid fuller: (512, 4736) takes 128."""
+    """Up to 128 tokens the single-CTA kernel (K a multiple of 1024; the GEMV per token row otherwise); above, the CTA-pair kernel
+    on activation planes with tiles of 256 tokens x 16..80 weights, for every K that is a multiple of 256; ragged N and M."""
     m, n, k = mnk
     _run(torch, oracle, m, n, k, seed=sum(mnk))
 

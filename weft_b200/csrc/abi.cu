@@ -295,7 +295,8 @@ int do_mul_mat(int fmt, int mode, const void *W, const float *X, void *Xq, const
     const int sms = g.prop.multiProcessorCount;
     const bool by_blocks = mode == 1 && prefill_blocks_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
     const bool by_codebook = mode == 1 && gr && sg && prefill_codebook_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq);
-    const bool to_prefill = by_blocks || by_codebook || (mode == 1 && prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq));
+    const bool to_prefill = by_blocks || by_codebook || (mode == 1 && (prefill_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq) ||
+                                                                       prefill_pair_supported(fmt, (long long)N, (long long)K, (long long)M, w, xq)));
     // decode: the GEMV's own prologue quantizes X (one launch) when the fp32 rows allow 16-byte loads
     const bool fuse_quantize = !have_xq && !to_prefill && K % 256 == 0 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
     if (!have_xq && !fuse_quantize &&

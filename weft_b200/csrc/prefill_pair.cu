@@ -1,37 +1,31 @@
-// Prefill contraction for token batches above 128: Q4_K x Q8_K on the int8 tensor cores with CTA PAIRS
-// (tcgen05.mma cta_group::2).  Same function as prefill.cu -- the reference's production_mul_mat_q4_k_staged
+// Prefill contractions for token batches above 128 on the int8 tensor cores with CTA PAIRS (tcgen05.mma
+// cta_group::2): Q4_K x Q8_K -- the reference's production_mul_mat_q4_k_staged
 // (examples/kernels/mul_mat/q4_k_staged.py:9-37; per block the math of examples/kernels/vec_dot/q4_k_q8_k.py:8-29,
-// GGML ggml-cpu/quants.c:645-718) -- and the same exact-integer formulation: the 6-bit scale split as 8a + c and
-// folded into two int8 weight limbs, the min term as one K = 16 MMA on exact small f16 integers, activation
-// codes brought in by TMA with the weight operand shifted to meet them (see prefill.cu for the derivation).
+// GGML ggml-cpu/quants.c:645-718) -- and TQ1_0 x Q8_K (production_mul_mat_tq1_0).  Same functions as prefill.cu and
+// the same exact-integer formulation (see prefill.cu for the derivation): for Q4_K the 6-bit scale split as 8a + c and
+// folded into two int8 weight limbs, the min term as one K = 16 MMA on exact small f16 integers.
 //
-// Tensor-core bound: 2*M*N*K useful integer ops; issued ops are twice that (two limbs).
+// Tensor-core bound: 2*M*N*K useful integer ops; Q4_K issues twice that (two limbs).
 //
-// What the pair changes.  A pair of CTAs on the two SMs of a TPC owns a tile of 256 tokens x w weights
-// (w = 16..80 in steps of 16, picked per launch so that the last round of the grid is as full as possible).
-// Each CTA holds its 128 tokens (TMEM lanes, A operand) and expands HALF of the tile's weights: one
-// N = 2w MMA per K step covers both limbs of all w weights, so every Q4_K record is expanded once per 256
-// tokens and the activation slab is read once per block.  Per 256-block and CTA:
-//   raw weights  one TMA box copy of w/2 records (144 B each) into a 4-slot ring, three blocks ahead
-//   activations  five TMA box copies (128 tokens x 304 bytes) into a 3-slot ring
-//   expanders    two groups of 5 warps that take the blocks in turn, four lanes per weight (lane = one pair of
-//                sub-blocks): nibbles -> two scaled limbs,
-//                shifted by the block's operand shift (neighbouring lanes exchange the carried words by
-//                shuffle), written as the K-major 128-byte-swizzled operand; lane layout chosen so that the
-//                16-byte stores of a quarter-warp never meet in a bank
-//   specials     2 warps: x.d of every token to a ring; the bsum pair sums, split as 64 h + l, to f16 in the
-//                two operand columns behind the codes (those bytes only ever meet zero weights in the int8 MMA)
-//   MMA          one lane of the even CTA: 9 int8 K steps (N = 2w) + 1 f16 K = 16 step (N = w), into one of two
-//                TMEM buffers; commits free the operand slots and publish the buffer in BOTH CTAs
-//   epilogue     8 warps = 4 lane quarters x the two halves of the tile's weights; per element
-//                acc += x.d * (d * f32(8 hi + lo) - dmin * msum) in the reference's op order.  The int32
-//                accumulators start at the bit pattern of 1.5 * 2^23 instead of zero (the epilogue writes it
-//                back after every read), so what comes out of TMEM is already the float 1.5 * 2^23 + limb:
-//                one packed subtraction converts two limbs, no integer-to-float instruction is issued.
-// Every wait is bounded; a wait that runs out raises an abort flag in both CTAs, every role leaves its loop,
-// copies in flight are waited for, tensor memory is freed, and the host sees a status code instead of a hang.
-// No copy, store or MMA touches another CTA's shared memory except the 8-byte scale words and the barrier
-// arrivals inside the pair; nothing here reads or writes another GPU's memory.
+// A pair of CTAs on the two SMs of a TPC owns a tile of 256 tokens x w weights (w picked per launch so that the last
+// round of the grid is as full as possible).  Each CTA holds its 128 tokens (TMEM lanes, A operand) and expands HALF of
+// the tile's weights: one MMA per K step covers all w weights, so every weight record is expanded once per 256 tokens
+// and the activations of a block are read once.
+//
+// Both kernels read the activations from PLANES that a small kernel makes of the Q8_K records just before: the codes as
+// an (M, K) int8 matrix, x.d as a (K/256, M) float matrix (and for Q4_K the min-term operand).  The records themselves
+// start every block at a different offset from a 16-byte boundary; the planes make a block's codes 256 aligned bytes
+// per token: two 128-byte-swizzled TMA boxes, eight K = 32 MMAs, expanded weights written as whole 16-byte chunks.
+//
+// Roles (warps): expanders (raw records from a TMA ring -> int8 operand rows), one activation-copy lane, one
+// weight-copy lane, two MMA-issuing lanes of the even CTA taking the blocks in turn (the odd CTA's first one forwards
+// the landing of its activation boxes), epilogue warps (tensor memory -> scaled fp32 accumulators in registers).  The
+// roles trade registers in whole groups of four warps (setmaxnreg); a group can only take what other groups of the same
+// CTA have given back, never registers the CTA did not get at launch.
+// Every wait is bounded; a wait that runs out raises an abort flag in both CTAs, every role leaves its loop, copies
+// in flight are waited for, tensor memory is freed, and the host sees a status code instead of a hang.  No copy,
+// store or MMA touches another CTA's shared memory except the barrier arrivals inside the pair; nothing here reads or
+// writes another GPU's memory.
 #include "prefill_common.cuh"
 #include "kernels.h"
 #include "ring.cuh"
@@ -43,53 +37,13 @@ namespace weft {
 namespace {
 
 constexpr int PP_TOKENS = 128;                 // tokens per CTA = TMEM lanes; a pair covers 256
-constexpr int PP_RMAX = 80;                    // B rows per CTA at most: [hi limb of w/2 weights | lo limb of w/2 weights]
-constexpr int PP_STAGES = 3;                   // operand slots (activations + expanded weights)
-constexpr int PP_RAW_SLOTS = 4;                // raw-record ring
-constexpr int PP_RING = 8;                     // x.d / weight-scale rings (see the note at their use)
-constexpr int PP_E_WARPS = 8, PP_X_WARPS = 5, PP_X_GROUPS = 2, PP_S_WARPS = 2;   // expander groups take the blocks in turn
-constexpr int PP_X_WARP0 = PP_E_WARPS, PP_S_WARP0 = PP_X_WARP0 + PP_X_GROUPS * PP_X_WARPS;
-constexpr int PP_ATMA_WARP = PP_S_WARP0 + PP_S_WARPS, PP_WTMA_WARP = PP_ATMA_WARP + 1, PP_MMA_WARP = PP_WTMA_WARP + 1;
-constexpr int PP_MMA_WARPS = 2;                 // issuer q takes the blocks with it % 2 == q: one TMEM buffer each
-constexpr int PP_THREADS = 32 * (PP_MMA_WARP + PP_MMA_WARPS);   // 24 warps
-// Registers: 80 per thread at launch; the epilogue (warp groups 0 and 1) takes sixteen more from what the copy and MMA
-// lanes (group 5) give back.  A group can only take what other groups of the same CTA have released.
-constexpr int PP_LAUNCH_REGS = 80, PP_E_REGS = 96, PP_IO_REGS = 24;
-static_assert(PP_THREADS == 768 && PP_E_WARPS == 8 && PP_X_GROUPS * PP_X_WARPS + PP_S_WARPS == 12, "warp groups of four: epilogue 0-1, expanders and per-token warps 2-4, copy and MMA lanes 5");
-static_assert(PP_E_WARPS * (PP_E_REGS - PP_LAUNCH_REGS) <= 4 * (PP_LAUNCH_REGS - PP_IO_REGS), "register trade between the warp groups");
-
-// ---- shared memory ---------------------------------------------------------------------------------------
-// A slot: K bytes 0..255 in two 128-byte-swizzled slabs of 128 rows, K bytes 256..303 in three plain 16-byte
-// columns (128 rows x 16 bytes each, i.e. stacked 8 x 16 core matrices).  Columns 1 and 2 are rewritten by the
-// specials warps as the f16 min-term operand {l | h}.
-constexpr int PP_A_SLAB = 128 * 128;
-constexpr int PP_A_COL = 128 * 16;
-constexpr int PP_A_THIN = 2 * PP_A_SLAB;
-constexpr int PP_A_SLOT = PP_A_THIN + 3 * PP_A_COL;          // 38 KB
-// B slot: two swizzled slabs of PP_RMAX rows, two plain columns (the second is always zero), the f16 rows {mn | 64 mn}
-constexpr int PP_B_SLAB = PP_RMAX * 128;
-constexpr int PP_B_COL = PP_RMAX * 16;
-constexpr int PP_B_THIN = 2 * PP_B_SLAB;
-constexpr int PP_B_M = PP_B_THIN + 2 * PP_B_COL;
-constexpr int PP_B_SLOT = 24 * 1024;
-static_assert(PP_B_M + (PP_RMAX / 2) * 32 <= PP_B_SLOT, "B slot");
-constexpr int PP_RAW_HEADS = (PP_RMAX / 2) * 144;            // after the records: the 16-byte headers of the partner's weights
+constexpr int PP_RMAX = 80;                    // B rows per CTA at most
+constexpr int PP_MMA_WARPS = 2;                // issuer q takes the blocks with it % 2 == q
+constexpr int PP_RAW_HEADS = (PP_RMAX / 2) * 144;            // Q4_K raw slot: after the records, the 16-byte headers of the partner's weights
 constexpr int PP_RAW_SLOT = PP_RAW_HEADS + (PP_RMAX / 2) * 16;  // 6400 B
-constexpr int PP_WD_SLOT = 2 * (PP_RMAX / 2) * 8;            // {d, -dmin} per weight of both halves: 640 B
-constexpr int PP_XD_SLOT = PP_TOKENS * 4;
+constexpr int PP_WD_SLOT = 2 * (PP_RMAX / 2) * 8;            // Q4_K: {d, -dmin} per weight of both halves: 640 B
 
-constexpr int PP_CONTROL = 1024;
-constexpr int PP_OFF_A = PP_CONTROL;
-constexpr int PP_OFF_B = PP_OFF_A + PP_STAGES * PP_A_SLOT;
-constexpr int PP_OFF_RAW = PP_OFF_B + PP_STAGES * PP_B_SLOT;
-constexpr int PP_OFF_WD = PP_OFF_RAW + PP_RAW_SLOTS * PP_RAW_SLOT;
-constexpr int PP_OFF_XD = PP_OFF_WD + PP_RING * PP_WD_SLOT;
-constexpr int PP_SMEM = PP_OFF_XD + PP_RING * PP_XD_SLOT;
-static_assert(PP_OFF_A % 1024 == 0 && PP_A_SLOT % 1024 == 0 && PP_OFF_B % 1024 == 0 && PP_B_SLOT % 1024 == 0, "swizzled slabs must stay 1024-byte aligned");
-static_assert(PP_B_SLAB % 1024 == 0 && PP_OFF_RAW % 128 == 0 && PP_RAW_SLOT % 128 == 0, "alignment of the rings");
-static_assert(PP_SMEM <= 227 * 1024, "shared memory budget");
-
-// ---- tensor memory: two buffers of 256 columns; limbs [0, 2w), min term [160, 160 + w) ----------------------
+// ---- tensor memory of the Q4_K kernel: two buffers of 256 columns; limbs [0, 2w), min term [160, 160 + w) ----------
 constexpr int PP_TMEM_COLS = 512;
 constexpr int PP_BUF_COLS = 256;
 constexpr int PP_MIN_COL = 2 * PP_RMAX;
@@ -100,22 +54,11 @@ struct PairParams {
     long long n, m, ldy;
     int nb;                // 256-blocks per row
     int m_tiles, n_tiles;  // tiles of 256 tokens, of w weights
-    int w;                 // weights per tile (multiple of 16, <= PP_RMAX)
+    int w;                 // weights per tile
+    const float *xd;       // (nb, xd_pitch): x.d of every token and block
+    long long xd_pitch;
     int *status;
 };
-
-struct PairControl {
-    uint64_t a_landed[PP_STAGES];        // this CTA's activation boxes (transaction bytes)
-    uint64_t raw_full[PP_RAW_SLOTS];     // this CTA's raw records (transaction bytes)
-    uint64_t raw_empty[PP_RAW_SLOTS];    // expander warps of this CTA are done reading the slot
-    uint64_t ab_full[PP_STAGES];         // EVEN CTA's copy is the live one: expander + specials warps of both CTAs
-    uint64_t ab_empty[PP_STAGES];        // both copies live: the MMAs that read the slot have completed
-    uint64_t tmem_full[2];               // both copies live: the buffer's accumulators are complete
-    uint64_t tmem_empty[2];              // EVEN CTA's copy is the live one: epilogue warps of both CTAs
-    uint32_t tmem_base;
-    volatile int abort;
-};
-static_assert(sizeof(PairControl) <= PP_CONTROL, "control block");
 
 // Bounded wait by one thread; gives up as soon as another role (of either CTA) has raised the abort flag.  The suspending
 // form of the wait: a lane that spins on test_wait issues an instruction every few cycles and takes a third of its
@@ -164,435 +107,6 @@ __device__ __forceinline__ bool pp_wait_warp_relaxed(uint64_t *bar, uint32_t par
 // Blocks of the pair's work list: tiles round-robin over the pairs; inside a tile the blocks are taken as
 // 0, 4, 8, ..., 1, 5, 9, ..., so that blocks with the same operand shift follow each other and the producers stay
 // in one of their four code variants for a quarter of the tile.
-struct PairAt {
-    long long n0, m0;
-    int b, tile, pairs;
-    __device__ __forceinline__ void set_tile(const PairParams &p, int t) {
-        tile = t;
-        n0 = (long long)(t / p.m_tiles) * p.w;
-        m0 = (long long)(t % p.m_tiles) * (2 * PP_TOKENS);
-    }
-    __device__ __forceinline__ void advance(const PairParams &p) {
-        b += 4;
-        if (b >= p.nb) {
-            b = (b & 3) + 1;
-            if (b == 4) { b = 0; set_tile(p, tile + pairs); }
-        }
-    }
-};
-__device__ __forceinline__ PairAt pair_first(const PairParams &p, int pair, int pairs) {
-    PairAt at;
-    at.b = 0;
-    at.pairs = pairs;
-    at.set_tile(p, pair);
-    return at;
-}
-
-// ---- expanders -----------------------------------------------------------------------------------------------
-// Lane (i8, j): weight i8 = 0..7 of the warp's eight, part j = 0..3 (sub-blocks 2j and 2j+1, weights 64j..64j+63 of
-// the block).  lane = 16 (j >> 1) + 2 i8 + (j & 1): the four parts of the weights in one quarter-warp store to
-// distinct 16-byte bank groups of the swizzled rows.
-// The limb bytes of a block form a stream of 64 words per limb; part j owns stream words 16j..16j+15.  With the
-// operand shift of W words they land at K words 16j + W .., so an output chunk (4 words) takes its first words from
-// the previous part: those W words come over by shuffle.
-template <int W>
-__device__ __forceinline__ void pp_expand(uint32_t raw, uint32_t partner_head, uint32_t b_slot, uint32_t wd_mine, uint32_t wd_partner, int i, int j, int half_rows, bool active) {
-    const int lane = threadIdx.x & 31;
-    uint4 hd = make_uint4(0, 0, 0, 0), qa = hd, qb = hd;
-    if (active) {
-        hd = lds128(raw);
-        qa = lds128(raw + 16 + 32 * j);
-        qb = lds128(raw + 32 + 32 * j);
-    }
-    const Q4KScales s = q4k_unpack_scales(hd.y, hd.z, hd.w);
-    const uint32_t scv = j < 2 ? s.sc_lo : s.sc_hi;
-    const uint32_t sl = byte_of(scv, (2 * j) & 3), sh = byte_of(scv, ((2 * j) & 3) + 1);
-    const uint32_t al = sl >> 3, cl = sl & 7u, ah = sh >> 3, ch = sh & 7u;
-    uint32_t cur_a[16], cur_c[16];
-    {
-        const uint32_t q[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const uint32_t lo = q[k] & 0x0f0f0f0fu, hi = (q[k] >> 4) & 0x0f0f0f0fu;
-            // every byte product is <= 15 * 7 = 105: one 32-bit multiply scales four weights
-            cur_a[k] = lo * al;      cur_c[k] = lo * cl;
-            cur_a[8 + k] = hi * ah;  cur_c[8 + k] = hi * ch;
-        }
-    }
-    // the last W stream words of the previous part (zeros in front of part 0)
-    const int src = j == 0 ? lane : (16 * ((j - 1) >> 1) + (lane & 14) + ((j - 1) & 1));
-    uint32_t ca[4] = {0, 0, 0, 0}, cc[4] = {0, 0, 0, 0};
-#pragma unroll
-    for (int k = 0; k < W; ++k) {
-        const uint32_t va = __shfl_sync(0xffffffffu, cur_a[16 - W + k], src);
-        const uint32_t vc = __shfl_sync(0xffffffffu, cur_c[16 - W + k], src);
-        ca[k] = j == 0 ? 0u : va;
-        cc[k] = j == 0 ? 0u : vc;
-    }
-    if (!active) return;
-    // rows i (hi limb) and half_rows + i (lo limb): same position inside the 8-row group, half_rows * 128 bytes apart
-    const uint32_t base = b_slot + (uint32_t)(i >> 3) * 1024u + (uint32_t)(i & 7) * 128u;
-    const uint32_t x7 = (uint32_t)(i & 7) << 4;
-    const uint32_t lo_limb = (uint32_t)half_rows * 128u;
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        uint32_t oa[4], oc[4];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int idx = 4 * q + k;
-            oa[k] = idx < W ? ca[idx < W ? idx : 0] : cur_a[idx < W ? 0 : idx - W];
-            oc[k] = idx < W ? cc[idx < W ? idx : 0] : cur_c[idx < W ? 0 : idx - W];
-        }
-        const int chunk = 4 * j + q;   // 16-byte K chunk 0..15
-        const uint32_t at = base + (uint32_t)(chunk >> 3) * PP_B_SLAB + (((uint32_t)(chunk & 7) << 4) ^ x7);
-        sts_u128(at, oa[0], oa[1], oa[2], oa[3]);
-        sts_u128(at + lo_limb, oc[0], oc[1], oc[2], oc[3]);
-    }
-    if (j == 3) {   // K chunk 16: the carried words of the last part, then zeros (chunk 17 stays zero for ever)
-        const uint32_t thin = b_slot + PP_B_THIN + (uint32_t)i * 16u;
-        sts_u128(thin, cur_a[16 - W], W > 1 ? cur_a[17 - W] : 0u, W > 2 ? cur_a[18 - W] : 0u, W > 3 ? cur_a[19 - W] : 0u);
-        sts_u128(thin + (uint32_t)half_rows * 16u, cur_c[16 - W], W > 1 ? cur_c[17 - W] : 0u, W > 2 ? cur_c[18 - W] : 0u, W > 3 ? cur_c[19 - W] : 0u);
-    } else if (j == 0) {   // {mn} and {64 mn} as f16: the min-term rows of this weight
-        const uint32_t bm = b_slot + PP_B_M + core_offset(i, 0, 2);
-        float mn[8];
-#pragma unroll
-        for (int g = 0; g < 8; ++g) mn[g] = (float)byte_of(g < 4 ? s.mn_lo : s.mn_hi, g & 3);
-        sts_u128(bm, pack_half2(mn[0], mn[1]), pack_half2(mn[2], mn[3]), pack_half2(mn[4], mn[5]), pack_half2(mn[6], mn[7]));
-        sts_u128(bm + 128u, pack_half2(64.f * mn[0], 64.f * mn[1]), pack_half2(64.f * mn[2], 64.f * mn[3]),
-                 pack_half2(64.f * mn[4], 64.f * mn[5]), pack_half2(64.f * mn[6], 64.f * mn[7]));
-    } else {       // {d, -dmin} for the epilogue: part 1 takes this CTA's weight i, part 2 weight i of the partner's half
-        const uint32_t dd = j == 1 ? hd.x : lds_u32(partner_head);
-        const uint32_t d = __float_as_uint(half_bits_to_float(dd)), nm = __float_as_uint(-half_bits_to_float(dd >> 16));
-        // per pair of weights {d, d', -dmin, -dmin'}
-        const uint32_t at = (j == 1 ? wd_mine : wd_partner) + 16u * (uint32_t)(i >> 1) + 4u * (uint32_t)(i & 1);
-        sts_u32(at, d);
-        sts_u32(at + 8u, nm);
-    }
-}
-
-// ---- specials --------------------------------------------------------------------------------------------------
-// One token row per call: x.d to the ring; the eight bsum pair sums s = 64 h + l (l in 0..63) as f16 into operand
-// columns 1 (l) and 2 (h) of the row.  W = (b & 3) + 1: record byte r sits at operand byte r + 4 (W - 1).
-template <int W>
-__device__ __forceinline__ void pp_special_row(uint32_t a_slot, uint32_t xd_slot, int row) {
-    const uint32_t thin = a_slot + PP_A_THIN + (uint32_t)row * 16u;
-    const uint4 c0 = lds128(thin), c1 = lds128(thin + PP_A_COL), c2 = lds128(thin + 2 * PP_A_COL);
-    const uint32_t w[12] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w, c2.x, c2.y, c2.z, c2.w};
-    const uint32_t xd = lds_u32(a_slot + sw128_offset(row, 0) + 4u * (uint32_t)(W - 1));
-    uint32_t l2[4], h2[4];
-#pragma unroll
-    for (int g = 0; g < 8; g += 2) {
-        int s0, s1;   // bsums 2g, 2g+1 are record bytes 260 + 4g ..: operand word 65 + g + (W - 1) = thin word g + W
-        asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(s0) : "r"(w[g + W]), "r"(0x0101u), "r"(0));
-        asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(s1) : "r"(w[g + 1 + W]), "r"(0x0101u), "r"(0));
-        const int l0 = s0 & 63, l1 = s1 & 63;
-        l2[g >> 1] = (uint32_t)__half_as_ushort(__int2half_rn(l0)) | ((uint32_t)__half_as_ushort(__int2half_rn(l1)) << 16);
-        h2[g >> 1] = (uint32_t)__half_as_ushort(__int2half_rn((s0 - l0) >> 6)) | ((uint32_t)__half_as_ushort(__int2half_rn((s1 - l1) >> 6)) << 16);
-    }
-    sts_u128(thin + PP_A_COL, l2[0], l2[1], l2[2], l2[3]);
-    sts_u128(thin + 2 * PP_A_COL, h2[0], h2[1], h2[2], h2[3]);
-    sts_u32(xd_slot + 4u * (uint32_t)row, xd);
-}
-
-__device__ __forceinline__ void pp_issue_activations(const CUtensorMap *wide, const CUtensorMap *narrow, int b, int m0, uint8_t *slot, uint64_t *bar) {
-    // word x0 = 73 b - (b & 3) of a token row is the 16-byte boundary at or before record b
-    const int x0 = 73 * b - (b & 3);
-    mbar_expect_tx(bar, PP_A_SLOT);
-    tma_load_2d(slot, wide, x0, m0, bar);
-    tma_load_2d(slot + PP_A_SLAB, wide, x0 + 32, m0, bar);
-    tma_load_2d(slot + PP_A_THIN, narrow, x0 + 64, m0, bar);
-    tma_load_2d(slot + PP_A_THIN + PP_A_COL, narrow, x0 + 68, m0, bar);
-    tma_load_2d(slot + PP_A_THIN + 2 * PP_A_COL, narrow, x0 + 72, m0, bar);
-}
-
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PP_THREADS, 1)
-prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap x_wide, const __grid_constant__ CUtensorMap x_narrow,
-                        const __grid_constant__ CUtensorMap w_rows, const __grid_constant__ CUtensorMap w_heads) {
-    extern __shared__ __align__(1024) uint8_t smem[];
-    PairControl *ctl = reinterpret_cast<PairControl *>(smem);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = tc::cluster_ctarank();          // 0: issues the MMAs; 1: partner
-    const int pair = (int)blockIdx.x >> 1, pairs = (int)gridDim.x >> 1;
-    const int tiles = p.m_tiles * p.n_tiles;
-    const int nb = p.nb;
-    const int my_tiles = (tiles - pair + pairs - 1) / pairs;
-    const int total = my_tiles * nb;                      // 256-blocks the pair works through
-    const int half_rows = p.w >> 1;                       // weights this CTA expands per block = rows per limb
-    const int R = p.w;                                    // B rows per CTA
-
-    // where the partner and the even CTA keep their copies of the control block
-    const uint32_t ctl_addr = smem_addr(ctl);
-    const uint32_t ctl_even = tc::map_to_cta(ctl_addr, 0), ctl_peer = tc::map_to_cta(ctl_addr, rank ^ 1u);
-    const uint32_t peer_abort = ctl_peer + (uint32_t)offsetof(PairControl, abort);
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < PP_STAGES; ++s) {
-            mbar_init(&ctl->a_landed[s], 1);
-            mbar_init(&ctl->ab_full[s], 2 * (PP_X_WARPS + PP_S_WARPS));
-            mbar_init(&ctl->ab_empty[s], 1);
-        }
-        for (int s = 0; s < PP_RAW_SLOTS; ++s) { mbar_init(&ctl->raw_full[s], 1); mbar_init(&ctl->raw_empty[s], PP_X_WARPS); }
-        for (int h = 0; h < 2; ++h) { mbar_init(&ctl->tmem_full[h], 1); mbar_init(&ctl->tmem_empty[h], 2 * PP_E_WARPS); }
-        ctl->abort = 0;
-        ctl->tmem_base = 0xffffffffu;
-        mbar_fence_init();
-    }
-    // K chunk 17 of every weight slot (operand bytes 272..287) is zero for the whole kernel
-    for (int i = threadIdx.x; i < PP_STAGES * PP_RMAX * 4; i += PP_THREADS) {
-        const int s = i / (PP_RMAX * 4), r = i % (PP_RMAX * 4);
-        reinterpret_cast<uint32_t *>(smem + PP_OFF_B + s * PP_B_SLOT + PP_B_THIN + PP_B_COL)[r] = 0u;
-    }
-    fence_proxy_async();
-    __syncthreads();
-    // Each CTA allocates its own tensor memory (cta_group::1: no pair-wide allocation protocol); the pair's MMAs then
-    // use the same columns in both.
-    if (warp == PP_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PP_TMEM_COLS);
-    tc::fence_before_sync();
-    __syncthreads();
-    tc::cluster_sync_all();          // barriers of both CTAs are initialised before anyone arrives on the partner's
-    tc::fence_after_sync();
-    const uint32_t tmem = *reinterpret_cast<volatile uint32_t *>(&ctl->tmem_base);
-    // The pair asked for all 512 columns, so the only valid base is lane 0, column 0; anything else means the allocation
-    // went wrong: say so and take no role (the partner's waits are bounded).
-    const bool tmem_ok = tmem == 0u;
-    if (!tmem_ok && threadIdx.x == 0) { ctl->abort = 1; tc::st_cluster_u32(peer_abort, 1u); report(p.status, 0x40000000 | (int)(tmem & 0xffffu) | (int)((tmem >> 16) & 0x3fffu) << 16); }
-    if (!tmem_ok) {
-        // nothing: fall through to the common exit
-    } else if (warp >= PP_X_WARP0 && warp < PP_X_WARP0 + PP_X_GROUPS * PP_X_WARPS) {
-        // ------------------------------------------------------------------ expanders
-        const int xw = (warp - PP_X_WARP0) % PP_X_WARPS, xg = (warp - PP_X_WARP0) / PP_X_WARPS;
-        const int i8 = (lane >> 1) & 7, j = (lane & 1) | ((lane >> 4) << 1);
-        const int i = 8 * xw + i8;
-        const bool active = i < half_rows;
-        PairAt at = pair_first(p, pair, pairs);
-        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
-        for (int skip = 0; skip < xg && skip < total; ++skip) at.advance(p);
-        for (int it = xg; it < total && !ctl->abort; it += PP_X_GROUPS) {
-            const int words = (at.b & 3) + 1;
-            for (int skip = 0; skip < PP_X_GROUPS; ++skip) at.advance(p);
-            const int s = it % PP_STAGES, rs = it % PP_RAW_SLOTS;
-            if (!pp_wait_warp(&ctl->raw_full[rs], (uint32_t)(it / PP_RAW_SLOTS) & 1u, ctl, peer_abort, p.status)) break;
-            if (!pp_wait_warp(&ctl->ab_empty[s], ((uint32_t)(it / PP_STAGES) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
-            const uint32_t raw_slot = smem_addr(smem + PP_OFF_RAW + rs * PP_RAW_SLOT);
-            const uint32_t raw = raw_slot + (uint32_t)i * 144u, partner_head = raw_slot + PP_RAW_HEADS + (uint32_t)i * 16u;
-            const uint32_t b_slot = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
-            // the scales of the tile's weights, this CTA's half and the partner's, in the order of the tile
-            const uint32_t wd_slot = smem_addr(smem + PP_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT);
-            const uint32_t wd_mine = wd_slot + rank * (uint32_t)(PP_WD_SLOT / 2), wd_partner = wd_slot + (rank ^ 1u) * (uint32_t)(PP_WD_SLOT / 2);
-            switch (words) {
-            case 1: pp_expand<1>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
-            case 2: pp_expand<2>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
-            case 3: pp_expand<3>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
-            default: pp_expand<4>(raw, partner_head, b_slot, wd_mine, wd_partner, i, j, half_rows, active); break;
-            }
-            fence_proxy_async();      // generic-proxy stores must be visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&ctl->raw_empty[rs]);
-                tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
-            }
-        }
-    } else if (warp >= PP_S_WARP0 && warp < PP_S_WARP0 + PP_S_WARPS) {
-        // ------------------------------------------------------------------ x.d and the min-term operand of the landed activations
-        const int ts = threadIdx.x - 32 * PP_S_WARP0;   // 0..63, rows ts and ts + 64
-        PairAt at = pair_first(p, pair, pairs);
-        const uint32_t full_even = ctl_even + (uint32_t)offsetof(PairControl, ab_full);
-        for (int it = 0; it < total && !ctl->abort; ++it) {
-            const int words = (at.b & 3) + 1;
-            at.advance(p);
-            const int s = it % PP_STAGES;
-            if (!pp_wait_warp(&ctl->a_landed[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
-            const uint32_t a_slot = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT);
-            const uint32_t xd_slot = smem_addr(smem + PP_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT);
-#pragma unroll
-            for (int k = 0; k < 2; ++k) {
-                const int row = ts + 64 * k;
-                switch (words) {
-                case 1: pp_special_row<1>(a_slot, xd_slot, row); break;
-                case 2: pp_special_row<2>(a_slot, xd_slot, row); break;
-                case 3: pp_special_row<3>(a_slot, xd_slot, row); break;
-                default: pp_special_row<4>(a_slot, xd_slot, row); break;
-                }
-            }
-            fence_proxy_async();
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive_cluster(full_even + 8u * (uint32_t)s);
-        }
-    } else if (warp == PP_ATMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PP_IO_REGS));
-        // ------------------------------------------------------------------ activation copies (this CTA's 128 tokens)
-        if (lane == 0) {
-            PairAt at = pair_first(p, pair, pairs);
-            int issued = 0;
-            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
-                const int s = it % PP_STAGES;
-                const uint32_t phase = (uint32_t)(it / PP_STAGES) & 1u;
-                // the slot was last read by the MMAs of block it - PP_STAGES (and, before them, by the specials warps)
-                if (!pp_wait_one(&ctl->ab_empty[s], phase ^ 1u, ctl, peer_abort, p.status)) break;
-                fence_proxy_async();
-                pp_issue_activations(&x_wide, &x_narrow, at.b, (int)at.m0 + (int)rank * PP_TOKENS, smem + PP_OFF_A + s * PP_A_SLOT, &ctl->a_landed[s]);
-                issued = it + 1;
-            }
-            // left early: let the copies in flight land (a phase that has completed already returns at once)
-            for (int k = issued > PP_STAGES ? issued - PP_STAGES : 0; k < issued; ++k) mbar_wait(&ctl->a_landed[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u);
-            // The even CTA's commits arrive on this CTA's barriers when the MMAs complete, whoever still waits for them:
-            // stay until the last ones have landed, so that none can reach a CTA that has already left the SM.
-            for (int k = total > PP_STAGES ? total - PP_STAGES : 0; k < total && !ctl->abort; ++k)
-                if (!pp_wait_one(&ctl->ab_empty[k % PP_STAGES], (uint32_t)(k / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
-        }
-    } else if (warp == PP_WTMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PP_IO_REGS));
-        // ------------------------------------------------------------------ raw weight records (this CTA's half of the tile's weights)
-        if (lane == 0) {
-            PairAt at = pair_first(p, pair, pairs);
-            int issued = 0;
-            const uint32_t bytes = (uint32_t)half_rows * 160u;   // this CTA's records and the 16-byte headers of the partner's
-            for (int it = 0; it < total && !ctl->abort; ++it, at.advance(p)) {
-                const int rs = it % PP_RAW_SLOTS;
-                if (!pp_wait_one(&ctl->raw_empty[rs], ((uint32_t)(it / PP_RAW_SLOTS) & 1u) ^ 1u, ctl, peer_abort, p.status)) break;
-                mbar_expect_tx(&ctl->raw_full[rs], bytes);
-                // rows past N read as zero records (d = dmin = 0: they contribute nothing and are never stored)
-                tma_load_2d(smem + PP_OFF_RAW + rs * PP_RAW_SLOT, &w_rows, 36 * at.b, (int)at.n0 + (int)rank * half_rows, &ctl->raw_full[rs]);
-                tma_load_2d(smem + PP_OFF_RAW + rs * PP_RAW_SLOT + PP_RAW_HEADS, &w_heads, 36 * at.b, (int)at.n0 + (int)(rank ^ 1u) * half_rows, &ctl->raw_full[rs]);
-                issued = it + 1;
-            }
-            for (int k = issued > PP_RAW_SLOTS ? issued - PP_RAW_SLOTS : 0; k < issued; ++k) mbar_wait(&ctl->raw_full[k % PP_RAW_SLOTS], (uint32_t)(k / PP_RAW_SLOTS) & 1u);
-        }
-    } else if (warp >= PP_MMA_WARP) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(PP_IO_REGS));
-        // ------------------------------------------------------------------ MMA issue (even CTA only), two issuers
-        // One thread's wait / issue / commit sequence takes longer than the MMAs of a block run, so two threads take the
-        // blocks in turn; each owns one TMEM buffer, and a commit covers the issuing thread's own MMAs only.
-        const int q = warp - PP_MMA_WARP;
-        if (lane == 0 && rank == 0) {
-            const uint32_t idesc_q = tc::idesc_i8(2 * PP_TOKENS, 2 * R, true, true);
-            const uint32_t idesc_m = tc::idesc_f16_f32acc(2 * PP_TOKENS, R);
-            const uint32_t full_mine = smem_addr(&ctl->tmem_full[q]), full_peer = ctl_peer + (uint32_t)offsetof(PairControl, tmem_full) + 8u * (uint32_t)q;
-            const uint32_t empty_peer = ctl_peer + (uint32_t)offsetof(PairControl, ab_empty);
-            const uint32_t d = tmem + (uint32_t)q * PP_BUF_COLS;
-            int last = -1;
-            for (int it = q; it < total && !ctl->abort; it += PP_MMA_WARPS) {
-                const int s = it % PP_STAGES;
-                if (!pp_wait_one(&ctl->ab_full[s], (uint32_t)(it / PP_STAGES) & 1u, ctl, peer_abort, p.status)) break;
-                // arrival n on tmem_empty: n = 0 the initial fill, n >= 1 after the epilogue of the buffer's n-th use
-                if (!pp_wait_one(&ctl->tmem_empty[q], (uint32_t)(it >> 1) & 1u, ctl, peer_abort, p.status)) break;
-                tc::fence_after_sync();
-                const uint32_t a_q = smem_addr(smem + PP_OFF_A + s * PP_A_SLOT), b_q = smem_addr(smem + PP_OFF_B + s * PP_B_SLOT);
-                const uint64_t a0 = tc::smem_desc_sw128(a_q), b0 = tc::smem_desc_sw128(b_q);
-#pragma unroll
-                for (int k = 0; k < 8; ++k)   // K = 32 per instruction: 32 bytes further inside the swizzled row, next slab after 4 (address field in 16-byte units)
-                    tc::mma_i8_pair(d, a0 + (uint64_t)(((k >> 2) * PP_A_SLAB + (k & 3) * 32) >> 4), b0 + (uint64_t)(((k >> 2) * PP_B_SLAB + (k & 3) * 32) >> 4), idesc_q, 1);
-                // K bytes 256..287: two 16-byte columns, K-adjacent core matrices one column apart
-                tc::mma_i8_pair(d, tc::smem_desc(a_q + PP_A_THIN, PP_A_COL, 128), tc::smem_desc(b_q + PP_B_THIN, PP_B_COL, 128), idesc_q, 1);
-                // min term: A = {l | h} in operand columns 1 and 2, B = {mn | 64 mn}
-                tc::mma_f16_pair(d + PP_MIN_COL, tc::smem_desc(a_q + PP_A_THIN + PP_A_COL, PP_A_COL, 128), tc::smem_desc(b_q + PP_B_M, 128, 256), idesc_m, 0);
-                tc::commit_pair(full_mine);
-                tc::commit_pair(full_peer);
-                tc::commit_pair(smem_addr(&ctl->ab_empty[s]));
-                tc::commit_pair(empty_peer + 8u * (uint32_t)s);
-                last = it;
-            }
-            // the epilogues of both CTAs arrive once more after the last use of the buffer: receive those arrivals
-            // before this CTA may leave
-            if (last >= 0 && !ctl->abort) pp_wait_one(&ctl->tmem_empty[q], ((uint32_t)(last >> 1) + 1u) & 1u, ctl, peer_abort, p.status);
-        }
-    } else if (warp < PP_E_WARPS) {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PP_E_REGS));
-        // ------------------------------------------------------------------ epilogue: warp = (32-token quarter, half of the tile's weights)
-        const int quarter = warp & 3, grp = warp >> 2;
-        const int row = quarter * 32 + lane;               // token row of this CTA = TMEM lane
-        const uint32_t lane_base = tmem + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t empty_even = ctl_even + (uint32_t)offsetof(PairControl, tmem_empty);
-        const int chunks = half_rows >> 3;                  // groups of 8 weights
-        // accumulators start at the bit pattern of 1.5 * 2^23
-        for (int buf = 0; buf < 2; ++buf) {
-            for (int c = 0; c < 2 * chunks; ++c) tc::tmem_st8_fill(lane_base + (uint32_t)(buf * PP_BUF_COLS + grp * R + 8 * c), PP_BIAS);
-            tc::tmem_st_wait();
-            tc::fence_before_sync();
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
-        }
-        uint64_t acc[PP_RMAX / 4];   // packed pairs of fp32: up to 40 weights
-        const uint64_t bias2 = pack2(-12582912.f, -12582912.f), eight2 = pack2(8.f, 8.f);
-        int it = 0;
-        bool ok = true;
-        for (int t = 0; t < my_tiles && ok && !ctl->abort; ++t) {
-            const int tile = pair + t * pairs;
-            const long long n0 = (long long)(tile / p.m_tiles) * p.w + grp * half_rows;
-            const long long m = (long long)(tile % p.m_tiles) * (2 * PP_TOKENS) + (long long)rank * PP_TOKENS + row;
-#pragma unroll
-            for (int k = 0; k < PP_RMAX / 4; ++k) acc[k] = 0ull;
-            for (int b = 0; b < nb && ok; ++b, ++it) {
-                const int buf = it & 1;
-                if (!pp_wait_warp(&ctl->tmem_full[buf], (uint32_t)(it >> 1) & 1u, ctl, peer_abort, p.status)) { ok = false; break; }
-                tc::fence_after_sync();
-                // The rings are PP_RING deep: the slot of block it is rewritten for block it + PP_RING, whose producers run
-                // only after the MMAs of block it + PP_RING - PP_STAGES, and those need this epilogue to have freed the buffer.
-                const float xd = reinterpret_cast<const float *>(smem + PP_OFF_XD + (it & (PP_RING - 1)) * PP_XD_SLOT)[row];
-                const ulonglong2 *wd = reinterpret_cast<const ulonglong2 *>(smem + PP_OFF_WD + (it & (PP_RING - 1)) * PP_WD_SLOT + grp * (PP_WD_SLOT / 2));
-                const uint64_t xd2 = pack2(xd, xd);
-                const uint32_t limb = lane_base + (uint32_t)(buf * PP_BUF_COLS + grp * R);
-                const uint32_t mins = lane_base + (uint32_t)(buf * PP_BUF_COLS + PP_MIN_COL + grp * half_rows);
-#pragma unroll
-                for (int c = 0; c < PP_RMAX / 16; ++c) {
-                    if (c < chunks) {
-                        uint32_t hi[8], lo[8], mt[8];
-                        tc::tmem_ld8(limb + 8 * c, hi);
-                        tc::tmem_ld8(limb + half_rows + 8 * c, lo);
-                        tc::tmem_ld8(mins + 8 * c, mt);
-                        tc::tmem_ld_wait();
-                        tc::tmem_st8_fill(limb + 8 * c, PP_BIAS);
-                        tc::tmem_st8_fill(limb + half_rows + 8 * c, PP_BIAS);
-#pragma unroll
-                        for (int k = 0; k < 8; k += 2) {
-                            const ulonglong2 s2 = wd[(8 * c + k) >> 1];   // {d, d'}, {-dmin, -dmin'}
-                            // limbs arrive as 1.5 * 2^23 + integer: subtracting the constant is exact; f32(8 hi + lo) rounds once
-                            const uint64_t fh = add2(pack2(__uint_as_float(hi[k]), __uint_as_float(hi[k + 1])), bias2);
-                            const uint64_t fl = add2(pack2(__uint_as_float(lo[k]), __uint_as_float(lo[k + 1])), bias2);
-                            const uint64_t v = fma2(eight2, fh, fl);
-                            const uint64_t u = fma2(s2.y, pack2(__uint_as_float(mt[k]), __uint_as_float(mt[k + 1])), mul2(s2.x, v));
-                            acc[(8 * c + k) >> 1] = fma2(xd2, u, acc[(8 * c + k) >> 1]);
-                        }
-                    }
-                }
-                tc::tmem_st_wait();
-                tc::fence_before_sync();
-                __syncwarp();
-                if (lane == 0) tc::mbar_arrive_cluster(empty_even + 8u * (uint32_t)buf);
-            }
-            if (!ok) break;
-            if (m < p.m) {
-                float *out = p.y + (size_t)m * p.ldy + n0;
-                const bool vec = (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
-#pragma unroll
-                for (int k = 0; k < PP_RMAX / 2; k += 4) {
-                    if (k < half_rows) {
-                        if (vec && n0 + k + 4 <= p.n) {
-                            *reinterpret_cast<ulonglong2 *>(out + k) = make_ulonglong2(acc[k >> 1], acc[(k >> 1) + 1]);
-                        } else {
-                            float a0, a1, a2, a3;
-                            unpack2(acc[k >> 1], a0, a1);
-                            unpack2(acc[(k >> 1) + 1], a2, a3);
-                            if (n0 + k < p.n) out[k] = a0;
-                            if (n0 + k + 1 < p.n) out[k + 1] = a1;
-                            if (n0 + k + 2 < p.n) out[k + 2] = a2;
-                            if (n0 + k + 3 < p.n) out[k + 3] = a3;
-                        }
-                    }
-                }
-            }
-        }
-    }
-
-    tc::fence_before_sync();
-    __syncthreads();
-    tc::cluster_sync_all();      // neither CTA leaves, or frees tensor memory, while the other may still use the pair's resources
-    if (warp == PP_MMA_WARP) {
-        __syncwarp();
-        if (tmem_ok) tc::tmem_free(tmem, PP_TMEM_COLS);
-    }
-}
-
 // ================================================================================================================
 // TQ1_0 x Q8_K on CTA pairs (production_mul_mat_tq1_0, examples/kernels/mul_mat/tq1_0.py; per block the math of
 // examples/kernels/vec_dot/tq1_0_q8_k.py:9-55, GGML ggml-cpu/quants.c:430-480).  The weight operand is the base-3 digits
@@ -600,11 +114,8 @@ prefill_pair_q4k_kernel(const PairParams p, const __grid_constant__ CUtensorMap 
 // w/2 operand rows, N = w), an accumulator buffer is w <= 160 columns and THREE of them fit in tensor memory; the epilogue
 // is acc += f32(isum) * (d * x.d) on one column per weight.
 //
-// Activations come from PLANES that a small kernel makes of the Q8_K records before this one runs: the codes as an
-// (M, K) int8 matrix, x.d as an (K/256, M) float matrix.  The codes of a block are then 256 aligned bytes per token --
-// two 128-byte-swizzled TMA boxes, eight K = 32 MMAs, nothing shifted -- and the expanded weights are written as whole
-// 16-byte operand chunks.  (The Q8_K records themselves start every block at a different offset from a 16-byte
-// boundary, which the Q4_K kernel above meets by shifting the weight operand.)
+// Activations come from the planes of q8k_planes_kernel: the codes as an (M, K) int8 matrix in the operand order
+// described at tq_operand_element(), x.d as an (K/256, M) float matrix.
 //
 // Per 256-block and CTA:
 //   raw weights  two TMA box copies (w/2 records in 80-byte boxes; the 16-byte boxes with the partner's d) into a ring
@@ -659,17 +170,6 @@ static_assert(PT_SMEM <= 227 * 1024 && PT_RAW_SLOT % 128 == 0 && PT_B_SLAB % 102
               "shared memory of the TQ1_0 kernel");
 static_assert(PT_RING > PT_B_STAGES + PT_BUFS, "the expanders run at most B slots + accumulator buffers ahead of the epilogue");
 
-struct TqParams {
-    float *y;              // (m, ldy)
-    long long n, m, ldy;
-    int nb;                // 256-blocks per row
-    int m_tiles, n_tiles;  // tiles of 256 tokens, of w weights
-    int w;                 // weights per tile (multiple of 32, <= 2 * PP_RMAX)
-    const float *xd;       // (nb, xd_pitch): x.d of every token and block
-    long long xd_pitch;
-    int *status;
-};
-
 struct TqControl {
     uint64_t a_full[PT_A_STAGES];        // this CTA's activation boxes (transaction bytes)
     uint64_t a_peer[PT_A_STAGES];        // EVEN CTA's copy is the live one: the odd CTA's boxes have landed
@@ -689,12 +189,12 @@ static_assert(sizeof(TqControl) <= PT_OFF_A, "control block");
 struct TqAt {
     int n0, m0;          // first weight and first token of the tile (both below 2^31)
     int b, tile, pairs;
-    __device__ __forceinline__ void set_tile(const TqParams &p, int t) {
+    __device__ __forceinline__ void set_tile(const PairParams &p, int t) {
         tile = t;
         n0 = (t / p.m_tiles) * p.w;
         m0 = (t % p.m_tiles) * (2 * PP_TOKENS);
     }
-    __device__ __forceinline__ void advance(const TqParams &p) {
+    __device__ __forceinline__ void advance(const PairParams &p) {
         b += 8;
         if (b >= p.nb) {
             b = (b & 7) + 1;
@@ -702,7 +202,7 @@ struct TqAt {
         }
     }
 };
-__device__ __forceinline__ TqAt tq_first(const TqParams &p, int pair, int pairs) {
+__device__ __forceinline__ TqAt tq_first(const PairParams &p, int pair, int pairs) {
     TqAt at;
     at.b = 0;
     at.pairs = pairs;
@@ -747,6 +247,16 @@ __host__ __device__ constexpr int tq_operand_element(int k) {
     const int p = k / 80, r = k % 80;
     return r < 64 ? tq_element_of(16 * p + r / 4, r % 4) : tq_element_of(16 * p + (r - 64), 4);
 }
+constexpr bool tq_operand_order_is_a_permutation() {
+    for (int k = 0; k < 256; ++k) {
+        const int e = tq_operand_element(k);
+        if (e < 0 || e > 255) return false;
+        for (int other = 0; other < k; ++other)
+            if (tq_operand_element(other) == e) return false;
+    }
+    return true;
+}
+static_assert(tq_operand_order_is_a_permutation(), "every element of a block sits at exactly one operand position");
 // Heavy task: record bytes 16 PART .. 16 PART + 15 -> operand chunks 5 PART .. 5 PART + 4
 template <int PART, int O>
 __device__ __forceinline__ void tq_expand_heavy(uint32_t box, uint32_t lut, uint32_t b_slot, int row) {
@@ -879,7 +389,7 @@ __global__ void __launch_bounds__(256) q8k_planes_kernel(const uint8_t *__restri
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PT_THREADS, 1)
-prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_constant__ CUtensorMap x_codes,
+prefill_pair_tq1_kernel(const PairParams p, const uint32_t *powers, const __grid_constant__ CUtensorMap x_codes,
                         const __grid_constant__ CUtensorMap w_rows, const __grid_constant__ CUtensorMap w_heads) {
     extern __shared__ __align__(1024) uint8_t smem[];
     TqControl *ctl = reinterpret_cast<TqControl *>(smem);
@@ -918,7 +428,9 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
         for (int c = 0; c < PT_LUT_COPIES; ++c) reinterpret_cast<uint2 *>(smem + PT_OFF_LUT)[v * PT_LUT_COPIES + c] = make_uint2(lo, hi);
     }
     __syncthreads();
-    if (warp == PT_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PP_TMEM_COLS);   // per CTA, see the Q4_K kernel
+    // Each CTA allocates its own tensor memory (cta_group::1: no pair-wide allocation protocol); the pair's MMAs then use
+    // the same columns in both.
+    if (warp == PT_MMA_WARP) tc::tmem_alloc(&ctl->tmem_base, PP_TMEM_COLS);
     tc::fence_before_sync();
     __syncthreads();
     tc::cluster_sync_all();
@@ -1142,20 +654,30 @@ prefill_pair_tq1_kernel(const TqParams p, const uint32_t *powers, const __grid_c
 }
 
 // ================================================================================================================
-// Q4_K x Q8_K on CTA pairs, reading activation PLANES (the arrangement of the TQ1_0 kernel above applied to the Q4_K
-// kernel at the top of this file; same exact-integer formulation, same tile and epilogue).  `q8k_planes_q4k_kernel`
+// Q4_K x Q8_K on CTA pairs.  A tile is 256 tokens x w weights, w = 16..80 in steps of 16.  `q8k_planes_q4k_kernel`
 // turns the Q8_K records into the codes as an (M, K) int8 matrix, x.d as a (K/256, M) float matrix and, per token and
-// block, the min-term operand {l_0..l_7 | h_0..h_7} as sixteen f16 (bsum pair sums split as 64 h + l).  What that
-// removes from the contraction kernel: the operand shift and its four code variants in the expanders (no carried words,
-// no shuffles), the thin K chunk (eight K = 32 MMAs per block instead of nine), the three 16-byte activation columns and
-// the two per-token warps (the min-term operand arrives by TMA ready to use, x.d comes to the epilogue by a global load
-// issued a block ahead).
-constexpr int PQ_E_WARPS = 8, PQ_X_WARPS = 5, PQ_X_GROUPS = 2;
-constexpr int PQ_X_WARP0 = PQ_E_WARPS, PQ_PAD_WARP0 = PQ_X_WARP0 + PQ_X_GROUPS * PQ_X_WARPS;   // 18, 19: complete the fifth group of four
-constexpr int PQ_ATMA_WARP = 20, PQ_WTMA_WARP = 21, PQ_MMA_WARP = 22;
-constexpr int PQ_THREADS = 32 * 24;
-constexpr int PQ_LAUNCH_REGS = 80, PQ_E_REGS = 96, PQ_IO_REGS = 24;
-static_assert(PQ_PAD_WARP0 == 18 && PQ_E_WARPS * (PQ_E_REGS - PQ_LAUNCH_REGS) <= 4 * (PQ_LAUNCH_REGS - PQ_IO_REGS), "warp groups and their register trade");
+// block, the min-term operand {l_0..l_7 | h_0..h_7} as sixteen f16 (bsum pair sums split as 64 h + l: those bytes arrive by
+// TMA ready for the K = 16 f16 MMA).  Per 256-block and CTA:
+//   raw weights  one TMA box copy of w/2 records (144 B each) and one of the partner's 16-byte headers into a 4-slot ring
+//   activations  two 128-byte-swizzled boxes of codes and two 16-byte columns of the min-term operand into a 3-slot ring
+//   expanders    two groups of 5 warps taking the blocks in turn, four lanes per weight (lane = one pair of sub-blocks):
+//                nibbles -> two scaled limbs (8a + c), written as the K-major 128-byte-swizzled operand; lane layout chosen
+//                so that the 16-byte stores of a quarter-warp never meet in a bank; the f16 rows {mn | 64 mn} of the min term
+//   MMA          8 int8 K steps (N = 2w) + 1 f16 K = 16 step (N = w), into one of two TMEM buffers of 256 columns
+//   epilogue     8 warps = 4 lane quarters x the two halves of the tile's weights; per element
+//                acc += x.d * (d * f32(8 hi + lo) - dmin * msum) in the reference's op order.  The int32 accumulators start
+//                at the bit pattern of 1.5 * 2^23 instead of zero (the epilogue writes it back after every read), so what
+//                comes out of TMEM is already the float 1.5 * 2^23 + limb: one packed subtraction converts two limbs.
+//                x.d comes by one global load per thread and block, issued a block ahead.
+// Measured on 512 x 14336 x 4096: 106 us (the kernel that read the Q8_K records as they lie, with the weight operand shifted
+// to meet them, three narrow activation columns and two per-token warps: 117.5 us; a single-CTA kernel: 191 us).
+// 24 warps at 80 registers; the epilogue takes 96, the copy and MMA lanes keep 24.
+constexpr int PQ_E_WARPS = 8, PQ_X_WARPS = 5, PQ_X_GROUPS = 2;   // two expander groups taking the blocks in turn (one: 121.6 us, three: 113.5 us, two: 108.1 us)
+constexpr int PQ_X_WARP0 = PQ_E_WARPS, PQ_PAD_WARP0 = PQ_X_WARP0 + PQ_X_GROUPS * PQ_X_WARPS;   // idle warps up to the next group of four
+constexpr int PQ_ATMA_WARP = (PQ_PAD_WARP0 + 3) / 4 * 4, PQ_WTMA_WARP = PQ_ATMA_WARP + 1, PQ_MMA_WARP = PQ_ATMA_WARP + 2;
+constexpr int PQ_THREADS = 32 * (PQ_ATMA_WARP + 4);
+constexpr int PQ_LAUNCH_REGS = 65536 / PQ_THREADS / 8 * 8, PQ_E_REGS = 96, PQ_IO_REGS = 24;
+static_assert(PQ_E_WARPS * (PQ_E_REGS - PQ_LAUNCH_REGS) <= 4 * (PQ_LAUNCH_REGS - PQ_IO_REGS), "warp groups and their register trade");
 constexpr int PQ_STAGES = 3, PQ_RAW_SLOTS = 4, PQ_RING = 8;
 constexpr int PQ_A_SLAB = 128 * 128, PQ_A_MIN = 2 * PQ_A_SLAB, PQ_A_COL = 128 * 16, PQ_A_SLOT = PQ_A_MIN + 2 * PQ_A_COL;   // 36 KB
 constexpr int PQ_B_SLAB = PP_RMAX * 128, PQ_B_M = 2 * PQ_B_SLAB, PQ_B_SLOT = 22 * 1024;
@@ -1183,16 +705,16 @@ static_assert(sizeof(QpControl) <= PQ_OFF_A, "control block");
 
 struct QpAt {   // blocks in order, tiles round-robin over the pairs
     int n0, m0, b, tile, pairs;
-    __device__ __forceinline__ void set_tile(const TqParams &p, int t) {
+    __device__ __forceinline__ void set_tile(const PairParams &p, int t) {
         tile = t;
         n0 = (t / p.m_tiles) * p.w;
         m0 = (t % p.m_tiles) * (2 * PP_TOKENS);
     }
-    __device__ __forceinline__ void advance(const TqParams &p) {
+    __device__ __forceinline__ void advance(const PairParams &p) {
         if (++b == p.nb) { b = 0; set_tile(p, tile + pairs); }
     }
 };
-__device__ __forceinline__ QpAt qp_first(const TqParams &p, int pair, int pairs) {
+__device__ __forceinline__ QpAt qp_first(const PairParams &p, int pair, int pairs) {
     QpAt at;
     at.b = 0;
     at.pairs = pairs;
@@ -1271,7 +793,7 @@ __global__ void __launch_bounds__(256) q8k_planes_q4k_kernel(const uint8_t *__re
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PQ_THREADS, 1)
-prefill_pair_q4k_planes_kernel(const TqParams p, const __grid_constant__ CUtensorMap x_codes, const __grid_constant__ CUtensorMap x_mins,
+prefill_pair_q4k_planes_kernel(const PairParams p, const __grid_constant__ CUtensorMap x_codes, const __grid_constant__ CUtensorMap x_mins,
                                const __grid_constant__ CUtensorMap w_rows, const __grid_constant__ CUtensorMap w_heads) {
     extern __shared__ __align__(1024) uint8_t smem[];
     QpControl *ctl = reinterpret_cast<QpControl *>(smem);
@@ -1553,13 +1075,13 @@ bool prefill_pair_supported(int fmt, long long n, long long k, long long m, cons
     if (fmt == F_TQ1_0)
         return m > PP_TOKENS && k > 0 && k % 2048 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
                (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
-    // above 128 tokens a pair's second CTA has work; K a multiple of 1024 keeps every Q8_K row a whole number of 16-byte
-    // units (TMA boxes), and Q4_K rows of 16-byte multiples at a 16-byte aligned base let TMA fetch the raw records
-    return fmt == F_Q4_K && m > PP_TOKENS && k > 0 && k % 1024 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
-           (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 15u) == 0;
+    // above 128 tokens a pair's second CTA has work; Q4_K rows are 16-byte multiples for every K, so a 16-byte aligned base
+    // lets TMA fetch the raw records; the activations come from planes of the library's own (the records need their 4 bytes)
+    return fmt == F_Q4_K && m > PP_TOKENS && k > 0 && k % 256 == 0 && n > 0 && n < (1LL << 31) && m < (1LL << 31) &&
+           (reinterpret_cast<uintptr_t>(w) & 15u) == 0 && (reinterpret_cast<uintptr_t>(xq) & 3u) == 0;
 }
 
-// The planes of the latest TQ1_0 call: one device allocation that only ever grows.  Calls are serialised by the
+// The planes of the latest call: one device allocation that only ever grows.  Calls are serialised by the
 // library and run on one stream, so the next call's plane kernel starts after this call's contraction has ended.  A
 // larger request gets a new allocation; the previous ones stay until the process ends, because work already queued (or a
 // captured graph) may still name them.
@@ -1605,7 +1127,7 @@ static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, c
         if (pairs < 1) return cudaErrorNotSupported;
         if (pairs > sm_count / 2) pairs = sm_count / 2;
     }
-    TqParams p;
+    PairParams p;
     p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
     p.m_tiles = (int)((a.m + 2 * PP_TOKENS - 1) / (2 * PP_TOKENS));
     p.w = pick_tile_width_tq1(a.n, p.m_tiles, pairs);
@@ -1641,8 +1163,6 @@ static cudaError_t launch_prefill_pair_tq1(const PrefillArgs &a, int sm_count, c
     return cudaGetLastError();
 }
 
-constexpr bool kQ4kOnPlanes = true;   // the Q4_K pair kernel that reads activation planes (false: the one that reads the Q8_K records as they lie)
-
 static cudaError_t launch_prefill_pair_q4k_planes(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_q4k_planes_kernel), PQ_SMEM);
     if (e == cudaSuccess) e = check_launch_registers(reinterpret_cast<const void *>(prefill_pair_q4k_planes_kernel), PQ_LAUNCH_REGS);
@@ -1657,7 +1177,7 @@ static cudaError_t launch_prefill_pair_q4k_planes(const PrefillArgs &a, int sm_c
         if (pairs < 1) return cudaErrorNotSupported;
         if (pairs > sm_count / 2) pairs = sm_count / 2;
     }
-    TqParams p;
+    PairParams p;
     p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
     p.m_tiles = (int)((a.m + 2 * PP_TOKENS - 1) / (2 * PP_TOKENS));
     p.w = pick_tile_width(a.n, p.m_tiles, pairs);
@@ -1698,50 +1218,12 @@ static cudaError_t launch_prefill_pair_q4k_planes(const PrefillArgs &a, int sm_c
     return cudaGetLastError();
 }
 
-int prefill_pair_launches(int fmt) { return fmt == F_TQ1_0 || kQ4kOnPlanes ? 2 : 1; }
+int prefill_pair_launches(int) { return 2; }   // plane kernel + contraction
 
 cudaError_t launch_prefill_pair(const PrefillArgs &a, int sm_count, cudaStream_t stream) {
     if (!prefill_pair_supported(a.fmt, a.n, a.k, a.m, a.w, a.xq)) return cudaErrorNotSupported;
     if (a.fmt == F_TQ1_0) return launch_prefill_pair_tq1(a, sm_count, stream);
-    if (kQ4kOnPlanes) return launch_prefill_pair_q4k_planes(a, sm_count, stream);
-    cudaError_t e = grant_dynamic_smem(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_SMEM);
-    if (e == cudaSuccess) e = check_launch_registers(reinterpret_cast<const void *>(prefill_pair_q4k_kernel), PP_LAUNCH_REGS);
-    if (e != cudaSuccess) return e;
-    // how many pairs the device can hold at once (one CTA per SM: the shared memory of a CTA fills an SM)
-    int pairs = 0;
-    {
-        cudaLaunchConfig_t probe = {};
-        probe.gridDim = dim3((unsigned)sm_count & ~1u);
-        probe.blockDim = dim3(PP_THREADS);
-        probe.dynamicSmemBytes = PP_SMEM;
-        if (cudaOccupancyMaxActiveClusters(&pairs, prefill_pair_q4k_kernel, &probe) != cudaSuccess) { cudaGetLastError(); pairs = sm_count / 2; }
-        if (pairs < 1) return cudaErrorNotSupported;
-        if (pairs > sm_count / 2) pairs = sm_count / 2;
-    }
-    PairParams p;
-    p.y = a.y; p.n = a.n; p.m = a.m; p.ldy = a.ldy; p.nb = (int)(a.k / 256); p.status = a.status;
-    p.m_tiles = (int)((a.m + 2 * PP_TOKENS - 1) / (2 * PP_TOKENS));
-    p.w = pick_tile_width(a.n, p.m_tiles, pairs);
-    p.n_tiles = (int)((a.n + p.w - 1) / p.w);
-    const long long tiles = (long long)p.m_tiles * p.n_tiles;
-    if (tiles < pairs) pairs = (int)tiles;
-    // the Q8_K matrix as (m) rows of 73 * nb 32-bit words; the weight matrix as (n) rows of 36 * nb words
-    CUtensorMap x_wide, x_narrow, w_rows;
-    e = encode_tile_map(&x_wide, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
-                        (unsigned long long)p.nb * 292, 32, PP_TOKENS, true);
-    if (e == cudaSuccess)
-        e = encode_tile_map(&x_narrow, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.xq, (unsigned long long)p.nb * 73, (unsigned long long)a.m,
-                            (unsigned long long)p.nb * 292, 4, PP_TOKENS, false);
-    if (e == cudaSuccess)
-        e = encode_tile_map(&w_rows, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.w, (unsigned long long)p.nb * 36, (unsigned long long)a.n,
-                            (unsigned long long)p.nb * 144, 36, (unsigned)(p.w / 2), false);
-    CUtensorMap w_heads;
-    if (e == cudaSuccess)
-        e = encode_tile_map(&w_heads, CU_TENSOR_MAP_DATA_TYPE_UINT32, a.w, (unsigned long long)p.nb * 36, (unsigned long long)a.n,
-                            (unsigned long long)p.nb * 144, 4, (unsigned)(p.w / 2), false);
-    if (e != cudaSuccess) return e;
-    prefill_pair_q4k_kernel<<<2 * pairs, PP_THREADS, PP_SMEM, stream>>>(p, x_wide, x_narrow, w_rows, w_heads);
-    return cudaGetLastError();
+    return launch_prefill_pair_q4k_planes(a, sm_count, stream);
 }
 
 }  // namespace weft
