@@ -72,7 +72,7 @@ DEFAULT_WORKLOAD = "q4_k_decode_14336x4096"
 NCU_DRAM_TRAFFIC = {
     "q4_k_decode_14336x4096": 33_078_272,
     "iq2_xxs_decode_28672x8192": 60_635_904,
-    "q4_k_prefill_4096x4096": 11_908_608,
+    "q4_k_prefill_4096x4096": 11_885_568,
     "q8_0_prefill_4096x4096": 20_104_448,
     "iq2_xxs_prefill_4096x4096": 6_777_344,
     "tq1_0_prefill_28672x8192": 69_316_352,
