@@ -60,13 +60,14 @@ struct PairParams {
     int *status;
 };
 
+// Sleep between failed polls (ns): single lanes that wait for a copy or for tensor memory, and whole warps.  A waiting
+// warp that polls without pause issues an instruction every few cycles; with these pauses the Q4_K kernel went from
+// 134 to 124 us on 512 x 14336 x 4096 (the TQ1_0 kernel did not change; lengths between 50 and 300 ns measure the same).
+constexpr uint32_t PP_LANE_NAP = 300, PP_WARP_NAP = 100;
+
 // Bounded wait by one thread; gives up as soon as another role (of either CTA) has raised the abort flag.  The suspending
 // form of the wait: a lane that spins on test_wait issues an instruction every few cycles and takes a third of its
 // scheduler's issue slots from the warps that work.
-// Sleep between failed polls (ns): single lanes that wait for a copy or for tensor memory, and whole warps.  A waiting
-// warp that polls without pause issues an instruction every few cycles; with these pauses the Q4_K kernel went from
-// 134 to 124 us on 512 x 14336 x 4096 (the TQ1_0 kernel did not change).
-constexpr uint32_t PP_LANE_NAP = 300, PP_WARP_NAP = 100;
 template <class Control>
 __device__ __forceinline__ bool pp_wait_one(uint64_t *bar, uint32_t parity, Control *ctl, uint32_t peer_abort, int *status) {
     for (uint32_t i = 0; i < (1u << 22); ++i) {
